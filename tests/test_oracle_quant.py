@@ -1,0 +1,128 @@
+"""The CPU oracle against the reference's own golden vectors for the block formats."""
+import json
+import os
+
+import numpy as np
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def lcg_weights(n, seed):
+    # crates/compute/tests/quant_gguf.rs weight generator shape: values in about [-1, 1)
+    s = np.uint64(seed * 2654435761 + 1)
+    out = np.empty(n, dtype=np.float32)
+    for i in range(n):
+        s = np.uint64((int(s) * 6364136223846793005 + 1442695040888963407) & 0xFFFFFFFFFFFFFFFF)
+        out[i] = ((int(s) >> 40) / float(1 << 24)) * 2.0 - 1.0
+    return out
+
+
+def test_q4k_hand_packed_superblock_decodes_to_the_documented_formula(oracle):
+    g = json.load(open(os.path.join(GOLD, "q4k_handpacked.json")))
+    quants = [(e * 7 + 3) % 16 for e in range(256)]
+    block = bytearray(g["d_bits"] + g["dmin_bits"] + g["packed"])
+    for grp in range(4):
+        for l in range(32):
+            at = grp * 64 + l
+            block.append(quants[at] | (quants[at + 32] << 4))
+    assert len(block) == 144
+    got = oracle.dequantize(oracle.Q4K, np.frombuffer(bytes(block), dtype=np.uint8), 256)
+    for e in range(256):
+        j = e // 32
+        want = np.float32(g["d"]) * np.float32(g["ls"][j]) * np.float32(quants[e]) - np.float32(g["dmin"]) * np.float32(g["lm"][j])
+        assert got[e] == want, (e, j)
+
+
+def test_q4k_scale_min_split_bytes(oracle):
+    import ctypes as C
+    g = json.load(open(os.path.join(GOLD, "q4k_handpacked.json")))
+    packed = (C.c_uint8 * 12)(*g["packed"])
+    for j in range(8):
+        sc, m = C.c_uint8(), C.c_uint8()
+        oracle.lib().tso_q4k_scale_min(j, packed, C.byref(sc), C.byref(m))
+        assert (sc.value, m.value) == (g["ls"][j], g["lm"][j])
+
+
+def test_q4k_round_trip_stays_inside_one_step(oracle):
+    w = lcg_weights(512, 11)
+    out = oracle.dequantize(oracle.Q4K, oracle.quantize(oracle.Q4K, w.reshape(1, -1)), 512)
+    for j in range(16):
+        sub = w[j * 32:(j + 1) * 32]
+        lo = min(0.0, sub.min())
+        hi = max(lo, sub.max())
+        bound = (hi - lo) / 15.0 * 0.5 + (hi - lo) * 0.05
+        assert np.all(np.abs(out[j * 32:(j + 1) * 32] - sub) <= bound)
+
+
+def test_q4k_min_term_carries_the_sign_and_zero_block(oracle):
+    w = np.array([-1.0 + (e % 32) / 64.0 for e in range(256)], dtype=np.float32)
+    out = oracle.dequantize(oracle.Q4K, oracle.quantize(oracle.Q4K, w.reshape(1, -1)), 256)
+    assert np.all(out < 0) and np.all(np.abs(out - w) < 0.05)
+    z = oracle.dequantize(oracle.Q4K, oracle.quantize(oracle.Q4K, np.zeros((1, 256), np.float32)), 256)
+    assert np.all(z == 0)
+
+
+def test_q6k_round_trip(oracle):
+    w = lcg_weights(512, 31)
+    out = oracle.dequantize(oracle.Q6K, oracle.quantize(oracle.Q6K, w.reshape(1, -1)), 512)
+    assert np.max(np.abs(out - w)) < 0.05
+    z = oracle.dequantize(oracle.Q6K, oracle.quantize(oracle.Q6K, np.zeros((1, 256), np.float32)), 256)
+    assert np.all(z == 0)
+
+
+def test_mxfp4_decoder_matches_ggml_bytes_floats_codebook_and_exponents(oracle):
+    g = json.load(open(os.path.join(GOLD, "mxfp4_ggml.json")))
+    got = oracle.dequantize(oracle.MXFP4, np.array(g["bytes"], dtype=np.uint8), 128)
+    want = np.array(g["floats"], dtype=np.float32)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    for i in range(16):
+        assert np.float32(oracle.lib().tso_mxfp4_value(i)) == np.float32(g["codebook"][i])
+    # index 8 is +0, not -0
+    assert np.float32(oracle.lib().tso_mxfp4_value(8)).view(np.uint32) == 0
+    for e in range(256):
+        got_e = np.float32(oracle.lib().tso_mxfp4_value(1)) * np.float32(oracle.lib().tso_mxfp4_scale(e))
+        assert got_e == np.float32(g["e8m0"][e]), e
+
+
+def test_mxfp4_own_encoder_round_trips(oracle):
+    rng = np.random.default_rng(3)
+    w = (rng.standard_normal(32 * 64) * 0.02).astype(np.float32)
+    q = oracle.quantize(oracle.MXFP4, w.reshape(1, -1))
+    out = oracle.dequantize(oracle.MXFP4, q, w.size)
+    for b in range(64):
+        blk, o = w[b * 32:(b + 1) * 32], out[b * 32:(b + 1) * 32]
+        amax = np.abs(blk).max()
+        # the coarsest code gap is 4 units of the block scale, and 12*scale < 2*amax
+        assert np.all(np.abs(o - blk) <= amax / 3.0 + 1e-9)
+    # idempotent in value: re-encoding decoded values decodes to the same floats
+    again = oracle.dequantize(oracle.MXFP4, oracle.quantize(oracle.MXFP4, out.reshape(1, -1)), w.size)
+    assert np.array_equal(again, out)
+
+
+def test_gemv_matches_dequantize_then_multiply(oracle):
+    n = 512
+    x = lcg_weights(n, 5)
+    for kind in (oracle.Q4K, oracle.Q6K, oracle.MXFP4):
+        rows = np.stack([lcg_weights(n, 20 + r) for r in range(4)])
+        q = oracle.quantize(kind, rows)
+        got = oracle.gemm_quant(kind, q, 4, n, x.reshape(1, -1))[0]
+        for i in range(4):
+            deq = oracle.dequantize(kind, q[i], n)
+            want = np.float32(0)
+            for c in range(n):
+                want = np.float32(want + np.float32(deq[c] * x[c]))
+            assert got[i] == want
+
+
+def test_f16_conversion_matches_numpy(oracle):
+    rng = np.random.default_rng(0)
+    x = np.concatenate([rng.standard_normal(4096).astype(np.float32) * s for s in (1e-8, 1e-5, 1e-3, 1.0, 100.0, 7e4)])
+    x = np.concatenate([x, np.array([0.0, -0.0, np.inf, -np.inf, 65504.0, 65520.0, 65519.99, 5.96e-8, 2.98e-8, 2.9802322e-8], np.float32)])
+    with np.errstate(over="ignore"):
+        want = x.astype(np.float16).view(np.uint16)
+    got = oracle.f32_to_f16_bits(x)
+    assert np.array_equal(got, want)
+    allbits = np.arange(65536, dtype=np.uint16)
+    back = oracle.f16_bits_to_f32(allbits)
+    ref = allbits.view(np.float16).astype(np.float32)
+    assert np.array_equal(back.view(np.uint32)[~np.isnan(ref)], ref.view(np.uint32)[~np.isnan(ref)])
