@@ -1,0 +1,267 @@
+/*
+ * tsb.h — C ABI of libtsb, a CUDA (sm_100a) backend for TurboSpark's
+ * speculative-decoding verify path.
+ *
+ * Each entry point replaces one operator of the reference's Metal backend
+ * (crates/gpu, "encode_*" functions) or one method of its SpeculativeProducer
+ * trait (crates/runtime/src/producer.rs); the comment above each declaration
+ * cites the reference interface it stands in for (path within the reference
+ * project : lines).
+ *
+ * Conventions, kept from the reference's operator API (crates/gpu/src/lib.rs:181-503):
+ *   - the caller owns every buffer; pointers are plain device pointers unless
+ *     a parameter is named host_*;
+ *   - quantized weights are the verbatim GGUF block bytes, one contiguous run
+ *     of blocks per output row, addressed as (region, byte offset);
+ *   - work is enqueued on the given CUDA stream (cudaStream_t passed as void*,
+ *     NULL = the legacy default stream) and the caller synchronises;
+ *   - precondition violations are refused before anything is enqueued;
+ *   - every function returns a tsb_status (0 = OK), never throws, never aborts;
+ *     tsb_last_error(ctx) returns the message of the last failure on that ctx;
+ *   - a ctx belongs to one host thread and one GPU.
+ *
+ * Activations are IEEE binary16, accumulation is fp32, norm weights are
+ * bfloat16 — the reference's storage contract
+ * (crates/gpu/src/shaders/dequant_q4_k.metal:98-130, rmsnorm.metal:70-95).
+ */
+#ifndef TSB_H
+#define TSB_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define TSB_API __attribute__((visibility("default")))
+#else
+#define TSB_API
+#endif
+
+typedef struct tsb_ctx tsb_ctx;
+typedef struct tsb_kv tsb_kv;
+typedef struct tsb_model tsb_model;
+typedef struct tsb_session tsb_session;
+typedef void* tsb_stream; /* cudaStream_t */
+
+typedef enum tsb_status {
+    TSB_OK = 0,
+    TSB_ERR_INVALID = 1,     /* bad argument; nothing was enqueued              */
+    TSB_ERR_CUDA = 2,        /* a CUDA runtime call failed                       */
+    TSB_ERR_UNSUPPORTED = 3, /* shape or format outside what the kernels cover   */
+    TSB_ERR_STATE = 4,       /* cursor / ordering contract violated              */
+    TSB_ERR_OOM = 5,         /* out of pages or device memory                    */
+    TSB_ERR_DEVICE = 6       /* a kernel reported an error word (bounded wait, bad index) */
+} tsb_status;
+
+/* Block formats.  The values in parentheses are the dtype tag bytes of the
+ * reference's resident weight index (crates/repack/src/resident_writer.rs:105,107,162). */
+typedef enum tsb_qtype {
+    TSB_Q4_K = 0, /* (7)  256 elements / 144 bytes: crates/compute/src/quant_gguf/q4_k.rs */
+    TSB_Q6_K = 1, /* (8)  256 elements / 210 bytes: crates/compute/src/quant_gguf/q6_k.rs */
+    TSB_MXFP4 = 2 /* (14) 32 elements / 17 bytes:   crates/compute/src/quant_gguf_mxfp4.rs */
+} tsb_qtype;
+
+/* ------------------------------------------------------------------ context */
+
+/* Replaces MetalContext::new (crates/gpu/src/context/mod.rs): one context per GPU per host thread. */
+TSB_API int32_t tsb_ctx_create(int32_t device_ordinal, tsb_ctx** out);
+TSB_API void tsb_ctx_destroy(tsb_ctx* ctx);
+/* Replaces GpuError's Display (crates/gpu/src/context/error.rs:5-22). */
+TSB_API const char* tsb_last_error(const tsb_ctx* ctx);
+TSB_API int32_t tsb_device_ordinal(const tsb_ctx* ctx);
+/* Device memory owned by the caller (replaces MetalContext buffer allocation). */
+TSB_API int32_t tsb_alloc(tsb_ctx* ctx, size_t bytes, void** out_dev);
+TSB_API int32_t tsb_free(tsb_ctx* ctx, void* dev);
+/* Replaces the resident weight buffer (crates/model-io/src/resident_buffer.rs): raw block bytes, verbatim. */
+TSB_API int32_t tsb_weights_upload(tsb_ctx* ctx, const void* host_bytes, size_t bytes, void** out_dev_region);
+TSB_API int32_t tsb_memcpy_h2d(tsb_ctx* ctx, tsb_stream s, void* dev, const void* host, size_t bytes);
+TSB_API int32_t tsb_memcpy_d2h(tsb_ctx* ctx, tsb_stream s, void* host, const void* dev, size_t bytes);
+/* Replaces PassEncoder commit_and_wait_checked (crates/gpu/src/context/pass.rs:180): waits, then
+ * surfaces both CUDA errors and the kernels' own error word. */
+TSB_API int32_t tsb_stream_sync(tsb_ctx* ctx, tsb_stream s);
+/* Bytes one row of `cols` elements occupies in the given format. */
+TSB_API int64_t tsb_row_bytes(int32_t qtype, int64_t cols);
+/* Number of kernel launches this ctx has enqueued since creation. */
+TSB_API uint64_t tsb_launch_count(const tsb_ctx* ctx);
+
+/* ---------------------------------------------------- quantized matmul (hot) */
+
+/* y[t, r] = sum_c W[r, c] * x[t, c],  W = `rows` rows of verbatim blocks at region + w_off,
+ * x [tokens, cols] f16, y [tokens, rows] f16 (y_f32 = 0) or f32 (y_f32 = 1), fp32 accumulate.
+ * A token's result never depends on the other tokens of the call (row invariance), so a
+ * decode step (tokens = 1) and a verify batch produce identical bits per token.
+ * Replaces encode_dequant_q4_k_gemv / encode_dequant_q6_k_gemv / encode_dequant_mxfp4_gemv
+ * (crates/gpu/src/dequant_q4_k_gemv.rs:110-140, dequant_q6_k_gemv.rs, dequant_ext_gemv.rs:176-201)
+ * for tokens = 1 and encode_dequant_kquant_gemm_batch (crates/gpu/src/dequant_kquant_gemm_batch.rs:96-126)
+ * for tokens > 1.  cols must be a whole number of blocks (256 for K-quants, 32 for MXFP4). */
+TSB_API int32_t tsb_gemm_quant(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* region, uint64_t w_off,
+                               int64_t rows, int64_t cols, const void* x_f16, void* y, int32_t tokens,
+                               int32_t y_f32);
+/* The reference's per-format names, kept so a binding reads like the original call sites. */
+TSB_API int32_t tsb_gemv_q4k(tsb_ctx* ctx, tsb_stream s, const void* region, uint64_t w_off, int64_t rows,
+                             int64_t cols, const void* x_f16, void* y_f16);
+TSB_API int32_t tsb_gemv_q6k(tsb_ctx* ctx, tsb_stream s, const void* region, uint64_t w_off, int64_t rows,
+                             int64_t cols, const void* x_f16, void* y_f16);
+TSB_API int32_t tsb_gemv_mxfp4(tsb_ctx* ctx, tsb_stream s, const void* region, uint64_t w_off, int64_t rows,
+                               int64_t cols, const void* x_f16, void* y_f16);
+TSB_API int32_t tsb_gemm_q4k(tsb_ctx* ctx, tsb_stream s, const void* region, uint64_t w_off, int64_t rows,
+                             int64_t cols, const void* x_f16, void* y_f16, int32_t tokens);
+TSB_API int32_t tsb_gemm_q6k(tsb_ctx* ctx, tsb_stream s, const void* region, uint64_t w_off, int64_t rows,
+                             int64_t cols, const void* x_f16, void* y_f16, int32_t tokens);
+TSB_API int32_t tsb_gemm_mxfp4(tsb_ctx* ctx, tsb_stream s, const void* region, uint64_t w_off, int64_t rows,
+                               int64_t cols, const void* x_f16, void* y_f16, int32_t tokens);
+
+/* out[i, :] = dequantized row row_ids[i] (row_ids NULL = rows 0..n-1), fp32, bit-exact with
+ * dequantize_q4_k / dequantize_q6_k / dequantize_mxfp4 (crates/compute/src/quant_gguf/q4_k.rs:67-108,
+ * q6_k.rs:52-95, quant_gguf_mxfp4.rs:114-141). */
+TSB_API int32_t tsb_dequant_rows(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* region, uint64_t w_off,
+                                 int64_t cols, const int32_t* row_ids, int32_t n_rows, float* out_f32);
+/* out[i, :] = f16(dequantized row token_ids[i] * out_scale).  Replaces encode_embed_lookup_q4_k /
+ * _mxfp4 (crates/gpu/src/shaders/dequant_q4_k.metal:142-169, dequant_ext.metal:176-189). */
+TSB_API int32_t tsb_embed_rows(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* region, uint64_t w_off,
+                               int64_t vocab_rows, int64_t cols, const int32_t* token_ids, int32_t n, void* out_f16,
+                               float out_scale);
+
+/* ------------------------------------------------------------ row operators */
+
+/* out[r,:] = f16( x[r,:] * rsqrt(mean(x^2) + eps) * w ), w bf16.  If residual != NULL, x[r,:] is first
+ * replaced by f16(x + residual) (the reference's residual_add_fp16 followed by rmsnorm_bf16w).
+ * Replaces encode_rms_norm rows variant (crates/gpu/src/shaders/rmsnorm.metal:70-95) and
+ * residual_add_fp16 (utility.metal:199-208). */
+TSB_API int32_t tsb_rmsnorm_rows(tsb_ctx* ctx, tsb_stream s, void* x_f16, const void* residual_f16,
+                                 const void* w_bf16, void* out_f16, int32_t rows, int32_t d, float eps);
+/* NeoX RoPE in place with one position per row: pairs (i, head_dim/2 + i), i < rotated_pairs, angle
+ * pos * theta^(-2i/head_dim).  x is [rows, row_stride] f16 with `heads` heads of head_dim at the start of
+ * each row.  Replaces encode_rope_neox_subdim_rows_positions (crates/gpu/src/shaders/rope.metal:80-180). */
+TSB_API int32_t tsb_rope_neox_rows_positions(tsb_ctx* ctx, tsb_stream s, void* x_f16, int32_t rows, int32_t heads,
+                                             int32_t head_dim, int32_t rotated_pairs, int64_t row_stride,
+                                             const int32_t* positions, float theta);
+/* out = f16( silu(gate) * up ).  gate/up/out are [rows, n] with the given row strides (elements).
+ * Replaces silu_mul_fp16 (utility.metal:41-52). */
+TSB_API int32_t tsb_silu_mul(tsb_ctx* ctx, tsb_stream s, const void* gate_f16, const void* up_f16, void* out_f16,
+                             int32_t rows, int32_t n, int64_t in_stride, int64_t out_stride);
+/* x = f16(x + y).  Replaces residual_add_fp16 (utility.metal:199-208). */
+TSB_API int32_t tsb_residual_add(tsb_ctx* ctx, tsb_stream s, void* x_f16, const void* y_f16, int64_t n);
+
+/* ------------------------------------------------------------ paged KV cache */
+
+/* An fp16 K/V cache for `layers` layers shared by up to max_seqs independent streams.  Storage is a
+ * pool of pages of page_tokens positions (a power of two >= 16); a stream's logical position p lives in
+ * page table[seq][p / page_tokens].  Replaces KvCacheManager (crates/gpu/src/kv_cache.rs:47-69,292-378),
+ * which is one linear buffer per layer; paging is this backend's addition for many streams. */
+TSB_API int32_t tsb_kv_create(tsb_ctx* ctx, int32_t layers, int32_t kv_heads, int32_t head_dim,
+                              int32_t page_tokens, int32_t num_pages, int32_t max_seqs, int32_t max_pages_per_seq,
+                              tsb_kv** out);
+TSB_API void tsb_kv_destroy(tsb_kv* kv);
+/* Make positions [0, tokens) of stream `seq` addressable (allocates pages; host side). */
+TSB_API int32_t tsb_kv_reserve(tsb_kv* kv, int32_t seq, int64_t tokens);
+/* Release every page of a stream and zero its cursor. */
+TSB_API int32_t tsb_kv_reset(tsb_kv* kv, int32_t seq);
+/* Cursor = number of committed positions.  Replaces KvCacheManager::position / advance. */
+TSB_API int64_t tsb_kv_cursor(const tsb_kv* kv, int32_t seq);
+TSB_API int32_t tsb_kv_set_cursor(tsb_kv* kv, int32_t seq, int64_t position);
+/* Replaces rewind_by (crates/gpu/src/kv_cache_rewind.rs:46-55): a cursor move; rows are overwritten later. */
+TSB_API int32_t tsb_kv_rewind_by(tsb_kv* kv, int32_t seq, int64_t count);
+/* Copy rows [pos0, pos0+n) of one layer to/from host, [n, kv_heads*head_dim] f16 (tests, prefix import). */
+TSB_API int32_t tsb_kv_write_rows(tsb_kv* kv, tsb_stream s, int32_t seq, int32_t layer, int64_t pos0, int32_t n,
+                                  const void* host_k_f16, const void* host_v_f16);
+TSB_API int32_t tsb_kv_read_rows(tsb_kv* kv, tsb_stream s, int32_t seq, int32_t layer, int64_t pos0, int32_t n,
+                                 void* host_k_f16, void* host_v_f16);
+/* Fill positions [0, tokens) of every layer of a stream with seeded pseudo-random f16 values in
+ * roughly N(0,1) (benchmark set-up: a pre-filled context without a prefill pass). */
+TSB_API int32_t tsb_kv_fill_random(tsb_kv* kv, tsb_stream s, int32_t seq, int64_t tokens, uint64_t seed);
+
+/* One row of a verify (or decode) batch, as the attention and KV-store kernels see it. */
+typedef struct tsb_row_desc {
+    int32_t seq;      /* stream the row belongs to                                      */
+    int32_t base;     /* committed prefix length: positions [0, base) are all attended   */
+    int32_t slot;     /* the row's own in-flight slot j: its K/V go to position base + j */
+    int32_t position; /* RoPE position (base + depth)                                    */
+    uint64_t mask[2]; /* bit j set = in-flight slot j is an ancestor-or-self of this row */
+} tsb_row_desc;
+
+/* Rotate q and k (NeoX, per-row position) and store k, v into the cache at each row's slot.
+ * qkv is [rows, (nq + 2*nkv) * head_dim] f16 (q heads, then k heads, then v heads); q is rotated in
+ * place.  Replaces the K/V projection's direct cache write plus encode_rope on Q and on the cached K
+ * (crates/runtime/src/families/llama/attn.rs:175-210,280-367). */
+TSB_API int32_t tsb_rope_store_kv(tsb_ctx* ctx, tsb_stream s, tsb_kv* kv, int32_t layer, void* qkv_f16,
+                                  const tsb_row_desc* rows_dev, int32_t rows, int32_t n_q_heads, float theta);
+
+/* Split-KV decode attention for a batch of rows.  Row r attends to its stream's committed prefix
+ * [0, base) and to the in-flight slots its mask names (a chain row m has bits 0..m; a tree row has its
+ * root path).  q is [rows, q_stride] f16 with nq*head_dim values per row, out [rows, nq*head_dim] f16.
+ * scratch must hold tsb_attn_scratch_bytes(...) bytes.  Replaces encode_attention_decode,
+ * encode_attention_decode_tree and the combine pass (crates/gpu/src/attention_decode.rs:920-1046,
+ * 1153-1230; shaders/attention.metal:285-446,983-1031).  rows of one stream must be adjacent and
+ * ordered by slot. */
+TSB_API int32_t tsb_attn_decode_rows(tsb_ctx* ctx, tsb_stream s, tsb_kv* kv, int32_t layer, const void* q_f16,
+                                     int64_t q_stride, void* out_f16, const tsb_row_desc* rows_dev,
+                                     const tsb_row_desc* rows_host, int32_t rows, int32_t n_q_heads, float scale,
+                                     void* scratch, size_t scratch_bytes);
+TSB_API size_t tsb_attn_scratch_bytes(int32_t rows, int32_t n_q_heads, int32_t head_dim);
+
+/* In-place compaction of an accepted tree path: for every layer and for K and V, row base+r <- row
+ * base+path[r], r < keep.  path[0] must be 0 and path strictly increasing (so path[r] >= r): the only
+ * shape for which an in-place gather is race-free.  Replaces encode_gather_rows_fp16 driven by
+ * dflash_tree_compact (crates/gpu/src/dflash_conv.rs:199-259, crates/runtime/src/families/qwen/dflash_tree.rs:106-207). */
+TSB_API int32_t tsb_kv_commit_path(tsb_ctx* ctx, tsb_stream s, tsb_kv* kv, int32_t seq, int64_t base,
+                                   const uint32_t* host_path, int32_t keep);
+
+/* --------------------------------------------------------------- acceptance */
+
+/* crates/selection/src/shaping.rs:40-50.  top_p <= 0 and min_p <= 0 mean "off". */
+typedef struct tsb_shaping {
+    double temperature;
+    uint32_t top_k;
+    uint32_t _pad;
+    double top_p;
+    double repetition_penalty;
+    double presence_penalty;
+    double frequency_penalty;
+    double min_p;
+    uint64_t seed;
+} tsb_shaping;
+
+typedef struct tsb_accept_out {
+    int32_t accepted;     /* accepted prefix length                                      */
+    int32_t draws;        /* uniforms consumed                                           */
+    int32_t tokens[16];   /* accepted proposals, then the corrected / bonus token        */
+    int32_t status;       /* 0 ok, 1 non-finite logit                                     */
+    int32_t _pad;
+    double margin_accept; /* min |r*q(x) - p(x)| over tested proposals                    */
+    double margin_draw;   /* distance from the uniform to the nearest cumulative boundary */
+} tsb_accept_out;
+
+/* One round's acceptance for `batch` independent streams, on the device.  Per stream b:
+ * target_logits [(k+1), V] f16, draft_logits [k, V] f16, proposals [k], uniforms [2k+1] u64 (the
+ * values derive_step_value would give for consecutive draw steps; mapped through the top-53-bit rule).
+ * For each proposal: accept iff r*q(x) <= p(x) over the shaped distributions; on rejection draw the
+ * corrected token from the normalised max(p-q, 0) in p's rank order (from p when the residual mass is
+ * below 1e-12); on full acceptance draw the bonus from the last row.  temperature 0 = argmax equality.
+ * Replaces the host-side accept step of the round loop (crates/runtime/src/speculative.rs:694-754,
+ * 861-879) and select / shaped_distribution / residual (crates/selection/src/choose.rs:62-232,
+ * distribution.rs:57-125).  Only temperature, top_k = 0, top_p off, min_p off, penalties off are
+ * accepted by this entry point; other shaping is refused with TSB_ERR_UNSUPPORTED. */
+TSB_API int32_t tsb_accept(tsb_ctx* ctx, tsb_stream s, const void* target_logits_f16, const void* draft_logits_f16,
+                           const int32_t* proposals, const uint64_t* uniforms, int32_t batch, int32_t k,
+                           int32_t vocab, const tsb_shaping* shaping, tsb_accept_out* out_dev, void* scratch,
+                           size_t scratch_bytes);
+TSB_API size_t tsb_accept_scratch_bytes(int32_t batch, int32_t k, int32_t vocab);
+
+/* token[b] = draw from the shaped distribution of logits[b, :] with uniforms[b] (argmax at temperature 0).
+ * Replaces select / ShapedDistribution::draw on the draft side (crates/runtime/src/speculative.rs:636-659). */
+TSB_API int32_t tsb_sample(tsb_ctx* ctx, tsb_stream s, const void* logits_f16, const uint64_t* uniforms,
+                           int32_t batch, int32_t vocab, const tsb_shaping* shaping, int32_t* tokens_dev,
+                           double* margins_dev, void* scratch, size_t scratch_bytes);
+
+/* Uniform sources: mode 0 = derive_step_value(seed, step) (crates/selection/src/derive.rs:20-48),
+ * mode 1 = Philox4x32-10 keyed by seed with counter = step (this backend's addition). */
+TSB_API uint64_t tsb_uniform_u64(int32_t mode, uint64_t seed, uint64_t step);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TSB_H */

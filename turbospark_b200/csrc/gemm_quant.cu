@@ -1,0 +1,622 @@
+// Fused dequantise + matmul over verbatim GGUF blocks (Q4_K, Q6_K, MXFP4).
+//
+// One kernel shape serves the M = 1 draft step and the K+1 verify batch:
+// weights stream HBM -> shared memory through 1-D bulk async copies
+// (cp.async.bulk, mbarrier completion) issued by a producer warp into a ring of
+// stages; eight consumer warps rebuild f16 operands from the packed nibbles in
+// registers and feed mma.sync m16n8k16 with the weights as the 16-row A operand
+// and up to eight tokens as the B operand, fp32 accumulation.  A token is one B
+// column, so its result does not depend on how many other tokens share the call
+// (decode and verify agree bit for bit per token).
+//
+// The kernel is HBM-bound for tokens <= 8: per 16x256 weight tile it moves 2304
+// bytes (Q4_K) and issues ~200 warp instructions, about half the SM's issue
+// slots at full memory bandwidth.
+//
+// A CTA owns 16 weight rows over the whole reduction dimension; its eight
+// consumer warps take one 256-column block each per stage and the partial sums
+// meet in shared memory in a fixed order (deterministic).
+//
+// Programmatic dependent launch: the weight prefetch does not depend on the
+// previous kernel, so the producer warp starts before griddepcontrol.wait; only
+// the consumers (which read activations and write y) wait.
+#include "gemm_quant.cuh"
+
+namespace {
+
+constexpr int TILE_ROWS = 16;
+constexpr int STAGE_UNITS = 8;  // 256-column units per row per stage (one per consumer warp)
+constexpr int CONSUMER_WARPS = 8;
+constexpr int GEMM_THREADS = (CONSUMER_WARPS + 1) * 32;
+constexpr int NUM_STAGES = 4;
+// Row stride inside a stage: the payload (<= 8*210 + 30 slack) rounded so that
+// stride = 64 (mod 128) bytes, which makes the 16-byte fragment loads of the
+// eight row groups hit distinct banks.
+__host__ __device__ constexpr int row_stride_for(int unit_bytes) {
+    int span = STAGE_UNITS * unit_bytes + 32;
+    int s = (span + 127) / 128 * 128 + 64;
+    return s;
+}
+
+template <int QT>
+struct Fmt;
+template <>
+struct Fmt<TSB_Q4_K> {
+    static constexpr int UNIT_BYTES = 144;
+};
+template <>
+struct Fmt<TSB_Q6_K> {
+    static constexpr int UNIT_BYTES = 210;
+};
+template <>
+struct Fmt<TSB_MXFP4> {
+    static constexpr int UNIT_BYTES = 136;  // eight 17-byte blocks
+};
+
+__device__ __forceinline__ uint32_t lds_u32_unaligned(const uint8_t* p) {
+    uint32_t a = smem_u32(p);
+    uint32_t base = a & ~3u;
+    uint32_t lo, hi;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(lo) : "r"(base));
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(hi) : "r"(base + 4));
+    return __funnelshift_r(lo, hi, (a & 3u) * 8u);
+}
+
+// ---- Q4_K: one 144-byte superblock for rows (gid, gid+8) -------------------
+// Layout (crates/compute/src/quant_gguf/q4_k.rs:17-41): f16 d, f16 dmin, 12
+// packed bytes of 6-bit scales/mins, 128 nibble bytes; in group g (64 elements)
+// byte l holds element 64g+l (low nibble, sub-block 2g) and 64g+32+l (high
+// nibble, sub-block 2g+1); w = d*sc*q - dmin*m.
+//
+// q*sc <= 15*63 is exact in f16, so the A operand is q*sc, built as
+// fma(1024+q, sc, -1024*sc) from the (nibble | 0x6400) bit pattern, and the
+// block's sum needs one multiply by d afterwards.  The min term is a second,
+// tiny contraction over the eight sub-blocks: sum_sub m[sub] * xsum[sub].
+template <int NT>
+__device__ __forceinline__ void q4k_block(const uint8_t* rA, const uint8_t* rB, const ActOperand& act, int cols,
+                                          int tokens, int blk, int gid, int tig, float (&acc)[NT][4]) {
+    const uint4 hA = *reinterpret_cast<const uint4*>(rA);
+    const uint4 hB = *reinterpret_cast<const uint4*>(rB);
+    const int h = tig >> 1;
+    const int l0 = (tig & 1) * 16;
+    const int subs_per_row = cols >> 5;
+
+    float cmain[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) cmain[nt][i] = 0.f;
+    const __half2 ddA = *reinterpret_cast<const __half2*>(&hA.x);
+    const __half2 ddB = *reinterpret_cast<const __half2*>(&hB.x);
+    const float dA = __low2float(ddA), dminA = __high2float(ddA);
+    const float dB = __low2float(ddB), dminB = __high2float(ddB);
+
+    // 6-bit fields as bytes: sc0..3 | sc4..7 | m0..3 | m4..7
+    const uint32_t scA_lo = hA.y & 0x3F3F3F3Fu, scA_hi = (hA.w & 0x0F0F0F0Fu) | ((hA.y >> 2) & 0x30303030u);
+    const uint32_t mA_lo = hA.z & 0x3F3F3F3Fu, mA_hi = ((hA.w >> 4) & 0x0F0F0F0Fu) | ((hA.z >> 2) & 0x30303030u);
+    const uint32_t scB_lo = hB.y & 0x3F3F3F3Fu, scB_hi = (hB.w & 0x0F0F0F0Fu) | ((hB.y >> 2) & 0x30303030u);
+    const uint32_t mB_lo = hB.z & 0x3F3F3F3Fu, mB_hi = ((hB.w >> 4) & 0x0F0F0F0Fu) | ((hB.z >> 2) & 0x30303030u);
+
+    // --- min term: A = mins of sub-blocks (2tig, 2tig+1), B = xsum hi / lo
+    {
+        const uint32_t bb = (2u * tig) & 3u;
+        const uint32_t sel = bb | (4u << 4) | ((bb + 1u) << 8) | (4u << 12);
+        uint32_t amin[2];
+        amin[0] = __byte_perm(tig < 2 ? mA_lo : mA_hi, 0x64646464u, sel);
+        amin[1] = __byte_perm(tig < 2 ? mB_lo : mB_hi, 0x64646464u, sel);
+        const uint32_t k1024 = 0x64006400u;
+        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(amin[0]) : "r"(amin[0]), "r"(k1024));
+        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(amin[1]) : "r"(amin[1]), "r"(k1024));
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            const int token = nt * 8 + gid;
+            uint32_t bhi = 0, blo = 0;
+            if (token < tokens) {
+                const size_t o = (size_t)token * subs_per_row + blk * 8 + 2 * tig;
+                bhi = __ldg(reinterpret_cast<const uint32_t*>(act.xs_hi + o));
+                blo = __ldg(reinterpret_cast<const uint32_t*>(act.xs_lo + o));
+            }
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            mma_1688(c, amin, bhi);
+            mma_1688(c, amin, blo);
+            acc[nt][0] -= dminA * c[0];
+            acc[nt][1] -= dminA * c[1];
+            acc[nt][2] -= dminB * c[2];
+            acc[nt][3] -= dminB * c[3];
+        }
+    }
+
+    const uint32_t selE = 0x4040u | ((2u * h) * 0x0101u);
+    const uint32_t selO = 0x4040u | ((2u * h + 1u) * 0x0101u);
+    const uint32_t kNeg1024 = 0xE400E400u;  // half2(-1024)
+    const uint32_t kNeg64 = 0xD400D400u;    // half2(-64)
+
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        const int g = 2 * r + h;
+        const uint4 qA = *reinterpret_cast<const uint4*>(rA + 16 + g * 32 + l0);
+        const uint4 qB = *reinterpret_cast<const uint4*>(rB + 16 + g * 32 + l0);
+        // scales of sub-blocks 2g (low nibbles) and 2g+1 (high nibbles) as half2(sc, sc)
+        uint32_t scLA = __byte_perm(r ? scA_hi : scA_lo, 0x64646464u, selE);
+        uint32_t scHA = __byte_perm(r ? scA_hi : scA_lo, 0x64646464u, selO);
+        uint32_t scLB = __byte_perm(r ? scB_hi : scB_lo, 0x64646464u, selE);
+        uint32_t scHB = __byte_perm(r ? scB_hi : scB_lo, 0x64646464u, selO);
+        const uint32_t k1024 = 0x64006400u;
+        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(scLA) : "r"(scLA), "r"(k1024));
+        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(scHA) : "r"(scHA), "r"(k1024));
+        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(scLB) : "r"(scLB), "r"(k1024));
+        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(scHB) : "r"(scHB), "r"(k1024));
+        uint32_t offLA, offHA, offLB, offHB;
+        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(offLA) : "r"(scLA), "r"(kNeg1024));
+        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(offHA) : "r"(scHA), "r"(kNeg64));
+        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(offLB) : "r"(scLB), "r"(kNeg1024));
+        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(offHB) : "r"(scHB), "r"(kNeg64));
+
+        const int k_lo = blk * 256 + g * 64 + l0;  // 16 consecutive columns of sub-block 2g
+        const uint32_t wA[4] = {qA.x, qA.y, qA.z, qA.w};
+        const uint32_t wB[4] = {qB.x, qB.y, qB.z, qB.w};
+#pragma unroll
+        for (int jj = 0; jj < 2; jj++) {
+            // eight columns (two mma steps) of activations per token tile
+            uint4 xl[NT], xh[NT];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const int token = nt * 8 + gid;
+                if (token < tokens) {
+                    const uint4* p = reinterpret_cast<const uint4*>(act.xp + (size_t)token * cols + k_lo) + jj;
+                    xl[nt] = __ldg(p);
+                    xh[nt] = __ldg(p + 4);  // +32 columns: sub-block 2g+1
+                } else {
+                    xl[nt] = xh[nt] = make_uint4(0, 0, 0, 0);
+                }
+            }
+#pragma unroll
+            for (int j2 = 0; j2 < 2; j2++) {
+                const int j = jj * 2 + j2;
+                uint32_t alo[4], ahi[4];
+                const uint32_t a = wA[j], b = wB[j];
+                const uint32_t a8 = a >> 8, b8 = b >> 8;
+                alo[0] = hfma2_u32(lop3_and_or(a, 0x000F000Fu, 0x64006400u), scLA, offLA);
+                alo[1] = hfma2_u32(lop3_and_or(b, 0x000F000Fu, 0x64006400u), scLB, offLB);
+                alo[2] = hfma2_u32(lop3_and_or(a8, 0x000F000Fu, 0x64006400u), scLA, offLA);
+                alo[3] = hfma2_u32(lop3_and_or(b8, 0x000F000Fu, 0x64006400u), scLB, offLB);
+                ahi[0] = hfma2_u32(lop3_and_or(a, 0x00F000F0u, 0x54005400u), scHA, offHA);
+                ahi[1] = hfma2_u32(lop3_and_or(b, 0x00F000F0u, 0x54005400u), scHB, offHB);
+                ahi[2] = hfma2_u32(lop3_and_or(a8, 0x00F000F0u, 0x54005400u), scHA, offHA);
+                ahi[3] = hfma2_u32(lop3_and_or(b8, 0x00F000F0u, 0x54005400u), scHB, offHB);
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    uint32_t bl[2], bh[2];
+                    bl[0] = j2 ? xl[nt].z : xl[nt].x;
+                    bl[1] = j2 ? xl[nt].w : xl[nt].y;
+                    bh[0] = j2 ? xh[nt].z : xh[nt].x;
+                    bh[1] = j2 ? xh[nt].w : xh[nt].y;
+                    mma_16816(cmain[nt], alo, bl);
+                    mma_16816(cmain[nt], ahi, bh);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        acc[nt][0] += dA * cmain[nt][0];
+        acc[nt][1] += dA * cmain[nt][1];
+        acc[nt][2] += dB * cmain[nt][2];
+        acc[nt][3] += dB * cmain[nt][3];
+    }
+}
+
+// ---- MXFP4: eight 17-byte blocks (256 columns) for rows (gid, gid+8) -------
+// Block (crates/compute/src/quant_gguf_mxfp4.rs:60-78): e8m0 byte, 16 nibble
+// bytes; byte j = element j (low) and j+16 (high); w = LUT[code] * 2^(e-128)
+// with LUT = 2 * e2m1.  The hardware e2m1x2 -> f16x2 conversion yields the
+// e2m1 value, so the fp32 partial sum is doubled before the block scale 2^(e-128) multiplies it.
+__device__ __forceinline__ void cvt_e2m1x4(uint32_t w, uint32_t (&out)[4]) {
+    // out[i] = half2( e2m1(byte i low nibble), e2m1(byte i high nibble) )
+    asm volatile(
+        "{\n"
+        ".reg .b8 b0, b1, b2, b3;\n"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n"
+        "}\n"
+        : "=r"(out[0]), "=r"(out[1]), "=r"(out[2]), "=r"(out[3])
+        : "r"(w));
+}
+__device__ __forceinline__ float mxfp4_scale_dev(uint32_t e) {
+    // crates/compute/src/quant_gguf_mxfp4.rs:95-102: 2^(e-128), subnormal for e < 2.
+    return __uint_as_float(e < 2 ? (0x00200000u << e) : ((e - 1u) << 23));
+}
+
+template <int NT>
+__device__ __forceinline__ void mxfp4_unit(const uint8_t* rA, const uint8_t* rB, const ActOperand& act, int cols,
+                                           int tokens, int unit, int gid, int tig, float (&acc)[NT][4]) {
+#pragma unroll 2
+    for (int b = 0; b < 8; b++) {
+        const uint8_t* pA = rA + b * 17;
+        const uint8_t* pB = rB + b * 17;
+        const float sA = mxfp4_scale_dev(pA[0]);
+        const float sB = mxfp4_scale_dev(pB[0]);
+        const uint32_t wA = lds_u32_unaligned(pA + 1 + 4 * tig);
+        const uint32_t wB = lds_u32_unaligned(pB + 1 + 4 * tig);
+        uint32_t cA[4], cB[4];
+        cvt_e2m1x4(wA, cA);
+        cvt_e2m1x4(wB, cB);
+        // byte i of the word is element 4tig+i (low) and 16+4tig+i (high); the
+        // swizzled activation row stores (x0,x2),(x1,x3), so pair bytes (0,2),(1,3).
+        uint32_t alo[4], ahi[4];
+        alo[0] = __byte_perm(cA[0], cA[2], 0x5410);
+        alo[1] = __byte_perm(cB[0], cB[2], 0x5410);
+        alo[2] = __byte_perm(cA[1], cA[3], 0x5410);
+        alo[3] = __byte_perm(cB[1], cB[3], 0x5410);
+        ahi[0] = __byte_perm(cA[0], cA[2], 0x7632);
+        ahi[1] = __byte_perm(cB[0], cB[2], 0x7632);
+        ahi[2] = __byte_perm(cA[1], cA[3], 0x7632);
+        ahi[3] = __byte_perm(cB[1], cB[3], 0x7632);
+        const int k0 = unit * 256 + b * 32 + 4 * tig;
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            const int token = nt * 8 + gid;
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t bl[2] = {0, 0}, bh[2] = {0, 0};
+            if (token < tokens) {
+                const uint2* p = reinterpret_cast<const uint2*>(act.xp + (size_t)token * cols + k0);
+                const uint2 l = __ldg(p), hh = __ldg(p + 4);  // +16 columns
+                bl[0] = l.x, bl[1] = l.y, bh[0] = hh.x, bh[1] = hh.y;
+            }
+            mma_16816(c, alo, bl);
+            mma_16816(c, ahi, bh);
+            // the hardware conversion yields e2m1 = LUT / 2, so the sum is doubled (exactly)
+            acc[nt][0] += sA * (c[0] + c[0]);
+            acc[nt][1] += sA * (c[1] + c[1]);
+            acc[nt][2] += sB * (c[2] + c[2]);
+            acc[nt][3] += sB * (c[3] + c[3]);
+        }
+    }
+}
+
+// ---- Q6_K: one 210-byte superblock for rows (gid, gid+8) -------------------
+// Layout (crates/compute/src/quant_gguf/q6_k.rs:17-50): ql[128], qh[64],
+// int8 sc[16], f16 d; per half h and l < 32 the four 6-bit values of elements
+// 128h + l + 32k (k = 0..3) take their low nibble from ql[64h + l + 32(k&1)]
+// (low nibble for k < 2, high for k >= 2) and bits 2k..2k+1 of qh[32h + l];
+// w = d * sc[8h + l/16 + 2k] * (q - 32).  One mma covers exactly one 16-element
+// scale group, so the int8 scale multiplies the fp32 partial sum.
+__device__ __forceinline__ float s8_to_float(uint32_t byte) {
+    // exact: (0x4B000000 | (b ^ 0x80)) is 8388608 + (b ^ 0x80)
+    return __uint_as_float(0x4B000000u | ((byte ^ 0x80u) & 0xFFu)) - 8388736.0f;
+}
+
+template <int NT>
+__device__ __forceinline__ void q6k_block(const uint8_t* rA, const uint8_t* rB, const ActOperand& act, int cols,
+                                          int tokens, int blk, int gid, int tig, float (&acc)[NT][4]) {
+    float blkacc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) blkacc[nt][i] = 0.f;
+    const uint32_t k1056 = 0x64206420u;  // half2(1056) = 1024 + 32
+#pragma unroll 1
+    for (int hh = 0; hh < 2; hh++) {
+#pragma unroll
+        for (int m = 0; m < 2; m++) {
+            const int l = 16 * m + 4 * tig;
+            const uint32_t qhA = lds_u32_unaligned(rA + 128 + 32 * hh + l);
+            const uint32_t qhB = lds_u32_unaligned(rB + 128 + 32 * hh + l);
+            const uint32_t qlA0 = lds_u32_unaligned(rA + 64 * hh + l), qlA1 = lds_u32_unaligned(rA + 64 * hh + 32 + l);
+            const uint32_t qlB0 = lds_u32_unaligned(rB + 64 * hh + l), qlB1 = lds_u32_unaligned(rB + 64 * hh + 32 + l);
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const uint32_t la = (k & 1) ? qlA1 : qlA0, lb = (k & 1) ? qlB1 : qlB0;
+                const uint32_t va = (((k & 2) ? (la >> 4) : la) & 0x0F0F0F0Fu) | (((qhA >> (2 * k)) & 0x03030303u) << 4);
+                const uint32_t vb = (((k & 2) ? (lb >> 4) : lb) & 0x0F0F0F0Fu) | (((qhB >> (2 * k)) & 0x03030303u) << 4);
+                uint32_t a[4];
+                a[0] = lop3_and_or(va, 0x00FF00FFu, 0x64006400u);
+                a[1] = lop3_and_or(vb, 0x00FF00FFu, 0x64006400u);
+                a[2] = lop3_and_or(va >> 8, 0x00FF00FFu, 0x64006400u);
+                a[3] = lop3_and_or(vb >> 8, 0x00FF00FFu, 0x64006400u);
+#pragma unroll
+                for (int i = 0; i < 4; i++) asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(a[i]) : "r"(a[i]), "r"(k1056));
+                const int si = 8 * hh + m + 2 * k;
+                const float sA = s8_to_float(rA[192 + si]);
+                const float sB = s8_to_float(rB[192 + si]);
+                const int k0 = blk * 256 + 128 * hh + 32 * k + l;
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const int token = nt * 8 + gid;
+                    float c[4] = {0.f, 0.f, 0.f, 0.f};
+                    uint32_t bb[2] = {0, 0};
+                    if (token < tokens) {
+                        const uint2 x = __ldg(reinterpret_cast<const uint2*>(act.xp + (size_t)token * cols + k0));
+                        bb[0] = x.x, bb[1] = x.y;
+                    }
+                    mma_16816(c, a, bb);
+                    blkacc[nt][0] += sA * c[0];
+                    blkacc[nt][1] += sA * c[1];
+                    blkacc[nt][2] += sB * c[2];
+                    blkacc[nt][3] += sB * c[3];
+                }
+            }
+        }
+    }
+    const float dA = __half2float(__ushort_as_half((unsigned short)(rA[208] | (rA[209] << 8))));
+    const float dB = __half2float(__ushort_as_half((unsigned short)(rB[208] | (rB[209] << 8))));
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        acc[nt][0] += dA * blkacc[nt][0];
+        acc[nt][1] += dA * blkacc[nt][1];
+        acc[nt][2] += dB * blkacc[nt][2];
+        acc[nt][3] += dB * blkacc[nt][3];
+    }
+}
+
+template <int QT, int NT, bool Y_F32>
+__global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
+    gemm_quant_kernel(const uint8_t* __restrict__ W, int64_t rows, int units /*256-col units per row*/,
+                      ActOperand act, int cols, void* __restrict__ y, int64_t y_stride, int tokens,
+                      uint32_t* __restrict__ err) {
+    constexpr int UB = Fmt<QT>::UNIT_BYTES;
+    constexpr int ROW_STRIDE = row_stride_for(UB);
+    constexpr int STAGE_BYTES = TILE_ROWS * ROW_STRIDE;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+    uint64_t* empty = full + NUM_STAGES;
+    uint8_t* stages = smem + 128;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t row0 = (int64_t)blockIdx.x * TILE_ROWS;
+    const int nrows = (int)min((int64_t)TILE_ROWS, rows - row0);
+    const int iters = (units + STAGE_UNITS - 1) / STAGE_UNITS;
+    const int64_t row_bytes = (int64_t)units * UB;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NUM_STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], CONSUMER_WARPS);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == CONSUMER_WARPS) {
+        // ---- producer: one bulk copy per row per stage; sources are rounded
+        // down to 16 bytes (formats whose rows are not 16-byte multiples) and
+        // the consumer skips the same slack.
+        for (int it = 0; it < iters; it++) {
+            const int s = it % NUM_STAGES;
+            if (it >= NUM_STAGES) {
+                if (!mbar_wait(&empty[s], ((it / NUM_STAGES) - 1) & 1, err)) return;
+            }
+            const int nun = min(STAGE_UNITS, units - it * STAGE_UNITS);
+            uint32_t bytes = 0;
+            const uint8_t* src = nullptr;
+            if (lane < nrows) {
+                const uint8_t* p = W + (row0 + lane) * row_bytes + (int64_t)it * STAGE_UNITS * UB;
+                const uint32_t slack = (uint32_t)(reinterpret_cast<uintptr_t>(p) & 15u);
+                src = p - slack;
+                bytes = (slack + (uint32_t)nun * UB + 15u) & ~15u;
+            }
+            uint32_t total = bytes;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+            if (lane == 0) mbar_expect_tx(&full[s], total);
+            __syncwarp();
+            if (lane < nrows) bulk_g2s(stages + s * STAGE_BYTES + lane * ROW_STRIDE, src, bytes, &full[s]);
+        }
+        pdl_launch_dependents();
+        return;
+    }
+
+    // ---- consumers
+    const int gid = lane >> 2, tig = lane & 3;
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[nt][i] = 0.f;
+
+    const uint32_t slackA = (uint32_t)(reinterpret_cast<uintptr_t>(W + (row0 + gid) * row_bytes) & 15u);
+    const uint32_t slackB = (uint32_t)(reinterpret_cast<uintptr_t>(W + (row0 + gid + 8) * row_bytes) & 15u);
+
+    pdl_wait();  // activations come from the previous kernel
+
+    bool ok = true;
+    for (int it = 0; it < iters && ok; it++) {
+        const int s = it % NUM_STAGES;
+        ok = mbar_wait(&full[s], (it / NUM_STAGES) & 1, err);
+        if (!ok) break;
+        const int nun = min(STAGE_UNITS, units - it * STAGE_UNITS);
+        if (warp < nun) {
+            // slack of this stage's source address: the row start's slack plus the stage offset
+            const uint32_t stA = (slackA + (uint32_t)((int64_t)it * STAGE_UNITS * UB)) & 15u;
+            const uint32_t stB = (slackB + (uint32_t)((int64_t)it * STAGE_UNITS * UB)) & 15u;
+            const uint8_t* rA = stages + s * STAGE_BYTES + gid * ROW_STRIDE + stA + warp * UB;
+            const uint8_t* rB = stages + s * STAGE_BYTES + (gid + 8) * ROW_STRIDE + stB + warp * UB;
+            const int unit = it * STAGE_UNITS + warp;
+            if constexpr (QT == TSB_Q4_K) q4k_block<NT>(rA, rB, act, cols, tokens, unit, gid, tig, acc);
+            if constexpr (QT == TSB_MXFP4) mxfp4_unit<NT>(rA, rB, act, cols, tokens, unit, gid, tig, acc);
+            if constexpr (QT == TSB_Q6_K) q6k_block<NT>(rA, rB, act, cols, tokens, unit, gid, tig, acc);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+    }
+    pdl_launch_dependents();
+
+    // ---- fixed-order reduction over the eight consumer warps
+    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
+    float* red = reinterpret_cast<float*>(stages);
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) red[((warp * NT + nt) * 4 + i) * 32 + lane] = acc[nt][i];
+    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
+    if (!ok) return;
+    for (int idx = threadIdx.x; idx < NT * 128; idx += CONSUMER_WARPS * 32) {
+        const int nt = idx >> 7, rem = idx & 127;
+        const int n = rem >> 4, row = rem & 15;
+        const int token = nt * 8 + n;
+        if (token >= tokens || row >= nrows) continue;
+        const int src_lane = (row & 7) * 4 + (n >> 1);
+        const int i = ((row >> 3) << 1) | (n & 1);
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < CONSUMER_WARPS; w++) sum += red[((w * NT + nt) * 4 + i) * 32 + src_lane];
+        const size_t o = (size_t)token * y_stride + row0 + row;
+        if constexpr (Y_F32)
+            reinterpret_cast<float*>(y)[o] = sum;
+        else
+            reinterpret_cast<__half*>(y)[o] = __float2half_rn(sum);
+    }
+}
+
+template <int QT>
+constexpr size_t gemm_smem_bytes() {
+    return 128 + (size_t)NUM_STAGES * TILE_ROWS * row_stride_for(Fmt<QT>::UNIT_BYTES);
+}
+
+template <int QT, int NT, bool F32>
+cudaError_t launch_one(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t rows, int units, ActOperand act,
+                       int cols, void* y, int64_t y_stride, int tokens) {
+    auto kern = gemm_quant_kernel<QT, NT, F32>;
+    static bool configured = false;  // per instantiation; attribute is per device function
+    constexpr size_t smem = gemm_smem_bytes<QT>();
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    dim3 grid((unsigned)((rows + TILE_ROWS - 1) / TILE_ROWS));
+    return tsb_launch(ctx, kern, grid, dim3(GEMM_THREADS), smem, st, true, w, rows, units, act, cols, y, y_stride,
+                      tokens, ctx->dev_error);
+}
+
+template <int QT, bool F32>
+cudaError_t launch_nt(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t rows, int units, ActOperand act,
+                      int cols, void* y, int64_t y_stride, int tokens) {
+    if (tokens <= 8) return launch_one<QT, 1, F32>(ctx, st, w, rows, units, act, cols, y, y_stride, tokens);
+    if (tokens <= 16) return launch_one<QT, 2, F32>(ctx, st, w, rows, units, act, cols, y, y_stride, tokens);
+    if (tokens <= 32) return launch_one<QT, 4, F32>(ctx, st, w, rows, units, act, cols, y, y_stride, tokens);
+    return launch_one<QT, 8, F32>(ctx, st, w, rows, units, act, cols, y, y_stride, tokens);
+}
+
+// x natural -> swizzled + sub-block sums
+__global__ void act_prepare_kernel(const __half* __restrict__ x, int64_t x_stride, int tokens, int cols,
+                                   __half* __restrict__ xp, __half* __restrict__ hi, __half* __restrict__ lo) {
+    pdl_wait();
+    const int per_row = cols >> 3;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool active = idx < (int64_t)tokens * per_row;
+    const int t = active ? (int)(idx / per_row) : 0;
+    const int e0 = active ? (int)(idx % per_row) * 8 : 0;
+    float v[8];
+    if (active) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)t * x_stride + e0);
+        const __half* hp = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = __half2float(hp[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = 0.f;
+    }
+    pdl_launch_dependents();
+    act_store8(v, xp + (size_t)t * cols, hi + (size_t)t * (cols >> 5), lo + (size_t)t * (cols >> 5), e0, active);
+}
+
+}  // namespace
+
+cudaError_t launch_act_prepare(tsb_ctx* ctx, cudaStream_t st, const __half* x, int64_t x_stride, int tokens, int cols,
+                               __half* xp, __half* xs_hi, __half* xs_lo) {
+    const int64_t n = (int64_t)tokens * (cols / 8);
+    const int threads = 256;  // a multiple of 4 and cols/8 is a multiple of 4, so quads never straddle rows
+    return tsb_launch(ctx, act_prepare_kernel, dim3((unsigned)((n + threads - 1) / threads)), dim3(threads), 0, st, true,
+                      x, x_stride, tokens, cols, xp, xs_hi, xs_lo);
+}
+
+cudaError_t launch_gemm_quant(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t rows, int64_t cols,
+                              ActOperand act, void* y, int64_t y_stride, int tokens, bool y_f32) {
+    const int units = (int)(cols / 256);
+    // more than 64 tokens: passes of 64 (each pass re-streams the weights)
+    for (int t0 = 0; t0 < tokens; t0 += 64) {
+        const int nt = min(64, tokens - t0);
+        ActOperand a = {act.xp + (size_t)t0 * cols, act.xs_hi + (size_t)t0 * (cols / 32),
+                        act.xs_lo + (size_t)t0 * (cols / 32)};
+        void* yy = y_f32 ? (void*)((float*)y + (size_t)t0 * y_stride) : (void*)((__half*)y + (size_t)t0 * y_stride);
+        cudaError_t e;
+#define TSB_DISPATCH(QT)                                                                                   \
+    e = y_f32 ? launch_nt<QT, true>(ctx, st, w, rows, units, a, (int)cols, yy, y_stride, nt)               \
+              : launch_nt<QT, false>(ctx, st, w, rows, units, a, (int)cols, yy, y_stride, nt)
+        switch (qtype) {
+            case TSB_Q4_K: TSB_DISPATCH(TSB_Q4_K); break;
+            case TSB_Q6_K: TSB_DISPATCH(TSB_Q6_K); break;
+            case TSB_MXFP4: TSB_DISPATCH(TSB_MXFP4); break;
+            default: return cudaErrorInvalidValue;
+        }
+#undef TSB_DISPATCH
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+// ------------------------------------------------------------------ C ABI
+extern "C" {
+
+int32_t tsb_gemm_quant(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* region, uint64_t w_off, int64_t rows,
+                       int64_t cols, const void* x_f16, void* y, int32_t tokens, int32_t y_f32) {
+    if (!ctx) return TSB_ERR_INVALID;
+    TSB_REQUIRE(ctx, region && x_f16 && y, "null buffer");
+    TSB_REQUIRE(ctx, qtype == TSB_Q4_K || qtype == TSB_Q6_K || qtype == TSB_MXFP4, "unknown block format %d", qtype);
+    TSB_REQUIRE(ctx, rows > 0 && cols > 0 && tokens > 0, "rows, cols and tokens must be positive");
+    if (cols % 256 != 0)
+        return tsb_fail(ctx, TSB_ERR_UNSUPPORTED,
+                        "cols (%lld) is not a whole number of 256-element superblocks", (long long)cols);
+    TSB_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(x_f16) & 15u) == 0, "x must be 16-byte aligned");
+    if (qtype == TSB_Q4_K) TSB_REQUIRE(ctx, ((reinterpret_cast<uintptr_t>(region) + w_off) & 15u) == 0,
+                                       "Q4_K rows must start on a 16-byte boundary");
+    DeviceGuard g(ctx);
+    cudaStream_t st = (cudaStream_t)s;
+    const size_t xp_bytes = (size_t)tokens * cols * sizeof(__half);
+    const size_t side = act_side_bytes(tokens, cols);
+    uint8_t* tmp = nullptr;
+    const size_t side_al = (side + 255) & ~(size_t)255;
+    TSB_CUDA(ctx, cudaMallocAsync((void**)&tmp, xp_bytes + 2 * side_al + 256, st));
+    __half* xp = reinterpret_cast<__half*>(tmp);
+    __half* hi = reinterpret_cast<__half*>(tmp + ((xp_bytes + 255) & ~(size_t)255));
+    __half* lo = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(hi) + side_al);
+    cudaError_t e = launch_act_prepare(ctx, st, (const __half*)x_f16, cols, tokens, (int)cols, xp, hi, lo);
+    if (e == cudaSuccess)
+        e = launch_gemm_quant(ctx, st, qtype, (const uint8_t*)region + w_off, rows, cols, ActOperand{xp, hi, lo}, y,
+                              rows, tokens, y_f32 != 0);
+    cudaError_t e2 = cudaFreeAsync(tmp, st);
+    TSB_CUDA(ctx, e);
+    TSB_CUDA(ctx, e2);
+    return TSB_OK;
+}
+
+int32_t tsb_gemv_q4k(tsb_ctx* c, tsb_stream s, const void* r, uint64_t o, int64_t rows, int64_t cols, const void* x,
+                     void* y) {
+    return tsb_gemm_quant(c, s, TSB_Q4_K, r, o, rows, cols, x, y, 1, 0);
+}
+int32_t tsb_gemv_q6k(tsb_ctx* c, tsb_stream s, const void* r, uint64_t o, int64_t rows, int64_t cols, const void* x,
+                     void* y) {
+    return tsb_gemm_quant(c, s, TSB_Q6_K, r, o, rows, cols, x, y, 1, 0);
+}
+int32_t tsb_gemv_mxfp4(tsb_ctx* c, tsb_stream s, const void* r, uint64_t o, int64_t rows, int64_t cols, const void* x,
+                       void* y) {
+    return tsb_gemm_quant(c, s, TSB_MXFP4, r, o, rows, cols, x, y, 1, 0);
+}
+int32_t tsb_gemm_q4k(tsb_ctx* c, tsb_stream s, const void* r, uint64_t o, int64_t rows, int64_t cols, const void* x,
+                     void* y, int32_t t) {
+    return tsb_gemm_quant(c, s, TSB_Q4_K, r, o, rows, cols, x, y, t, 0);
+}
+int32_t tsb_gemm_q6k(tsb_ctx* c, tsb_stream s, const void* r, uint64_t o, int64_t rows, int64_t cols, const void* x,
+                     void* y, int32_t t) {
+    return tsb_gemm_quant(c, s, TSB_Q6_K, r, o, rows, cols, x, y, t, 0);
+}
+int32_t tsb_gemm_mxfp4(tsb_ctx* c, tsb_stream s, const void* r, uint64_t o, int64_t rows, int64_t cols, const void* x,
+                       void* y, int32_t t) {
+    return tsb_gemm_quant(c, s, TSB_MXFP4, r, o, rows, cols, x, y, t, 0);
+}
+
+}  // extern "C"

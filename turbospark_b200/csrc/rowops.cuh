@@ -1,0 +1,18 @@
+// Internal launchers of the row operators (shared with the model runner).
+#pragma once
+#include "gemm_quant.cuh"
+
+// Where a producer writes the matmul activation operand (all null = do not).
+struct ActOut {
+    __half* xp;
+    __half* xs_hi;
+    __half* xs_lo;
+};
+
+cudaError_t launch_embed_rows(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t vocab_rows, int cols,
+                              const int32_t* ids, int n, __half* out, float out_scale);
+// x <- f16(x + residual) when residual != null; out (natural f16, may be null) and/or act get the normed rows.
+cudaError_t launch_rmsnorm_rows(tsb_ctx* ctx, cudaStream_t st, __half* x, const __half* residual, const void* w_bf16,
+                                __half* out, ActOut act, int rows, int d, float eps);
+cudaError_t launch_silu_mul(tsb_ctx* ctx, cudaStream_t st, const __half* gate, const __half* up, __half* out, ActOut act,
+                            int rows, int n, int64_t in_stride, int64_t out_stride);
