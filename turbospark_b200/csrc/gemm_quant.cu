@@ -28,7 +28,7 @@ constexpr int TILE_ROWS = 16;
 constexpr int STAGE_UNITS = 8;  // 256-column units per row per stage (one per consumer warp)
 constexpr int CONSUMER_WARPS = 8;
 constexpr int GEMM_THREADS = (CONSUMER_WARPS + 1) * 32;
-constexpr int NUM_STAGES = 4;
+constexpr int NUM_STAGES = 3;
 // Row stride inside a stage: the payload (<= 8*210 + 30 slack) rounded so that
 // stride = 64 (mod 128) bytes, which makes the 16-byte fragment loads of the
 // eight row groups hit distinct banks.
@@ -72,20 +72,68 @@ __device__ __forceinline__ uint32_t lds_u32_unaligned(const uint8_t* p) {
 // fma(1024+q, sc, -1024*sc) from the (nibble | 0x6400) bit pattern, and the
 // block's sum needs one multiply by d afterwards.  The min term is a second,
 // tiny contraction over the eight sub-blocks: sum_sub m[sub] * xsum[sub].
+// Per-lane activation pointers, fixed for the whole kernel: token index is
+// clamped (columns past `tokens` compute a duplicate that is never stored), so
+// the hot loop carries no predicates.
 template <int NT>
-__device__ __forceinline__ void q4k_block(const uint8_t* rA, const uint8_t* rB, const ActOperand& act, int cols,
-                                          int tokens, int blk, int gid, int tig, float (&acc)[NT][4]) {
-    const uint4 hA = *reinterpret_cast<const uint4*>(rA);
-    const uint4 hB = *reinterpret_cast<const uint4*>(rB);
-    const int h = tig >> 1;
-    const int l0 = (tig & 1) * 16;
-    const int subs_per_row = cols >> 5;
+struct LaneAct {
+    const uint4* xp[NT];  // token tile nt of the fragment-major operand, advanced by the lane index
+    const uint2* xs[NT];  // sub-block sums of tile nt, advanced by the lane index
+    int nblk;
+};
 
-    float cmain[NT][4];
+__device__ __forceinline__ void mma_16816_first(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]), "f"(0.f));
+}
+__device__ __forceinline__ void mma_1688_first(float (&d)[4], const uint32_t (&a)[2], uint32_t b) {
+    asm("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(b), "f"(0.f));
+}
+__device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+// rowA/rowB: the 144-byte superblock of rows gid and gid+8 in shared memory.
+// blk: index of the 256-column block (for the activation offsets).
+template <int NT>
+__device__ __forceinline__ void q4k_block(const uint4* __restrict__ rowA, const uint4* __restrict__ rowB,
+                                          const LaneAct<NT>& la, int blk, int tig, float (&acc)[NT][4]) {
+    // all activation loads of the block first: one scoreboard wait, hidden behind the scale decode
+    uint4 xl[2][2][NT], xh[2][2][NT];
+    uint32_t xsh[NT], xsl[NT];
 #pragma unroll
-    for (int nt = 0; nt < NT; nt++)
+    for (int nt = 0; nt < NT; nt++) {
+        const uint4* p = la.xp[nt] + blk * 256;  // eight 32-lane chunks per block
 #pragma unroll
-        for (int i = 0; i < 4; i++) cmain[nt][i] = 0.f;
+        for (int r = 0; r < 2; r++)
+#pragma unroll
+            for (int jj = 0; jj < 2; jj++) {
+                xl[r][jj][nt] = __ldg(p + ((r * 2 + jj) * 2) * 32);
+                xh[r][jj][nt] = __ldg(p + ((r * 2 + jj) * 2 + 1) * 32);  // sub-block 2g+1
+            }
+        const uint2 sums = __ldg(la.xs[nt] + blk * 32);
+        xsh[nt] = sums.x;
+        xsl[nt] = sums.y;
+    }
+    const uint4 hA = rowA[0];
+    const uint4 hB = rowB[0];
+    const int h = tig >> 1;
+    // this lane's nibble bytes: group g = 2r + h, bytes (tig&1)*16 .. +15  -> uint4 index 1 + 2g + (tig&1)
+    const int qoff = 1 + 2 * h + (tig & 1);
+    const uint4 qA0 = rowA[qoff], qB0 = rowB[qoff];
+    const uint4 qA1 = rowA[qoff + 4], qB1 = rowB[qoff + 4];
+
     const __half2 ddA = *reinterpret_cast<const __half2*>(&hA.x);
     const __half2 ddB = *reinterpret_cast<const __half2*>(&hB.x);
     const float dA = __low2float(ddA), dminA = __high2float(ddA);
@@ -93,31 +141,23 @@ __device__ __forceinline__ void q4k_block(const uint8_t* rA, const uint8_t* rB, 
 
     // 6-bit fields as bytes: sc0..3 | sc4..7 | m0..3 | m4..7
     const uint32_t scA_lo = hA.y & 0x3F3F3F3Fu, scA_hi = (hA.w & 0x0F0F0F0Fu) | ((hA.y >> 2) & 0x30303030u);
-    const uint32_t mA_lo = hA.z & 0x3F3F3F3Fu, mA_hi = ((hA.w >> 4) & 0x0F0F0F0Fu) | ((hA.z >> 2) & 0x30303030u);
     const uint32_t scB_lo = hB.y & 0x3F3F3F3Fu, scB_hi = (hB.w & 0x0F0F0F0Fu) | ((hB.y >> 2) & 0x30303030u);
-    const uint32_t mB_lo = hB.z & 0x3F3F3F3Fu, mB_hi = ((hB.w >> 4) & 0x0F0F0F0Fu) | ((hB.z >> 2) & 0x30303030u);
+    const uint32_t mA = (tig < 2) ? (hA.z & 0x3F3F3F3Fu) : (((hA.w >> 4) & 0x0F0F0F0Fu) | ((hA.z >> 2) & 0x30303030u));
+    const uint32_t mB = (tig < 2) ? (hB.z & 0x3F3F3F3Fu) : (((hB.w >> 4) & 0x0F0F0F0Fu) | ((hB.z >> 2) & 0x30303030u));
 
+    const uint32_t k1024 = 0x64006400u;
     // --- min term: A = mins of sub-blocks (2tig, 2tig+1), B = xsum hi / lo
     {
         const uint32_t bb = (2u * tig) & 3u;
         const uint32_t sel = bb | (4u << 4) | ((bb + 1u) << 8) | (4u << 12);
         uint32_t amin[2];
-        amin[0] = __byte_perm(tig < 2 ? mA_lo : mA_hi, 0x64646464u, sel);
-        amin[1] = __byte_perm(tig < 2 ? mB_lo : mB_hi, 0x64646464u, sel);
-        const uint32_t k1024 = 0x64006400u;
-        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(amin[0]) : "r"(amin[0]), "r"(k1024));
-        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(amin[1]) : "r"(amin[1]), "r"(k1024));
+        amin[0] = hsub2_u32(__byte_perm(mA, 0x64646464u, sel), k1024);
+        amin[1] = hsub2_u32(__byte_perm(mB, 0x64646464u, sel), k1024);
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
-            const int token = nt * 8 + gid;
-            uint32_t bhi = 0, blo = 0;
-            if (token < tokens) {
-                const size_t o = (size_t)token * subs_per_row + blk * 8 + 2 * tig;
-                bhi = __ldg(reinterpret_cast<const uint32_t*>(act.xs_hi + o));
-                blo = __ldg(reinterpret_cast<const uint32_t*>(act.xs_lo + o));
-            }
-            float c[4] = {0.f, 0.f, 0.f, 0.f};
-            mma_1688(c, amin, bhi);
+            const uint32_t bhi = xsh[nt], blo = xsl[nt];
+            float c[4];
+            mma_1688_first(c, amin, bhi);
             mma_1688(c, amin, blo);
             acc[nt][0] -= dminA * c[0];
             acc[nt][1] -= dminA * c[1];
@@ -127,49 +167,26 @@ __device__ __forceinline__ void q4k_block(const uint8_t* rA, const uint8_t* rB, 
     }
 
     const uint32_t selE = 0x4040u | ((2u * h) * 0x0101u);
-    const uint32_t selO = 0x4040u | ((2u * h + 1u) * 0x0101u);
+    const uint32_t selO = selE + 0x0101u;
     const uint32_t kNeg1024 = 0xE400E400u;  // half2(-1024)
     const uint32_t kNeg64 = 0xD400D400u;    // half2(-64)
 
+    float cL[NT][4], cH[NT][4];  // two independent mma chains (low / high nibbles)
 #pragma unroll
     for (int r = 0; r < 2; r++) {
-        const int g = 2 * r + h;
-        const uint4 qA = *reinterpret_cast<const uint4*>(rA + 16 + g * 32 + l0);
-        const uint4 qB = *reinterpret_cast<const uint4*>(rB + 16 + g * 32 + l0);
+        const uint4 qA = r ? qA1 : qA0, qB = r ? qB1 : qB0;
         // scales of sub-blocks 2g (low nibbles) and 2g+1 (high nibbles) as half2(sc, sc)
-        uint32_t scLA = __byte_perm(r ? scA_hi : scA_lo, 0x64646464u, selE);
-        uint32_t scHA = __byte_perm(r ? scA_hi : scA_lo, 0x64646464u, selO);
-        uint32_t scLB = __byte_perm(r ? scB_hi : scB_lo, 0x64646464u, selE);
-        uint32_t scHB = __byte_perm(r ? scB_hi : scB_lo, 0x64646464u, selO);
-        const uint32_t k1024 = 0x64006400u;
-        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(scLA) : "r"(scLA), "r"(k1024));
-        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(scHA) : "r"(scHA), "r"(k1024));
-        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(scLB) : "r"(scLB), "r"(k1024));
-        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(scHB) : "r"(scHB), "r"(k1024));
-        uint32_t offLA, offHA, offLB, offHB;
-        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(offLA) : "r"(scLA), "r"(kNeg1024));
-        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(offHA) : "r"(scHA), "r"(kNeg64));
-        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(offLB) : "r"(scLB), "r"(kNeg1024));
-        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(offHB) : "r"(scHB), "r"(kNeg64));
+        const uint32_t scLA = hsub2_u32(__byte_perm(r ? scA_hi : scA_lo, 0x64646464u, selE), k1024);
+        const uint32_t scHA = hsub2_u32(__byte_perm(r ? scA_hi : scA_lo, 0x64646464u, selO), k1024);
+        const uint32_t scLB = hsub2_u32(__byte_perm(r ? scB_hi : scB_lo, 0x64646464u, selE), k1024);
+        const uint32_t scHB = hsub2_u32(__byte_perm(r ? scB_hi : scB_lo, 0x64646464u, selO), k1024);
+        const uint32_t offLA = hmul2_u32(scLA, kNeg1024), offHA = hmul2_u32(scHA, kNeg64);
+        const uint32_t offLB = hmul2_u32(scLB, kNeg1024), offHB = hmul2_u32(scHB, kNeg64);
 
-        const int k_lo = blk * 256 + g * 64 + l0;  // 16 consecutive columns of sub-block 2g
         const uint32_t wA[4] = {qA.x, qA.y, qA.z, qA.w};
         const uint32_t wB[4] = {qB.x, qB.y, qB.z, qB.w};
 #pragma unroll
         for (int jj = 0; jj < 2; jj++) {
-            // eight columns (two mma steps) of activations per token tile
-            uint4 xl[NT], xh[NT];
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-                const int token = nt * 8 + gid;
-                if (token < tokens) {
-                    const uint4* p = reinterpret_cast<const uint4*>(act.xp + (size_t)token * cols + k_lo) + jj;
-                    xl[nt] = __ldg(p);
-                    xh[nt] = __ldg(p + 4);  // +32 columns: sub-block 2g+1
-                } else {
-                    xl[nt] = xh[nt] = make_uint4(0, 0, 0, 0);
-                }
-            }
 #pragma unroll
             for (int j2 = 0; j2 < 2; j2++) {
                 const int j = jj * 2 + j2;
@@ -187,22 +204,27 @@ __device__ __forceinline__ void q4k_block(const uint8_t* rA, const uint8_t* rB, 
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
                     uint32_t bl[2], bh[2];
-                    bl[0] = j2 ? xl[nt].z : xl[nt].x;
-                    bl[1] = j2 ? xl[nt].w : xl[nt].y;
-                    bh[0] = j2 ? xh[nt].z : xh[nt].x;
-                    bh[1] = j2 ? xh[nt].w : xh[nt].y;
-                    mma_16816(cmain[nt], alo, bl);
-                    mma_16816(cmain[nt], ahi, bh);
+                    bl[0] = j2 ? xl[r][jj][nt].z : xl[r][jj][nt].x;
+                    bl[1] = j2 ? xl[r][jj][nt].w : xl[r][jj][nt].y;
+                    bh[0] = j2 ? xh[r][jj][nt].z : xh[r][jj][nt].x;
+                    bh[1] = j2 ? xh[r][jj][nt].w : xh[r][jj][nt].y;
+                    if (r == 0 && j == 0) {
+                        mma_16816_first(cL[nt], alo, bl);
+                        mma_16816_first(cH[nt], ahi, bh);
+                    } else {
+                        mma_16816(cL[nt], alo, bl);
+                        mma_16816(cH[nt], ahi, bh);
+                    }
                 }
             }
         }
     }
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
-        acc[nt][0] += dA * cmain[nt][0];
-        acc[nt][1] += dA * cmain[nt][1];
-        acc[nt][2] += dB * cmain[nt][2];
-        acc[nt][3] += dB * cmain[nt][3];
+        acc[nt][0] += dA * (cL[nt][0] + cH[nt][0]);
+        acc[nt][1] += dA * (cL[nt][1] + cH[nt][1]);
+        acc[nt][2] += dB * (cL[nt][2] + cH[nt][2]);
+        acc[nt][3] += dB * (cL[nt][3] + cH[nt][3]);
     }
 }
 
@@ -231,8 +253,8 @@ __device__ __forceinline__ float mxfp4_scale_dev(uint32_t e) {
 }
 
 template <int NT>
-__device__ __forceinline__ void mxfp4_unit(const uint8_t* rA, const uint8_t* rB, const ActOperand& act, int cols,
-                                           int tokens, int unit, int gid, int tig, float (&acc)[NT][4]) {
+__device__ __forceinline__ void mxfp4_unit(const uint8_t* rA, const uint8_t* rB, const ActOperand& act, int nblk,
+                                           int unit, int gid, int tig, float (&acc)[NT][4]) {
 #pragma unroll 2
     for (int b = 0; b < 8; b++) {
         const uint8_t* pA = rA + b * 17;
@@ -260,10 +282,11 @@ __device__ __forceinline__ void mxfp4_unit(const uint8_t* rA, const uint8_t* rB,
         for (int nt = 0; nt < NT; nt++) {
             const int token = nt * 8 + gid;
             float c[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t bl[2] = {0, 0}, bh[2] = {0, 0};
-            if (token < tokens) {
-                const uint2* p = reinterpret_cast<const uint2*>(act.xp + (size_t)token * cols + k0);
-                const uint2 l = __ldg(p), hh = __ldg(p + 4);  // +16 columns
+            uint32_t bl[2], bh[2];
+            {
+                const __half* xh16 = reinterpret_cast<const __half*>(act.xp);
+                const uint2 l = __ldg(reinterpret_cast<const uint2*>(xh16 + act_xp_half_index(token, k0, nblk)));
+                const uint2 hh = __ldg(reinterpret_cast<const uint2*>(xh16 + act_xp_half_index(token, k0 + 16, nblk)));
                 bl[0] = l.x, bl[1] = l.y, bh[0] = hh.x, bh[1] = hh.y;
             }
             mma_16816(c, alo, bl);
@@ -290,8 +313,8 @@ __device__ __forceinline__ float s8_to_float(uint32_t byte) {
 }
 
 template <int NT>
-__device__ __forceinline__ void q6k_block(const uint8_t* rA, const uint8_t* rB, const ActOperand& act, int cols,
-                                          int tokens, int blk, int gid, int tig, float (&acc)[NT][4]) {
+__device__ __forceinline__ void q6k_block(const uint8_t* rA, const uint8_t* rB, const ActOperand& act, int nblk,
+                                          int blk, int gid, int tig, float (&acc)[NT][4]) {
     float blkacc[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; nt++)
@@ -327,9 +350,10 @@ __device__ __forceinline__ void q6k_block(const uint8_t* rA, const uint8_t* rB, 
                 for (int nt = 0; nt < NT; nt++) {
                     const int token = nt * 8 + gid;
                     float c[4] = {0.f, 0.f, 0.f, 0.f};
-                    uint32_t bb[2] = {0, 0};
-                    if (token < tokens) {
-                        const uint2 x = __ldg(reinterpret_cast<const uint2*>(act.xp + (size_t)token * cols + k0));
+                    uint32_t bb[2];
+                    {
+                        const __half* xh16 = reinterpret_cast<const __half*>(act.xp);
+                        const uint2 x = __ldg(reinterpret_cast<const uint2*>(xh16 + act_xp_half_index(token, k0, nblk)));
                         bb[0] = x.x, bb[1] = x.y;
                     }
                     mma_16816(c, a, bb);
@@ -356,19 +380,19 @@ template <int QT, int NT, bool Y_F32>
 __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
     gemm_quant_kernel(const uint8_t* __restrict__ W, int64_t rows, int units /*256-col units per row*/,
                       ActOperand act, int cols, void* __restrict__ y, int64_t y_stride, int tokens,
-                      uint32_t* __restrict__ err) {
+                      uint32_t* __restrict__ err, int probe) {
     constexpr int UB = Fmt<QT>::UNIT_BYTES;
     constexpr int ROW_STRIDE = row_stride_for(UB);
     constexpr int STAGE_BYTES = TILE_ROWS * ROW_STRIDE;
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + NUM_STAGES;
-    uint8_t* stages = smem + 128;
+    float* red = reinterpret_cast<float*>(smem + 128);
+    uint8_t* stages = smem + 128 + CONSUMER_WARPS * NT * 4 * 32 * sizeof(float);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t row0 = (int64_t)blockIdx.x * TILE_ROWS;
-    const int nrows = (int)min((int64_t)TILE_ROWS, rows - row0);
-    const int iters = (units + STAGE_UNITS - 1) / STAGE_UNITS;
+    const int n_tiles = (int)((rows + TILE_ROWS - 1) / TILE_ROWS);
+    const int iters = (units + STAGE_UNITS - 1) / STAGE_UNITS;  // stages per row tile
     const int64_t row_bytes = (int64_t)units * UB;
 
     if (threadIdx.x == 0) {
@@ -380,30 +404,39 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
     }
     __syncthreads();
 
+    // The CTA is persistent: it walks row tiles blockIdx.x, +gridDim.x, ... and the
+    // stage ring runs on across tile boundaries, so weight bytes stay in flight
+    // while the consumers reduce and store a finished tile.
     if (warp == CONSUMER_WARPS) {
         // ---- producer: one bulk copy per row per stage; sources are rounded
         // down to 16 bytes (formats whose rows are not 16-byte multiples) and
         // the consumer skips the same slack.
-        for (int it = 0; it < iters; it++) {
-            const int s = it % NUM_STAGES;
-            if (it >= NUM_STAGES) {
-                if (!mbar_wait(&empty[s], ((it / NUM_STAGES) - 1) & 1, err)) return;
-            }
-            const int nun = min(STAGE_UNITS, units - it * STAGE_UNITS);
-            uint32_t bytes = 0;
-            const uint8_t* src = nullptr;
-            if (lane < nrows) {
-                const uint8_t* p = W + (row0 + lane) * row_bytes + (int64_t)it * STAGE_UNITS * UB;
-                const uint32_t slack = (uint32_t)(reinterpret_cast<uintptr_t>(p) & 15u);
-                src = p - slack;
-                bytes = (slack + (uint32_t)nun * UB + 15u) & ~15u;
-            }
-            uint32_t total = bytes;
+        uint32_t n = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            const int64_t row0 = (int64_t)tile * TILE_ROWS;
+            const int nrows = (int)min((int64_t)TILE_ROWS, rows - row0);
+            for (int it = 0; it < iters; it++, n++) {
+                const uint32_t s = n % NUM_STAGES;
+                if (n >= NUM_STAGES) {
+                    if (!mbar_wait(&empty[s], ((n / NUM_STAGES) - 1) & 1, err)) return;
+                }
+                const int nun = min(STAGE_UNITS, units - it * STAGE_UNITS);
+                uint32_t bytes = 0;
+                const uint8_t* src = nullptr;
+                if (lane < nrows) {
+                    const uint8_t* p = W + (row0 + lane) * row_bytes + (int64_t)it * STAGE_UNITS * UB;
+                    const uint32_t slack = (uint32_t)(reinterpret_cast<uintptr_t>(p) & 15u);
+                    src = p - slack;
+                    bytes = (slack + (uint32_t)nun * UB + 15u) & ~15u;
+                }
+                uint32_t total = bytes;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
-            if (lane == 0) mbar_expect_tx(&full[s], total);
-            __syncwarp();
-            if (lane < nrows) bulk_g2s(stages + s * STAGE_BYTES + lane * ROW_STRIDE, src, bytes, &full[s]);
+                for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+                if (probe == 2) { if (lane == 0) mbar_arrive(&full[s]); continue; }
+                if (lane == 0) mbar_expect_tx(&full[s], total);
+                __syncwarp();
+                if (lane < nrows) bulk_g2s(stages + s * STAGE_BYTES + lane * ROW_STRIDE, src, bytes, &full[s]);
+            }
         }
         pdl_launch_dependents();
         return;
@@ -411,69 +444,81 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
 
     // ---- consumers
     const int gid = lane >> 2, tig = lane & 3;
-    float acc[NT][4];
+    LaneAct<NT> la;
 #pragma unroll
-    for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-        for (int i = 0; i < 4; i++) acc[nt][i] = 0.f;
-
-    const uint32_t slackA = (uint32_t)(reinterpret_cast<uintptr_t>(W + (row0 + gid) * row_bytes) & 15u);
-    const uint32_t slackB = (uint32_t)(reinterpret_cast<uintptr_t>(W + (row0 + gid + 8) * row_bytes) & 15u);
-
+    la.nblk = units;
+    for (int nt = 0; nt < NT; nt++) {
+        la.xp[nt] = act.xp + (size_t)nt * units * 256 + lane;
+        la.xs[nt] = act.xs + (size_t)nt * units * 32 + lane;
+    }
     pdl_wait();  // activations come from the previous kernel
 
     bool ok = true;
-    for (int it = 0; it < iters && ok; it++) {
-        const int s = it % NUM_STAGES;
-        ok = mbar_wait(&full[s], (it / NUM_STAGES) & 1, err);
-        if (!ok) break;
-        const int nun = min(STAGE_UNITS, units - it * STAGE_UNITS);
-        if (warp < nun) {
-            // slack of this stage's source address: the row start's slack plus the stage offset
-            const uint32_t stA = (slackA + (uint32_t)((int64_t)it * STAGE_UNITS * UB)) & 15u;
-            const uint32_t stB = (slackB + (uint32_t)((int64_t)it * STAGE_UNITS * UB)) & 15u;
-            const uint8_t* rA = stages + s * STAGE_BYTES + gid * ROW_STRIDE + stA + warp * UB;
-            const uint8_t* rB = stages + s * STAGE_BYTES + (gid + 8) * ROW_STRIDE + stB + warp * UB;
-            const int unit = it * STAGE_UNITS + warp;
-            if constexpr (QT == TSB_Q4_K) q4k_block<NT>(rA, rB, act, cols, tokens, unit, gid, tig, acc);
-            if constexpr (QT == TSB_MXFP4) mxfp4_unit<NT>(rA, rB, act, cols, tokens, unit, gid, tig, acc);
-            if constexpr (QT == TSB_Q6_K) q6k_block<NT>(rA, rB, act, cols, tokens, unit, gid, tig, acc);
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]);
-    }
-    pdl_launch_dependents();
+    uint32_t n = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const int64_t row0 = (int64_t)tile * TILE_ROWS;
+        const int nrows = (int)min((int64_t)TILE_ROWS, rows - row0);
+        if (tile + (int)gridDim.x >= n_tiles) pdl_launch_dependents();  // last tile of this CTA
+        float acc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[nt][i] = 0.f;
+        const uint32_t slackA = (uint32_t)(reinterpret_cast<uintptr_t>(W + (row0 + gid) * row_bytes) & 15u);
+        const uint32_t slackB = (uint32_t)(reinterpret_cast<uintptr_t>(W + (row0 + gid + 8) * row_bytes) & 15u);
 
-    // ---- fixed-order reduction over the eight consumer warps
-    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
-    float* red = reinterpret_cast<float*>(stages);
+        for (int it = 0; it < iters; it++, n++) {
+            const uint32_t s = n % NUM_STAGES;
+            if (ok) ok = mbar_wait(&full[s], (n / NUM_STAGES) & 1, err);
+            const int nun = min(STAGE_UNITS, units - it * STAGE_UNITS);
+            if (ok && warp < nun && probe != 1) {
+                // slack of this stage's source address: the row start's slack plus the stage offset
+                const uint32_t stA = (slackA + (uint32_t)((int64_t)it * STAGE_UNITS * UB)) & 15u;
+                const uint32_t stB = (slackB + (uint32_t)((int64_t)it * STAGE_UNITS * UB)) & 15u;
+                const uint8_t* rA = stages + s * STAGE_BYTES + gid * ROW_STRIDE + stA + warp * UB;
+                const uint8_t* rB = stages + s * STAGE_BYTES + (gid + 8) * ROW_STRIDE + stB + warp * UB;
+                const int unit = it * STAGE_UNITS + warp;
+                if constexpr (QT == TSB_Q4_K)
+                    q4k_block<NT>(reinterpret_cast<const uint4*>(rA), reinterpret_cast<const uint4*>(rB), la, unit, tig, acc);
+                if constexpr (QT == TSB_MXFP4) mxfp4_unit<NT>(rA, rB, act, units, unit, gid, tig, acc);
+                if constexpr (QT == TSB_Q6_K) q6k_block<NT>(rA, rB, act, units, unit, gid, tig, acc);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+
+        // ---- fixed-order reduction over the eight consumer warps
 #pragma unroll
-    for (int nt = 0; nt < NT; nt++)
+        for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-        for (int i = 0; i < 4; i++) red[((warp * NT + nt) * 4 + i) * 32 + lane] = acc[nt][i];
-    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
-    if (!ok) return;
-    for (int idx = threadIdx.x; idx < NT * 128; idx += CONSUMER_WARPS * 32) {
-        const int nt = idx >> 7, rem = idx & 127;
-        const int n = rem >> 4, row = rem & 15;
-        const int token = nt * 8 + n;
-        if (token >= tokens || row >= nrows) continue;
-        const int src_lane = (row & 7) * 4 + (n >> 1);
-        const int i = ((row >> 3) << 1) | (n & 1);
-        float sum = 0.f;
+            for (int i = 0; i < 4; i++) red[((warp * NT + nt) * 4 + i) * 32 + lane] = acc[nt][i];
+        asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
+        if (ok) {
+            for (int idx = threadIdx.x; idx < NT * 128; idx += CONSUMER_WARPS * 32) {
+                const int nt = idx >> 7, rem = idx & 127;
+                const int nn = rem >> 4, row = rem & 15;
+                const int token = nt * 8 + nn;
+                if (token >= tokens || row >= nrows) continue;
+                const int src_lane = (row & 7) * 4 + (nn >> 1);
+                const int i = ((row >> 3) << 1) | (nn & 1);
+                float sum = 0.f;
 #pragma unroll
-        for (int w = 0; w < CONSUMER_WARPS; w++) sum += red[((w * NT + nt) * 4 + i) * 32 + src_lane];
-        const size_t o = (size_t)token * y_stride + row0 + row;
-        if constexpr (Y_F32)
-            reinterpret_cast<float*>(y)[o] = sum;
-        else
-            reinterpret_cast<__half*>(y)[o] = __float2half_rn(sum);
+                for (int w = 0; w < CONSUMER_WARPS; w++) sum += red[((w * NT + nt) * 4 + i) * 32 + src_lane];
+                const size_t o = (size_t)token * y_stride + row0 + row;
+                if constexpr (Y_F32)
+                    reinterpret_cast<float*>(y)[o] = sum;
+                else
+                    reinterpret_cast<__half*>(y)[o] = __float2half_rn(sum);
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");  // red is reused by the next tile
     }
 }
 
-template <int QT>
+template <int QT, int NT>
 constexpr size_t gemm_smem_bytes() {
-    return 128 + (size_t)NUM_STAGES * TILE_ROWS * row_stride_for(Fmt<QT>::UNIT_BYTES);
+    return 128 + (size_t)CONSUMER_WARPS * NT * 4 * 32 * sizeof(float) +
+           (size_t)NUM_STAGES * TILE_ROWS * row_stride_for(Fmt<QT>::UNIT_BYTES);
 }
 
 template <int QT, int NT, bool F32>
@@ -481,15 +526,17 @@ cudaError_t launch_one(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t 
                        int cols, void* y, int64_t y_stride, int tokens) {
     auto kern = gemm_quant_kernel<QT, NT, F32>;
     static bool configured = false;  // per instantiation; attribute is per device function
-    constexpr size_t smem = gemm_smem_bytes<QT>();
+    constexpr size_t smem = gemm_smem_bytes<QT, NT>();
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    dim3 grid((unsigned)((rows + TILE_ROWS - 1) / TILE_ROWS));
+    const int n_tiles = (int)((rows + TILE_ROWS - 1) / TILE_ROWS);
+    const int per_sm = NT <= 2 ? 2 : 1;
+    dim3 grid((unsigned)min(n_tiles, ctx->sm_count * per_sm));
     return tsb_launch(ctx, kern, grid, dim3(GEMM_THREADS), smem, st, true, w, rows, units, act, cols, y, y_stride,
-                      tokens, ctx->dev_error);
+                      tokens, ctx->dev_error, getenv("TSB_GEMM_PROBE") ? atoi(getenv("TSB_GEMM_PROBE")) : 0);
 }
 
 template <int QT, bool F32>
@@ -501,37 +548,37 @@ cudaError_t launch_nt(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t r
     return launch_one<QT, 8, F32>(ctx, st, w, rows, units, act, cols, y, y_stride, tokens);
 }
 
-// x natural -> swizzled + sub-block sums
+// x natural -> fragment-major operand + sub-block sums
 __global__ void act_prepare_kernel(const __half* __restrict__ x, int64_t x_stride, int tokens, int cols,
-                                   __half* __restrict__ xp, __half* __restrict__ hi, __half* __restrict__ lo) {
+                                   uint4* __restrict__ xp, uint2* __restrict__ xs) {
     pdl_wait();
     const int per_row = cols >> 3;
+    const int padded = ((tokens + 7) >> 3) << 3;  // slots of the last tile are zero-filled
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const bool active = idx < (int64_t)tokens * per_row;
+    const bool active = idx < (int64_t)padded * per_row;
     const int t = active ? (int)(idx / per_row) : 0;
     const int e0 = active ? (int)(idx % per_row) * 8 : 0;
     float v[8];
-    if (active) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = 0.f;
+    if (active && t < tokens) {
         const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)t * x_stride + e0);
         const __half* hp = reinterpret_cast<const __half*>(&raw);
 #pragma unroll
         for (int i = 0; i < 8; i++) v[i] = __half2float(hp[i]);
-    } else {
-#pragma unroll
-        for (int i = 0; i < 8; i++) v[i] = 0.f;
     }
     pdl_launch_dependents();
-    act_store8(v, xp + (size_t)t * cols, hi + (size_t)t * (cols >> 5), lo + (size_t)t * (cols >> 5), e0, active);
+    act_store8(v, xp, xs, t, e0, cols >> 8, active);
 }
 
 }  // namespace
 
 cudaError_t launch_act_prepare(tsb_ctx* ctx, cudaStream_t st, const __half* x, int64_t x_stride, int tokens, int cols,
-                               __half* xp, __half* xs_hi, __half* xs_lo) {
-    const int64_t n = (int64_t)tokens * (cols / 8);
+                               uint4* xp, uint2* xs) {
+    const int64_t n = (int64_t)act_tiles(tokens) * 8 * (cols / 8);
     const int threads = 256;  // a multiple of 4 and cols/8 is a multiple of 4, so quads never straddle rows
     return tsb_launch(ctx, act_prepare_kernel, dim3((unsigned)((n + threads - 1) / threads)), dim3(threads), 0, st, true,
-                      x, x_stride, tokens, cols, xp, xs_hi, xs_lo);
+                      x, x_stride, tokens, cols, xp, xs);
 }
 
 cudaError_t launch_gemm_quant(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t rows, int64_t cols,
@@ -540,8 +587,7 @@ cudaError_t launch_gemm_quant(tsb_ctx* ctx, cudaStream_t st, int qtype, const ui
     // more than 64 tokens: passes of 64 (each pass re-streams the weights)
     for (int t0 = 0; t0 < tokens; t0 += 64) {
         const int nt = min(64, tokens - t0);
-        ActOperand a = {act.xp + (size_t)t0 * cols, act.xs_hi + (size_t)t0 * (cols / 32),
-                        act.xs_lo + (size_t)t0 * (cols / 32)};
+        ActOperand a = {act.xp + (size_t)(t0 / 8) * units * 256, act.xs + (size_t)(t0 / 8) * units * 32};
         void* yy = y_f32 ? (void*)((float*)y + (size_t)t0 * y_stride) : (void*)((__half*)y + (size_t)t0 * y_stride);
         cudaError_t e;
 #define TSB_DISPATCH(QT)                                                                                   \
@@ -576,17 +622,14 @@ int32_t tsb_gemm_quant(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* re
                                        "Q4_K rows must start on a 16-byte boundary");
     DeviceGuard g(ctx);
     cudaStream_t st = (cudaStream_t)s;
-    const size_t xp_bytes = (size_t)tokens * cols * sizeof(__half);
-    const size_t side = act_side_bytes(tokens, cols);
+    const size_t xp_bytes = (act_xp_bytes(tokens, cols) + 255) & ~(size_t)255;
     uint8_t* tmp = nullptr;
-    const size_t side_al = (side + 255) & ~(size_t)255;
-    TSB_CUDA(ctx, cudaMallocAsync((void**)&tmp, xp_bytes + 2 * side_al + 256, st));
-    __half* xp = reinterpret_cast<__half*>(tmp);
-    __half* hi = reinterpret_cast<__half*>(tmp + ((xp_bytes + 255) & ~(size_t)255));
-    __half* lo = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(hi) + side_al);
-    cudaError_t e = launch_act_prepare(ctx, st, (const __half*)x_f16, cols, tokens, (int)cols, xp, hi, lo);
+    TSB_CUDA(ctx, cudaMallocAsync((void**)&tmp, xp_bytes + act_xs_bytes(tokens, cols), st));
+    uint4* xp = reinterpret_cast<uint4*>(tmp);
+    uint2* xs = reinterpret_cast<uint2*>(tmp + xp_bytes);
+    cudaError_t e = launch_act_prepare(ctx, st, (const __half*)x_f16, cols, tokens, (int)cols, xp, xs);
     if (e == cudaSuccess)
-        e = launch_gemm_quant(ctx, st, qtype, (const uint8_t*)region + w_off, rows, cols, ActOperand{xp, hi, lo}, y,
+        e = launch_gemm_quant(ctx, st, qtype, (const uint8_t*)region + w_off, rows, cols, ActOperand{xp, xs}, y,
                               rows, tokens, y_f32 != 0);
     cudaError_t e2 = cudaFreeAsync(tmp, st);
     TSB_CUDA(ctx, e);

@@ -154,8 +154,7 @@ __global__ void __launch_bounds__(NORM_THREADS)
 #pragma unroll
                 for (int i = 0; i < 8; i++) o[i] = 0.f;
             }
-            act_store8(o, act.xp + (size_t)r * d, act.xs_hi + (size_t)r * (d >> 5), act.xs_lo + (size_t)r * (d >> 5),
-                       active ? e0 : 0, active);
+            act_store8(o, act.xp, act.xs, r, active ? e0 : 0, d >> 8, active);
         }
     }
 }
@@ -226,9 +225,7 @@ __global__ void silu_mul_kernel(const __half* __restrict__ gate, const __half* _
         for (int i = 0; i < 8; i++) pp[i] = __float2half_rn(o[i]);
         *reinterpret_cast<uint4*>(out + (size_t)r * out_stride + e0) = pk;
     }
-    if (act.xp)
-        act_store8(o, act.xp + (size_t)r * n, act.xs_hi + (size_t)r * (n >> 5), act.xs_lo + (size_t)r * (n >> 5), e0,
-                   active);
+    if (act.xp) act_store8(o, act.xp, act.xs, r, e0, n >> 8, active);
 }
 
 __global__ void residual_add_kernel(__half* __restrict__ x, const __half* __restrict__ y, int64_t n) {
@@ -322,7 +319,7 @@ int32_t tsb_rmsnorm_rows(tsb_ctx* ctx, tsb_stream s, void* x_f16, const void* re
                         NORM_THREADS * 8 * NORM_MAX_ITERS);
     DeviceGuard g(ctx);
     TSB_CUDA(ctx, launch_rmsnorm_rows(ctx, (cudaStream_t)s, (__half*)x_f16, (const __half*)residual_f16, w_bf16,
-                                      (__half*)out_f16, ActOut{nullptr, nullptr, nullptr}, rows, d, eps));
+                                      (__half*)out_f16, ActOut{nullptr, nullptr}, rows, d, eps));
     return TSB_OK;
 }
 
@@ -349,7 +346,7 @@ int32_t tsb_silu_mul(tsb_ctx* ctx, tsb_stream s, const void* gate_f16, const voi
         return tsb_fail(ctx, TSB_ERR_UNSUPPORTED, "n must be a multiple of 32 and strides multiples of 8");
     DeviceGuard g(ctx);
     TSB_CUDA(ctx, launch_silu_mul(ctx, (cudaStream_t)s, (const __half*)gate_f16, (const __half*)up_f16, (__half*)out_f16,
-                                  ActOut{nullptr, nullptr, nullptr}, rows, n, in_stride, out_stride));
+                                  ActOut{nullptr, nullptr}, rows, n, in_stride, out_stride));
     return TSB_OK;
 }
 

@@ -4,9 +4,8 @@
 
 // Where a producer writes the matmul activation operand (all null = do not).
 struct ActOut {
-    __half* xp;
-    __half* xs_hi;
-    __half* xs_lo;
+    uint4* xp;
+    uint2* xs;
 };
 
 cudaError_t launch_embed_rows(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t vocab_rows, int cols,
