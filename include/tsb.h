@@ -190,16 +190,18 @@ typedef struct tsb_row_desc {
 TSB_API int32_t tsb_rope_store_kv(tsb_ctx* ctx, tsb_stream s, tsb_kv* kv, int32_t layer, void* qkv_f16,
                                   const tsb_row_desc* rows_dev, int32_t rows, int32_t n_q_heads, float theta);
 
-/* Split-KV decode attention for a batch of rows.  Row r attends to its stream's committed prefix
- * [0, base) and to the in-flight slots its mask names (a chain row m has bits 0..m; a tree row has its
- * root path).  q is [rows, q_stride] f16 with nq*head_dim values per row, out [rows, nq*head_dim] f16.
- * scratch must hold tsb_attn_scratch_bytes(...) bytes.  Replaces encode_attention_decode,
- * encode_attention_decode_tree and the combine pass (crates/gpu/src/attention_decode.rs:920-1046,
- * 1153-1230; shaders/attention.metal:285-446,983-1031).  rows of one stream must be adjacent and
- * ordered by slot. */
+/* Split-KV decode attention for a batch of rows.  Rows are grouped per stream: rows_per_seq
+ * consecutive rows belong to one stream, share `seq` and `base`, and are ordered by slot (row j of a
+ * group has slot j).  Row r attends to its stream's committed prefix [0, base) and to the in-flight
+ * slots its mask names (a chain row m has bits 0..m; a tree row has its root path).  q is
+ * [rows, q_stride] f16 with nq*head_dim values at the start of each row, out [rows, nq*head_dim] f16.
+ * max_len bounds base + rows_per_seq over the batch (it sizes the split; the kernels read the true
+ * lengths from the descriptors).  scratch must hold tsb_attn_scratch_bytes(...) bytes.  Replaces
+ * encode_attention_decode, encode_attention_decode_tree and the combine pass
+ * (crates/gpu/src/attention_decode.rs:920-1046,1153-1230; shaders/attention.metal:285-446,983-1031). */
 TSB_API int32_t tsb_attn_decode_rows(tsb_ctx* ctx, tsb_stream s, tsb_kv* kv, int32_t layer, const void* q_f16,
-                                     int64_t q_stride, void* out_f16, const tsb_row_desc* rows_dev,
-                                     const tsb_row_desc* rows_host, int32_t rows, int32_t n_q_heads, float scale,
+                                     int64_t q_stride, void* out_f16, const tsb_row_desc* rows_dev, int32_t rows,
+                                     int32_t rows_per_seq, int32_t n_q_heads, float scale, int32_t max_len,
                                      void* scratch, size_t scratch_bytes);
 TSB_API size_t tsb_attn_scratch_bytes(int32_t rows, int32_t n_q_heads, int32_t head_dim);
 

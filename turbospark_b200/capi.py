@@ -41,6 +41,17 @@ class AcceptOut(C.Structure):
                 ("_pad", C.c_int32), ("margin_accept", C.c_double), ("margin_draw", C.c_double)]
 
 
+def row_descs(entries):
+    """entries: iterable of (seq, base, slot, position, mask_int) -> ctypes array of RowDesc."""
+    entries = list(entries)
+    arr = (RowDesc * len(entries))()
+    for i, (seq, base, slot, position, mask) in enumerate(entries):
+        arr[i].seq, arr[i].base, arr[i].slot, arr[i].position = seq, base, slot, position
+        arr[i].mask[0] = mask & 0xFFFFFFFFFFFFFFFF
+        arr[i].mask[1] = (mask >> 64) & 0xFFFFFFFFFFFFFFFF
+    return arr
+
+
 def lib():
     """Loads libtsb.so; raises if it has not been built (there is no fallback path)."""
     global _lib
@@ -135,6 +146,8 @@ class Ctx:
         return DeviceBuffer(self, nbytes)
 
     def to_device(self, arr):
+        if isinstance(arr, C.Array):
+            arr = np.frombuffer(bytes(arr), dtype=np.uint8)
         arr = np.ascontiguousarray(arr)
         return DeviceBuffer(self, max(arr.nbytes, 16)).upload(arr)
 
@@ -176,6 +189,20 @@ class Ctx:
     def silu_mul(self, gate, up, out, rows, n, in_stride, out_stride, stream=None):
         self.check(lib().tsb_silu_mul(self.h, stream, _vp(gate), _vp(up), _vp(out), C.c_int32(rows), C.c_int32(n),
                                       C.c_int64(in_stride), C.c_int64(out_stride)))
+
+    def attn_scratch_bytes(self, rows, n_q_heads, head_dim):
+        return int(lib().tsb_attn_scratch_bytes(C.c_int32(rows), C.c_int32(n_q_heads), C.c_int32(head_dim)))
+
+    def rope_store_kv(self, kv, layer, qkv, rows_dev, rows, n_q_heads, theta, stream=None):
+        self.check(lib().tsb_rope_store_kv(self.h, stream, kv.h, C.c_int32(layer), _vp(qkv), _vp(rows_dev),
+                                           C.c_int32(rows), C.c_int32(n_q_heads), C.c_float(theta)))
+
+    def attn_decode_rows(self, kv, layer, q, q_stride, out, rows_dev, rows, rows_per_seq, n_q_heads, scale, max_len,
+                         scratch, stream=None):
+        self.check(lib().tsb_attn_decode_rows(self.h, stream, kv.h, C.c_int32(layer), _vp(q), C.c_int64(q_stride),
+                                              _vp(out), _vp(rows_dev), C.c_int32(rows), C.c_int32(rows_per_seq),
+                                              C.c_int32(n_q_heads), C.c_float(scale), C.c_int32(max_len), _vp(scratch),
+                                              C.c_size_t(scratch.nbytes)))
 
     def residual_add(self, x, y, n, stream=None):
         self.check(lib().tsb_residual_add(self.h, stream, _vp(x), _vp(y), C.c_int64(n)))

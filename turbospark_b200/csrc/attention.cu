@@ -1,0 +1,431 @@
+// Split-KV ("flash-decoding") attention over the paged fp16 cache for a batch of
+// verify rows, with the speculative tree's ancestor mask.
+//
+// Rows come grouped per stream (rows_per_seq each, ordered by in-flight slot).
+// A CTA owns one (stream, kv head, 32-query tile, KV chunk): the queries are the
+// stream's rows x the kv head's group of q heads, so every K/V byte is read once
+// for the whole group (GQA-shared) and once for all rows of the round.  Inside
+// the CTA four warps split the work 2 x 2: two 16-query mma tiles x two halves
+// of each 64-token K/V tile.  Scores S = Q K^T and O += P V run on mma.sync
+// m16n8k16 (f16 in, f32 accumulate) with K/V staged in shared memory by
+// cp.async, double buffered, 16-byte-chunk XOR swizzle, fragments pulled with
+// ldmatrix.  The online softmax keeps (m, l, O) per query in registers; row max
+// and sum are combined across the four lanes of a quad with warp shuffles.
+// Each CTA writes one partial (m, l, O[head_dim]) per query; a second kernel
+// merges the partials of all chunks and emits f16 rows plus the o_proj matmul's
+// activation operand.
+//
+// Masking: positions below the row's `base` are the committed prefix (always
+// visible); position base + j is in-flight slot j and is visible iff bit j of
+// the row's 128-bit mask is set (a chain row m has bits 0..m, a tree row its
+// root path).  HBM-bound: bytes = context * kv_heads * head_dim * 2 (K and V) * 2 B per layer.
+#include "attention.cuh"
+
+namespace {
+
+constexpr int ATT_THREADS = 128;
+constexpr int TILE_TOKENS = 64;
+constexpr int MAX_SPLITS = 64;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+
+// byte offset of 16-byte chunk `c` of token row `r` inside a swizzled [64][HD] f16 tile
+template <int HD>
+__device__ __forceinline__ uint32_t tile_off(int r, int c) {
+    return (uint32_t)(r * (HD * 2) + ((c ^ (r & 7)) << 4));
+}
+
+template <int HD>
+__global__ void __launch_bounds__(ATT_THREADS)
+    attn_partial_kernel(KvView kv, int layer, const __half* __restrict__ q, int64_t q_stride,
+                        const tsb_row_desc* __restrict__ rows, int rows_per_seq, int n_q_heads, float scale_log2e,
+                        int chunk, int n_splits, float* __restrict__ part_o, float2* __restrict__ part_ml,
+                        uint32_t* __restrict__ err) {
+    constexpr int CH = HD / 8;    // 16-byte chunks per token row
+    constexpr int KS = HD / 16;   // k steps of S = Q K^T
+    constexpr int NO = HD / 8;    // n tiles of O
+    constexpr int TILE_BYTES = TILE_TOKENS * HD * 2;
+    extern __shared__ __align__(128) uint8_t smem[];  // [2 stages][K tile | V tile]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int mt = warp >> 1, th = warp & 1;
+    const int nkv = kv.kv_heads, G = n_q_heads / nkv;
+    const int n_queries = rows_per_seq * G;
+    const int n_qpairs = (n_queries + 31) / 32;
+    const int split = blockIdx.x;
+    const int kvh = blockIdx.y / n_qpairs, qpair = blockIdx.y % n_qpairs;
+    const int row_first = blockIdx.z * rows_per_seq;
+
+    pdl_wait();
+    const tsb_row_desc rd0 = rows[row_first];
+    const int seq = rd0.seq, base = rd0.base;
+    const int L = base + rows_per_seq;
+    const int t_begin = split * chunk;
+    const int t_end = min(L, t_begin + chunk);
+    if (t_begin >= t_end) return;  // the merge kernel knows how many chunks this stream has
+    if (seq < 0 || seq >= kv.max_seqs) {
+        if (threadIdx.x == 0) atomicCAS(err, 0u, (uint32_t)TSB_DEV_BAD_INDEX);
+        return;
+    }
+    const int n_tiles = (t_end - t_begin + TILE_TOKENS - 1) / TILE_TOKENS;
+
+    // ---- this lane's two queries (rows gid and gid+8 of the warp's mma tile)
+    const int q0 = qpair * 32 + mt * 16 + gid, q1 = q0 + 8;
+    const bool v0 = q0 < n_queries, v1 = q1 < n_queries;
+    const int r0 = v0 ? q0 / G : 0, r1 = v1 ? q1 / G : 0;
+    const int h0 = kvh * G + (v0 ? q0 % G : 0), h1 = kvh * G + (v1 ? q1 % G : 0);
+    uint64_t mask0[2] = {0, 0}, mask1[2] = {0, 0};
+    if (v0) mask0[0] = rows[row_first + r0].mask[0], mask0[1] = rows[row_first + r0].mask[1];
+    if (v1) mask1[0] = rows[row_first + r1].mask[0], mask1[1] = rows[row_first + r1].mask[1];
+
+    uint32_t qa[KS][4];
+    {
+        const __half* p0 = q + (size_t)(row_first + r0) * q_stride + (size_t)h0 * HD;
+        const __half* p1 = q + (size_t)(row_first + r1) * q_stride + (size_t)h1 * HD;
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+            qa[ks][0] = *reinterpret_cast<const uint32_t*>(p0 + 16 * ks + 2 * tig);
+            qa[ks][1] = *reinterpret_cast<const uint32_t*>(p1 + 16 * ks + 2 * tig);
+            qa[ks][2] = *reinterpret_cast<const uint32_t*>(p0 + 16 * ks + 8 + 2 * tig);
+            qa[ks][3] = *reinterpret_cast<const uint32_t*>(p1 + 16 * ks + 8 + 2 * tig);
+        }
+    }
+
+    float o[NO][4];
+#pragma unroll
+    for (int n = 0; n < NO; n++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) o[n][i] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    const uint32_t smem_base = smem_u32(smem);
+    auto issue_tile = [&](int tile, int stage) {
+        const int t0 = t_begin + tile * TILE_TOKENS;
+        const uint32_t kdst = smem_base + stage * 2 * TILE_BYTES, vdst = kdst + TILE_BYTES;
+#pragma unroll
+        for (int i = 0; i < TILE_TOKENS * CH / ATT_THREADS; i++) {
+            const int idx = threadIdx.x + i * ATT_THREADS;
+            const int r = idx / CH, c = idx % CH;
+            const int pos = t0 + r;
+            const bool valid = pos < t_end;
+            const __half* kr = valid ? kv_row(kv, layer, 0, seq, pos) : nullptr;
+            const __half* vr = valid ? kv_row(kv, layer, 1, seq, pos) : nullptr;
+            const bool ok = kr != nullptr && vr != nullptr;
+            const uint32_t off = tile_off<HD>(r, c);
+            cp_async16_zfill(kdst + off, ok ? (const void*)(kr + (size_t)kvh * HD + c * 8) : (const void*)kv.pool, ok);
+            cp_async16_zfill(vdst + off, ok ? (const void*)(vr + (size_t)kvh * HD + c * 8) : (const void*)kv.pool, ok);
+        }
+        cp_async_commit();
+    };
+
+    issue_tile(0, 0);
+    for (int tile = 0; tile < n_tiles; tile++) {
+        const int stage = tile & 1;
+        if (tile + 1 < n_tiles) {
+            issue_tile(tile + 1, stage ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const uint32_t ktile = smem_base + stage * 2 * TILE_BYTES, vtile = ktile + TILE_BYTES;
+        const int tok0 = th * 32;  // this warp's 32 tokens of the tile
+        const int pos0 = t_begin + tile * TILE_TOKENS + tok0;
+
+        // ---- S = Q K^T for 16 queries x 32 tokens
+        float s[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) s[nt][i] = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+#pragma unroll
+            for (int kp = 0; kp < KS / 2; kp++) {
+                uint32_t b[4];
+                const int r = tok0 + nt * 8 + (lane & 7);
+                const int c = kp * 4 + (lane >> 3);
+                ldmatrix_x4(b, ktile + tile_off<HD>(r, c));
+                const uint32_t b01[2] = {b[0], b[1]}, b23[2] = {b[2], b[3]};
+                mma_16816(s[nt], qa[2 * kp], b01);
+                mma_16816(s[nt], qa[2 * kp + 1], b23);
+            }
+        }
+        // ---- scale, mask, online softmax
+        const bool need_mask = pos0 + 32 > base;
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                float v = s[nt][i] * scale_log2e;
+                if (need_mask) {
+                    const int p = pos0 + nt * 8 + 2 * tig + (i & 1);
+                    const int j = p - base;
+                    bool vis = j < 0;
+                    if (j >= 0 && j < 128) {
+                        const uint64_t w = (i < 2) ? mask0[j >> 6] : mask1[j >> 6];
+                        vis = (w >> (j & 63)) & 1ull;
+                    }
+                    if (!vis) v = -INFINITY;
+                }
+                s[nt][i] = v;
+                mx[i >> 1] = fmaxf(mx[i >> 1], v);
+            }
+        float alpha[2], m_use[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+            const float m_new = fmaxf(m_run[h], mx[h]);
+            m_use[h] = (m_new == -INFINITY) ? 0.f : m_new;
+            alpha[h] = exp2f(m_run[h] - m_use[h]);  // 0 when m_run is -inf
+            m_run[h] = m_new;
+        }
+        float rs[2] = {0.f, 0.f};
+        uint32_t pa[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+            const float p0 = exp2f(s[nt][0] - m_use[0]), p1 = exp2f(s[nt][1] - m_use[0]);
+            const float p2 = exp2f(s[nt][2] - m_use[1]), p3 = exp2f(s[nt][3] - m_use[1]);
+            rs[0] += p0 + p1;
+            rs[1] += p2 + p3;
+            pa[nt >> 1][(nt & 1) * 2 + 0] = pack_half2(p0, p1);
+            pa[nt >> 1][(nt & 1) * 2 + 1] = pack_half2(p2, p3);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 1);
+            rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 2);
+            l_run[h] = l_run[h] * alpha[h] + rs[h];
+        }
+#pragma unroll
+        for (int n = 0; n < NO; n++) {
+            o[n][0] *= alpha[0];
+            o[n][1] *= alpha[0];
+            o[n][2] *= alpha[1];
+            o[n][3] *= alpha[1];
+        }
+        // ---- O += P V
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++) {
+#pragma unroll
+            for (int np = 0; np < NO / 2; np++) {
+                uint32_t b[4];
+                const int r = tok0 + kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                const int c = np * 2 + (lane >> 4);
+                ldmatrix_x4_trans(b, vtile + tile_off<HD>(r, c));
+                const uint32_t b01[2] = {b[0], b[1]}, b23[2] = {b[2], b[3]};
+                mma_16816(o[2 * np], pa[kk], b01);
+                mma_16816(o[2 * np + 1], pa[kk], b23);
+            }
+        }
+        __syncthreads();  // both stages are rewritten only after every warp is done with this one
+    }
+    pdl_launch_dependents();
+
+    // ---- merge the two token halves of each query tile, then write the partial
+    float* mbuf = reinterpret_cast<float*>(smem);  // [2 tiles][32 lanes][NO*4 + 4]
+    constexpr int MB = NO * 4 + 4;
+    if (th == 1) {
+        float* dst = mbuf + ((size_t)mt * 32 + lane) * MB;
+#pragma unroll
+        for (int n = 0; n < NO; n++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) dst[n * 4 + i] = o[n][i];
+        dst[NO * 4 + 0] = m_run[0];
+        dst[NO * 4 + 1] = m_run[1];
+        dst[NO * 4 + 2] = l_run[0];
+        dst[NO * 4 + 3] = l_run[1];
+    }
+    __syncthreads();
+    if (th == 0) {
+        const float* src = mbuf + ((size_t)mt * 32 + lane) * MB;
+        float wa[2], wb[2], m_out[2], l_out[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const float mb = src[NO * 4 + h], lb = src[NO * 4 + 2 + h];
+            const float m_new = fmaxf(m_run[h], mb);
+            const float mu = (m_new == -INFINITY) ? 0.f : m_new;
+            wa[h] = exp2f(m_run[h] - mu);
+            wb[h] = exp2f(mb - mu);
+            m_out[h] = m_new;
+            l_out[h] = l_run[h] * wa[h] + lb * wb[h];
+        }
+        const size_t i0 = ((size_t)(row_first + r0) * n_q_heads + h0) * n_splits + split;
+        const size_t i1 = ((size_t)(row_first + r1) * n_q_heads + h1) * n_splits + split;
+#pragma unroll
+        for (int n = 0; n < NO; n++) {
+            const float a0 = o[n][0] * wa[0] + src[n * 4 + 0] * wb[0], a1 = o[n][1] * wa[0] + src[n * 4 + 1] * wb[0];
+            const float a2 = o[n][2] * wa[1] + src[n * 4 + 2] * wb[1], a3 = o[n][3] * wa[1] + src[n * 4 + 3] * wb[1];
+            if (v0) *reinterpret_cast<float2*>(part_o + i0 * HD + n * 8 + 2 * tig) = make_float2(a0, a1);
+            if (v1) *reinterpret_cast<float2*>(part_o + i1 * HD + n * 8 + 2 * tig) = make_float2(a2, a3);
+        }
+        if (tig == 0) {
+            if (v0) part_ml[i0] = make_float2(m_out[0], l_out[0]);
+            if (v1) part_ml[i1] = make_float2(m_out[1], l_out[1]);
+        }
+    }
+}
+
+// Merge the chunk partials: out = sum_c O_c 2^(m_c - m) / sum_c l_c 2^(m_c - m)
+// (crates/gpu/src/shaders/attention.metal:983-1031).  One thread per eight
+// head_dim elements of one (row, q head).
+template <int HD>
+__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float2* __restrict__ part_ml,
+                                  const tsb_row_desc* __restrict__ rows, int n_rows, int rows_per_seq, int n_q_heads,
+                                  int chunk, int n_splits, __half* __restrict__ out, ActOut act) {
+    pdl_wait();
+    constexpr int TPH = HD / 8;  // threads per head
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool active = idx < (int64_t)n_rows * n_q_heads * TPH;
+    const int part = active ? (int)(idx % TPH) : 0;
+    const int rh = active ? (int)(idx / TPH) : 0;
+    const int row = rh / n_q_heads, head = rh % n_q_heads;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[i] = 0.f;
+    if (active) {
+        const int L = rows[(row / rows_per_seq) * rows_per_seq].base + rows_per_seq;
+        const int ns = min(n_splits, (L + chunk - 1) / chunk);
+        const float2* ml = part_ml + (size_t)rh * n_splits;
+        float m = -INFINITY;
+        for (int c = 0; c < ns; c++) m = fmaxf(m, ml[c].x);
+        const float mu = (m == -INFINITY) ? 0.f : m;
+        float den = 0.f;
+        for (int c = 0; c < ns; c++) {
+            const float2 v = ml[c];
+            const float w = exp2f(v.x - mu);
+            den += v.y * w;
+            const float4* po = reinterpret_cast<const float4*>(part_o + ((size_t)rh * n_splits + c) * HD + part * 8);
+            const float4 a = po[0], b = po[1];
+            acc[0] += a.x * w, acc[1] += a.y * w, acc[2] += a.z * w, acc[3] += a.w * w;
+            acc[4] += b.x * w, acc[5] += b.y * w, acc[6] += b.z * w, acc[7] += b.w * w;
+        }
+        const float inv = den > 0.f ? 1.0f / den : 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc[i] *= inv;
+    }
+    pdl_launch_dependents();
+    const int e0 = head * HD + part * 8;
+    if (out && active) {
+        uint4 pk;
+        __half* pp = reinterpret_cast<__half*>(&pk);
+#pragma unroll
+        for (int i = 0; i < 8; i++) pp[i] = __float2half_rn(acc[i]);
+        *reinterpret_cast<uint4*>(out + (size_t)row * n_q_heads * HD + e0) = pk;
+    }
+    if (act.xp) act_store8(acc, act.xp, act.xs, row, e0, (n_q_heads * HD) >> 8, active);
+}
+
+}  // namespace
+
+AttnPlan attn_plan(const tsb_ctx* ctx, const tsb_kv* kv, int rows, int rows_per_seq, int n_q_heads, int max_len) {
+    AttnPlan p;
+    const int G = n_q_heads / kv->view.kv_heads;
+    const int n_qpairs = (rows_per_seq * G + 31) / 32;
+    const int groups = rows / rows_per_seq;
+    const int tiles_total = (max_len + TILE_TOKENS - 1) / TILE_TOKENS;
+    const int base_ctas = groups * kv->view.kv_heads * n_qpairs;
+    int splits = (2 * ctx->sm_count + base_ctas - 1) / base_ctas;
+    splits = splits < 1 ? 1 : splits;
+    if (splits > MAX_SPLITS) splits = MAX_SPLITS;
+    if (splits > tiles_total) splits = tiles_total > 0 ? tiles_total : 1;
+    const int tiles_per = (tiles_total + splits - 1) / splits;
+    p.chunk = (tiles_per < 1 ? 1 : tiles_per) * TILE_TOKENS;
+    p.n_splits = (max_len + p.chunk - 1) / p.chunk;
+    if (p.n_splits < 1) p.n_splits = 1;
+    p.n_qpairs = n_qpairs;
+    p.groups = groups;
+    return p;
+}
+
+size_t attn_scratch_bytes(int rows, int n_q_heads, int head_dim) {
+    return (size_t)rows * n_q_heads * MAX_SPLITS * ((size_t)head_dim * sizeof(float) + sizeof(float2));
+}
+
+cudaError_t launch_attn_decode_rows(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, int layer, const __half* q, int64_t q_stride,
+                                    __half* out, ActOut act, const tsb_row_desc* rows_dev, int rows, int rows_per_seq,
+                                    int n_q_heads, float scale, int max_len, void* scratch) {
+    const AttnPlan p = attn_plan(ctx, kv, rows, rows_per_seq, n_q_heads, max_len);
+    const int hd = kv->view.head_dim;
+    float* part_o = reinterpret_cast<float*>(scratch);
+    float2* part_ml = reinterpret_cast<float2*>(part_o + (size_t)rows * n_q_heads * p.n_splits * hd);
+    const float scale_log2e = scale * 1.4426950408889634f;
+    dim3 grid((unsigned)p.n_splits, (unsigned)(kv->view.kv_heads * p.n_qpairs), (unsigned)p.groups);
+    const size_t smem = (size_t)2 * 2 * TILE_TOKENS * hd * sizeof(__half);
+    cudaError_t e;
+    static bool configured[2] = {false, false};
+    if (hd == 128) {
+        if (!configured[1]) {
+            e = cudaFuncSetAttribute(attn_partial_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return e;
+            configured[1] = true;
+        }
+        e = tsb_launch(ctx, attn_partial_kernel<128>, grid, dim3(ATT_THREADS), smem, st, true, kv->view, layer, q, q_stride,
+                       rows_dev, rows_per_seq, n_q_heads, scale_log2e, p.chunk, p.n_splits, part_o, part_ml, ctx->dev_error);
+    } else {
+        if (!configured[0]) {
+            e = cudaFuncSetAttribute(attn_partial_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return e;
+            configured[0] = true;
+        }
+        e = tsb_launch(ctx, attn_partial_kernel<64>, grid, dim3(ATT_THREADS), smem, st, true, kv->view, layer, q, q_stride,
+                       rows_dev, rows_per_seq, n_q_heads, scale_log2e, p.chunk, p.n_splits, part_o, part_ml, ctx->dev_error);
+    }
+    if (e != cudaSuccess) return e;
+    const int64_t threads = (int64_t)rows * n_q_heads * (hd / 8);
+    dim3 mgrid((unsigned)((threads + 127) / 128));
+    if (hd == 128)
+        return tsb_launch(ctx, attn_merge_kernel<128>, mgrid, dim3(128), 0, st, true, (const float*)part_o,
+                          (const float2*)part_ml, rows_dev, rows, rows_per_seq, n_q_heads, p.chunk, p.n_splits, out, act);
+    return tsb_launch(ctx, attn_merge_kernel<64>, mgrid, dim3(128), 0, st, true, (const float*)part_o,
+                      (const float2*)part_ml, rows_dev, rows, rows_per_seq, n_q_heads, p.chunk, p.n_splits, out, act);
+}
+
+extern "C" {
+
+size_t tsb_attn_scratch_bytes(int32_t rows, int32_t n_q_heads, int32_t head_dim) {
+    if (rows <= 0 || n_q_heads <= 0 || head_dim <= 0) return 0;
+    return attn_scratch_bytes(rows, n_q_heads, head_dim);
+}
+
+int32_t tsb_attn_decode_rows(tsb_ctx* ctx, tsb_stream s, tsb_kv* kv, int32_t layer, const void* q_f16, int64_t q_stride,
+                             void* out_f16, const tsb_row_desc* rows_dev, int32_t rows, int32_t rows_per_seq,
+                             int32_t n_q_heads, float scale, int32_t max_len, void* scratch, size_t scratch_bytes) {
+    if (!ctx || !kv) return TSB_ERR_INVALID;
+    TSB_REQUIRE(ctx, q_f16 && out_f16 && rows_dev && scratch, "null buffer");
+    TSB_REQUIRE(ctx, rows > 0 && rows_per_seq > 0 && rows % rows_per_seq == 0, "rows must be a whole number of streams");
+    TSB_REQUIRE(ctx, rows_per_seq <= 128, "at most 128 in-flight rows per stream (mask width), got %d", rows_per_seq);
+    TSB_REQUIRE(ctx, layer >= 0 && layer < kv->view.layers, "layer %d outside 0..%d", layer, kv->view.layers);
+    TSB_REQUIRE(ctx, n_q_heads > 0 && n_q_heads % kv->view.kv_heads == 0, "n_q_heads must be a multiple of the kv heads");
+    TSB_REQUIRE(ctx, (n_q_heads * kv->view.head_dim) % 256 == 0, "n_q_heads * head_dim must be a multiple of 256");
+    TSB_REQUIRE(ctx, q_stride >= (int64_t)n_q_heads * kv->view.head_dim && q_stride % 2 == 0, "q_stride smaller than a row");
+    // the longest stream bounds what the kernel may read; computed in 64 bits so it cannot wrap
+    const int64_t reach = (int64_t)max_len;
+    TSB_REQUIRE(ctx, reach >= rows_per_seq && reach <= (int64_t)kv->view.max_pages_per_seq * kv->view.page_tokens,
+                "max_len %lld outside the cache (%lld positions per stream)", (long long)reach,
+                (long long)kv->view.max_pages_per_seq * kv->view.page_tokens);
+    TSB_REQUIRE(ctx, scratch_bytes >= attn_scratch_bytes(rows, n_q_heads, kv->view.head_dim), "scratch too small");
+    DeviceGuard g(ctx);
+    TSB_CUDA(ctx, launch_attn_decode_rows(ctx, (cudaStream_t)s, kv, layer, (const __half*)q_f16, q_stride, (__half*)out_f16,
+                                          ActOut{nullptr, nullptr}, rows_dev, rows, rows_per_seq, n_q_heads, scale, max_len,
+                                          scratch));
+    return TSB_OK;
+}
+
+}  // extern "C"
