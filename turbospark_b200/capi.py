@@ -204,6 +204,20 @@ class Ctx:
                                               C.c_int32(n_q_heads), C.c_float(scale), C.c_int32(max_len), _vp(scratch),
                                               C.c_size_t(scratch.nbytes)))
 
+    def accept_scratch_bytes(self, batch, k, vocab):
+        return int(lib().tsb_accept_scratch_bytes(C.c_int32(batch), C.c_int32(k), C.c_int32(vocab)))
+
+    def accept(self, target_logits, draft_logits, proposals, uniforms, batch, k, vocab, shaping_cfg, out, scratch,
+               stream=None):
+        self.check(lib().tsb_accept(self.h, stream, _vp(target_logits), _vp(draft_logits), _vp(proposals), _vp(uniforms),
+                                    C.c_int32(batch), C.c_int32(k), C.c_int32(vocab), C.byref(shaping_cfg), _vp(out),
+                                    _vp(scratch), C.c_size_t(scratch.nbytes)))
+
+    def sample(self, logits, uniforms, batch, vocab, shaping_cfg, tokens, margins, scratch, stream=None):
+        self.check(lib().tsb_sample(self.h, stream, _vp(logits), _vp(uniforms), C.c_int32(batch), C.c_int32(vocab),
+                                    C.byref(shaping_cfg), _vp(tokens), _vp(margins), _vp(scratch),
+                                    C.c_size_t(scratch.nbytes)))
+
     def residual_add(self, x, y, n, stream=None):
         self.check(lib().tsb_residual_add(self.h, stream, _vp(x), _vp(y), C.c_int64(n)))
 
