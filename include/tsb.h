@@ -263,6 +263,111 @@ TSB_API int32_t tsb_sample(tsb_ctx* ctx, tsb_stream s, const void* logits_f16, c
  * mode 1 = Philox4x32-10 keyed by seed with counter = step (this backend's addition). */
 TSB_API uint64_t tsb_uniform_u64(int32_t mode, uint64_t seed, uint64_t step);
 
+/* ------------------------------------------------------ model and producer */
+
+/* A dense Llama-style decoder (RMSNorm -> q/k/v -> RoPE -> attention -> o_proj -> residual -> RMSNorm ->
+ * gate/up -> SiLU*up -> down -> residual; final RMSNorm + lm_head): the op order of
+ * crates/runtime/src/families/llama/mod.rs:205-291 and dense.rs:48-120. */
+typedef struct tsb_model_config {
+    int32_t n_layers, d_model, n_q_heads, n_kv_heads, head_dim, ffn, vocab, max_context;
+    float rms_eps, rope_theta;
+} tsb_model_config;
+
+enum { TSB_W_Q = 0, TSB_W_K, TSB_W_V, TSB_W_O, TSB_W_GATE, TSB_W_UP, TSB_W_DOWN, TSB_W_EMBED, TSB_W_LM_HEAD };
+enum { TSB_N_ATTN = 0, TSB_N_FFN, TSB_N_OUT };
+
+TSB_API int32_t tsb_model_create(tsb_ctx* ctx, const tsb_model_config* cfg, tsb_model** out);
+TSB_API void tsb_model_destroy(tsb_model* m);
+/* Upload one matrix as verbatim block rows (rows x cols, row-major rows of blocks).  q, k and v of a
+ * layer must share a format, as must gate and up: they are laid out back to back and run as one matmul.
+ * layer is ignored for TSB_W_EMBED / TSB_W_LM_HEAD.  A model may point its embedding and head at another
+ * model's tensors with tsb_model_share (a drafter sharing the trunk's tables). */
+TSB_API int32_t tsb_model_set_matrix(tsb_model* m, int32_t layer, int32_t which, int32_t qtype,
+                                     const void* host_blocks, int64_t rows, int64_t cols);
+TSB_API int32_t tsb_model_set_norm(tsb_model* m, int32_t layer, int32_t which, const void* host_bf16, int32_t n);
+/* dst layer `dst_layer` uses src layer `src_layer`'s tensors (no copy); layer < 0 shares embedding, final
+ * norm and head.  src must outlive dst. */
+TSB_API int32_t tsb_model_share(tsb_model* dst, int32_t dst_layer, const tsb_model* src, int32_t src_layer);
+/* Fill every tensor with seeded synthetic blocks directly on the device (benchmark set-up: weights of the
+ * right shapes and formats without a host copy; values are valid blocks with small scales). */
+TSB_API int32_t tsb_model_fill_synthetic(tsb_model* m, int32_t qtype, int32_t lm_head_qtype, uint64_t seed);
+TSB_API int64_t tsb_model_weight_bytes(const tsb_model* m);
+
+/* A session = the producer: a target model, an optional stand-alone draft model, paged K/V caches for
+ * `n_streams` independent request streams, and every activation / logits / scratch buffer a round
+ * needs for up to `max_rows` rows per stream.  Mirrors what RealForwardRunner owns
+ * (crates/runtime/src/real_forward_traits.rs:6-60). */
+TSB_API int32_t tsb_session_create(tsb_ctx* ctx, const tsb_model* target, const tsb_model* draft, int32_t n_streams,
+                                   int32_t max_rows, int32_t page_tokens, tsb_session** out);
+TSB_API void tsb_session_destroy(tsb_session* s);
+TSB_API tsb_kv* tsb_session_kv(tsb_session* s, int32_t which_model /* 0 target, 1 draft */);
+/* Number of kernel launches / CUDA-graph launches issued so far by this session's ctx is tsb_launch_count. */
+
+/* LogitProducer / SpeculativeProducer, one stream at a time (crates/runtime/src/producer.rs:17-104,164-387).
+ * logits_out_host: vocab f16 values per row, or NULL to leave them on the device.  Errors keep the
+ * reference's contract: a call that violates the cursor is refused and changes nothing. */
+TSB_API int32_t tsb_producer_reset(tsb_session* s, int32_t stream);
+TSB_API int32_t tsb_producer_produce(tsb_session* s, int32_t stream, int32_t token, int64_t position, void* logits_out_host);
+TSB_API int32_t tsb_producer_produce_prefill(tsb_session* s, int32_t stream, int32_t token, int64_t position);
+TSB_API int32_t tsb_producer_prime_drafter(tsb_session* s, int32_t stream, int32_t next, int64_t position);
+TSB_API int32_t tsb_producer_draft_step(tsb_session* s, int32_t stream, int32_t next, int64_t position, void* logits_out_host);
+TSB_API int32_t tsb_producer_verify(tsb_session* s, int32_t stream, const int32_t* feed, int32_t n, int64_t base,
+                                    void* logits_out_host);
+/* verify_tree: feed[0] is the anchor, slot_parent[0] = -1 and parents precede children
+ * (crates/runtime/src/families/qwen/batched_scratch.rs:97-124). */
+TSB_API int32_t tsb_producer_verify_tree(tsb_session* s, int32_t stream, const int32_t* feed, const int32_t* slot_parent,
+                                         int32_t n, int64_t base, void* logits_out_host);
+TSB_API int32_t tsb_producer_compact_tree(tsb_session* s, int32_t stream, int64_t base, const uint32_t* path, int32_t keep);
+TSB_API int64_t tsb_producer_checkpoint(tsb_session* s, int32_t stream);
+TSB_API int32_t tsb_producer_rollback(tsb_session* s, int32_t stream, int64_t point);
+TSB_API int32_t tsb_producer_rollback_retaining(tsb_session* s, int32_t stream, int64_t point, int32_t keep_rows);
+TSB_API int32_t tsb_producer_rewind_drafter(tsb_session* s, int32_t stream, int64_t position);
+
+/* Generation settings of the round loop (crates/runtime/src/config.rs GenerationConfig, reduced to what
+ * the loop reads without a tokenizer). */
+typedef struct tsb_run_config {
+    tsb_shaping shaping;
+    int32_t max_new_tokens;
+    int32_t block;        /* proposals per round, 1..=15 (crates/core/src/runtime_config.rs:43) */
+    int32_t uniform_mode; /* 0 derive_step_value, 1 Philox4x32-10 */
+    int32_t n_stop;
+    int32_t stop_tokens[8];
+    int32_t adaptive;     /* 0 = fixed depth, else the adaptive controller's floor */
+} tsb_run_config;
+
+typedef struct tsb_run_result {
+    int32_t new_tokens, reason /* 0 max tokens, 1 stop token */, rounds, accepted_total, rollbacks, history_len;
+    int64_t kv_position;
+    uint64_t draws;
+    double prefill_seconds, decode_seconds;
+} tsb_run_result;
+
+/* run_raw_completion_speculative (crates/runtime/src/speculative.rs:54-940) for one stream: prefill,
+ * then rounds of draft / verify / accept / rollback / commit with the acceptance on the device.
+ * out_tokens receives prompt + committed history (kv_backed_token_ids), out_emitted every generated
+ * token (the stopping one included).  Refuses an empty prompt, a zero budget, prompt + budget beyond the
+ * context window and block == 0, as the reference does (crates/runtime/src/raw_completion.rs:126-146,
+ * speculative.rs:208-212). */
+TSB_API int32_t tsb_spec_run(tsb_session* s, int32_t stream, const int32_t* prompt, int32_t n_prompt,
+                             const tsb_run_config* cfg, int32_t* out_tokens, int32_t* out_emitted, tsb_run_result* res);
+/* run_raw_completion (crates/runtime/src/raw_completion.rs:300-420): the sequential loop the speculative
+ * one must reproduce token for token at temperature 0. */
+TSB_API int32_t tsb_sequential_run(tsb_session* s, int32_t stream, const int32_t* prompt, int32_t n_prompt,
+                                   const tsb_run_config* cfg, int32_t* out_tokens, int32_t* out_emitted, tsb_run_result* res);
+
+/* One speculative round for every stream of the session in lockstep (the benchmark's step and the
+ * serving inner loop): k draft steps + the row-only step, one batched verify of k+1 rows per stream, the
+ * acceptance kernel, cursor commit.  next_tokens_host[stream] is the confirmed token entering the
+ * round and receives the token entering the next one; accepted_host[stream] receives the accepted count.
+ * Streams must have equal cursors in the target and draft caches (lockstep). */
+TSB_API int32_t tsb_session_round(tsb_session* s, const tsb_run_config* cfg, int32_t* next_tokens_host,
+                                  int32_t* accepted_host, uint64_t* draw_step_inout);
+/* Timings of the last tsb_session_round in milliseconds: draft, verify, accept, commit (CUDA events). */
+TSB_API int32_t tsb_session_round_times(tsb_session* s, float* out4_ms);
+/* Benchmark set-up: pretend `tokens` positions are committed in both caches of every stream, filling
+ * them with seeded pseudo-random K/V. */
+TSB_API int32_t tsb_session_fill_context(tsb_session* s, int64_t tokens, uint64_t seed);
+
 #ifdef __cplusplus
 }
 #endif

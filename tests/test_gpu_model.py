@@ -1,0 +1,185 @@
+"""The producer (forward pass), the round loop and the generation loops on the GPU against the CPU oracle,
+on the CPU-runnable tiny configuration: 4-layer Llama-style target, draft = its first 2 layers + shared head."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+REL, ABS = 2e-3, 1e-3
+
+
+@pytest.fixture(scope="module")
+def rig(oracle):
+    import turbospark_b200 as tsb
+    ctx = tsb.Ctx(0)
+    cfg = tsb.config_tiny(max_context=512)
+    dcfg = tsb.ModelConfig(2, cfg.d_model, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.vocab, cfg.max_context,
+                           cfg.rms_eps, cfg.rope_theta)
+    mats, norms = tsb.random_weights(cfg, 0, oracle, real_ffn=1408)
+    target = tsb.Model(ctx, cfg)
+    tsb.load_weights(target, mats, norms)
+    draft = tsb.Model(ctx, dcfg)
+    for l in range(2):
+        draft.share(l, target, l)
+    draft.share(-1, target, -1)
+    # the oracle's copies
+    ocfg = oracle.ModelCfg(cfg.n_layers, cfg.d_model, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.vocab,
+                           cfg.max_context, cfg.rms_eps, cfg.rope_theta)
+    odcfg = oracle.ModelCfg(2, cfg.d_model, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.vocab, cfg.max_context,
+                            cfg.rms_eps, cfg.rope_theta)
+    ot = oracle.Model(ocfg, threads=8)
+    tsb.load_weights(ot, mats, norms)
+    od = oracle.Model(odcfg, threads=8)
+    tsb.load_weights(od, mats, norms, layers=2)
+    yield dict(ctx=ctx, cfg=cfg, target=target, draft=draft, ot=ot, od=od, tsb=tsb)
+    target.close(), draft.close(), ctx.close()
+
+
+def _close(oracle, got16, want16, rel=REL, abs_=ABS):
+    got, want = oracle.f16_bits_to_f32(got16), oracle.f16_bits_to_f32(want16)
+    assert not np.isnan(got).any()
+    err = np.abs(got - want)
+    assert np.all(err <= abs_ + rel * np.abs(want)), float(err.max())
+
+
+def test_decode_and_verify_logits_match_the_oracle_forward(rig, oracle):
+    tsb = rig["tsb"]
+    sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 8)
+    ost = oracle.State(rig["ot"])
+    rng = np.random.default_rng(1)
+    prompt = rng.integers(0, rig["cfg"].vocab, size=12).astype(np.int32)
+    # token-by-token decode
+    for i, t in enumerate(prompt):
+        got = sess.produce(int(t), i)
+        want = ost.forward([int(t)], i)[0]
+        _close(oracle, got, want, rel=4e-3, abs_=4e-3)  # f16 rounding points compound over 4 layers
+    # a 6-row verify at the cursor must equal decoding the same rows one by one, bit for bit
+    feed = rng.integers(0, rig["cfg"].vocab, size=6).astype(np.int32)
+    point = sess.checkpoint()
+    batch = sess.verify(feed, point)
+    sess.rollback_retaining(point, 0)
+    single = np.stack([sess.produce(int(t), point + i) for i, t in enumerate(feed)])
+    assert np.array_equal(batch, single)
+    want = ost.forward(feed, point)
+    _close(oracle, batch, want, rel=4e-3, abs_=4e-3)
+    # the cursor contract: a position that does not continue the cache is refused and changes nothing
+    with pytest.raises(tsb.TsbError):
+        sess.produce(1, point)
+    assert sess.checkpoint() == point + 6
+    sess.close()
+
+
+def test_tree_verify_matches_the_oracle_and_compaction_restores_a_chain(rig, oracle):
+    tsb = rig["tsb"]
+    sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 8)
+    ost = oracle.State(rig["ot"])
+    rng = np.random.default_rng(2)
+    prompt = rng.integers(0, rig["cfg"].vocab, size=20).astype(np.int32)
+    for i, t in enumerate(prompt):
+        sess.produce_prefill(int(t), i)
+    ost.forward(prompt, 0, want_logits=False)
+    parent = [-1, 0, 1, 2, 3, 0, 5, 2]
+    feed = rng.integers(0, rig["cfg"].vocab, size=8).astype(np.int32)
+    base = sess.checkpoint()
+    got = sess.verify_tree(feed, parent, base)
+    want = ost.forward(feed, base, parent=parent)
+    _close(oracle, got, want, rel=4e-3, abs_=4e-3)
+    # accept the branch 0 -> 5 -> 6, compact it to rows 0..2 and continue as a chain
+    sess.compact_tree(base, [0, 5, 6])
+    sess.rollback_retaining(base, 3) if False else None  # the tree verify did not advance past base + 8
+    sess.kv(0).set_cursor(0, base + 3)
+    ost.cursor = base
+    ost.forward([int(feed[0]), int(feed[5]), int(feed[6])], base)
+    nxt = 77
+    _close(oracle, sess.produce(nxt, base + 3), ost.forward([nxt], base + 3)[0], rel=4e-3, abs_=4e-3)
+    sess.close()
+
+
+@pytest.mark.parametrize("block", [1, 4])
+def test_greedy_speculative_equals_greedy_sequential_token_for_token(rig, oracle, block):
+    tsb = rig["tsb"]
+    sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 16)
+    rng = np.random.default_rng(1)
+    prompt = rng.integers(0, rig["cfg"].vocab, size=32).astype(np.int32)
+    rc = tsb.run_config(tsb.shaping(temperature=0.0), 48, block)
+    seq_hist, seq_emit, seq_res = sess.sequential_run(prompt, rc)
+    spec_hist, spec_emit, spec_res = sess.spec_run(prompt, rc)
+    assert np.array_equal(seq_emit, spec_emit) and np.array_equal(seq_hist, spec_hist)
+    assert spec_res.new_tokens == 48 and spec_res.reason == 0 and spec_res.kv_position == spec_res.history_len
+    assert spec_res.rounds <= 48
+    # and against the CPU oracle's own loop over its own forward pass
+    orc = oracle.run_config(oracle.shaping(temperature=0.0), 48, block)
+    oh, oe, ores = oracle.run_speculative_model(oracle.State(rig["ot"]), oracle.State(rig["od"]), prompt, orc)
+    # token-identical up to the first near-tie: where the two streams part, the oracle's own logits must show
+    # the two candidates within the matmul tolerance of each other (a different summation order flipped an argmax)
+    n_same = 0
+    while n_same < len(oe) and oe[n_same] == spec_emit[n_same]:
+        n_same += 1
+    assert n_same >= 8, n_same
+    if n_same < len(oe):
+        ost = oracle.State(rig["ot"])
+        ctx_tokens = list(prompt) + [int(t) for t in oe[:n_same]]
+        lg = oracle.f16_bits_to_f32(ost.forward(ctx_tokens, 0)[-1])
+        gap = lg[int(oe[n_same])] - lg[int(spec_emit[n_same])]
+        assert 0 <= gap <= 2 * (4e-3 + 4e-3 * abs(lg[int(oe[n_same])])), (n_same, gap)
+    sess.close()
+
+
+def test_sampled_round_decisions_match_the_oracle_given_the_devices_logits(rig, oracle):
+    tsb = rig["tsb"]
+    ctx = rig["ctx"]
+    K = 4
+    sess = tsb.Session(ctx, rig["target"], rig["draft"], 1, K + 1)
+    rng = np.random.default_rng(3)
+    prompt = rng.integers(0, rig["cfg"].vocab, size=16).astype(np.int32)
+    for i, t in enumerate(prompt[:-1]):
+        sess.produce_prefill(int(t), i)
+    sess.produce(int(prompt[-1]), len(prompt) - 1)
+    sess.prime_drafter(int(prompt[-1]), len(prompt) - 2)
+    rc = tsb.run_config(tsb.shaping(temperature=1.0, seed=2), 64, K, uniform_mode=1)
+    nxt = np.array([123], dtype=np.int32)
+    steps = np.zeros(1, dtype=np.uint64)
+    ocfg = oracle.shaping(temperature=1.0, seed=2)
+    for rnd in range(6):
+        base = sess.checkpoint()
+        step0 = int(steps[0])
+        confirmed = int(nxt[0])
+        accepted = sess.round(rc, nxt, steps)[0]
+        # replay the round through the single-stream producer calls to obtain the logits the kernels saw
+        sess.kv(0).set_cursor(0, base)
+        sess.kv(1).set_cursor(0, base)
+        chained, props, dlogits = confirmed, [], []
+        for d in range(K):
+            lg = sess.draft_step(chained, base - 1 + d)
+            tok, _ = oracle.sample(lg, ocfg, oracle.uniform_u64(1, 2, step0 + d))
+            dlogits.append(lg), props.append(tok)
+            chained = tok
+        tlogits = sess.verify([confirmed] + props, base)
+        unis = [oracle.uniform_u64(1, 2, step0 + K + 1 + j) for j in range(2 * K + 1)]
+        acc, toks, draws, margins = oracle.accept_round(tlogits, np.stack(dlogits), props, ocfg, unis)
+        assert acc == accepted and toks[-1] == nxt[0], (rnd, acc, accepted, toks, nxt)
+        assert int(steps[0]) == step0 + K + 1 + draws
+        sess.kv(0).set_cursor(0, base + acc + 1)
+        sess.kv(1).set_cursor(0, base + acc + 1)
+    sess.close()
+
+
+def test_stop_token_budget_and_refusals(rig, oracle):
+    tsb = rig["tsb"]
+    sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 8)
+    rng = np.random.default_rng(5)
+    prompt = rng.integers(0, rig["cfg"].vocab, size=8).astype(np.int32)
+    rc = tsb.run_config(tsb.shaping(temperature=0.0), 24, 3)
+    _, emitted, _ = sess.sequential_run(prompt, rc)
+    stop_tok = int(emitted[9])
+    rc2 = tsb.run_config(tsb.shaping(temperature=0.0), 24, 3, stop_tokens=(stop_tok,))
+    h1, e1, r1 = sess.sequential_run(prompt, rc2)
+    h2, e2, r2 = sess.spec_run(prompt, rc2)
+    assert r1.reason == r2.reason == 1 and np.array_equal(e1, e2) and np.array_equal(h1, h2)
+    assert e2[-1] == stop_tok and len(h2) == len(prompt) + len(e2) - 1  # the stopping token is counted, not fed
+    for bad in (tsb.run_config(tsb.shaping(temperature=0.0), 24, 0), tsb.run_config(tsb.shaping(temperature=0.0), 0, 2),
+                tsb.run_config(tsb.shaping(temperature=0.0), 600, 2), tsb.run_config(tsb.shaping(temperature=0.7, top_k=64), 8, 2)):
+        with pytest.raises(tsb.TsbError):
+            sess.spec_run(prompt, bad)
+    with pytest.raises(tsb.TsbError):
+        sess.spec_run(np.zeros(0, np.int32), rc)
+    sess.close()

@@ -20,7 +20,7 @@
 // and total = sum_i w_i with w_i = ((e_i / sum) / top)^(1/T).
 // Kernel 2 (one CTA per stream): the accept chain on thread 0, then the one draw
 // the round needs (residual, or bonus from the last row) by the whole CTA.
-#include "common.cuh"
+#include "accept.cuh"
 
 namespace {
 
@@ -64,7 +64,7 @@ __device__ __forceinline__ double weight_of(double e, double sum, double top, do
 
 __global__ void __launch_bounds__(ACC_THREADS)
     accept_stats_kernel(const __half* __restrict__ target, const __half* __restrict__ draft, int k, int vocab,
-                        double temperature, RowStats* __restrict__ stats, int rows_per_stream, int target_only) {
+                        double temperature, RowStats* __restrict__ stats, int rows_per_stream, int64_t single_stride) {
     __shared__ double red[ACC_THREADS / 32];
     __shared__ float fred[ACC_THREADS / 32];
     __shared__ int ired[ACC_THREADS / 32];
@@ -72,8 +72,10 @@ __global__ void __launch_bounds__(ACC_THREADS)
     pdl_wait();
     const int b = blockIdx.x / rows_per_stream, r = blockIdx.x % rows_per_stream;
     // rows 0..k are the target's, k+1..2k the drafter's
-    const __half* row = (r <= k || target_only) ? target + ((size_t)b * (target_only ? rows_per_stream : (k + 1)) + r) * vocab
-                                                : draft + ((size_t)b * k + (r - k - 1)) * vocab;
+    // single_stride != 0: one row per stream, `single_stride` elements apart (the draft-side draw)
+    const __half* row = single_stride ? target + (size_t)b * single_stride
+                        : (r <= k)    ? target + ((size_t)b * (k + 1) + r) * vocab
+                                      : draft + ((size_t)b * k + (r - k - 1)) * vocab;
     if (threadIdx.x == 0) nf_flag = 0;
     __syncthreads();
     // pass A: max and first argmax, finiteness
@@ -298,9 +300,10 @@ __device__ __forceinline__ double unit_interval(uint64_t v) { return (double)(v 
 
 __global__ void __launch_bounds__(ACC_THREADS)
     accept_decide_kernel(const __half* __restrict__ target, const __half* __restrict__ draft,
-                         const int32_t* __restrict__ proposals, const uint64_t* __restrict__ uniforms, int k, int vocab,
-                         double temperature, const RowStats* __restrict__ stats, unsigned long long* __restrict__ scratch,
-                         tsb_accept_out* __restrict__ out) {
+                         const int32_t* __restrict__ proposals, int prop_stride, const uint64_t* __restrict__ uniforms,
+                         int k, int vocab, double temperature, const RowStats* __restrict__ stats,
+                         unsigned long long* __restrict__ scratch, tsb_accept_out* __restrict__ out,
+                         int32_t* __restrict__ next_tokens, int next_stride) {
     __shared__ DrawCtx c;
     __shared__ int s_accepted, s_draws, s_rejected, s_status;
     __shared__ double s_margin;
@@ -310,7 +313,7 @@ __global__ void __launch_bounds__(ACC_THREADS)
     const RowStats* st = stats + (size_t)b * rps;
     const __half* trows = target + (size_t)b * (k + 1) * vocab;
     const __half* drows = draft + (size_t)b * k * vocab;
-    const int32_t* prop = proposals + (size_t)b * k;
+    const int32_t* prop = proposals + (size_t)b * prop_stride;
     const uint64_t* un = uniforms + (size_t)b * rps;
     unsigned long long* fp = scratch + (size_t)b * vocab;
     const bool sampled = temperature != 0.0;
@@ -378,19 +381,21 @@ __global__ void __launch_bounds__(ACC_THREADS)
         o._pad = 0;
         o.margin_accept = s_margin;
         o.margin_draw = (double)(gap_lo < gap_hi ? gap_lo : gap_hi) / FP_ONE;
+        if (next_tokens) next_tokens[(size_t)b * next_stride] = token;
     }
 }
 
 // Draft-side draw: one CTA per stream, one row each.
 __global__ void __launch_bounds__(ACC_THREADS)
-    sample_kernel(const __half* __restrict__ logits, const uint64_t* __restrict__ uniforms, int vocab, double temperature,
-                  const RowStats* __restrict__ stats, unsigned long long* __restrict__ scratch, int32_t* __restrict__ tokens,
+    sample_kernel(const __half* __restrict__ logits, int64_t logits_stride, const uint64_t* __restrict__ uniforms,
+                  int uni_stride, int vocab, double temperature, const RowStats* __restrict__ stats,
+                  unsigned long long* __restrict__ scratch, int32_t* __restrict__ tokens, int token_stride,
                   double* __restrict__ margins, uint32_t* __restrict__ err) {
     __shared__ DrawCtx c;
     pdl_wait();
     const int b = blockIdx.x;
     const RowStats st = stats[b];
-    const __half* row = logits + (size_t)b * vocab;
+    const __half* row = logits + (size_t)b * logits_stride;
     int token;
     unsigned long long gap_lo = ~0ull, gap_hi = ~0ull;
     if (st.nonfinite) {
@@ -401,13 +406,13 @@ __global__ void __launch_bounds__(ACC_THREADS)
     } else {
         unsigned long long* fp = scratch + (size_t)b * vocab;
         fill_masses(c, row, st, nullptr, nullptr, vocab, 1.0 / temperature, temperature == 1.0, fp);
-        const unsigned long long tgt = (unsigned long long)(uniforms[b] >> 11) << 7;
+        const unsigned long long tgt = (unsigned long long)(uniforms[(size_t)b * uni_stride] >> 11) << 7;
         token = radix_draw(c, row, fp, vocab, tgt, &gap_lo, &gap_hi);
         if (token < 0) token = (int)c.last_idx, gap_lo = gap_hi = 0;
     }
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
-        tokens[b] = token;
+        tokens[(size_t)b * token_stride] = token;
         if (margins) margins[b] = (double)(gap_lo < gap_hi ? gap_lo : gap_hi) / FP_ONE;
     }
 }
@@ -430,12 +435,47 @@ int32_t check_shaping(tsb_ctx* ctx, const tsb_shaping* sh) {
 
 }  // namespace
 
+size_t accept_scratch_bytes(int batch, int k, int vocab) {
+    const size_t stats = ((size_t)batch * (2 * k + 1) * sizeof(RowStats) + 255) & ~(size_t)255;
+    return stats + (size_t)batch * vocab * sizeof(unsigned long long);
+}
+
+cudaError_t launch_accept(tsb_ctx* ctx, cudaStream_t st, const __half* target, const __half* draft, const int32_t* proposals,
+                          int prop_stride, const uint64_t* uniforms, int batch, int k, int vocab, double temperature,
+                          tsb_accept_out* out_dev, int32_t* next_tokens, int next_stride, void* scratch) {
+    RowStats* stats = reinterpret_cast<RowStats*>(scratch);
+    const size_t stats_bytes = ((size_t)batch * (2 * k + 1) * sizeof(RowStats) + 255) & ~(size_t)255;
+    unsigned long long* fp = reinterpret_cast<unsigned long long*>((char*)scratch + stats_bytes);
+    const int rps = 2 * k + 1;
+    cudaError_t e = tsb_launch(ctx, accept_stats_kernel, dim3((unsigned)(batch * rps)), dim3(ACC_THREADS), 0, st, true, target,
+                               draft, k, vocab, temperature, stats, rps, (int64_t)0);
+    if (e != cudaSuccess) return e;
+    return tsb_launch(ctx, accept_decide_kernel, dim3((unsigned)batch), dim3(ACC_THREADS), 0, st, true, target, draft,
+                      proposals, prop_stride, uniforms, k, vocab, temperature, (const RowStats*)stats, fp, out_dev,
+                      next_tokens, next_stride);
+}
+
+cudaError_t launch_sample(tsb_ctx* ctx, cudaStream_t st, const __half* logits, int64_t logits_stride,
+                          const uint64_t* uniforms, int uni_stride, int batch, int vocab, double temperature,
+                          int32_t* tokens_dev, int token_stride, double* margins_dev, void* scratch) {
+    RowStats* stats = reinterpret_cast<RowStats*>(scratch);
+    const size_t stats_bytes = ((size_t)batch * sizeof(RowStats) + 255) & ~(size_t)255;
+    unsigned long long* fp = reinterpret_cast<unsigned long long*>((char*)scratch + stats_bytes);
+    cudaError_t e = tsb_launch(ctx, accept_stats_kernel, dim3((unsigned)batch), dim3(ACC_THREADS), 0, st, true, logits,
+                               (const __half*)nullptr, 0, vocab, temperature, stats, 1, logits_stride);
+    if (e != cudaSuccess) return e;
+    return tsb_launch(ctx, sample_kernel, dim3((unsigned)batch), dim3(ACC_THREADS), 0, st, true, logits, logits_stride,
+                      uniforms, uni_stride, vocab, temperature, (const RowStats*)stats, fp, tokens_dev, token_stride,
+                      margins_dev, ctx->dev_error);
+}
+
+int32_t accept_check_shaping(tsb_ctx* ctx, const tsb_shaping* sh) { return check_shaping(ctx, sh); }
+
 extern "C" {
 
 size_t tsb_accept_scratch_bytes(int32_t batch, int32_t k, int32_t vocab) {
     if (batch <= 0 || k < 0 || vocab <= 0) return 0;
-    const size_t stats = ((size_t)batch * (2 * k + 1) * sizeof(RowStats) + 255) & ~(size_t)255;
-    return stats + (size_t)batch * vocab * sizeof(unsigned long long);
+    return accept_scratch_bytes(batch, k, vocab);
 }
 
 int32_t tsb_accept(tsb_ctx* ctx, tsb_stream s, const void* target_logits_f16, const void* draft_logits_f16,
@@ -451,17 +491,8 @@ int32_t tsb_accept(tsb_ctx* ctx, tsb_stream s, const void* target_logits_f16, co
     TSB_REQUIRE(ctx, shaping->temperature == 0.0 || uniforms, "uniforms are required at a positive temperature");
     TSB_REQUIRE(ctx, scratch_bytes >= tsb_accept_scratch_bytes(batch, k, vocab), "scratch too small");
     DeviceGuard g(ctx);
-    cudaStream_t st = (cudaStream_t)s;
-    RowStats* stats = reinterpret_cast<RowStats*>(scratch);
-    const size_t stats_bytes = ((size_t)batch * (2 * k + 1) * sizeof(RowStats) + 255) & ~(size_t)255;
-    unsigned long long* fp = reinterpret_cast<unsigned long long*>((char*)scratch + stats_bytes);
-    const int rps = 2 * k + 1;
-    TSB_CUDA(ctx, tsb_launch(ctx, accept_stats_kernel, dim3((unsigned)(batch * rps)), dim3(ACC_THREADS), 0, st, true,
-                             (const __half*)target_logits_f16, (const __half*)draft_logits_f16, (int)k, (int)vocab,
-                             shaping->temperature, stats, rps, 0));
-    TSB_CUDA(ctx, tsb_launch(ctx, accept_decide_kernel, dim3((unsigned)batch), dim3(ACC_THREADS), 0, st, true,
-                             (const __half*)target_logits_f16, (const __half*)draft_logits_f16, proposals, uniforms, (int)k,
-                             (int)vocab, shaping->temperature, (const RowStats*)stats, fp, out_dev));
+    TSB_CUDA(ctx, launch_accept(ctx, (cudaStream_t)s, (const __half*)target_logits_f16, (const __half*)draft_logits_f16,
+                                proposals, k, uniforms, batch, k, vocab, shaping->temperature, out_dev, nullptr, 0, scratch));
     return TSB_OK;
 }
 
@@ -476,16 +507,8 @@ int32_t tsb_sample(tsb_ctx* ctx, tsb_stream s, const void* logits_f16, const uin
     TSB_REQUIRE(ctx, shaping->temperature == 0.0 || uniforms, "uniforms are required at a positive temperature");
     TSB_REQUIRE(ctx, scratch_bytes >= tsb_accept_scratch_bytes(batch, 0, vocab), "scratch too small");
     DeviceGuard g(ctx);
-    cudaStream_t st = (cudaStream_t)s;
-    RowStats* stats = reinterpret_cast<RowStats*>(scratch);
-    const size_t stats_bytes = ((size_t)batch * sizeof(RowStats) + 255) & ~(size_t)255;
-    unsigned long long* fp = reinterpret_cast<unsigned long long*>((char*)scratch + stats_bytes);
-    TSB_CUDA(ctx, tsb_launch(ctx, accept_stats_kernel, dim3((unsigned)batch), dim3(ACC_THREADS), 0, st, true,
-                             (const __half*)logits_f16, (const __half*)nullptr, 0, (int)vocab, shaping->temperature, stats, 1,
-                             1));
-    TSB_CUDA(ctx, tsb_launch(ctx, sample_kernel, dim3((unsigned)batch), dim3(ACC_THREADS), 0, st, true,
-                             (const __half*)logits_f16, uniforms, (int)vocab, shaping->temperature, (const RowStats*)stats, fp,
-                             tokens_dev, margins_dev, ctx->dev_error));
+    TSB_CUDA(ctx, launch_sample(ctx, (cudaStream_t)s, (const __half*)logits_f16, vocab, uniforms, 1, batch, vocab,
+                                shaping->temperature, tokens_dev, 1, margins_dev, scratch));
     return TSB_OK;
 }
 

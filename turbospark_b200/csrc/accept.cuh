@@ -1,0 +1,15 @@
+// Internal launchers of the acceptance / sampling kernels (shared with the model runner).
+#pragma once
+#include "common.cuh"
+
+size_t accept_scratch_bytes(int batch, int k, int vocab);
+int32_t accept_check_shaping(tsb_ctx* ctx, const tsb_shaping* sh);
+// proposals[b * prop_stride + i]; when next_tokens != null the corrected / bonus token of stream b is also
+// written to next_tokens[b * next_stride].
+cudaError_t launch_accept(tsb_ctx* ctx, cudaStream_t st, const __half* target, const __half* draft, const int32_t* proposals,
+                          int prop_stride, const uint64_t* uniforms, int batch, int k, int vocab, double temperature,
+                          tsb_accept_out* out_dev, int32_t* next_tokens, int next_stride, void* scratch);
+// row b at logits + b * logits_stride, uniform at uniforms[b * uni_stride], token to tokens_dev[b * token_stride].
+cudaError_t launch_sample(tsb_ctx* ctx, cudaStream_t st, const __half* logits, int64_t logits_stride,
+                          const uint64_t* uniforms, int uni_stride, int batch, int vocab, double temperature,
+                          int32_t* tokens_dev, int token_stride, double* margins_dev, void* scratch);

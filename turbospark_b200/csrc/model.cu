@@ -1,0 +1,810 @@
+// The producer: a dense Llama-style decoder running on the kernels of this
+// library, with the reference's rounding points (f16 storage between operators,
+// fp32 accumulation, bf16 norm weights), plus the sessions that own K/V caches
+// and work buffers for a set of independent request streams.
+//
+// Op order of one layer (crates/runtime/src/families/llama/mod.rs:205-291,
+// dense.rs:48-120), fused where two reference dispatches are adjacent:
+//   [residual add +] RMSNorm -> qkv matmul (one matmul over q|k|v rows) ->
+//   RoPE + K/V store -> split-KV attention -> o_proj matmul ->
+//   residual add + RMSNorm -> gate|up matmul -> SiLU*up -> down matmul
+// Every producer of a matmul input writes the matmul's activation operand
+// directly, so a layer is 9 launches.
+#include <algorithm>
+#include <cstring>
+#include <memory>
+#include <new>
+#include <vector>
+
+#include "accept.cuh"
+#include "attention.cuh"
+#include "model.cuh"
+
+namespace {
+
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+    x ^= x >> 16;
+    x *= 0x7feb352du;
+    x ^= x >> 15;
+    x *= 0x846ca68bu;
+    x ^= x >> 16;
+    return x;
+}
+
+// Seeded synthetic blocks: every byte pseudo-random, then the scale fields are overwritten so the
+// dequantised weights are finite and small (|w| of a few 1e-2).
+__global__ void fill_blocks_kernel(uint8_t* __restrict__ data, int64_t n_blocks, int qtype, uint32_t seed) {
+    const int bb = qtype == TSB_Q4_K ? 144 : (qtype == TSB_Q6_K ? 210 : 17);
+    for (int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b < n_blocks; b += (int64_t)gridDim.x * blockDim.x) {
+        uint8_t* p = data + b * bb;
+        uint32_t h = mix32((uint32_t)b * 0x9E3779B9u + seed) ^ mix32((uint32_t)(b >> 32) + seed * 31u);
+        for (int i = 0; i < bb; i++) {
+            if ((i & 3) == 0) h = mix32(h + 0x9E3779B9u);
+            p[i] = (uint8_t)(h >> ((i & 3) * 8));
+        }
+        const float u = (float)(mix32(h) >> 8) * (1.0f / 16777216.0f);
+        if (qtype == TSB_Q4_K) {
+            const __half d = __float2half_rn(2.5e-4f * (0.5f + u)), dm = __float2half_rn(1.2e-3f * (0.5f + u));
+            const unsigned short db = __half_as_ushort(d), mb = __half_as_ushort(dm);
+            p[0] = db & 0xFF, p[1] = db >> 8, p[2] = mb & 0xFF, p[3] = mb >> 8;
+        } else if (qtype == TSB_Q6_K) {
+            const unsigned short db = __half_as_ushort(__float2half_rn(2.0e-5f * (0.5f + u)));
+            p[208] = db & 0xFF, p[209] = db >> 8;
+        } else {
+            p[0] = (uint8_t)(120 + (h & 1));
+        }
+    }
+}
+
+__global__ void fill_u16_kernel(uint16_t* p, int64_t n, uint16_t v) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) p[i] = v;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------ model
+
+static int64_t mat_bytes(const Mat& m) { return m.rows * tsb_row_bytes(m.qtype, m.cols); }
+
+static int32_t mat_alloc(tsb_ctx* ctx, Mat& m, int qtype, int64_t rows, int64_t cols) {
+    m.qtype = qtype, m.rows = rows, m.cols = cols;
+    void* p = nullptr;
+    // spare bytes: the bulk-copy path may over-fetch one 16-byte granule past an unaligned row run
+    int32_t rc = tsb_alloc(ctx, (size_t)mat_bytes(m) + 256, &p);
+    if (rc) return rc;
+    m.data = (uint8_t*)p;
+    m.owned = true;
+    cudaMemset(m.data + mat_bytes(m), 0, 256);
+    return TSB_OK;
+}
+
+static void mat_free(tsb_ctx* ctx, Mat& m) {
+    if (m.owned && m.data) tsb_free(ctx, m.data);
+    m = Mat();
+}
+
+static Mat* fused_slot(tsb_model* m, int layer, int which, int64_t* row_off, int64_t* total_rows, int64_t* want_rows,
+                       int64_t* want_cols) {
+    const tsb_model_config& c = m->cfg;
+    const int64_t qd = (int64_t)c.n_q_heads * c.head_dim, kd = (int64_t)c.n_kv_heads * c.head_dim;
+    *row_off = 0;
+    if (which == TSB_W_EMBED) {
+        *total_rows = *want_rows = c.vocab, *want_cols = c.d_model;
+        return &m->embed;
+    }
+    if (which == TSB_W_LM_HEAD) {
+        *total_rows = *want_rows = c.vocab, *want_cols = c.d_model;
+        return &m->lm_head;
+    }
+    if (layer < 0 || layer >= c.n_layers) return nullptr;
+    LayerW& l = m->layers[layer];
+    switch (which) {
+        case TSB_W_Q: *total_rows = qd + 2 * kd, *want_rows = qd, *want_cols = c.d_model; return &l.wqkv;
+        case TSB_W_K: *total_rows = qd + 2 * kd, *want_rows = kd, *want_cols = c.d_model, *row_off = qd; return &l.wqkv;
+        case TSB_W_V: *total_rows = qd + 2 * kd, *want_rows = kd, *want_cols = c.d_model, *row_off = qd + kd; return &l.wqkv;
+        case TSB_W_O: *total_rows = *want_rows = c.d_model, *want_cols = qd; return &l.wo;
+        case TSB_W_GATE: *total_rows = 2 * (int64_t)c.ffn, *want_rows = c.ffn, *want_cols = c.d_model; return &l.wgu;
+        case TSB_W_UP: *total_rows = 2 * (int64_t)c.ffn, *want_rows = c.ffn, *want_cols = c.d_model, *row_off = c.ffn; return &l.wgu;
+        case TSB_W_DOWN: *total_rows = *want_rows = c.d_model, *want_cols = c.ffn; return &l.wdown;
+        default: return nullptr;
+    }
+}
+
+extern "C" {
+
+int32_t tsb_model_create(tsb_ctx* ctx, const tsb_model_config* cfg, tsb_model** out) {
+    if (!ctx || !cfg || !out) return TSB_ERR_INVALID;
+    *out = nullptr;
+    TSB_REQUIRE(ctx, cfg->n_layers > 0 && cfg->d_model > 0 && cfg->n_q_heads > 0 && cfg->n_kv_heads > 0 && cfg->ffn > 0 &&
+                         cfg->vocab > 0 && cfg->max_context > 0,
+                "model dimensions must be positive");
+    TSB_REQUIRE(ctx, cfg->head_dim == 64 || cfg->head_dim == 128, "head_dim must be 64 or 128");
+    TSB_REQUIRE(ctx, cfg->n_q_heads % cfg->n_kv_heads == 0, "n_q_heads must be a multiple of n_kv_heads");
+    if (cfg->d_model % 256 || cfg->ffn % 256 || (cfg->n_q_heads * cfg->head_dim) % 256)
+        return tsb_fail(ctx, TSB_ERR_UNSUPPORTED, "d_model, ffn and n_q_heads*head_dim must be multiples of 256");
+    tsb_model* m = new (std::nothrow) tsb_model();
+    if (!m) return TSB_ERR_OOM;
+    m->ctx = ctx;
+    m->cfg = *cfg;
+    m->layers.resize(cfg->n_layers);
+    *out = m;
+    return TSB_OK;
+}
+
+void tsb_model_destroy(tsb_model* m) {
+    if (!m) return;
+    DeviceGuard g(m->ctx);
+    cudaDeviceSynchronize();
+    for (auto& l : m->layers) {
+        mat_free(m->ctx, l.wqkv), mat_free(m->ctx, l.wo), mat_free(m->ctx, l.wgu), mat_free(m->ctx, l.wdown);
+        if (l.norms_owned) {
+            if (l.attn_norm) tsb_free(m->ctx, l.attn_norm);
+            if (l.ffn_norm) tsb_free(m->ctx, l.ffn_norm);
+        }
+    }
+    mat_free(m->ctx, m->embed), mat_free(m->ctx, m->lm_head);
+    if (m->out_norm_owned && m->out_norm) tsb_free(m->ctx, m->out_norm);
+    delete m;
+}
+
+int32_t tsb_model_set_matrix(tsb_model* m, int32_t layer, int32_t which, int32_t qtype, const void* host_blocks,
+                             int64_t rows, int64_t cols) {
+    if (!m) return TSB_ERR_INVALID;
+    tsb_ctx* ctx = m->ctx;
+    TSB_REQUIRE(ctx, host_blocks, "null data");
+    TSB_REQUIRE(ctx, qtype >= TSB_Q4_K && qtype <= TSB_MXFP4, "unknown block format %d", qtype);
+    int64_t off, total, wr, wc;
+    Mat* slot = fused_slot(m, layer, which, &off, &total, &wr, &wc);
+    TSB_REQUIRE(ctx, slot, "no such tensor (layer %d, which %d)", layer, which);
+    TSB_REQUIRE(ctx, rows == wr && cols == wc, "tensor %d of layer %d must be %lld x %lld, got %lld x %lld", which, layer,
+                (long long)wr, (long long)wc, (long long)rows, (long long)cols);
+    DeviceGuard g(ctx);
+    if (!slot->data) {
+        int32_t rc = mat_alloc(ctx, *slot, qtype, total, cols);
+        if (rc) return rc;
+    } else if (slot->qtype != qtype) {
+        return tsb_fail(ctx, TSB_ERR_UNSUPPORTED, "q/k/v (and gate/up) of a layer must share one block format");
+    }
+    const int64_t rb = tsb_row_bytes(qtype, cols);
+    TSB_CUDA(ctx, cudaMemcpy(slot->data + off * rb, host_blocks, (size_t)(rows * rb), cudaMemcpyHostToDevice));
+    return TSB_OK;
+}
+
+int32_t tsb_model_set_norm(tsb_model* m, int32_t layer, int32_t which, const void* host_bf16, int32_t n) {
+    if (!m) return TSB_ERR_INVALID;
+    tsb_ctx* ctx = m->ctx;
+    TSB_REQUIRE(ctx, host_bf16 && n == m->cfg.d_model, "a norm weight has d_model entries");
+    uint16_t** slot;
+    if (which == TSB_N_OUT) {
+        slot = &m->out_norm;
+        m->out_norm_owned = true;
+    } else {
+        TSB_REQUIRE(ctx, layer >= 0 && layer < m->cfg.n_layers, "layer %d outside the model", layer);
+        slot = which == TSB_N_ATTN ? &m->layers[layer].attn_norm : &m->layers[layer].ffn_norm;
+        m->layers[layer].norms_owned = true;
+    }
+    DeviceGuard g(ctx);
+    if (!*slot) {
+        void* p;
+        int32_t rc = tsb_alloc(ctx, (size_t)n * 2, &p);
+        if (rc) return rc;
+        *slot = (uint16_t*)p;
+    }
+    TSB_CUDA(ctx, cudaMemcpy(*slot, host_bf16, (size_t)n * 2, cudaMemcpyHostToDevice));
+    return TSB_OK;
+}
+
+int32_t tsb_model_share(tsb_model* dst, int32_t dst_layer, const tsb_model* src, int32_t src_layer) {
+    if (!dst || !src) return TSB_ERR_INVALID;
+    tsb_ctx* ctx = dst->ctx;
+    TSB_REQUIRE(ctx, dst->cfg.d_model == src->cfg.d_model && dst->cfg.vocab == src->cfg.vocab, "models differ in width or vocabulary");
+    auto borrow = [](Mat& d, const Mat& s) {
+        d = s;
+        d.owned = false;
+    };
+    if (dst_layer < 0) {
+        borrow(dst->embed, src->embed), borrow(dst->lm_head, src->lm_head);
+        dst->out_norm = src->out_norm, dst->out_norm_owned = false;
+        return TSB_OK;
+    }
+    TSB_REQUIRE(ctx, dst_layer < dst->cfg.n_layers && src_layer >= 0 && src_layer < src->cfg.n_layers, "layer out of range");
+    TSB_REQUIRE(ctx, dst->cfg.ffn == src->cfg.ffn && dst->cfg.n_q_heads == src->cfg.n_q_heads &&
+                         dst->cfg.n_kv_heads == src->cfg.n_kv_heads && dst->cfg.head_dim == src->cfg.head_dim,
+                "layer shapes differ");
+    LayerW& d = dst->layers[dst_layer];
+    const LayerW& s = src->layers[src_layer];
+    borrow(d.wqkv, s.wqkv), borrow(d.wo, s.wo), borrow(d.wgu, s.wgu), borrow(d.wdown, s.wdown);
+    d.attn_norm = s.attn_norm, d.ffn_norm = s.ffn_norm, d.norms_owned = false;
+    return TSB_OK;
+}
+
+int32_t tsb_model_fill_synthetic(tsb_model* m, int32_t qtype, int32_t lm_head_qtype, uint64_t seed) {
+    if (!m) return TSB_ERR_INVALID;
+    tsb_ctx* ctx = m->ctx;
+    TSB_REQUIRE(ctx, qtype >= TSB_Q4_K && qtype <= TSB_MXFP4 && lm_head_qtype >= TSB_Q4_K && lm_head_qtype <= TSB_MXFP4, "bad format");
+    DeviceGuard g(ctx);
+    const tsb_model_config& c = m->cfg;
+    const int64_t qd = (int64_t)c.n_q_heads * c.head_dim, kd = (int64_t)c.n_kv_heads * c.head_dim;
+    uint32_t sd = (uint32_t)seed * 2654435761u + (uint32_t)(seed >> 32);
+    auto fill = [&](Mat& t, int qt, int64_t rows, int64_t cols) -> int32_t {
+        if (!t.data) {
+            int32_t rc = mat_alloc(ctx, t, qt, rows, cols);
+            if (rc) return rc;
+        }
+        const int64_t nb = mat_bytes(t) / (qt == TSB_Q4_K ? 144 : (qt == TSB_Q6_K ? 210 : 17));
+        fill_blocks_kernel<<<1024, 256>>>(t.data, nb, qt, sd);
+        sd = sd * 1664525u + 1013904223u;
+        return TSB_OK;
+    };
+    auto ones = [&](uint16_t** p) -> int32_t {
+        if (!*p) {
+            void* q;
+            int32_t rc = tsb_alloc(ctx, (size_t)c.d_model * 2, &q);
+            if (rc) return rc;
+            *p = (uint16_t*)q;
+        }
+        fill_u16_kernel<<<32, 256>>>(*p, c.d_model, (uint16_t)0x3F80);  // bf16 1.0
+        return TSB_OK;
+    };
+    int32_t rc;
+    for (auto& l : m->layers) {
+        if ((rc = fill(l.wqkv, qtype, qd + 2 * kd, c.d_model))) return rc;
+        if ((rc = fill(l.wo, qtype, c.d_model, qd))) return rc;
+        if ((rc = fill(l.wgu, qtype, 2 * (int64_t)c.ffn, c.d_model))) return rc;
+        if ((rc = fill(l.wdown, qtype, c.d_model, c.ffn))) return rc;
+        l.norms_owned = true;
+        if ((rc = ones(&l.attn_norm)) || (rc = ones(&l.ffn_norm))) return rc;
+    }
+    if ((rc = fill(m->embed, qtype, c.vocab, c.d_model))) return rc;
+    if ((rc = fill(m->lm_head, lm_head_qtype, c.vocab, c.d_model))) return rc;
+    m->out_norm_owned = true;
+    if ((rc = ones(&m->out_norm))) return rc;
+    TSB_CUDA(ctx, cudaDeviceSynchronize());
+    return TSB_OK;
+}
+
+int64_t tsb_model_weight_bytes(const tsb_model* m) {
+    if (!m) return 0;
+    int64_t t = mat_bytes(m->lm_head);
+    for (auto& l : m->layers) t += mat_bytes(l.wqkv) + mat_bytes(l.wo) + mat_bytes(l.wgu) + mat_bytes(l.wdown);
+    return t;
+}
+
+}  // extern "C"
+
+static int32_t model_complete(const tsb_model* m) {
+    tsb_ctx* ctx = m->ctx;
+    for (size_t i = 0; i < m->layers.size(); i++) {
+        const LayerW& l = m->layers[i];
+        TSB_REQUIRE(ctx, l.wqkv.data && l.wo.data && l.wgu.data && l.wdown.data && l.attn_norm && l.ffn_norm,
+                    "layer %zu is missing a tensor", i);
+    }
+    TSB_REQUIRE(ctx, m->embed.data && m->lm_head.data && m->out_norm, "embedding, head or final norm missing");
+    return TSB_OK;
+}
+
+// ------------------------------------------------------------------ session
+
+static int32_t dev_alloc(tsb_ctx* ctx, std::vector<void*>& owned, size_t bytes, void** out) {
+    int32_t rc = tsb_alloc(ctx, bytes, out);
+    if (rc == TSB_OK) owned.push_back(*out);
+    return rc;
+}
+
+static int32_t runtime_init(tsb_session* s, ModelRt& rt, const tsb_model* model, int n_streams, int max_rows, int page_tokens) {
+    tsb_ctx* ctx = s->ctx;
+    rt.model = model;
+    const tsb_model_config& c = model->cfg;
+    const int R = n_streams * max_rows;
+    const int Rp = (R + 7) / 8 * 8;  // activation operands hold whole token tiles
+    const int64_t qkv_dim = (int64_t)(c.n_q_heads + 2 * c.n_kv_heads) * c.head_dim;
+    const int pages_per_seq = (c.max_context + page_tokens - 1) / page_tokens;
+    int32_t rc = tsb_kv_create(ctx, c.n_layers, c.n_kv_heads, c.head_dim, page_tokens, pages_per_seq * n_streams, n_streams,
+                               pages_per_seq, &rt.kv);
+    if (rc) return rc;
+    auto A = [&](size_t bytes, void** p) { return dev_alloc(ctx, s->owned, bytes, p); };
+    if ((rc = A((size_t)R * c.d_model * 2, (void**)&rt.h))) return rc;
+    if ((rc = A((size_t)R * qkv_dim * 2, (void**)&rt.qkv))) return rc;
+    if ((rc = A((size_t)R * c.d_model * 2, (void**)&rt.o))) return rc;
+    if ((rc = A((size_t)R * 2 * c.ffn * 2, (void**)&rt.gu))) return rc;
+    if ((rc = A((size_t)R * c.d_model * 2, (void**)&rt.dn))) return rc;
+    const int64_t od = (int64_t)c.n_q_heads * c.head_dim;
+    if ((rc = A(act_xp_bytes(Rp, c.d_model), (void**)&rt.act_d.xp)) || (rc = A(act_xs_bytes(Rp, c.d_model), (void**)&rt.act_d.xs))) return rc;
+    if ((rc = A(act_xp_bytes(Rp, od), (void**)&rt.act_o.xp)) || (rc = A(act_xs_bytes(Rp, od), (void**)&rt.act_o.xs))) return rc;
+    if ((rc = A(act_xp_bytes(Rp, c.ffn), (void**)&rt.act_f.xp)) || (rc = A(act_xs_bytes(Rp, c.ffn), (void**)&rt.act_f.xs))) return rc;
+    cudaMemset(rt.act_d.xp, 0, act_xp_bytes(Rp, c.d_model));
+    cudaMemset(rt.act_o.xp, 0, act_xp_bytes(Rp, od));
+    cudaMemset(rt.act_f.xp, 0, act_xp_bytes(Rp, c.ffn));
+    cudaMemset(rt.act_d.xs, 0, act_xs_bytes(Rp, c.d_model));
+    cudaMemset(rt.act_o.xs, 0, act_xs_bytes(Rp, od));
+    cudaMemset(rt.act_f.xs, 0, act_xs_bytes(Rp, c.ffn));
+    rt.attn_scratch_bytes = attn_scratch_bytes(R, c.n_q_heads, c.head_dim);
+    if ((rc = A(rt.attn_scratch_bytes, &rt.attn_scratch))) return rc;
+    rt.fed.assign(n_streams, std::vector<int32_t>());
+    return TSB_OK;
+}
+
+// One forward pass over `rows` rows (rows_per_seq per stream).  Row descriptors and token ids are
+// already on the device.  Cursors are not touched here.
+static cudaError_t forward_device(tsb_session* s, ModelRt& rt, const int32_t* tokens_dev, int token_stride,
+                                  const tsb_row_desc* rows_dev, int rows, int rows_per_seq, int max_len, __half* logits,
+                                  int64_t logits_stride) {
+    tsb_ctx* ctx = s->ctx;
+    cudaStream_t st = s->stream;
+    const tsb_model* m = rt.model;
+    const tsb_model_config& c = m->cfg;
+    const int64_t qkv_dim = (int64_t)(c.n_q_heads + 2 * c.n_kv_heads) * c.head_dim;
+    const float scale = 1.0f / sqrtf((float)c.head_dim);
+    cudaError_t e;
+#define FW(x)                         \
+    do {                              \
+        e = (x);                      \
+        if (e != cudaSuccess) return e; \
+    } while (0)
+    FW(launch_embed_rows(ctx, st, m->embed.qtype, m->embed.data, c.vocab, c.d_model, tokens_dev, token_stride, rows, rt.h, 1.0f));
+    const ActOut out_d{rt.act_d.xp, rt.act_d.xs}, out_o{rt.act_o.xp, rt.act_o.xs}, out_f{rt.act_f.xp, rt.act_f.xs};
+    const ActOperand in_d{rt.act_d.xp, rt.act_d.xs}, in_o{rt.act_o.xp, rt.act_o.xs}, in_f{rt.act_f.xp, rt.act_f.xs};
+    for (int L = 0; L < c.n_layers; L++) {
+        const LayerW& l = m->layers[L];
+        FW(launch_rmsnorm_rows(ctx, st, rt.h, L == 0 ? nullptr : rt.dn, l.attn_norm, nullptr, out_d, rows, c.d_model, c.rms_eps));
+        FW(launch_gemm_quant(ctx, st, l.wqkv.qtype, l.wqkv.data, l.wqkv.rows, l.wqkv.cols, in_d, rt.qkv, qkv_dim, rows, false));
+        FW(launch_rope_store_kv(ctx, st, rt.kv, L, rt.qkv, rows_dev, rows, c.n_q_heads, c.rope_theta));
+        FW(launch_attn_decode_rows(ctx, st, rt.kv, L, rt.qkv, qkv_dim, nullptr, out_o, rows_dev, rows, rows_per_seq,
+                                   c.n_q_heads, scale, max_len, rt.attn_scratch));
+        FW(launch_gemm_quant(ctx, st, l.wo.qtype, l.wo.data, l.wo.rows, l.wo.cols, in_o, rt.o, c.d_model, rows, false));
+        FW(launch_rmsnorm_rows(ctx, st, rt.h, rt.o, l.ffn_norm, nullptr, out_d, rows, c.d_model, c.rms_eps));
+        FW(launch_gemm_quant(ctx, st, l.wgu.qtype, l.wgu.data, l.wgu.rows, l.wgu.cols, in_d, rt.gu, 2 * (int64_t)c.ffn, rows, false));
+        FW(launch_silu_mul(ctx, st, rt.gu, rt.gu + c.ffn, nullptr, out_f, rows, c.ffn, 2 * (int64_t)c.ffn, c.ffn));
+        FW(launch_gemm_quant(ctx, st, l.wdown.qtype, l.wdown.data, l.wdown.rows, l.wdown.cols, in_f, rt.dn, c.d_model, rows, false));
+    }
+    FW(launch_rmsnorm_rows(ctx, st, rt.h, rt.dn, m->out_norm, nullptr, out_d, rows, c.d_model, c.rms_eps));
+    if (logits) {
+        // logits rows may be strided (a drafter's step d of k): one matmul call per row when not dense
+        // row t of the logits sits at logits + t * logits_stride (a drafter's step d of k is strided)
+        FW(launch_gemm_quant(ctx, st, m->lm_head.qtype, m->lm_head.data, m->lm_head.rows, m->lm_head.cols, in_d, logits,
+                             logits_stride, rows, false));
+    }
+#undef FW
+    return cudaSuccess;
+}
+
+// Host side of a forward: descriptors for `n_active` streams x rows_per_seq rows, uploaded through the
+// pinned staging ring.  parent == nullptr: a chain.  Returns the device pointers.
+static int32_t stage_rows(tsb_session* s, ModelRt& rt, const int32_t* streams, int n_active, int rows_per_seq,
+                          const int32_t* slot_parent, const int32_t* tokens_host /* may be null */,
+                          const tsb_row_desc** rows_dev, const int32_t** tokens_dev, int* max_len) {
+    tsb_ctx* ctx = s->ctx;
+    const int rows = n_active * rows_per_seq;
+    TSB_REQUIRE(ctx, rows <= s->n_streams * s->max_rows, "%d rows exceed the session's %d", rows, s->n_streams * s->max_rows);
+    TSB_REQUIRE(ctx, rows_per_seq <= 128, "at most 128 in-flight rows per stream");
+    if (s->stage_used + rows > s->stage_cap) {
+        // the ring is reused only after the work that read it has finished
+        TSB_CUDA(ctx, cudaStreamSynchronize(s->stream));
+        s->stage_used = 0;
+    }
+    tsb_row_desc* hd = s->stage_rows_host + s->stage_used;
+    int32_t* ht = s->stage_tok_host + s->stage_used;
+    std::vector<int> depth(rows_per_seq, 0);
+    std::vector<uint64_t> mlo(rows_per_seq, 0), mhi(rows_per_seq, 0);
+    for (int j = 0; j < rows_per_seq; j++) {
+        if (slot_parent) {
+            if (j == 0) {
+                TSB_REQUIRE(ctx, slot_parent[0] == -1, "a tree's slot 0 is the anchor (parent -1)");
+            } else {
+                const int p = slot_parent[j];
+                TSB_REQUIRE(ctx, p >= 0 && p < j, "slot %d's parent %d must precede it", j, p);
+                depth[j] = depth[p] + 1;
+                mlo[j] = mlo[p], mhi[j] = mhi[p];
+            }
+        } else {
+            depth[j] = j;
+            if (j) mlo[j] = mlo[j - 1], mhi[j] = mhi[j - 1];
+        }
+        if (j < 64) mlo[j] |= 1ull << j; else mhi[j] |= 1ull << (j - 64);
+    }
+    int ml = 0;
+    for (int a = 0; a < n_active; a++) {
+        const int seq = streams[a];
+        TSB_REQUIRE(ctx, seq >= 0 && seq < s->n_streams, "stream %d outside the session", seq);
+        const int64_t base = tsb_kv_cursor(rt.kv, seq);
+        if (base + rows_per_seq > rt.model->cfg.max_context)
+            return tsb_fail(ctx, TSB_ERR_STATE, "stream %d: %lld + %d rows exceed the context window %d", seq, (long long)base,
+                            rows_per_seq, rt.model->cfg.max_context);
+        int32_t rc = tsb_kv_reserve(rt.kv, seq, base + rows_per_seq);
+        if (rc) return rc;
+        for (int j = 0; j < rows_per_seq; j++) {
+            tsb_row_desc& d = hd[a * rows_per_seq + j];
+            d.seq = seq, d.base = (int32_t)base, d.slot = j, d.position = (int32_t)base + depth[j];
+            d.mask[0] = mlo[j], d.mask[1] = mhi[j];
+            if (tokens_host) ht[a * rows_per_seq + j] = tokens_host[a * rows_per_seq + j];
+        }
+        ml = ml > (int)base + rows_per_seq ? ml : (int)base + rows_per_seq;
+    }
+    tsb_row_desc* dd = s->stage_rows_dev + s->stage_used;
+    int32_t* dt = s->stage_tok_dev + s->stage_used;
+    TSB_CUDA(ctx, cudaMemcpyAsync(dd, hd, rows * sizeof(tsb_row_desc), cudaMemcpyHostToDevice, s->stream));
+    if (tokens_host) TSB_CUDA(ctx, cudaMemcpyAsync(dt, ht, rows * sizeof(int32_t), cudaMemcpyHostToDevice, s->stream));
+    s->stage_used += rows;
+    *rows_dev = dd;
+    if (tokens_dev) *tokens_dev = dt;
+    *max_len = ml;
+    return TSB_OK;
+}
+
+extern "C" {
+static int32_t drafter_catch_up(tsb_session* s, int stream, int64_t upto);
+}
+
+// forward + cursor advance for one stream (the single-stream producer calls)
+static int32_t forward_stream(tsb_session* s, ModelRt& rt, int stream, const int32_t* tokens, int n, const int32_t* slot_parent,
+                              __half* logits_dev, void* logits_out_host) {
+    tsb_ctx* ctx = s->ctx;
+    const tsb_row_desc* rd;
+    const int32_t* td;
+    int max_len;
+    int32_t rc = stage_rows(s, rt, &stream, 1, n, slot_parent, tokens, &rd, &td, &max_len);
+    if (rc) return rc;
+    const int vocab = rt.model->cfg.vocab;
+    TSB_CUDA(ctx, forward_device(s, rt, td, 1, rd, n, n, max_len, logits_dev, vocab));
+    tsb_kv_set_cursor(rt.kv, stream, tsb_kv_cursor(rt.kv, stream) + n);
+    if (logits_dev && logits_out_host)
+        TSB_CUDA(ctx, cudaMemcpyAsync(logits_out_host, logits_dev, (size_t)n * vocab * 2, cudaMemcpyDeviceToHost, s->stream));
+    if (logits_out_host) return tsb_stream_sync(ctx, s->stream);
+    return TSB_OK;
+}
+
+extern "C" {
+
+int32_t tsb_session_create(tsb_ctx* ctx, const tsb_model* target, const tsb_model* draft, int32_t n_streams,
+                           int32_t max_rows, int32_t page_tokens, tsb_session** out) {
+    if (!ctx || !target || !out) return TSB_ERR_INVALID;
+    *out = nullptr;
+    TSB_REQUIRE(ctx, n_streams > 0 && max_rows > 0 && max_rows <= 128, "n_streams must be positive and max_rows in 1..128");
+    int32_t rc = model_complete(target);
+    if (rc) return rc;
+    if (draft) {
+        if ((rc = model_complete(draft))) return rc;
+        TSB_REQUIRE(ctx, draft->cfg.vocab == target->cfg.vocab, "the drafter must share the target's vocabulary");
+    }
+    DeviceGuard g(ctx);
+    tsb_session* s = new (std::nothrow) tsb_session();
+    if (!s) return TSB_ERR_OOM;
+    s->ctx = ctx, s->n_streams = n_streams, s->max_rows = max_rows;
+    auto fail = [&](int32_t code) {
+        tsb_session_destroy(s);
+        return code;
+    };
+    if (cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking) != cudaSuccess) return fail(TSB_ERR_CUDA);
+    for (auto& ev : s->ev)
+        if (cudaEventCreate(&ev) != cudaSuccess) return fail(TSB_ERR_CUDA);
+    if ((rc = runtime_init(s, s->target, target, n_streams, max_rows, page_tokens))) return fail(rc);
+    if (draft && (rc = runtime_init(s, s->draft, draft, n_streams, max_rows, page_tokens))) return fail(rc);
+    s->has_draft = draft != nullptr;
+    const int R = n_streams * max_rows, V = target->cfg.vocab;
+    auto A = [&](size_t bytes, void** p) { return dev_alloc(ctx, s->owned, bytes, p); };
+    if ((rc = A((size_t)R * V * 2, (void**)&s->logits_target))) return fail(rc);
+    if ((rc = A((size_t)R * V * 2, (void**)&s->logits_draft))) return fail(rc);
+    if ((rc = A((size_t)R * sizeof(int32_t), (void**)&s->feed_dev))) return fail(rc);
+    if ((rc = A((size_t)n_streams * (3 * max_rows + 2) * sizeof(uint64_t), (void**)&s->uniforms_dev))) return fail(rc);
+    if ((rc = A((size_t)n_streams * sizeof(tsb_accept_out), (void**)&s->accept_out_dev))) return fail(rc);
+    s->accept_scratch_bytes = accept_scratch_bytes(n_streams, max_rows, V);
+    if ((rc = A(s->accept_scratch_bytes, &s->accept_scratch))) return fail(rc);
+    if ((rc = A((size_t)n_streams * sizeof(int32_t), (void**)&s->tok1_dev))) return fail(rc);
+    // pinned staging: descriptors and tokens of several forwards in flight
+    s->stage_cap = R * (2 * max_rows + 8);
+    if (cudaMallocHost((void**)&s->stage_rows_host, (size_t)s->stage_cap * sizeof(tsb_row_desc)) != cudaSuccess) return fail(TSB_ERR_CUDA);
+    if (cudaMallocHost((void**)&s->stage_tok_host, (size_t)s->stage_cap * sizeof(int32_t)) != cudaSuccess) return fail(TSB_ERR_CUDA);
+    if ((rc = A((size_t)s->stage_cap * sizeof(tsb_row_desc), (void**)&s->stage_rows_dev))) return fail(rc);
+    if ((rc = A((size_t)s->stage_cap * sizeof(int32_t), (void**)&s->stage_tok_dev))) return fail(rc);
+    if (cudaMallocHost((void**)&s->accept_out_host, (size_t)n_streams * sizeof(tsb_accept_out)) != cudaSuccess) return fail(TSB_ERR_CUDA);
+    if (cudaMallocHost((void**)&s->uniforms_host, (size_t)n_streams * (3 * max_rows + 2) * sizeof(uint64_t)) != cudaSuccess) return fail(TSB_ERR_CUDA);
+    if (cudaMallocHost((void**)&s->feed_host, (size_t)R * sizeof(int32_t)) != cudaSuccess) return fail(TSB_ERR_CUDA);
+    if (cudaMallocHost((void**)&s->logits_host, (size_t)V * 2) != cudaSuccess) return fail(TSB_ERR_CUDA);
+    *out = s;
+    return TSB_OK;
+}
+
+void tsb_session_destroy(tsb_session* s) {
+    if (!s) return;
+    DeviceGuard g(s->ctx);
+    cudaDeviceSynchronize();
+    for (void* p : s->owned) tsb_free(s->ctx, p);
+    if (s->target.kv) tsb_kv_destroy(s->target.kv);
+    if (s->draft.kv) tsb_kv_destroy(s->draft.kv);
+    cudaFreeHost(s->stage_rows_host), cudaFreeHost(s->stage_tok_host), cudaFreeHost(s->accept_out_host);
+    cudaFreeHost(s->uniforms_host), cudaFreeHost(s->feed_host), cudaFreeHost(s->logits_host);
+    for (auto& ev : s->ev)
+        if (ev) cudaEventDestroy(ev);
+    if (s->stream) cudaStreamDestroy(s->stream);
+    delete s;
+}
+
+tsb_kv* tsb_session_kv(tsb_session* s, int32_t which) { return !s ? nullptr : (which == 0 ? s->target.kv : s->draft.kv); }
+
+// ---- LogitProducer / SpeculativeProducer, one stream ----------------------
+
+int32_t tsb_producer_reset(tsb_session* s, int32_t stream) {
+    if (!s) return TSB_ERR_INVALID;
+    TSB_REQUIRE(s->ctx, stream >= 0 && stream < s->n_streams, "stream %d outside the session", stream);
+    DeviceGuard g(s->ctx);
+    TSB_CUDA(s->ctx, cudaStreamSynchronize(s->stream));
+    int32_t rc = tsb_kv_reset(s->target.kv, stream);
+    if (rc) return rc;
+    s->target.fed[stream].clear();
+    if (s->has_draft) {
+        if ((rc = tsb_kv_reset(s->draft.kv, stream))) return rc;
+    }
+    return TSB_OK;
+}
+
+static int32_t check_position(tsb_session* s, ModelRt& rt, int stream, int64_t position) {
+    TSB_REQUIRE(s->ctx, stream >= 0 && stream < s->n_streams, "stream %d outside the session", stream);
+    const int64_t cur = tsb_kv_cursor(rt.kv, stream);
+    if (position != cur)  // crates/runtime/src/families/qwen/batched.rs:150-160: start must equal the cursor
+        return tsb_fail(s->ctx, TSB_ERR_STATE, "position %lld does not continue the cache (cursor %lld)", (long long)position,
+                        (long long)cur);
+    return TSB_OK;
+}
+
+static void record_fed(ModelRt& rt, int stream, int64_t position, const int32_t* tokens, int n) {
+    auto& f = rt.fed[stream];
+    f.resize((size_t)position);
+    f.insert(f.end(), tokens, tokens + n);
+}
+
+int32_t tsb_producer_produce(tsb_session* s, int32_t stream, int32_t token, int64_t position, void* logits_out_host) {
+    if (!s) return TSB_ERR_INVALID;
+    DeviceGuard g(s->ctx);
+    int32_t rc = check_position(s, s->target, stream, position);
+    if (rc) return rc;
+    record_fed(s->target, stream, position, &token, 1);
+    return forward_stream(s, s->target, stream, &token, 1, nullptr, s->logits_target, logits_out_host);
+}
+
+int32_t tsb_producer_produce_prefill(tsb_session* s, int32_t stream, int32_t token, int64_t position) {
+    if (!s) return TSB_ERR_INVALID;
+    DeviceGuard g(s->ctx);
+    int32_t rc = check_position(s, s->target, stream, position);
+    if (rc) return rc;
+    record_fed(s->target, stream, position, &token, 1);
+    return forward_stream(s, s->target, stream, &token, 1, nullptr, nullptr, nullptr);
+}
+
+// the drafter is a stand-alone decoder: bring its cache up to `upto` from the record of fed tokens
+static int32_t drafter_catch_up(tsb_session* s, int stream, int64_t upto) {
+    ModelRt& d = s->draft;
+    const auto& fed = s->target.fed[stream];
+    while (tsb_kv_cursor(d.kv, stream) < upto) {
+        const int64_t p = tsb_kv_cursor(d.kv, stream);
+        if ((size_t)p >= fed.size()) return tsb_fail(s->ctx, TSB_ERR_STATE, "drafter position %lld was never fed to the target", (long long)p);
+        int64_t n64 = upto - p;
+        if (n64 > s->max_rows) n64 = s->max_rows;
+        if (n64 > (int64_t)fed.size() - p) n64 = (int64_t)fed.size() - p;
+        const int n = (int)n64;
+        int32_t rc = forward_stream(s, d, stream, fed.data() + p, n, nullptr, nullptr, nullptr);
+        if (rc) return rc;
+    }
+    return TSB_OK;
+}
+
+static int32_t drafter_step(tsb_session* s, int32_t stream, int32_t next, int64_t position, bool head, void* logits_out_host) {
+    if (!s) return TSB_ERR_INVALID;
+    if (!s->has_draft) return tsb_fail(s->ctx, TSB_ERR_STATE, "the session has no drafter");
+    TSB_REQUIRE(s->ctx, stream >= 0 && stream < s->n_streams, "stream %d outside the session", stream);
+    DeviceGuard g(s->ctx);
+    int32_t rc = drafter_catch_up(s, stream, position + 1);
+    if (rc) return rc;
+    if ((rc = check_position(s, s->draft, stream, position + 1))) return rc;
+    return forward_stream(s, s->draft, stream, &next, 1, nullptr, head ? s->logits_draft : nullptr, logits_out_host);
+}
+
+int32_t tsb_producer_prime_drafter(tsb_session* s, int32_t stream, int32_t next, int64_t position) {
+    return drafter_step(s, stream, next, position, false, nullptr);
+}
+int32_t tsb_producer_draft_step(tsb_session* s, int32_t stream, int32_t next, int64_t position, void* logits_out_host) {
+    return drafter_step(s, stream, next, position, true, logits_out_host);
+}
+
+int32_t tsb_producer_verify(tsb_session* s, int32_t stream, const int32_t* feed, int32_t n, int64_t base, void* logits_out_host) {
+    if (!s) return TSB_ERR_INVALID;
+    TSB_REQUIRE(s->ctx, feed && n > 0 && n <= s->max_rows, "verify takes 1..%d rows", s->max_rows);
+    DeviceGuard g(s->ctx);
+    int32_t rc = check_position(s, s->target, stream, base);
+    if (rc) return rc;
+    record_fed(s->target, stream, base, feed, n);
+    return forward_stream(s, s->target, stream, feed, n, nullptr, s->logits_target, logits_out_host);
+}
+
+int32_t tsb_producer_verify_tree(tsb_session* s, int32_t stream, const int32_t* feed, const int32_t* slot_parent, int32_t n,
+                                 int64_t base, void* logits_out_host) {
+    if (!s) return TSB_ERR_INVALID;
+    TSB_REQUIRE(s->ctx, feed && slot_parent && n > 0 && n <= s->max_rows, "verify_tree takes 1..%d rows", s->max_rows);
+    DeviceGuard g(s->ctx);
+    int32_t rc = check_position(s, s->target, stream, base);
+    if (rc) return rc;
+    return forward_stream(s, s->target, stream, feed, n, slot_parent, s->logits_target, logits_out_host);
+}
+
+int32_t tsb_producer_compact_tree(tsb_session* s, int32_t stream, int64_t base, const uint32_t* path, int32_t keep) {
+    if (!s) return TSB_ERR_INVALID;
+    DeviceGuard g(s->ctx);
+    return tsb_kv_commit_path(s->ctx, s->stream, s->target.kv, stream, base, path, keep);
+}
+
+int64_t tsb_producer_checkpoint(tsb_session* s, int32_t stream) { return s ? tsb_kv_cursor(s->target.kv, stream) : -1; }
+
+int32_t tsb_producer_rollback(tsb_session* s, int32_t stream, int64_t point) {
+    return tsb_producer_rollback_retaining(s, stream, point, 0);
+}
+
+// crates/runtime/src/real_forward_rollback.rs:268-405 for a pure-attention model: a cursor move.
+int32_t tsb_producer_rollback_retaining(tsb_session* s, int32_t stream, int64_t point, int32_t keep_rows) {
+    if (!s) return TSB_ERR_INVALID;
+    TSB_REQUIRE(s->ctx, stream >= 0 && stream < s->n_streams, "stream %d outside the session", stream);
+    const int64_t cur = tsb_kv_cursor(s->target.kv, stream);
+    if (point < 0 || keep_rows < 0 || point + keep_rows > cur)
+        return tsb_fail(s->ctx, TSB_ERR_STATE, "cannot keep %d rows after %lld: the cursor is %lld", keep_rows, (long long)point,
+                        (long long)cur);
+    int32_t rc = tsb_kv_set_cursor(s->target.kv, stream, point + keep_rows);
+    if (rc) return rc;
+    s->target.fed[stream].resize((size_t)(point + keep_rows));
+    return TSB_OK;
+}
+
+int32_t tsb_producer_rewind_drafter(tsb_session* s, int32_t stream, int64_t position) {
+    if (!s) return TSB_ERR_INVALID;
+    if (!s->has_draft) return TSB_OK;
+    TSB_REQUIRE(s->ctx, stream >= 0 && stream < s->n_streams, "stream %d outside the session", stream);
+    if (tsb_kv_cursor(s->draft.kv, stream) > position + 1) return tsb_kv_set_cursor(s->draft.kv, stream, position + 1);
+    return TSB_OK;
+}
+
+// ---- one lockstep round over every stream ----------------------------------
+
+int32_t tsb_session_fill_context(tsb_session* s, int64_t tokens, uint64_t seed) {
+    if (!s) return TSB_ERR_INVALID;
+    DeviceGuard g(s->ctx);
+    for (int q = 0; q < s->n_streams; q++) {
+        int32_t rc = tsb_kv_fill_random(s->target.kv, s->stream, q, tokens, seed + 2 * q);
+        if (rc) return rc;
+        tsb_kv_set_cursor(s->target.kv, q, tokens);
+        s->target.fed[q].assign((size_t)tokens, 0);
+        if (s->has_draft) {
+            if ((rc = tsb_kv_fill_random(s->draft.kv, s->stream, q, tokens, seed + 2 * q + 1))) return rc;
+            tsb_kv_set_cursor(s->draft.kv, q, tokens);
+        }
+    }
+    return tsb_stream_sync(s->ctx, s->stream);
+}
+
+}  // extern "C"
+
+int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_active, int k, const tsb_run_config* cfg,
+                              int32_t* next_tokens_host, int32_t* accepted_host, int32_t* tokens_out, int32_t* draws_out,
+                              uint64_t* draw_step_inout) {
+    tsb_ctx* ctx = s->ctx;
+    if (!s->has_draft) return tsb_fail(ctx, TSB_ERR_STATE, "the session has no drafter");
+    int32_t rc = accept_check_shaping(ctx, &cfg->shaping);
+    if (rc) return rc;
+    const int K = k, S = n_active;
+    TSB_REQUIRE(ctx, K >= 1 && K <= 15 && K + 1 <= s->max_rows, "block must be 1..15 and fit the session's max_rows");
+    TSB_REQUIRE(ctx, S >= 1 && S <= s->n_streams, "bad stream count");
+    cudaStream_t st = s->stream;
+    const int V = s->target.model->cfg.vocab;
+    const double T = cfg->shaping.temperature;
+    const bool sampled = T != 0.0;
+    for (int a = 0; a < S; a++) {
+        const int q = streams[a];
+        TSB_REQUIRE(ctx, q >= 0 && q < s->n_streams, "stream %d outside the session", q);
+        const int64_t ct = tsb_kv_cursor(s->target.kv, q);
+        if (tsb_kv_cursor(s->draft.kv, q) < ct && (rc = drafter_catch_up(s, q, ct))) return rc;  // a lagging drafter replays fed tokens
+        const int64_t cd = tsb_kv_cursor(s->draft.kv, q);
+        if (ct != cd)
+            return tsb_fail(ctx, TSB_ERR_STATE, "stream %d: target cursor %lld and drafter cursor %lld differ", q, (long long)ct,
+                            (long long)cd);
+    }
+    // uniforms: per stream, K draft draws (the row-only step burns one more index), then up to 2K+1 for acceptance
+    const int UD = K, UA = 2 * K + 1;
+    uint64_t* un = s->uniforms_host;
+    for (int a = 0; a < S; a++) {
+        const uint64_t seed = cfg->shaping.seed + (uint64_t)streams[a];
+        for (int d = 0; d < UD; d++) un[(size_t)a * UD + d] = tsb_uniform_u64(cfg->uniform_mode, seed, draw_step_inout[a] + d);
+        for (int j = 0; j < UA; j++)
+            un[(size_t)S * UD + (size_t)a * UA + j] = tsb_uniform_u64(cfg->uniform_mode, seed, draw_step_inout[a] + K + 1 + j);
+        s->feed_host[(size_t)a * (K + 1)] = next_tokens_host[a];
+    }
+    uint64_t* un_draft = s->uniforms_dev;
+    uint64_t* un_acc = s->uniforms_dev + (size_t)S * UD;
+    TSB_CUDA(ctx, cudaMemcpyAsync(s->uniforms_dev, un, (size_t)S * (UD + UA) * sizeof(uint64_t), cudaMemcpyHostToDevice, st));
+    TSB_CUDA(ctx, cudaMemcpyAsync(s->feed_dev, s->feed_host, (size_t)S * (K + 1) * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+
+    TSB_CUDA(ctx, cudaEventRecord(s->ev[0], st));
+    // ---- draft: K steps with a head + one row-only step (crates/runtime/src/speculative.rs:607-659)
+    for (int d = 0; d <= K; d++) {
+        const tsb_row_desc* rd;
+        int max_len;
+        if ((rc = stage_rows(s, s->draft, streams, S, 1, nullptr, nullptr, &rd, nullptr, &max_len))) return rc;
+        const bool head = d < K;
+        TSB_CUDA(ctx, forward_device(s, s->draft, s->feed_dev + d, K + 1, rd, S, 1, max_len,
+                                     head ? s->logits_draft + (size_t)d * V : nullptr, (int64_t)K * V));
+        for (int a = 0; a < S; a++) tsb_kv_set_cursor(s->draft.kv, streams[a], tsb_kv_cursor(s->draft.kv, streams[a]) + 1);
+        if (head)
+            TSB_CUDA(ctx, launch_sample(ctx, st, s->logits_draft + (size_t)d * V, (int64_t)K * V, un_draft + d, UD, S, V, T,
+                                        s->feed_dev + d + 1, K + 1, nullptr, s->accept_scratch));
+    }
+    TSB_CUDA(ctx, cudaEventRecord(s->ev[1], st));
+    // ---- verify: K+1 rows per stream in one pass
+    {
+        const tsb_row_desc* rd;
+        int max_len;
+        if ((rc = stage_rows(s, s->target, streams, S, K + 1, nullptr, nullptr, &rd, nullptr, &max_len))) return rc;
+        TSB_CUDA(ctx, forward_device(s, s->target, s->feed_dev, 1, rd, S * (K + 1), K + 1, max_len, s->logits_target, V));
+    }
+    TSB_CUDA(ctx, cudaEventRecord(s->ev[2], st));
+    // ---- accept on the device; the next confirmed token also lands in feed[.][0]
+    TSB_CUDA(ctx, launch_accept(ctx, st, s->logits_target, s->logits_draft, s->feed_dev + 1, K + 1, un_acc, S, K, V, T,
+                                s->accept_out_dev, s->feed_dev, K + 1, s->accept_scratch));
+    TSB_CUDA(ctx, cudaMemcpyAsync(s->accept_out_host, s->accept_out_dev, (size_t)S * sizeof(tsb_accept_out),
+                                  cudaMemcpyDeviceToHost, st));
+    TSB_CUDA(ctx, cudaEventRecord(s->ev[3], st));
+    if ((rc = tsb_stream_sync(ctx, st))) return rc;
+    s->stage_used = 0;
+    // ---- commit: cursors to the accepted prefix (rollback_retaining + rewind_drafter)
+    for (int a = 0; a < S; a++) {
+        const int q = streams[a];
+        const tsb_accept_out& o = s->accept_out_host[a];
+        if (o.status != 0)
+            return tsb_fail(ctx, TSB_ERR_DEVICE, "stream %d: a logit was not finite or a proposal was out of range", q);
+        const int64_t base = tsb_kv_cursor(s->target.kv, q);
+        auto& fed = s->target.fed[q];
+        fed.resize((size_t)base);
+        fed.push_back(next_tokens_host[a]);
+        for (int i = 0; i < o.accepted; i++) fed.push_back(o.tokens[i]);
+        tsb_kv_set_cursor(s->target.kv, q, base + o.accepted + 1);
+        tsb_kv_set_cursor(s->draft.kv, q, base + o.accepted + 1);
+        accepted_host[a] = o.accepted;
+        if (tokens_out) memcpy(tokens_out + (size_t)a * 16, o.tokens, sizeof(o.tokens));
+        if (draws_out) draws_out[a] = o.draws;
+        next_tokens_host[a] = o.tokens[o.accepted];
+        draw_step_inout[a] += (sampled ? (uint64_t)(K + 1) : 0) + (uint64_t)o.draws;
+    }
+    return TSB_OK;
+}
+
+int32_t session_select_target(tsb_session* s, const tsb_run_config* cfg, uint64_t uniform, int32_t* token_host) {
+    tsb_ctx* ctx = s->ctx;
+    const int V = s->target.model->cfg.vocab;
+    uint64_t* u = s->uniforms_host;
+    u[0] = uniform;
+    TSB_CUDA(ctx, cudaMemcpyAsync(s->uniforms_dev, u, sizeof(uint64_t), cudaMemcpyHostToDevice, s->stream));
+    TSB_CUDA(ctx, launch_sample(ctx, s->stream, s->logits_target, V, s->uniforms_dev, 1, 1, V, cfg->shaping.temperature,
+                                s->tok1_dev, 1, nullptr, s->accept_scratch));
+    TSB_CUDA(ctx, cudaMemcpyAsync(s->feed_host, s->tok1_dev, sizeof(int32_t), cudaMemcpyDeviceToHost, s->stream));
+    int32_t rc = tsb_stream_sync(ctx, s->stream);
+    if (rc) return rc;
+    *token_host = s->feed_host[0];
+    return TSB_OK;
+}
+
+extern "C" {
+
+int32_t tsb_session_round(tsb_session* s, const tsb_run_config* cfg, int32_t* next_tokens_host, int32_t* accepted_host,
+                          uint64_t* draw_step_inout) {
+    if (!s || !cfg || !next_tokens_host || !accepted_host || !draw_step_inout) return TSB_ERR_INVALID;
+    DeviceGuard g(s->ctx);
+    std::vector<int32_t> streams(s->n_streams);
+    for (int q = 0; q < s->n_streams; q++) streams[q] = q;
+    return session_round_streams(s, streams.data(), s->n_streams, cfg->block, cfg, next_tokens_host, accepted_host, nullptr,
+                                 nullptr, draw_step_inout);
+}
+
+int32_t tsb_session_round_times(tsb_session* s, float* out4_ms) {
+    if (!s || !out4_ms) return TSB_ERR_INVALID;
+    DeviceGuard g(s->ctx);
+    for (int i = 0; i < 3; i++)
+        if (cudaEventElapsedTime(&out4_ms[i], s->ev[i], s->ev[i + 1]) != cudaSuccess) out4_ms[i] = -1.f;
+    out4_ms[3] = 0.f;
+    return TSB_OK;
+}
+
+}  // extern "C"

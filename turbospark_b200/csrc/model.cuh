@@ -1,0 +1,80 @@
+// Model, per-model runtime state and session objects behind the opaque C handles.
+#pragma once
+#include <vector>
+
+#include "gemm_quant.cuh"
+#include "kv.cuh"
+
+struct Mat {
+    uint8_t* data = nullptr;
+    int qtype = 0;
+    int64_t rows = 0, cols = 0;
+    bool owned = false;
+};
+
+struct LayerW {
+    Mat wqkv, wo, wgu, wdown;  // q|k|v rows back to back; gate|up rows back to back
+    uint16_t* attn_norm = nullptr;
+    uint16_t* ffn_norm = nullptr;
+    bool norms_owned = false;
+};
+
+struct tsb_model {
+    tsb_ctx* ctx = nullptr;
+    tsb_model_config cfg{};
+    std::vector<LayerW> layers;
+    Mat embed, lm_head;
+    uint16_t* out_norm = nullptr;
+    bool out_norm_owned = false;
+};
+
+struct ActBuf {
+    uint4* xp = nullptr;
+    uint2* xs = nullptr;
+};
+
+// What one model needs to run inside a session.
+struct ModelRt {
+    const tsb_model* model = nullptr;
+    tsb_kv* kv = nullptr;
+    __half *h = nullptr, *qkv = nullptr, *o = nullptr, *gu = nullptr, *dn = nullptr;
+    ActBuf act_d, act_o, act_f;  // matmul operands of width d_model, n_q_heads*head_dim, ffn
+    void* attn_scratch = nullptr;
+    size_t attn_scratch_bytes = 0;
+    std::vector<std::vector<int32_t>> fed;  // per stream: tokens absorbed, by position (target only)
+};
+
+struct tsb_session {
+    tsb_ctx* ctx = nullptr;
+    int n_streams = 0, max_rows = 0;
+    bool has_draft = false;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+    ModelRt target, draft;
+    __half* logits_target = nullptr;  // [n_streams * max_rows, vocab]
+    __half* logits_draft = nullptr;   // [n_streams, k, vocab]
+    int32_t* feed_dev = nullptr;      // [n_streams, k + 1]: confirmed token, then the proposals
+    int32_t* tok1_dev = nullptr;
+    uint64_t* uniforms_dev = nullptr;
+    tsb_accept_out* accept_out_dev = nullptr;
+    void* accept_scratch = nullptr;
+    size_t accept_scratch_bytes = 0;
+    // pinned staging
+    tsb_row_desc* stage_rows_host = nullptr;
+    int32_t* stage_tok_host = nullptr;
+    tsb_row_desc* stage_rows_dev = nullptr;
+    int32_t* stage_tok_dev = nullptr;
+    int stage_cap = 0, stage_used = 0;
+    tsb_accept_out* accept_out_host = nullptr;
+    uint64_t* uniforms_host = nullptr;
+    int32_t* feed_host = nullptr;
+    void* logits_host = nullptr;
+    std::vector<void*> owned;
+};
+
+// One speculative round for the listed streams with k proposals each (model.cu).
+int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_active, int k, const tsb_run_config* cfg,
+                              int32_t* next_tokens_host, int32_t* accepted_host, int32_t* tokens_out /* [n_active][16] */,
+                              int32_t* draws_out, uint64_t* draw_step_inout);
+// token = select(logits row of the last single-row target forward) for one stream (model.cu).
+int32_t session_select_target(tsb_session* s, const tsb_run_config* cfg, uint64_t uniform, int32_t* token_host);

@@ -64,11 +64,11 @@ __device__ __forceinline__ float dequant_elem(const uint8_t* row, int e) {
 
 template <int QT, bool TO_F16>
 __global__ void dequant_rows_kernel(const uint8_t* __restrict__ w, int64_t row_bytes, int64_t table_rows, int cols,
-                                    const int32_t* __restrict__ ids, int n, void* __restrict__ out, float out_scale,
-                                    uint32_t* __restrict__ err) {
+                                    const int32_t* __restrict__ ids, int id_stride, int n, void* __restrict__ out,
+                                    float out_scale, uint32_t* __restrict__ err) {
     pdl_wait();
     const int r = blockIdx.y;
-    int64_t src = ids ? (int64_t)ids[r] : (int64_t)r;
+    int64_t src = ids ? (int64_t)ids[(size_t)r * id_stride] : (int64_t)r;
     if (src < 0 || src >= table_rows) {
         if (threadIdx.x == 0) atomicCAS(err, 0u, (uint32_t)TSB_DEV_BAD_INDEX);
         src = 0;
@@ -247,27 +247,27 @@ __global__ void residual_add_kernel(__half* __restrict__ x, const __half* __rest
 
 template <bool F16>
 cudaError_t launch_dequant(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t table_rows, int cols,
-                           const int32_t* ids, int n, void* out, float scale) {
+                           const int32_t* ids, int id_stride, int n, void* out, float scale) {
     const int64_t rb = tsb_row_bytes(qtype, cols);
     dim3 grid((unsigned)min(8, (cols + 255) / 256), (unsigned)n);
     switch (qtype) {
         case TSB_Q4_K:
             return tsb_launch(ctx, dequant_rows_kernel<TSB_Q4_K, F16>, grid, dim3(256), 0, st, true, w, rb, table_rows,
-                              cols, ids, n, out, scale, ctx->dev_error);
+                              cols, ids, id_stride, n, out, scale, ctx->dev_error);
         case TSB_Q6_K:
             return tsb_launch(ctx, dequant_rows_kernel<TSB_Q6_K, F16>, grid, dim3(256), 0, st, true, w, rb, table_rows,
-                              cols, ids, n, out, scale, ctx->dev_error);
+                              cols, ids, id_stride, n, out, scale, ctx->dev_error);
         default:
             return tsb_launch(ctx, dequant_rows_kernel<TSB_MXFP4, F16>, grid, dim3(256), 0, st, true, w, rb, table_rows,
-                              cols, ids, n, out, scale, ctx->dev_error);
+                              cols, ids, id_stride, n, out, scale, ctx->dev_error);
     }
 }
 
 }  // namespace
 
 cudaError_t launch_embed_rows(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t vocab_rows, int cols,
-                              const int32_t* ids, int n, __half* out, float out_scale) {
-    return launch_dequant<true>(ctx, st, qtype, w, vocab_rows, cols, ids, n, out, out_scale);
+                              const int32_t* ids, int id_stride, int n, __half* out, float out_scale) {
+    return launch_dequant<true>(ctx, st, qtype, w, vocab_rows, cols, ids, id_stride, n, out, out_scale);
 }
 
 cudaError_t launch_rmsnorm_rows(tsb_ctx* ctx, cudaStream_t st, __half* x, const __half* residual, const void* w_bf16,
@@ -293,7 +293,7 @@ int32_t tsb_dequant_rows(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* 
     TSB_REQUIRE(ctx, cols % (qtype == TSB_MXFP4 ? 32 : 256) == 0, "cols is not a whole number of blocks");
     DeviceGuard g(ctx);
     TSB_CUDA(ctx, launch_dequant<false>(ctx, (cudaStream_t)s, qtype, (const uint8_t*)region + w_off, INT64_MAX,
-                                        (int)cols, row_ids, n_rows, out_f32, 1.0f));
+                                        (int)cols, row_ids, 1, n_rows, out_f32, 1.0f));
     return TSB_OK;
 }
 
@@ -306,7 +306,7 @@ int32_t tsb_embed_rows(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* re
     TSB_REQUIRE(ctx, cols % (qtype == TSB_MXFP4 ? 32 : 256) == 0, "cols is not a whole number of blocks");
     DeviceGuard g(ctx);
     TSB_CUDA(ctx, launch_embed_rows(ctx, (cudaStream_t)s, qtype, (const uint8_t*)region + w_off, vocab_rows, (int)cols,
-                                    token_ids, n, (__half*)out_f16, out_scale));
+                                    token_ids, 1, n, (__half*)out_f16, out_scale));
     return TSB_OK;
 }
 

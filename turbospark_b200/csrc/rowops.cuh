@@ -9,7 +9,7 @@ struct ActOut {
 };
 
 cudaError_t launch_embed_rows(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t vocab_rows, int cols,
-                              const int32_t* ids, int n, __half* out, float out_scale);
+                              const int32_t* ids, int id_stride, int n, __half* out, float out_scale);
 // x <- f16(x + residual) when residual != null; out (natural f16, may be null) and/or act get the normed rows.
 cudaError_t launch_rmsnorm_rows(tsb_ctx* ctx, cudaStream_t st, __half* x, const __half* residual, const void* w_bf16,
                                 __half* out, ActOut act, int rows, int d, float eps);

@@ -1,0 +1,242 @@
+"""Model / session bindings and the synthetic configurations the tests and the benchmark use."""
+import ctypes as C
+
+import numpy as np
+
+from . import capi
+from .capi import lib, Shaping
+
+W_Q, W_K, W_V, W_O, W_GATE, W_UP, W_DOWN, W_EMBED, W_LM_HEAD = range(9)
+N_ATTN, N_FFN, N_OUT = range(3)
+
+
+class ModelConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n_layers", "d_model", "n_q_heads", "n_kv_heads", "head_dim", "ffn", "vocab",
+                                         "max_context")] + [("rms_eps", C.c_float), ("rope_theta", C.c_float)]
+
+
+class RunConfig(C.Structure):
+    _fields_ = [("shaping", Shaping), ("max_new_tokens", C.c_int32), ("block", C.c_int32), ("uniform_mode", C.c_int32),
+                ("n_stop", C.c_int32), ("stop_tokens", C.c_int32 * 8), ("adaptive", C.c_int32)]
+
+
+class RunResult(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("new_tokens", "reason", "rounds", "accepted_total", "rollbacks", "history_len")] + \
+               [("kv_position", C.c_int64), ("draws", C.c_uint64), ("prefill_seconds", C.c_double),
+                ("decode_seconds", C.c_double)]
+
+
+def run_config(shaping_cfg, max_new_tokens, block, uniform_mode=0, stop_tokens=(), adaptive=0):
+    rc = RunConfig()
+    rc.shaping = shaping_cfg
+    rc.max_new_tokens, rc.block, rc.uniform_mode, rc.adaptive = max_new_tokens, block, uniform_mode, adaptive
+    rc.n_stop = len(stop_tokens)
+    for i, t in enumerate(stop_tokens):
+        rc.stop_tokens[i] = t
+    return rc
+
+
+# Configurations named by the benchmark definition (shapes only; weights are synthetic).
+def config_tiny(max_context=1024):
+    """4-layer Llama-style decoder: d 512, 8 q x 64, 2 kv, SwiGLU FFN 1408 zero-padded to 1536 (Q4_K needs whole
+    256-column superblocks), RMSNorm eps 1e-6, RoPE theta 1e4, vocabulary 8192."""
+    return ModelConfig(4, 512, 8, 2, 64, 1536, 8192, max_context, 1e-6, 1e4)
+
+
+def config_8b_target(max_context=4608):
+    return ModelConfig(32, 4096, 32, 8, 128, 14336, 128256, max_context, 1e-5, 5e5)
+
+
+def config_8b_draft(max_context=4608):
+    return ModelConfig(16, 2048, 32, 8, 64, 8192, 128256, max_context, 1e-5, 5e5)
+
+
+class Model:
+    def __init__(self, ctx, cfg):
+        self.ctx, self.cfg = ctx, cfg
+        h = C.c_void_p()
+        ctx.check(lib().tsb_model_create(ctx.h, C.byref(cfg), C.byref(h)))
+        self.h = h
+
+    def set_matrix(self, layer, which, qtype, blocks, rows, cols):
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        self.ctx.check(lib().tsb_model_set_matrix(self.h, C.c_int32(layer), C.c_int32(which), C.c_int32(qtype),
+                                                  blocks.ctypes.data_as(C.c_void_p), C.c_int64(rows), C.c_int64(cols)))
+
+    def set_norm(self, layer, which, bf16):
+        bf16 = np.ascontiguousarray(bf16, dtype=np.uint16)
+        self.ctx.check(lib().tsb_model_set_norm(self.h, C.c_int32(layer), C.c_int32(which),
+                                                bf16.ctypes.data_as(C.c_void_p), C.c_int32(bf16.size)))
+
+    def share(self, dst_layer, src, src_layer):
+        self.ctx.check(lib().tsb_model_share(self.h, C.c_int32(dst_layer), src.h, C.c_int32(src_layer)))
+
+    def fill_synthetic(self, qtype=capi.Q4_K, lm_head_qtype=None, seed=0):
+        self.ctx.check(lib().tsb_model_fill_synthetic(self.h, C.c_int32(qtype),
+                                                      C.c_int32(qtype if lm_head_qtype is None else lm_head_qtype),
+                                                      C.c_uint64(seed)))
+
+    @property
+    def weight_bytes(self):
+        lib().tsb_model_weight_bytes.restype = C.c_int64
+        return int(lib().tsb_model_weight_bytes(self.h))
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib().tsb_model_destroy(self.h)
+            self.h = None
+
+
+class Session:
+    def __init__(self, ctx, target, draft, n_streams, max_rows, page_tokens=64):
+        self.ctx, self.target, self.draft = ctx, target, draft
+        self.n_streams, self.max_rows = n_streams, max_rows
+        h = C.c_void_p()
+        ctx.check(lib().tsb_session_create(ctx.h, target.h, draft.h if draft else None, C.c_int32(n_streams),
+                                           C.c_int32(max_rows), C.c_int32(page_tokens), C.byref(h)))
+        self.h = h
+        self.vocab = target.cfg.vocab
+
+    def _logits(self, n):
+        return np.empty((n, self.vocab), dtype=np.uint16)
+
+    def reset(self, stream=0):
+        self.ctx.check(lib().tsb_producer_reset(self.h, C.c_int32(stream)))
+
+    def produce(self, token, position, stream=0, want_logits=True):
+        out = self._logits(1) if want_logits else None
+        self.ctx.check(lib().tsb_producer_produce(self.h, C.c_int32(stream), C.c_int32(token), C.c_int64(position),
+                                                  out.ctypes.data_as(C.c_void_p) if want_logits else None))
+        return out[0] if want_logits else None
+
+    def produce_prefill(self, token, position, stream=0):
+        self.ctx.check(lib().tsb_producer_produce_prefill(self.h, C.c_int32(stream), C.c_int32(token), C.c_int64(position)))
+
+    def prime_drafter(self, nxt, position, stream=0):
+        self.ctx.check(lib().tsb_producer_prime_drafter(self.h, C.c_int32(stream), C.c_int32(nxt), C.c_int64(position)))
+
+    def draft_step(self, nxt, position, stream=0):
+        out = self._logits(1)
+        self.ctx.check(lib().tsb_producer_draft_step(self.h, C.c_int32(stream), C.c_int32(nxt), C.c_int64(position),
+                                                     out.ctypes.data_as(C.c_void_p)))
+        return out[0]
+
+    def verify(self, feed, base, stream=0):
+        feed = np.ascontiguousarray(feed, dtype=np.int32)
+        out = self._logits(feed.size)
+        self.ctx.check(lib().tsb_producer_verify(self.h, C.c_int32(stream), feed.ctypes.data_as(C.c_void_p),
+                                                 C.c_int32(feed.size), C.c_int64(base), out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def verify_tree(self, feed, slot_parent, base, stream=0):
+        feed = np.ascontiguousarray(feed, dtype=np.int32)
+        par = np.ascontiguousarray(slot_parent, dtype=np.int32)
+        out = self._logits(feed.size)
+        self.ctx.check(lib().tsb_producer_verify_tree(self.h, C.c_int32(stream), feed.ctypes.data_as(C.c_void_p),
+                                                      par.ctypes.data_as(C.c_void_p), C.c_int32(feed.size), C.c_int64(base),
+                                                      out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def compact_tree(self, base, path, stream=0):
+        p = np.ascontiguousarray(path, dtype=np.uint32)
+        self.ctx.check(lib().tsb_producer_compact_tree(self.h, C.c_int32(stream), C.c_int64(base),
+                                                       p.ctypes.data_as(C.c_void_p), C.c_int32(p.size)))
+
+    def checkpoint(self, stream=0):
+        lib().tsb_producer_checkpoint.restype = C.c_int64
+        return int(lib().tsb_producer_checkpoint(self.h, C.c_int32(stream)))
+
+    def rollback_retaining(self, point, keep_rows, stream=0):
+        self.ctx.check(lib().tsb_producer_rollback_retaining(self.h, C.c_int32(stream), C.c_int64(point), C.c_int32(keep_rows)))
+
+    def rewind_drafter(self, position, stream=0):
+        self.ctx.check(lib().tsb_producer_rewind_drafter(self.h, C.c_int32(stream), C.c_int64(position)))
+
+    def _run(self, fn, prompt, rc, stream):
+        p = np.ascontiguousarray(prompt, dtype=np.int32)
+        toks = np.zeros(p.size + rc.max_new_tokens + 8, dtype=np.int32)
+        emitted = np.zeros(rc.max_new_tokens + 8, dtype=np.int32)
+        res = RunResult()
+        self.ctx.check(fn(self.h, C.c_int32(stream), p.ctypes.data_as(C.c_void_p), C.c_int32(p.size), C.byref(rc),
+                          toks.ctypes.data_as(C.c_void_p), emitted.ctypes.data_as(C.c_void_p), C.byref(res)))
+        return toks[:res.history_len].copy(), emitted[:res.new_tokens].copy(), res
+
+    def spec_run(self, prompt, rc, stream=0):
+        return self._run(lib().tsb_spec_run, prompt, rc, stream)
+
+    def sequential_run(self, prompt, rc, stream=0):
+        return self._run(lib().tsb_sequential_run, prompt, rc, stream)
+
+    def fill_context(self, tokens, seed=0):
+        self.ctx.check(lib().tsb_session_fill_context(self.h, C.c_int64(tokens), C.c_uint64(seed)))
+
+    def round(self, rc, next_tokens, draw_steps):
+        """One lockstep round; next_tokens (int32[n_streams]) and draw_steps (uint64[n_streams]) are updated in place."""
+        accepted = np.zeros(self.n_streams, dtype=np.int32)
+        self.ctx.check(lib().tsb_session_round(self.h, C.byref(rc), next_tokens.ctypes.data_as(C.c_void_p),
+                                               accepted.ctypes.data_as(C.c_void_p), draw_steps.ctypes.data_as(C.c_void_p)))
+        return accepted
+
+    def round_times(self):
+        t = (C.c_float * 4)()
+        self.ctx.check(lib().tsb_session_round_times(self.h, t))
+        return list(t)
+
+    def kv(self, which=0):
+        lib().tsb_session_kv.restype = C.c_void_p
+        k = capi.KvCache.__new__(capi.KvCache)
+        cfg = (self.target if which == 0 else self.draft).cfg
+        k.ctx, k.layers, k.kv_heads, k.head_dim = self.ctx, cfg.n_layers, cfg.n_kv_heads, cfg.head_dim
+        k.h = C.c_void_p(lib().tsb_session_kv(self.h, C.c_int32(which)))
+        return k
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib().tsb_session_destroy(self.h)
+            self.h = None
+
+
+def random_weights(cfg, seed, oracle, qtype=capi.Q4_K, std=0.02, real_ffn=None):
+    """Seeded N(0, std) weights quantized by the oracle's encoder (test / small-model set-up).  Returns a dict
+    (layer, which) -> (blocks uint8 [rows, row_bytes], rows, cols) and norms (layer, which) -> bf16 bits.
+    real_ffn < cfg.ffn zero-pads the FFN (rows of gate/up and columns of down beyond real_ffn are zero)."""
+    rng = np.random.default_rng(seed)
+    qd, kd, d, f = cfg.n_q_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim, cfg.d_model, cfg.ffn
+    rf = real_ffn or f
+    mats, norms = {}, {}
+
+    def mk(rows, cols, zero_rows_from=None, zero_cols_from=None):
+        w = (rng.standard_normal((rows, cols)) * std).astype(np.float32)
+        if zero_rows_from is not None:
+            w[zero_rows_from:] = 0
+        if zero_cols_from is not None:
+            w[:, zero_cols_from:] = 0
+        return oracle.quantize(qtype, w), rows, cols
+
+    mats[(-1, W_EMBED)] = mk(cfg.vocab, d)
+    for l in range(cfg.n_layers):
+        mats[(l, W_Q)] = mk(qd, d)
+        mats[(l, W_K)] = mk(kd, d)
+        mats[(l, W_V)] = mk(kd, d)
+        mats[(l, W_O)] = mk(d, qd)
+        mats[(l, W_GATE)] = mk(f, d, zero_rows_from=rf)
+        mats[(l, W_UP)] = mk(f, d, zero_rows_from=rf)
+        mats[(l, W_DOWN)] = mk(d, f, zero_cols_from=rf)
+        for which in (N_ATTN, N_FFN):
+            norms[(l, which)] = np.array([oracle.lib().tso_f32_to_bf16(float(v)) for v in 1.0 + 0.05 * rng.standard_normal(d)], dtype=np.uint16)
+    mats[(-1, W_LM_HEAD)] = mk(cfg.vocab, d)
+    norms[(-1, N_OUT)] = np.array([oracle.lib().tso_f32_to_bf16(float(v)) for v in 1.0 + 0.05 * rng.standard_normal(d)], dtype=np.uint16)
+    return mats, norms
+
+
+def load_weights(model, mats, norms, qtype=capi.Q4_K, layers=None):
+    """Push a random_weights() set into a tsb Model or an oracle Model (same builder interface)."""
+    n_layers = model.cfg.n_layers if layers is None else layers
+    for (l, which), (blocks, rows, cols) in mats.items():
+        if l >= n_layers:
+            continue
+        model.set_matrix(max(l, 0), which, qtype, blocks, rows, cols)
+    for (l, which), bits in norms.items():
+        if l >= n_layers:
+            continue
+        model.set_norm(max(l, 0), which, bits)
