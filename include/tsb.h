@@ -368,6 +368,14 @@ TSB_API int32_t tsb_session_round_times(tsb_session* s, float* out4_ms);
  * them with seeded pseudo-random K/V. */
 TSB_API int32_t tsb_session_fill_context(tsb_session* s, int64_t tokens, uint64_t seed);
 
+/* The CUDA stream (cudaStream_t) the session enqueues on, so a caller can record its own events on it. */
+TSB_API void* tsb_session_stream(tsb_session* s);
+/* Measurement aid: enqueue the target's per-layer matmul sequence (qkv, o_proj, gate|up, down for every layer:
+ * the kernels that dominate a verify pass) `iters` times for `rows` token rows over whatever the activation
+ * buffers hold, and return the elapsed device time and the weight bytes one sequence streams. */
+TSB_API int32_t tsb_session_time_matmuls(tsb_session* s, int32_t rows, int32_t iters, float* out_ms, int64_t* out_bytes_per_iter,
+                                         int32_t* out_launches_per_iter);
+
 #ifdef __cplusplus
 }
 #endif

@@ -182,6 +182,18 @@ class Session:
         self.ctx.check(lib().tsb_session_round_times(self.h, t))
         return list(t)
 
+    @property
+    def stream_ptr(self):
+        lib().tsb_session_stream.restype = C.c_void_p
+        return int(lib().tsb_session_stream(self.h))
+
+    def time_matmuls(self, rows, iters):
+        """-> (ms per sequence, algorithmic bytes per sequence, launches per sequence)"""
+        ms, by, ln = C.c_float(), C.c_int64(), C.c_int32()
+        self.ctx.check(lib().tsb_session_time_matmuls(self.h, C.c_int32(rows), C.c_int32(iters), C.byref(ms), C.byref(by),
+                                                      C.byref(ln)))
+        return ms.value / iters, by.value, ln.value
+
     def kv(self, which=0):
         lib().tsb_session_kv.restype = C.c_void_p
         k = capi.KvCache.__new__(capi.KvCache)
