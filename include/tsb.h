@@ -362,7 +362,11 @@ TSB_API int32_t tsb_sequential_run(tsb_session* s, int32_t stream, const int32_t
  * Streams must have equal cursors in the target and draft caches (lockstep). */
 TSB_API int32_t tsb_session_round(tsb_session* s, const tsb_run_config* cfg, int32_t* next_tokens_host,
                                   int32_t* accepted_host, uint64_t* draw_step_inout);
-/* Timings of the last tsb_session_round in milliseconds: draft, verify, accept, commit (CUDA events). */
+/* Rounds run as one CUDA graph after the first (copies, kernels); 0 switches to plain launches, which is what
+ * makes the per-phase timings below available.  Env TSB_GRAPH=0 does the same at session creation. */
+TSB_API int32_t tsb_session_set_graph(tsb_session* s, int32_t enabled);
+/* Device time of the last tsb_session_round in milliseconds (CUDA events): [0] draft, [1] verify, [2] accept
+ * (-1 when the round ran as a graph), [3] the whole round. */
 TSB_API int32_t tsb_session_round_times(tsb_session* s, float* out4_ms);
 /* Benchmark set-up: pretend `tokens` positions are committed in both caches of every stream, filling
  * them with seeded pseudo-random K/V. */

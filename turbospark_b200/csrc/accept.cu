@@ -5,27 +5,36 @@
 // sampler it calls (crates/selection/src/choose.rs:111-321, distribution.rs:57-125).
 // The reference shapes every row into an explicit distribution in RANK order
 // (probability descending, ties by ascending index) and walks cumulative sums
-// in that order; everything is f64, summed sequentially.  This kernel keeps the
-// arithmetic in f64 and the order semantics, but replaces the sort + sequential
-// walk by an order-preserving radix descent over the logit keys with exact
-// integer (2^-60 fixed point) bin masses, so the result does not depend on
-// thread scheduling.  Decisions (accept / reject, drawn token) equal the
+// in that order; everything is f64, summed sequentially.  These kernels keep
+// the arithmetic in f64 and the order semantics, but replace the sort and the
+// sequential walk by an order-preserving radix descent over the logit keys with
+// exact integer (2^-60 fixed point) bin masses, so the outcome does not depend
+// on thread scheduling.  Decisions (accept / reject, drawn token) equal the
 // reference's unless a uniform lies within ~1e-13 of a decision boundary; the
-// distances to the nearest boundary are returned so such a case is visible.
+// distance to the nearest boundary is returned so such a case is visible.
 //
-// Shaping covered here: temperature (including 0 = argmax), whole vocabulary
-// (top_k = 0, top_p off, min_p off), no penalties.
+// Shaping covered: temperature (0 = argmax), whole vocabulary (top_k = 0, top_p
+// and min_p off), no penalties.
 //
-// Kernel 1 (one CTA per logits row): max, first argmax, sum = sum_i exp(l_i - max)
-// and total = sum_i w_i with w_i = ((e_i / sum) / top)^(1/T).
-// Kernel 2 (one CTA per stream): the accept chain on thread 0, then the one draw
-// the round needs (residual, or bonus from the last row) by the whole CTA.
+// Parallel layout: one thread-block cluster of eight CTAs per logits row
+// (statistics) or per stream (decision + draw).  Each CTA owns a contiguous
+// eighth of the vocabulary, keeps its f64 exponentials / fixed-point masses in
+// its own shared memory, and the eight CTAs reduce and broadcast through
+// distributed shared memory in a fixed rank order.  Everything a draw needs
+// stays on chip: the logits are read from HBM/L2 once or twice per row.
+#include <cooperative_groups.h>
+
 #include "accept.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 
 constexpr int ACC_THREADS = 1024;
+constexpr int CL = 8;               // CTAs per cluster
+constexpr int SLICE_MAX = 20480;    // vocabulary entries one CTA can hold (8 * 20480 = 163840)
 constexpr int NBINS = 2048;
+constexpr double FP_ONE = 1152921504606846976.0;  // 2^60
 
 struct RowStats {
     float max;
@@ -35,6 +44,28 @@ struct RowStats {
     int32_t nonfinite;
     int32_t _pad;
 };
+
+// Exchange area every CTA of a cluster exposes to its peers.
+struct Xchg {
+    double d[4];
+    unsigned long long u[4];
+    float f;
+    int i[4];
+};
+
+__device__ __forceinline__ uint32_t desc_key(float x) {
+    // ascending unsigned order of the key == descending order of x
+    uint32_t u = __float_as_uint(x);
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return ~u;
+}
+
+// w_i of reweight (choose.rs:296-321): ((e/sum)/top)^(1/T), top = max_i e_i/sum = 1/sum.
+__device__ __forceinline__ double weight_of(double e, double sum, double top, double inv_t, bool unit_t) {
+    const double p = e / sum;
+    const double r = top > 0.0 ? p / top : p;
+    return unit_t ? r : pow(r, inv_t);
+}
 
 __device__ __forceinline__ double block_sum_f64(double v, double* red) {
     // fixed shape: lane tree, then warps in index order
@@ -48,44 +79,58 @@ __device__ __forceinline__ double block_sum_f64(double v, double* red) {
     return t;
 }
 
-__device__ __forceinline__ uint32_t desc_key(float x) {
-    // ascending unsigned order of ~key == descending order of x
-    uint32_t u = __float_as_uint(x);
-    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-    return ~u;
+// Sum of one double per CTA over the cluster, ranks in order.  Slot selects which field of the exchange area.
+__device__ __forceinline__ double cluster_sum_f64(cg::cluster_group& cluster, Xchg* x, int slot, double mine) {
+    if (threadIdx.x == 0) x->d[slot] = mine;
+    cluster.sync();
+    double t = 0.0;
+    for (int r = 0; r < CL; r++) t += cluster.map_shared_rank(x, r)->d[slot];
+    cluster.sync();
+    return t;
 }
 
-// w_i of reweight (choose.rs:296-321): ((e/sum)/top)^(1/T), top = max_i e_i/sum = 1/sum.
-__device__ __forceinline__ double weight_of(double e, double sum, double top, double inv_t, bool unit_t) {
-    const double p = e / sum;
-    const double r = top > 0.0 ? p / top : p;
-    return unit_t ? r : pow(r, inv_t);
+struct Slice {
+    int lo, n;
+};
+__device__ __forceinline__ Slice my_slice(int vocab, int rank) {
+    const int sl = ((vocab + CL - 1) / CL + 1) & ~1;
+    Slice s;
+    s.lo = min(vocab, rank * sl);
+    s.n = min(vocab, s.lo + sl) - s.lo;
+    return s;
 }
 
+// ---------------------------------------------------------------- statistics
+// One cluster per row: max / first argmax / finiteness, sum_i exp(l_i - max), total = sum_i w_i.
 __global__ void __launch_bounds__(ACC_THREADS)
     accept_stats_kernel(const __half* __restrict__ target, const __half* __restrict__ draft, int k, int vocab,
                         double temperature, RowStats* __restrict__ stats, int rows_per_stream, int64_t single_stride) {
+    extern __shared__ __align__(16) uint8_t dyn[];
+    double* ecache = reinterpret_cast<double*>(dyn);  // exp(l - max) of this CTA's slice
+    __shared__ Xchg xch;
     __shared__ double red[ACC_THREADS / 32];
     __shared__ float fred[ACC_THREADS / 32];
     __shared__ int ired[ACC_THREADS / 32];
-    __shared__ int nf_flag;
+    __shared__ int bad_flag;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
+    const int row_id = blockIdx.x / CL;
     pdl_wait();
-    const int b = blockIdx.x / rows_per_stream, r = blockIdx.x % rows_per_stream;
-    // rows 0..k are the target's, k+1..2k the drafter's
-    // single_stride != 0: one row per stream, `single_stride` elements apart (the draft-side draw)
+    const int b = row_id / rows_per_stream, r = row_id % rows_per_stream;
+    // rows 0..k are the target's, k+1..2k the drafter's; single_stride != 0: one row per stream, that many elements apart
     const __half* row = single_stride ? target + (size_t)b * single_stride
                         : (r <= k)    ? target + ((size_t)b * (k + 1) + r) * vocab
                                       : draft + ((size_t)b * k + (r - k - 1)) * vocab;
-    if (threadIdx.x == 0) nf_flag = 0;
+    const Slice sl = my_slice(vocab, rank);
+    if (threadIdx.x == 0) bad_flag = 0;
     __syncthreads();
-    // pass A: max and first argmax, finiteness
     float mx = -INFINITY;
     int am = 0x7fffffff;
     bool bad = false;
-    for (int i = threadIdx.x; i < vocab; i += ACC_THREADS) {
-        const float v = __half2float(row[i]);
+    for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
+        const float v = __half2float(row[sl.lo + j]);
         bad |= !isfinite(v);
-        if (v > mx || (v == mx && i < am)) mx = v, am = i;
+        if (v > mx) mx = v, am = sl.lo + j;  // indices grow with j, so the first maximum is kept
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -93,30 +138,47 @@ __global__ void __launch_bounds__(ACC_THREADS)
         const int oam = __shfl_xor_sync(0xffffffffu, am, o);
         if (omx > mx || (omx == mx && oam < am)) mx = omx, am = oam;
     }
-    if (bad) nf_flag = 1;
+    if (bad) bad_flag = 1;
     if ((threadIdx.x & 31) == 0) fred[threadIdx.x >> 5] = mx, ired[threadIdx.x >> 5] = am;
     __syncthreads();
-    mx = fred[0], am = ired[0];
-    for (int i = 1; i < ACC_THREADS / 32; i++)
-        if (fred[i] > mx || (fred[i] == mx && ired[i] < am)) mx = fred[i], am = ired[i];
+    if (threadIdx.x == 0) {
+        mx = fred[0], am = ired[0];
+        for (int i = 1; i < ACC_THREADS / 32; i++)
+            if (fred[i] > mx || (fred[i] == mx && ired[i] < am)) mx = fred[i], am = ired[i];
+        xch.f = mx, xch.i[0] = am, xch.i[1] = bad_flag;
+    }
+    cluster.sync();
+    int nonfinite = 0;
+    mx = -INFINITY, am = 0x7fffffff;
+    for (int rr = 0; rr < CL; rr++) {
+        const Xchg* o = cluster.map_shared_rank(&xch, rr);
+        const float omx = o->f;
+        const int oam = o->i[0];
+        nonfinite |= o->i[1];
+        if (omx > mx || (omx == mx && oam < am)) mx = omx, am = oam;
+    }
+    cluster.sync();
     RowStats st;
-    st.max = mx, st.argmax = am, st.sum = 1.0, st.total = 1.0, st.nonfinite = nf_flag, st._pad = 0;
-    if (temperature != 0.0 && !nf_flag) {
+    st.max = mx, st.argmax = am, st.sum = 1.0, st.total = 1.0, st.nonfinite = nonfinite, st._pad = 0;
+    if (temperature != 0.0 && !nonfinite) {
         const double dmx = (double)mx;
         double s = 0.0;
-        for (int i = threadIdx.x; i < vocab; i += ACC_THREADS) s += exp((double)__half2float(row[i]) - dmx);
-        const double sum = block_sum_f64(s, red);
+        for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
+            const double e = exp((double)__half2float(row[sl.lo + j]) - dmx);
+            ecache[j] = e;
+            s += e;
+        }
+        const double sum = cluster_sum_f64(cluster, &xch, 0, block_sum_f64(s, red));
         const double top = 1.0 / sum;  // the max entry's exp is exactly 1
         const double inv_t = 1.0 / temperature;
         const bool unit_t = temperature == 1.0;
         double t = 0.0;
-        for (int i = threadIdx.x; i < vocab; i += ACC_THREADS)
-            t += weight_of(exp((double)__half2float(row[i]) - dmx), sum, top, inv_t, unit_t);
-        const double total = block_sum_f64(t, red);
-        st.sum = sum, st.total = total;
+        for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) t += weight_of(ecache[j], sum, top, inv_t, unit_t);
+        st.sum = sum;
+        st.total = cluster_sum_f64(cluster, &xch, 1, block_sum_f64(t, red));
     }
     pdl_launch_dependents();
-    if (threadIdx.x == 0) stats[blockIdx.x] = st;
+    if (rank == 0 && threadIdx.x == 0) stats[row_id] = st;
 }
 
 // probability of one token under a row's shaped distribution (distribution.rs:61-66 over the full support)
@@ -126,56 +188,27 @@ __device__ __forceinline__ double prob_of(const __half* row, const RowStats& st,
     return st.total > 0.0 ? w / st.total : 0.0;
 }
 
-struct DrawCtx {
+// --------------------------------------------------------------------- draw
+struct DrawShared {
     unsigned long long hist[NBINS];
-    unsigned long long scan[ACC_THREADS];
+    unsigned long long scan[ACC_THREADS / 32];
     double red[ACC_THREADS / 32];
-    unsigned long long last_key;  // fallback: smallest exp (bits) then largest index
-    unsigned int last_idx;
+    Xchg xch;
+    // written by rank 0 for everybody, or by the winning CTA into rank 0
     unsigned int sel_bin;
     unsigned long long sel_before;
     int result;
     unsigned long long gap_lo, gap_hi;
+    unsigned long long best_exp;
+    unsigned int best_idx;
 };
 
-// Exclusive scan of hist[0..NBINS) in place by the block; finds the first bin whose inclusive prefix
-// exceeds `target` (strictly), returns it through ctx.sel_bin with the prefix before it.  If no bin
-// does (rounding at the tail) sel_bin = NBINS.
-__device__ void find_bin(DrawCtx& c, unsigned long long target, unsigned long long before) {
-    constexpr int PER = NBINS / ACC_THREADS;  // 2
-    unsigned long long loc[PER], s = 0;
-#pragma unroll
-    for (int j = 0; j < PER; j++) loc[j] = c.hist[threadIdx.x * PER + j], s += loc[j];
-    // block exclusive scan of s
-    unsigned long long v = s;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const unsigned long long n = __shfl_up_sync(0xffffffffu, v, o);
-        if ((threadIdx.x & 31) >= o) v += n;
-    }
-    __syncthreads();
-    if ((threadIdx.x & 31) == 31) c.scan[threadIdx.x >> 5] = v;
-    if (threadIdx.x == 0) c.sel_bin = NBINS, c.sel_before = 0;
-    __syncthreads();
-    unsigned long long wbase = 0;
-    for (int i = 0; i < (int)(threadIdx.x >> 5); i++) wbase += c.scan[i];
-    unsigned long long run = before + wbase + v - s;  // mass before this thread's first bin
-#pragma unroll
-    for (int j = 0; j < PER; j++) {
-        const unsigned long long after = run + loc[j];
-        if (target >= run && target < after) {  // exactly one thread/bin satisfies this
-            c.sel_bin = threadIdx.x * PER + j;
-            c.sel_before = run;
-        }
-        run = after;
-    }
-    __syncthreads();
-}
-
-// One draw from a distribution given as fixed-point masses fp[i] (2^-60 units) over keys key(i), in rank
-// order (key ascending = logit descending, ties index ascending).  target in 2^-60 units.
-__device__ int radix_draw(DrawCtx& c, const __half* __restrict__ krow, const unsigned long long* __restrict__ fp,
-                          int vocab, unsigned long long target, unsigned long long* gap_lo, unsigned long long* gap_hi) {
+// The draw over this cluster's row: fp[] holds every CTA's slice of fixed-point masses (2^-60 units), keys come
+// from krow.  target in 2^-60 units.  Returns the token (same value in every CTA), -1 for "past the end".
+__device__ int cluster_radix_draw(cg::cluster_group& cluster, DrawShared& c, const unsigned long long* fp,
+                                  const __half* __restrict__ krow, Slice sl, unsigned long long target,
+                                  unsigned long long* gap) {
+    const int rank = (int)cluster.block_rank();
     uint32_t prefix = 0;
     unsigned long long before = 0;
     const int shifts[3] = {21, 10, 0};
@@ -185,27 +218,60 @@ __device__ int radix_draw(DrawCtx& c, const __half* __restrict__ krow, const uns
         for (int i = threadIdx.x; i < NBINS; i += ACC_THREADS) c.hist[i] = 0;
         __syncthreads();
         const uint32_t hi_mask = done_bits ? (0xFFFFFFFFu << (32 - done_bits)) : 0u;
-        for (int i = threadIdx.x; i < vocab; i += ACC_THREADS) {
-            const uint32_t kd = desc_key(__half2float(krow[i]));
+        for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
+            const uint32_t kd = desc_key(__half2float(krow[sl.lo + j]));
             if ((kd & hi_mask) == prefix) {
-                const unsigned long long m = fp[i];
+                const unsigned long long m = fp[j];
                 if (m) atomicAdd(&c.hist[(kd >> shifts[pass]) & ((1u << widths[pass]) - 1)], m);
             }
         }
-        __syncthreads();
-        find_bin(c, target, before);
-        if (c.sel_bin == NBINS) return -1;  // past the end: the caller takes the last support entry
-        prefix |= c.sel_bin << shifts[pass];
-        before = c.sel_before;
+        cluster.sync();
+        if (rank == 0) {
+            // sum the eight histograms bin by bin, scan, find the bin the target falls into
+            constexpr int PER = NBINS / ACC_THREADS;  // 2
+            unsigned long long loc[PER], s = 0;
+#pragma unroll
+            for (int j = 0; j < PER; j++) {
+                unsigned long long t = 0;
+                for (int rr = 0; rr < CL; rr++) t += cluster.map_shared_rank(c.hist, rr)[threadIdx.x * PER + j];
+                loc[j] = t, s += t;
+            }
+            unsigned long long v = s;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long n = __shfl_up_sync(0xffffffffu, v, o);
+                if ((threadIdx.x & 31) >= o) v += n;
+            }
+            if ((threadIdx.x & 31) == 31) c.scan[threadIdx.x >> 5] = v;
+            if (threadIdx.x == 0) c.sel_bin = NBINS, c.sel_before = 0;
+            __syncthreads();
+            unsigned long long wbase = 0;
+            for (int i = 0; i < (int)(threadIdx.x >> 5); i++) wbase += c.scan[i];
+            unsigned long long run = before + wbase + v - s;
+#pragma unroll
+            for (int j = 0; j < PER; j++) {
+                const unsigned long long after = run + loc[j];
+                if (target >= run && target < after) c.sel_bin = threadIdx.x * PER + j, c.sel_before = run;
+                run = after;
+            }
+        }
+        cluster.sync();
+        const DrawShared* root = cluster.map_shared_rank(&c, 0);
+        const unsigned int bin = root->sel_bin;
+        const unsigned long long bef = root->sel_before;
+        cluster.sync();
+        if (bin == NBINS) return -1;
+        prefix |= bin << shifts[pass];
+        before = bef;
         done_bits += widths[pass];
-        __syncthreads();
     }
-    // all members share the key: walk them in index order (contiguous index ranges per thread)
-    const int per = (vocab + ACC_THREADS - 1) / ACC_THREADS;
-    const int lo = threadIdx.x * per, hi = min(vocab, lo + per);
+    // every member shares the key: walk them in index order.  Threads own contiguous runs of their CTA's slice;
+    // CTAs are ordered by rank.
+    const int per = (sl.n + ACC_THREADS - 1) / ACC_THREADS;
+    const int lo = min(sl.n, (int)threadIdx.x * per), hi = min(sl.n, lo + per);
     unsigned long long mine = 0;
-    for (int i = lo; i < hi; i++)
-        if (desc_key(__half2float(krow[i])) == prefix) mine += fp[i];
+    for (int j = lo; j < hi; j++)
+        if (desc_key(__half2float(krow[sl.lo + j])) == prefix) mine += fp[j];
     unsigned long long v = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -216,82 +282,96 @@ __device__ int radix_draw(DrawCtx& c, const __half* __restrict__ krow, const uns
     if ((threadIdx.x & 31) == 31) c.scan[threadIdx.x >> 5] = v;
     if (threadIdx.x == 0) c.result = -1;
     __syncthreads();
-    unsigned long long wbase = 0;
-    for (int i = 0; i < (int)(threadIdx.x >> 5); i++) wbase += c.scan[i];
-    unsigned long long run = before + wbase + v - mine;
-    for (int i = lo; i < hi; i++) {
-        if (desc_key(__half2float(krow[i])) != prefix) continue;
-        const unsigned long long after = run + fp[i];
-        if (target >= run && target < after) {
-            c.result = i;
-            c.gap_lo = target - run;
-            c.gap_hi = after - target;
+    unsigned long long wbase = 0, cta_total = 0;
+    for (int i = 0; i < ACC_THREADS / 32; i++) {
+        if (i < (int)(threadIdx.x >> 5)) wbase += c.scan[i];
+        cta_total += c.scan[i];
+    }
+    if (threadIdx.x == 0) c.xch.u[0] = cta_total;
+    cluster.sync();
+    unsigned long long rank_base = 0;
+    for (int rr = 0; rr < rank; rr++) rank_base += cluster.map_shared_rank(&c.xch, rr)->u[0];
+    unsigned long long run = before + rank_base + wbase + v - mine;
+    DrawShared* root = cluster.map_shared_rank(&c, 0);
+    for (int j = lo; j < hi; j++) {
+        if (desc_key(__half2float(krow[sl.lo + j])) != prefix) continue;
+        const unsigned long long after = run + fp[j];
+        if (target >= run && target < after) {  // exactly one thread of one CTA
+            root->result = sl.lo + j;
+            root->gap_lo = target - run;
+            root->gap_hi = after - target;
         }
         run = after;
     }
-    __syncthreads();
-    *gap_lo = c.gap_lo;
-    *gap_hi = c.gap_hi;
-    return c.result;
+    cluster.sync();
+    const int res = root->result;
+    const unsigned long long gl = root->gap_lo, gh = root->gap_hi;
+    cluster.sync();
+    *gap = gl < gh ? gl : gh;
+    return res;
 }
 
-constexpr double FP_ONE = 1152921504606846976.0;  // 2^60
-
-// Fills fp[i] with the fixed-point probability of every token under (a) the shaped row `prow` or
-// (b) the normalised residual max(p - q, 0), and finds the last support entry in rank order.
-// Returns false when the residual is empty / below the reference's 1e-12 floor.
-__device__ bool fill_masses(DrawCtx& c, const __half* prow, const RowStats& ps, const __half* qrow, const RowStats* qs,
-                            int vocab, double inv_t, bool unit_t, unsigned long long* fp) {
+// Fills fp[] (this CTA's slice) with the fixed-point probability of every token under (a) the shaped row prow
+// or (b) the normalised residual max(p - q, 0), and finds the last support entry in rank order (smallest exp,
+// then largest index).  Returns false when the residual is empty or below the reference's 1e-12 floor.
+__device__ bool cluster_fill_masses(cg::cluster_group& cluster, DrawShared& c, unsigned long long* fp, const __half* prow,
+                                    const RowStats& ps, const __half* qrow, const RowStats* qs, Slice sl, double inv_t,
+                                    bool unit_t, unsigned int* last_idx) {
     const double pmax = (double)ps.max, ptop = 1.0 / ps.sum;
-    double norm = ps.total;
-    if (qrow) {
-        const double qmax = (double)qs->max, qtop = 1.0 / qs->sum;
-        double t = 0.0;
-        int any = 0;
-        for (int i = threadIdx.x; i < vocab; i += ACC_THREADS) {
-            const double pp = weight_of(exp((double)__half2float(prow[i]) - pmax), ps.sum, ptop, inv_t, unit_t) / ps.total;
-            const double qq = weight_of(exp((double)__half2float(qrow[i]) - qmax), qs->sum, qtop, inv_t, unit_t) / qs->total;
-            const double m = fmax(pp - qq, 0.0);
-            t += m;
-            any |= m > 0.0;
-        }
-        norm = block_sum_f64(t, c.red);
-        const int have = __syncthreads_or(any);
-        if (norm < 1e-12 || !have) return false;  // distribution.rs:119-121
-    }
-    if (threadIdx.x == 0) c.last_key = ~0ull, c.last_idx = 0;
-    __syncthreads();
+    double norm = 1.0;
+    double* mass = reinterpret_cast<double*>(fp);  // the same storage holds f64 masses first, fixed point after
+    double t = 0.0;
+    int any = 0;
     unsigned long long best = ~0ull;
-    for (int i = threadIdx.x; i < vocab; i += ACC_THREADS) {
-        const double e = exp((double)__half2float(prow[i]) - pmax);
+    for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
+        const double e = exp((double)__half2float(prow[sl.lo + j]) - pmax);
         double m = weight_of(e, ps.sum, ptop, inv_t, unit_t) / ps.total;
         bool in_support = true;
         if (qrow) {
-            const double qq = weight_of(exp((double)__half2float(qrow[i]) - (double)qs->max), qs->sum, 1.0 / qs->sum, inv_t,
-                                        unit_t) / qs->total;
+            const double qq =
+                weight_of(exp((double)__half2float(qrow[sl.lo + j]) - (double)qs->max), qs->sum, 1.0 / qs->sum, inv_t, unit_t) /
+                qs->total;
             m = fmax(m - qq, 0.0);
             in_support = m > 0.0;
-            m = m / norm;
+            t += m;
+            any |= in_support;
         }
-        fp[i] = (unsigned long long)__double2ull_rn(m * FP_ONE);
+        mass[j] = m;
         if (in_support) best = min(best, (unsigned long long)__double_as_longlong(e));
     }
-    atomicMin(&c.last_key, best);
-    __syncthreads();
-    const unsigned long long lk = c.last_key;
-    unsigned int li = 0;
-    for (int i = threadIdx.x; i < vocab; i += ACC_THREADS) {
-        const double e = exp((double)__half2float(prow[i]) - pmax);
-        if ((unsigned long long)__double_as_longlong(e) != lk) continue;
-        if (qrow) {
-            const double pp = weight_of(e, ps.sum, ptop, inv_t, unit_t) / ps.total;
-            const double qq = weight_of(exp((double)__half2float(qrow[i]) - (double)qs->max), qs->sum, 1.0 / qs->sum, inv_t,
-                                        unit_t) / qs->total;
-            if (!(pp - qq > 0.0)) continue;
-        }
-        li = max(li, (unsigned int)i);
+    if (qrow) {
+        norm = cluster_sum_f64(cluster, &c.xch, 0, block_sum_f64(t, c.red));
+        const int have_local = __syncthreads_or(any);
+        if (threadIdx.x == 0) c.xch.i[0] = have_local;
+        cluster.sync();
+        int have = 0;
+        for (int rr = 0; rr < CL; rr++) have |= cluster.map_shared_rank(&c.xch, rr)->i[0];
+        cluster.sync();
+        if (norm < 1e-12 || !have) return false;  // distribution.rs:119-121
     }
-    atomicMax(&c.last_idx, li);
+    // last support entry: smallest exp over the support, then the largest index holding it
+    if (threadIdx.x == 0) c.best_exp = ~0ull, c.best_idx = 0;
+    __syncthreads();
+    atomicMin(&c.best_exp, best);
+    cluster.sync();
+    unsigned long long gbest = ~0ull;
+    for (int rr = 0; rr < CL; rr++) gbest = min(gbest, cluster.map_shared_rank(&c, rr)->best_exp);
+    unsigned int li = 0;
+    for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
+        const double e = exp((double)__half2float(prow[sl.lo + j]) - pmax);
+        if ((unsigned long long)__double_as_longlong(e) == gbest && (!qrow || mass[j] > 0.0)) li = max(li, (unsigned int)(sl.lo + j));
+    }
+    atomicMax(&c.best_idx, li);
+    cluster.sync();
+    unsigned int gl = 0;
+    for (int rr = 0; rr < CL; rr++) gl = max(gl, cluster.map_shared_rank(&c, rr)->best_idx);
+    cluster.sync();
+    *last_idx = gl;
+    // f64 masses -> fixed point, in place
+    for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
+        const double m = qrow ? mass[j] / norm : mass[j];
+        fp[j] = (unsigned long long)__double2ull_rn(m * FP_ONE);
+    }
     __syncthreads();
     return true;
 }
@@ -302,24 +382,28 @@ __global__ void __launch_bounds__(ACC_THREADS)
     accept_decide_kernel(const __half* __restrict__ target, const __half* __restrict__ draft,
                          const int32_t* __restrict__ proposals, int prop_stride, const uint64_t* __restrict__ uniforms,
                          int k, int vocab, double temperature, const RowStats* __restrict__ stats,
-                         unsigned long long* __restrict__ scratch, tsb_accept_out* __restrict__ out,
-                         int32_t* __restrict__ next_tokens, int next_stride) {
-    __shared__ DrawCtx c;
+                         tsb_accept_out* __restrict__ out, int32_t* __restrict__ next_tokens, int next_stride) {
+    extern __shared__ __align__(16) uint8_t dyn[];
+    unsigned long long* fp = reinterpret_cast<unsigned long long*>(dyn);
+    __shared__ DrawShared c;
     __shared__ int s_accepted, s_draws, s_rejected, s_status;
     __shared__ double s_margin;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
     pdl_wait();
-    const int b = blockIdx.x;
+    const int b = blockIdx.x / CL;
     const int rps = 2 * k + 1;
     const RowStats* st = stats + (size_t)b * rps;
     const __half* trows = target + (size_t)b * (k + 1) * vocab;
     const __half* drows = draft + (size_t)b * k * vocab;
     const int32_t* prop = proposals + (size_t)b * prop_stride;
     const uint64_t* un = uniforms + (size_t)b * rps;
-    unsigned long long* fp = scratch + (size_t)b * vocab;
     const bool sampled = temperature != 0.0;
     const double inv_t = sampled ? 1.0 / temperature : 1.0;
     const bool unit_t = temperature == 1.0;
+    const Slice sl = my_slice(vocab, rank);
 
+    // the accept chain is a few scalar steps: every CTA runs it redundantly (same inputs, same result)
     if (threadIdx.x == 0) {
         int accepted = 0, draws = 0, rejected = 0, status = 0;
         double margin = INFINITY;
@@ -337,14 +421,14 @@ __global__ void __launch_bounds__(ACC_THREADS)
                     const double r = unit_interval(un[draws++]);
                     margin = fmin(margin, fabs(r * qx - px));
                     if (r * qx <= px) {
-                        out[b].tokens[accepted++] = x;
+                        accepted++;
                     } else {
                         rejected = 1;
                         break;
                     }
                 } else {
                     if (st[i].argmax != x) break;
-                    out[b].tokens[accepted++] = x;
+                    accepted++;
                 }
             }
         }
@@ -353,7 +437,7 @@ __global__ void __launch_bounds__(ACC_THREADS)
     __syncthreads();
     const int accepted = s_accepted;
     int token = -1;
-    unsigned long long gap_lo = ~0ull, gap_hi = ~0ull;
+    unsigned long long gap = ~0ull;
     if (s_status == 0) {
         const __half* prow = trows + (size_t)accepted * vocab;
         if (!sampled) {
@@ -362,58 +446,64 @@ __global__ void __launch_bounds__(ACC_THREADS)
             const uint64_t u = un[s_draws];
             const unsigned long long tgt = (unsigned long long)(u >> 11) << 7;  // k * 2^-53 in 2^-60 units
             bool have = false;
+            unsigned int last = 0;
             if (s_rejected)
-                have = fill_masses(c, prow, st[accepted], drows + (size_t)accepted * vocab, &st[k + 1 + accepted], vocab, inv_t,
-                                   unit_t, fp);
-            if (!have) fill_masses(c, prow, st[accepted], nullptr, nullptr, vocab, inv_t, unit_t, fp);
-            token = radix_draw(c, prow, fp, vocab, tgt, &gap_lo, &gap_hi);
-            if (token < 0) token = (int)c.last_idx, gap_lo = gap_hi = 0;
+                have = cluster_fill_masses(cluster, c, fp, prow, st[accepted], drows + (size_t)accepted * vocab,
+                                           &st[k + 1 + accepted], sl, inv_t, unit_t, &last);
+            if (!have) cluster_fill_masses(cluster, c, fp, prow, st[accepted], nullptr, nullptr, sl, inv_t, unit_t, &last);
+            token = cluster_radix_draw(cluster, c, fp, prow, sl, tgt, &gap);
+            if (token < 0) token = (int)last, gap = 0;
         }
     }
     pdl_launch_dependents();
-    if (threadIdx.x == 0) {
+    if (rank == 0 && threadIdx.x == 0) {
         tsb_accept_out& o = out[b];
         o.accepted = accepted;
         o.draws = s_draws + ((sampled && s_status == 0) ? 1 : 0);
+        for (int i = 0; i < accepted; i++) o.tokens[i] = prop[i];
         o.tokens[accepted] = token;
         for (int i = accepted + 1; i < 16; i++) o.tokens[i] = -1;
         o.status = s_status;
         o._pad = 0;
         o.margin_accept = s_margin;
-        o.margin_draw = (double)(gap_lo < gap_hi ? gap_lo : gap_hi) / FP_ONE;
+        o.margin_draw = (double)gap / FP_ONE;
         if (next_tokens) next_tokens[(size_t)b * next_stride] = token;
     }
 }
 
-// Draft-side draw: one CTA per stream, one row each.
+// Draft-side draw: one cluster per stream, one row each.
 __global__ void __launch_bounds__(ACC_THREADS)
     sample_kernel(const __half* __restrict__ logits, int64_t logits_stride, const uint64_t* __restrict__ uniforms,
                   int uni_stride, int vocab, double temperature, const RowStats* __restrict__ stats,
-                  unsigned long long* __restrict__ scratch, int32_t* __restrict__ tokens, int token_stride,
-                  double* __restrict__ margins, uint32_t* __restrict__ err) {
-    __shared__ DrawCtx c;
+                  int32_t* __restrict__ tokens, int token_stride, double* __restrict__ margins, uint32_t* __restrict__ err) {
+    extern __shared__ __align__(16) uint8_t dyn[];
+    unsigned long long* fp = reinterpret_cast<unsigned long long*>(dyn);
+    __shared__ DrawShared c;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
     pdl_wait();
-    const int b = blockIdx.x;
+    const int b = blockIdx.x / CL;
     const RowStats st = stats[b];
     const __half* row = logits + (size_t)b * logits_stride;
+    const Slice sl = my_slice(vocab, rank);
     int token;
-    unsigned long long gap_lo = ~0ull, gap_hi = ~0ull;
+    unsigned long long gap = ~0ull;
     if (st.nonfinite) {
         token = -1;
-        if (threadIdx.x == 0) atomicCAS(err, 0u, (uint32_t)TSB_DEV_NONFINITE);
+        if (rank == 0 && threadIdx.x == 0) atomicCAS(err, 0u, (uint32_t)TSB_DEV_NONFINITE);
     } else if (temperature == 0.0) {
         token = st.argmax;
     } else {
-        unsigned long long* fp = scratch + (size_t)b * vocab;
-        fill_masses(c, row, st, nullptr, nullptr, vocab, 1.0 / temperature, temperature == 1.0, fp);
+        unsigned int last = 0;
+        cluster_fill_masses(cluster, c, fp, row, st, nullptr, nullptr, sl, 1.0 / temperature, temperature == 1.0, &last);
         const unsigned long long tgt = (unsigned long long)(uniforms[(size_t)b * uni_stride] >> 11) << 7;
-        token = radix_draw(c, row, fp, vocab, tgt, &gap_lo, &gap_hi);
-        if (token < 0) token = (int)c.last_idx, gap_lo = gap_hi = 0;
+        token = cluster_radix_draw(cluster, c, fp, row, sl, tgt, &gap);
+        if (token < 0) token = (int)last, gap = 0;
     }
     pdl_launch_dependents();
-    if (threadIdx.x == 0) {
+    if (rank == 0 && threadIdx.x == 0) {
         tokens[(size_t)b * token_stride] = token;
-        if (margins) margins[b] = (double)(gap_lo < gap_hi ? gap_lo : gap_hi) / FP_ONE;
+        if (margins) margins[b] = (double)gap / FP_ONE;
     }
 }
 
@@ -433,40 +523,64 @@ int32_t check_shaping(tsb_ctx* ctx, const tsb_shaping* sh) {
     return TSB_OK;
 }
 
+size_t slice_smem(int vocab) { return (size_t)(((vocab + CL - 1) / CL + 1) & ~1) * sizeof(unsigned long long); }
+
+template <typename K>
+cudaError_t ensure_smem(K kernel, size_t bytes) {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
 }  // namespace
 
 size_t accept_scratch_bytes(int batch, int k, int vocab) {
-    const size_t stats = ((size_t)batch * (2 * k + 1) * sizeof(RowStats) + 255) & ~(size_t)255;
-    return stats + (size_t)batch * vocab * sizeof(unsigned long long);
+    (void)vocab;
+    return ((size_t)batch * (2 * k + 1) * sizeof(RowStats) + 255) & ~(size_t)255;
 }
+
+int accept_max_vocab() { return CL * SLICE_MAX; }
 
 cudaError_t launch_accept(tsb_ctx* ctx, cudaStream_t st, const __half* target, const __half* draft, const int32_t* proposals,
                           int prop_stride, const uint64_t* uniforms, int batch, int k, int vocab, double temperature,
                           tsb_accept_out* out_dev, int32_t* next_tokens, int next_stride, void* scratch) {
     RowStats* stats = reinterpret_cast<RowStats*>(scratch);
-    const size_t stats_bytes = ((size_t)batch * (2 * k + 1) * sizeof(RowStats) + 255) & ~(size_t)255;
-    unsigned long long* fp = reinterpret_cast<unsigned long long*>((char*)scratch + stats_bytes);
     const int rps = 2 * k + 1;
-    cudaError_t e = tsb_launch(ctx, accept_stats_kernel, dim3((unsigned)(batch * rps)), dim3(ACC_THREADS), 0, st, true, target,
-                               draft, k, vocab, temperature, stats, rps, (int64_t)0);
+    const size_t smem = slice_smem(vocab);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = ensure_smem(accept_stats_kernel, (size_t)SLICE_MAX * 8);
+        if (e == cudaSuccess) e = ensure_smem(accept_decide_kernel, (size_t)SLICE_MAX * 8);
+        if (e == cudaSuccess) e = ensure_smem(sample_kernel, (size_t)SLICE_MAX * 8);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    cudaError_t e = tsb_launch_cluster(ctx, accept_stats_kernel, dim3((unsigned)(batch * rps * CL)), dim3(ACC_THREADS), smem, st,
+                                       true, (unsigned)CL, target, draft, k, vocab, temperature, stats, rps, (int64_t)0);
     if (e != cudaSuccess) return e;
-    return tsb_launch(ctx, accept_decide_kernel, dim3((unsigned)batch), dim3(ACC_THREADS), 0, st, true, target, draft,
-                      proposals, prop_stride, uniforms, k, vocab, temperature, (const RowStats*)stats, fp, out_dev,
-                      next_tokens, next_stride);
+    return tsb_launch_cluster(ctx, accept_decide_kernel, dim3((unsigned)(batch * CL)), dim3(ACC_THREADS), smem, st, true,
+                              (unsigned)CL, target, draft, proposals, prop_stride, uniforms, k, vocab, temperature,
+                              (const RowStats*)stats, out_dev, next_tokens, next_stride);
 }
 
 cudaError_t launch_sample(tsb_ctx* ctx, cudaStream_t st, const __half* logits, int64_t logits_stride,
                           const uint64_t* uniforms, int uni_stride, int batch, int vocab, double temperature,
                           int32_t* tokens_dev, int token_stride, double* margins_dev, void* scratch) {
     RowStats* stats = reinterpret_cast<RowStats*>(scratch);
-    const size_t stats_bytes = ((size_t)batch * sizeof(RowStats) + 255) & ~(size_t)255;
-    unsigned long long* fp = reinterpret_cast<unsigned long long*>((char*)scratch + stats_bytes);
-    cudaError_t e = tsb_launch(ctx, accept_stats_kernel, dim3((unsigned)batch), dim3(ACC_THREADS), 0, st, true, logits,
-                               (const __half*)nullptr, 0, vocab, temperature, stats, 1, logits_stride);
+    const size_t smem = slice_smem(vocab);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = ensure_smem(accept_stats_kernel, (size_t)SLICE_MAX * 8);
+        if (e == cudaSuccess) e = ensure_smem(accept_decide_kernel, (size_t)SLICE_MAX * 8);
+        if (e == cudaSuccess) e = ensure_smem(sample_kernel, (size_t)SLICE_MAX * 8);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    cudaError_t e = tsb_launch_cluster(ctx, accept_stats_kernel, dim3((unsigned)(batch * CL)), dim3(ACC_THREADS), smem, st, true,
+                                       (unsigned)CL, logits, (const __half*)nullptr, 0, vocab, temperature, stats, 1,
+                                       logits_stride);
     if (e != cudaSuccess) return e;
-    return tsb_launch(ctx, sample_kernel, dim3((unsigned)batch), dim3(ACC_THREADS), 0, st, true, logits, logits_stride,
-                      uniforms, uni_stride, vocab, temperature, (const RowStats*)stats, fp, tokens_dev, token_stride,
-                      margins_dev, ctx->dev_error);
+    return tsb_launch_cluster(ctx, sample_kernel, dim3((unsigned)(batch * CL)), dim3(ACC_THREADS), smem, st, true, (unsigned)CL,
+                              logits, logits_stride, uniforms, uni_stride, vocab, temperature, (const RowStats*)stats,
+                              tokens_dev, token_stride, margins_dev, ctx->dev_error);
 }
 
 int32_t accept_check_shaping(tsb_ctx* ctx, const tsb_shaping* sh) { return check_shaping(ctx, sh); }
@@ -486,6 +600,8 @@ int32_t tsb_accept(tsb_ctx* ctx, tsb_stream s, const void* target_logits_f16, co
     if (rc) return rc;
     TSB_REQUIRE(ctx, target_logits_f16 && out_dev && scratch, "null buffer");
     TSB_REQUIRE(ctx, batch > 0 && vocab > 0, "batch and vocab must be positive");
+    if (vocab > accept_max_vocab())
+        return tsb_fail(ctx, TSB_ERR_UNSUPPORTED, "vocabulary %d exceeds the %d entries one cluster holds on chip", vocab, accept_max_vocab());
     TSB_REQUIRE(ctx, k >= 0 && k <= 15, "k must be 0..15 (the reference allows blocks 1..=15)");
     TSB_REQUIRE(ctx, k == 0 || (draft_logits_f16 && proposals), "draft logits and proposals are required when k > 0");
     TSB_REQUIRE(ctx, shaping->temperature == 0.0 || uniforms, "uniforms are required at a positive temperature");
@@ -504,6 +620,8 @@ int32_t tsb_sample(tsb_ctx* ctx, tsb_stream s, const void* logits_f16, const uin
     if (rc) return rc;
     TSB_REQUIRE(ctx, logits_f16 && tokens_dev && scratch, "null buffer");
     TSB_REQUIRE(ctx, batch > 0 && vocab > 0, "batch and vocab must be positive");
+    if (vocab > accept_max_vocab())
+        return tsb_fail(ctx, TSB_ERR_UNSUPPORTED, "vocabulary %d exceeds the %d entries one cluster holds on chip", vocab, accept_max_vocab());
     TSB_REQUIRE(ctx, shaping->temperature == 0.0 || uniforms, "uniforms are required at a positive temperature");
     TSB_REQUIRE(ctx, scratch_bytes >= tsb_accept_scratch_bytes(batch, 0, vocab), "scratch too small");
     DeviceGuard g(ctx);

@@ -3,6 +3,7 @@
 #include "common.cuh"
 
 size_t accept_scratch_bytes(int batch, int k, int vocab);
+int accept_max_vocab();  // largest vocabulary the on-chip draw holds
 int32_t accept_check_shaping(tsb_ctx* ctx, const tsb_shaping* sh);
 // proposals[b * prop_stride + i]; when next_tokens != null the corrected / bonus token of stream b is also
 // written to next_tokens[b * next_stride].

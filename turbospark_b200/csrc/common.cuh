@@ -77,24 +77,37 @@ struct DeviceGuard {
 // launched this way must execute griddepcontrol.wait before touching anything a
 // predecessor wrote.
 template <typename... KArgs, typename... Args>
-inline cudaError_t tsb_launch(tsb_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                              cudaStream_t stream, bool pdl, Args... args) {
+inline cudaError_t tsb_launch_cluster(tsb_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                      cudaStream_t stream, bool pdl, unsigned cluster_x, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     unsigned n = 0;
     if (pdl && ctx->pdl) {
         attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[n].val.programmaticStreamSerializationAllowed = 1;
         n++;
     }
+    if (cluster_x > 1) {  // thread-block cluster: the CTAs of one cluster share distributed shared memory
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster_x;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        n++;
+    }
     cfg.attrs = attr;
     cfg.numAttrs = n;
     ctx->launches++;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t tsb_launch(tsb_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, bool pdl, Args... args) {
+    return tsb_launch_cluster(ctx, kernel, grid, block, smem, stream, pdl, 1u, args...);
 }
 
 // ---------------------------------------------------------------- device side

@@ -330,12 +330,14 @@ static int32_t runtime_init(tsb_session* s, ModelRt& rt, const tsb_model* model,
 static cudaError_t forward_device(tsb_session* s, ModelRt& rt, const int32_t* tokens_dev, int token_stride,
                                   const tsb_row_desc* rows_dev, int rows, int rows_per_seq, int max_len, __half* logits,
                                   int64_t logits_stride) {
+    if (s->replay) return cudaSuccess;  // the captured graph already holds this work
     tsb_ctx* ctx = s->ctx;
     cudaStream_t st = s->stream;
     const tsb_model* m = rt.model;
     const tsb_model_config& c = m->cfg;
     const int64_t qkv_dim = (int64_t)(c.n_q_heads + 2 * c.n_kv_heads) * c.head_dim;
     const float scale = 1.0f / sqrtf((float)c.head_dim);
+    max_len = (max_len + 511) / 512 * 512;  // the split plan changes only every 512 positions (graph reuse)
     cudaError_t e;
 #define FW(x)                         \
     do {                              \
@@ -379,6 +381,7 @@ static int32_t stage_rows(tsb_session* s, ModelRt& rt, const int32_t* streams, i
     TSB_REQUIRE(ctx, rows <= s->n_streams * s->max_rows, "%d rows exceed the session's %d", rows, s->n_streams * s->max_rows);
     TSB_REQUIRE(ctx, rows_per_seq <= 128, "at most 128 in-flight rows per stream");
     if (s->stage_used + rows > s->stage_cap) {
+        if (s->replay) return tsb_fail(ctx, TSB_ERR_STATE, "staging ring overflow inside a captured round");
         // the ring is reused only after the work that read it has finished
         TSB_CUDA(ctx, cudaStreamSynchronize(s->stream));
         s->stage_used = 0;
@@ -423,8 +426,10 @@ static int32_t stage_rows(tsb_session* s, ModelRt& rt, const int32_t* streams, i
     }
     tsb_row_desc* dd = s->stage_rows_dev + s->stage_used;
     int32_t* dt = s->stage_tok_dev + s->stage_used;
-    TSB_CUDA(ctx, cudaMemcpyAsync(dd, hd, rows * sizeof(tsb_row_desc), cudaMemcpyHostToDevice, s->stream));
-    if (tokens_host) TSB_CUDA(ctx, cudaMemcpyAsync(dt, ht, rows * sizeof(int32_t), cudaMemcpyHostToDevice, s->stream));
+    if (!s->replay) {
+        TSB_CUDA(ctx, cudaMemcpyAsync(dd, hd, rows * sizeof(tsb_row_desc), cudaMemcpyHostToDevice, s->stream));
+        if (tokens_host) TSB_CUDA(ctx, cudaMemcpyAsync(dt, ht, rows * sizeof(int32_t), cudaMemcpyHostToDevice, s->stream));
+    }
     s->stage_used += rows;
     *rows_dev = dd;
     if (tokens_dev) *tokens_dev = dt;
@@ -467,6 +472,8 @@ int32_t tsb_session_create(tsb_ctx* ctx, const tsb_model* target, const tsb_mode
         if ((rc = model_complete(draft))) return rc;
         TSB_REQUIRE(ctx, draft->cfg.vocab == target->cfg.vocab, "the drafter must share the target's vocabulary");
     }
+    if (target->cfg.vocab > accept_max_vocab())
+        return tsb_fail(ctx, TSB_ERR_UNSUPPORTED, "vocabulary %d exceeds the device sampler's %d", target->cfg.vocab, accept_max_vocab());
     DeviceGuard g(ctx);
     tsb_session* s = new (std::nothrow) tsb_session();
     if (!s) return TSB_ERR_OOM;
@@ -481,6 +488,10 @@ int32_t tsb_session_create(tsb_ctx* ctx, const tsb_model* target, const tsb_mode
     if ((rc = runtime_init(s, s->target, target, n_streams, max_rows, page_tokens))) return fail(rc);
     if (draft && (rc = runtime_init(s, s->draft, draft, n_streams, max_rows, page_tokens))) return fail(rc);
     s->has_draft = draft != nullptr;
+    {
+        const char* env = getenv("TSB_GRAPH");
+        if (env && env[0] == '0') s->use_graph = false;
+    }
     const int R = n_streams * max_rows, V = target->cfg.vocab;
     auto A = [&](size_t bytes, void** p) { return dev_alloc(ctx, s->owned, bytes, p); };
     if ((rc = A((size_t)R * V * 2, (void**)&s->logits_target))) return fail(rc);
@@ -509,6 +520,7 @@ void tsb_session_destroy(tsb_session* s) {
     if (!s) return;
     DeviceGuard g(s->ctx);
     cudaDeviceSynchronize();
+    if (s->graph) cudaGraphExecDestroy(s->graph);
     for (void* p : s->owned) tsb_free(s->ctx, p);
     if (s->target.kv) tsb_kv_destroy(s->target.kv);
     if (s->draft.kv) tsb_kv_destroy(s->draft.kv);
@@ -716,38 +728,108 @@ int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_acti
     }
     uint64_t* un_draft = s->uniforms_dev;
     uint64_t* un_acc = s->uniforms_dev + (size_t)S * UD;
-    TSB_CUDA(ctx, cudaMemcpyAsync(s->uniforms_dev, un, (size_t)S * (UD + UA) * sizeof(uint64_t), cudaMemcpyHostToDevice, st));
-    TSB_CUDA(ctx, cudaMemcpyAsync(s->feed_dev, s->feed_host, (size_t)S * (K + 1) * sizeof(int32_t), cudaMemcpyHostToDevice, st));
-
-    TSB_CUDA(ctx, cudaEventRecord(s->ev[0], st));
-    // ---- draft: K steps with a head + one row-only step (crates/runtime/src/speculative.rs:607-659)
-    for (int d = 0; d <= K; d++) {
-        const tsb_row_desc* rd;
-        int max_len;
-        if ((rc = stage_rows(s, s->draft, streams, S, 1, nullptr, nullptr, &rd, nullptr, &max_len))) return rc;
-        const bool head = d < K;
-        TSB_CUDA(ctx, forward_device(s, s->draft, s->feed_dev + d, K + 1, rd, S, 1, max_len,
-                                     head ? s->logits_draft + (size_t)d * V : nullptr, (int64_t)K * V));
-        for (int a = 0; a < S; a++) tsb_kv_set_cursor(s->draft.kv, streams[a], tsb_kv_cursor(s->draft.kv, streams[a]) + 1);
-        if (head)
-            TSB_CUDA(ctx, launch_sample(ctx, st, s->logits_draft + (size_t)d * V, (int64_t)K * V, un_draft + d, UD, S, V, T,
-                                        s->feed_dev + d + 1, K + 1, nullptr, s->accept_scratch));
-    }
-    TSB_CUDA(ctx, cudaEventRecord(s->ev[1], st));
-    // ---- verify: K+1 rows per stream in one pass
+    // pages for every row of the round are reserved up front (a reservation copies the page table synchronously,
+    // which must not happen inside a capture), and the shape key of the round is formed
+    uint64_t key = 1469598103934665603ull;
+    auto mixk = [&](uint64_t v) { key = (key ^ v) * 1099511628211ull; };
+    mixk(S), mixk(K), mixk(sampled), mixk(T == 1.0);
     {
-        const tsb_row_desc* rd;
-        int max_len;
-        if ((rc = stage_rows(s, s->target, streams, S, K + 1, nullptr, nullptr, &rd, nullptr, &max_len))) return rc;
-        TSB_CUDA(ctx, forward_device(s, s->target, s->feed_dev, 1, rd, S * (K + 1), K + 1, max_len, s->logits_target, V));
+        uint64_t tb;
+        memcpy(&tb, &T, 8);
+        mixk(tb);
     }
-    TSB_CUDA(ctx, cudaEventRecord(s->ev[2], st));
-    // ---- accept on the device; the next confirmed token also lands in feed[.][0]
-    TSB_CUDA(ctx, launch_accept(ctx, st, s->logits_target, s->logits_draft, s->feed_dev + 1, K + 1, un_acc, S, K, V, T,
-                                s->accept_out_dev, s->feed_dev, K + 1, s->accept_scratch));
-    TSB_CUDA(ctx, cudaMemcpyAsync(s->accept_out_host, s->accept_out_dev, (size_t)S * sizeof(tsb_accept_out),
-                                  cudaMemcpyDeviceToHost, st));
-    TSB_CUDA(ctx, cudaEventRecord(s->ev[3], st));
+    int64_t max_base = 0;
+    for (int a = 0; a < S; a++) {
+        const int q = streams[a];
+        mixk(q);
+        const int64_t base = tsb_kv_cursor(s->target.kv, q);
+        if (base + K + 1 > s->target.model->cfg.max_context)
+            return tsb_fail(ctx, TSB_ERR_STATE, "stream %d: round of %d rows at %lld exceeds the context window", q, K + 1, (long long)base);
+        if ((rc = tsb_kv_reserve(s->target.kv, q, base + K + 1)) || (rc = tsb_kv_reserve(s->draft.kv, q, base + K + 1))) return rc;
+        max_base = std::max(max_base, base);
+    }
+    for (int d = 0; d <= K + 1; d++) mixk((uint64_t)((max_base + d + 1 + 511) / 512));
+    s->stage_used = 0;
+
+    auto body = [&]() -> int32_t {
+        int32_t rc2;
+        if (!s->replay) {
+            TSB_CUDA(ctx, cudaMemcpyAsync(s->uniforms_dev, un, (size_t)S * (UD + UA) * sizeof(uint64_t), cudaMemcpyHostToDevice, st));
+            TSB_CUDA(ctx, cudaMemcpyAsync(s->feed_dev, s->feed_host, (size_t)S * (K + 1) * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+            if (!s->capturing) TSB_CUDA(ctx, cudaEventRecord(s->ev[0], st));
+        }
+        // ---- draft: K steps with a head + one row-only step (crates/runtime/src/speculative.rs:607-659)
+        for (int d = 0; d <= K; d++) {
+            const tsb_row_desc* rd;
+            int max_len;
+            if ((rc2 = stage_rows(s, s->draft, streams, S, 1, nullptr, nullptr, &rd, nullptr, &max_len))) return rc2;
+            const bool head = d < K;
+            TSB_CUDA(ctx, forward_device(s, s->draft, s->feed_dev + d, K + 1, rd, S, 1, max_len,
+                                         head ? s->logits_draft + (size_t)d * V : nullptr, (int64_t)K * V));
+            for (int a = 0; a < S; a++) tsb_kv_set_cursor(s->draft.kv, streams[a], tsb_kv_cursor(s->draft.kv, streams[a]) + 1);
+            if (head && !s->replay)
+                TSB_CUDA(ctx, launch_sample(ctx, st, s->logits_draft + (size_t)d * V, (int64_t)K * V, un_draft + d, UD, S, V, T,
+                                            s->feed_dev + d + 1, K + 1, nullptr, s->accept_scratch));
+        }
+        if (!s->replay && !s->capturing) TSB_CUDA(ctx, cudaEventRecord(s->ev[1], st));
+        // ---- verify: K+1 rows per stream in one pass
+        {
+            const tsb_row_desc* rd;
+            int max_len;
+            if ((rc2 = stage_rows(s, s->target, streams, S, K + 1, nullptr, nullptr, &rd, nullptr, &max_len))) return rc2;
+            TSB_CUDA(ctx, forward_device(s, s->target, s->feed_dev, 1, rd, S * (K + 1), K + 1, max_len, s->logits_target, V));
+        }
+        if (!s->replay) {
+            if (!s->capturing) TSB_CUDA(ctx, cudaEventRecord(s->ev[2], st));
+            // ---- accept on the device; the next confirmed token also lands in feed[.][0]
+            TSB_CUDA(ctx, launch_accept(ctx, st, s->logits_target, s->logits_draft, s->feed_dev + 1, K + 1, un_acc, S, K, V, T,
+                                        s->accept_out_dev, s->feed_dev, K + 1, s->accept_scratch));
+            TSB_CUDA(ctx, cudaMemcpyAsync(s->accept_out_host, s->accept_out_dev, (size_t)S * sizeof(tsb_accept_out),
+                                          cudaMemcpyDeviceToHost, st));
+            if (!s->capturing) TSB_CUDA(ctx, cudaEventRecord(s->ev[3], st));
+        }
+        return TSB_OK;
+    };
+
+    const bool want_graph = s->use_graph && s->rounds_done >= 1;
+    if (want_graph && s->graph && s->graph_key == key) {
+        s->replay = true;  // host-side staging only: descriptors land in the pinned ring at the captured offsets
+        rc = body();
+        s->replay = false;
+        if (rc) return rc;
+        TSB_CUDA(ctx, cudaEventRecord(s->ev[0], st));
+        TSB_CUDA(ctx, cudaGraphLaunch(s->graph, st));
+        TSB_CUDA(ctx, cudaEventRecord(s->ev[3], st));
+        ctx->launches += s->graph_launches;
+        s->last_round_graphed = true;
+    } else if (want_graph) {
+        if (s->graph) cudaGraphExecDestroy(s->graph), s->graph = nullptr;
+        const uint64_t l0 = ctx->launches;
+        TSB_CUDA(ctx, cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+        s->capturing = true;
+        rc = body();
+        s->capturing = false;
+        cudaGraph_t g = nullptr;
+        cudaError_t ce = cudaStreamEndCapture(st, &g);
+        if (rc) {
+            if (g) cudaGraphDestroy(g);
+            return rc;
+        }
+        TSB_CUDA(ctx, ce);
+        ce = cudaGraphInstantiate(&s->graph, g, 0);
+        cudaGraphDestroy(g);
+        TSB_CUDA(ctx, ce);
+        s->graph_key = key;
+        s->graph_launches = ctx->launches - l0;
+        TSB_CUDA(ctx, cudaEventRecord(s->ev[0], st));
+        TSB_CUDA(ctx, cudaGraphLaunch(s->graph, st));
+        TSB_CUDA(ctx, cudaEventRecord(s->ev[3], st));
+        s->last_round_graphed = true;
+    } else {
+        if ((rc = body())) return rc;
+        s->last_round_graphed = false;
+    }
+    s->rounds_done++;
     if ((rc = tsb_stream_sync(ctx, st))) return rc;
     s->stage_used = 0;
     // ---- commit: cursors to the accepted prefix (rollback_retaining + rewind_drafter)
@@ -801,6 +883,12 @@ int32_t tsb_session_round(tsb_session* s, const tsb_run_config* cfg, int32_t* ne
 
 void* tsb_session_stream(tsb_session* s) { return s ? (void*)s->stream : nullptr; }
 
+int32_t tsb_session_set_graph(tsb_session* s, int32_t enabled) {
+    if (!s) return TSB_ERR_INVALID;
+    s->use_graph = enabled != 0;
+    return TSB_OK;
+}
+
 int32_t tsb_session_time_matmuls(tsb_session* s, int32_t rows, int32_t iters, float* out_ms, int64_t* out_bytes_per_iter,
                                  int32_t* out_launches_per_iter) {
     if (!s || !out_ms) return TSB_ERR_INVALID;
@@ -844,9 +932,13 @@ int32_t tsb_session_time_matmuls(tsb_session* s, int32_t rows, int32_t iters, fl
 int32_t tsb_session_round_times(tsb_session* s, float* out4_ms) {
     if (!s || !out4_ms) return TSB_ERR_INVALID;
     DeviceGuard g(s->ctx);
-    for (int i = 0; i < 3; i++)
-        if (cudaEventElapsedTime(&out4_ms[i], s->ev[i], s->ev[i + 1]) != cudaSuccess) out4_ms[i] = -1.f;
-    out4_ms[3] = 0.f;
+    // a graphed round has no event records inside it: only the total (index 3) is known
+    for (int i = 0; i < 3; i++) {
+        out4_ms[i] = -1.f;
+        if (!s->last_round_graphed && cudaEventElapsedTime(&out4_ms[i], s->ev[i], s->ev[i + 1]) != cudaSuccess) out4_ms[i] = -1.f;
+    }
+    if (cudaEventElapsedTime(&out4_ms[3], s->ev[0], s->ev[3]) != cudaSuccess) out4_ms[3] = -1.f;
+    cudaGetLastError();
     return TSB_OK;
 }
 

@@ -70,6 +70,11 @@ struct tsb_session {
     int32_t* feed_host = nullptr;
     void* logits_host = nullptr;
     std::vector<void*> owned;
+    // CUDA graph of one round's device work (copies, kernels, event records); rebuilt when the shape key changes
+    bool use_graph = true, replay = false, capturing = false, last_round_graphed = false;
+    cudaGraphExec_t graph = nullptr;
+    uint64_t graph_key = 0, graph_launches = 0;
+    int rounds_done = 0;
 };
 
 // One speculative round for the listed streams with k proposals each (model.cu).

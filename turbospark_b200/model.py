@@ -177,6 +177,9 @@ class Session:
                                                accepted.ctypes.data_as(C.c_void_p), draw_steps.ctypes.data_as(C.c_void_p)))
         return accepted
 
+    def set_graph(self, enabled):
+        self.ctx.check(lib().tsb_session_set_graph(self.h, C.c_int32(int(enabled))))
+
     def round_times(self):
         t = (C.c_float * 4)()
         self.ctx.check(lib().tsb_session_round_times(self.h, t))
