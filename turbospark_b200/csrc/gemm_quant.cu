@@ -78,7 +78,7 @@ __device__ __forceinline__ uint32_t lds_u32_unaligned(const uint8_t* p) {
 template <int NT>
 struct LaneAct {
     const uint4* xp[NT];  // token tile nt of the fragment-major operand, advanced by the lane index
-    const uint2* xs[NT];  // sub-block sums of tile nt, advanced by the lane index
+    const uint4* xs[NT];  // 16-column sums of tile nt, advanced by the lane index
     int nblk;
 };
 
@@ -111,7 +111,7 @@ __device__ __forceinline__ void q4k_block(const uint4* __restrict__ rowA, const 
                                           const LaneAct<NT>& la, int blk, int tig, float (&acc)[NT][4]) {
     // all activation loads of the block first: one scoreboard wait, hidden behind the scale decode
     uint4 xl[2][2][NT], xh[2][2][NT];
-    uint32_t xsh[NT], xsl[NT];
+    uint4 xsum[NT];
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
         const uint4* p = la.xp[nt] + blk * 256;  // eight 32-lane chunks per block
@@ -122,9 +122,7 @@ __device__ __forceinline__ void q4k_block(const uint4* __restrict__ rowA, const 
                 xl[r][jj][nt] = __ldg(p + ((r * 2 + jj) * 2) * 32);
                 xh[r][jj][nt] = __ldg(p + ((r * 2 + jj) * 2 + 1) * 32);  // sub-block 2g+1
             }
-        const uint2 sums = __ldg(la.xs[nt] + blk * 32);
-        xsh[nt] = sums.x;
-        xsl[nt] = sums.y;
+        xsum[nt] = __ldg(la.xs[nt] + blk * 32);
     }
     const uint4 hA = rowA[0];
     const uint4 hB = rowB[0];
@@ -142,23 +140,25 @@ __device__ __forceinline__ void q4k_block(const uint4* __restrict__ rowA, const 
     // 6-bit fields as bytes: sc0..3 | sc4..7 | m0..3 | m4..7
     const uint32_t scA_lo = hA.y & 0x3F3F3F3Fu, scA_hi = (hA.w & 0x0F0F0F0Fu) | ((hA.y >> 2) & 0x30303030u);
     const uint32_t scB_lo = hB.y & 0x3F3F3F3Fu, scB_hi = (hB.w & 0x0F0F0F0Fu) | ((hB.y >> 2) & 0x30303030u);
-    const uint32_t mA = (tig < 2) ? (hA.z & 0x3F3F3F3Fu) : (((hA.w >> 4) & 0x0F0F0F0Fu) | ((hA.z >> 2) & 0x30303030u));
-    const uint32_t mB = (tig < 2) ? (hB.z & 0x3F3F3F3Fu) : (((hB.w >> 4) & 0x0F0F0F0Fu) | ((hB.z >> 2) & 0x30303030u));
+    const uint32_t mA_lo = hA.z & 0x3F3F3F3Fu, mA_hi = ((hA.w >> 4) & 0x0F0F0F0Fu) | ((hA.z >> 2) & 0x30303030u);
+    const uint32_t mB_lo = hB.z & 0x3F3F3F3Fu, mB_hi = ((hB.w >> 4) & 0x0F0F0F0Fu) | ((hB.z >> 2) & 0x30303030u);
 
     const uint32_t k1024 = 0x64006400u;
-    // --- min term: A = mins of sub-blocks (2tig, 2tig+1), B = xsum hi / lo
+    // --- min term: one m16n8k16 over the block's sixteen 16-column sums; k slots (2tig, 2tig+1) belong to
+    // sub-block tig, slots (2tig+8, 2tig+9) to sub-block tig+4, so A repeats each min twice
     {
-        const uint32_t bb = (2u * tig) & 3u;
-        const uint32_t sel = bb | (4u << 4) | ((bb + 1u) << 8) | (4u << 12);
-        uint32_t amin[2];
-        amin[0] = hsub2_u32(__byte_perm(mA, 0x64646464u, sel), k1024);
-        amin[1] = hsub2_u32(__byte_perm(mB, 0x64646464u, sel), k1024);
+        const uint32_t sel = (uint32_t)tig * 0x0101u | 0x4040u;
+        uint32_t amin[4];
+        amin[0] = hsub2_u32(__byte_perm(mA_lo, 0x64646464u, sel), k1024);
+        amin[1] = hsub2_u32(__byte_perm(mB_lo, 0x64646464u, sel), k1024);
+        amin[2] = hsub2_u32(__byte_perm(mA_hi, 0x64646464u, sel), k1024);
+        amin[3] = hsub2_u32(__byte_perm(mB_hi, 0x64646464u, sel), k1024);
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
-            const uint32_t bhi = xsh[nt], blo = xsl[nt];
+            const uint32_t bhi[2] = {xsum[nt].x, xsum[nt].y}, blo[2] = {xsum[nt].z, xsum[nt].w};
             float c[4];
-            mma_1688_first(c, amin, bhi);
-            mma_1688(c, amin, blo);
+            mma_16816_first(c, amin, bhi);
+            mma_16816(c, amin, blo);
             acc[nt][0] -= dminA * c[0];
             acc[nt][1] -= dminA * c[1];
             acc[nt][2] -= dminB * c[2];
@@ -376,22 +376,179 @@ __device__ __forceinline__ void q6k_block(const uint8_t* rA, const uint8_t* rB, 
     }
 }
 
-template <int QT, int NT, bool Y_F32>
+// ---- work decomposition ----------------------------------------------------
+// A group is one 16-row tile, or two tiles whose results meet in one epilogue:
+//   EPI_SILU        group p: gate rows [16p, 16p+16) and up rows [rows/2 + 16p, ...)
+//   EPI_ROPE_STORE  q and k heads: rows [16t, 16t+16) and [16t + hd/2, ...) of a head (the NeoX pair halves);
+//                   v heads: single tiles
+struct Group {
+    int tile0, tile1, n;
+};
+template <int EPI>
+__device__ __forceinline__ int num_groups(int n_tiles, const EpiArgs& e) {
+    if (EPI == EPI_SILU) return n_tiles / 2;
+    if (EPI == EPI_ROPE_STORE) {
+        const int tph = e.head_dim / 16;  // tiles per head
+        return (e.n_q_heads + e.n_kv_heads) * (tph / 2) + e.n_kv_heads * tph;
+    }
+    return n_tiles;
+}
+template <int EPI>
+__device__ __forceinline__ Group group_of(int g, int n_tiles, const EpiArgs& e) {
+    Group r;
+    if (EPI == EPI_SILU) {
+        r.tile0 = g, r.tile1 = n_tiles / 2 + g, r.n = 2;
+    } else if (EPI == EPI_ROPE_STORE) {
+        const int tph = e.head_dim / 16, pph = tph / 2;
+        const int paired = (e.n_q_heads + e.n_kv_heads) * pph;
+        if (g < paired) {
+            const int head = g / pph, t = g % pph;
+            r.tile0 = head * tph + t, r.tile1 = r.tile0 + pph, r.n = 2;
+        } else {
+            r.tile0 = (e.n_q_heads + e.n_kv_heads) * tph + (g - paired), r.tile1 = 0, r.n = 1;
+        }
+    } else {
+        r.tile0 = g, r.tile1 = 0, r.n = 1;
+    }
+    return r;
+}
+
+// ---- epilogues: 256 consumer threads, results of the group's tiles in tile_out[which][token][row] ---------
+template <int EPI, int NT>
+__device__ __forceinline__ void run_epilogue(const EpiArgs& e, const Group& gr, const float* tile_out, const float* inv_rms,
+                                             int64_t rows, int tokens, int tok0, uint32_t* err) {
+    constexpr int NTOK = NT * 8;
+    const int tid = threadIdx.x;
+    if constexpr (EPI == EPI_PLAIN || EPI == EPI_SCALE) {
+        const int64_t row0 = (int64_t)gr.tile0 * TILE_ROWS;
+        for (int idx = tid; idx < NTOK * 16; idx += CONSUMER_WARPS * 32) {
+            const int tok = idx >> 4, row = idx & 15;
+            if (tok >= tokens || row0 + row >= rows) continue;
+            float v = tile_out[tok * 16 + row];
+            if (EPI == EPI_SCALE) v *= inv_rms[tok];
+            const size_t o = (size_t)(tok0 + tok) * e.y_stride + row0 + row;
+            if (e.y_f32)
+                reinterpret_cast<float*>(e.y)[o] = v;
+            else
+                reinterpret_cast<__half*>(e.y)[o] = __float2half_rn(v);
+        }
+    } else if constexpr (EPI == EPI_RESID_NORM) {
+        // thread = (token, eight columns); the two threads of a token are neighbours
+        const int tok = tid >> 1, part = tid & 1;
+        const bool active = tok < tokens;
+        const int col0 = gr.tile0 * TILE_ROWS + part * 8;
+        float ss = 0.f, sx = 0.f;
+        if (active) {
+            __half* hp = e.h + (size_t)(tok0 + tok) * rows + col0;
+            uint4 hv = *reinterpret_cast<const uint4*>(hp);
+            const uint4 gv = *reinterpret_cast<const uint4*>(e.g + col0);
+            __half* hh = reinterpret_cast<__half*>(&hv);
+            const uint16_t* gg = reinterpret_cast<const uint16_t*>(&gv);
+            __half xg[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                // the matmul output is rounded to f16, then added to the residual stream in fp32 and rounded again
+                // (crates/gpu/src/shaders/dequant_q4_k.metal:112-130, utility.metal:199-208)
+                const float y = __half2float(__float2half_rn(tile_out[tok * 16 + part * 8 + i]));
+                hh[i] = __float2half_rn(__half2float(hh[i]) + y);
+                const float hn = __half2float(hh[i]);
+                ss = fmaf(hn, hn, ss);
+                xg[i] = __float2half_rn(hn * bf16_bits_to_float(gg[i]));
+                sx += __half2float(xg[i]);
+            }
+            *reinterpret_cast<uint4*>(hp) = hv;
+            e.out.xp[act_xp_index(tok0 + tok, col0, (int)(rows >> 8))] = act_pack8(xg);
+        }
+        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+        sx += __shfl_xor_sync(0xffffffffu, sx, 1);
+        if (active && part == 0) {
+            act_store_sum16(e.out.xs, tok0 + tok, gr.tile0 * TILE_ROWS, (int)(rows >> 8), sx);
+            e.ss_out[(size_t)(tok0 + tok) * (rows / 16) + gr.tile0] = ss;
+        }
+    } else if constexpr (EPI == EPI_SILU) {
+        const int tok = tid >> 1, part = tid & 1;
+        const bool active = tok < tokens;
+        const int ffn = (int)(rows / 2);
+        const int col0 = gr.tile0 * TILE_ROWS + part * 8;
+        float sx = 0.f;
+        if (active) {
+            const float inv = inv_rms[tok];
+            __half a[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float g = __half2float(__float2half_rn(inv * tile_out[tok * 16 + part * 8 + i]));
+                const float u = __half2float(__float2half_rn(inv * tile_out[NTOK * 16 + tok * 16 + part * 8 + i]));
+                // utility.metal:41-52: (g / (1 + exp(-g))) * u in f32
+                const float ex = (float)exp((double)(-g));
+                a[i] = __float2half_rn(__fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, ex)), u));
+                sx += __half2float(a[i]);
+            }
+            e.out.xp[act_xp_index(tok0 + tok, col0, ffn >> 8)] = act_pack8(a);
+        }
+        sx += __shfl_xor_sync(0xffffffffu, sx, 1);
+        if (active && part == 0) act_store_sum16(e.out.xs, tok0 + tok, gr.tile0 * TILE_ROWS, ffn >> 8, sx);
+    } else if constexpr (EPI == EPI_ROPE_STORE) {
+        const int hd = e.head_dim, tph = hd / 16;
+        const int head = gr.tile0 / tph, t_in = gr.tile0 % tph;
+        for (int idx = tid; idx < NTOK * 16; idx += CONSUMER_WARPS * 32) {
+            const int tok = idx >> 4, r = idx & 15;
+            if (tok >= tokens) continue;
+            const float inv = inv_rms[tok];
+            const tsb_row_desc rd = e.row_desc[tok0 + tok];
+            if (gr.n == 2) {
+                // rows i and i + hd/2 of one head: NeoX pair (crates/compute/src/rope.rs:208-255)
+                const int i = t_in * 16 + r;
+                const float x0 = __half2float(__float2half_rn(inv * tile_out[tok * 16 + r]));
+                const float x1 = __half2float(__float2half_rn(inv * tile_out[NTOK * 16 + tok * 16 + r]));
+                const float c = e.cs[(size_t)(tok0 + tok) * hd + i], sn = e.cs[(size_t)(tok0 + tok) * hd + hd / 2 + i];
+                const __half o0 = __float2half_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn)));
+                const __half o1 = __float2half_rn(__fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c)));
+                __half* dst;
+                if (head < e.n_q_heads) {
+                    dst = e.q_out + (size_t)(tok0 + tok) * e.n_q_heads * hd + (size_t)head * hd;
+                } else {
+                    dst = kv_row(e.kv, e.layer, 0, rd.seq, rd.base + rd.slot);
+                    if (!dst) {
+                        atomicCAS(err, 0u, (uint32_t)TSB_DEV_BAD_INDEX);
+                        continue;
+                    }
+                    dst += (size_t)(head - e.n_q_heads) * hd;
+                }
+                dst[i] = o0;
+                dst[hd / 2 + i] = o1;
+            } else {
+                const int vh = head - e.n_q_heads - e.n_kv_heads;
+                __half* dst = kv_row(e.kv, e.layer, 1, rd.seq, rd.base + rd.slot);
+                if (!dst) {
+                    atomicCAS(err, 0u, (uint32_t)TSB_DEV_BAD_INDEX);
+                    continue;
+                }
+                dst[(size_t)vh * hd + t_in * 16 + r] = __float2half_rn(inv * tile_out[tok * 16 + r]);
+            }
+        }
+    }
+}
+
+template <int QT, int NT, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
     gemm_quant_kernel(const uint8_t* __restrict__ W, int64_t rows, int units /*256-col units per row*/,
-                      ActOperand act, int cols, void* __restrict__ y, int64_t y_stride, int tokens,
-                      uint32_t* __restrict__ err, int probe) {
+                      ActOperand act, int tokens, int tok0, EpiArgs epi, uint32_t* __restrict__ err) {
     constexpr int UB = Fmt<QT>::UNIT_BYTES;
     constexpr int ROW_STRIDE = row_stride_for(UB);
     constexpr int STAGE_BYTES = TILE_ROWS * ROW_STRIDE;
+    constexpr int NTOK = NT * 8;
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + NUM_STAGES;
-    float* red = reinterpret_cast<float*>(smem + 128);
-    uint8_t* stages = smem + 128 + CONSUMER_WARPS * NT * 4 * 32 * sizeof(float);
+    float* inv_rms = reinterpret_cast<float*>(smem + 64);                                  // [NTOK] (<= 64 floats)
+    float* red = reinterpret_cast<float*>(smem + 64 + 256);                                // [8 warps][NT][4][32]
+    float* tile_out = red + CONSUMER_WARPS * NT * 4 * 32;                                  // [2][NTOK][16]
+    uint8_t* stages = reinterpret_cast<uint8_t*>(tile_out + 2 * NTOK * 16);
+    constexpr bool NEEDS_INV = EPI == EPI_SCALE || EPI == EPI_SILU || EPI == EPI_ROPE_STORE;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = (int)((rows + TILE_ROWS - 1) / TILE_ROWS);
+    const int n_groups = num_groups<EPI>(n_tiles, epi);
     const int iters = (units + STAGE_UNITS - 1) / STAGE_UNITS;  // stages per row tile
     const int64_t row_bytes = (int64_t)units * UB;
 
@@ -404,39 +561,67 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
     }
     __syncthreads();
 
-    // The CTA is persistent: it walks row tiles blockIdx.x, +gridDim.x, ... and the
-    // stage ring runs on across tile boundaries, so weight bytes stay in flight
-    // while the consumers reduce and store a finished tile.
+    // The CTA is persistent: it walks groups blockIdx.x, +gridDim.x, ... and the stage ring runs on across
+    // tile boundaries, so weight bytes stay in flight while the consumers reduce and store a finished tile.
     if (warp == CONSUMER_WARPS) {
-        // ---- producer: one bulk copy per row per stage; sources are rounded
-        // down to 16 bytes (formats whose rows are not 16-byte multiples) and
-        // the consumer skips the same slack.
+        // ---- producer: one bulk copy per row per stage; sources are rounded down to 16 bytes (formats whose
+        // rows are not 16-byte multiples) and the consumer skips the same slack.
         uint32_t n = 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-            const int64_t row0 = (int64_t)tile * TILE_ROWS;
-            const int nrows = (int)min((int64_t)TILE_ROWS, rows - row0);
-            for (int it = 0; it < iters; it++, n++) {
-                const uint32_t s = n % NUM_STAGES;
-                if (n >= NUM_STAGES) {
-                    if (!mbar_wait(&empty[s], ((n / NUM_STAGES) - 1) & 1, err)) return;
-                }
-                const int nun = min(STAGE_UNITS, units - it * STAGE_UNITS);
-                uint32_t bytes = 0;
-                const uint8_t* src = nullptr;
-                if (lane < nrows) {
-                    const uint8_t* p = W + (row0 + lane) * row_bytes + (int64_t)it * STAGE_UNITS * UB;
-                    const uint32_t slack = (uint32_t)(reinterpret_cast<uintptr_t>(p) & 15u);
-                    src = p - slack;
-                    bytes = (slack + (uint32_t)nun * UB + 15u) & ~15u;
-                }
-                uint32_t total = bytes;
+        bool inv_done = !NEEDS_INV;
+        for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
+            const Group gr = group_of<EPI>(g, n_tiles, epi);
+            for (int ti = 0; ti < gr.n; ti++) {
+                const int64_t row0 = (int64_t)(ti ? gr.tile1 : gr.tile0) * TILE_ROWS;
+                const int nrows = (int)min((int64_t)TILE_ROWS, rows - row0);
+                for (int it = 0; it < iters; it++, n++) {
+                    const uint32_t s = n % NUM_STAGES;
+                    if (n >= NUM_STAGES) {
+                        if (!inv_done) {
+                            // the ring is primed: before blocking on it, turn the predecessor's partial sums of
+                            // x^2 into 1/rms per token for the epilogue (the consumers pick it up at barrier 2)
+                            pdl_wait();
+                            for (int t = 0; t < tokens; t++) {
+                                float sacc = 0.f;
+                                for (int i = lane; i < epi.ss_parts; i += 32) sacc += epi.ss_in[(size_t)(tok0 + t) * epi.ss_parts + i];
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
-                if (probe == 2) { if (lane == 0) mbar_arrive(&full[s]); continue; }
-                if (lane == 0) mbar_expect_tx(&full[s], total);
-                __syncwarp();
-                if (lane < nrows) bulk_g2s(stages + s * STAGE_BYTES + lane * ROW_STRIDE, src, bytes, &full[s]);
+                                for (int o = 16; o > 0; o >>= 1) sacc += __shfl_xor_sync(0xffffffffu, sacc, o);
+                                if (lane == 0) inv_rms[t] = 1.0f / sqrtf(sacc / (float)epi.d_in + epi.eps);
+                            }
+                            __syncwarp();
+                            asm volatile("bar.arrive 2, %0;" ::"n"(GEMM_THREADS) : "memory");
+                            inv_done = true;
+                        }
+                        if (!mbar_wait(&empty[s], ((n / NUM_STAGES) - 1) & 1, err)) return;
+                    }
+                    const int nun = min(STAGE_UNITS, units - it * STAGE_UNITS);
+                    uint32_t bytes = 0;
+                    const uint8_t* src = nullptr;
+                    if (lane < nrows) {
+                        const uint8_t* p = W + (row0 + lane) * row_bytes + (int64_t)it * STAGE_UNITS * UB;
+                        const uint32_t slack = (uint32_t)(reinterpret_cast<uintptr_t>(p) & 15u);
+                        src = p - slack;
+                        bytes = (slack + (uint32_t)nun * UB + 15u) & ~15u;
+                    }
+                    uint32_t total = bytes;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+                    if (lane == 0) mbar_expect_tx(&full[s], total);
+                    __syncwarp();
+                    if (lane < nrows) bulk_g2s(stages + s * STAGE_BYTES + lane * ROW_STRIDE, src, bytes, &full[s]);
+                }
             }
+        }
+        if (!inv_done) {
+            pdl_wait();
+            for (int t = 0; t < tokens; t++) {
+                float sacc = 0.f;
+                for (int i = lane; i < epi.ss_parts; i += 32) sacc += epi.ss_in[(size_t)(tok0 + t) * epi.ss_parts + i];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sacc += __shfl_xor_sync(0xffffffffu, sacc, o);
+                if (lane == 0) inv_rms[t] = 1.0f / sqrtf(sacc / (float)epi.d_in + epi.eps);
+            }
+            __syncwarp();
+            asm volatile("bar.arrive 2, %0;" ::"n"(GEMM_THREADS) : "memory");
         }
         pdl_launch_dependents();
         return;
@@ -445,7 +630,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
     // ---- consumers
     const int gid = lane >> 2, tig = lane & 3;
     LaneAct<NT> la;
-#pragma unroll
     la.nblk = units;
     for (int nt = 0; nt < NT; nt++) {
         la.xp[nt] = act.xp + (size_t)nt * units * 256 + lane;
@@ -453,79 +637,80 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
     }
     pdl_wait();  // activations come from the previous kernel
 
-    bool ok = true;
+    bool ok = true, have_inv = !NEEDS_INV;
     uint32_t n = 0;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        const int64_t row0 = (int64_t)tile * TILE_ROWS;
-        const int nrows = (int)min((int64_t)TILE_ROWS, rows - row0);
-        if (tile + (int)gridDim.x >= n_tiles) pdl_launch_dependents();  // last tile of this CTA
-        float acc[NT][4];
+    for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
+        const Group gr = group_of<EPI>(g, n_tiles, epi);
+        if (g + (int)gridDim.x >= n_groups) pdl_launch_dependents();  // last group of this CTA
+        for (int ti = 0; ti < gr.n; ti++) {
+            const int64_t row0 = (int64_t)(ti ? gr.tile1 : gr.tile0) * TILE_ROWS;
+            float acc[NT][4];
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++)
+            for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-            for (int i = 0; i < 4; i++) acc[nt][i] = 0.f;
-        const uint32_t slackA = (uint32_t)(reinterpret_cast<uintptr_t>(W + (row0 + gid) * row_bytes) & 15u);
-        const uint32_t slackB = (uint32_t)(reinterpret_cast<uintptr_t>(W + (row0 + gid + 8) * row_bytes) & 15u);
+                for (int i = 0; i < 4; i++) acc[nt][i] = 0.f;
+            const uint32_t slackA = (uint32_t)(reinterpret_cast<uintptr_t>(W + (row0 + gid) * row_bytes) & 15u);
+            const uint32_t slackB = (uint32_t)(reinterpret_cast<uintptr_t>(W + (row0 + gid + 8) * row_bytes) & 15u);
 
-        for (int it = 0; it < iters; it++, n++) {
-            const uint32_t s = n % NUM_STAGES;
-            if (ok) ok = mbar_wait(&full[s], (n / NUM_STAGES) & 1, err);
-            const int nun = min(STAGE_UNITS, units - it * STAGE_UNITS);
-            if (ok && warp < nun && probe != 1) {
-                // slack of this stage's source address: the row start's slack plus the stage offset
-                const uint32_t stA = (slackA + (uint32_t)((int64_t)it * STAGE_UNITS * UB)) & 15u;
-                const uint32_t stB = (slackB + (uint32_t)((int64_t)it * STAGE_UNITS * UB)) & 15u;
-                const uint8_t* rA = stages + s * STAGE_BYTES + gid * ROW_STRIDE + stA + warp * UB;
-                const uint8_t* rB = stages + s * STAGE_BYTES + (gid + 8) * ROW_STRIDE + stB + warp * UB;
-                const int unit = it * STAGE_UNITS + warp;
-                if constexpr (QT == TSB_Q4_K)
-                    q4k_block<NT>(reinterpret_cast<const uint4*>(rA), reinterpret_cast<const uint4*>(rB), la, unit, tig, acc);
-                if constexpr (QT == TSB_MXFP4) mxfp4_unit<NT>(rA, rB, act, units, unit, gid, tig, acc);
-                if constexpr (QT == TSB_Q6_K) q6k_block<NT>(rA, rB, act, units, unit, gid, tig, acc);
+            for (int it = 0; it < iters; it++, n++) {
+                const uint32_t s = n % NUM_STAGES;
+                if (ok) ok = mbar_wait(&full[s], (n / NUM_STAGES) & 1, err);
+                const int nun = min(STAGE_UNITS, units - it * STAGE_UNITS);
+                if (ok && warp < nun) {
+                    // slack of this stage's source address: the row start's slack plus the stage offset
+                    const uint32_t stA = (slackA + (uint32_t)((int64_t)it * STAGE_UNITS * UB)) & 15u;
+                    const uint32_t stB = (slackB + (uint32_t)((int64_t)it * STAGE_UNITS * UB)) & 15u;
+                    const uint8_t* rA = stages + s * STAGE_BYTES + gid * ROW_STRIDE + stA + warp * UB;
+                    const uint8_t* rB = stages + s * STAGE_BYTES + (gid + 8) * ROW_STRIDE + stB + warp * UB;
+                    const int unit = it * STAGE_UNITS + warp;
+                    if constexpr (QT == TSB_Q4_K)
+                        q4k_block<NT>(reinterpret_cast<const uint4*>(rA), reinterpret_cast<const uint4*>(rB), la, unit, tig, acc);
+                    if constexpr (QT == TSB_MXFP4) mxfp4_unit<NT>(rA, rB, act, units, unit, gid, tig, acc);
+                    if constexpr (QT == TSB_Q6_K) q6k_block<NT>(rA, rB, act, units, unit, gid, tig, acc);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
-        }
 
-        // ---- fixed-order reduction over the eight consumer warps
+            // ---- fixed-order reduction over the eight consumer warps into tile_out[ti]
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++)
+            for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-            for (int i = 0; i < 4; i++) red[((warp * NT + nt) * 4 + i) * 32 + lane] = acc[nt][i];
-        asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
-        if (ok) {
-            for (int idx = threadIdx.x; idx < NT * 128; idx += CONSUMER_WARPS * 32) {
-                const int nt = idx >> 7, rem = idx & 127;
-                const int nn = rem >> 4, row = rem & 15;
-                const int token = nt * 8 + nn;
-                if (token >= tokens || row >= nrows) continue;
+                for (int i = 0; i < 4; i++) red[((warp * NT + nt) * 4 + i) * 32 + lane] = acc[nt][i];
+            asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
+            for (int idx = threadIdx.x; idx < NTOK * 16; idx += CONSUMER_WARPS * 32) {
+                const int tok = idx >> 4, row = idx & 15;
+                const int nt = tok >> 3, nn = tok & 7;
                 const int src_lane = (row & 7) * 4 + (nn >> 1);
                 const int i = ((row >> 3) << 1) | (nn & 1);
                 float sum = 0.f;
 #pragma unroll
                 for (int w = 0; w < CONSUMER_WARPS; w++) sum += red[((w * NT + nt) * 4 + i) * 32 + src_lane];
-                const size_t o = (size_t)token * y_stride + row0 + row;
-                if constexpr (Y_F32)
-                    reinterpret_cast<float*>(y)[o] = sum;
-                else
-                    reinterpret_cast<__half*>(y)[o] = __float2half_rn(sum);
+                tile_out[ti * NTOK * 16 + idx] = sum;
             }
+            asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");  // tile_out complete, red reusable
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");  // red is reused by the next tile
+        if (!have_inv) {
+            asm volatile("bar.sync 2, %0;" ::"n"(GEMM_THREADS) : "memory");  // 1/rms per token from the producer warp
+            have_inv = true;
+        }
+        if (ok) run_epilogue<EPI, NT>(epi, gr, tile_out, inv_rms, rows, tokens, tok0, err);
+        asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");  // tile_out is reused by the next group
     }
+    if (!have_inv) asm volatile("bar.sync 2, %0;" ::"n"(GEMM_THREADS) : "memory");
 }
 
 template <int QT, int NT>
 constexpr size_t gemm_smem_bytes() {
-    return 128 + (size_t)CONSUMER_WARPS * NT * 4 * 32 * sizeof(float) +
-           (size_t)NUM_STAGES * TILE_ROWS * row_stride_for(Fmt<QT>::UNIT_BYTES);
+    return 64 + 256 + (size_t)CONSUMER_WARPS * NT * 4 * 32 * sizeof(float) + (size_t)2 * NT * 8 * 16 * sizeof(float) +
+           (size_t)NUM_STAGES * TILE_ROWS * row_stride_for(Fmt<QT>::UNIT_BYTES) + 128;
 }
 
-template <int QT, int NT, bool F32>
-cudaError_t launch_one(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t rows, int units, ActOperand act,
-                       int cols, void* y, int64_t y_stride, int tokens) {
-    auto kern = gemm_quant_kernel<QT, NT, F32>;
-    static bool configured = false;  // per instantiation; attribute is per device function
+template <int QT, int NT, int EPI>
+cudaError_t launch_one(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t rows, int units, ActOperand act, int tokens,
+                       int tok0, const EpiArgs& args) {
+    auto kern = gemm_quant_kernel<QT, NT, EPI>;
+    static bool configured = false;  // per instantiation; the attribute belongs to the device function
     constexpr size_t smem = gemm_smem_bytes<QT, NT>();
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -533,24 +718,42 @@ cudaError_t launch_one(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t 
         configured = true;
     }
     const int n_tiles = (int)((rows + TILE_ROWS - 1) / TILE_ROWS);
+    int groups = n_tiles;
+    if (EPI == EPI_SILU) groups = n_tiles / 2;
+    if (EPI == EPI_ROPE_STORE) {
+        const int tph = args.head_dim / 16;
+        groups = (args.n_q_heads + args.n_kv_heads) * (tph / 2) + args.n_kv_heads * tph;
+    }
     const int per_sm = NT <= 2 ? 2 : 1;
-    dim3 grid((unsigned)min(n_tiles, ctx->sm_count * per_sm));
-    return tsb_launch(ctx, kern, grid, dim3(GEMM_THREADS), smem, st, true, w, rows, units, act, cols, y, y_stride,
-                      tokens, ctx->dev_error, getenv("TSB_GEMM_PROBE") ? atoi(getenv("TSB_GEMM_PROBE")) : 0);
+    dim3 grid((unsigned)min(groups, ctx->sm_count * per_sm));
+    return tsb_launch(ctx, kern, grid, dim3(GEMM_THREADS), smem, st, true, w, rows, units, act, tokens, tok0, args, ctx->dev_error);
 }
 
-template <int QT, bool F32>
-cudaError_t launch_nt(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t rows, int units, ActOperand act,
-                      int cols, void* y, int64_t y_stride, int tokens) {
-    if (tokens <= 8) return launch_one<QT, 1, F32>(ctx, st, w, rows, units, act, cols, y, y_stride, tokens);
-    if (tokens <= 16) return launch_one<QT, 2, F32>(ctx, st, w, rows, units, act, cols, y, y_stride, tokens);
-    if (tokens <= 32) return launch_one<QT, 4, F32>(ctx, st, w, rows, units, act, cols, y, y_stride, tokens);
-    return launch_one<QT, 8, F32>(ctx, st, w, rows, units, act, cols, y, y_stride, tokens);
+template <int QT, int EPI>
+cudaError_t launch_nt(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t rows, int units, ActOperand act, int tokens,
+                      int tok0, const EpiArgs& args) {
+    if (tokens <= 8) return launch_one<QT, 1, EPI>(ctx, st, w, rows, units, act, tokens, tok0, args);
+    if (tokens <= 16) return launch_one<QT, 2, EPI>(ctx, st, w, rows, units, act, tokens, tok0, args);
+    if (tokens <= 32) return launch_one<QT, 4, EPI>(ctx, st, w, rows, units, act, tokens, tok0, args);
+    return launch_one<QT, 8, EPI>(ctx, st, w, rows, units, act, tokens, tok0, args);
 }
 
-// x natural -> fragment-major operand + sub-block sums
+template <int QT>
+cudaError_t launch_epi(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t rows, int units, ActOperand act, int tokens,
+                       int tok0, int epi, const EpiArgs& args) {
+    switch (epi) {
+        case EPI_PLAIN: return launch_nt<QT, EPI_PLAIN>(ctx, st, w, rows, units, act, tokens, tok0, args);
+        case EPI_SCALE: return launch_nt<QT, EPI_SCALE>(ctx, st, w, rows, units, act, tokens, tok0, args);
+        case EPI_RESID_NORM: return launch_nt<QT, EPI_RESID_NORM>(ctx, st, w, rows, units, act, tokens, tok0, args);
+        case EPI_SILU: return launch_nt<QT, EPI_SILU>(ctx, st, w, rows, units, act, tokens, tok0, args);
+        case EPI_ROPE_STORE: return launch_nt<QT, EPI_ROPE_STORE>(ctx, st, w, rows, units, act, tokens, tok0, args);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+// x natural -> fragment-major operand + 16-column sums
 __global__ void act_prepare_kernel(const __half* __restrict__ x, int64_t x_stride, int tokens, int cols,
-                                   uint4* __restrict__ xp, uint2* __restrict__ xs) {
+                                   uint4* __restrict__ xp, uint4* __restrict__ xs) {
     pdl_wait();
     const int per_row = cols >> 3;
     const int padded = ((tokens + 7) >> 3) << 3;  // slots of the last tile are zero-filled
@@ -574,35 +777,37 @@ __global__ void act_prepare_kernel(const __half* __restrict__ x, int64_t x_strid
 }  // namespace
 
 cudaError_t launch_act_prepare(tsb_ctx* ctx, cudaStream_t st, const __half* x, int64_t x_stride, int tokens, int cols,
-                               uint4* xp, uint2* xs) {
+                               uint4* xp, uint4* xs) {
     const int64_t n = (int64_t)act_tiles(tokens) * 8 * (cols / 8);
-    const int threads = 256;  // a multiple of 4 and cols/8 is a multiple of 4, so quads never straddle rows
+    const int threads = 256;  // even, and cols/8 is even, so the 16-column pairs never straddle rows
     return tsb_launch(ctx, act_prepare_kernel, dim3((unsigned)((n + threads - 1) / threads)), dim3(threads), 0, st, true,
                       x, x_stride, tokens, cols, xp, xs);
 }
 
-cudaError_t launch_gemm_quant(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t rows, int64_t cols,
-                              ActOperand act, void* y, int64_t y_stride, int tokens, bool y_f32) {
+cudaError_t launch_gemm_fused(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t rows, int64_t cols,
+                              ActOperand act, int tokens, int epi, const EpiArgs& args) {
     const int units = (int)(cols / 256);
     // more than 64 tokens: passes of 64 (each pass re-streams the weights)
     for (int t0 = 0; t0 < tokens; t0 += 64) {
         const int nt = min(64, tokens - t0);
         ActOperand a = {act.xp + (size_t)(t0 / 8) * units * 256, act.xs + (size_t)(t0 / 8) * units * 32};
-        void* yy = y_f32 ? (void*)((float*)y + (size_t)t0 * y_stride) : (void*)((__half*)y + (size_t)t0 * y_stride);
         cudaError_t e;
-#define TSB_DISPATCH(QT)                                                                                   \
-    e = y_f32 ? launch_nt<QT, true>(ctx, st, w, rows, units, a, (int)cols, yy, y_stride, nt)               \
-              : launch_nt<QT, false>(ctx, st, w, rows, units, a, (int)cols, yy, y_stride, nt)
         switch (qtype) {
-            case TSB_Q4_K: TSB_DISPATCH(TSB_Q4_K); break;
-            case TSB_Q6_K: TSB_DISPATCH(TSB_Q6_K); break;
-            case TSB_MXFP4: TSB_DISPATCH(TSB_MXFP4); break;
+            case TSB_Q4_K: e = launch_epi<TSB_Q4_K>(ctx, st, w, rows, units, a, nt, t0, epi, args); break;
+            case TSB_Q6_K: e = launch_epi<TSB_Q6_K>(ctx, st, w, rows, units, a, nt, t0, epi, args); break;
+            case TSB_MXFP4: e = launch_epi<TSB_MXFP4>(ctx, st, w, rows, units, a, nt, t0, epi, args); break;
             default: return cudaErrorInvalidValue;
         }
-#undef TSB_DISPATCH
         if (e != cudaSuccess) return e;
     }
     return cudaSuccess;
+}
+
+cudaError_t launch_gemm_quant(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t rows, int64_t cols,
+                              ActOperand act, void* y, int64_t y_stride, int tokens, bool y_f32) {
+    EpiArgs a;
+    a.y = y, a.y_stride = y_stride, a.y_f32 = y_f32 ? 1 : 0;
+    return launch_gemm_fused(ctx, st, qtype, w, rows, cols, act, tokens, EPI_PLAIN, a);
 }
 
 // ------------------------------------------------------------------ C ABI
@@ -626,7 +831,7 @@ int32_t tsb_gemm_quant(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* re
     uint8_t* tmp = nullptr;
     TSB_CUDA(ctx, cudaMallocAsync((void**)&tmp, xp_bytes + act_xs_bytes(tokens, cols), st));
     uint4* xp = reinterpret_cast<uint4*>(tmp);
-    uint2* xs = reinterpret_cast<uint2*>(tmp + xp_bytes);
+    uint4* xs = reinterpret_cast<uint4*>(tmp + xp_bytes);
     cudaError_t e = launch_act_prepare(ctx, st, (const __half*)x_f16, cols, tokens, (int)cols, xp, xs);
     if (e == cudaSuccess)
         e = launch_gemm_quant(ctx, st, qtype, (const uint8_t*)region + w_off, rows, cols, ActOperand{xp, xs}, y,

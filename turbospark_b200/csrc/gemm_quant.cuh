@@ -1,8 +1,9 @@
 // Internal interface of the quantized-matmul kernels (shared with the model runner).
 #pragma once
 #include "common.cuh"
+#include "kv.cuh"
 
-// The activation operand the GEMM kernels consume ("fragment-major" f16).
+// The activation operand the matmul kernels consume ("fragment-major" f16).
 //
 // Tokens are grouped in tiles of eight (an mma B operand has eight columns) and
 // columns in blocks of 256.  For tile nt and block blk the data is eight chunks
@@ -17,23 +18,72 @@
 // fully coalesced 512-byte request.  Unused token slots of the last tile must
 // be readable (they are computed and never stored).
 //
-// xs holds, per tile, block and lane, a uint2: the f32 sum of each 32-column
-// sub-block's f16 values split into an f16 high part and an f16 remainder;
-// .x = hi(sub 2tig) | hi(sub 2tig+1) << 16, .y the same for the remainders
-// (the Q4_K min term multiplies these sums).
+// xs holds, per tile, block and lane, a uint4 with the sums of the f16 values
+// of every 16-column run of the block (sixteen sums s[0..16) per token), each
+// split into an f16 high part and an f16 remainder, laid out as the B operand
+// of one m16n8k16 mma over those sums:
+//   .x = hi(s[2tig]) | hi(s[2tig+1]) << 16     .y = hi(s[2tig+8]) | hi(s[2tig+9]) << 16
+//   .z, .w the same for the remainders
+// (the Q4_K min term multiplies these sums by the sub-block mins).
 struct ActOperand {
     const uint4* xp;  // [tiles][cols/256][8][32]
-    const uint2* xs;  // [tiles][cols/256][32]
+    const uint4* xs;  // [tiles][cols/256][32]
+};
+struct ActOut {  // where a producer writes an operand (both null = do not)
+    uint4* xp;
+    uint4* xs;
 };
 
 inline int act_tiles(int tokens) { return (tokens + 7) / 8; }
 inline size_t act_xp_bytes(int tokens, int64_t cols) { return (size_t)act_tiles(tokens) * 8 * cols * sizeof(__half); }
-inline size_t act_xs_bytes(int tokens, int64_t cols) { return (size_t)act_tiles(tokens) * (cols / 256) * 32 * sizeof(uint2); }
+inline size_t act_xs_bytes(int tokens, int64_t cols) { return (size_t)act_tiles(tokens) * (cols / 256) * 32 * sizeof(uint4); }
+
+// What the kernel does with a finished 16-row tile (or pair of tiles).
+enum GemmEpi {
+    EPI_PLAIN = 0,       // y[t, row] = acc                               (public operator)
+    EPI_SCALE = 1,       // y[t, row] = inv_rms[t] * acc                  (head over a pre-normed operand)
+    EPI_RESID_NORM = 2,  // h += f16(acc); next operand = f16(h * g); partial sum of h^2   (o_proj, down)
+    EPI_SILU = 3,        // pair (gate tile, up tile): operand = f16(silu(f16(inv*g)) * f16(inv*u))
+    EPI_ROPE_STORE = 4,  // pair (low half, high half) of a q or k head: scale, rotate, q -> buffer, k -> cache; v -> cache
+};
+
+// RMSNorm split around a matmul.  The reference computes xn = f16(x * w * inv_rms) and feeds it to the matmul
+// (crates/gpu/src/shaders/rmsnorm.metal:70-95).  Here the producer of x (an epilogue) writes f16(x * w) as the
+// operand plus per-tile partial sums of x^2, and the consuming matmul multiplies its fp32 result by
+// inv_rms = 1/sqrt(mean(x^2) + eps): the matmul is linear, so only the position of one f16 rounding moves.
+struct EpiArgs {
+    // input-side norm (EPI_SCALE, EPI_SILU, EPI_ROPE_STORE): partial sums of x^2, [tokens][ss_parts]
+    const float* ss_in = nullptr;
+    int ss_parts = 0;
+    int d_in = 0;
+    float eps = 0.f;
+    // EPI_PLAIN / EPI_SCALE
+    void* y = nullptr;
+    int64_t y_stride = 0;
+    int y_f32 = 0;
+    // EPI_RESID_NORM: residual stream h [tokens, rows], next norm weight g (bf16, [rows]), outputs
+    __half* h = nullptr;
+    const uint16_t* g = nullptr;
+    float* ss_out = nullptr;  // [tokens][rows/16]
+    // operand written by EPI_RESID_NORM (width rows) and EPI_SILU (width rows/2)
+    ActOut out{nullptr, nullptr};
+    // EPI_ROPE_STORE
+    KvView kv{};
+    int layer = 0;
+    const tsb_row_desc* row_desc = nullptr;
+    const float* cs = nullptr;  // [tokens][head_dim]: cos[0..hd/2) then sin[0..hd/2) of the row's position
+    __half* q_out = nullptr;    // [tokens, n_q_heads * head_dim]
+    int n_q_heads = 0, n_kv_heads = 0, head_dim = 0;
+};
 
 // x [tokens, cols] f16 natural order -> ActOperand buffers.
 cudaError_t launch_act_prepare(tsb_ctx* ctx, cudaStream_t st, const __half* x, int64_t x_stride, int tokens, int cols,
-                               uint4* xp, uint2* xs);
+                               uint4* xp, uint4* xs);
 
+// The matmul over verbatim block rows with the chosen epilogue.  rows = weight rows (for EPI_SILU the gate and
+// up halves back to back; for EPI_ROPE_STORE q heads, k heads, v heads back to back).
+cudaError_t launch_gemm_fused(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t rows, int64_t cols,
+                              ActOperand act, int tokens, int epi, const EpiArgs& args);
 // y[t, r] = W[r,:] . x[t,:]; y f16 or f32, [tokens, rows] with row stride y_stride (elements).
 cudaError_t launch_gemm_quant(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t rows, int64_t cols,
                               ActOperand act, void* y, int64_t y_stride, int tokens, bool y_f32);
@@ -54,14 +104,32 @@ __device__ __forceinline__ size_t act_xp_half_index(int t, int col, int nblk) {
     const int pos = (w & 4) | (q == 1 ? 2 : (q == 2 ? 1 : q));
     return act_xp_index(t, col & ~7, nblk) * 8 + pos;
 }
+// Store the sum of one 16-column run (columns col16..col16+15 of token t) as hi + lo halves.
+__device__ __forceinline__ void act_store_sum16(uint4* xs, int t, int col16, int nblk, float s) {
+    const int blk = col16 >> 8, i = (col16 >> 4) & 15;
+    const int tig = (i & 7) >> 1, comp = i >> 3, pos = i & 1;
+    __half* q = reinterpret_cast<__half*>(xs + ((((size_t)(t >> 3) * nblk + blk) << 5) + ((t & 7) << 2) + tig));
+    const __half hi = __float2half_rn(s);
+    q[comp * 2 + pos] = hi;
+    q[4 + comp * 2 + pos] = __float2half_rn(s - __half2float(hi));
+}
+// Pack eight f16 values (natural order) into the operand's stored order.
+__device__ __forceinline__ uint4 act_pack8(const __half (&h)[8]) {
+    uint4 o;
+    __half2 a = __halves2half2(h[0], h[2]), b = __halves2half2(h[1], h[3]);
+    __half2 c = __halves2half2(h[4], h[6]), d = __halves2half2(h[5], h[7]);
+    o.x = *reinterpret_cast<uint32_t*>(&a);
+    o.y = *reinterpret_cast<uint32_t*>(&b);
+    o.z = *reinterpret_cast<uint32_t*>(&c);
+    o.w = *reinterpret_cast<uint32_t*>(&d);
+    return o;
+}
 
-// Device helper for producers of GEMM inputs: a thread that holds eight
-// consecutive f32 outputs v[0..8) of column e0 (a multiple of 8) of token t
-// stores them, rounded to f16, into the operand, and the four threads of an
-// aligned quad (lane & 3) that together cover one 32-column sub-block add up
-// the rounded values and store the hi/lo sums.  All 32 lanes of the warp must
-// call it together.
-__device__ __forceinline__ void act_store8(const float (&v)[8], uint4* xp, uint2* xs, int t, int e0, int nblk,
+// Device helper for producers of matmul inputs: a thread that holds eight consecutive f32 outputs v[0..8) of
+// column e0 (a multiple of 8) of token t stores them, rounded to f16, into the operand; the thread holding the
+// even run of each 16-column pair also stores the pair's sum.  Threads of a warp must hold consecutive runs
+// (lane i and lane i^1 form a pair) and all 32 lanes must call it together.
+__device__ __forceinline__ void act_store8(const float (&v)[8], uint4* xp, uint4* xs, int t, int e0, int nblk,
                                            bool active) {
     __half h[8];
     float s = 0.f;
@@ -72,23 +140,9 @@ __device__ __forceinline__ void act_store8(const float (&v)[8], uint4* xp, uint2
     }
     if (!active) s = 0.f;
     s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
     if (active) {
-        uint4 o;
-        __half2 a = __halves2half2(h[0], h[2]), b = __halves2half2(h[1], h[3]);
-        __half2 c = __halves2half2(h[4], h[6]), d = __halves2half2(h[5], h[7]);
-        o.x = *reinterpret_cast<uint32_t*>(&a);
-        o.y = *reinterpret_cast<uint32_t*>(&b);
-        o.z = *reinterpret_cast<uint32_t*>(&c);
-        o.w = *reinterpret_cast<uint32_t*>(&d);
-        xp[act_xp_index(t, e0, nblk)] = o;
-        if ((threadIdx.x & 3) == 0) {
-            const int blk = e0 >> 8, sb = (e0 >> 5) & 7;
-            __half* q = reinterpret_cast<__half*>(xs + ((((size_t)(t >> 3) * nblk + blk) << 5) + ((t & 7) << 2) + (sb >> 1)));
-            const __half hi = __float2half_rn(s);
-            q[sb & 1] = hi;
-            q[2 + (sb & 1)] = __float2half_rn(s - __half2float(hi));
-        }
+        xp[act_xp_index(t, e0, nblk)] = act_pack8(h);
+        if ((e0 & 8) == 0) act_store_sum16(xs, t, e0, nblk, s);
     }
 }
 #endif

@@ -305,10 +305,9 @@ static int32_t runtime_init(tsb_session* s, ModelRt& rt, const tsb_model* model,
     if (rc) return rc;
     auto A = [&](size_t bytes, void** p) { return dev_alloc(ctx, s->owned, bytes, p); };
     if ((rc = A((size_t)R * c.d_model * 2, (void**)&rt.h))) return rc;
-    if ((rc = A((size_t)R * qkv_dim * 2, (void**)&rt.qkv))) return rc;
-    if ((rc = A((size_t)R * c.d_model * 2, (void**)&rt.o))) return rc;
-    if ((rc = A((size_t)R * 2 * c.ffn * 2, (void**)&rt.gu))) return rc;
-    if ((rc = A((size_t)R * c.d_model * 2, (void**)&rt.dn))) return rc;
+    if ((rc = A((size_t)R * c.n_q_heads * c.head_dim * 2, (void**)&rt.q))) return rc;
+    if ((rc = A((size_t)R * c.head_dim * sizeof(float), (void**)&rt.cs))) return rc;
+    if ((rc = A((size_t)(2 * c.n_layers + 1) * R * (c.d_model / 16) * sizeof(float), (void**)&rt.ss))) return rc;
     const int64_t od = (int64_t)c.n_q_heads * c.head_dim;
     if ((rc = A(act_xp_bytes(Rp, c.d_model), (void**)&rt.act_d.xp)) || (rc = A(act_xs_bytes(Rp, c.d_model), (void**)&rt.act_d.xs))) return rc;
     if ((rc = A(act_xp_bytes(Rp, od), (void**)&rt.act_o.xp)) || (rc = A(act_xs_bytes(Rp, od), (void**)&rt.act_o.xs))) return rc;
@@ -335,7 +334,6 @@ static cudaError_t forward_device(tsb_session* s, ModelRt& rt, const int32_t* to
     cudaStream_t st = s->stream;
     const tsb_model* m = rt.model;
     const tsb_model_config& c = m->cfg;
-    const int64_t qkv_dim = (int64_t)(c.n_q_heads + 2 * c.n_kv_heads) * c.head_dim;
     const float scale = 1.0f / sqrtf((float)c.head_dim);
     max_len = (max_len + 511) / 512 * 512;  // the split plan changes only every 512 positions (graph reuse)
     cudaError_t e;
@@ -344,28 +342,48 @@ static cudaError_t forward_device(tsb_session* s, ModelRt& rt, const int32_t* to
         e = (x);                      \
         if (e != cudaSuccess) return e; \
     } while (0)
-    FW(launch_embed_rows(ctx, st, m->embed.qtype, m->embed.data, c.vocab, c.d_model, tokens_dev, token_stride, rows, rt.h, 1.0f));
     const ActOut out_d{rt.act_d.xp, rt.act_d.xs}, out_o{rt.act_o.xp, rt.act_o.xs}, out_f{rt.act_f.xp, rt.act_f.xs};
     const ActOperand in_d{rt.act_d.xp, rt.act_d.xs}, in_o{rt.act_o.xp, rt.act_o.xs}, in_f{rt.act_f.xp, rt.act_f.xs};
+    const int R = s->n_streams * s->max_rows;
+    const int parts = c.d_model / 16;
+    auto ss_slot = [&](int i) { return rt.ss + (size_t)i * R * parts; };
+    // embedding: residual stream, layer 0's operand f16(h * g), sum of h^2 (one partial per row), RoPE table
+    FW(launch_embed_norm(ctx, st, m->embed.qtype, m->embed.data, c.vocab, c.d_model, tokens_dev, token_stride, rows, rt.h,
+                         m->layers[0].attn_norm, out_d, ss_slot(0), rt.cs, rows_dev, c.head_dim, c.rope_theta));
     for (int L = 0; L < c.n_layers; L++) {
         const LayerW& l = m->layers[L];
-        FW(launch_rmsnorm_rows(ctx, st, rt.h, L == 0 ? nullptr : rt.dn, l.attn_norm, nullptr, out_d, rows, c.d_model, c.rms_eps));
-        FW(launch_gemm_quant(ctx, st, l.wqkv.qtype, l.wqkv.data, l.wqkv.rows, l.wqkv.cols, in_d, rt.qkv, qkv_dim, rows, false));
-        FW(launch_rope_store_kv(ctx, st, rt.kv, L, rt.qkv, rows_dev, rows, c.n_q_heads, c.rope_theta));
-        FW(launch_attn_decode_rows(ctx, st, rt.kv, L, rt.qkv, qkv_dim, nullptr, out_o, rows_dev, rows, rows_per_seq,
-                                   c.n_q_heads, scale, max_len, rt.attn_scratch));
-        FW(launch_gemm_quant(ctx, st, l.wo.qtype, l.wo.data, l.wo.rows, l.wo.cols, in_o, rt.o, c.d_model, rows, false));
-        FW(launch_rmsnorm_rows(ctx, st, rt.h, rt.o, l.ffn_norm, nullptr, out_d, rows, c.d_model, c.rms_eps));
-        FW(launch_gemm_quant(ctx, st, l.wgu.qtype, l.wgu.data, l.wgu.rows, l.wgu.cols, in_d, rt.gu, 2 * (int64_t)c.ffn, rows, false));
-        FW(launch_silu_mul(ctx, st, rt.gu, rt.gu + c.ffn, nullptr, out_f, rows, c.ffn, 2 * (int64_t)c.ffn, c.ffn));
-        FW(launch_gemm_quant(ctx, st, l.wdown.qtype, l.wdown.data, l.wdown.rows, l.wdown.cols, in_f, rt.dn, c.d_model, rows, false));
+        {   // q|k|v matmul; epilogue: 1/rms, RoPE, q -> buffer, k and v -> cache slots
+            EpiArgs a;
+            a.ss_in = ss_slot(2 * L), a.ss_parts = L == 0 ? 1 : parts, a.d_in = c.d_model, a.eps = c.rms_eps;
+            a.kv = rt.kv->view, a.layer = L, a.row_desc = rows_dev, a.cs = rt.cs, a.q_out = rt.q;
+            a.n_q_heads = c.n_q_heads, a.n_kv_heads = c.n_kv_heads, a.head_dim = c.head_dim;
+            FW(launch_gemm_fused(ctx, st, l.wqkv.qtype, l.wqkv.data, l.wqkv.rows, l.wqkv.cols, in_d, rows, EPI_ROPE_STORE, a));
+        }
+        FW(launch_attn_decode_rows(ctx, st, rt.kv, L, rt.q, (int64_t)c.n_q_heads * c.head_dim, nullptr, out_o, rows_dev, rows,
+                                   rows_per_seq, c.n_q_heads, scale, max_len, rt.attn_scratch));
+        {   // o_proj; epilogue: residual add, next operand f16(h * g_ffn), partial sums of h^2
+            EpiArgs a;
+            a.h = rt.h, a.g = l.ffn_norm, a.out = out_d, a.ss_out = ss_slot(2 * L + 1);
+            FW(launch_gemm_fused(ctx, st, l.wo.qtype, l.wo.data, l.wo.rows, l.wo.cols, in_o, rows, EPI_RESID_NORM, a));
+        }
+        {   // gate|up matmul; epilogue: 1/rms, SiLU(gate) * up -> operand of the down projection
+            EpiArgs a;
+            a.ss_in = ss_slot(2 * L + 1), a.ss_parts = parts, a.d_in = c.d_model, a.eps = c.rms_eps, a.out = out_f;
+            FW(launch_gemm_fused(ctx, st, l.wgu.qtype, l.wgu.data, l.wgu.rows, l.wgu.cols, in_d, rows, EPI_SILU, a));
+        }
+        {   // down projection; epilogue: residual add, operand for the next layer's norm (or the final norm)
+            EpiArgs a;
+            a.h = rt.h, a.g = L + 1 < c.n_layers ? m->layers[L + 1].attn_norm : m->out_norm, a.out = out_d;
+            a.ss_out = ss_slot(2 * L + 2);
+            FW(launch_gemm_fused(ctx, st, l.wdown.qtype, l.wdown.data, l.wdown.rows, l.wdown.cols, in_f, rows, EPI_RESID_NORM, a));
+        }
     }
-    FW(launch_rmsnorm_rows(ctx, st, rt.h, rt.dn, m->out_norm, nullptr, out_d, rows, c.d_model, c.rms_eps));
     if (logits) {
-        // logits rows may be strided (a drafter's step d of k): one matmul call per row when not dense
-        // row t of the logits sits at logits + t * logits_stride (a drafter's step d of k is strided)
-        FW(launch_gemm_quant(ctx, st, m->lm_head.qtype, m->lm_head.data, m->lm_head.rows, m->lm_head.cols, in_d, logits,
-                             logits_stride, rows, false));
+        // head over the final-normed operand; row t of the logits sits at logits + t * logits_stride
+        EpiArgs a;
+        a.ss_in = ss_slot(2 * c.n_layers), a.ss_parts = parts, a.d_in = c.d_model, a.eps = c.rms_eps;
+        a.y = logits, a.y_stride = logits_stride, a.y_f32 = 0;
+        FW(launch_gemm_fused(ctx, st, m->lm_head.qtype, m->lm_head.data, m->lm_head.rows, m->lm_head.cols, in_d, rows, EPI_SCALE, a));
     }
 #undef FW
     return cudaSuccess;
@@ -903,14 +921,16 @@ int32_t tsb_session_time_matmuls(tsb_session* s, int32_t rows, int32_t iters, fl
     cudaStream_t st = s->stream;
     int64_t bytes = 0;
     int launches = 0;
+    // plain epilogues into the logits buffer: the weight streaming and the mma work are those of the forward pass
+    void* sink = s->logits_target;
     for (int it = -1; it < iters; it++) {  // iteration -1 is a warm-up
         if (it == 0) TSB_CUDA(ctx, cudaEventRecord(s->ev[0], st));
         for (int L = 0; L < c.n_layers; L++) {
             const LayerW& l = m->layers[L];
-            TSB_CUDA(ctx, launch_gemm_quant(ctx, st, l.wqkv.qtype, l.wqkv.data, l.wqkv.rows, l.wqkv.cols, in_d, rt.qkv, qkv_dim, rows, false));
-            TSB_CUDA(ctx, launch_gemm_quant(ctx, st, l.wo.qtype, l.wo.data, l.wo.rows, l.wo.cols, in_o, rt.o, c.d_model, rows, false));
-            TSB_CUDA(ctx, launch_gemm_quant(ctx, st, l.wgu.qtype, l.wgu.data, l.wgu.rows, l.wgu.cols, in_d, rt.gu, 2 * (int64_t)c.ffn, rows, false));
-            TSB_CUDA(ctx, launch_gemm_quant(ctx, st, l.wdown.qtype, l.wdown.data, l.wdown.rows, l.wdown.cols, in_f, rt.dn, c.d_model, rows, false));
+            TSB_CUDA(ctx, launch_gemm_quant(ctx, st, l.wqkv.qtype, l.wqkv.data, l.wqkv.rows, l.wqkv.cols, in_d, sink, qkv_dim, rows, false));
+            TSB_CUDA(ctx, launch_gemm_quant(ctx, st, l.wo.qtype, l.wo.data, l.wo.rows, l.wo.cols, in_o, sink, c.d_model, rows, false));
+            TSB_CUDA(ctx, launch_gemm_quant(ctx, st, l.wgu.qtype, l.wgu.data, l.wgu.rows, l.wgu.cols, in_d, sink, 2 * (int64_t)c.ffn, rows, false));
+            TSB_CUDA(ctx, launch_gemm_quant(ctx, st, l.wdown.qtype, l.wdown.data, l.wdown.rows, l.wdown.cols, in_f, sink, c.d_model, rows, false));
             if (it == 0) {
                 bytes += mat_bytes(l.wqkv) + mat_bytes(l.wo) + mat_bytes(l.wgu) + mat_bytes(l.wdown);
                 launches += 4 * ((rows + 63) / 64);

@@ -30,14 +30,16 @@ struct tsb_model {
 
 struct ActBuf {
     uint4* xp = nullptr;
-    uint2* xs = nullptr;
+    uint4* xs = nullptr;
 };
 
 // What one model needs to run inside a session.
 struct ModelRt {
     const tsb_model* model = nullptr;
     tsb_kv* kv = nullptr;
-    __half *h = nullptr, *qkv = nullptr, *o = nullptr, *gu = nullptr, *dn = nullptr;
+    __half *h = nullptr, *q = nullptr;  // residual stream [R, d]; rotated queries [R, n_q_heads*head_dim]
+    float* cs = nullptr;                // RoPE table [R, head_dim]: cos | sin of each row's position
+    float* ss = nullptr;                // partial sums of h^2: [2*layers + 1][R][d/16]
     ActBuf act_d, act_o, act_f;  // matmul operands of width d_model, n_q_heads*head_dim, ffn
     void* attn_scratch = nullptr;
     size_t attn_scratch_bytes = 0;

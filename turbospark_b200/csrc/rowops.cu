@@ -245,6 +245,68 @@ __global__ void residual_add_kernel(__half* __restrict__ x, const __half* __rest
     pdl_launch_dependents();
 }
 
+// Embedding for the fused forward: h[r,:] = f16(dequantised row), the first layer's matmul operand f16(h * g), one
+// partial sum of h^2 per row, and the row's RoPE table cos|sin (double-precision exp / sin / cos rounded once, which
+// reproduces a correctly rounded f32 libm: crates/compute/src/rope.rs:208-255).  One CTA per row.
+template <int QT>
+__global__ void __launch_bounds__(256)
+    embed_norm_kernel(const uint8_t* __restrict__ w, int64_t row_bytes, int64_t table_rows, int d,
+                      const int32_t* __restrict__ ids, int id_stride, __half* __restrict__ h, const uint16_t* __restrict__ g,
+                      ActOut act, float* __restrict__ ss_out, float* __restrict__ cs, const tsb_row_desc* __restrict__ rows,
+                      int head_dim, float log_theta, uint32_t* __restrict__ err) {
+    __shared__ float warp_sums[8];
+    pdl_wait();
+    const int r = blockIdx.x;
+    int64_t src = (int64_t)ids[(size_t)r * id_stride];
+    if (src < 0 || src >= table_rows) {
+        if (threadIdx.x == 0) atomicCAS(err, 0u, (uint32_t)TSB_DEV_BAD_INDEX);
+        src = 0;
+    }
+    const uint8_t* row = w + src * row_bytes;
+    const int half = head_dim >> 1;
+    const float pos = (float)rows[r].position;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float exponent = -((float)(2 * i)) / (float)head_dim;
+        const float freq = (float)exp((double)__fmul_rn(exponent, log_theta));
+        const float angle = __fmul_rn(pos, freq);
+        cs[(size_t)r * head_dim + i] = (float)cos((double)angle);
+        cs[(size_t)r * head_dim + half + i] = (float)sin((double)angle);
+    }
+    float ss = 0.f;
+    for (int base = 0; base < d; base += 256 * 8) {
+        const int e0 = base + threadIdx.x * 8;
+        const bool active = e0 < d;  // d is a multiple of 256, so a warp is active or idle as a whole
+        float xg[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) xg[i] = 0.f;
+        if (active) {
+            uint4 hv;
+            __half* hh = reinterpret_cast<__half*>(&hv);
+            const uint4 gv = *reinterpret_cast<const uint4*>(g + e0);
+            const uint16_t* gg = reinterpret_cast<const uint16_t*>(&gv);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                hh[i] = __float2half_rn(dequant_elem<QT>(row, e0 + i));
+                const float hn = __half2float(hh[i]);
+                ss = fmaf(hn, hn, ss);
+                xg[i] = hn * bf16_bits_to_float(gg[i]);
+            }
+            *reinterpret_cast<uint4*>(h + (size_t)r * d + e0) = hv;
+        }
+        act_store8(xg, act.xp, act.xs, r, active ? e0 : 0, d >> 8, active);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int i = 0; i < 8; i++) t += warp_sums[i];
+        ss_out[r] = t;
+    }
+}
+
 template <bool F16>
 cudaError_t launch_dequant(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t table_rows, int cols,
                            const int32_t* ids, int id_stride, int n, void* out, float scale) {
@@ -268,6 +330,24 @@ cudaError_t launch_dequant(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8
 cudaError_t launch_embed_rows(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t vocab_rows, int cols,
                               const int32_t* ids, int id_stride, int n, __half* out, float out_scale) {
     return launch_dequant<true>(ctx, st, qtype, w, vocab_rows, cols, ids, id_stride, n, out, out_scale);
+}
+
+cudaError_t launch_embed_norm(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t vocab_rows, int d,
+                              const int32_t* ids, int id_stride, int n, __half* h, const void* g_bf16, ActOut act, float* ss_out,
+                              float* cs, const tsb_row_desc* rows, int head_dim, float theta) {
+    const int64_t rb = tsb_row_bytes(qtype, d);
+    const float lt = logf(theta);
+    switch (qtype) {
+        case TSB_Q4_K:
+            return tsb_launch(ctx, embed_norm_kernel<TSB_Q4_K>, dim3((unsigned)n), dim3(256), 0, st, true, w, rb, vocab_rows, d, ids,
+                              id_stride, h, (const uint16_t*)g_bf16, act, ss_out, cs, rows, head_dim, lt, ctx->dev_error);
+        case TSB_Q6_K:
+            return tsb_launch(ctx, embed_norm_kernel<TSB_Q6_K>, dim3((unsigned)n), dim3(256), 0, st, true, w, rb, vocab_rows, d, ids,
+                              id_stride, h, (const uint16_t*)g_bf16, act, ss_out, cs, rows, head_dim, lt, ctx->dev_error);
+        default:
+            return tsb_launch(ctx, embed_norm_kernel<TSB_MXFP4>, dim3((unsigned)n), dim3(256), 0, st, true, w, rb, vocab_rows, d, ids,
+                              id_stride, h, (const uint16_t*)g_bf16, act, ss_out, cs, rows, head_dim, lt, ctx->dev_error);
+    }
 }
 
 cudaError_t launch_rmsnorm_rows(tsb_ctx* ctx, cudaStream_t st, __half* x, const __half* residual, const void* w_bf16,

@@ -2,12 +2,6 @@
 #pragma once
 #include "gemm_quant.cuh"
 
-// Where a producer writes the matmul activation operand (all null = do not).
-struct ActOut {
-    uint4* xp;
-    uint2* xs;
-};
-
 cudaError_t launch_embed_rows(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t vocab_rows, int cols,
                               const int32_t* ids, int id_stride, int n, __half* out, float out_scale);
 // x <- f16(x + residual) when residual != null; out (natural f16, may be null) and/or act get the normed rows.
@@ -15,3 +9,7 @@ cudaError_t launch_rmsnorm_rows(tsb_ctx* ctx, cudaStream_t st, __half* x, const 
                                 __half* out, ActOut act, int rows, int d, float eps);
 cudaError_t launch_silu_mul(tsb_ctx* ctx, cudaStream_t st, const __half* gate, const __half* up, __half* out, ActOut act,
                             int rows, int n, int64_t in_stride, int64_t out_stride);
+// Fused embedding for the model forward: residual stream, first operand f16(h * g), sum of h^2, RoPE table.
+cudaError_t launch_embed_norm(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t vocab_rows, int d,
+                              const int32_t* ids, int id_stride, int n, __half* h, const void* g_bf16, ActOut act, float* ss_out,
+                              float* cs, const tsb_row_desc* rows, int head_dim, float theta);
