@@ -8,12 +8,13 @@
 // the CTA four warps split the work 2 x 2: two 16-query mma tiles x two halves
 // of each 64-token K/V tile.  Scores S = Q K^T and O += P V run on mma.sync
 // m16n8k16 (f16 in, f32 accumulate) with K/V staged in shared memory by
-// cp.async, double buffered, 16-byte-chunk XOR swizzle, fragments pulled with
+// cp.async (three stages), 16-byte-chunk XOR swizzle, fragments pulled with
 // ldmatrix.  The online softmax keeps (m, l, O) per query in registers; row max
 // and sum are combined across the four lanes of a quad with warp shuffles.
-// Each CTA writes one partial (m, l, O[head_dim]) per query; a second kernel
-// merges the partials of all chunks and emits f16 rows plus the o_proj matmul's
-// activation operand.
+// Each CTA writes one partial (m, l, O[head_dim]) per query; the last CTA of a
+// (stream, kv head, query tile) to finish - decided by a ticket counter, nobody
+// waits - merges the partials of all chunks with warp shuffles and emits f16
+// rows and/or the o_proj matmul's activation operand.
 //
 // Masking: positions below the row's `base` are the committed prefix (always
 // visible); position base + j is in-flight slot j and is visible iff bit j of
@@ -26,6 +27,7 @@ namespace {
 constexpr int ATT_THREADS = 128;
 constexpr int TILE_TOKENS = 64;
 constexpr int MAX_SPLITS = 64;
+constexpr int NST = 3;  // K/V tile stages in shared memory
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -53,12 +55,13 @@ __global__ void __launch_bounds__(ATT_THREADS)
     attn_partial_kernel(KvView kv, int layer, const __half* __restrict__ q, int64_t q_stride,
                         const tsb_row_desc* __restrict__ rows, int rows_per_seq, int n_q_heads, float scale_log2e,
                         int chunk, int n_splits, float* __restrict__ part_o, float2* __restrict__ part_ml,
-                        uint32_t* __restrict__ err) {
+                        uint32_t* __restrict__ tickets, __half* __restrict__ out, ActOut act, uint32_t* __restrict__ err) {
     constexpr int CH = HD / 8;    // 16-byte chunks per token row
     constexpr int KS = HD / 16;   // k steps of S = Q K^T
     constexpr int NO = HD / 8;    // n tiles of O
     constexpr int TILE_BYTES = TILE_TOKENS * HD * 2;
-    extern __shared__ __align__(128) uint8_t smem[];  // [2 stages][K tile | V tile]
+    extern __shared__ __align__(128) uint8_t smem[];  // [NST stages][K tile | V tile]
+    __shared__ int s_last;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tig = lane & 3;
@@ -113,34 +116,38 @@ __global__ void __launch_bounds__(ATT_THREADS)
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
     const uint32_t smem_base = smem_u32(smem);
+    // a thread copies half a token row (K and V) of every tile: one page-table lookup per thread per tile
     auto issue_tile = [&](int tile, int stage) {
         const int t0 = t_begin + tile * TILE_TOKENS;
         const uint32_t kdst = smem_base + stage * 2 * TILE_BYTES, vdst = kdst + TILE_BYTES;
+        const int r = threadIdx.x >> 1, c0 = (threadIdx.x & 1) * (CH / 2);
+        const int pos = t0 + r;
+        const bool valid = pos < t_end;
+        const __half* kr = valid ? kv_row(kv, layer, 0, seq, pos) : nullptr;
+        const bool ok = kr != nullptr;
+        const __half* ksrc = ok ? kr + (size_t)kvh * HD : kv.pool;
+        const __half* vsrc = ok ? ksrc + kv.kv_stride : kv.pool;  // V sits one kv_stride after K in the same layer
 #pragma unroll
-        for (int i = 0; i < TILE_TOKENS * CH / ATT_THREADS; i++) {
-            const int idx = threadIdx.x + i * ATT_THREADS;
-            const int r = idx / CH, c = idx % CH;
-            const int pos = t0 + r;
-            const bool valid = pos < t_end;
-            const __half* kr = valid ? kv_row(kv, layer, 0, seq, pos) : nullptr;
-            const __half* vr = valid ? kv_row(kv, layer, 1, seq, pos) : nullptr;
-            const bool ok = kr != nullptr && vr != nullptr;
+        for (int i = 0; i < CH / 2; i++) {
+            const int c = c0 + i;
             const uint32_t off = tile_off<HD>(r, c);
-            cp_async16_zfill(kdst + off, ok ? (const void*)(kr + (size_t)kvh * HD + c * 8) : (const void*)kv.pool, ok);
-            cp_async16_zfill(vdst + off, ok ? (const void*)(vr + (size_t)kvh * HD + c * 8) : (const void*)kv.pool, ok);
+            cp_async16_zfill(kdst + off, ok ? (const void*)(ksrc + c * 8) : (const void*)kv.pool, ok);
+            cp_async16_zfill(vdst + off, ok ? (const void*)(vsrc + c * 8) : (const void*)kv.pool, ok);
         }
         cp_async_commit();
     };
 
-    issue_tile(0, 0);
+    // NST-deep cp.async pipeline: NST - 1 tiles in flight while one is consumed
+#pragma unroll
+    for (int i = 0; i < NST - 1; i++) {
+        if (i < n_tiles) issue_tile(i, i);
+        else cp_async_commit();
+    }
     for (int tile = 0; tile < n_tiles; tile++) {
-        const int stage = tile & 1;
-        if (tile + 1 < n_tiles) {
-            issue_tile(tile + 1, stage ^ 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
+        const int stage = tile % NST;
+        if (tile + NST - 1 < n_tiles) issue_tile(tile + NST - 1, (tile + NST - 1) % NST);
+        else cp_async_commit();
+        cp_async_wait<NST - 1>();
         __syncthreads();
         const uint32_t ktile = smem_base + stage * 2 * TILE_BYTES, vtile = ktile + TILE_BYTES;
         const int tok0 = th * 32;  // this warp's 32 tokens of the tile
@@ -280,56 +287,70 @@ __global__ void __launch_bounds__(ATT_THREADS)
             if (v1) part_ml[i1] = make_float2(m_out[1], l_out[1]);
         }
     }
-}
 
-// Merge the chunk partials: out = sum_c O_c 2^(m_c - m) / sum_c l_c 2^(m_c - m)
-// (crates/gpu/src/shaders/attention.metal:983-1031).  One thread per eight
-// head_dim elements of one (row, q head).
-template <int HD>
-__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float2* __restrict__ part_ml,
-                                  const tsb_row_desc* __restrict__ rows, int n_rows, int rows_per_seq, int n_q_heads,
-                                  int chunk, int n_splits, __half* __restrict__ out, ActOut act) {
-    pdl_wait();
-    constexpr int TPH = HD / 8;  // threads per head
-    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const bool active = idx < (int64_t)n_rows * n_q_heads * TPH;
-    const int part = active ? (int)(idx % TPH) : 0;
-    const int rh = active ? (int)(idx / TPH) : 0;
-    const int row = rh / n_q_heads, head = rh % n_q_heads;
-    float acc[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) acc[i] = 0.f;
-    if (active) {
-        const int L = rows[(row / rows_per_seq) * rows_per_seq].base + rows_per_seq;
-        const int ns = min(n_splits, (L + chunk - 1) / chunk);
-        const float2* ml = part_ml + (size_t)rh * n_splits;
+    // ---- the last CTA of this (stream, kv head, query tile) to finish merges the chunk partials:
+    // out = sum_c O_c 2^(m_c - m) / sum_c l_c 2^(m_c - m)   (crates/gpu/src/shaders/attention.metal:983-1031).
+    // A ticket counter decides who is last; nobody waits on anybody.
+    const int ns = min(n_splits, (L + chunk - 1) / chunk);  // chunks that exist for this stream
+    const int ticket_id = (blockIdx.z * nkv + kvh) * n_qpairs + qpair;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t old = atomicAdd(&tickets[ticket_id], 1u);
+        s_last = old == (uint32_t)(ns - 1);
+        if (s_last) tickets[ticket_id] = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    constexpr int TPH = HD / 8;     // 8-column runs per head
+    constexpr int SF = 32 / TPH;    // lanes sharing one run, each taking every SF-th chunk
+    const int part = lane % TPH, sidx = lane / TPH;
+    for (int qo = warp; qo < 32; qo += ATT_THREADS / 32) {
+        const int qi = qpair * 32 + qo;
+        if (qi >= n_queries) break;  // uniform per warp
+        const int row = row_first + qi / G, head = kvh * G + qi % G;
+        const size_t rh = (size_t)row * n_q_heads + head;
+        const float2* ml = part_ml + rh * n_splits;
+        // global max over the chunks: lanes stride over the chunk list, then a warp max
         float m = -INFINITY;
-        for (int c = 0; c < ns; c++) m = fmaxf(m, ml[c].x);
+        for (int c = lane; c < ns; c += 32) m = fmaxf(m, __ldcg(&ml[c]).x);
+#pragma unroll
+        for (int o2 = 16; o2 > 0; o2 >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o2));
         const float mu = (m == -INFINITY) ? 0.f : m;
-        float den = 0.f;
-        for (int c = 0; c < ns; c++) {
-            const float2 v = ml[c];
+        float den = 0.f, accv[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) accv[i] = 0.f;
+#pragma unroll 4
+        for (int c = sidx; c < ns; c += SF) {
+            const float2 v = __ldcg(&ml[c]);
             const float w = exp2f(v.x - mu);
             den += v.y * w;
-            const float4* po = reinterpret_cast<const float4*>(part_o + ((size_t)rh * n_splits + c) * HD + part * 8);
-            const float4 a = po[0], b = po[1];
-            acc[0] += a.x * w, acc[1] += a.y * w, acc[2] += a.z * w, acc[3] += a.w * w;
-            acc[4] += b.x * w, acc[5] += b.y * w, acc[6] += b.z * w, acc[7] += b.w * w;
+            const float4* po = reinterpret_cast<const float4*>(part_o + (rh * n_splits + c) * HD + part * 8);
+            const float4 a = __ldcg(po), b2 = __ldcg(po + 1);
+            accv[0] += a.x * w, accv[1] += a.y * w, accv[2] += a.z * w, accv[3] += a.w * w;
+            accv[4] += b2.x * w, accv[5] += b2.y * w, accv[6] += b2.z * w, accv[7] += b2.w * w;
+        }
+#pragma unroll
+        for (int o2 = TPH; o2 < 32; o2 <<= 1) {
+            den += __shfl_xor_sync(0xffffffffu, den, o2);
+#pragma unroll
+            for (int i = 0; i < 8; i++) accv[i] += __shfl_xor_sync(0xffffffffu, accv[i], o2);
         }
         const float inv = den > 0.f ? 1.0f / den : 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; i++) acc[i] *= inv;
-    }
-    pdl_launch_dependents();
-    const int e0 = head * HD + part * 8;
-    if (out && active) {
-        uint4 pk;
-        __half* pp = reinterpret_cast<__half*>(&pk);
+        for (int i = 0; i < 8; i++) accv[i] *= inv;
+        const int e0 = head * HD + part * 8;
+        const bool writer = sidx == 0;  // lanes 0..TPH-1 hold the runs of this head in order
+        if (out && writer) {
+            uint4 pk;
+            __half* pp = reinterpret_cast<__half*>(&pk);
 #pragma unroll
-        for (int i = 0; i < 8; i++) pp[i] = __float2half_rn(acc[i]);
-        *reinterpret_cast<uint4*>(out + (size_t)row * n_q_heads * HD + e0) = pk;
+            for (int i = 0; i < 8; i++) pp[i] = __float2half_rn(accv[i]);
+            *reinterpret_cast<uint4*>(out + (size_t)row * n_q_heads * HD + e0) = pk;
+        }
+        if (act.xp) act_store8(accv, act.xp, act.xs, row, e0, (n_q_heads * HD) >> 8, writer);
     }
-    if (act.xp) act_store8(acc, act.xp, act.xs, row, e0, (n_q_heads * HD) >> 8, active);
 }
 
 }  // namespace
@@ -341,7 +362,7 @@ AttnPlan attn_plan(const tsb_ctx* ctx, const tsb_kv* kv, int rows, int rows_per_
     const int groups = rows / rows_per_seq;
     const int tiles_total = (max_len + TILE_TOKENS - 1) / TILE_TOKENS;
     const int base_ctas = groups * kv->view.kv_heads * n_qpairs;
-    int splits = (2 * ctx->sm_count + base_ctas - 1) / base_ctas;
+    int splits = (ctx->sm_count * 5 / 4 + base_ctas - 1) / base_ctas;  // about 1.25 CTAs per SM in total
     splits = splits < 1 ? 1 : splits;
     if (splits > MAX_SPLITS) splits = MAX_SPLITS;
     if (splits > tiles_total) splits = tiles_total > 0 ? tiles_total : 1;
@@ -355,46 +376,44 @@ AttnPlan attn_plan(const tsb_ctx* ctx, const tsb_kv* kv, int rows, int rows_per_
 }
 
 size_t attn_scratch_bytes(int rows, int n_q_heads, int head_dim) {
-    return (size_t)rows * n_q_heads * MAX_SPLITS * ((size_t)head_dim * sizeof(float) + sizeof(float2));
+    // chunk partials (O and (m, l)) plus one ticket word per (stream, kv head, query tile), which is at most
+    // rows * n_q_heads words; the tickets must be zero before the first launch and reset themselves
+    return (size_t)rows * n_q_heads * MAX_SPLITS * ((size_t)head_dim * sizeof(float) + sizeof(float2)) +
+           (size_t)rows * n_q_heads * sizeof(uint32_t);
 }
 
 cudaError_t launch_attn_decode_rows(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, int layer, const __half* q, int64_t q_stride,
                                     __half* out, ActOut act, const tsb_row_desc* rows_dev, int rows, int rows_per_seq,
-                                    int n_q_heads, float scale, int max_len, void* scratch) {
+                                    int n_q_heads, float scale, int max_len, void* scratch, int rows_cap) {
     const AttnPlan p = attn_plan(ctx, kv, rows, rows_per_seq, n_q_heads, max_len);
     const int hd = kv->view.head_dim;
     float* part_o = reinterpret_cast<float*>(scratch);
     float2* part_ml = reinterpret_cast<float2*>(part_o + (size_t)rows * n_q_heads * p.n_splits * hd);
+    // tickets sit at the very end of the scratch area, whatever the split count of this call
+    uint32_t* tickets = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(scratch) +
+                                                    (size_t)rows_cap * n_q_heads * MAX_SPLITS * ((size_t)hd * sizeof(float) + sizeof(float2)));
     const float scale_log2e = scale * 1.4426950408889634f;
     dim3 grid((unsigned)p.n_splits, (unsigned)(kv->view.kv_heads * p.n_qpairs), (unsigned)p.groups);
-    const size_t smem = (size_t)2 * 2 * TILE_TOKENS * hd * sizeof(__half);
-    cudaError_t e;
+    const size_t smem = (size_t)NST * 2 * TILE_TOKENS * hd * sizeof(__half);
     static bool configured[2] = {false, false};
     if (hd == 128) {
         if (!configured[1]) {
-            e = cudaFuncSetAttribute(attn_partial_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return e;
             configured[1] = true;
         }
-        e = tsb_launch(ctx, attn_partial_kernel<128>, grid, dim3(ATT_THREADS), smem, st, true, kv->view, layer, q, q_stride,
-                       rows_dev, rows_per_seq, n_q_heads, scale_log2e, p.chunk, p.n_splits, part_o, part_ml, ctx->dev_error);
-    } else {
-        if (!configured[0]) {
-            e = cudaFuncSetAttribute(attn_partial_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return e;
-            configured[0] = true;
-        }
-        e = tsb_launch(ctx, attn_partial_kernel<64>, grid, dim3(ATT_THREADS), smem, st, true, kv->view, layer, q, q_stride,
-                       rows_dev, rows_per_seq, n_q_heads, scale_log2e, p.chunk, p.n_splits, part_o, part_ml, ctx->dev_error);
+        return tsb_launch(ctx, attn_partial_kernel<128>, grid, dim3(ATT_THREADS), smem, st, true, kv->view, layer, q, q_stride,
+                          rows_dev, rows_per_seq, n_q_heads, scale_log2e, p.chunk, p.n_splits, part_o, part_ml, tickets, out, act,
+                          ctx->dev_error);
     }
-    if (e != cudaSuccess) return e;
-    const int64_t threads = (int64_t)rows * n_q_heads * (hd / 8);
-    dim3 mgrid((unsigned)((threads + 127) / 128));
-    if (hd == 128)
-        return tsb_launch(ctx, attn_merge_kernel<128>, mgrid, dim3(128), 0, st, true, (const float*)part_o,
-                          (const float2*)part_ml, rows_dev, rows, rows_per_seq, n_q_heads, p.chunk, p.n_splits, out, act);
-    return tsb_launch(ctx, attn_merge_kernel<64>, mgrid, dim3(128), 0, st, true, (const float*)part_o,
-                      (const float2*)part_ml, rows_dev, rows, rows_per_seq, n_q_heads, p.chunk, p.n_splits, out, act);
+    if (!configured[0]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured[0] = true;
+    }
+    return tsb_launch(ctx, attn_partial_kernel<64>, grid, dim3(ATT_THREADS), smem, st, true, kv->view, layer, q, q_stride,
+                      rows_dev, rows_per_seq, n_q_heads, scale_log2e, p.chunk, p.n_splits, part_o, part_ml, tickets, out, act,
+                      ctx->dev_error);
 }
 
 extern "C" {
@@ -422,9 +441,13 @@ int32_t tsb_attn_decode_rows(tsb_ctx* ctx, tsb_stream s, tsb_kv* kv, int32_t lay
                 (long long)kv->view.max_pages_per_seq * kv->view.page_tokens);
     TSB_REQUIRE(ctx, scratch_bytes >= attn_scratch_bytes(rows, n_q_heads, kv->view.head_dim), "scratch too small");
     DeviceGuard g(ctx);
+    // the ticket words at the end of the caller's scratch are not known to be zero
+    TSB_CUDA(ctx, cudaMemsetAsync(reinterpret_cast<uint8_t*>(scratch) + attn_scratch_bytes(rows, n_q_heads, kv->view.head_dim) -
+                                      (size_t)rows * n_q_heads * sizeof(uint32_t),
+                                  0, (size_t)rows * n_q_heads * sizeof(uint32_t), (cudaStream_t)s));
     TSB_CUDA(ctx, launch_attn_decode_rows(ctx, (cudaStream_t)s, kv, layer, (const __half*)q_f16, q_stride, (__half*)out_f16,
                                           ActOut{nullptr, nullptr}, rows_dev, rows, rows_per_seq, n_q_heads, scale, max_len,
-                                          scratch));
+                                          scratch, rows));
     return TSB_OK;
 }
 

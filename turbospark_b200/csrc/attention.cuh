@@ -11,9 +11,10 @@ struct AttnPlan {
 };
 AttnPlan attn_plan(const tsb_ctx* ctx, const tsb_kv* kv, int rows, int rows_per_seq, int n_q_heads, int max_len);
 size_t attn_scratch_bytes(int rows, int n_q_heads, int head_dim);
-// out (natural f16 rows, may be null) and/or act (matmul operand) receive the attention output.
+// out (natural f16 rows, may be null) and/or act (matmul operand) receive the attention output.  scratch was sized
+// by attn_scratch_bytes(rows_cap, ...) and its trailing ticket words are zero (they reset themselves).
 cudaError_t launch_attn_decode_rows(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, int layer, const __half* q, int64_t q_stride,
                                     __half* out, ActOut act, const tsb_row_desc* rows_dev, int rows, int rows_per_seq,
-                                    int n_q_heads, float scale, int max_len, void* scratch);
+                                    int n_q_heads, float scale, int max_len, void* scratch, int rows_cap);
 cudaError_t launch_rope_store_kv(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, int layer, __half* qkv,
                                  const tsb_row_desc* rows_dev, int rows, int n_q_heads, float theta);

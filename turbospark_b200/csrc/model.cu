@@ -320,6 +320,7 @@ static int32_t runtime_init(tsb_session* s, ModelRt& rt, const tsb_model* model,
     cudaMemset(rt.act_f.xs, 0, act_xs_bytes(Rp, c.ffn));
     rt.attn_scratch_bytes = attn_scratch_bytes(R, c.n_q_heads, c.head_dim);
     if ((rc = A(rt.attn_scratch_bytes, &rt.attn_scratch))) return rc;
+    cudaMemset(rt.attn_scratch, 0, rt.attn_scratch_bytes);  // the ticket words start at zero
     rt.fed.assign(n_streams, std::vector<int32_t>());
     return TSB_OK;
 }
@@ -360,7 +361,7 @@ static cudaError_t forward_device(tsb_session* s, ModelRt& rt, const int32_t* to
             FW(launch_gemm_fused(ctx, st, l.wqkv.qtype, l.wqkv.data, l.wqkv.rows, l.wqkv.cols, in_d, rows, EPI_ROPE_STORE, a));
         }
         FW(launch_attn_decode_rows(ctx, st, rt.kv, L, rt.q, (int64_t)c.n_q_heads * c.head_dim, nullptr, out_o, rows_dev, rows,
-                                   rows_per_seq, c.n_q_heads, scale, max_len, rt.attn_scratch));
+                                   rows_per_seq, c.n_q_heads, scale, max_len, rt.attn_scratch, s->n_streams * s->max_rows));
         {   // o_proj; epilogue: residual add, next operand f16(h * g_ffn), partial sums of h^2
             EpiArgs a;
             a.h = rt.h, a.g = l.ffn_norm, a.out = out_d, a.ss_out = ss_slot(2 * L + 1);
