@@ -205,6 +205,26 @@ TSB_API int32_t tsb_attn_decode_rows(tsb_ctx* ctx, tsb_stream s, tsb_kv* kv, int
                                      void* scratch, size_t scratch_bytes);
 TSB_API size_t tsb_attn_scratch_bytes(int32_t rows, int32_t n_q_heads, int32_t head_dim);
 
+/* The same attention for callers that cannot supply scratch memory: a binding that owns no device
+ * allocator (it only forwards buffers it was handed), or a caller that must not allocate where the
+ * call sits.  It has no counterpart in the reference, whose encoders always take caller buffers.
+ * The chunk partials go to a fixed area of TSB_ATTN_STATIC_SCRATCH_BYTES that is part of the loaded
+ * library, one copy per device; the call allocates nothing, on the host's heap or on the device.
+ *  - A shape needing more than that (tsb_attn_scratch_bytes(rows, n_q_heads, head_dim) bytes) is
+ *    refused with TSB_ERR_INVALID and a message naming both sizes; nothing is launched.
+ *  - The first call on each device looks the area's address up once; make that call before any
+ *    stream capture is begun on that device.
+ *  - All calls on a device share the one area and it keeps what the previous call left.  The
+ *    call clears the words that must start at zero itself, in stream order.  Two calls that may
+ *    overlap in time (different streams, different threads) race on the area: keep such calls on
+ *    one stream, or use tsb_attn_decode_rows with separate buffers.
+ * Results equal tsb_attn_decode_rows on the same inputs. */
+#define TSB_ATTN_STATIC_SCRATCH_BYTES (8u << 20)
+TSB_API int32_t tsb_attn_decode_rows_static(tsb_ctx* ctx, tsb_stream s, tsb_kv* kv, int32_t layer, const void* q_f16,
+                                            int64_t q_stride, void* out_f16, const tsb_row_desc* rows_dev,
+                                            int32_t rows, int32_t rows_per_seq, int32_t n_q_heads, float scale,
+                                            int32_t max_len);
+
 /* In-place compaction of an accepted tree path: for every layer and for K and V, row base+r <- row
  * base+path[r], r < keep.  path[0] must be 0 and path strictly increasing (so path[r] >= r): the only
  * shape for which an in-place gather is race-free.  Replaces encode_gather_rows_fp16 driven by

@@ -204,6 +204,13 @@ class Ctx:
                                               C.c_int32(n_q_heads), C.c_float(scale), C.c_int32(max_len), _vp(scratch),
                                               C.c_size_t(scratch.nbytes)))
 
+    def attn_decode_rows_static(self, kv, layer, q, q_stride, out, rows_dev, rows, rows_per_seq, n_q_heads, scale, max_len,
+                                stream=None):
+        """tsb_attn_decode_rows with the library's built-in scratch area (no buffer argument, no allocation)."""
+        self.check(lib().tsb_attn_decode_rows_static(self.h, stream, kv.h, C.c_int32(layer), _vp(q), C.c_int64(q_stride),
+                                                     _vp(out), _vp(rows_dev), C.c_int32(rows), C.c_int32(rows_per_seq),
+                                                     C.c_int32(n_q_heads), C.c_float(scale), C.c_int32(max_len)))
+
     def accept_scratch_bytes(self, batch, k, vocab):
         return int(lib().tsb_accept_scratch_bytes(C.c_int32(batch), C.c_int32(k), C.c_int32(vocab)))
 

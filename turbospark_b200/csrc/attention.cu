@@ -21,6 +21,7 @@
 // the row's 128-bit mask is set (a chain row m has bits 0..m, a tree row its
 // root path).  HBM-bound: bytes = context * kv_heads * head_dim * 2 (K and V) * 2 B per layer.
 #include "attention.cuh"
+#include <mutex>
 
 namespace {
 
@@ -449,6 +450,55 @@ int32_t tsb_attn_decode_rows(tsb_ctx* ctx, tsb_stream s, tsb_kv* kv, int32_t lay
                                           ActOut{nullptr, nullptr}, rows_dev, rows, rows_per_seq, n_q_heads, scale, max_len,
                                           scratch, rows));
     return TSB_OK;
+}
+
+
+// ---- attention without a scratch argument ---------------------------------------------------------------
+// Some callers cannot hand over a scratch buffer: a host that owns no device allocator of its own (an FFI
+// binding that only forwards the buffers it was given), or one that must not allocate at the point of the
+// call (inside a latency-critical loop where an allocation could block on other work of the device).  For
+// them the chunk partials live in a fixed array that is part of the loaded module.
+namespace {
+constexpr size_t ATTN_STATIC_BYTES = TSB_ATTN_STATIC_SCRATCH_BYTES;
+__device__ __align__(256) unsigned char g_attn_static_scratch[ATTN_STATIC_BYTES];
+constexpr int ATTN_STATIC_MAX_DEVICES = 64;
+void* g_attn_static_ptr[ATTN_STATIC_MAX_DEVICES] = {};  // per device: address of its copy of the array
+std::mutex g_attn_static_mutex;
+
+// Address of the array on the context's device (which must be current).  The first call per device asks the
+// runtime for it; later calls read the table.
+cudaError_t attn_static_scratch(const tsb_ctx* ctx, void** out) {
+    if (ctx->device < 0 || ctx->device >= ATTN_STATIC_MAX_DEVICES) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_attn_static_mutex);
+    void*& slot = g_attn_static_ptr[ctx->device];
+    if (!slot) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_attn_static_scratch);
+        if (e != cudaSuccess) return e;
+        slot = p;
+    }
+    *out = slot;
+    return cudaSuccess;
+}
+}  // namespace
+
+int32_t tsb_attn_decode_rows_static(tsb_ctx* ctx, tsb_stream s, tsb_kv* kv, int32_t layer, const void* q_f16,
+                                    int64_t q_stride, void* out_f16, const tsb_row_desc* rows_dev, int32_t rows,
+                                    int32_t rows_per_seq, int32_t n_q_heads, float scale, int32_t max_len) {
+    if (!ctx || !kv) return TSB_ERR_INVALID;
+    TSB_REQUIRE(ctx, rows > 0 && n_q_heads > 0, "rows and n_q_heads must be positive");
+    const size_t need = attn_scratch_bytes(rows, n_q_heads, kv->view.head_dim);
+    if (need > ATTN_STATIC_BYTES)
+        return tsb_fail(ctx, TSB_ERR_INVALID,
+                        "tsb_attn_decode_rows_static: %d rows x %d heads x head_dim %d need %zu bytes of scratch, the built-in "
+                        "area holds %zu; use tsb_attn_decode_rows with a caller buffer",
+                        rows, n_q_heads, kv->view.head_dim, need, (size_t)ATTN_STATIC_BYTES);
+    DeviceGuard g(ctx);
+    void* scratch = nullptr;
+    TSB_CUDA(ctx, attn_static_scratch(ctx, &scratch));
+    // same checks, same ticket clearing, same kernel as the entry point with a caller buffer
+    return tsb_attn_decode_rows(ctx, s, kv, layer, q_f16, q_stride, out_f16, rows_dev, rows, rows_per_seq, n_q_heads, scale,
+                                max_len, scratch, need);
 }
 
 }  // extern "C"
