@@ -21,7 +21,9 @@
 // the row's 128-bit mask is set (a chain row m has bits 0..m, a tree row its
 // root path).  HBM-bound: bytes = context * kv_heads * head_dim * 2 (K and V) * 2 B per layer.
 #include "attention.cuh"
+#include <cooperative_groups.h>
 #include <mutex>
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -29,6 +31,7 @@ constexpr int ATT_THREADS = 128;
 constexpr int TILE_TOKENS = 64;
 constexpr int MAX_SPLITS = 64;
 constexpr int NST = 3;  // K/V tile stages in shared memory
+constexpr int ATTN_MAX_DEVICES = 64;
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -51,44 +54,91 @@ __device__ __forceinline__ uint32_t tile_off(int r, int c) {
     return (uint32_t)(r * (HD * 2) + ((c ^ (r & 7)) << 4));
 }
 
-template <int HD>
-__global__ void __launch_bounds__(ATT_THREADS)
+// MT = query m-tiles per CTA (1 -> 16 queries, 4 warps; 2 -> 32 queries, 8 warps).  Whatever MT is, a warp owns one
+// m-tile and one 16-token slice of every 64-token tile, so the arithmetic done for a query - the order of its
+// running maxima, sums and merges - does not depend on how many other rows are in flight: a row verified in a
+// batch of six comes out bit-identical to the same row decoded alone.
+// Grid: x = KV chunks (a multiple of the cluster size; the CTAs of a cluster hold consecutive chunks of the same
+// queries), y = kv head * query tiles, z = streams.
+template <int HD, int MT>
+__global__ void __launch_bounds__(ATT_THREADS * MT)
     attn_partial_kernel(KvView kv, int layer, const __half* __restrict__ q, int64_t q_stride,
                         const tsb_row_desc* __restrict__ rows, int rows_per_seq, int n_q_heads, float scale_log2e,
-                        int chunk, int n_splits, float* __restrict__ part_o, float2* __restrict__ part_ml,
+                        int chunk, int cluster_size, float* __restrict__ part_o, float2* __restrict__ part_ml,
                         uint32_t* __restrict__ tickets, __half* __restrict__ out, ActOut act, uint32_t* __restrict__ err) {
-    constexpr int CH = HD / 8;    // 16-byte chunks per token row
-    constexpr int KS = HD / 16;   // k steps of S = Q K^T
-    constexpr int NO = HD / 8;    // n tiles of O
+    constexpr int CH = HD / 8;         // 16-byte chunks per token row
+    constexpr int KS = HD / 16;        // k steps of S = Q K^T
+    constexpr int NO = HD / 8;         // n tiles of O
+    constexpr int QT = 16 * MT;        // queries per CTA
+    constexpr int NTHR = ATT_THREADS * MT;
+    constexpr int SL = 4;              // token slices of a tile (one per warp of an m-tile)
+    constexpr int WTOK = TILE_TOKENS / SL;  // tokens of a tile one warp covers
+    constexpr int NT8 = WTOK / 8, KK = WTOK / 16;
     constexpr int TILE_BYTES = TILE_TOKENS * HD * 2;
-    extern __shared__ __align__(128) uint8_t smem[];  // [NST stages][K tile | V tile]
+    extern __shared__ __align__(128) uint8_t smem[];  // [NST stages][K tile | V tile]; later the warps' partials
     __shared__ int s_last;
+    cg::cluster_group cluster = cg::this_cluster();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tig = lane & 3;
-    const int mt = warp >> 1, th = warp & 1;
+    const int mt = warp % MT, sl = warp / MT;
     const int nkv = kv.kv_heads, G = n_q_heads / nkv;
     const int n_queries = rows_per_seq * G;
-    const int n_qpairs = (n_queries + 31) / 32;
+    const int n_qtiles = (n_queries + QT - 1) / QT;
     const int split = blockIdx.x;
-    const int kvh = blockIdx.y / n_qpairs, qpair = blockIdx.y % n_qpairs;
+    const int kvh = blockIdx.y / n_qtiles, qtile = blockIdx.y % n_qtiles;
     const int row_first = blockIdx.z * rows_per_seq;
 
-    pdl_wait();
+    // The row descriptors and page table were written before the pass began and cache rows below `base` in
+    // earlier passes, so they may be touched before the preceding kernel has finished.
     const tsb_row_desc rd0 = rows[row_first];
     const int seq = rd0.seq, base = rd0.base;
     const int L = base + rows_per_seq;
     const int t_begin = split * chunk;
     const int t_end = min(L, t_begin + chunk);
-    if (t_begin >= t_end) return;  // the merge kernel knows how many chunks this stream has
-    if (seq < 0 || seq >= kv.max_seqs) {
+    if (seq < 0 || seq >= kv.max_seqs) {  // the same for every CTA of the cluster: all leave together
         if (threadIdx.x == 0) atomicCAS(err, 0u, (uint32_t)TSB_DEV_BAD_INDEX);
         return;
     }
-    const int n_tiles = (t_end - t_begin + TILE_TOKENS - 1) / TILE_TOKENS;
+    const int n_tiles = t_end > t_begin ? (t_end - t_begin + TILE_TOKENS - 1) / TILE_TOKENS : 0;
+
+    const uint32_t smem_base = smem_u32(smem);
+    // a thread copies half a token row (K and V) of every tile: one page-table lookup per thread per tile
+    auto issue_tile = [&](int tile, int stage) {
+        const int t0 = t_begin + tile * TILE_TOKENS;
+        const uint32_t kdst = smem_base + stage * 2 * TILE_BYTES, vdst = kdst + TILE_BYTES;
+        constexpr int TPR = NTHR / TILE_TOKENS;  // threads sharing a token row
+        const int r = threadIdx.x / TPR, c0 = (threadIdx.x % TPR) * (CH / TPR);
+        const int pos = t0 + r;
+        const bool valid = pos < t_end;
+        const __half* kr = valid ? kv_row(kv, layer, 0, seq, pos) : nullptr;
+        const bool ok = kr != nullptr;
+        const __half* ksrc = ok ? kr + (size_t)kvh * HD : kv.pool;
+        const __half* vsrc = ok ? ksrc + kv.kv_stride : kv.pool;  // V sits one kv_stride after K in the same layer
+#pragma unroll
+        for (int i = 0; i < CH / TPR; i++) {
+            const int c = c0 + i;
+            const uint32_t off = tile_off<HD>(r, c);
+            cp_async16_zfill(kdst + off, ok ? (const void*)(ksrc + c * 8) : (const void*)kv.pool, ok);
+            cp_async16_zfill(vdst + off, ok ? (const void*)(vsrc + c * 8) : (const void*)kv.pool, ok);
+        }
+        cp_async_commit();
+    };
+    auto prologue = [&]() {  // every stage of the ring starts filled
+#pragma unroll
+        for (int i = 0; i < NST; i++) {
+            if (i < n_tiles) issue_tile(i, i);
+            else cp_async_commit();
+        }
+    };
+    // tiles made only of committed rows can start moving while the kernel that produces q is still running
+    const bool early = t_begin + NST * TILE_TOKENS <= base;
+    if (early) prologue();
+    pdl_wait();
+    if (!early) prologue();
 
     // ---- this lane's two queries (rows gid and gid+8 of the warp's mma tile)
-    const int q0 = qpair * 32 + mt * 16 + gid, q1 = q0 + 8;
+    const int q0 = qtile * QT + mt * 16 + gid, q1 = q0 + 8;
     const bool v0 = q0 < n_queries, v1 = q1 < n_queries;
     const int r0 = v0 ? q0 / G : 0, r1 = v1 ? q1 / G : 0;
     const int h0 = kvh * G + (v0 ? q0 % G : 0), h1 = kvh * G + (v1 ? q1 % G : 0);
@@ -116,52 +166,23 @@ __global__ void __launch_bounds__(ATT_THREADS)
         for (int i = 0; i < 4; i++) o[n][i] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
-    const uint32_t smem_base = smem_u32(smem);
-    // a thread copies half a token row (K and V) of every tile: one page-table lookup per thread per tile
-    auto issue_tile = [&](int tile, int stage) {
-        const int t0 = t_begin + tile * TILE_TOKENS;
-        const uint32_t kdst = smem_base + stage * 2 * TILE_BYTES, vdst = kdst + TILE_BYTES;
-        const int r = threadIdx.x >> 1, c0 = (threadIdx.x & 1) * (CH / 2);
-        const int pos = t0 + r;
-        const bool valid = pos < t_end;
-        const __half* kr = valid ? kv_row(kv, layer, 0, seq, pos) : nullptr;
-        const bool ok = kr != nullptr;
-        const __half* ksrc = ok ? kr + (size_t)kvh * HD : kv.pool;
-        const __half* vsrc = ok ? ksrc + kv.kv_stride : kv.pool;  // V sits one kv_stride after K in the same layer
-#pragma unroll
-        for (int i = 0; i < CH / 2; i++) {
-            const int c = c0 + i;
-            const uint32_t off = tile_off<HD>(r, c);
-            cp_async16_zfill(kdst + off, ok ? (const void*)(ksrc + c * 8) : (const void*)kv.pool, ok);
-            cp_async16_zfill(vdst + off, ok ? (const void*)(vsrc + c * 8) : (const void*)kv.pool, ok);
-        }
-        cp_async_commit();
-    };
-
-    // NST-deep cp.async pipeline: NST - 1 tiles in flight while one is consumed
-#pragma unroll
-    for (int i = 0; i < NST - 1; i++) {
-        if (i < n_tiles) issue_tile(i, i);
-        else cp_async_commit();
-    }
+    // NST-deep cp.async ring: a stage is refilled as soon as every warp is done with it
     for (int tile = 0; tile < n_tiles; tile++) {
         const int stage = tile % NST;
-        if (tile + NST - 1 < n_tiles) issue_tile(tile + NST - 1, (tile + NST - 1) % NST);
-        else cp_async_commit();
-        cp_async_wait<NST - 1>();
+        cp_async_wait<NST - 1>();  // all but the NST - 1 youngest groups have landed: tile `tile` is here
         __syncthreads();
         const uint32_t ktile = smem_base + stage * 2 * TILE_BYTES, vtile = ktile + TILE_BYTES;
-        const int tok0 = th * 32;  // this warp's 32 tokens of the tile
+        const int tok0 = sl * WTOK;  // this warp's tokens of the tile
         const int pos0 = t_begin + tile * TILE_TOKENS + tok0;
 
-        // ---- S = Q K^T for 16 queries x 32 tokens
-        float s[4][4];
+        // ---- S = Q K^T for 16 queries x WTOK tokens
+        float s[NT8][4];
 #pragma unroll
-        for (int nt = 0; nt < 4; nt++)
+        for (int nt = 0; nt < NT8; nt++)
 #pragma unroll
             for (int i = 0; i < 4; i++) s[nt][i] = 0.f;
 #pragma unroll
-        for (int nt = 0; nt < 4; nt++) {
+        for (int nt = 0; nt < NT8; nt++) {
 #pragma unroll
             for (int kp = 0; kp < KS / 2; kp++) {
                 uint32_t b[4];
@@ -174,10 +195,10 @@ __global__ void __launch_bounds__(ATT_THREADS)
             }
         }
         // ---- scale, mask, online softmax
-        const bool need_mask = pos0 + 32 > base;
+        const bool need_mask = pos0 + WTOK > base;
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int nt = 0; nt < 4; nt++)
+        for (int nt = 0; nt < NT8; nt++)
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 float v = s[nt][i] * scale_log2e;
@@ -205,9 +226,9 @@ __global__ void __launch_bounds__(ATT_THREADS)
             m_run[h] = m_new;
         }
         float rs[2] = {0.f, 0.f};
-        uint32_t pa[2][4];
+        uint32_t pa[KK][4];
 #pragma unroll
-        for (int nt = 0; nt < 4; nt++) {
+        for (int nt = 0; nt < NT8; nt++) {
             const float p0 = exp2f(s[nt][0] - m_use[0]), p1 = exp2f(s[nt][1] - m_use[0]);
             const float p2 = exp2f(s[nt][2] - m_use[1]), p3 = exp2f(s[nt][3] - m_use[1]);
             rs[0] += p0 + p1;
@@ -230,7 +251,7 @@ __global__ void __launch_bounds__(ATT_THREADS)
         }
         // ---- O += P V
 #pragma unroll
-        for (int kk = 0; kk < 2; kk++) {
+        for (int kk = 0; kk < KK; kk++) {
 #pragma unroll
             for (int np = 0; np < NO / 2; np++) {
                 uint32_t b[4];
@@ -242,137 +263,257 @@ __global__ void __launch_bounds__(ATT_THREADS)
                 mma_16816(o[2 * np + 1], pa[kk], b23);
             }
         }
-        __syncthreads();  // both stages are rewritten only after every warp is done with this one
+        __syncthreads();  // a stage is rewritten only after every warp is done with it
+        if (tile + NST < n_tiles) issue_tile(tile + NST, stage);
+        else cp_async_commit();
     }
+    cp_async_wait<0>();
     pdl_launch_dependents();
 
-    // ---- merge the two token halves of each query tile, then write the partial
-    float* mbuf = reinterpret_cast<float*>(smem);  // [2 tiles][32 lanes][NO*4 + 4]
-    constexpr int MB = NO * 4 + 4;
-    if (th == 1) {
-        float* dst = mbuf + ((size_t)mt * 32 + lane) * MB;
-#pragma unroll
-        for (int n = 0; n < NO; n++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) dst[n * 4 + i] = o[n][i];
-        dst[NO * 4 + 0] = m_run[0];
-        dst[NO * 4 + 1] = m_run[1];
-        dst[NO * 4 + 2] = l_run[0];
-        dst[NO * 4 + 3] = l_run[1];
-    }
-    __syncthreads();
-    if (th == 0) {
-        const float* src = mbuf + ((size_t)mt * 32 + lane) * MB;
-        float wa[2], wb[2], m_out[2], l_out[2];
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const float mb = src[NO * 4 + h], lb = src[NO * 4 + 2 + h];
-            const float m_new = fmaxf(m_run[h], mb);
-            const float mu = (m_new == -INFINITY) ? 0.f : m_new;
-            wa[h] = exp2f(m_run[h] - mu);
-            wb[h] = exp2f(mb - mu);
-            m_out[h] = m_new;
-            l_out[h] = l_run[h] * wa[h] + lb * wb[h];
-        }
-        const size_t i0 = ((size_t)(row_first + r0) * n_q_heads + h0) * n_splits + split;
-        const size_t i1 = ((size_t)(row_first + r1) * n_q_heads + h1) * n_splits + split;
+    // ---- every warp leaves its (m, l, O) for its 16 queries in shared memory: wo[warp][16][HD], wml[warp][16]
+    float* wo = reinterpret_cast<float*>(smem);
+    float2* wml = reinterpret_cast<float2*>(smem + (size_t)4 * MT * 16 * HD * sizeof(float));
+    {
+        float* dst = wo + (size_t)warp * 16 * HD;
 #pragma unroll
         for (int n = 0; n < NO; n++) {
-            const float a0 = o[n][0] * wa[0] + src[n * 4 + 0] * wb[0], a1 = o[n][1] * wa[0] + src[n * 4 + 1] * wb[0];
-            const float a2 = o[n][2] * wa[1] + src[n * 4 + 2] * wb[1], a3 = o[n][3] * wa[1] + src[n * 4 + 3] * wb[1];
-            if (v0) *reinterpret_cast<float2*>(part_o + i0 * HD + n * 8 + 2 * tig) = make_float2(a0, a1);
-            if (v1) *reinterpret_cast<float2*>(part_o + i1 * HD + n * 8 + 2 * tig) = make_float2(a2, a3);
+            *reinterpret_cast<float2*>(dst + gid * HD + n * 8 + 2 * tig) = make_float2(o[n][0], o[n][1]);
+            *reinterpret_cast<float2*>(dst + (gid + 8) * HD + n * 8 + 2 * tig) = make_float2(o[n][2], o[n][3]);
         }
         if (tig == 0) {
-            if (v0) part_ml[i0] = make_float2(m_out[0], l_out[0]);
-            if (v1) part_ml[i1] = make_float2(m_out[1], l_out[1]);
+            wml[warp * 16 + gid] = make_float2(m_run[0], l_run[0]);
+            wml[warp * 16 + gid + 8] = make_float2(m_run[1], l_run[1]);
         }
     }
+    __syncthreads();
 
-    // ---- the last CTA of this (stream, kv head, query tile) to finish merges the chunk partials:
-    // out = sum_c O_c 2^(m_c - m) / sum_c l_c 2^(m_c - m)   (crates/gpu/src/shaders/attention.metal:983-1031).
-    // A ticket counter decides who is last; nobody waits on anybody.
-    const int ns = min(n_splits, (L + chunk - 1) / chunk);  // chunks that exist for this stream
-    const int ticket_id = (blockIdx.z * nkv + kvh) * n_qpairs + qpair;
+    // ---- merges:  out = sum_c O_c 2^(m_c - m) / sum_c l_c 2^(m_c - m)   (crates/gpu/src/shaders/attention.metal:983-1031)
+    // first the four token slices inside the CTA, then the CTAs of the cluster through distributed shared memory,
+    // then (if the context needed more than one cluster) the clusters through memory.  A thread owns a run of
+    // eight columns of one query.
+    constexpr int TPH = HD / 8;             // 8-column runs per head
+    constexpr int QPP = NTHR / TPH;         // queries finished per pass over the threads
+    float* co = wo + (size_t)4 * MT * 16 * HD + 2 * 4 * MT * 16;  // [QT][HD] after wo and wml
+    float2* cml = reinterpret_cast<float2*>(co + (size_t)QT * HD);
+    const int part = threadIdx.x % TPH;
+#pragma unroll
+    for (int ql0 = 0; ql0 < QT; ql0 += QPP) {
+        const int ql = ql0 + threadIdx.x / TPH;
+        const int w0 = ql / 16, qq = ql % 16;  // warp (m-tile) and row that held the query
+        float m = -INFINITY, den = 0.f, accv[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) accv[i] = 0.f;
+#pragma unroll
+        for (int s2 = 0; s2 < SL; s2++) m = fmaxf(m, wml[(s2 * MT + w0) * 16 + qq].x);
+        const float mu = (m == -INFINITY) ? 0.f : m;
+#pragma unroll
+        for (int s2 = 0; s2 < SL; s2++) {
+            const int w = s2 * MT + w0;
+            const float2 v = wml[w * 16 + qq];
+            const float wgt = exp2f(v.x - mu);
+            den += v.y * wgt;
+            const float4* po = reinterpret_cast<const float4*>(wo + ((size_t)w * 16 + qq) * HD + part * 8);
+            const float4 a = po[0], b2 = po[1];
+            accv[0] += a.x * wgt, accv[1] += a.y * wgt, accv[2] += a.z * wgt, accv[3] += a.w * wgt;
+            accv[4] += b2.x * wgt, accv[5] += b2.y * wgt, accv[6] += b2.z * wgt, accv[7] += b2.w * wgt;
+        }
+        float4* dst = reinterpret_cast<float4*>(co + (size_t)ql * HD + part * 8);
+        dst[0] = make_float4(accv[0], accv[1], accv[2], accv[3]);
+        dst[1] = make_float4(accv[4], accv[5], accv[6], accv[7]);
+        if (part == 0) cml[ql] = make_float2(m, den);
+    }
+    if (cluster_size > 1) cluster.sync();
+    else __syncthreads();
+
+    // CTA `rank` of the cluster finishes queries rank, rank + cluster_size, ... of the tile
+    const int rank = cluster_size > 1 ? (int)cluster.block_rank() : 0;
+    const int n_clusters = gridDim.x / cluster_size, cl = blockIdx.x / cluster_size;
+    const int n_own = (QT - rank + cluster_size - 1) / cluster_size;  // queries rank, rank + cs, ... below QT
+    for (int j0 = 0; j0 < n_own; j0 += QPP) {  // uniform trip count per CTA
+        const int j = j0 + threadIdx.x / TPH;
+        const int ql = rank + j * cluster_size;  // query within the tile
+        const int qi = qtile * QT + ql;
+        const bool active = j < n_own && qi < n_queries;
+        float m = -INFINITY, den = 0.f, accv[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) accv[i] = 0.f;
+        if (active) {
+            float2 ml[8];
+            float4 va[8], vb[8];
+#pragma unroll
+            for (int c = 0; c < 8; c++)
+                if (c < cluster_size) {
+                    const float2* rml = cluster_size > 1 ? cluster.map_shared_rank(cml, c) : cml;
+                    const float* ro = cluster_size > 1 ? cluster.map_shared_rank(co, c) : co;
+                    ml[c] = rml[ql];
+                    const float4* po = reinterpret_cast<const float4*>(ro + (size_t)ql * HD + part * 8);
+                    va[c] = po[0], vb[c] = po[1];
+                }
+#pragma unroll
+            for (int c = 0; c < 8; c++)
+                if (c < cluster_size) m = fmaxf(m, ml[c].x);
+            const float mu = (m == -INFINITY) ? 0.f : m;
+#pragma unroll
+            for (int c = 0; c < 8; c++)
+                if (c < cluster_size) {
+                    const float wgt = exp2f(ml[c].x - mu);
+                    den += ml[c].y * wgt;
+                    accv[0] += va[c].x * wgt, accv[1] += va[c].y * wgt, accv[2] += va[c].z * wgt, accv[3] += va[c].w * wgt;
+                    accv[4] += vb[c].x * wgt, accv[5] += vb[c].y * wgt, accv[6] += vb[c].z * wgt, accv[7] += vb[c].w * wgt;
+                }
+        }
+        const int row = row_first + (active ? qi / G : 0), head = kvh * G + (active ? qi % G : 0);
+        const int e0 = head * HD + part * 8;
+        if (n_clusters == 1) {
+            const float inv = den > 0.f ? 1.0f / den : 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) accv[i] *= inv;
+            if (out && active) {
+                uint4 pk;
+                __half* pp = reinterpret_cast<__half*>(&pk);
+#pragma unroll
+                for (int i = 0; i < 8; i++) pp[i] = __float2half_rn(accv[i]);
+                *reinterpret_cast<uint4*>(out + (size_t)row * n_q_heads * HD + e0) = pk;
+            }
+            if (act.xp) act_store8(accv, act.xp, act.xs, row, e0, (n_q_heads * HD) >> 8, active);
+        } else if (active) {  // this cluster's share goes to memory; the last CTA of all clusters finishes the job
+            const size_t pi = ((size_t)row * n_q_heads + head) * n_clusters + cl;
+            float4* po = reinterpret_cast<float4*>(part_o + pi * HD + part * 8);
+            po[0] = make_float4(accv[0], accv[1], accv[2], accv[3]);
+            po[1] = make_float4(accv[4], accv[5], accv[6], accv[7]);
+            if (part == 0) part_ml[pi] = make_float2(m, den);
+        }
+    }
+    // nobody may leave while a neighbour still reads its shared memory
+    if (cluster_size > 1) cluster.sync();
+    if (n_clusters == 1) return;
+
+    // ---- the last CTA to finish among all clusters of this (stream, kv head, query tile) merges the clusters'
+    // shares.  A ticket counter decides who is last; nobody waits on anybody.
+    const int ticket_id = (blockIdx.z * nkv + kvh) * n_qtiles + qtile;
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
         const uint32_t old = atomicAdd(&tickets[ticket_id], 1u);
-        s_last = old == (uint32_t)(ns - 1);
+        s_last = old == gridDim.x - 1;
         if (s_last) tickets[ticket_id] = 0;  // ready for the next launch
     }
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    constexpr int TPH = HD / 8;     // 8-column runs per head
-    constexpr int SF = 32 / TPH;    // lanes sharing one run, each taking every SF-th chunk
-    const int part = lane % TPH, sidx = lane / TPH;
-    for (int qo = warp; qo < 32; qo += ATT_THREADS / 32) {
-        const int qi = qpair * 32 + qo;
-        if (qi >= n_queries) break;  // uniform per warp
-        const int row = row_first + qi / G, head = kvh * G + qi % G;
-        const size_t rh = (size_t)row * n_q_heads + head;
-        const float2* ml = part_ml + rh * n_splits;
-        // global max over the chunks: lanes stride over the chunk list, then a warp max
-        float m = -INFINITY;
-        for (int c = lane; c < ns; c += 32) m = fmaxf(m, __ldcg(&ml[c]).x);
-#pragma unroll
-        for (int o2 = 16; o2 > 0; o2 >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o2));
-        const float mu = (m == -INFINITY) ? 0.f : m;
-        float den = 0.f, accv[8];
+    for (int ql0 = 0; ql0 < QT; ql0 += QPP) {
+        const int ql = ql0 + threadIdx.x / TPH;
+        const int qi = qtile * QT + ql;
+        const bool active = ql < QT && qi < n_queries;
+        const int row = row_first + (active ? qi / G : 0), head = kvh * G + (active ? qi % G : 0);
+        const size_t pi = ((size_t)row * n_q_heads + head) * n_clusters;
+        float m = -INFINITY, den = 0.f, accv[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) accv[i] = 0.f;
+        if (active) {
+            for (int c = 0; c < n_clusters; c++) m = fmaxf(m, __ldcg(&part_ml[pi + c]).x);
+            const float mu = (m == -INFINITY) ? 0.f : m;
 #pragma unroll 4
-        for (int c = sidx; c < ns; c += SF) {
-            const float2 v = __ldcg(&ml[c]);
-            const float w = exp2f(v.x - mu);
-            den += v.y * w;
-            const float4* po = reinterpret_cast<const float4*>(part_o + (rh * n_splits + c) * HD + part * 8);
-            const float4 a = __ldcg(po), b2 = __ldcg(po + 1);
-            accv[0] += a.x * w, accv[1] += a.y * w, accv[2] += a.z * w, accv[3] += a.w * w;
-            accv[4] += b2.x * w, accv[5] += b2.y * w, accv[6] += b2.z * w, accv[7] += b2.w * w;
-        }
-#pragma unroll
-        for (int o2 = TPH; o2 < 32; o2 <<= 1) {
-            den += __shfl_xor_sync(0xffffffffu, den, o2);
-#pragma unroll
-            for (int i = 0; i < 8; i++) accv[i] += __shfl_xor_sync(0xffffffffu, accv[i], o2);
+            for (int c = 0; c < n_clusters; c++) {
+                const float2 v = __ldcg(&part_ml[pi + c]);
+                const float wgt = exp2f(v.x - mu);
+                den += v.y * wgt;
+                const float4* po = reinterpret_cast<const float4*>(part_o + (pi + c) * HD + part * 8);
+                const float4 a = __ldcg(po), b2 = __ldcg(po + 1);
+                accv[0] += a.x * wgt, accv[1] += a.y * wgt, accv[2] += a.z * wgt, accv[3] += a.w * wgt;
+                accv[4] += b2.x * wgt, accv[5] += b2.y * wgt, accv[6] += b2.z * wgt, accv[7] += b2.w * wgt;
+            }
         }
         const float inv = den > 0.f ? 1.0f / den : 0.f;
 #pragma unroll
         for (int i = 0; i < 8; i++) accv[i] *= inv;
         const int e0 = head * HD + part * 8;
-        const bool writer = sidx == 0;  // lanes 0..TPH-1 hold the runs of this head in order
-        if (out && writer) {
+        if (out && active) {
             uint4 pk;
             __half* pp = reinterpret_cast<__half*>(&pk);
 #pragma unroll
             for (int i = 0; i < 8; i++) pp[i] = __float2half_rn(accv[i]);
             *reinterpret_cast<uint4*>(out + (size_t)row * n_q_heads * HD + e0) = pk;
         }
-        if (act.xp) act_store8(accv, act.xp, act.xs, row, e0, (n_q_heads * HD) >> 8, writer);
+        if (act.xp) act_store8(accv, act.xp, act.xs, row, e0, (n_q_heads * HD) >> 8, active);
     }
 }
 
 }  // namespace
 
+// How many clusters of `cs` CTAs of the kernel can be resident at once (cached per shape and device).
+template <int HD, int MT>
+static int max_clusters_t(int device, int cs) {
+    static int cache[ATTN_MAX_DEVICES][4] = {};
+    const int slot = cs == 8 ? 3 : cs == 4 ? 2 : cs == 2 ? 1 : 0;
+    if (device < 0 || device >= ATTN_MAX_DEVICES) return 0;
+    if (cache[device][slot]) return cache[device][slot];
+    const size_t smem = (size_t)NST * 2 * TILE_TOKENS * HD * sizeof(__half);
+    if (cudaFuncSetAttribute(attn_partial_kernel<HD, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cs * 64, 1, 1);
+    cfg.blockDim = dim3(ATT_THREADS * MT);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cs, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = cs > 1 ? 1 : 0;
+    int n = 0;
+    if (cs > 1) {
+        if (cudaOccupancyMaxActiveClusters(&n, attn_partial_kernel<HD, MT>, &cfg) != cudaSuccess) n = 0;
+    } else {
+        int per_sm = 0, sms = 0;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_partial_kernel<HD, MT>, ATT_THREADS * MT, smem);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        n = per_sm * sms;
+    }
+    cudaGetLastError();
+    cache[device][slot] = n > 0 ? n : 1;
+    return cache[device][slot];
+}
+static int max_clusters(int device, int hd, int mt, int cs) {
+    if (hd == 128) return mt == 2 ? max_clusters_t<128, 2>(device, cs) : max_clusters_t<128, 1>(device, cs);
+    return mt == 2 ? max_clusters_t<64, 2>(device, cs) : max_clusters_t<64, 1>(device, cs);
+}
+
 AttnPlan attn_plan(const tsb_ctx* ctx, const tsb_kv* kv, int rows, int rows_per_seq, int n_q_heads, int max_len) {
     AttnPlan p;
     const int G = n_q_heads / kv->view.kv_heads;
-    const int n_qpairs = (rows_per_seq * G + 31) / 32;
-    const int groups = rows / rows_per_seq;
-    const int tiles_total = (max_len + TILE_TOKENS - 1) / TILE_TOKENS;
-    const int base_ctas = groups * kv->view.kv_heads * n_qpairs;
-    int splits = (ctx->sm_count * 5 / 4 + base_ctas - 1) / base_ctas;  // about 1.25 CTAs per SM in total
-    splits = splits < 1 ? 1 : splits;
-    if (splits > MAX_SPLITS) splits = MAX_SPLITS;
-    if (splits > tiles_total) splits = tiles_total > 0 ? tiles_total : 1;
-    const int tiles_per = (tiles_total + splits - 1) / splits;
+    const int n_queries = rows_per_seq * G;
+    p.mt = n_queries <= 16 ? 1 : 2;
+    p.n_qtiles = (n_queries + 16 * p.mt - 1) / (16 * p.mt);
+    p.groups = rows / rows_per_seq;
+    // the split is planned for the length rounded up to 512, so calls whose lengths differ by a few rows (a row
+    // verified in a batch, then decoded alone) cut the context at the same places and sum in the same order
+    const int planned = max_len > 0 ? (max_len + 511) / 512 * 512 : 512;
+    const int tiles_total = planned / TILE_TOKENS;
+    const int base_ctas = p.groups * kv->view.kv_heads * p.n_qtiles;
+    // one wave: as many chunks per (stream, kv head, query tile) as the device can hold at once, in clusters of
+    // up to four CTAs (larger clusters leave SMs of a GPC unused)
+    int cand_splits[3] = {1, 1, 1}, most = 1;  // for cluster sizes 1, 2, 4
+    for (int i = 0; i < 3; i++) {
+        const int cs = 1 << i;
+        const int resident = max_clusters(ctx->device, kv->view.head_dim, p.mt, cs);  // clusters
+        int clusters_per = resident / base_ctas;                                        // per (stream, head, tile)
+        if (clusters_per < 1) clusters_per = 1;
+        if (clusters_per > MAX_SPLITS) clusters_per = MAX_SPLITS;
+        int splits = clusters_per * cs;
+        if (splits > tiles_total) splits = (tiles_total / cs) * cs;
+        cand_splits[i] = splits;  // 0 when a cluster would be longer than the context
+        if (splits > most) most = splits;
+    }
+    // the largest cluster that keeps at least 4/5 of the parallelism: fewer shares travel through memory
+    int best_splits = cand_splits[0] > 0 ? cand_splits[0] : 1, best_cs = 1;
+    for (int i = 2; i >= 1; i--)
+        if (cand_splits[i] * 5 >= most * 4 && cand_splits[i] > 0) {
+            best_splits = cand_splits[i], best_cs = 1 << i;
+            break;
+        }
+    p.cluster_size = best_cs;
+    p.n_splits = best_splits;
+    const int tiles_per = (tiles_total + p.n_splits - 1) / p.n_splits;
     p.chunk = (tiles_per < 1 ? 1 : tiles_per) * TILE_TOKENS;
-    p.n_splits = (max_len + p.chunk - 1) / p.chunk;
-    if (p.n_splits < 1) p.n_splits = 1;
-    p.n_qpairs = n_qpairs;
-    p.groups = groups;
     return p;
 }
 
@@ -383,38 +524,48 @@ size_t attn_scratch_bytes(int rows, int n_q_heads, int head_dim) {
            (size_t)rows * n_q_heads * sizeof(uint32_t);
 }
 
+template <int HD, int MT>
+static cudaError_t launch_attn_t(tsb_ctx* ctx, cudaStream_t st, const AttnPlan& p, dim3 grid, size_t smem, KvView view, int layer,
+                                 const __half* q, int64_t q_stride, const tsb_row_desc* rows_dev, int rows_per_seq,
+                                 int n_q_heads, float scale_log2e, float* part_o, float2* part_ml, uint32_t* tickets,
+                                 __half* out, ActOut act) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<HD, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    return tsb_launch_cluster(ctx, attn_partial_kernel<HD, MT>, grid, dim3(ATT_THREADS * MT), smem, st, true,
+                              (unsigned)p.cluster_size, view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
+                              scale_log2e, p.chunk, p.cluster_size, part_o, part_ml, tickets, out, act, ctx->dev_error);
+}
+
 cudaError_t launch_attn_decode_rows(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, int layer, const __half* q, int64_t q_stride,
                                     __half* out, ActOut act, const tsb_row_desc* rows_dev, int rows, int rows_per_seq,
                                     int n_q_heads, float scale, int max_len, void* scratch, int rows_cap) {
     const AttnPlan p = attn_plan(ctx, kv, rows, rows_per_seq, n_q_heads, max_len);
     const int hd = kv->view.head_dim;
+    const int n_clusters = p.n_splits / p.cluster_size;
     float* part_o = reinterpret_cast<float*>(scratch);
-    float2* part_ml = reinterpret_cast<float2*>(part_o + (size_t)rows * n_q_heads * p.n_splits * hd);
+    float2* part_ml = reinterpret_cast<float2*>(part_o + (size_t)rows * n_q_heads * n_clusters * hd);
     // tickets sit at the very end of the scratch area, whatever the split count of this call
     uint32_t* tickets = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(scratch) +
                                                     (size_t)rows_cap * n_q_heads * MAX_SPLITS * ((size_t)hd * sizeof(float) + sizeof(float2)));
     const float scale_log2e = scale * 1.4426950408889634f;
-    dim3 grid((unsigned)p.n_splits, (unsigned)(kv->view.kv_heads * p.n_qpairs), (unsigned)p.groups);
+    dim3 grid((unsigned)p.n_splits, (unsigned)(kv->view.kv_heads * p.n_qtiles), (unsigned)p.groups);
     const size_t smem = (size_t)NST * 2 * TILE_TOKENS * hd * sizeof(__half);
-    static bool configured[2] = {false, false};
     if (hd == 128) {
-        if (!configured[1]) {
-            cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return e;
-            configured[1] = true;
-        }
-        return tsb_launch(ctx, attn_partial_kernel<128>, grid, dim3(ATT_THREADS), smem, st, true, kv->view, layer, q, q_stride,
-                          rows_dev, rows_per_seq, n_q_heads, scale_log2e, p.chunk, p.n_splits, part_o, part_ml, tickets, out, act,
-                          ctx->dev_error);
+        if (p.mt == 2)
+            return launch_attn_t<128, 2>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
+                                         scale_log2e, part_o, part_ml, tickets, out, act);
+        return launch_attn_t<128, 1>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
+                                     scale_log2e, part_o, part_ml, tickets, out, act);
     }
-    if (!configured[0]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        configured[0] = true;
-    }
-    return tsb_launch(ctx, attn_partial_kernel<64>, grid, dim3(ATT_THREADS), smem, st, true, kv->view, layer, q, q_stride,
-                      rows_dev, rows_per_seq, n_q_heads, scale_log2e, p.chunk, p.n_splits, part_o, part_ml, tickets, out, act,
-                      ctx->dev_error);
+    if (p.mt == 2)
+        return launch_attn_t<64, 2>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
+                                    scale_log2e, part_o, part_ml, tickets, out, act);
+    return launch_attn_t<64, 1>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
+                                scale_log2e, part_o, part_ml, tickets, out, act);
 }
 
 extern "C" {

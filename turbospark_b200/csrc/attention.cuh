@@ -4,10 +4,12 @@
 #include "rowops.cuh"
 
 struct AttnPlan {
-    int chunk;     // KV positions per split (multiple of 64)
-    int n_splits;  // grid.x
-    int n_qpairs;  // 32-query tiles per (stream, kv head)
-    int groups;    // streams in the batch
+    int chunk;         // KV positions per CTA (multiple of 64)
+    int n_splits;      // grid.x = clusters * cluster_size
+    int cluster_size;  // CTAs whose shares are merged through distributed shared memory (1, 2, 4 or 8)
+    int mt;            // 16-query tiles per CTA (1 or 2)
+    int n_qtiles;      // query tiles per (stream, kv head)
+    int groups;        // streams in the batch
 };
 AttnPlan attn_plan(const tsb_ctx* ctx, const tsb_kv* kv, int rows, int rows_per_seq, int n_q_heads, int max_len);
 size_t attn_scratch_bytes(int rows, int n_q_heads, int head_dim);

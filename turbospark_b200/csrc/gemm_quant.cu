@@ -623,7 +623,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
             __syncwarp();
             asm volatile("bar.arrive 2, %0;" ::"n"(GEMM_THREADS) : "memory");
         }
-        pdl_launch_dependents();
+        // the dependents are released by the consumers, which have waited for the predecessor by then: a kernel
+        // never lets its successor start before its own predecessor has finished
         return;
     }
 
