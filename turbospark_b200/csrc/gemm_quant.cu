@@ -424,9 +424,14 @@ __device__ __forceinline__ void run_epilogue(const EpiArgs& e, const Group& gr, 
         for (int idx = tid; idx < NTOK * 16; idx += CONSUMER_WARPS * 32) {
             const int tok = idx >> 4, row = idx & 15;
             if (tok >= tokens || row0 + row >= rows) continue;
+            int out_row = tok0 + tok;
+            if (e.y_every > 1) {
+                if (out_row % e.y_every != e.y_every - 1) continue;
+                out_row /= e.y_every;
+            }
             float v = tile_out[tok * 16 + row];
             if (EPI == EPI_SCALE) v *= inv_rms[tok];
-            const size_t o = (size_t)(tok0 + tok) * e.y_stride + row0 + row;
+            const size_t o = (size_t)out_row * e.y_stride + row0 + row;
             if (e.y_f32)
                 reinterpret_cast<float*>(e.y)[o] = v;
             else

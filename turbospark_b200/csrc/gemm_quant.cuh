@@ -61,6 +61,7 @@ struct EpiArgs {
     void* y = nullptr;
     int64_t y_stride = 0;
     int y_f32 = 0;
+    int y_every = 0;  // > 1: only the last token of every run of y_every tokens is stored, as output row token / y_every
     // EPI_RESID_NORM: residual stream h [tokens, rows], next norm weight g (bf16, [rows]), outputs
     __half* h = nullptr;
     const uint16_t* g = nullptr;

@@ -329,7 +329,7 @@ static int32_t runtime_init(tsb_session* s, ModelRt& rt, const tsb_model* model,
 // already on the device.  Cursors are not touched here.
 static cudaError_t forward_device(tsb_session* s, ModelRt& rt, const int32_t* tokens_dev, int token_stride,
                                   const tsb_row_desc* rows_dev, int rows, int rows_per_seq, int max_len, __half* logits,
-                                  int64_t logits_stride) {
+                                  int64_t logits_stride, bool last_rows_only = false) {
     if (s->replay) return cudaSuccess;  // the captured graph already holds this work
     tsb_ctx* ctx = s->ctx;
     cudaStream_t st = s->stream;
@@ -384,6 +384,7 @@ static cudaError_t forward_device(tsb_session* s, ModelRt& rt, const int32_t* to
         EpiArgs a;
         a.ss_in = ss_slot(2 * c.n_layers), a.ss_parts = parts, a.d_in = c.d_model, a.eps = c.rms_eps;
         a.y = logits, a.y_stride = logits_stride, a.y_f32 = 0;
+        a.y_every = last_rows_only ? rows_per_seq : 0;  // logits of each stream's last row only, one output row per stream
         FW(launch_gemm_fused(ctx, st, m->lm_head.qtype, m->lm_head.data, m->lm_head.rows, m->lm_head.cols, in_d, rows, EPI_SCALE, a));
     }
 #undef FW
@@ -515,7 +516,8 @@ int32_t tsb_session_create(tsb_ctx* ctx, const tsb_model* target, const tsb_mode
     auto A = [&](size_t bytes, void** p) { return dev_alloc(ctx, s->owned, bytes, p); };
     if ((rc = A((size_t)R * V * 2, (void**)&s->logits_target))) return fail(rc);
     if ((rc = A((size_t)R * V * 2, (void**)&s->logits_draft))) return fail(rc);
-    if ((rc = A((size_t)R * sizeof(int32_t), (void**)&s->feed_dev))) return fail(rc);
+    if ((rc = A((size_t)(R + 2 * n_streams) * sizeof(int32_t), (void**)&s->feed_dev))) return fail(rc);
+    s->pair_dev = s->feed_dev + R;
     if ((rc = A((size_t)n_streams * (3 * max_rows + 2) * sizeof(uint64_t), (void**)&s->uniforms_dev))) return fail(rc);
     if ((rc = A((size_t)n_streams * sizeof(tsb_accept_out), (void**)&s->accept_out_dev))) return fail(rc);
     s->accept_scratch_bytes = accept_scratch_bytes(n_streams, max_rows, V);
@@ -529,7 +531,8 @@ int32_t tsb_session_create(tsb_ctx* ctx, const tsb_model* target, const tsb_mode
     if ((rc = A((size_t)s->stage_cap * sizeof(int32_t), (void**)&s->stage_tok_dev))) return fail(rc);
     if (cudaMallocHost((void**)&s->accept_out_host, (size_t)n_streams * sizeof(tsb_accept_out)) != cudaSuccess) return fail(TSB_ERR_CUDA);
     if (cudaMallocHost((void**)&s->uniforms_host, (size_t)n_streams * (3 * max_rows + 2) * sizeof(uint64_t)) != cudaSuccess) return fail(TSB_ERR_CUDA);
-    if (cudaMallocHost((void**)&s->feed_host, (size_t)R * sizeof(int32_t)) != cudaSuccess) return fail(TSB_ERR_CUDA);
+    if (cudaMallocHost((void**)&s->feed_host, (size_t)(R + 2 * n_streams) * sizeof(int32_t)) != cudaSuccess) return fail(TSB_ERR_CUDA);
+    s->pair_host = s->feed_host + R;
     if (cudaMallocHost((void**)&s->logits_host, (size_t)V * 2) != cudaSuccess) return fail(TSB_ERR_CUDA);
     *out = s;
     return TSB_OK;
@@ -744,6 +747,16 @@ int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_acti
         for (int j = 0; j < UA; j++)
             un[(size_t)S * UD + (size_t)a * UA + j] = tsb_uniform_u64(cfg->uniform_mode, seed, draw_step_inout[a] + K + 1 + j);
         s->feed_host[(size_t)a * (K + 1)] = next_tokens_host[a];
+        // the drafter's first step feeds two rows: the token before the cursor again, then the confirmed one.  After a
+        // round in which every proposal was accepted the drafter has never seen the last proposal; feeding the row
+        // before the cursor every time keeps the pass shape fixed and replaces the reference's row-only step
+        // (crates/runtime/src/speculative.rs:621-623) - a row that is already in the cache is rewritten bit for bit.
+        const auto& fed = s->target.fed[streams[a]];
+        const int64_t ct = tsb_kv_cursor(s->target.kv, streams[a]);
+        if (ct < 1 || (int64_t)fed.size() < ct)
+            return tsb_fail(ctx, TSB_ERR_STATE, "stream %d: a round needs at least one fed token before the cursor", streams[a]);
+        s->pair_host[2 * a] = fed[(size_t)ct - 1];
+        s->pair_host[2 * a + 1] = next_tokens_host[a];
     }
     uint64_t* un_draft = s->uniforms_dev;
     uint64_t* un_acc = s->uniforms_dev + (size_t)S * UD;
@@ -775,18 +788,23 @@ int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_acti
         if (!s->replay) {
             TSB_CUDA(ctx, cudaMemcpyAsync(s->uniforms_dev, un, (size_t)S * (UD + UA) * sizeof(uint64_t), cudaMemcpyHostToDevice, st));
             TSB_CUDA(ctx, cudaMemcpyAsync(s->feed_dev, s->feed_host, (size_t)S * (K + 1) * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+            TSB_CUDA(ctx, cudaMemcpyAsync(s->pair_dev, s->pair_host, (size_t)S * 2 * sizeof(int32_t), cudaMemcpyHostToDevice, st));
             if (!s->capturing) TSB_CUDA(ctx, cudaEventRecord(s->ev[0], st));
         }
-        // ---- draft: K steps with a head + one row-only step (crates/runtime/src/speculative.rs:607-659)
-        for (int d = 0; d <= K; d++) {
+        // ---- draft: K steps with a head (crates/runtime/src/speculative.rs:607-659); step 0 carries two rows
+        for (int a = 0; a < S; a++) tsb_kv_set_cursor(s->draft.kv, streams[a], tsb_kv_cursor(s->draft.kv, streams[a]) - 1);
+        for (int d = 0; d < K; d++) {
             const tsb_row_desc* rd;
             int max_len;
-            if ((rc2 = stage_rows(s, s->draft, streams, S, 1, nullptr, nullptr, &rd, nullptr, &max_len))) return rc2;
-            const bool head = d < K;
-            TSB_CUDA(ctx, forward_device(s, s->draft, s->feed_dev + d, K + 1, rd, S, 1, max_len,
-                                         head ? s->logits_draft + (size_t)d * V : nullptr, (int64_t)K * V));
-            for (int a = 0; a < S; a++) tsb_kv_set_cursor(s->draft.kv, streams[a], tsb_kv_cursor(s->draft.kv, streams[a]) + 1);
-            if (head && !s->replay)
+            const int nrow = d == 0 ? 2 : 1;
+            if ((rc2 = stage_rows(s, s->draft, streams, S, nrow, nullptr, nullptr, &rd, nullptr, &max_len))) return rc2;
+            if (d == 0)
+                TSB_CUDA(ctx, forward_device(s, s->draft, s->pair_dev, 1, rd, 2 * S, 2, max_len, s->logits_draft, (int64_t)K * V, true));
+            else
+                TSB_CUDA(ctx, forward_device(s, s->draft, s->feed_dev + d, K + 1, rd, S, 1, max_len,
+                                             s->logits_draft + (size_t)d * V, (int64_t)K * V));
+            for (int a = 0; a < S; a++) tsb_kv_set_cursor(s->draft.kv, streams[a], tsb_kv_cursor(s->draft.kv, streams[a]) + nrow);
+            if (!s->replay)
                 TSB_CUDA(ctx, launch_sample(ctx, st, s->logits_draft + (size_t)d * V, (int64_t)K * V, un_draft + d, UD, S, V, T,
                                             s->feed_dev + d + 1, K + 1, nullptr, s->accept_scratch));
         }

@@ -70,6 +70,8 @@ struct tsb_session {
     tsb_accept_out* accept_out_host = nullptr;
     uint64_t* uniforms_host = nullptr;
     int32_t* feed_host = nullptr;
+    int32_t* pair_host = nullptr;     // [n_streams, 2]: token before the cursor, confirmed token (drafter's first step)
+    int32_t* pair_dev = nullptr;
     void* logits_host = nullptr;
     std::vector<void*> owned;
     // CUDA graph of one round's device work (copies, kernels, event records); rebuilt when the shape key changes
