@@ -471,31 +471,109 @@ __global__ void __launch_bounds__(ACC_THREADS)
     }
 }
 
-// Draft-side draw: one cluster per stream, one row each.
+// Draft-side draw: one cluster per stream, one row each; statistics and draw in one kernel, so exp(l - max) is
+// evaluated once per entry and stays in shared memory (first as e, then as the weight, then as the fixed-point mass).
 __global__ void __launch_bounds__(ACC_THREADS)
     sample_kernel(const __half* __restrict__ logits, int64_t logits_stride, const uint64_t* __restrict__ uniforms,
-                  int uni_stride, int vocab, double temperature, const RowStats* __restrict__ stats,
-                  int32_t* __restrict__ tokens, int token_stride, double* __restrict__ margins, uint32_t* __restrict__ err) {
+                  int uni_stride, int vocab, double temperature, int32_t* __restrict__ tokens, int token_stride,
+                  double* __restrict__ margins, uint32_t* __restrict__ err) {
     extern __shared__ __align__(16) uint8_t dyn[];
     unsigned long long* fp = reinterpret_cast<unsigned long long*>(dyn);
+    double* ecache = reinterpret_cast<double*>(dyn);
     __shared__ DrawShared c;
+    __shared__ float fred[ACC_THREADS / 32];
+    __shared__ int ired[ACC_THREADS / 32];
+    __shared__ int bad_flag;
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
     pdl_wait();
     const int b = blockIdx.x / CL;
-    const RowStats st = stats[b];
     const __half* row = logits + (size_t)b * logits_stride;
     const Slice sl = my_slice(vocab, rank);
+    // ---- max, first argmax, finiteness (as accept_stats_kernel)
+    if (threadIdx.x == 0) bad_flag = 0;
+    __syncthreads();
+    float mx = -INFINITY;
+    int am = 0x7fffffff;
+    bool bad = false;
+    for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
+        const float v = __half2float(row[sl.lo + j]);
+        bad |= !isfinite(v);
+        if (v > mx) mx = v, am = sl.lo + j;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float omx = __shfl_xor_sync(0xffffffffu, mx, o);
+        const int oam = __shfl_xor_sync(0xffffffffu, am, o);
+        if (omx > mx || (omx == mx && oam < am)) mx = omx, am = oam;
+    }
+    if (bad) bad_flag = 1;
+    if ((threadIdx.x & 31) == 0) fred[threadIdx.x >> 5] = mx, ired[threadIdx.x >> 5] = am;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        mx = fred[0], am = ired[0];
+        for (int i = 1; i < ACC_THREADS / 32; i++)
+            if (fred[i] > mx || (fred[i] == mx && ired[i] < am)) mx = fred[i], am = ired[i];
+        c.xch.f = mx, c.xch.i[0] = am, c.xch.i[1] = bad_flag;
+    }
+    cluster.sync();
+    int nonfinite = 0;
+    mx = -INFINITY, am = 0x7fffffff;
+    for (int rr = 0; rr < CL; rr++) {
+        const Xchg* o = cluster.map_shared_rank(&c.xch, rr);
+        const float omx = o->f;
+        const int oam = o->i[0];
+        nonfinite |= o->i[1];
+        if (omx > mx || (omx == mx && oam < am)) mx = omx, am = oam;
+    }
+    cluster.sync();
+
     int token;
     unsigned long long gap = ~0ull;
-    if (st.nonfinite) {
+    if (nonfinite) {
         token = -1;
         if (rank == 0 && threadIdx.x == 0) atomicCAS(err, 0u, (uint32_t)TSB_DEV_NONFINITE);
     } else if (temperature == 0.0) {
-        token = st.argmax;
+        token = am;
     } else {
+        const double dmx = (double)mx, inv_t = 1.0 / temperature;
+        const bool unit_t = temperature == 1.0;
+        // e = exp(l - max), its sum, and the last entry in rank order (smallest e, then the largest index)
+        double acc = 0.0;
+        unsigned long long best = ~0ull;
+        unsigned int best_i = 0;
+        for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
+            const double e = exp((double)__half2float(row[sl.lo + j]) - dmx);
+            ecache[j] = e;
+            acc += e;
+            const unsigned long long eb = (unsigned long long)__double_as_longlong(e);
+            if (eb <= best) best = eb, best_i = (unsigned int)(sl.lo + j);  // indices grow with j
+        }
+        const double sum = cluster_sum_f64(cluster, &c.xch, 0, block_sum_f64(acc, c.red));
+        const double top = 1.0 / sum;
+        acc = 0.0;
+        for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
+            const double w = weight_of(ecache[j], sum, top, inv_t, unit_t);
+            ecache[j] = w;
+            acc += w;
+        }
+        const double total = cluster_sum_f64(cluster, &c.xch, 1, block_sum_f64(acc, c.red));
+        if (threadIdx.x == 0) c.best_exp = ~0ull, c.best_idx = 0;
+        __syncthreads();
+        atomicMin(&c.best_exp, best);
+        cluster.sync();
+        unsigned long long gbest = ~0ull;
+        for (int rr = 0; rr < CL; rr++) gbest = min(gbest, cluster.map_shared_rank(&c, rr)->best_exp);
+        if (best == gbest && sl.n > 0 && (int)threadIdx.x < sl.n) atomicMax(&c.best_idx, best_i);
+        cluster.sync();
         unsigned int last = 0;
-        cluster_fill_masses(cluster, c, fp, row, st, nullptr, nullptr, sl, 1.0 / temperature, temperature == 1.0, &last);
+        for (int rr = 0; rr < CL; rr++) last = max(last, cluster.map_shared_rank(&c, rr)->best_idx);
+        cluster.sync();
+        for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
+            const double m = ecache[j] / total;
+            fp[j] = (unsigned long long)__double2ull_rn(m * FP_ONE);
+        }
+        __syncthreads();
         const unsigned long long tgt = (unsigned long long)(uniforms[(size_t)b * uni_stride] >> 11) << 7;
         token = cluster_radix_draw(cluster, c, fp, row, sl, tgt, &gap);
         if (token < 0) token = (int)last, gap = 0;
@@ -564,7 +642,7 @@ cudaError_t launch_accept(tsb_ctx* ctx, cudaStream_t st, const __half* target, c
 cudaError_t launch_sample(tsb_ctx* ctx, cudaStream_t st, const __half* logits, int64_t logits_stride,
                           const uint64_t* uniforms, int uni_stride, int batch, int vocab, double temperature,
                           int32_t* tokens_dev, int token_stride, double* margins_dev, void* scratch) {
-    RowStats* stats = reinterpret_cast<RowStats*>(scratch);
+    (void)scratch;
     const size_t smem = slice_smem(vocab);
     static bool configured = false;
     if (!configured) {
@@ -574,13 +652,9 @@ cudaError_t launch_sample(tsb_ctx* ctx, cudaStream_t st, const __half* logits, i
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    cudaError_t e = tsb_launch_cluster(ctx, accept_stats_kernel, dim3((unsigned)(batch * CL)), dim3(ACC_THREADS), smem, st, true,
-                                       (unsigned)CL, logits, (const __half*)nullptr, 0, vocab, temperature, stats, 1,
-                                       logits_stride);
-    if (e != cudaSuccess) return e;
     return tsb_launch_cluster(ctx, sample_kernel, dim3((unsigned)(batch * CL)), dim3(ACC_THREADS), smem, st, true, (unsigned)CL,
-                              logits, logits_stride, uniforms, uni_stride, vocab, temperature, (const RowStats*)stats,
-                              tokens_dev, token_stride, margins_dev, ctx->dev_error);
+                              logits, logits_stride, uniforms, uni_stride, vocab, temperature, tokens_dev, token_stride,
+                              margins_dev, ctx->dev_error);
 }
 
 int32_t accept_check_shaping(tsb_ctx* ctx, const tsb_shaping* sh) { return check_shaping(ctx, sh); }
