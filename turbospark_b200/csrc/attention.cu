@@ -494,7 +494,8 @@ AttnPlan attn_plan(const tsb_ctx* ctx, const tsb_kv* kv, int rows, int rows_per_
     int cand_splits[3] = {1, 1, 1}, most = 1;  // for cluster sizes 1, 2, 4
     for (int i = 0; i < 3; i++) {
         const int cs = 1 << i;
-        const int resident = max_clusters(ctx->device, kv->view.head_dim, p.mt, cs);  // clusters
+        int resident = max_clusters(ctx->device, kv->view.head_dim, p.mt, cs);  // clusters
+        if (resident > ctx->sm_count / cs) resident = ctx->sm_count / cs;       // one CTA per SM is enough to saturate loads
         int clusters_per = resident / base_ctas;                                        // per (stream, head, tile)
         if (clusters_per < 1) clusters_per = 1;
         if (clusters_per > MAX_SPLITS) clusters_per = MAX_SPLITS;

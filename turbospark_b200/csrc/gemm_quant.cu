@@ -655,8 +655,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
             for (int nt = 0; nt < NT; nt++)
 #pragma unroll
                 for (int i = 0; i < 4; i++) acc[nt][i] = 0.f;
-            const uint32_t slackA = (uint32_t)(reinterpret_cast<uintptr_t>(W + (row0 + gid) * row_bytes) & 15u);
-            const uint32_t slackB = (uint32_t)(reinterpret_cast<uintptr_t>(W + (row0 + gid + 8) * row_bytes) & 15u);
+            // formats whose block rows are 16-byte multiples (Q4_K) start every row on a 16-byte boundary: no slack
+            constexpr bool ALIGNED_ROWS = (UB % 16) == 0;
+            const uint32_t slackA = ALIGNED_ROWS ? 0u : (uint32_t)(reinterpret_cast<uintptr_t>(W + (row0 + gid) * row_bytes) & 15u);
+            const uint32_t slackB = ALIGNED_ROWS ? 0u : (uint32_t)(reinterpret_cast<uintptr_t>(W + (row0 + gid + 8) * row_bytes) & 15u);
 
             for (int it = 0; it < iters; it++, n++) {
                 const uint32_t s = n % NUM_STAGES;
@@ -664,8 +666,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
                 const int nun = min(STAGE_UNITS, units - it * STAGE_UNITS);
                 if (ok && warp < nun) {
                     // slack of this stage's source address: the row start's slack plus the stage offset
-                    const uint32_t stA = (slackA + (uint32_t)((int64_t)it * STAGE_UNITS * UB)) & 15u;
-                    const uint32_t stB = (slackB + (uint32_t)((int64_t)it * STAGE_UNITS * UB)) & 15u;
+                    const uint32_t stA = ALIGNED_ROWS ? 0u : (slackA + (uint32_t)((int64_t)it * STAGE_UNITS * UB)) & 15u;
+                    const uint32_t stB = ALIGNED_ROWS ? 0u : (slackB + (uint32_t)((int64_t)it * STAGE_UNITS * UB)) & 15u;
                     const uint8_t* rA = stages + s * STAGE_BYTES + gid * ROW_STRIDE + stA + warp * UB;
                     const uint8_t* rB = stages + s * STAGE_BYTES + (gid + 8) * ROW_STRIDE + stB + warp * UB;
                     const int unit = it * STAGE_UNITS + warp;

@@ -4,6 +4,7 @@
     python -m turbospark_b200.opbench --op gemm --sweep            # the operator-sweep shapes
     python -m turbospark_b200.opbench --op attention --context 4096 --tokens 6
     python -m turbospark_b200.opbench --op accept --batch 64
+    python -m turbospark_b200.opbench --op sample --batch 1
 
 Each line reports the launch time (CUDA events around `--iters` back-to-back launches that rotate over weight
 copies larger than the L2 cache, minimum of five repeats after warm-up) and the algorithmic bytes over that time.
@@ -115,13 +116,26 @@ def bench_accept(ctx, batch, k, vocab, iters, repeats=5, warm=3):
             "gbs": round(algo / ms / 1e6, 1)}
 
 
+def bench_sample(ctx, batch, vocab, iters, repeats=5, warm=3):
+    rng = np.random.default_rng(6)
+    lg = ctx.to_device(f16_bits(rng.standard_normal((batch, vocab), dtype=np.float32) * 3.0))
+    uni = ctx.to_device(rng.integers(0, 1 << 63, size=batch, dtype=np.uint64))
+    toks = ctx.alloc(batch * 4)
+    margins = ctx.alloc(batch * 8)
+    scratch = ctx.alloc(ctx.accept_scratch_bytes(batch, 1, vocab))
+    cfg = capi.shaping(temperature=1.0)
+    ms = time_launches(lambda i: ctx.sample(lg, uni, batch, vocab, cfg, toks, margins, scratch), iters, repeats, warm)
+    algo = batch * vocab * 2
+    return {"op": "sample", "batch": batch, "vocab": vocab, "us": round(ms * 1e3, 2), "bytes": algo, "gbs": round(algo / ms / 1e6, 1)}
+
+
 SWEEP_SHAPES = [(14336, 4096), (4096, 14336), (128256, 4096)]
 SWEEP_TOKENS = [1, 2, 4, 6, 8, 16, 32, 64]
 
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--op", default="gemm", choices=["gemm", "attention", "accept"])
+    ap.add_argument("--op", default="gemm", choices=["gemm", "attention", "accept", "sample"])
     ap.add_argument("--qtype", default="q4k", choices=sorted(QTYPES))
     ap.add_argument("--rows", type=int, default=14336)
     ap.add_argument("--cols", type=int, default=4096)
@@ -149,6 +163,8 @@ def main():
     elif a.op == "attention":
         print(json.dumps(bench_attention(ctx, a.head_dim, a.q_heads, a.kv_heads, a.context, a.tokens, a.streams, a.iters,
                                          a.repeats, a.warm)), flush=True)
+    elif a.op == "sample":
+        print(json.dumps(bench_sample(ctx, a.batch, a.vocab, a.iters, a.repeats, a.warm)), flush=True)
     else:
         batches = [1, 4, 16, 64, 256] if a.sweep else [a.batch]
         for b in batches:
