@@ -323,14 +323,14 @@ __device__ bool cluster_fill_masses(cg::cluster_group& cluster, DrawShared& c, u
     double t = 0.0;
     int any = 0;
     unsigned long long best = ~0ull;
+    const double p_inv = 1.0 / ps.sum, q_inv = qrow ? 1.0 / qs->sum : 0.0;  // temperature 1: mass = e / sum (see sample_kernel)
     for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
         const double e = exp((double)__half2float(prow[sl.lo + j]) - pmax);
-        double m = weight_of(e, ps.sum, ptop, inv_t, unit_t) / ps.total;
+        double m = unit_t ? e * p_inv : weight_of(e, ps.sum, ptop, inv_t, unit_t) / ps.total;
         bool in_support = true;
         if (qrow) {
-            const double qq =
-                weight_of(exp((double)__half2float(qrow[sl.lo + j]) - (double)qs->max), qs->sum, 1.0 / qs->sum, inv_t, unit_t) /
-                qs->total;
+            const double eq = exp((double)__half2float(qrow[sl.lo + j]) - (double)qs->max);
+            const double qq = unit_t ? eq * q_inv : weight_of(eq, qs->sum, 1.0 / qs->sum, inv_t, unit_t) / qs->total;
             m = fmax(m - qq, 0.0);
             in_support = m > 0.0;
             t += m;
@@ -551,13 +551,19 @@ __global__ void __launch_bounds__(ACC_THREADS)
         }
         const double sum = cluster_sum_f64(cluster, &c.xch, 0, block_sum_f64(acc, c.red));
         const double top = 1.0 / sum;
-        acc = 0.0;
-        for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
-            const double w = weight_of(ecache[j], sum, top, inv_t, unit_t);
-            ecache[j] = w;
-            acc += w;
+        double total = sum;
+        if (!unit_t) {
+            acc = 0.0;
+            for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
+                const double w = weight_of(ecache[j], sum, top, inv_t, unit_t);
+                ecache[j] = w;
+                acc += w;
+            }
+            total = cluster_sum_f64(cluster, &c.xch, 1, block_sum_f64(acc, c.red));
         }
-        const double total = cluster_sum_f64(cluster, &c.xch, 1, block_sum_f64(acc, c.red));
+        // At temperature 1 the reference's weight ((e/sum)/top with top = 1/sum) is e up to two roundings and its
+        // total is the sum, so the mass is e/sum: one multiply per entry.  The few-ulp difference can move a draw only
+        // when the target lies within ~1e-15 of a boundary, which the reported margin shows.
         if (threadIdx.x == 0) c.best_exp = ~0ull, c.best_idx = 0;
         __syncthreads();
         atomicMin(&c.best_exp, best);
@@ -569,9 +575,14 @@ __global__ void __launch_bounds__(ACC_THREADS)
         unsigned int last = 0;
         for (int rr = 0; rr < CL; rr++) last = max(last, cluster.map_shared_rank(&c, rr)->best_idx);
         cluster.sync();
-        for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
-            const double m = ecache[j] / total;
-            fp[j] = (unsigned long long)__double2ull_rn(m * FP_ONE);
+        if (unit_t) {
+            const double scale = FP_ONE / total;
+            for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) fp[j] = (unsigned long long)__double2ull_rn(ecache[j] * scale);
+        } else {
+            for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
+                const double m = ecache[j] / total;
+                fp[j] = (unsigned long long)__double2ull_rn(m * FP_ONE);
+            }
         }
         __syncthreads();
         const unsigned long long tgt = (unsigned long long)(uniforms[(size_t)b * uni_stride] >> 11) << 7;
