@@ -73,6 +73,9 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+NCU_TRAFFIC_RATIO = 1.034
+
+
 def cpu_round_estimate(threads):
     """Bounded CPU sample of one round on the oracle: one target layer's matmuls at K+1 rows, one layer of
     attention at the benchmark context, one drafter layer at 1 row, 1/16 of the head; scaled to the full
@@ -241,13 +244,18 @@ def run_ours(args, rank, world, local_rank):
                        "accepted_per_round": accepted / (n_rounds * S), "committed_per_round": committed / (n_rounds * S),
                        "value_definition": "tokens committed per second (accepted proposals + the corrected/bonus token), all GPUs"},
             "e2e": {"value": committed_all / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms / n_rounds,
-                    "h2d_bytes_per_step": S * ((K + 1) * 4 + (3 * K + 1) * 8 + (2 * K + 2) * 32), "d2h_bytes_per_step": S * 96},
+                    "h2d_bytes_per_step": S * ((K + 3) * 4 + (3 * K + 1) * 8 + (2 * K + 2) * 32), "d2h_bytes_per_step": S * 96},
             "gpu_launches": launches,
             "phases_ms_per_step": {"draft": phase[0] / n_rounds, "verify": phase[1] / n_rounds, "accept": phase[2] / n_rounds},
             "verify_pass": {"ms": verify_ms / n_rounds, "algorithmic_bytes": verify_bytes, "gbs": verify_gbs, "frac_of_peak": verify_gbs / peak},
             "roofline": {"bound": "hbm", "kernel": "gemm_quant_kernel<Q4_K> (all layer matmuls of one verify pass, %d rows)" % (S * (K + 1)),
                          "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
-                         "launches": mm_launches, "us_per_launch": mm_ms * 1e3 / mm_launches, "traffic": None},
+                         "launches": mm_launches, "us_per_launch": mm_ms * 1e3 / mm_launches,
+                         "bytes_per_launch": mm_bytes / mm_launches,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of the captured 57344 x 4096 launch were 1.034 x its
+                         # algorithmic bytes (profiles/gemm_quant_q4k_57344x4096_m6.md); traffic grows with the weight bytes
+                         "traffic": NCU_TRAFFIC_RATIO * mm_bytes / mm_launches,
+                         "traffic_source": "ncu capture of a 132 MB launch, scaled by algorithmic bytes"},
             "clocks": clocks,
             "weights_bytes": {"target": tb, "draft": db},
         }
