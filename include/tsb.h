@@ -353,6 +353,14 @@ typedef struct tsb_run_config {
     int32_t n_stop;
     int32_t stop_tokens[8];
     int32_t adaptive;     /* 0 = fixed depth, else the adaptive controller's floor */
+    /* Tree rounds (crates/runtime/src/speculative.rs:461-560).  tree_nodes > 0 turns them on for rounds that are
+     * neither truncated nor adaptive: a static tree is drafted level by level - every node of level l gets the
+     * tree_branching[l] most likely next tokens of the drafter at that node - and cut breadth-first at tree_nodes
+     * nodes; `block` must equal tree_levels (the longest path a round can accept).  The target verifies anchor +
+     * nodes in one pass with the ancestor mask, the walk accepts a child that carries the target's pick, and the
+     * accepted path is compacted in place.  Temperature must be 0 (the reference refuses sampled tree rounds). */
+    int32_t tree_nodes, tree_levels;
+    int32_t tree_branching[8];
 } tsb_run_config;
 
 typedef struct tsb_run_result {

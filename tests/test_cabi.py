@@ -56,7 +56,8 @@ def test_struct_layouts_match_the_header():
     assert C.sizeof(tsb.Shaping) == 64
     assert C.sizeof(tsb.AcceptOut) == 96
     assert C.sizeof(tsb.ModelConfig) == 40
-    assert C.sizeof(tsb.RunConfig) == 64 + 4 * 4 + 32 + 4 + 4  # shaping, four ints, stop tokens, adaptive, padding
+    # shaping, four ints, stop tokens, adaptive, tree nodes/levels, branching list, padding to 8
+    assert C.sizeof(tsb.RunConfig) == 64 + 4 * 4 + 32 + 4 + 2 * 4 + 32 + 4
     assert tsb.lib().tsb_row_bytes(0, 4096) == 2304 and tsb.lib().tsb_row_bytes(1, 4096) == 3360
     assert tsb.lib().tsb_row_bytes(2, 4096) == 2176
 

@@ -183,3 +183,29 @@ def test_stop_token_budget_and_refusals(rig, oracle):
     with pytest.raises(tsb.TsbError):
         sess.spec_run(np.zeros(0, np.int32), rc)
     sess.close()
+
+
+@pytest.mark.parametrize("nodes,branching", [(10, (2, 2, 1)), (14, (2, 2, 2)), (6, (3, 1))])
+def test_greedy_tree_rounds_equal_the_sequential_loop_token_for_token(rig, oracle, nodes, branching):
+    """Static-tree rounds: drafter top-b children per level, one tree verify, the accept walk and in-place compaction
+    must leave exactly what greedy sequential decoding leaves (crates/runtime/src/speculative.rs:461-560)."""
+    tsb = rig["tsb"]
+    sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 16)
+    rng = np.random.default_rng(21)
+    prompt = rng.integers(0, rig["cfg"].vocab, size=24).astype(np.int32)
+    plain = tsb.run_config(tsb.shaping(temperature=0.0), 40, len(branching))
+    tree = tsb.run_config(tsb.shaping(temperature=0.0), 40, len(branching), tree_nodes=nodes, tree_branching=branching)
+    seq_hist, seq_emit, _ = sess.sequential_run(prompt, plain)
+    hist, emit, res = sess.spec_run(prompt, tree)
+    assert np.array_equal(seq_emit, emit) and np.array_equal(seq_hist, hist)
+    assert res.new_tokens == 40 and res.kv_position == res.history_len
+    # a tree offers the chain's first proposal among others, so it accepts at least as much as the chain does
+    _, _, chain = sess.spec_run(prompt, plain)
+    assert res.accepted_total >= chain.accepted_total and res.rounds <= chain.rounds
+    # refusals: sampled tree rounds, block != levels, a tree larger than the session's rows
+    for bad in (tsb.run_config(tsb.shaping(temperature=1.0), 8, len(branching), tree_nodes=nodes, tree_branching=branching),
+                tsb.run_config(tsb.shaping(temperature=0.0), 8, len(branching) + 1, tree_nodes=nodes, tree_branching=branching),
+                tsb.run_config(tsb.shaping(temperature=0.0), 8, 2, tree_nodes=40, tree_branching=(8, 8))):
+        with pytest.raises(tsb.TsbError):
+            sess.spec_run(prompt, bad)
+    sess.close()

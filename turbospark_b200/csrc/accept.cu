@@ -596,6 +596,47 @@ __global__ void __launch_bounds__(ACC_THREADS)
     }
 }
 
+// The `width` largest logits of each listed row, by value descending and token id ascending on ties (the order
+// in which a static draft tree takes the children of a node).  One CTA per row; width <= 8.  Row r of the launch
+// reads logits + rows[r] * vocab and writes out[r * 8 .. r * 8 + width).
+__global__ void __launch_bounds__(1024)
+    topk_rows_kernel(const __half* __restrict__ logits, int vocab, const int32_t* __restrict__ rows, int width,
+                     int32_t* __restrict__ out) {
+    __shared__ float fred[32];
+    __shared__ int ired[32];
+    __shared__ int chosen[8];
+    pdl_wait();
+    const __half* row = logits + (size_t)rows[blockIdx.x] * vocab;
+    for (int pick = 0; pick < width; pick++) {
+        float mx = -INFINITY;
+        int am = 0x7fffffff;
+        for (int j = threadIdx.x; j < vocab; j += blockDim.x) {
+            bool taken = false;
+            for (int c = 0; c < pick; c++) taken |= chosen[c] == j;
+            if (taken) continue;
+            const float v = __half2float(row[j]);
+            if (v > mx || (v == mx && j < am) || am == 0x7fffffff) mx = v, am = j;  // NaN never wins over a number
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float omx = __shfl_xor_sync(0xffffffffu, mx, o);
+            const int oam = __shfl_xor_sync(0xffffffffu, am, o);
+            if (oam != 0x7fffffff && (am == 0x7fffffff || omx > mx || (omx == mx && oam < am))) mx = omx, am = oam;
+        }
+        if ((threadIdx.x & 31) == 0) fred[threadIdx.x >> 5] = mx, ired[threadIdx.x >> 5] = am;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            mx = fred[0], am = ired[0];
+            for (int i = 1; i < (int)(blockDim.x >> 5); i++)
+                if (ired[i] != 0x7fffffff && (am == 0x7fffffff || fred[i] > mx || (fred[i] == mx && ired[i] < am))) mx = fred[i], am = ired[i];
+            chosen[pick] = am;
+            out[blockIdx.x * 8 + pick] = am == 0x7fffffff ? -1 : am;
+        }
+        __syncthreads();
+    }
+    pdl_launch_dependents();
+}
+
 int32_t check_shaping(tsb_ctx* ctx, const tsb_shaping* sh) {
     TSB_REQUIRE(ctx, sh, "null shaping");
     // crates/selection/src/shaping.rs:84-123
@@ -666,6 +707,28 @@ cudaError_t launch_sample(tsb_ctx* ctx, cudaStream_t st, const __half* logits, i
     return tsb_launch_cluster(ctx, sample_kernel, dim3((unsigned)(batch * CL)), dim3(ACC_THREADS), smem, st, true, (unsigned)CL,
                               logits, logits_stride, uniforms, uni_stride, vocab, temperature, tokens_dev, token_stride,
                               margins_dev, ctx->dev_error);
+}
+
+cudaError_t launch_topk_rows(tsb_ctx* ctx, cudaStream_t st, const __half* logits, int vocab, const int32_t* rows_dev, int n_rows,
+                             int width, int32_t* out_dev) {
+    return tsb_launch(ctx, topk_rows_kernel, dim3((unsigned)n_rows), dim3(1024), 0, st, true, logits, vocab, rows_dev, width, out_dev);
+}
+
+cudaError_t launch_argmax_rows(tsb_ctx* ctx, cudaStream_t st, const __half* logits, int n_rows, int vocab, void* scratch) {
+    // the statistics kernel at temperature 0: max, first argmax and finiteness of every row (rows are "target rows")
+    RowStats* stats = reinterpret_cast<RowStats*>(scratch);
+    const size_t smem = slice_smem(vocab);
+    cudaError_t e = ensure_smem(accept_stats_kernel, (size_t)SLICE_MAX * 8);
+    if (e != cudaSuccess) return e;
+    return tsb_launch_cluster(ctx, accept_stats_kernel, dim3((unsigned)(n_rows * CL)), dim3(ACC_THREADS), smem, st, true,
+                              (unsigned)CL, logits, (const __half*)nullptr, n_rows - 1, vocab, 0.0, stats, n_rows, (int64_t)0);
+}
+
+int accept_row_stats_bytes() { return (int)sizeof(RowStats); }
+void accept_row_stats_read(const void* host_stats, int row, int32_t* argmax, int32_t* nonfinite) {
+    const RowStats* st = reinterpret_cast<const RowStats*>(host_stats) + row;
+    *argmax = st->argmax;
+    *nonfinite = st->nonfinite;
 }
 
 int32_t accept_check_shaping(tsb_ctx* ctx, const tsb_shaping* sh) { return check_shaping(ctx, sh); }

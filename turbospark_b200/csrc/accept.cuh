@@ -14,3 +14,11 @@ cudaError_t launch_accept(tsb_ctx* ctx, cudaStream_t st, const __half* target, c
 cudaError_t launch_sample(tsb_ctx* ctx, cudaStream_t st, const __half* logits, int64_t logits_stride,
                           const uint64_t* uniforms, int uni_stride, int batch, int vocab, double temperature,
                           int32_t* tokens_dev, int token_stride, double* margins_dev, void* scratch);
+// The `width` (<= 8) largest logits of rows rows_dev[0..n_rows) of a [*, vocab] matrix, value descending, token id
+// ascending on ties; row r's picks land in out_dev[r * 8 ..].
+cudaError_t launch_topk_rows(tsb_ctx* ctx, cudaStream_t st, const __half* logits, int vocab, const int32_t* rows_dev, int n_rows,
+                             int width, int32_t* out_dev);
+// max / first argmax / finiteness of n_rows consecutive rows into scratch (one record per row).
+cudaError_t launch_argmax_rows(tsb_ctx* ctx, cudaStream_t st, const __half* logits, int n_rows, int vocab, void* scratch);
+int accept_row_stats_bytes();
+void accept_row_stats_read(const void* host_stats, int row, int32_t* argmax, int32_t* nonfinite);

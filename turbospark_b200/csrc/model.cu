@@ -523,6 +523,7 @@ int32_t tsb_session_create(tsb_ctx* ctx, const tsb_model* target, const tsb_mode
     s->accept_scratch_bytes = accept_scratch_bytes(n_streams, max_rows, V);
     if ((rc = A(s->accept_scratch_bytes, &s->accept_scratch))) return fail(rc);
     if ((rc = A((size_t)n_streams * sizeof(int32_t), (void**)&s->tok1_dev))) return fail(rc);
+    if ((rc = A((size_t)128 * 9 * sizeof(int32_t), (void**)&s->tree_dev))) return fail(rc);
     // pinned staging: descriptors and tokens of several forwards in flight
     s->stage_cap = R * (2 * max_rows + 8);
     if (cudaMallocHost((void**)&s->stage_rows_host, (size_t)s->stage_cap * sizeof(tsb_row_desc)) != cudaSuccess) return fail(TSB_ERR_CUDA);
@@ -888,6 +889,102 @@ int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_acti
         next_tokens_host[a] = o.tokens[o.accepted];
         draw_step_inout[a] += (sampled ? (uint64_t)(K + 1) : 0) + (uint64_t)o.draws;
     }
+    return TSB_OK;
+}
+
+// ---- tree round (crates/runtime/src/speculative.rs:461-560; tree shape helpers runtime/src/dflash_tree.rs:106-124)
+int32_t session_tree_round(tsb_session* s, int stream, const tsb_run_config* cfg, int32_t next, int64_t base,
+                           std::vector<int32_t>& feed, std::vector<int32_t>& slot_parent, std::vector<int32_t>& picks,
+                           int* drafter_rows) {
+    tsb_ctx* ctx = s->ctx;
+    if (!s->has_draft) return tsb_fail(ctx, TSB_ERR_STATE, "the session has no drafter");
+    TSB_REQUIRE(ctx, cfg->shaping.temperature == 0.0, "tree rounds need temperature 0 (sampled tree acceptance is not defined)");
+    const int N = cfg->tree_nodes, LV = cfg->tree_levels;
+    TSB_REQUIRE(ctx, N >= 1 && N + 1 <= s->max_rows && N + 1 <= 128, "tree of %d nodes + anchor exceeds the session's %d rows", N, s->max_rows);
+    TSB_REQUIRE(ctx, LV >= 1 && LV <= 8, "tree_levels must be 1..8");
+    for (int l = 0; l < LV; l++) TSB_REQUIRE(ctx, cfg->tree_branching[l] >= 1 && cfg->tree_branching[l] <= 8, "tree_branching must be 1..8");
+    const int V = s->target.model->cfg.vocab;
+    int32_t rc;
+    if (tsb_kv_cursor(s->draft.kv, stream) < base && (rc = drafter_catch_up(s, stream, base))) return rc;
+    if (tsb_kv_cursor(s->draft.kv, stream) != base || tsb_kv_cursor(s->target.kv, stream) != base)
+        return tsb_fail(ctx, TSB_ERR_STATE, "tree round at %lld: target cursor %lld, drafter cursor %lld", (long long)base,
+                        (long long)tsb_kv_cursor(s->target.kv, stream), (long long)tsb_kv_cursor(s->draft.kv, stream));
+    // the static shape, breadth-first, cut at N nodes: slot 0 is the anchor, node i sits in slot i + 1
+    slot_parent.assign(1, -1);
+    std::vector<int> level_begin{0, 1};  // slots of level l are [level_begin[l], level_begin[l+1])
+    for (int l = 0; l < LV && (int)slot_parent.size() < N + 1; l++) {
+        const int lo = level_begin[l], hi = level_begin[l + 1];
+        for (int p = lo; p < hi && (int)slot_parent.size() < N + 1; p++)
+            for (int c = 0; c < cfg->tree_branching[l] && (int)slot_parent.size() < N + 1; c++) slot_parent.push_back(p);
+        level_begin.push_back((int)slot_parent.size());
+    }
+    const int rows = (int)slot_parent.size();
+    TSB_REQUIRE(ctx, rows == N + 1, "the branching list yields %d nodes, fewer than tree_nodes %d", rows - 1, N);
+    feed.assign(rows, 0);
+    feed[0] = next;
+    // ---- draft level by level: the drafter runs over every slot drafted so far (tree mask), its logits at the rows of
+    // the newest level give those nodes' children
+    const int n_levels = (int)level_begin.size() - 1;  // levels that hold slots (anchor level included)
+    int drafted = 0;
+    std::vector<int32_t> row_ids, child(8 * 128);
+    for (int l = 0; l + 1 < n_levels; l++) {
+        const int n = level_begin[l + 1];  // slots 0 .. n-1 are known
+        if ((rc = forward_stream(s, s->draft, stream, feed.data(), n, slot_parent.data(), s->logits_draft, nullptr))) return rc;
+        tsb_kv_set_cursor(s->draft.kv, stream, base);
+        drafted = n;
+        const int lo = level_begin[l], hi = level_begin[l + 1];
+        row_ids.resize(hi - lo);
+        for (int p = lo; p < hi; p++) row_ids[p - lo] = p;
+        int32_t* rows_dev = s->tree_dev;  // row list (128 ints), then eight picks per row
+        int32_t* child_dev = s->tree_dev + 128;
+        TSB_CUDA(ctx, cudaMemcpyAsync(rows_dev, row_ids.data(), (hi - lo) * sizeof(int32_t), cudaMemcpyHostToDevice, s->stream));
+        TSB_CUDA(ctx, launch_topk_rows(ctx, s->stream, s->logits_draft, V, rows_dev, hi - lo, cfg->tree_branching[l], child_dev));
+        TSB_CUDA(ctx, cudaMemcpyAsync(child.data(), child_dev, (size_t)(hi - lo) * 8 * sizeof(int32_t), cudaMemcpyDeviceToHost, s->stream));
+        if ((rc = tsb_stream_sync(ctx, s->stream))) return rc;
+        // children of the level's nodes, in slot order
+        int slot = level_begin[l + 1];
+        for (int p = lo; p < hi; p++)
+            for (int c = 0; c < cfg->tree_branching[l] && slot < level_begin[l + 2]; c++, slot++) {
+                const int32_t t = child[(size_t)(p - lo) * 8 + c];
+                if (t < 0) return tsb_fail(ctx, TSB_ERR_DEVICE, "the drafter's logits at tree slot %d are not finite", p);
+                feed[slot] = t;
+            }
+    }
+    *drafter_rows = drafted;
+    // ---- verify: anchor + nodes in one target pass, then the target's pick at every row
+    if ((rc = forward_stream(s, s->target, stream, feed.data(), rows, slot_parent.data(), s->logits_target, nullptr))) return rc;
+    tsb_kv_set_cursor(s->target.kv, stream, base);
+    TSB_REQUIRE(ctx, (size_t)rows * accept_row_stats_bytes() <= s->accept_scratch_bytes, "tree of %d rows exceeds the acceptance scratch", rows);
+    TSB_CUDA(ctx, launch_argmax_rows(ctx, s->stream, s->logits_target, rows, V, s->accept_scratch));
+    std::vector<uint8_t> stats((size_t)rows * accept_row_stats_bytes());
+    TSB_CUDA(ctx, cudaMemcpyAsync(stats.data(), s->accept_scratch, stats.size(), cudaMemcpyDeviceToHost, s->stream));
+    if ((rc = tsb_stream_sync(ctx, s->stream))) return rc;
+    picks.resize(rows);
+    for (int r = 0; r < rows; r++) {
+        int32_t am, bad;
+        accept_row_stats_read(stats.data(), r, &am, &bad);
+        if (bad) return tsb_fail(ctx, TSB_ERR_DEVICE, "a target logit at tree slot %d is not finite", r);
+        picks[r] = am;
+    }
+    return TSB_OK;
+}
+
+int32_t session_tree_commit(tsb_session* s, int stream, int64_t base, const std::vector<int32_t>& feed,
+                            const std::vector<uint32_t>& path, int keep, int drafter_rows) {
+    tsb_ctx* ctx = s->ctx;
+    int32_t rc = tsb_kv_commit_path(ctx, s->stream, s->target.kv, stream, base, path.data(), keep);
+    if (rc) return rc;
+    // the drafter holds rows only for the slots it was run over: keep the part of the path it has, the rest is
+    // replayed from the record of fed tokens before its next step
+    int dkeep = 0;
+    while (dkeep < keep && (int)path[dkeep] < drafter_rows) dkeep++;
+    if (dkeep > 0 && (rc = tsb_kv_commit_path(ctx, s->stream, s->draft.kv, stream, base, path.data(), dkeep))) return rc;
+    if ((rc = tsb_stream_sync(ctx, s->stream))) return rc;
+    tsb_kv_set_cursor(s->target.kv, stream, base + keep);
+    tsb_kv_set_cursor(s->draft.kv, stream, base + dkeep);
+    auto& fed = s->target.fed[stream];
+    fed.resize((size_t)base);
+    for (int r = 0; r < keep; r++) fed.push_back(feed[path[r]]);
     return TSB_OK;
 }
 

@@ -57,6 +57,7 @@ struct tsb_session {
     __half* logits_draft = nullptr;   // [n_streams, k, vocab]
     int32_t* feed_dev = nullptr;      // [n_streams, k + 1]: confirmed token, then the proposals
     int32_t* tok1_dev = nullptr;
+    int32_t* tree_dev = nullptr;      // tree drafting scratch: 128 row ids, then 8 picks per row
     uint64_t* uniforms_dev = nullptr;
     tsb_accept_out* accept_out_dev = nullptr;
     void* accept_scratch = nullptr;
@@ -85,5 +86,15 @@ struct tsb_session {
 int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_active, int k, const tsb_run_config* cfg,
                               int32_t* next_tokens_host, int32_t* accepted_host, int32_t* tokens_out /* [n_active][16] */,
                               int32_t* draws_out, uint64_t* draw_step_inout);
+// One tree round for one stream at temperature 0 (model.cu): drafts the static tree of cfg level by level, verifies
+// anchor + nodes in one target pass and returns, per slot (0 = anchor, node i = slot i + 1), the fed token, the
+// slot's parent and the target's pick at that row.  Both caches' cursors are left at `base`; rows base + slot hold
+// the tree (the drafter's only for the first *drafter_rows slots).
+int32_t session_tree_round(tsb_session* s, int stream, const tsb_run_config* cfg, int32_t next, int64_t base,
+                           std::vector<int32_t>& feed, std::vector<int32_t>& slot_parent, std::vector<int32_t>& picks,
+                           int* drafter_rows);
+// Keep path[0..keep) of the tree rows of both caches as a chain at base (compaction + cursors + fed-token record).
+int32_t session_tree_commit(tsb_session* s, int stream, int64_t base, const std::vector<int32_t>& feed,
+                            const std::vector<uint32_t>& path, int keep, int drafter_rows);
 // token = select(logits row of the last single-row target forward) for one stream (model.cu).
 int32_t session_select_target(tsb_session* s, const tsb_run_config* cfg, uint64_t uniform, int32_t* token_host);

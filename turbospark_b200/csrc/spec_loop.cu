@@ -114,6 +114,10 @@ int32_t tsb_spec_run(tsb_session* s, int32_t stream, const int32_t* prompt, int3
     if (cfg->block == 0)  // speculative.rs:208-212
         return tsb_fail(ctx, TSB_ERR_INVALID, "block size 0 proposes nothing; call tsb_sequential_run instead");
     TSB_REQUIRE(ctx, cfg->block >= 1 && cfg->block <= 15, "block must be 1..=15");
+    if (cfg->tree_nodes > 0) {
+        TSB_REQUIRE(ctx, cfg->tree_levels == cfg->block, "tree rounds need block (%d) == tree_levels (%d)", cfg->block, cfg->tree_levels);
+        TSB_REQUIRE(ctx, cfg->shaping.temperature == 0.0, "tree rounds need temperature 0");
+    }
     TSB_REQUIRE(ctx, stream >= 0 && stream < s->n_streams, "stream %d outside the session", stream);
     if (!s->has_draft) return tsb_fail(ctx, TSB_ERR_STATE, "speculation needs a drafter");
     const int block = cfg->block;
@@ -154,6 +158,49 @@ int32_t tsb_spec_run(tsb_session* s, int32_t stream, const int32_t* prompt, int3
         if (tsb_kv_cursor(s->target.kv, stream) != base)
             return tsb_fail(ctx, TSB_ERR_STATE, "target cursor %lld does not sit at the confirmed token %lld",
                             (long long)tsb_kv_cursor(s->target.kv, stream), (long long)base);
+
+        if (cfg->tree_nodes > 0 && round_block == block && !cfg->adaptive) {
+            // ---- a tree round: the walk is the chain's acceptance generalised - at the current node's row the target's
+            // pick is accepted when a child of that node carries it (speculative.rs:494-529)
+            std::vector<int32_t> feed, parent, picks;
+            int drafter_rows = 0;
+            if ((rc = session_tree_round(s, stream, cfg, next, base, feed, parent, picks, &drafter_rows))) return rc;
+            rounds++;
+            std::vector<uint32_t> path{0};
+            int at = 0, stopped = -1;
+            int32_t bonus = -1;
+            for (;;) {
+                const int32_t target = picks[at];
+                int hit = -1;
+                for (int c = at + 1; c < (int)feed.size(); c++)
+                    if (parent[c] == at && feed[c] == target) {
+                        hit = c;
+                        break;
+                    }
+                if (hit < 0) {
+                    bonus = target;
+                    break;
+                }
+                path.push_back((uint32_t)hit);
+                at = hit;
+                const int st = sink.commit(target);
+                if (st >= 0) {
+                    stopped = st;
+                    break;
+                }
+            }
+            accepted_total += (int)path.size() - 1;
+            const int64_t committed = (int64_t)sink.history.size() - (base + 1);
+            if (committed + 1 < (int64_t)feed.size()) rollbacks++;
+            if ((rc = session_tree_commit(s, stream, base, feed, path, (int)committed + 1, drafter_rows))) return rc;
+            position = (int64_t)sink.history.size();
+            if (stopped >= 0) {
+                reason = stopped;
+                break;
+            }
+            next = bonus;
+            continue;
+        }
 
         int32_t accepted = 0, draws = 0, toks[16];
         int32_t confirmed = next;

@@ -17,7 +17,8 @@ class ModelConfig(C.Structure):
 
 class RunConfig(C.Structure):
     _fields_ = [("shaping", Shaping), ("max_new_tokens", C.c_int32), ("block", C.c_int32), ("uniform_mode", C.c_int32),
-                ("n_stop", C.c_int32), ("stop_tokens", C.c_int32 * 8), ("adaptive", C.c_int32)]
+                ("n_stop", C.c_int32), ("stop_tokens", C.c_int32 * 8), ("adaptive", C.c_int32),
+                ("tree_nodes", C.c_int32), ("tree_levels", C.c_int32), ("tree_branching", C.c_int32 * 8)]
 
 
 class RunResult(C.Structure):
@@ -26,8 +27,11 @@ class RunResult(C.Structure):
                 ("decode_seconds", C.c_double)]
 
 
-def run_config(shaping_cfg, max_new_tokens, block, uniform_mode=0, stop_tokens=(), adaptive=0):
+def run_config(shaping_cfg, max_new_tokens, block, uniform_mode=0, stop_tokens=(), adaptive=0, tree_nodes=0, tree_branching=()):
     rc = RunConfig()
+    rc.tree_nodes, rc.tree_levels = tree_nodes, len(tree_branching)
+    for i, b in enumerate(tree_branching):
+        rc.tree_branching[i] = b
     rc.shaping = shaping_cfg
     rc.max_new_tokens, rc.block, rc.uniform_mode, rc.adaptive = max_new_tokens, block, uniform_mode, adaptive
     rc.n_stop = len(stop_tokens)
