@@ -283,6 +283,27 @@ TSB_API int32_t tsb_sample(tsb_ctx* ctx, tsb_stream s, const void* logits_f16, c
  * mode 1 = Philox4x32-10 keyed by seed with counter = step (this backend's addition). */
 TSB_API uint64_t tsb_uniform_u64(int32_t mode, uint64_t seed, uint64_t step);
 
+/* ------------------------------------------------------ mixture of experts */
+
+/* Routing of `tokens` rows over n_experts router logits (f32, [tokens, n_experts]): the k (<= 8) largest logits,
+ * ties to the lower expert index, softmax over the selected logits only, times per_expert_scale (null = ones);
+ * ids_out [tokens, k] in rank order, weights [tokens, k] as f16.  Replaces router_topk_gemma4
+ * (crates/runtime/src/real_forward_dispatch.rs:1135-1158) and the f16 routing-weight upload
+ * (crates/runtime/src/families/llama/moe.rs:118-127). */
+TSB_API int32_t tsb_moe_route(tsb_ctx* ctx, tsb_stream s, const float* router_logits_f32, int32_t tokens, int32_t n_experts,
+                              int32_t k, const float* per_expert_scale, int32_t* ids_out, void* weights_f16_out);
+/* The routed feed-forward: for every row, y = half(residual + sum over its k slots, in slot order, of
+ * float(weight) * down_e(half(act(gate_e x) * (up_e x)))).  Expert e's gate rows then up rows sit at
+ * gate_up_region + gate_up_off + e * (2*ffn rows of d_model columns), its down rows at down_region + down_off +
+ * e * (d_model rows of ffn columns), all verbatim blocks of `qtype`.  x, residual and y are [tokens, d_model] f16;
+ * ids / weights come from tsb_moe_route.  The call reads the routing result back once (it synchronises the
+ * stream) and runs the rows of each active expert through the matmul kernel.  Replaces
+ * moe_phase1_gate_up_act_* and moe_phase2_down_reduce_k8_* (crates/gpu/src/shaders/moe_gguf.metal:561-678). */
+TSB_API int32_t tsb_moe_ffn(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* gate_up_region, uint64_t gate_up_off,
+                            const void* down_region, uint64_t down_off, int32_t n_experts, int32_t d_model, int32_t ffn,
+                            const void* x_f16, const void* residual_f16, const int32_t* ids_dev, const void* weights_f16_dev,
+                            int32_t tokens, int32_t k, void* y_f16);
+
 /* ------------------------------------------------------ model and producer */
 
 /* A dense Llama-style decoder (RMSNorm -> q/k/v -> RoPE -> attention -> o_proj -> residual -> RMSNorm ->

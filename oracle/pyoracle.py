@@ -156,6 +156,32 @@ def gemm_quant(kind, w_bytes, rows, cols, x, threads=1):
     return y
 
 
+def moe_route(logits, k, scale=None):
+    """router_topk_gemma4: ids [tokens, k] in rank order, weights [tokens, k] as f16 bits."""
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    tokens, n_experts = logits.shape
+    ids = np.empty((tokens, k), dtype=np.int32)
+    w = np.empty((tokens, k), dtype=np.uint16)
+    sc = None if scale is None else np.ascontiguousarray(scale, dtype=np.float32)
+    lib().tso_moe_route(_p(logits), C.c_int64(tokens), C.c_int64(n_experts), C.c_int64(k), _p(sc) if sc is not None else None,
+                        _p(ids), _p(w))
+    return ids, w
+
+
+def moe_ffn(kind, gate_up, down, n_experts, d_model, ffn, x16, resid16, ids, w16, threads=1):
+    gate_up = np.ascontiguousarray(gate_up, dtype=np.uint8)
+    down = np.ascontiguousarray(down, dtype=np.uint8)
+    x16 = np.ascontiguousarray(x16, dtype=np.uint16)
+    resid16 = np.ascontiguousarray(resid16, dtype=np.uint16)
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    w16 = np.ascontiguousarray(w16, dtype=np.uint16)
+    tokens, k = ids.shape
+    y = np.empty((tokens, d_model), dtype=np.uint16)
+    lib().tso_moe_ffn(C.c_int(kind), _p(gate_up), _p(down), C.c_int64(n_experts), C.c_int64(d_model), C.c_int64(ffn), _p(x16),
+                      _p(resid16), _p(ids), _p(w16), C.c_int64(tokens), C.c_int64(k), _p(y), C.c_int(threads))
+    return y
+
+
 def rms_norm(x, w, eps):
     x = np.ascontiguousarray(x, dtype=np.float32)
     w = np.ascontiguousarray(w, dtype=np.float32)

@@ -470,6 +470,76 @@ TSO_API void tso_gemm_quant(int kind, const uint8_t* w, int64_t rows, int64_t co
 }
 
 // ---------------------------------------------------------------------------
+// Mixture of experts: routing and the routed feed-forward
+// ---------------------------------------------------------------------------
+// router_topk_gemma4 (crates/runtime/src/real_forward_dispatch.rs:1135-1158): order by logit descending
+// (total_cmp), ties to the lower index; softmax over the selected logits only; times the per-expert scale.
+// The weights are what the host then uploads as f16 (crates/runtime/src/families/llama/moe.rs:118-127).
+TSO_API void tso_moe_route(const float* logits, int64_t tokens, int64_t n_experts, int64_t k, const float* scale,
+                           int32_t* ids, uint16_t* weights_f16) {
+    for (int64_t t = 0; t < tokens; t++) {
+        const float* row = logits + t * n_experts;
+        std::vector<int64_t> order((size_t)n_experts);
+        for (int64_t e = 0; e < n_experts; e++) order[(size_t)e] = e;
+        std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return row[a] > row[b]; });
+        const float mx = row[order[0]];
+        std::vector<float> ex((size_t)k);
+        float sum = 0.f;
+        for (int64_t r = 0; r < k; r++) {
+            ex[(size_t)r] = expf(row[order[(size_t)r]] - mx);
+            sum += ex[(size_t)r];
+        }
+        for (int64_t r = 0; r < k; r++) {
+            const int64_t e = order[(size_t)r];
+            ids[t * k + r] = (int32_t)e;
+            weights_f16[t * k + r] = f32_to_f16(ex[(size_t)r] / sum * (scale ? scale[e] : 1.0f));
+        }
+    }
+}
+
+// moe_phase1_gate_up_act_* and moe_phase2_down_reduce_k8_* (crates/gpu/src/shaders/moe_gguf.metal:561-678):
+//   acts[slot][f] = half(silu(gate . x) * (up . x));   y[d] = half(float(residual[d]) + sum_slot float(w[slot]) * (down[d] . acts[slot]))
+// with the slot sum taken in slot order.  gate_up: per expert [2F rows: gate then up][D cols]; down: per expert [D][F].
+TSO_API void tso_moe_ffn(int kind, const uint8_t* gate_up, const uint8_t* down, int64_t n_experts, int64_t d_model, int64_t ffn,
+                         const uint16_t* x_f16, const uint16_t* residual_f16, const int32_t* ids, const uint16_t* weights_f16,
+                         int64_t tokens, int64_t k, uint16_t* y_f16, int threads) {
+    (void)n_experts;
+    const int64_t gu_rb = row_bytes_of(kind, d_model), dn_rb = row_bytes_of(kind, ffn);
+    parallel_for(tokens, threads, [&](int64_t lo, int64_t hi) {
+        std::vector<float> x((size_t)d_model), deq((size_t)std::max(d_model, ffn)), acts((size_t)ffn), partial((size_t)(k * d_model));
+        for (int64_t t = lo; t < hi; t++) {
+            for (int64_t c = 0; c < d_model; c++) x[(size_t)c] = f16_to_f32(x_f16[t * d_model + c]);
+            for (int64_t s = 0; s < k; s++) {
+                const int64_t e = ids[t * k + s];
+                const uint8_t* gw = gate_up + e * 2 * ffn * gu_rb;
+                for (int64_t f = 0; f < ffn; f++) {
+                    float g = 0.f, u = 0.f;
+                    dequant_row(kind, gw + f * gu_rb, d_model, deq.data());
+                    for (int64_t c = 0; c < d_model; c++) g += deq[(size_t)c] * x[(size_t)c];
+                    dequant_row(kind, gw + (ffn + f) * gu_rb, d_model, deq.data());
+                    for (int64_t c = 0; c < d_model; c++) u += deq[(size_t)c] * x[(size_t)c];
+                    const float a = (g / (1.0f + expf(-g))) * u;
+                    acts[(size_t)f] = f16_to_f32(f32_to_f16(a));
+                }
+                const uint8_t* dw = down + e * d_model * dn_rb;
+                const float w = f16_to_f32(weights_f16[t * k + s]);
+                for (int64_t d = 0; d < d_model; d++) {
+                    dequant_row(kind, dw + d * dn_rb, ffn, deq.data());
+                    float v = 0.f;
+                    for (int64_t f = 0; f < ffn; f++) v += deq[(size_t)f] * acts[(size_t)f];
+                    partial[(size_t)(s * d_model + d)] = w * v;
+                }
+            }
+            for (int64_t d = 0; d < d_model; d++) {
+                float acc = f16_to_f32(residual_f16[t * d_model + d]);
+                for (int64_t s = 0; s < k; s++) acc += partial[(size_t)(s * d_model + d)];
+                y_f16[t * d_model + d] = f32_to_f16(acc);
+            }
+        }
+    });
+}
+
+// ---------------------------------------------------------------------------
 // Row operators with the reference's rounding points
 // ---------------------------------------------------------------------------
 

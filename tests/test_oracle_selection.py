@@ -259,3 +259,19 @@ def test_gather_rows_refuses_non_compactions(oracle):
     assert np.array_equal(rows[:3], want)
     assert oracle.gather_rows_inplace(rows, [1, 0]) == 1
     assert oracle.gather_rows_inplace(rows, [0, 2, 2]) == 1
+
+
+def test_moe_routing_follows_the_router_rules(oracle):
+    """router_topk_gemma4 (crates/runtime/src/real_forward_dispatch.rs:1135-1158): top-k by logit, ties to the lower
+    index, softmax over the selected logits only, times the per-expert scale."""
+    lg = np.array([[0.5, 2.0, -1.0, 2.0, 1.0, 0.0]], dtype=np.float32)
+    ids, w = oracle.moe_route(lg, 3)
+    assert ids.tolist() == [[1, 3, 4]]
+    e = np.exp(np.array([0.0, 0.0, -1.0], dtype=np.float32))
+    want = (e / e.sum()).astype(np.float32)
+    assert np.allclose(oracle.f16_bits_to_f32(w[0]), want, rtol=1e-3)
+    # not a softmax over all experts: the weights of the selected ones sum to one
+    assert abs(float(oracle.f16_bits_to_f32(w[0]).sum()) - 1.0) < 2e-3
+    ids2, w2 = oracle.moe_route(lg, 3, scale=np.array([1, 2, 1, 0.5, 1, 1], dtype=np.float32))
+    assert ids2.tolist() == [[1, 3, 4]]
+    assert np.allclose(oracle.f16_bits_to_f32(w2[0]), want * np.array([2, 0.5, 1], dtype=np.float32), rtol=1e-3)

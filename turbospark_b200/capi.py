@@ -225,6 +225,15 @@ class Ctx:
                                     C.byref(shaping_cfg), _vp(tokens), _vp(margins), _vp(scratch),
                                     C.c_size_t(scratch.nbytes)))
 
+    def moe_route(self, router_logits, tokens, n_experts, k, ids_out, weights_out, scale=None, stream=None):
+        self.check(lib().tsb_moe_route(self.h, stream, _vp(router_logits), C.c_int32(tokens), C.c_int32(n_experts), C.c_int32(k),
+                                       _vp(scale) if scale is not None else None, _vp(ids_out), _vp(weights_out)))
+
+    def moe_ffn(self, qtype, gate_up, down, n_experts, d_model, ffn, x, residual, ids, weights, tokens, k, y, stream=None):
+        self.check(lib().tsb_moe_ffn(self.h, stream, C.c_int32(qtype), _vp(gate_up), C.c_uint64(0), _vp(down), C.c_uint64(0),
+                                     C.c_int32(n_experts), C.c_int32(d_model), C.c_int32(ffn), _vp(x), _vp(residual), _vp(ids),
+                                     _vp(weights), C.c_int32(tokens), C.c_int32(k), _vp(y)))
+
     def residual_add(self, x, y, n, stream=None):
         self.check(lib().tsb_residual_add(self.h, stream, _vp(x), _vp(y), C.c_int64(n)))
 

@@ -386,7 +386,7 @@ struct Group {
 };
 template <int EPI>
 __device__ __forceinline__ int num_groups(int n_tiles, const EpiArgs& e) {
-    if (EPI == EPI_SILU) return n_tiles / 2;
+    if (EPI == EPI_SILU || EPI == EPI_MOE_ACT) return n_tiles / 2;
     if (EPI == EPI_ROPE_STORE) {
         const int tph = e.head_dim / 16;  // tiles per head
         return (e.n_q_heads + e.n_kv_heads) * (tph / 2) + e.n_kv_heads * tph;
@@ -396,7 +396,7 @@ __device__ __forceinline__ int num_groups(int n_tiles, const EpiArgs& e) {
 template <int EPI>
 __device__ __forceinline__ Group group_of(int g, int n_tiles, const EpiArgs& e) {
     Group r;
-    if (EPI == EPI_SILU) {
+    if (EPI == EPI_SILU || EPI == EPI_MOE_ACT) {
         r.tile0 = g, r.tile1 = n_tiles / 2 + g, r.n = 2;
     } else if (EPI == EPI_ROPE_STORE) {
         const int tph = e.head_dim / 16, pph = tph / 2;
@@ -425,6 +425,10 @@ __device__ __forceinline__ void run_epilogue(const EpiArgs& e, const Group& gr, 
             const int tok = idx >> 4, row = idx & 15;
             if (tok >= tokens || row0 + row >= rows) continue;
             int out_row = tok0 + tok;
+            if (e.y_rows) {
+                out_row = e.y_rows[tok0 + tok];
+                if (out_row < 0) continue;
+            }
             if (e.y_every > 1) {
                 if (out_row % e.y_every != e.y_every - 1) continue;
                 out_row /= e.y_every;
@@ -484,6 +488,27 @@ __device__ __forceinline__ void run_epilogue(const EpiArgs& e, const Group& gr, 
                 const float g = __half2float(__float2half_rn(inv * tile_out[tok * 16 + part * 8 + i]));
                 const float u = __half2float(__float2half_rn(inv * tile_out[NTOK * 16 + tok * 16 + part * 8 + i]));
                 // utility.metal:41-52: (g / (1 + exp(-g))) * u in f32
+                const float ex = (float)exp((double)(-g));
+                a[i] = __float2half_rn(__fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, ex)), u));
+                sx += __half2float(a[i]);
+            }
+            e.out.xp[act_xp_index(tok0 + tok, col0, ffn >> 8)] = act_pack8(a);
+        }
+        sx += __shfl_xor_sync(0xffffffffu, sx, 1);
+        if (active && part == 0) act_store_sum16(e.out.xs, tok0 + tok, gr.tile0 * TILE_ROWS, ffn >> 8, sx);
+    } else if constexpr (EPI == EPI_MOE_ACT) {
+        // crates/gpu/src/shaders/moe_gguf.metal:561-606: gate and up stay f32, acts = half(act(gate) * up)
+        const int tok = tid >> 1, part = tid & 1;
+        const bool active = tok < tokens;
+        const int ffn = (int)(rows / 2);
+        const int col0 = gr.tile0 * TILE_ROWS + part * 8;
+        float sx = 0.f;
+        if (active) {
+            __half a[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float g = tile_out[tok * 16 + part * 8 + i];
+                const float u = tile_out[NTOK * 16 + tok * 16 + part * 8 + i];
                 const float ex = (float)exp((double)(-g));
                 a[i] = __float2half_rn(__fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, ex)), u));
                 sx += __half2float(a[i]);
@@ -727,7 +752,7 @@ cudaError_t launch_one(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t 
     }
     const int n_tiles = (int)((rows + TILE_ROWS - 1) / TILE_ROWS);
     int groups = n_tiles;
-    if (EPI == EPI_SILU) groups = n_tiles / 2;
+    if (EPI == EPI_SILU || EPI == EPI_MOE_ACT) groups = n_tiles / 2;
     if (EPI == EPI_ROPE_STORE) {
         const int tph = args.head_dim / 16;
         groups = (args.n_q_heads + args.n_kv_heads) * (tph / 2) + args.n_kv_heads * tph;
@@ -754,14 +779,15 @@ cudaError_t launch_epi(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t 
         case EPI_SCALE: return launch_nt<QT, EPI_SCALE>(ctx, st, w, rows, units, act, tokens, tok0, args);
         case EPI_RESID_NORM: return launch_nt<QT, EPI_RESID_NORM>(ctx, st, w, rows, units, act, tokens, tok0, args);
         case EPI_SILU: return launch_nt<QT, EPI_SILU>(ctx, st, w, rows, units, act, tokens, tok0, args);
+        case EPI_MOE_ACT: return launch_nt<QT, EPI_MOE_ACT>(ctx, st, w, rows, units, act, tokens, tok0, args);
         case EPI_ROPE_STORE: return launch_nt<QT, EPI_ROPE_STORE>(ctx, st, w, rows, units, act, tokens, tok0, args);
         default: return cudaErrorInvalidValue;
     }
 }
 
 // x natural -> fragment-major operand + 16-column sums
-__global__ void act_prepare_kernel(const __half* __restrict__ x, int64_t x_stride, int tokens, int cols,
-                                   uint4* __restrict__ xp, uint4* __restrict__ xs) {
+__global__ void act_prepare_kernel(const __half* __restrict__ x, int64_t x_stride, const int32_t* __restrict__ src_rows, int tokens,
+                                   int cols, uint4* __restrict__ xp, uint4* __restrict__ xs) {
     pdl_wait();
     const int per_row = cols >> 3;
     const int padded = ((tokens + 7) >> 3) << 3;  // slots of the last tile are zero-filled
@@ -773,7 +799,8 @@ __global__ void act_prepare_kernel(const __half* __restrict__ x, int64_t x_strid
 #pragma unroll
     for (int i = 0; i < 8; i++) v[i] = 0.f;
     if (active && t < tokens) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)t * x_stride + e0);
+        const int src = src_rows ? src_rows[t] : t;
+        const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)src * x_stride + e0);
         const __half* hp = reinterpret_cast<const __half*>(&raw);
 #pragma unroll
         for (int i = 0; i < 8; i++) v[i] = __half2float(hp[i]);
@@ -789,7 +816,15 @@ cudaError_t launch_act_prepare(tsb_ctx* ctx, cudaStream_t st, const __half* x, i
     const int64_t n = (int64_t)act_tiles(tokens) * 8 * (cols / 8);
     const int threads = 256;  // even, and cols/8 is even, so the 16-column pairs never straddle rows
     return tsb_launch(ctx, act_prepare_kernel, dim3((unsigned)((n + threads - 1) / threads)), dim3(threads), 0, st, true,
-                      x, x_stride, tokens, cols, xp, xs);
+                      x, x_stride, (const int32_t*)nullptr, tokens, cols, xp, xs);
+}
+
+cudaError_t launch_act_prepare_gather(tsb_ctx* ctx, cudaStream_t st, const __half* x, int64_t x_stride, const int32_t* src_rows,
+                                      int tokens, int cols, uint4* xp, uint4* xs) {
+    const int64_t n = (int64_t)act_tiles(tokens) * 8 * (cols / 8);
+    const int threads = 256;
+    return tsb_launch(ctx, act_prepare_kernel, dim3((unsigned)((n + threads - 1) / threads)), dim3(threads), 0, st, true,
+                      x, x_stride, src_rows, tokens, cols, xp, xs);
 }
 
 cudaError_t launch_gemm_fused(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t rows, int64_t cols,

@@ -45,6 +45,7 @@ enum GemmEpi {
     EPI_RESID_NORM = 2,  // h += f16(acc); next operand = f16(h * g); partial sum of h^2   (o_proj, down)
     EPI_SILU = 3,        // pair (gate tile, up tile): operand = f16(silu(f16(inv*g)) * f16(inv*u))
     EPI_ROPE_STORE = 4,  // pair (low half, high half) of a q or k head: scale, rotate, q -> buffer, k -> cache; v -> cache
+    EPI_MOE_ACT = 5,     // pair (gate tile, up tile) of one expert: operand = f16(act(g) * u), no norm, no f16 rounding of g, u
 };
 
 // RMSNorm split around a matmul.  The reference computes xn = f16(x * w * inv_rms) and feeds it to the matmul
@@ -61,6 +62,7 @@ struct EpiArgs {
     void* y = nullptr;
     int64_t y_stride = 0;
     int y_f32 = 0;
+    const int32_t* y_rows = nullptr;  // EPI_PLAIN: output row of token t is y_rows[t] (negative: not stored) instead of t
     int y_every = 0;  // > 1: only the last token of every run of y_every tokens is stored, as output row token / y_every
     // EPI_RESID_NORM: residual stream h [tokens, rows], next norm weight g (bf16, [rows]), outputs
     __half* h = nullptr;
@@ -80,6 +82,9 @@ struct EpiArgs {
 // x [tokens, cols] f16 natural order -> ActOperand buffers.
 cudaError_t launch_act_prepare(tsb_ctx* ctx, cudaStream_t st, const __half* x, int64_t x_stride, int tokens, int cols,
                                uint4* xp, uint4* xs);
+// the same with a row gather: operand token t comes from x row src_rows[t] (device array)
+cudaError_t launch_act_prepare_gather(tsb_ctx* ctx, cudaStream_t st, const __half* x, int64_t x_stride, const int32_t* src_rows,
+                                      int tokens, int cols, uint4* xp, uint4* xs);
 
 // The matmul over verbatim block rows with the chosen epilogue.  rows = weight rows (for EPI_SILU the gate and
 // up halves back to back; for EPI_ROPE_STORE q heads, k heads, v heads back to back).
