@@ -892,6 +892,19 @@ int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_acti
     return TSB_OK;
 }
 
+int32_t session_prefill_rows(tsb_session* s, int stream, const int32_t* tokens, int n) {
+    TSB_REQUIRE(s->ctx, stream >= 0 && stream < s->n_streams, "stream %d outside the session", stream);
+    const int chunk = std::min(s->max_rows, 64);
+    for (int i = 0; i < n; i += chunk) {
+        const int m = std::min(chunk, n - i);
+        const int64_t pos = tsb_kv_cursor(s->target.kv, stream);
+        record_fed(s->target, stream, pos, tokens + i, m);
+        int32_t rc = forward_stream(s, s->target, stream, tokens + i, m, nullptr, nullptr, nullptr);
+        if (rc) return rc;
+    }
+    return TSB_OK;
+}
+
 // ---- tree round (crates/runtime/src/speculative.rs:461-560; tree shape helpers runtime/src/dflash_tree.rs:106-124)
 int32_t session_tree_round(tsb_session* s, int stream, const tsb_run_config* cfg, int32_t next, int64_t base,
                            std::vector<int32_t>& feed, std::vector<int32_t>& slot_parent, std::vector<int32_t>& picks,

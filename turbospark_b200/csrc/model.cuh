@@ -96,5 +96,7 @@ int32_t session_tree_round(tsb_session* s, int stream, const tsb_run_config* cfg
 // Keep path[0..keep) of the tree rows of both caches as a chain at base (compaction + cursors + fed-token record).
 int32_t session_tree_commit(tsb_session* s, int stream, int64_t base, const std::vector<int32_t>& feed,
                             const std::vector<uint32_t>& path, int keep, int drafter_rows);
+// produce_prefill for tokens[0..n) starting at the stream's cursor, several rows per pass (model.cu).
+int32_t session_prefill_rows(tsb_session* s, int stream, const int32_t* tokens, int n);
 // token = select(logits row of the last single-row target forward) for one stream (model.cu).
 int32_t session_select_target(tsb_session* s, const tsb_run_config* cfg, uint64_t uniform, int32_t* token_host);

@@ -67,8 +67,9 @@ int32_t admission(tsb_ctx* ctx, int n_prompt, const tsb_run_config* cfg, int max
 int32_t prefill(tsb_session* s, int stream, const int32_t* prompt, int n_prompt, bool with_drafter) {
     int32_t rc = tsb_producer_reset(s, stream);
     if (rc) return rc;
-    for (int i = 0; i + 1 < n_prompt; i++)
-        if ((rc = tsb_producer_produce_prefill(s, stream, prompt[i], i))) return rc;
+    // all but the last prompt token go through in chunks of rows (one chain pass each, no head); the last one alone,
+    // with the head.  Both generation loops prefill this way, so they start from the same cache contents.
+    if (n_prompt > 1 && (rc = session_prefill_rows(s, stream, prompt, n_prompt - 1))) return rc;
     if ((rc = tsb_producer_produce(s, stream, prompt[n_prompt - 1], n_prompt - 1, nullptr))) return rc;
     if (with_drafter && n_prompt >= 2) {
         // prime_drafter(prompt[i+1], i) for every i: after it the drafter holds rows 0..n_prompt-1
