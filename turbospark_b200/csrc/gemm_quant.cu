@@ -870,6 +870,19 @@ int32_t tsb_gemm_quant(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* re
                                        "Q4_K rows must start on a 16-byte boundary");
     DeviceGuard g(ctx);
     cudaStream_t st = (cudaStream_t)s;
+    {
+        // many token rows: the tensor-memory path dequantises every weight once per 128-row tile
+        static int wide_min = -1;
+        if (wide_min < 0) {
+            const char* env = getenv("TSB_WIDE_MIN");
+            wide_min = env ? atoi(env) : 16;
+        }
+        if (tokens >= wide_min && gemm_wide_supported(qtype, rows, cols, tokens)) {
+            TSB_CUDA(ctx, launch_gemm_wide_q4k(ctx, st, static_cast<const uint8_t*>(region) + w_off, rows, cols, (const __half*)x_f16, cols,
+                                               tokens, y, rows, y_f32 != 0));
+            return TSB_OK;
+        }
+    }
     const size_t xp_bytes = (act_xp_bytes(tokens, cols) + 255) & ~(size_t)255;
     uint8_t* tmp = nullptr;
     TSB_CUDA(ctx, cudaMallocAsync((void**)&tmp, xp_bytes + act_xs_bytes(tokens, cols), st));
