@@ -50,6 +50,33 @@ def test_gemm_matches_oracle(ctx, oracle, kind, rows, cols, tokens):
     assert np.array_equal(got16, oracle.f32_to_f16_bits(got))
 
 
+@pytest.mark.parametrize("rows,cols,tokens", [(128, 256, 24), (256, 2048, 40), (1024, 4096, 64), (384, 1536, 100), (128, 14336, 33)])
+def test_many_token_rows_take_the_tensor_memory_path_and_match_the_oracle(ctx, oracle, rows, cols, tokens):
+    """24 token rows and more of a Q4_K matrix whose rows are a multiple of 128 run on tcgen05 with the dequantised
+    operand in tensor memory; q*sc is exact in f16 and d, dmin are applied in fp32, so the sums match as closely as
+    the few-row path's."""
+    q = _weights(oracle, 0, rows, cols, 5)
+    rng = np.random.default_rng(tokens)
+    x16 = oracle.f32_to_f16_bits(rng.standard_normal((tokens, cols)).astype(np.float32))
+    want = oracle.gemm_quant(0, q, rows, cols, oracle.f16_bits_to_f32(x16), threads=8)
+    w = ctx.upload_weights(q)
+    xd = ctx.to_device(x16)
+    yd = ctx.alloc(tokens * rows * 4)
+    ctx.gemm_quant(0, w, rows, cols, xd, yd, tokens, y_f32=True)
+    ctx.sync()
+    got = yd.download(np.float32, tokens * rows).reshape(tokens, rows)
+    _check(got, want)
+    yh = ctx.alloc(tokens * rows * 2)
+    ctx.gemm_quant(0, w, rows, cols, xd, yh, tokens, y_f32=False)
+    ctx.sync()
+    assert np.array_equal(yh.download(np.uint16, tokens * rows).reshape(tokens, rows), oracle.f32_to_f16_bits(got))
+    # a token's row does not depend on its batch mates: the first 24 rows alone give the same bits
+    y2 = ctx.alloc(24 * rows * 4)
+    ctx.gemm_quant(0, w, rows, cols, xd, y2, 24, y_f32=True)
+    ctx.sync()
+    assert np.array_equal(y2.download(np.float32, 24 * rows).reshape(24, rows), got[:24])
+
+
 @pytest.mark.parametrize("kind", [0, 1, 2])
 def test_a_tokens_result_does_not_depend_on_the_batch(ctx, oracle, kind):
     # the verify batch must reproduce the decode step bit for bit, at every width

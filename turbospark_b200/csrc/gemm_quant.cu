@@ -875,7 +875,7 @@ int32_t tsb_gemm_quant(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* re
         static int wide_min = -1;
         if (wide_min < 0) {
             const char* env = getenv("TSB_WIDE_MIN");
-            wide_min = env ? atoi(env) : 16;
+            wide_min = env ? atoi(env) : 24;
         }
         if (tokens >= wide_min && gemm_wide_supported(qtype, rows, cols, tokens)) {
             TSB_CUDA(ctx, launch_gemm_wide_q4k(ctx, st, static_cast<const uint8_t*>(region) + w_off, rows, cols, (const __half*)x_f16, cols,

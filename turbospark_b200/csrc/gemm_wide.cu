@@ -316,13 +316,16 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1)
                         const uint32_t a_col = tmem_a0 + as * WIDE_A_COLS + lane_base;
                         tc_st32(a_col + 32 * g, r);
                         tc_st2(a_col + 128 + 2 * g, m0, m1);
+                    }
+                    // while the stores to tensor memory are in flight: the previous block's products are ready by now
+                    // (its MMAs ran under this block's dequantisation)
+                    if (blk > 0) drain(nb - 1, d_prev, dmin_prev, acc);
+                    if (ok) {
                         tc_wait_st();
                         tc_fence_before();
                     }
                     __syncwarp();
                     if (lane == 0 && ok) mbar_arrive(&bars->a_full[as]);
-                    // the previous block's products are ready by now (its MMAs ran under this block's dequantisation)
-                    if (blk > 0) drain(nb - 1, d_prev, dmin_prev, acc);
                     d_prev = d, dmin_prev = dmin;
                 }
                 __syncwarp();
