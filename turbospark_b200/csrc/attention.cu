@@ -495,7 +495,15 @@ AttnPlan attn_plan(const tsb_ctx* ctx, const tsb_kv* kv, int rows, int rows_per_
     for (int i = 0; i < 3; i++) {
         const int cs = 1 << i;
         int resident = max_clusters(ctx->device, kv->view.head_dim, p.mt, cs);  // clusters
-        if (resident > ctx->sm_count / cs) resident = ctx->sm_count / cs;       // one CTA per SM is enough to saturate loads
+        {
+            static int per_sm = 0;  // CTAs per SM the plan aims for (TSB_ATTN_CTAS_PER_SM overrides, for experiments)
+            if (!per_sm) {
+                const char* env = getenv("TSB_ATTN_CTAS_PER_SM");
+                per_sm = env ? atoi(env) : 2;
+                if (per_sm < 1) per_sm = 1;
+            }
+            if (resident > ctx->sm_count * per_sm / cs) resident = ctx->sm_count * per_sm / cs;
+        }
         int clusters_per = resident / base_ctas;                                        // per (stream, head, tile)
         if (clusters_per < 1) clusters_per = 1;
         if (clusters_per > MAX_SPLITS) clusters_per = MAX_SPLITS;
