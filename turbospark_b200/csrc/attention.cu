@@ -270,15 +270,17 @@ __global__ void __launch_bounds__(ATT_THREADS * MT)
     cp_async_wait<0>();
     pdl_launch_dependents();
 
-    // ---- every warp leaves its (m, l, O) for its 16 queries in shared memory: wo[warp][16][HD], wml[warp][16]
+    // ---- every warp leaves its (m, l, O) for its 16 queries in shared memory: wo[warp][16][HDP], wml[warp][16]
+    // (rows padded by four floats: the eight query rows a warp stores at once land in different banks)
+    constexpr int HDP = HD + 4;
     float* wo = reinterpret_cast<float*>(smem);
-    float2* wml = reinterpret_cast<float2*>(smem + (size_t)4 * MT * 16 * HD * sizeof(float));
+    float2* wml = reinterpret_cast<float2*>(smem + (size_t)4 * MT * 16 * HDP * sizeof(float));
     {
-        float* dst = wo + (size_t)warp * 16 * HD;
+        float* dst = wo + (size_t)warp * 16 * HDP;
 #pragma unroll
         for (int n = 0; n < NO; n++) {
-            *reinterpret_cast<float2*>(dst + gid * HD + n * 8 + 2 * tig) = make_float2(o[n][0], o[n][1]);
-            *reinterpret_cast<float2*>(dst + (gid + 8) * HD + n * 8 + 2 * tig) = make_float2(o[n][2], o[n][3]);
+            *reinterpret_cast<float2*>(dst + gid * HDP + n * 8 + 2 * tig) = make_float2(o[n][0], o[n][1]);
+            *reinterpret_cast<float2*>(dst + (gid + 8) * HDP + n * 8 + 2 * tig) = make_float2(o[n][2], o[n][3]);
         }
         if (tig == 0) {
             wml[warp * 16 + gid] = make_float2(m_run[0], l_run[0]);
@@ -293,7 +295,7 @@ __global__ void __launch_bounds__(ATT_THREADS * MT)
     // eight columns of one query.
     constexpr int TPH = HD / 8;             // 8-column runs per head
     constexpr int QPP = NTHR / TPH;         // queries finished per pass over the threads
-    float* co = wo + (size_t)4 * MT * 16 * HD + 2 * 4 * MT * 16;  // [QT][HD] after wo and wml
+    float* co = wo + (size_t)4 * MT * 16 * HDP + 2 * 4 * MT * 16;  // [QT][HD] after wo and wml
     float2* cml = reinterpret_cast<float2*>(co + (size_t)QT * HD);
     const int part = threadIdx.x % TPH;
 #pragma unroll
@@ -312,7 +314,7 @@ __global__ void __launch_bounds__(ATT_THREADS * MT)
             const float2 v = wml[w * 16 + qq];
             const float wgt = exp2f(v.x - mu);
             den += v.y * wgt;
-            const float4* po = reinterpret_cast<const float4*>(wo + ((size_t)w * 16 + qq) * HD + part * 8);
+            const float4* po = reinterpret_cast<const float4*>(wo + ((size_t)w * 16 + qq) * HDP + part * 8);
             const float4 a = po[0], b2 = po[1];
             accv[0] += a.x * wgt, accv[1] += a.y * wgt, accv[2] += a.z * wgt, accv[3] += a.w * wgt;
             accv[4] += b2.x * wgt, accv[5] += b2.y * wgt, accv[6] += b2.z * wgt, accv[7] += b2.w * wgt;
@@ -514,7 +516,13 @@ AttnPlan attn_plan(const tsb_ctx* ctx, const tsb_kv* kv, int rows, int rows_per_
     }
     // the largest cluster that keeps at least 4/5 of the parallelism: fewer shares travel through memory
     int best_splits = cand_splits[0] > 0 ? cand_splits[0] : 1, best_cs = 1;
-    for (int i = 2; i >= 1; i--)
+    static int max_cs_log2 = -1;  // TSB_ATTN_MAX_CLUSTER = 1, 2 or 4 limits the cluster size (experiments)
+    if (max_cs_log2 < 0) {
+        const char* env = getenv("TSB_ATTN_MAX_CLUSTER");
+        const int v = env ? atoi(env) : 4;
+        max_cs_log2 = v >= 4 ? 2 : (v >= 2 ? 1 : 0);
+    }
+    for (int i = max_cs_log2; i >= 1; i--)
         if (cand_splits[i] * 5 >= most * 4 && cand_splits[i] > 0) {
             best_splits = cand_splits[i], best_cs = 1 << i;
             break;
