@@ -340,29 +340,33 @@ __global__ void __launch_bounds__(ATT_THREADS * MT)
 #pragma unroll
         for (int i = 0; i < 8; i++) accv[i] = 0.f;
         if (active) {
-            float2 ml[8];
-            float4 va[8], vb[8];
-#pragma unroll
-            for (int c = 0; c < 8; c++)
-                if (c < cluster_size) {
-                    const float2* rml = cluster_size > 1 ? cluster.map_shared_rank(cml, c) : cml;
-                    const float* ro = cluster_size > 1 ? cluster.map_shared_rank(co, c) : co;
-                    ml[c] = rml[ql];
-                    const float4* po = reinterpret_cast<const float4*>(ro + (size_t)ql * HD + part * 8);
-                    va[c] = po[0], vb[c] = po[1];
-                }
-#pragma unroll
-            for (int c = 0; c < 8; c++)
-                if (c < cluster_size) m = fmaxf(m, ml[c].x);
+            // members in rank order, eight at a time (all loads of a batch are in flight together)
+            for (int c = 0; c < cluster_size; c++) {
+                const float2* rml = cluster_size > 1 ? cluster.map_shared_rank(cml, c) : cml;
+                m = fmaxf(m, rml[ql].x);
+            }
             const float mu = (m == -INFINITY) ? 0.f : m;
+            for (int c0 = 0; c0 < cluster_size; c0 += 8) {
+                float2 ml[8];
+                float4 va[8], vb[8];
 #pragma unroll
-            for (int c = 0; c < 8; c++)
-                if (c < cluster_size) {
-                    const float wgt = exp2f(ml[c].x - mu);
-                    den += ml[c].y * wgt;
-                    accv[0] += va[c].x * wgt, accv[1] += va[c].y * wgt, accv[2] += va[c].z * wgt, accv[3] += va[c].w * wgt;
-                    accv[4] += vb[c].x * wgt, accv[5] += vb[c].y * wgt, accv[6] += vb[c].z * wgt, accv[7] += vb[c].w * wgt;
-                }
+                for (int c = 0; c < 8; c++)
+                    if (c0 + c < cluster_size) {
+                        const float2* rml = cluster_size > 1 ? cluster.map_shared_rank(cml, c0 + c) : cml;
+                        const float* ro = cluster_size > 1 ? cluster.map_shared_rank(co, c0 + c) : co;
+                        ml[c] = rml[ql];
+                        const float4* po = reinterpret_cast<const float4*>(ro + (size_t)ql * HD + part * 8);
+                        va[c] = po[0], vb[c] = po[1];
+                    }
+#pragma unroll
+                for (int c = 0; c < 8; c++)
+                    if (c0 + c < cluster_size) {
+                        const float wgt = exp2f(ml[c].x - mu);
+                        den += ml[c].y * wgt;
+                        accv[0] += va[c].x * wgt, accv[1] += va[c].y * wgt, accv[2] += va[c].z * wgt, accv[3] += va[c].w * wgt;
+                        accv[4] += vb[c].x * wgt, accv[5] += vb[c].y * wgt, accv[6] += vb[c].z * wgt, accv[7] += vb[c].w * wgt;
+                    }
+            }
         }
         const int row = row_first + (active ? qi / G : 0), head = kvh * G + (active ? qi % G : 0);
         const int e0 = head * HD + part * 8;
@@ -446,12 +450,17 @@ __global__ void __launch_bounds__(ATT_THREADS * MT)
 // How many clusters of `cs` CTAs of the kernel can be resident at once (cached per shape and device).
 template <int HD, int MT>
 static int max_clusters_t(int device, int cs) {
-    static int cache[ATTN_MAX_DEVICES][4] = {};
-    const int slot = cs == 8 ? 3 : cs == 4 ? 2 : cs == 2 ? 1 : 0;
+    static int cache[ATTN_MAX_DEVICES][5] = {};
+    const int slot = cs == 16 ? 4 : cs == 8 ? 3 : cs == 4 ? 2 : cs == 2 ? 1 : 0;
     if (device < 0 || device >= ATTN_MAX_DEVICES) return 0;
-    if (cache[device][slot]) return cache[device][slot];
+    if (cache[device][slot]) return cache[device][slot] > 0 ? cache[device][slot] : 0;
     const size_t smem = (size_t)NST * 2 * TILE_TOKENS * HD * sizeof(__half);
     if (cudaFuncSetAttribute(attn_partial_kernel<HD, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
+    // clusters of sixteen are beyond the portable size: allowed on this part, the occupancy query says whether they fit
+    if (cudaFuncSetAttribute(attn_partial_kernel<HD, MT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+        cudaGetLastError();
+        if (cs > 8) return 0;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(cs * 64, 1, 1);
     cfg.blockDim = dim3(ATT_THREADS * MT);
@@ -471,8 +480,8 @@ static int max_clusters_t(int device, int cs) {
         n = per_sm * sms;
     }
     cudaGetLastError();
-    cache[device][slot] = n > 0 ? n : 1;
-    return cache[device][slot];
+    cache[device][slot] = n > 0 ? n : (cs > 1 ? -1 : 1);  // -1: clusters of this size do not fit at all
+    return cache[device][slot] > 0 ? cache[device][slot] : 0;
 }
 static int max_clusters(int device, int hd, int mt, int cs) {
     if (hd == 128) return mt == 2 ? max_clusters_t<128, 2>(device, cs) : max_clusters_t<128, 1>(device, cs);
@@ -493,40 +502,37 @@ AttnPlan attn_plan(const tsb_ctx* ctx, const tsb_kv* kv, int rows, int rows_per_
     const int base_ctas = p.groups * kv->view.kv_heads * p.n_qtiles;
     // one wave: as many chunks per (stream, kv head, query tile) as the device can hold at once, in clusters of
     // up to four CTAs (larger clusters leave SMs of a GPC unused)
-    int cand_splits[3] = {1, 1, 1}, most = 1;  // for cluster sizes 1, 2, 4
-    for (int i = 0; i < 3; i++) {
+    int cand_splits[5] = {1, 0, 0, 0, 0}, cand_clusters[5] = {1, 0, 0, 0, 0}, most = 1;  // for cluster sizes 1, 2, 4, 8, 16
+    static int per_sm = 0, max_cs_log2 = -1;  // TSB_ATTN_CTAS_PER_SM, TSB_ATTN_MAX_CLUSTER override (experiments)
+    if (!per_sm) {
+        const char* env = getenv("TSB_ATTN_CTAS_PER_SM");
+        per_sm = env ? atoi(env) : 2;
+        if (per_sm < 1) per_sm = 1;
+        env = getenv("TSB_ATTN_MAX_CLUSTER");
+        const int v = env ? atoi(env) : 4;  // larger clusters measured slower: fewer of them fit, and their barriers cost more
+        max_cs_log2 = v >= 16 ? 4 : v >= 8 ? 3 : v >= 4 ? 2 : (v >= 2 ? 1 : 0);
+    }
+    for (int i = 0; i <= max_cs_log2; i++) {
         const int cs = 1 << i;
         int resident = max_clusters(ctx->device, kv->view.head_dim, p.mt, cs);  // clusters
-        {
-            static int per_sm = 0;  // CTAs per SM the plan aims for (TSB_ATTN_CTAS_PER_SM overrides, for experiments)
-            if (!per_sm) {
-                const char* env = getenv("TSB_ATTN_CTAS_PER_SM");
-                per_sm = env ? atoi(env) : 2;
-                if (per_sm < 1) per_sm = 1;
-            }
-            if (resident > ctx->sm_count * per_sm / cs) resident = ctx->sm_count * per_sm / cs;
+        if (resident > ctx->sm_count * per_sm / cs) resident = ctx->sm_count * per_sm / cs;
+        int clusters_per = resident / base_ctas;  // per (stream, head, tile)
+        if (clusters_per < 1) {
+            if (cs > 1) continue;  // clusters of this size would not all be resident: a second wave costs more than it saves
+            clusters_per = 1;
         }
-        int clusters_per = resident / base_ctas;                                        // per (stream, head, tile)
-        if (clusters_per < 1) clusters_per = 1;
         if (clusters_per > MAX_SPLITS) clusters_per = MAX_SPLITS;
         int splits = clusters_per * cs;
         if (splits > tiles_total) splits = (tiles_total / cs) * cs;
         cand_splits[i] = splits;  // 0 when a cluster would be longer than the context
+        cand_clusters[i] = splits / cs;
         if (splits > most) most = splits;
     }
     // the largest cluster that keeps at least 4/5 of the parallelism: fewer shares travel through memory
     int best_splits = cand_splits[0] > 0 ? cand_splits[0] : 1, best_cs = 1;
-    static int max_cs_log2 = -1;  // TSB_ATTN_MAX_CLUSTER = 1, 2 or 4 limits the cluster size (experiments)
-    if (max_cs_log2 < 0) {
-        const char* env = getenv("TSB_ATTN_MAX_CLUSTER");
-        const int v = env ? atoi(env) : 4;
-        max_cs_log2 = v >= 4 ? 2 : (v >= 2 ? 1 : 0);
-    }
-    for (int i = max_cs_log2; i >= 1; i--)
-        if (cand_splits[i] * 5 >= most * 4 && cand_splits[i] > 0) {
-            best_splits = cand_splits[i], best_cs = 1 << i;
-            break;
-        }
+    bool chosen = false;
+    for (int i = max_cs_log2; i >= 1 && !chosen; i--)
+        if (cand_splits[i] * 5 >= most * 4 && cand_splits[i] > 0) best_splits = cand_splits[i], best_cs = 1 << i, chosen = true;
     p.cluster_size = best_cs;
     p.n_splits = best_splits;
     const int tiles_per = (tiles_total + p.n_splits - 1) / p.n_splits;

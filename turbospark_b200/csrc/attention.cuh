@@ -6,7 +6,7 @@
 struct AttnPlan {
     int chunk;         // KV positions per CTA (multiple of 64)
     int n_splits;      // grid.x = clusters * cluster_size
-    int cluster_size;  // CTAs whose shares are merged through distributed shared memory (1, 2, 4 or 8)
+    int cluster_size;  // CTAs whose shares are merged through distributed shared memory (1, 2, 4, 8 or 16)
     int mt;            // 16-query tiles per CTA (1 or 2)
     int n_qtiles;      // query tiles per (stream, kv head)
     int groups;        // streams in the batch
