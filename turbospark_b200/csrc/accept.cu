@@ -59,6 +59,14 @@ __device__ __forceinline__ uint32_t desc_key(float x) {
     u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
     return ~u;
 }
+// The same order on the 16 bits of an f16 logit (the rows are f16, so 16 bits carry the whole order; -0 ranks as +0,
+// as it does when the values are compared).
+__device__ __forceinline__ uint32_t desc_key16(__half h) {
+    uint32_t u = __half_as_ushort(h);
+    if (u == 0x8000u) u = 0;
+    u = (u & 0x8000u) ? (~u & 0xFFFFu) : (u | 0x8000u);
+    return ~u & 0xFFFFu;
+}
 
 // w_i of reweight (choose.rs:296-321): ((e/sum)/top)^(1/T), top = max_i e_i/sum = 1/sum.
 __device__ __forceinline__ double weight_of(double e, double sum, double top, double inv_t, bool unit_t) {
@@ -81,11 +89,12 @@ __device__ __forceinline__ double block_sum_f64(double v, double* red) {
 
 // Sum of one double per CTA over the cluster, ranks in order.  Slot selects which field of the exchange area.
 __device__ __forceinline__ double cluster_sum_f64(cg::cluster_group& cluster, Xchg* x, int slot, double mine) {
+    // one barrier: a slot is written once per kernel (or again only after other cluster barriers), so nobody can
+    // overwrite it while a neighbour still reads
     if (threadIdx.x == 0) x->d[slot] = mine;
     cluster.sync();
     double t = 0.0;
     for (int r = 0; r < CL; r++) t += cluster.map_shared_rank(x, r)->d[slot];
-    cluster.sync();
     return t;
 }
 
@@ -179,6 +188,7 @@ __global__ void __launch_bounds__(ACC_THREADS)
     }
     pdl_launch_dependents();
     if (rank == 0 && threadIdx.x == 0) stats[row_id] = st;
+    cluster.sync();  // nobody leaves while a neighbour may still read its exchange area
 }
 
 // probability of one token under a row's shaped distribution (distribution.rs:61-66 over the full support)
@@ -211,59 +221,52 @@ __device__ int cluster_radix_draw(cg::cluster_group& cluster, DrawShared& c, con
     const int rank = (int)cluster.block_rank();
     uint32_t prefix = 0;
     unsigned long long before = 0;
-    const int shifts[3] = {21, 10, 0};
-    const int widths[3] = {11, 11, 10};
-    int done_bits = 0;
-    for (int pass = 0; pass < 3; pass++) {
-        for (int i = threadIdx.x; i < NBINS; i += ACC_THREADS) c.hist[i] = 0;
+    constexpr int RB = 256;  // bins per pass: the 16-bit key is resolved in two passes of eight bits
+    for (int pass = 0; pass < 2; pass++) {
+        const int shift = pass ? 0 : 8;
+        for (int i = threadIdx.x; i < RB; i += ACC_THREADS) c.hist[i] = 0;
         __syncthreads();
-        const uint32_t hi_mask = done_bits ? (0xFFFFFFFFu << (32 - done_bits)) : 0u;
         for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
-            const uint32_t kd = desc_key(__half2float(krow[sl.lo + j]));
-            if ((kd & hi_mask) == prefix) {
+            const uint32_t kd = desc_key16(krow[sl.lo + j]);
+            if (pass == 0 || (kd >> 8) == (prefix >> 8)) {
                 const unsigned long long m = fp[j];
-                if (m) atomicAdd(&c.hist[(kd >> shifts[pass]) & ((1u << widths[pass]) - 1)], m);
+                if (m) atomicAdd(&c.hist[(kd >> shift) & (RB - 1)], m);
             }
         }
         cluster.sync();
         if (rank == 0) {
-            // sum the eight histograms bin by bin, scan, find the bin the target falls into
-            constexpr int PER = NBINS / ACC_THREADS;  // 2
-            unsigned long long loc[PER], s = 0;
-#pragma unroll
-            for (int j = 0; j < PER; j++) {
-                unsigned long long t = 0;
-                for (int rr = 0; rr < CL; rr++) t += cluster.map_shared_rank(c.hist, rr)[threadIdx.x * PER + j];
-                loc[j] = t, s += t;
-            }
-            unsigned long long v = s;
+            // sum the members' histograms bin by bin, scan, find the bin the target falls into
+            unsigned long long t = 0;
+            if (threadIdx.x < RB)
+                for (int rr = 0; rr < CL; rr++) t += cluster.map_shared_rank(c.hist, rr)[threadIdx.x];
+            unsigned long long v = t;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const unsigned long long n = __shfl_up_sync(0xffffffffu, v, o);
                 if ((threadIdx.x & 31) >= o) v += n;
             }
             if ((threadIdx.x & 31) == 31) c.scan[threadIdx.x >> 5] = v;
-            if (threadIdx.x == 0) c.sel_bin = NBINS, c.sel_before = 0;
+            if (threadIdx.x == 0) c.sel_bin = RB, c.sel_before = 0;
             __syncthreads();
-            unsigned long long wbase = 0;
-            for (int i = 0; i < (int)(threadIdx.x >> 5); i++) wbase += c.scan[i];
-            unsigned long long run = before + wbase + v - s;
-#pragma unroll
-            for (int j = 0; j < PER; j++) {
-                const unsigned long long after = run + loc[j];
-                if (target >= run && target < after) c.sel_bin = threadIdx.x * PER + j, c.sel_before = run;
-                run = after;
+            if (threadIdx.x < RB) {
+                unsigned long long wbase = 0;
+                for (int i = 0; i < (int)(threadIdx.x >> 5); i++) wbase += c.scan[i];
+                const unsigned long long run = before + wbase + v - t, after = run + t;
+                if (target >= run && target < after) c.sel_bin = threadIdx.x, c.sel_before = run;
             }
         }
         cluster.sync();
         const DrawShared* root = cluster.map_shared_rank(&c, 0);
         const unsigned int bin = root->sel_bin;
         const unsigned long long bef = root->sel_before;
-        cluster.sync();
-        if (bin == NBINS) return -1;
-        prefix |= bin << shifts[pass];
+        // no barrier here: rank 0 rewrites the selection only after the next pass's first cluster barrier, which every
+        // member reaches after this read
+        if (bin == RB) {
+            cluster.sync();  // leave together: the caller may go on to use the exchange area
+            return -1;
+        }
+        prefix |= bin << shift;
         before = bef;
-        done_bits += widths[pass];
     }
     // every member shares the key: walk them in index order.  Threads own contiguous runs of their CTA's slice;
     // CTAs are ordered by rank.
@@ -271,7 +274,7 @@ __device__ int cluster_radix_draw(cg::cluster_group& cluster, DrawShared& c, con
     const int lo = min(sl.n, (int)threadIdx.x * per), hi = min(sl.n, lo + per);
     unsigned long long mine = 0;
     for (int j = lo; j < hi; j++)
-        if (desc_key(__half2float(krow[sl.lo + j])) == prefix) mine += fp[j];
+        if (desc_key16(krow[sl.lo + j]) == prefix) mine += fp[j];
     unsigned long long v = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -294,7 +297,7 @@ __device__ int cluster_radix_draw(cg::cluster_group& cluster, DrawShared& c, con
     unsigned long long run = before + rank_base + wbase + v - mine;
     DrawShared* root = cluster.map_shared_rank(&c, 0);
     for (int j = lo; j < hi; j++) {
-        if (desc_key(__half2float(krow[sl.lo + j])) != prefix) continue;
+        if (desc_key16(krow[sl.lo + j]) != prefix) continue;
         const unsigned long long after = run + fp[j];
         if (target >= run && target < after) {  // exactly one thread of one CTA
             root->result = sl.lo + j;

@@ -61,7 +61,7 @@ __device__ __forceinline__ uint32_t tile_off(int r, int c) {
 // Grid: x = KV chunks (a multiple of the cluster size; the CTAs of a cluster hold consecutive chunks of the same
 // queries), y = kv head * query tiles, z = streams.
 template <int HD, int MT>
-__global__ void __launch_bounds__(ATT_THREADS * MT)
+__global__ void __maxnreg__(136)
     attn_partial_kernel(KvView kv, int layer, const __half* __restrict__ q, int64_t q_stride,
                         const tsb_row_desc* __restrict__ rows, int rows_per_seq, int n_q_heads, float scale_log2e,
                         int chunk, int cluster_size, float* __restrict__ part_o, float2* __restrict__ part_ml,
