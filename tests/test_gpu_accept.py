@@ -25,11 +25,11 @@ def _logits(oracle, rng, batch, k, vocab, noise=1.0):
     return oracle.f32_to_f16_bits(tgt), oracle.f32_to_f16_bits(drf)
 
 
-def _run_accept(ctx, oracle, t16, d16, props, unis, temperature):
+def _run_accept(ctx, oracle, t16, d16, props, unis, temperature, **shape):
     import turbospark_b200 as tsb
     batch, kp1, vocab = t16.shape
     k = kp1 - 1
-    cfg = tsb.shaping(temperature=temperature, seed=4)
+    cfg = tsb.shaping(temperature=temperature, seed=4, **shape)
     out = ctx.alloc(batch * C.sizeof(tsb.AcceptOut))
     scratch = ctx.alloc(ctx.accept_scratch_bytes(batch, k, vocab))
     ctx.accept(ctx.to_device(t16), ctx.to_device(d16) if k else None, ctx.to_device(props) if k else None,
@@ -127,8 +127,9 @@ def test_unsupported_shaping_is_refused(ctx, oracle):
     out = ctx.alloc(256)
     scratch = ctx.alloc(ctx.accept_scratch_bytes(1, 1, 64))
     buf = ctx.alloc(4096)
-    for cfg in (tsb.shaping(temperature=0.7, top_k=64), tsb.shaping(temperature=0.7, top_p=0.95),
-                tsb.shaping(temperature=1.0, repetition_penalty=1.1), tsb.shaping(temperature=-1.0)):
+    for cfg in (tsb.shaping(temperature=0.7, top_k=300), tsb.shaping(temperature=0.7, top_p=1.5), tsb.shaping(temperature=0.7, min_p=2.0),
+                tsb.shaping(temperature=1.0, repetition_penalty=1.1), tsb.shaping(temperature=1.0, presence_penalty=0.5),
+                tsb.shaping(temperature=-1.0)):
         with pytest.raises(tsb.TsbError):
             ctx.accept(buf, buf, buf, buf, 1, 1, 64, cfg, out, scratch)
 
@@ -155,3 +156,56 @@ def test_sample_matches_the_oracle_draw(ctx, oracle, temperature):
     if temperature != 0.0:
         for b in range(4):
             assert oracle.select(lg[b], ocfg, None, b) == got[b]
+
+
+SHAPES = [dict(top_k=64, top_p=0.95), dict(top_p=0.9), dict(top_k=8), dict(min_p=0.05), dict(top_k=40, top_p=0.8, min_p=0.02),
+          dict(top_k=1), dict(top_p=1.0)]
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=[str(sorted(d.items())) for d in SHAPES])
+@pytest.mark.parametrize("temperature", [1.0, 0.7])
+def test_truncated_sampling_matches_the_oracle_draw(ctx, oracle, temperature, shape):
+    """top-k, top-p and min-p on the device: the support is the same rank-order prefix the reference keeps
+    (crates/selection/src/choose.rs:176-222) and the draw over it lands on the same token."""
+    import turbospark_b200 as tsb
+    rng = np.random.default_rng(21)
+    batch, vocab = 32, 32000
+    lg = oracle.f32_to_f16_bits(rng.standard_normal((batch, vocab)).astype(np.float32) * 3.0)
+    lg[0, :] = lg[0, 0]                # every logit equal: the rank order is the index order
+    lg[1, 100:200] = lg[1, 100]        # a run of ties crossing the top-k cut
+    unis = np.array([oracle.uniform_u64(0, 2, i) for i in range(batch)], dtype=np.uint64)
+    toks = ctx.alloc(batch * 4)
+    margins = ctx.alloc(batch * 8)
+    scratch = ctx.alloc(ctx.accept_scratch_bytes(batch, 0, vocab))
+    ctx.sample(ctx.to_device(lg), ctx.to_device(unis), batch, vocab, tsb.shaping(temperature=temperature, **shape), toks, margins, scratch)
+    ctx.sync()
+    got = toks.download(np.int32, batch)
+    ocfg = oracle.shaping(temperature=temperature, seed=2, **shape)
+    for b in range(batch):
+        want, margin = oracle.sample(lg[b], ocfg, int(unis[b]))
+        assert got[b] == want, (b, got[b], want, margin)
+
+
+@pytest.mark.parametrize("shape", SHAPES[:5], ids=[str(sorted(d.items())) for d in SHAPES[:5]])
+@pytest.mark.parametrize("temperature", [1.0, 0.7])
+def test_truncated_acceptance_matches_the_oracle(ctx, oracle, temperature, shape):
+    rng = np.random.default_rng(31)
+    vocab, batch, k = 32000, 12, 4
+    t16, d16 = _logits(oracle, rng, batch, k, vocab, noise=0.5)
+    ocfg = oracle.shaping(temperature=temperature, seed=4, **shape)
+    props = np.zeros((batch, k), dtype=np.int32)
+    unis = np.zeros((batch, 2 * k + 1), dtype=np.uint64)
+    for b in range(batch):
+        for i in range(k):
+            props[b, i] = oracle.sample(d16[b, i], ocfg, oracle.uniform_u64(1, 4, 1000 * b + i))[0]
+        for j in range(2 * k + 1):
+            unis[b, j] = oracle.uniform_u64(1, 4, 5000 + 100 * b + j)
+    props[0, 1] = int(np.argmin(oracle.f16_bits_to_f32(t16[0, 1])))  # a proposal outside the target's support: p(x) = 0
+    outs = _run_accept(ctx, oracle, t16, d16, props, unis, temperature, **shape)
+    for b in range(batch):
+        acc, toks, draws, margins = oracle.accept_round(t16[b], d16[b], props[b], ocfg, unis[b])
+        o = outs[b]
+        assert o.status == 0
+        assert o.accepted == acc, (b, o.accepted, acc)
+        assert list(o.tokens[:acc + 1]) == list(toks), (b, list(o.tokens[:acc + 1]), list(toks))
+        assert o.draws == draws

@@ -177,7 +177,7 @@ def test_stop_token_budget_and_refusals(rig, oracle):
     assert r1.reason == r2.reason == 1 and np.array_equal(e1, e2) and np.array_equal(h1, h2)
     assert e2[-1] == stop_tok and len(h2) == len(prompt) + len(e2) - 1  # the stopping token is counted, not fed
     for bad in (tsb.run_config(tsb.shaping(temperature=0.0), 24, 0), tsb.run_config(tsb.shaping(temperature=0.0), 0, 2),
-                tsb.run_config(tsb.shaping(temperature=0.0), 600, 2), tsb.run_config(tsb.shaping(temperature=0.7, top_k=64), 8, 2)):
+                tsb.run_config(tsb.shaping(temperature=0.0), 600, 2), tsb.run_config(tsb.shaping(temperature=0.7, repetition_penalty=1.2), 8, 2)):
         with pytest.raises(tsb.TsbError):
             sess.spec_run(prompt, bad)
     with pytest.raises(tsb.TsbError):

@@ -40,9 +40,12 @@ struct RowStats {
     float max;
     int32_t argmax;
     double sum;
-    double total;
+    double total;    // sum of the weights of the surviving entries
     int32_t nonfinite;
-    int32_t _pad;
+    int32_t has_cut;  // truncation: the support is the rank-order prefix up to (cut_key, cut_idx) ...
+    uint32_t cut_key;
+    int32_t cut_idx;
+    double min_e;     // ... whose exp is at least this (min-p), 0 = off
 };
 
 // Exchange area every CTA of a cluster exposes to its peers.
@@ -109,15 +112,180 @@ __device__ __forceinline__ Slice my_slice(int vocab, int rank) {
     return s;
 }
 
+// --------------------------------------------------------------------- draw
+struct DrawShared {
+    unsigned long long hist[NBINS];
+    unsigned long long scan[ACC_THREADS / 32];
+    double red[ACC_THREADS / 32];
+    Xchg xch;
+    // written by rank 0 for everybody, or by the winning CTA into rank 0
+    unsigned int sel_bin;
+    unsigned long long sel_before;
+    int result;
+    unsigned long long gap_lo, gap_hi;
+    unsigned long long best_exp;
+    unsigned int best_idx;
+};
+
+// The draw over this cluster's row: fp[] holds every CTA's slice of fixed-point masses (2^-60 units), keys come
+// from krow.  target in 2^-60 units.  Returns the token (same value in every CTA), -1 for "past the end".
+template <class MassFn>
+__device__ int cluster_radix_select(cg::cluster_group& cluster, DrawShared& c, MassFn fp, const __half* __restrict__ krow, Slice sl,
+                                    unsigned long long target, unsigned long long* gap) {
+    const int rank = (int)cluster.block_rank();
+    uint32_t prefix = 0;
+    unsigned long long before = 0;
+    constexpr int RB = 256;  // bins per pass: the 16-bit key is resolved in two passes of eight bits
+    for (int pass = 0; pass < 2; pass++) {
+        const int shift = pass ? 0 : 8;
+        for (int i = threadIdx.x; i < RB; i += ACC_THREADS) c.hist[i] = 0;
+        __syncthreads();
+        for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
+            const uint32_t kd = desc_key16(krow[sl.lo + j]);
+            if (pass == 0 || (kd >> 8) == (prefix >> 8)) {
+                const unsigned long long m = fp(j);
+                if (m) atomicAdd(&c.hist[(kd >> shift) & (RB - 1)], m);
+            }
+        }
+        cluster.sync();
+        if (rank == 0) {
+            // sum the members' histograms bin by bin, scan, find the bin the target falls into
+            unsigned long long t = 0;
+            if (threadIdx.x < RB)
+                for (int rr = 0; rr < CL; rr++) t += cluster.map_shared_rank(c.hist, rr)[threadIdx.x];
+            unsigned long long v = t;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long n = __shfl_up_sync(0xffffffffu, v, o);
+                if ((threadIdx.x & 31) >= o) v += n;
+            }
+            if ((threadIdx.x & 31) == 31) c.scan[threadIdx.x >> 5] = v;
+            if (threadIdx.x == 0) c.sel_bin = RB, c.sel_before = 0;
+            __syncthreads();
+            if (threadIdx.x < RB) {
+                unsigned long long wbase = 0;
+                for (int i = 0; i < (int)(threadIdx.x >> 5); i++) wbase += c.scan[i];
+                const unsigned long long run = before + wbase + v - t, after = run + t;
+                if (target >= run && target < after) c.sel_bin = threadIdx.x, c.sel_before = run;
+            }
+        }
+        cluster.sync();
+        const DrawShared* root = cluster.map_shared_rank(&c, 0);
+        const unsigned int bin = root->sel_bin;
+        const unsigned long long bef = root->sel_before;
+        // no barrier here: rank 0 rewrites the selection only after the next pass's first cluster barrier, which every
+        // member reaches after this read
+        if (bin == RB) {
+            cluster.sync();  // leave together: the caller may go on to use the exchange area
+            return -1;
+        }
+        prefix |= bin << shift;
+        before = bef;
+    }
+    // every member shares the key: walk them in index order.  Threads own contiguous runs of their CTA's slice;
+    // CTAs are ordered by rank.
+    const int per = (sl.n + ACC_THREADS - 1) / ACC_THREADS;
+    const int lo = min(sl.n, (int)threadIdx.x * per), hi = min(sl.n, lo + per);
+    unsigned long long mine = 0;
+    for (int j = lo; j < hi; j++)
+        if (desc_key16(krow[sl.lo + j]) == prefix) mine += fp(j);
+    unsigned long long v = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long n = __shfl_up_sync(0xffffffffu, v, o);
+        if ((threadIdx.x & 31) >= o) v += n;
+    }
+    __syncthreads();
+    if ((threadIdx.x & 31) == 31) c.scan[threadIdx.x >> 5] = v;
+    if (threadIdx.x == 0) c.result = -1;
+    __syncthreads();
+    unsigned long long wbase = 0, cta_total = 0;
+    for (int i = 0; i < ACC_THREADS / 32; i++) {
+        if (i < (int)(threadIdx.x >> 5)) wbase += c.scan[i];
+        cta_total += c.scan[i];
+    }
+    if (threadIdx.x == 0) c.xch.u[0] = cta_total;
+    cluster.sync();
+    unsigned long long rank_base = 0;
+    for (int rr = 0; rr < rank; rr++) rank_base += cluster.map_shared_rank(&c.xch, rr)->u[0];
+    unsigned long long run = before + rank_base + wbase + v - mine;
+    DrawShared* root = cluster.map_shared_rank(&c, 0);
+    for (int j = lo; j < hi; j++) {
+        if (desc_key16(krow[sl.lo + j]) != prefix) continue;
+        const unsigned long long after = run + fp(j);
+        if (target >= run && target < after) {  // exactly one thread of one CTA
+            root->result = sl.lo + j;
+            root->gap_lo = target - run;
+            root->gap_hi = after - target;
+        }
+        run = after;
+    }
+    cluster.sync();
+    const int res = root->result;
+    const unsigned long long gl = root->gap_lo, gh = root->gap_hi;
+    cluster.sync();
+    *gap = gl < gh ? gl : gh;
+    return res;
+}
+
+// The draw over this cluster's row: fp[] holds every CTA's slice of fixed-point masses.
+__device__ int cluster_radix_draw(cg::cluster_group& cluster, DrawShared& c, const unsigned long long* fp,
+                                  const __half* __restrict__ krow, Slice sl, unsigned long long target,
+                                  unsigned long long* gap) {
+    return cluster_radix_select(cluster, c, [fp](int j) { return fp[j]; }, krow, sl, target, gap);
+}
+
+// What survives truncation (crates/selection/src/choose.rs:176-222): a prefix of the rank order (exp descending,
+// index ascending) - the first top_k entries, cut further where the cumulative e/sum first reaches top_p - and of
+// those the entries whose exp is at least min_p times the largest exp (which is exactly 1).
+struct TruncShape {
+    unsigned int top_k;
+    double top_p, min_p;
+};
+__device__ __forceinline__ bool survives(const RowStats& st, __half logit, int idx, double e) {
+    if (st.has_cut) {
+        const uint32_t k = desc_key16(logit);
+        if (k > st.cut_key || (k == st.cut_key && idx > st.cut_idx)) return false;
+    }
+    return !(st.min_e > 0.0) || e >= st.min_e;
+}
+// Finds the cut of a row whose exps sit in ecache[] (this CTA's slice) and whose sum is known.  Same result in
+// every CTA of the cluster.
+__device__ void cluster_find_cut(cg::cluster_group& cluster, DrawShared& c, const double* ecache, double sum,
+                                 const __half* __restrict__ krow, Slice sl, int vocab, TruncShape tr, RowStats* st) {
+    st->has_cut = 0, st->cut_key = 0xFFFFu, st->cut_idx = 0x7fffffff;
+    st->min_e = tr.min_p > 0.0 ? tr.min_p : 0.0;
+    unsigned long long gap;
+    if (tr.top_k > 0 && tr.top_k < (unsigned)vocab) {
+        const int t = cluster_radix_select(cluster, c, [](int) { return 1ull; }, krow, sl, (unsigned long long)tr.top_k - 1, &gap);
+        if (t >= 0) st->has_cut = 1, st->cut_key = desc_key16(krow[t]), st->cut_idx = t;
+    }
+    if (tr.top_p > 0.0) {
+        // first entry whose cumulative e/sum reaches the threshold, in 2^-60 fixed point ("push, then test >=")
+        const unsigned long long thr = (unsigned long long)__double2ull_ru(tr.top_p * FP_ONE);
+        if (thr > 0) {
+            const int t = cluster_radix_select(
+                cluster, c, [ecache, sum](int j) { return (unsigned long long)__double2ull_rn(ecache[j] / sum * FP_ONE); }, krow, sl,
+                thr - 1, &gap);
+            if (t >= 0) {
+                const uint32_t k = desc_key16(krow[t]);
+                if (!st->has_cut || k < st->cut_key || (k == st->cut_key && t < st->cut_idx)) st->cut_key = k, st->cut_idx = t;
+                st->has_cut = 1;
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------- statistics
 // One cluster per row: max / first argmax / finiteness, sum_i exp(l_i - max), total = sum_i w_i.
 __global__ void __launch_bounds__(ACC_THREADS)
     accept_stats_kernel(const __half* __restrict__ target, const __half* __restrict__ draft, int k, int vocab,
-                        double temperature, RowStats* __restrict__ stats, int rows_per_stream, int64_t single_stride) {
+                        double temperature, TruncShape tr, RowStats* __restrict__ stats, int rows_per_stream, int64_t single_stride) {
     extern __shared__ __align__(16) uint8_t dyn[];
     double* ecache = reinterpret_cast<double*>(dyn);  // exp(l - max) of this CTA's slice
-    __shared__ Xchg xch;
-    __shared__ double red[ACC_THREADS / 32];
+    __shared__ DrawShared c;
+    Xchg& xch = c.xch;
+    double* red = c.red;
     __shared__ float fred[ACC_THREADS / 32];
     __shared__ int ired[ACC_THREADS / 32];
     __shared__ int bad_flag;
@@ -168,7 +336,8 @@ __global__ void __launch_bounds__(ACC_THREADS)
     }
     cluster.sync();
     RowStats st;
-    st.max = mx, st.argmax = am, st.sum = 1.0, st.total = 1.0, st.nonfinite = nonfinite, st._pad = 0;
+    st.max = mx, st.argmax = am, st.sum = 1.0, st.total = 1.0, st.nonfinite = nonfinite;
+    st.has_cut = 0, st.cut_key = 0xFFFFu, st.cut_idx = 0x7fffffff, st.min_e = 0.0;
     if (temperature != 0.0 && !nonfinite) {
         const double dmx = (double)mx;
         double s = 0.0;
@@ -181,9 +350,12 @@ __global__ void __launch_bounds__(ACC_THREADS)
         const double top = 1.0 / sum;  // the max entry's exp is exactly 1
         const double inv_t = 1.0 / temperature;
         const bool unit_t = temperature == 1.0;
-        double t = 0.0;
-        for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) t += weight_of(ecache[j], sum, top, inv_t, unit_t);
         st.sum = sum;
+        const bool truncating = (tr.top_k > 0 && tr.top_k < (unsigned)vocab) || tr.top_p > 0.0 || tr.min_p > 0.0;
+        if (truncating) cluster_find_cut(cluster, c, ecache, sum, row, sl, vocab, tr, &st);
+        double t = 0.0;
+        for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS)
+            if (!truncating || survives(st, row[sl.lo + j], sl.lo + j, ecache[j])) t += weight_of(ecache[j], sum, top, inv_t, unit_t);
         st.total = cluster_sum_f64(cluster, &xch, 1, block_sum_f64(t, red));
     }
     pdl_launch_dependents();
@@ -194,124 +366,9 @@ __global__ void __launch_bounds__(ACC_THREADS)
 // probability of one token under a row's shaped distribution (distribution.rs:61-66 over the full support)
 __device__ __forceinline__ double prob_of(const __half* row, const RowStats& st, int token, double inv_t, bool unit_t) {
     const double e = exp((double)__half2float(row[token]) - (double)st.max);
+    if (!survives(st, row[token], token, e)) return 0.0;  // distribution.rs:61-66: not in the support
     const double w = weight_of(e, st.sum, 1.0 / st.sum, inv_t, unit_t);
     return st.total > 0.0 ? w / st.total : 0.0;
-}
-
-// --------------------------------------------------------------------- draw
-struct DrawShared {
-    unsigned long long hist[NBINS];
-    unsigned long long scan[ACC_THREADS / 32];
-    double red[ACC_THREADS / 32];
-    Xchg xch;
-    // written by rank 0 for everybody, or by the winning CTA into rank 0
-    unsigned int sel_bin;
-    unsigned long long sel_before;
-    int result;
-    unsigned long long gap_lo, gap_hi;
-    unsigned long long best_exp;
-    unsigned int best_idx;
-};
-
-// The draw over this cluster's row: fp[] holds every CTA's slice of fixed-point masses (2^-60 units), keys come
-// from krow.  target in 2^-60 units.  Returns the token (same value in every CTA), -1 for "past the end".
-__device__ int cluster_radix_draw(cg::cluster_group& cluster, DrawShared& c, const unsigned long long* fp,
-                                  const __half* __restrict__ krow, Slice sl, unsigned long long target,
-                                  unsigned long long* gap) {
-    const int rank = (int)cluster.block_rank();
-    uint32_t prefix = 0;
-    unsigned long long before = 0;
-    constexpr int RB = 256;  // bins per pass: the 16-bit key is resolved in two passes of eight bits
-    for (int pass = 0; pass < 2; pass++) {
-        const int shift = pass ? 0 : 8;
-        for (int i = threadIdx.x; i < RB; i += ACC_THREADS) c.hist[i] = 0;
-        __syncthreads();
-        for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
-            const uint32_t kd = desc_key16(krow[sl.lo + j]);
-            if (pass == 0 || (kd >> 8) == (prefix >> 8)) {
-                const unsigned long long m = fp[j];
-                if (m) atomicAdd(&c.hist[(kd >> shift) & (RB - 1)], m);
-            }
-        }
-        cluster.sync();
-        if (rank == 0) {
-            // sum the members' histograms bin by bin, scan, find the bin the target falls into
-            unsigned long long t = 0;
-            if (threadIdx.x < RB)
-                for (int rr = 0; rr < CL; rr++) t += cluster.map_shared_rank(c.hist, rr)[threadIdx.x];
-            unsigned long long v = t;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const unsigned long long n = __shfl_up_sync(0xffffffffu, v, o);
-                if ((threadIdx.x & 31) >= o) v += n;
-            }
-            if ((threadIdx.x & 31) == 31) c.scan[threadIdx.x >> 5] = v;
-            if (threadIdx.x == 0) c.sel_bin = RB, c.sel_before = 0;
-            __syncthreads();
-            if (threadIdx.x < RB) {
-                unsigned long long wbase = 0;
-                for (int i = 0; i < (int)(threadIdx.x >> 5); i++) wbase += c.scan[i];
-                const unsigned long long run = before + wbase + v - t, after = run + t;
-                if (target >= run && target < after) c.sel_bin = threadIdx.x, c.sel_before = run;
-            }
-        }
-        cluster.sync();
-        const DrawShared* root = cluster.map_shared_rank(&c, 0);
-        const unsigned int bin = root->sel_bin;
-        const unsigned long long bef = root->sel_before;
-        // no barrier here: rank 0 rewrites the selection only after the next pass's first cluster barrier, which every
-        // member reaches after this read
-        if (bin == RB) {
-            cluster.sync();  // leave together: the caller may go on to use the exchange area
-            return -1;
-        }
-        prefix |= bin << shift;
-        before = bef;
-    }
-    // every member shares the key: walk them in index order.  Threads own contiguous runs of their CTA's slice;
-    // CTAs are ordered by rank.
-    const int per = (sl.n + ACC_THREADS - 1) / ACC_THREADS;
-    const int lo = min(sl.n, (int)threadIdx.x * per), hi = min(sl.n, lo + per);
-    unsigned long long mine = 0;
-    for (int j = lo; j < hi; j++)
-        if (desc_key16(krow[sl.lo + j]) == prefix) mine += fp[j];
-    unsigned long long v = mine;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const unsigned long long n = __shfl_up_sync(0xffffffffu, v, o);
-        if ((threadIdx.x & 31) >= o) v += n;
-    }
-    __syncthreads();
-    if ((threadIdx.x & 31) == 31) c.scan[threadIdx.x >> 5] = v;
-    if (threadIdx.x == 0) c.result = -1;
-    __syncthreads();
-    unsigned long long wbase = 0, cta_total = 0;
-    for (int i = 0; i < ACC_THREADS / 32; i++) {
-        if (i < (int)(threadIdx.x >> 5)) wbase += c.scan[i];
-        cta_total += c.scan[i];
-    }
-    if (threadIdx.x == 0) c.xch.u[0] = cta_total;
-    cluster.sync();
-    unsigned long long rank_base = 0;
-    for (int rr = 0; rr < rank; rr++) rank_base += cluster.map_shared_rank(&c.xch, rr)->u[0];
-    unsigned long long run = before + rank_base + wbase + v - mine;
-    DrawShared* root = cluster.map_shared_rank(&c, 0);
-    for (int j = lo; j < hi; j++) {
-        if (desc_key16(krow[sl.lo + j]) != prefix) continue;
-        const unsigned long long after = run + fp[j];
-        if (target >= run && target < after) {  // exactly one thread of one CTA
-            root->result = sl.lo + j;
-            root->gap_lo = target - run;
-            root->gap_hi = after - target;
-        }
-        run = after;
-    }
-    cluster.sync();
-    const int res = root->result;
-    const unsigned long long gl = root->gap_lo, gh = root->gap_hi;
-    cluster.sync();
-    *gap = gl < gh ? gl : gh;
-    return res;
 }
 
 // Fills fp[] (this CTA's slice) with the fixed-point probability of every token under (a) the shaped row prow
@@ -326,14 +383,17 @@ __device__ bool cluster_fill_masses(cg::cluster_group& cluster, DrawShared& c, u
     double t = 0.0;
     int any = 0;
     unsigned long long best = ~0ull;
-    const double p_inv = 1.0 / ps.sum, q_inv = qrow ? 1.0 / qs->sum : 0.0;  // temperature 1: mass = e / sum (see sample_kernel)
+    // temperature 1: the weight is e up to two roundings, so the mass is e / total (see sample_kernel)
+    const double p_inv = 1.0 / ps.total, q_inv = qrow ? 1.0 / qs->total : 0.0;
     for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
         const double e = exp((double)__half2float(prow[sl.lo + j]) - pmax);
         double m = unit_t ? e * p_inv : weight_of(e, ps.sum, ptop, inv_t, unit_t) / ps.total;
-        bool in_support = true;
-        if (qrow) {
+        bool in_support = survives(ps, prow[sl.lo + j], sl.lo + j, e);
+        if (!in_support) m = 0.0;
+        if (qrow && in_support) {
             const double eq = exp((double)__half2float(qrow[sl.lo + j]) - (double)qs->max);
-            const double qq = unit_t ? eq * q_inv : weight_of(eq, qs->sum, 1.0 / qs->sum, inv_t, unit_t) / qs->total;
+            double qq = unit_t ? eq * q_inv : weight_of(eq, qs->sum, 1.0 / qs->sum, inv_t, unit_t) / qs->total;
+            if (!survives(*qs, qrow[sl.lo + j], sl.lo + j, eq)) qq = 0.0;
             m = fmax(m - qq, 0.0);
             in_support = m > 0.0;
             t += m;
@@ -362,7 +422,8 @@ __device__ bool cluster_fill_masses(cg::cluster_group& cluster, DrawShared& c, u
     unsigned int li = 0;
     for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
         const double e = exp((double)__half2float(prow[sl.lo + j]) - pmax);
-        if ((unsigned long long)__double_as_longlong(e) == gbest && (!qrow || mass[j] > 0.0)) li = max(li, (unsigned int)(sl.lo + j));
+        if ((unsigned long long)__double_as_longlong(e) == gbest && survives(ps, prow[sl.lo + j], sl.lo + j, e) && (!qrow || mass[j] > 0.0))
+            li = max(li, (unsigned int)(sl.lo + j));
     }
     atomicMax(&c.best_idx, li);
     cluster.sync();
@@ -478,7 +539,7 @@ __global__ void __launch_bounds__(ACC_THREADS)
 // evaluated once per entry and stays in shared memory (first as e, then as the weight, then as the fixed-point mass).
 __global__ void __launch_bounds__(ACC_THREADS)
     sample_kernel(const __half* __restrict__ logits, int64_t logits_stride, const uint64_t* __restrict__ uniforms,
-                  int uni_stride, int vocab, double temperature, int32_t* __restrict__ tokens, int token_stride,
+                  int uni_stride, int vocab, double temperature, TruncShape tr, int32_t* __restrict__ tokens, int token_stride,
                   double* __restrict__ margins, uint32_t* __restrict__ err) {
     extern __shared__ __align__(16) uint8_t dyn[];
     unsigned long long* fp = reinterpret_cast<unsigned long long*>(dyn);
@@ -541,51 +602,53 @@ __global__ void __launch_bounds__(ACC_THREADS)
     } else {
         const double dmx = (double)mx, inv_t = 1.0 / temperature;
         const bool unit_t = temperature == 1.0;
-        // e = exp(l - max), its sum, and the last entry in rank order (smallest e, then the largest index)
+        const bool truncating = (tr.top_k > 0 && tr.top_k < (unsigned)vocab) || tr.top_p > 0.0 || tr.min_p > 0.0;
+        // e = exp(l - max) and its sum
         double acc = 0.0;
-        unsigned long long best = ~0ull;
-        unsigned int best_i = 0;
         for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
             const double e = exp((double)__half2float(row[sl.lo + j]) - dmx);
             ecache[j] = e;
             acc += e;
-            const unsigned long long eb = (unsigned long long)__double_as_longlong(e);
-            if (eb <= best) best = eb, best_i = (unsigned int)(sl.lo + j);  // indices grow with j
         }
         const double sum = cluster_sum_f64(cluster, &c.xch, 0, block_sum_f64(acc, c.red));
         const double top = 1.0 / sum;
-        double total = sum;
-        if (!unit_t) {
-            acc = 0.0;
-            for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
-                const double w = weight_of(ecache[j], sum, top, inv_t, unit_t);
-                ecache[j] = w;
-                acc += w;
+        RowStats st;
+        st.has_cut = 0, st.cut_key = 0xFFFFu, st.cut_idx = 0x7fffffff, st.min_e = 0.0;
+        if (truncating) cluster_find_cut(cluster, c, ecache, sum, row, sl, vocab, tr, &st);
+        // weights of the survivors, their total, and the last survivor in rank order (smallest e, then the largest index)
+        acc = 0.0;
+        unsigned long long best = ~0ull;
+        unsigned int best_i = 0;
+        for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
+            const double e = ecache[j];
+            if (truncating && !survives(st, row[sl.lo + j], sl.lo + j, e)) {
+                ecache[j] = 0.0;
+                continue;
             }
-            total = cluster_sum_f64(cluster, &c.xch, 1, block_sum_f64(acc, c.red));
+            // At temperature 1 the reference's weight ((e/sum)/top with top = 1/sum) is e up to two roundings.  The
+            // few-ulp difference can move a draw only when the target lies within ~1e-15 of a boundary, which the
+            // reported margin shows.
+            const double w = unit_t ? e : weight_of(e, sum, top, inv_t, unit_t);
+            ecache[j] = w;
+            acc += w;
+            const unsigned long long eb = (unsigned long long)__double_as_longlong(e);
+            if (eb <= best) best = eb, best_i = (unsigned int)(sl.lo + j);  // indices grow with j
         }
-        // At temperature 1 the reference's weight ((e/sum)/top with top = 1/sum) is e up to two roundings and its
-        // total is the sum, so the mass is e/sum: one multiply per entry.  The few-ulp difference can move a draw only
-        // when the target lies within ~1e-15 of a boundary, which the reported margin shows.
+        const double total = cluster_sum_f64(cluster, &c.xch, 1, block_sum_f64(acc, c.red));
         if (threadIdx.x == 0) c.best_exp = ~0ull, c.best_idx = 0;
         __syncthreads();
         atomicMin(&c.best_exp, best);
         cluster.sync();
         unsigned long long gbest = ~0ull;
         for (int rr = 0; rr < CL; rr++) gbest = min(gbest, cluster.map_shared_rank(&c, rr)->best_exp);
-        if (best == gbest && sl.n > 0 && (int)threadIdx.x < sl.n) atomicMax(&c.best_idx, best_i);
+        if (best == gbest && best != ~0ull) atomicMax(&c.best_idx, best_i);
         cluster.sync();
         unsigned int last = 0;
         for (int rr = 0; rr < CL; rr++) last = max(last, cluster.map_shared_rank(&c, rr)->best_idx);
         cluster.sync();
-        if (unit_t) {
+        {
             const double scale = FP_ONE / total;
             for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) fp[j] = (unsigned long long)__double2ull_rn(ecache[j] * scale);
-        } else {
-            for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
-                const double m = ecache[j] / total;
-                fp[j] = (unsigned long long)__double2ull_rn(m * FP_ONE);
-            }
         }
         __syncthreads();
         const unsigned long long tgt = (unsigned long long)(uniforms[(size_t)b * uni_stride] >> 11) << 7;
@@ -647,12 +710,11 @@ int32_t check_shaping(tsb_ctx* ctx, const tsb_shaping* sh) {
     TSB_REQUIRE(ctx, sh->top_k <= 256, "top_k must be between 0 and 256");
     TSB_REQUIRE(ctx, !(sh->top_p > 0.0) || sh->top_p <= 1.0, "top_p must be in (0, 1]");
     TSB_REQUIRE(ctx, isfinite(sh->repetition_penalty) && sh->repetition_penalty > 0.0, "repetition_penalty must be > 0");
-    if (sh->temperature != 0.0 &&
-        (sh->top_k != 0 || sh->top_p > 0.0 || sh->min_p > 0.0 || sh->repetition_penalty != 1.0 ||
-         sh->presence_penalty != 0.0 || sh->frequency_penalty != 0.0))
+    TSB_REQUIRE(ctx, !(sh->min_p > 0.0) || sh->min_p <= 1.0, "min_p must be in (0, 1]");
+    if (sh->temperature != 0.0 && (sh->repetition_penalty != 1.0 || sh->presence_penalty != 0.0 || sh->frequency_penalty != 0.0))
         return tsb_fail(ctx, TSB_ERR_UNSUPPORTED,
-                        "the device sampler covers temperature with the whole vocabulary only (top_k = 0, top_p, min_p "
-                        "and penalties off)");
+                        "the device sampler covers temperature, top_k, top_p and min_p; repetition, presence and frequency "
+                        "penalties need the token history and are not applied on the device");
     return TSB_OK;
 }
 
@@ -673,7 +735,7 @@ size_t accept_scratch_bytes(int batch, int k, int vocab) {
 int accept_max_vocab() { return CL * SLICE_MAX; }
 
 cudaError_t launch_accept(tsb_ctx* ctx, cudaStream_t st, const __half* target, const __half* draft, const int32_t* proposals,
-                          int prop_stride, const uint64_t* uniforms, int batch, int k, int vocab, double temperature,
+                          int prop_stride, const uint64_t* uniforms, int batch, int k, int vocab, AcceptShape shape,
                           tsb_accept_out* out_dev, int32_t* next_tokens, int next_stride, void* scratch) {
     RowStats* stats = reinterpret_cast<RowStats*>(scratch);
     const int rps = 2 * k + 1;
@@ -686,8 +748,10 @@ cudaError_t launch_accept(tsb_ctx* ctx, cudaStream_t st, const __half* target, c
         if (e != cudaSuccess) return e;
         configured = true;
     }
+    const TruncShape tr{shape.top_k, shape.top_p, shape.min_p};
+    const double temperature = shape.temperature;
     cudaError_t e = tsb_launch_cluster(ctx, accept_stats_kernel, dim3((unsigned)(batch * rps * CL)), dim3(ACC_THREADS), smem, st,
-                                       true, (unsigned)CL, target, draft, k, vocab, temperature, stats, rps, (int64_t)0);
+                                       true, (unsigned)CL, target, draft, k, vocab, temperature, tr, stats, rps, (int64_t)0);
     if (e != cudaSuccess) return e;
     return tsb_launch_cluster(ctx, accept_decide_kernel, dim3((unsigned)(batch * CL)), dim3(ACC_THREADS), smem, st, true,
                               (unsigned)CL, target, draft, proposals, prop_stride, uniforms, k, vocab, temperature,
@@ -695,9 +759,11 @@ cudaError_t launch_accept(tsb_ctx* ctx, cudaStream_t st, const __half* target, c
 }
 
 cudaError_t launch_sample(tsb_ctx* ctx, cudaStream_t st, const __half* logits, int64_t logits_stride,
-                          const uint64_t* uniforms, int uni_stride, int batch, int vocab, double temperature,
+                          const uint64_t* uniforms, int uni_stride, int batch, int vocab, AcceptShape shape,
                           int32_t* tokens_dev, int token_stride, double* margins_dev, void* scratch) {
     (void)scratch;
+    const TruncShape tr{shape.top_k, shape.top_p, shape.min_p};
+    const double temperature = shape.temperature;
     const size_t smem = slice_smem(vocab);
     static bool configured = false;
     if (!configured) {
@@ -708,7 +774,7 @@ cudaError_t launch_sample(tsb_ctx* ctx, cudaStream_t st, const __half* logits, i
         configured = true;
     }
     return tsb_launch_cluster(ctx, sample_kernel, dim3((unsigned)(batch * CL)), dim3(ACC_THREADS), smem, st, true, (unsigned)CL,
-                              logits, logits_stride, uniforms, uni_stride, vocab, temperature, tokens_dev, token_stride,
+                              logits, logits_stride, uniforms, uni_stride, vocab, temperature, tr, tokens_dev, token_stride,
                               margins_dev, ctx->dev_error);
 }
 
@@ -724,7 +790,8 @@ cudaError_t launch_argmax_rows(tsb_ctx* ctx, cudaStream_t st, const __half* logi
     cudaError_t e = ensure_smem(accept_stats_kernel, (size_t)SLICE_MAX * 8);
     if (e != cudaSuccess) return e;
     return tsb_launch_cluster(ctx, accept_stats_kernel, dim3((unsigned)(n_rows * CL)), dim3(ACC_THREADS), smem, st, true,
-                              (unsigned)CL, logits, (const __half*)nullptr, n_rows - 1, vocab, 0.0, stats, n_rows, (int64_t)0);
+                              (unsigned)CL, logits, (const __half*)nullptr, n_rows - 1, vocab, 0.0, TruncShape{0u, 0.0, 0.0}, stats, n_rows,
+                              (int64_t)0);
 }
 
 int accept_row_stats_bytes() { return (int)sizeof(RowStats); }
@@ -759,7 +826,7 @@ int32_t tsb_accept(tsb_ctx* ctx, tsb_stream s, const void* target_logits_f16, co
     TSB_REQUIRE(ctx, scratch_bytes >= tsb_accept_scratch_bytes(batch, k, vocab), "scratch too small");
     DeviceGuard g(ctx);
     TSB_CUDA(ctx, launch_accept(ctx, (cudaStream_t)s, (const __half*)target_logits_f16, (const __half*)draft_logits_f16,
-                                proposals, k, uniforms, batch, k, vocab, shaping->temperature, out_dev, nullptr, 0, scratch));
+                                proposals, k, uniforms, batch, k, vocab, AcceptShape(*shaping), out_dev, nullptr, 0, scratch));
     return TSB_OK;
 }
 
@@ -777,7 +844,7 @@ int32_t tsb_sample(tsb_ctx* ctx, tsb_stream s, const void* logits_f16, const uin
     TSB_REQUIRE(ctx, scratch_bytes >= tsb_accept_scratch_bytes(batch, 0, vocab), "scratch too small");
     DeviceGuard g(ctx);
     TSB_CUDA(ctx, launch_sample(ctx, (cudaStream_t)s, (const __half*)logits_f16, vocab, uniforms, 1, batch, vocab,
-                                shaping->temperature, tokens_dev, 1, margins_dev, scratch));
+                                AcceptShape(*shaping), tokens_dev, 1, margins_dev, scratch));
     return TSB_OK;
 }
 

@@ -770,6 +770,12 @@ int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_acti
         uint64_t tb;
         memcpy(&tb, &T, 8);
         mixk(tb);
+        // the truncation settings are kernel parameters of the captured launches
+        memcpy(&tb, &cfg->shaping.top_p, 8);
+        mixk(tb);
+        memcpy(&tb, &cfg->shaping.min_p, 8);
+        mixk(tb);
+        mixk(cfg->shaping.top_k);
     }
     int64_t max_base = 0;
     for (int a = 0; a < S; a++) {
@@ -806,7 +812,7 @@ int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_acti
                                              s->logits_draft + (size_t)d * V, (int64_t)K * V));
             for (int a = 0; a < S; a++) tsb_kv_set_cursor(s->draft.kv, streams[a], tsb_kv_cursor(s->draft.kv, streams[a]) + nrow);
             if (!s->replay)
-                TSB_CUDA(ctx, launch_sample(ctx, st, s->logits_draft + (size_t)d * V, (int64_t)K * V, un_draft + d, UD, S, V, T,
+                TSB_CUDA(ctx, launch_sample(ctx, st, s->logits_draft + (size_t)d * V, (int64_t)K * V, un_draft + d, UD, S, V, AcceptShape(cfg->shaping),
                                             s->feed_dev + d + 1, K + 1, nullptr, s->accept_scratch));
         }
         if (!s->replay && !s->capturing) TSB_CUDA(ctx, cudaEventRecord(s->ev[1], st));
@@ -820,7 +826,7 @@ int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_acti
         if (!s->replay) {
             if (!s->capturing) TSB_CUDA(ctx, cudaEventRecord(s->ev[2], st));
             // ---- accept on the device; the next confirmed token also lands in feed[.][0]
-            TSB_CUDA(ctx, launch_accept(ctx, st, s->logits_target, s->logits_draft, s->feed_dev + 1, K + 1, un_acc, S, K, V, T,
+            TSB_CUDA(ctx, launch_accept(ctx, st, s->logits_target, s->logits_draft, s->feed_dev + 1, K + 1, un_acc, S, K, V, AcceptShape(cfg->shaping),
                                         s->accept_out_dev, s->feed_dev, K + 1, s->accept_scratch));
             TSB_CUDA(ctx, cudaMemcpyAsync(s->accept_out_host, s->accept_out_dev, (size_t)S * sizeof(tsb_accept_out),
                                           cudaMemcpyDeviceToHost, st));
@@ -1007,7 +1013,7 @@ int32_t session_select_target(tsb_session* s, const tsb_run_config* cfg, uint64_
     uint64_t* u = s->uniforms_host;
     u[0] = uniform;
     TSB_CUDA(ctx, cudaMemcpyAsync(s->uniforms_dev, u, sizeof(uint64_t), cudaMemcpyHostToDevice, s->stream));
-    TSB_CUDA(ctx, launch_sample(ctx, s->stream, s->logits_target, V, s->uniforms_dev, 1, 1, V, cfg->shaping.temperature,
+    TSB_CUDA(ctx, launch_sample(ctx, s->stream, s->logits_target, V, s->uniforms_dev, 1, 1, V, AcceptShape(cfg->shaping),
                                 s->tok1_dev, 1, nullptr, s->accept_scratch));
     TSB_CUDA(ctx, cudaMemcpyAsync(s->feed_host, s->tok1_dev, sizeof(int32_t), cudaMemcpyDeviceToHost, s->stream));
     int32_t rc = tsb_stream_sync(ctx, s->stream);
