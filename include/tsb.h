@@ -265,8 +265,9 @@ typedef struct tsb_accept_out {
  * below 1e-12); on full acceptance draw the bonus from the last row.  temperature 0 = argmax equality.
  * Replaces the host-side accept step of the round loop (crates/runtime/src/speculative.rs:694-754,
  * 861-879) and select / shaped_distribution / residual (crates/selection/src/choose.rs:62-232,
- * distribution.rs:57-125).  Only temperature, top_k = 0, top_p off, min_p off, penalties off are
- * accepted by this entry point; other shaping is refused with TSB_ERR_UNSUPPORTED. */
+ * distribution.rs:57-125).  Temperature, top_k (<= 256), top_p and min_p are applied on the device (the support is
+ * the reference's rank-order prefix); repetition, presence and frequency penalties need the token history and are
+ * refused with TSB_ERR_UNSUPPORTED. */
 TSB_API int32_t tsb_accept(tsb_ctx* ctx, tsb_stream s, const void* target_logits_f16, const void* draft_logits_f16,
                            const int32_t* proposals, const uint64_t* uniforms, int32_t batch, int32_t k,
                            int32_t vocab, const tsb_shaping* shaping, tsb_accept_out* out_dev, void* scratch,
