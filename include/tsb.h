@@ -364,6 +364,14 @@ TSB_API int64_t tsb_producer_checkpoint(tsb_session* s, int32_t stream);
 TSB_API int32_t tsb_producer_rollback(tsb_session* s, int32_t stream, int64_t point);
 TSB_API int32_t tsb_producer_rollback_retaining(tsb_session* s, int32_t stream, int64_t point, int32_t keep_rows);
 TSB_API int32_t tsb_producer_rewind_drafter(tsb_session* s, int32_t stream, int64_t position);
+/* try_reuse_prefix (crates/runtime/src/producer.rs:21-47): commit to continuing from the stream's current state for
+ * the leading N tokens of the prompt and return N (at most n - 1, so the last prompt token is always fed for its
+ * logits).  Keyed on the token ids that were actually fed; cursors past the agreed prefix are moved back to it. */
+TSB_API int64_t tsb_producer_try_reuse_prefix(tsb_session* s, int32_t stream, const int32_t* prompt_ids, int32_t n);
+/* record_committed (crates/runtime/src/producer.rs:324-330): the tokens a round committed, at pos0, for later
+ * prefix reuse.  The loops of this library keep that record themselves; the call is for callers that drive the
+ * producer functions directly. */
+TSB_API int32_t tsb_producer_record_committed(tsb_session* s, int32_t stream, const int32_t* tokens, int32_t n, int64_t pos0);
 
 /* Generation settings of the round loop (crates/runtime/src/config.rs GenerationConfig, reduced to what
  * the loop reads without a tokenizer). */
@@ -383,10 +391,15 @@ typedef struct tsb_run_config {
      * accepted path is compacted in place.  Temperature must be 0 (the reference refuses sampled tree rounds). */
     int32_t tree_nodes, tree_levels;
     int32_t tree_branching[8];
+    /* 1: keep what the stream's caches already hold for the longest prefix of the prompt whose token ids equal the
+     * ids that were fed (try_reuse_prefix, crates/runtime/src/producer.rs:21-47) instead of resetting the stream */
+    int32_t reuse_prefix;
 } tsb_run_config;
 
 typedef struct tsb_run_result {
     int32_t new_tokens, reason /* 0 max tokens, 1 stop token */, rounds, accepted_total, rollbacks, history_len;
+    int32_t reused_prefix; /* prompt tokens whose cache rows were kept from the previous run */
+    int32_t _pad;
     int64_t kv_position;
     uint64_t draws;
     double prefill_seconds, decode_seconds;

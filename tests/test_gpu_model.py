@@ -209,3 +209,34 @@ def test_greedy_tree_rounds_equal_the_sequential_loop_token_for_token(rig, oracl
         with pytest.raises(tsb.TsbError):
             sess.spec_run(prompt, bad)
     sess.close()
+
+
+def test_prefix_reuse_keeps_the_shared_rows_and_changes_nothing_else(rig, oracle):
+    """try_reuse_prefix (crates/runtime/src/producer.rs:21-47): a second prompt that repeats the first turn's history
+    and adds to it keeps the cache rows of the common prefix; the output equals a run from an empty cache."""
+    tsb = rig["tsb"]
+    sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 16)
+    rng = np.random.default_rng(9)
+    prompt = rng.integers(0, rig["cfg"].vocab, size=40).astype(np.int32)
+    rc = tsb.run_config(tsb.shaping(temperature=0.0), 24, 3)
+    h1, _, r1 = sess.spec_run(prompt, rc)
+    assert r1.reused_prefix == 0
+    # second turn: the first turn's history (as committed) plus new tokens
+    turn2 = np.concatenate([h1, rng.integers(0, rig["cfg"].vocab, size=12).astype(np.int32)])
+    reuse = tsb.run_config(tsb.shaping(temperature=0.0), 24, 3, reuse_prefix=True)
+    h2, e2, r2 = sess.spec_run(turn2, reuse)
+    assert r2.reused_prefix == len(h1)  # every committed row of the first turn was kept
+    fresh = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 16)
+    h3, e3, r3 = fresh.spec_run(turn2, rc)
+    assert np.array_equal(e2, e3) and np.array_equal(h2, h3)
+    # a prompt that diverges inside the cached part keeps only the common prefix
+    turn3 = turn2.copy()
+    turn3[10] = (turn3[10] + 1) % rig["cfg"].vocab
+    _, e4, r4 = sess.spec_run(turn3, reuse)
+    assert r4.reused_prefix == 10
+    _, e5, _ = fresh.spec_run(turn3, rc)
+    assert np.array_equal(e4, e5)
+    # the sequential loop takes the same option
+    _, e6, r6 = sess.sequential_run(turn3, reuse)
+    assert r6.reused_prefix > 0 and np.array_equal(e6, e5)
+    sess.close(), fresh.close()

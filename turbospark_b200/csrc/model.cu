@@ -695,6 +695,27 @@ int32_t tsb_producer_rewind_drafter(tsb_session* s, int32_t stream, int64_t posi
     return TSB_OK;
 }
 
+int64_t tsb_producer_try_reuse_prefix(tsb_session* s, int32_t stream, const int32_t* prompt_ids, int32_t n) {
+    if (!s || !prompt_ids || n <= 0 || stream < 0 || stream >= s->n_streams) return 0;
+    auto& fed = s->target.fed[stream];
+    const int64_t cur = tsb_kv_cursor(s->target.kv, stream);
+    int64_t lim = std::min<int64_t>(std::min<int64_t>(cur, (int64_t)fed.size()), (int64_t)n - 1);
+    int64_t keep = 0;
+    while (keep < lim && fed[(size_t)keep] == prompt_ids[keep]) keep++;
+    tsb_kv_set_cursor(s->target.kv, stream, keep);
+    fed.resize((size_t)keep);
+    if (s->has_draft && tsb_kv_cursor(s->draft.kv, stream) > keep) tsb_kv_set_cursor(s->draft.kv, stream, keep);
+    return keep;
+}
+
+int32_t tsb_producer_record_committed(tsb_session* s, int32_t stream, const int32_t* tokens, int32_t n, int64_t pos0) {
+    if (!s || (!tokens && n) || n < 0) return TSB_ERR_INVALID;
+    TSB_REQUIRE(s->ctx, stream >= 0 && stream < s->n_streams, "stream %d outside the session", stream);
+    TSB_REQUIRE(s->ctx, pos0 >= 0 && pos0 <= (int64_t)s->target.fed[stream].size(), "pos0 %lld does not continue the record", (long long)pos0);
+    record_fed(s->target, stream, pos0, tokens, n);
+    return TSB_OK;
+}
+
 // ---- one lockstep round over every stream ----------------------------------
 
 int32_t tsb_session_fill_context(tsb_session* s, int64_t tokens, uint64_t seed) {

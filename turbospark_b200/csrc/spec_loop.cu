@@ -64,12 +64,18 @@ int32_t admission(tsb_ctx* ctx, int n_prompt, const tsb_run_config* cfg, int max
 }
 
 // Prefill through the target (head on the last token only) and, when present, the drafter.
-int32_t prefill(tsb_session* s, int stream, const int32_t* prompt, int n_prompt, bool with_drafter) {
-    int32_t rc = tsb_producer_reset(s, stream);
-    if (rc) return rc;
+int32_t prefill(tsb_session* s, int stream, const int32_t* prompt, int n_prompt, bool with_drafter, bool reuse, int32_t* reused) {
+    int32_t rc;
+    int64_t kept = 0;
+    if (reuse) {
+        kept = tsb_producer_try_reuse_prefix(s, stream, prompt, n_prompt);
+    } else if ((rc = tsb_producer_reset(s, stream))) {
+        return rc;
+    }
+    *reused = (int32_t)kept;
     // all but the last prompt token go through in chunks of rows (one chain pass each, no head); the last one alone,
     // with the head.  Both generation loops prefill this way, so they start from the same cache contents.
-    if (n_prompt > 1 && (rc = session_prefill_rows(s, stream, prompt, n_prompt - 1))) return rc;
+    if (n_prompt - 1 > kept && (rc = session_prefill_rows(s, stream, prompt + kept, n_prompt - 1 - (int)kept))) return rc;
     if ((rc = tsb_producer_produce(s, stream, prompt[n_prompt - 1], n_prompt - 1, nullptr))) return rc;
     if (with_drafter && n_prompt >= 2) {
         // prime_drafter(prompt[i+1], i) for every i: after it the drafter holds rows 0..n_prompt-1
@@ -125,7 +131,7 @@ int32_t tsb_spec_run(tsb_session* s, int32_t stream, const int32_t* prompt, int3
     const bool sampled = cfg->shaping.temperature != 0.0;
 
     const double t0 = now_s();
-    if ((rc = prefill(s, stream, prompt, n_prompt, true))) return rc;
+    if ((rc = prefill(s, stream, prompt, n_prompt, true, cfg->reuse_prefix != 0, &res->reused_prefix))) return rc;
     const double t1 = now_s();
 
     Sink sink;
@@ -248,7 +254,7 @@ int32_t tsb_sequential_run(tsb_session* s, int32_t stream, const int32_t* prompt
     if (rc) return rc;
     TSB_REQUIRE(ctx, stream >= 0 && stream < s->n_streams, "stream %d outside the session", stream);
     const double t0 = now_s();
-    if ((rc = prefill(s, stream, prompt, n_prompt, false))) return rc;
+    if ((rc = prefill(s, stream, prompt, n_prompt, false, cfg->reuse_prefix != 0, &res->reused_prefix))) return rc;
     const double t1 = now_s();
     Sink sink;
     sink.cfg = cfg;

@@ -18,17 +18,21 @@ class ModelConfig(C.Structure):
 class RunConfig(C.Structure):
     _fields_ = [("shaping", Shaping), ("max_new_tokens", C.c_int32), ("block", C.c_int32), ("uniform_mode", C.c_int32),
                 ("n_stop", C.c_int32), ("stop_tokens", C.c_int32 * 8), ("adaptive", C.c_int32),
-                ("tree_nodes", C.c_int32), ("tree_levels", C.c_int32), ("tree_branching", C.c_int32 * 8)]
+                ("tree_nodes", C.c_int32), ("tree_levels", C.c_int32), ("tree_branching", C.c_int32 * 8),
+                ("reuse_prefix", C.c_int32)]
 
 
 class RunResult(C.Structure):
-    _fields_ = [(n, C.c_int32) for n in ("new_tokens", "reason", "rounds", "accepted_total", "rollbacks", "history_len")] + \
+    _fields_ = [(n, C.c_int32) for n in ("new_tokens", "reason", "rounds", "accepted_total", "rollbacks", "history_len",
+                                         "reused_prefix", "_pad")] + \
                [("kv_position", C.c_int64), ("draws", C.c_uint64), ("prefill_seconds", C.c_double),
                 ("decode_seconds", C.c_double)]
 
 
-def run_config(shaping_cfg, max_new_tokens, block, uniform_mode=0, stop_tokens=(), adaptive=0, tree_nodes=0, tree_branching=()):
+def run_config(shaping_cfg, max_new_tokens, block, uniform_mode=0, stop_tokens=(), adaptive=0, tree_nodes=0, tree_branching=(),
+               reuse_prefix=False):
     rc = RunConfig()
+    rc.reuse_prefix = 1 if reuse_prefix else 0
     rc.tree_nodes, rc.tree_levels = tree_nodes, len(tree_branching)
     for i, b in enumerate(tree_branching):
         rc.tree_branching[i] = b
