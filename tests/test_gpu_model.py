@@ -240,3 +240,34 @@ def test_prefix_reuse_keeps_the_shared_rows_and_changes_nothing_else(rig, oracle
     _, e6, r6 = sess.sequential_run(turn3, reuse)
     assert r6.reused_prefix > 0 and np.array_equal(e6, e5)
     sess.close(), fresh.close()
+
+
+def test_many_row_passes_match_the_oracle_forward(rig, oracle):
+    """Passes of 24 rows and more run the matmuls on tensor memory with the reference's own operator order; a 40-row
+    chain verify and a 33-row tree verify must match the oracle's forward within the matmul tolerance."""
+    tsb = rig["tsb"]
+    sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 48)
+    ost = oracle.State(rig["ot"])
+    rng = np.random.default_rng(17)
+    prompt = rng.integers(0, rig["cfg"].vocab, size=30).astype(np.int32)
+    for i, t in enumerate(prompt):
+        sess.produce_prefill(int(t), i)
+    ost.forward(prompt, 0, want_logits=False)
+    feed = rng.integers(0, rig["cfg"].vocab, size=40).astype(np.int32)
+    base = sess.checkpoint()
+    got = sess.verify(feed, base)
+    want = ost.forward(feed, base)
+    _close(oracle, got, want, rel=4e-3, abs_=4e-3)
+    # the same rows a few at a time (register-MMA path) agree with the many-row pass within the same tolerance
+    sess.rollback_retaining(base, 0)
+    few = np.concatenate([sess.verify(feed[i:i + 8], base + i) for i in range(0, 40, 8)])
+    _close(oracle, got, few, rel=4e-3, abs_=4e-3)
+    # a tree of 32 nodes + anchor
+    sess.rollback_retaining(base, 0)
+    ost.cursor = base
+    parent = [-1] + [max(0, (i - 1) // 2) for i in range(1, 33)]
+    tfeed = rng.integers(0, rig["cfg"].vocab, size=33).astype(np.int32)
+    got_t = sess.verify_tree(tfeed, parent, base)
+    want_t = ost.forward(tfeed, base, parent=parent)
+    _close(oracle, got_t, want_t, rel=4e-3, abs_=4e-3)
+    sess.close()

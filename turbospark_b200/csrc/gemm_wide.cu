@@ -364,8 +364,10 @@ bool gemm_wide_supported(int qtype, int64_t rows, int64_t cols, int tokens) {
 }
 
 // x natural f16 [tokens, cols]; y [tokens, rows].  Token rows go through in passes of 64.
+size_t gemm_wide_workspace_bytes(int64_t cols) { return (size_t)(cols / 256) * WIDE_CHUNKS * WIDE_NMAX * 16; }
+
 cudaError_t launch_gemm_wide_q4k(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t rows, int64_t cols, const __half* x,
-                                 int64_t x_stride, int tokens, void* y, int64_t y_stride, bool y_f32) {
+                                 int64_t x_stride, int tokens, void* y, int64_t y_stride, bool y_f32, void* workspace) {
     const int units = (int)(cols / 256);
     static bool configured = false;
     const size_t smem_max = 1024 + (size_t)WIDE_RAW_STAGES * WIDE_RAW_BYTES + (size_t)WIDE_B_STAGES * WIDE_CHUNKS * WIDE_NMAX * 16;
@@ -377,9 +379,10 @@ cudaError_t launch_gemm_wide_q4k(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w
     for (int t0 = 0; t0 < tokens; t0 += WIDE_NMAX) {
         const int nt = min(WIDE_NMAX, tokens - t0);
         const int n_pad = (nt + 15) / 16 * 16;
-        uint4* xw = nullptr;
+        uint4* xw = static_cast<uint4*>(workspace);  // successive passes reuse it in stream order
         const size_t xw_bytes = (size_t)units * WIDE_CHUNKS * n_pad * 16;
-        cudaError_t e = cudaMallocAsync((void**)&xw, xw_bytes, st);
+        cudaError_t e = cudaSuccess;
+        if (!workspace) e = cudaMallocAsync((void**)&xw, xw_bytes, st);
         if (e != cudaSuccess) return e;
         const int64_t total = (int64_t)units * WIDE_CHUNKS * n_pad;
         e = tsb_launch(ctx, wide_prepare_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, true, x + (size_t)t0 * x_stride,
@@ -393,7 +396,7 @@ cudaError_t launch_gemm_wide_q4k(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w
             e = tsb_launch(ctx, gemm_wide_q4k_kernel, grid, dim3(WIDE_THREADS), smem, st, true, w, rows, units, (const uint4*)xw, n_pad, nt,
                            (void*)yp, y_stride, (int)(y_f32 ? 1 : 0), ctx->dev_error);
         }
-        cudaFreeAsync(xw, st);
+        if (!workspace) cudaFreeAsync(xw, st);
         if (e != cudaSuccess) return e;
     }
     return cudaSuccess;

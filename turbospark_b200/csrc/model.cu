@@ -273,6 +273,8 @@ int64_t tsb_model_weight_bytes(const tsb_model* m) {
 
 }  // extern "C"
 
+constexpr int WIDE_MIN_ROWS = 24;  // passes of this many rows and more take the tensor-memory matmul
+
 static int32_t model_complete(const tsb_model* m) {
     tsb_ctx* ctx = m->ctx;
     for (size_t i = 0; i < m->layers.size(); i++) {
@@ -322,7 +324,77 @@ static int32_t runtime_init(tsb_session* s, ModelRt& rt, const tsb_model* model,
     if ((rc = A(rt.attn_scratch_bytes, &rt.attn_scratch))) return rc;
     cudaMemset(rt.attn_scratch, 0, rt.attn_scratch_bytes);  // the ticket words start at zero
     rt.fed.assign(n_streams, std::vector<int32_t>());
+    // the many-row path: only when the session can hold that many rows and every matrix suits the kernel
+    bool wide = R >= WIDE_MIN_ROWS && gemm_wide_supported(model->lm_head.qtype, model->lm_head.rows, model->lm_head.cols, R);
+    for (const LayerW& l : model->layers)
+        wide = wide && gemm_wide_supported(l.wqkv.qtype, l.wqkv.rows, l.wqkv.cols, R) && gemm_wide_supported(l.wo.qtype, l.wo.rows, l.wo.cols, R) &&
+               gemm_wide_supported(l.wgu.qtype, l.wgu.rows, l.wgu.cols, R) && gemm_wide_supported(l.wdown.qtype, l.wdown.rows, l.wdown.cols, R);
+    {
+        const char* env = getenv("TSB_WIDE_FORWARD");
+        if (env && env[0] == '0') wide = false;
+    }
+    if (wide) {
+        const int64_t widest = std::max<int64_t>(std::max<int64_t>(c.d_model, od), c.ffn);
+        if ((rc = A((size_t)R * c.d_model * 2, (void**)&rt.w_xn)) || (rc = A((size_t)R * qkv_dim * 2, (void**)&rt.w_qkv)) ||
+            (rc = A((size_t)R * od * 2, (void**)&rt.w_ao)) || (rc = A((size_t)R * c.d_model * 2, (void**)&rt.w_o)) ||
+            (rc = A((size_t)R * 2 * c.ffn * 2, (void**)&rt.w_gu)) || (rc = A((size_t)R * c.ffn * 2, (void**)&rt.w_a)) ||
+            (rc = A((size_t)R * c.vocab * 2, (void**)&rt.w_logits)) || (rc = A(gemm_wide_workspace_bytes(widest), &rt.w_ws)))
+            return rc;
+        rt.wide_ok = true;
+    }
     return TSB_OK;
+}
+
+// The same pass for many rows: natural-layout f16 activations, the tensor-memory matmul, and the reference's own
+// operator order and rounding points (rms_norm -> matmul -> rope/store -> attention -> o_proj -> residual + rms_norm ->
+// gate|up -> silu*up -> down -> residual; crates/runtime/src/families/llama/mod.rs:205-291).
+static cudaError_t forward_device_wide(tsb_session* s, ModelRt& rt, const int32_t* tokens_dev, int token_stride,
+                                       const tsb_row_desc* rows_dev, int rows, int rows_per_seq, int max_len, __half* logits,
+                                       int64_t logits_stride, bool last_rows_only) {
+    tsb_ctx* ctx = s->ctx;
+    cudaStream_t st = s->stream;
+    const tsb_model* m = rt.model;
+    const tsb_model_config& c = m->cfg;
+    const float scale = 1.0f / sqrtf((float)c.head_dim);
+    const int64_t od = (int64_t)c.n_q_heads * c.head_dim, qkv_dim = (int64_t)(c.n_q_heads + 2 * c.n_kv_heads) * c.head_dim;
+    const ActOut none{nullptr, nullptr};
+    cudaError_t e;
+#define FW(x)                           \
+    do {                                \
+        e = (x);                        \
+        if (e != cudaSuccess) return e; \
+    } while (0)
+    FW(launch_embed_rows(ctx, st, m->embed.qtype, m->embed.data, c.vocab, c.d_model, tokens_dev, token_stride, rows, rt.h, 1.0f));
+    FW(launch_rmsnorm_rows(ctx, st, rt.h, nullptr, m->layers[0].attn_norm, rt.w_xn, none, rows, c.d_model, c.rms_eps));
+    for (int L = 0; L < c.n_layers; L++) {
+        const LayerW& l = m->layers[L];
+        FW(launch_gemm_wide_q4k(ctx, st, l.wqkv.data, l.wqkv.rows, l.wqkv.cols, rt.w_xn, c.d_model, rows, rt.w_qkv, qkv_dim, false, rt.w_ws));
+        FW(launch_rope_store_kv(ctx, st, rt.kv, L, rt.w_qkv, rows_dev, rows, c.n_q_heads, c.rope_theta));
+        FW(launch_attn_decode_rows(ctx, st, rt.kv, L, rt.w_qkv, qkv_dim, rt.w_ao, none, rows_dev, rows, rows_per_seq, c.n_q_heads, scale,
+                                   max_len, rt.attn_scratch, s->n_streams * s->max_rows));
+        FW(launch_gemm_wide_q4k(ctx, st, l.wo.data, l.wo.rows, l.wo.cols, rt.w_ao, od, rows, rt.w_o, c.d_model, false, rt.w_ws));
+        FW(launch_rmsnorm_rows(ctx, st, rt.h, rt.w_o, l.ffn_norm, rt.w_xn, none, rows, c.d_model, c.rms_eps));
+        FW(launch_gemm_wide_q4k(ctx, st, l.wgu.data, l.wgu.rows, l.wgu.cols, rt.w_xn, c.d_model, rows, rt.w_gu, 2 * (int64_t)c.ffn, false, rt.w_ws));
+        FW(launch_silu_mul(ctx, st, rt.w_gu, rt.w_gu + c.ffn, rt.w_a, none, rows, c.ffn, 2 * (int64_t)c.ffn, c.ffn));
+        FW(launch_gemm_wide_q4k(ctx, st, l.wdown.data, l.wdown.rows, l.wdown.cols, rt.w_a, c.ffn, rows, rt.w_o, c.d_model, false, rt.w_ws));
+        const void* g = L + 1 < c.n_layers ? (const void*)m->layers[L + 1].attn_norm : (const void*)m->out_norm;
+        FW(launch_rmsnorm_rows(ctx, st, rt.h, rt.w_o, g, rt.w_xn, none, rows, c.d_model, c.rms_eps));
+    }
+    if (logits) {
+        if (last_rows_only && rows_per_seq > 1) {
+            // every row's logits into the staging buffer, then each stream's last row to its place
+            FW(launch_gemm_wide_q4k(ctx, st, m->lm_head.data, m->lm_head.rows, m->lm_head.cols, rt.w_xn, c.d_model, rows, rt.w_logits, c.vocab,
+                                    false, rt.w_ws));
+            FW(cudaMemcpy2DAsync(logits, (size_t)logits_stride * 2, rt.w_logits + (size_t)(rows_per_seq - 1) * c.vocab,
+                                 (size_t)rows_per_seq * c.vocab * 2, (size_t)c.vocab * 2, (size_t)(rows / rows_per_seq),
+                                 cudaMemcpyDeviceToDevice, st));
+        } else {
+            FW(launch_gemm_wide_q4k(ctx, st, m->lm_head.data, m->lm_head.rows, m->lm_head.cols, rt.w_xn, c.d_model, rows, logits, logits_stride,
+                                    false, rt.w_ws));
+        }
+    }
+#undef FW
+    return cudaSuccess;
 }
 
 // One forward pass over `rows` rows (rows_per_seq per stream).  Row descriptors and token ids are
@@ -331,6 +403,9 @@ static cudaError_t forward_device(tsb_session* s, ModelRt& rt, const int32_t* to
                                   const tsb_row_desc* rows_dev, int rows, int rows_per_seq, int max_len, __half* logits,
                                   int64_t logits_stride, bool last_rows_only = false) {
     if (s->replay) return cudaSuccess;  // the captured graph already holds this work
+    if (rt.wide_ok && rows >= WIDE_MIN_ROWS)
+        return forward_device_wide(s, rt, tokens_dev, token_stride, rows_dev, rows, rows_per_seq, (max_len + 511) / 512 * 512, logits,
+                                   logits_stride, last_rows_only);
     tsb_ctx* ctx = s->ctx;
     cudaStream_t st = s->stream;
     const tsb_model* m = rt.model;

@@ -43,6 +43,10 @@ struct ModelRt {
     ActBuf act_d, act_o, act_f;  // matmul operands of width d_model, n_q_heads*head_dim, ffn
     void* attn_scratch = nullptr;
     size_t attn_scratch_bytes = 0;
+    // many-row passes (24 rows and more, all matrices Q4_K): natural-layout f16 buffers around the tensor-memory matmul
+    bool wide_ok = false;
+    __half *w_xn = nullptr, *w_qkv = nullptr, *w_ao = nullptr, *w_o = nullptr, *w_gu = nullptr, *w_a = nullptr, *w_logits = nullptr;
+    void* w_ws = nullptr;
     std::vector<std::vector<int32_t>> fed;  // per stream: tokens absorbed, by position (target only)
 };
 
