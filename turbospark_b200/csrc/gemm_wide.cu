@@ -133,16 +133,23 @@ __global__ void wide_prepare_kernel(const __half* __restrict__ x, int64_t x_stri
 
 __global__ void __launch_bounds__(WIDE_THREADS, 1)
     gemm_wide_q4k_kernel(const uint8_t* __restrict__ W, int64_t rows, int units, const uint4* __restrict__ xw, int n_pad, int tokens,
-                         void* __restrict__ y, int64_t y_stride, int y_f32, uint32_t* __restrict__ err) {
+                         void* __restrict__ y, int64_t y_stride, int y_f32, int ksplit, float* __restrict__ part,
+                         uint32_t* __restrict__ err) {
     extern __shared__ __align__(1024) uint8_t smem[];
     WideBars* bars = reinterpret_cast<WideBars*>(smem);
     uint8_t* raw_ring = smem + 1024;
     uint8_t* b_ring = raw_ring + WIDE_RAW_STAGES * WIDE_RAW_BYTES;
     const int b_stage_bytes = WIDE_CHUNKS * n_pad * 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_tiles = (int)(rows / WM);
+    // a work item is a 128-row tile, or (matrices with few tiles) one of `ksplit` runs of its blocks; the partial
+    // sums of the runs go to `part` and a small kernel adds them in run order
+    const int n_items = (int)(rows / WM) * ksplit;
     const int64_t row_bytes = (int64_t)units * 144;
-    const int raw_iters = (units + WIDE_UPS - 1) / WIDE_UPS;
+    const int upk = ((units + ksplit - 1) / ksplit + WIDE_UPS - 1) / WIDE_UPS * WIDE_UPS;  // blocks per run, whole raw stages
+    auto item_blocks = [&](int item, int* b0) {
+        *b0 = (item % ksplit) * upk;
+        return max(0, min(units, *b0 + upk) - *b0);
+    };
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < WIDE_RAW_STAGES; i++) mbar_init(&bars->raw_full[i], 1), mbar_init(&bars->raw_empty[i], WIDE_DEQ_WARPS);
@@ -171,13 +178,16 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1)
         // ---- producer
         uint32_t nraw = 0, nb = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-            const uint8_t* wt = W + (int64_t)tile * WM * row_bytes;
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            int b0;
+            const int nblk = item_blocks(item, &b0);
+            const int raw_iters = (nblk + WIDE_UPS - 1) / WIDE_UPS;
+            const uint8_t* wt = W + (int64_t)(item / ksplit) * WM * row_bytes + (int64_t)b0 * 144;
             for (int it = 0; it < raw_iters && ok; it++, nraw++) {
                 const uint32_t s = nraw % WIDE_RAW_STAGES;
                 if (nraw >= WIDE_RAW_STAGES) ok = mbar_wait(&bars->raw_empty[s], ((nraw / WIDE_RAW_STAGES) - 1) & 1, err);
                 if (!ok) break;
-                const int nun = min(WIDE_UPS, units - it * WIDE_UPS);
+                const int nun = min(WIDE_UPS, nblk - it * WIDE_UPS);
                 const uint32_t per_row = (uint32_t)nun * 144u;
                 if (lane == 0) mbar_expect_tx(&bars->raw_full[s], per_row * WM);
                 __syncwarp();
@@ -194,7 +204,7 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1)
                     if (!ok) break;
                     if (lane == 0) {
                         mbar_expect_tx(&bars->b_full[bs], (uint32_t)b_stage_bytes);
-                        bulk_g2s(b_ring + bs * b_stage_bytes, xw + (size_t)(it * WIDE_UPS + u) * WIDE_CHUNKS * n_pad, (uint32_t)b_stage_bytes,
+                        bulk_g2s(b_ring + bs * b_stage_bytes, xw + (size_t)(b0 + it * WIDE_UPS + u) * WIDE_CHUNKS * n_pad, (uint32_t)b_stage_bytes,
                                  &bars->b_full[bs]);
                     }
                     __syncwarp();
@@ -212,8 +222,10 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1)
             const uint64_t desc_hi = ((uint64_t)((uint32_t)(n_pad * 16) >> 4) << 16) | ((uint64_t)(128u >> 4) << 32) | (1ull << 46);
             uint32_t nb = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                for (int blk = 0; blk < units && ok; blk++, nb++) {
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                int b0;
+                const int nblk = item_blocks(item, &b0);
+                for (int blk = 0; blk < nblk && ok; blk++, nb++) {
                     const uint32_t as = nb & 1, bs = nb % WIDE_B_STAGES;
                     ok = mbar_wait(&bars->a_full[as], (nb >> 1) & 1, err) && mbar_wait(&bars->b_full[bs], (nb / WIDE_B_STAGES) & 1, err);
                     if (ok && nb >= 1) ok = mbar_wait(&bars->d_empty, (nb - 1) & 1, err);  // the previous block's accumulators were read
@@ -259,7 +271,11 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1)
             __syncwarp();
             if (lane == 0 && ok) mbar_arrive(&bars->d_empty);
         };
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+            int b0;
+            const int nblk = item_blocks(item, &b0);
+            const int raw_iters = (nblk + WIDE_UPS - 1) / WIDE_UPS;
+            const int tile = item / ksplit, ks = item % ksplit;
             float acc[16];
 #pragma unroll
             for (int i = 0; i < 16; i++) acc[i] = 0.f;
@@ -268,7 +284,7 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1)
             for (int it = 0; it < raw_iters; it++, nraw++) {
                 const uint32_t s = nraw % WIDE_RAW_STAGES;
                 if (ok) ok = mbar_wait(&bars->raw_full[s], (nraw / WIDE_RAW_STAGES) & 1, err);
-                const int nun = min(WIDE_UPS, units - it * WIDE_UPS);
+                const int nun = min(WIDE_UPS, nblk - it * WIDE_UPS);
                 for (int u = 0; u < nun; u++, nb++, blk++) {
                     const uint32_t as = nb & 1;
                     if (ok && nb >= 2) ok = mbar_wait(&bars->a_empty[as], ((nb >> 1) - 1) & 1, err);
@@ -331,14 +347,16 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1)
                 __syncwarp();
                 if (lane == 0 && ok) mbar_arrive(&bars->raw_empty[s]);
             }
-            drain(nb - 1, d_prev, dmin_prev, acc);  // the tile's last block
+            if (nblk > 0) drain(nb - 1, d_prev, dmin_prev, acc);  // the item's last block
             if (ok && reads_d) {
                 const int64_t orow = (int64_t)tile * WM + row;
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
                     const int n = 16 * g + i;
                     if (n < tokens) {
-                        if (y_f32)
+                        if (ksplit > 1)
+                            part[((size_t)ks * tokens + n) * rows + orow] = acc[i];
+                        else if (y_f32)
                             reinterpret_cast<float*>(y)[(size_t)n * y_stride + orow] = acc[i];
                         else
                             reinterpret_cast<__half*>(y)[(size_t)n * y_stride + orow] = __float2half_rn(acc[i]);
@@ -357,6 +375,22 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1)
     }
 }
 
+// y[n, r] = sum over runs, in run order, of part[run][n][r]
+__global__ void wide_reduce_kernel(const float* __restrict__ part, int ksplit, int tokens, int64_t rows, void* __restrict__ y,
+                                   int64_t y_stride, int y_f32) {
+    pdl_wait();
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)tokens * rows) return;
+    const int n = (int)(idx / rows);
+    const int64_t r = idx % rows;
+    float v = 0.f;
+    for (int k = 0; k < ksplit; k++) v += part[((size_t)k * tokens + n) * rows + r];
+    if (y_f32)
+        reinterpret_cast<float*>(y)[(size_t)n * y_stride + r] = v;
+    else
+        reinterpret_cast<__half*>(y)[(size_t)n * y_stride + r] = __float2half_rn(v);
+}
+
 }  // namespace
 
 bool gemm_wide_supported(int qtype, int64_t rows, int64_t cols, int tokens) {
@@ -364,11 +398,23 @@ bool gemm_wide_supported(int qtype, int64_t rows, int64_t cols, int tokens) {
 }
 
 // x natural f16 [tokens, cols]; y [tokens, rows].  Token rows go through in passes of 64.
+// how many runs a tile's blocks are cut into so that a matrix with few 128-row tiles still fills the device
+static int wide_ksplit(const tsb_ctx* ctx, int64_t rows, int units) {
+    const int tiles = (int)(rows / WM);
+    int k = 1;
+    while (k < 8 && tiles * (k * 2) <= ctx->sm_count + ctx->sm_count / 4 && units / (k * 2) >= 4) k *= 2;
+    return k;
+}
 size_t gemm_wide_workspace_bytes(int64_t cols) { return (size_t)(cols / 256) * WIDE_CHUNKS * WIDE_NMAX * 16; }
+size_t gemm_wide_partial_bytes(const tsb_ctx* ctx, int64_t rows, int64_t cols) {
+    const int k = wide_ksplit(ctx, rows, (int)(cols / 256));
+    return k > 1 ? (size_t)k * WIDE_NMAX * rows * sizeof(float) : 0;
+}
 
 cudaError_t launch_gemm_wide_q4k(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t rows, int64_t cols, const __half* x,
-                                 int64_t x_stride, int tokens, void* y, int64_t y_stride, bool y_f32, void* workspace) {
+                                 int64_t x_stride, int tokens, void* y, int64_t y_stride, bool y_f32, void* workspace, void* partials) {
     const int units = (int)(cols / 256);
+    const int ksplit = wide_ksplit(ctx, rows, units);
     static bool configured = false;
     const size_t smem_max = 1024 + (size_t)WIDE_RAW_STAGES * WIDE_RAW_BYTES + (size_t)WIDE_B_STAGES * WIDE_CHUNKS * WIDE_NMAX * 16;
     if (!configured) {
@@ -390,11 +436,20 @@ cudaError_t launch_gemm_wide_q4k(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w
         if (e == cudaSuccess) {
             // one CTA per SM: the kernel wants the whole tensor memory and most of the shared memory
             const size_t smem = 1024 + (size_t)WIDE_RAW_STAGES * WIDE_RAW_BYTES + (size_t)WIDE_B_STAGES * WIDE_CHUNKS * n_pad * 16;
-            const int n_tiles = (int)(rows / WM);
-            dim3 grid((unsigned)min(n_tiles, ctx->sm_count));
+            const int n_items = (int)(rows / WM) * ksplit;
+            dim3 grid((unsigned)min(n_items, ctx->sm_count));
             uint8_t* yp = static_cast<uint8_t*>(y) + (size_t)t0 * y_stride * (y_f32 ? 4 : 2);
-            e = tsb_launch(ctx, gemm_wide_q4k_kernel, grid, dim3(WIDE_THREADS), smem, st, true, w, rows, units, (const uint4*)xw, n_pad, nt,
-                           (void*)yp, y_stride, (int)(y_f32 ? 1 : 0), ctx->dev_error);
+            float* part = static_cast<float*>(partials);
+            if (ksplit > 1 && !part) e = cudaMallocAsync((void**)&part, (size_t)ksplit * nt * rows * sizeof(float), st);
+            if (e == cudaSuccess)
+                e = tsb_launch(ctx, gemm_wide_q4k_kernel, grid, dim3(WIDE_THREADS), smem, st, true, w, rows, units, (const uint4*)xw, n_pad,
+                               nt, (void*)yp, y_stride, (int)(y_f32 ? 1 : 0), ksplit, part, ctx->dev_error);
+            if (e == cudaSuccess && ksplit > 1) {
+                const int64_t total = (int64_t)nt * rows;
+                e = tsb_launch(ctx, wide_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, true, (const float*)part,
+                               ksplit, nt, rows, (void*)yp, y_stride, (int)(y_f32 ? 1 : 0));
+            }
+            if (ksplit > 1 && !partials && part) cudaFreeAsync(part, st);
         }
         if (!workspace) cudaFreeAsync(xw, st);
         if (e != cudaSuccess) return e;

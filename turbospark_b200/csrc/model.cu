@@ -340,6 +340,10 @@ static int32_t runtime_init(tsb_session* s, ModelRt& rt, const tsb_model* model,
             (rc = A((size_t)R * 2 * c.ffn * 2, (void**)&rt.w_gu)) || (rc = A((size_t)R * c.ffn * 2, (void**)&rt.w_a)) ||
             (rc = A((size_t)R * c.vocab * 2, (void**)&rt.w_logits)) || (rc = A(gemm_wide_workspace_bytes(widest), &rt.w_ws)))
             return rc;
+        size_t part = gemm_wide_partial_bytes(ctx, model->lm_head.rows, model->lm_head.cols);
+        for (const LayerW& l : model->layers)
+            for (const Mat* mt : {&l.wqkv, &l.wo, &l.wgu, &l.wdown}) part = std::max(part, gemm_wide_partial_bytes(ctx, mt->rows, mt->cols));
+        if (part && (rc = A(part, &rt.w_part))) return rc;
         rt.wide_ok = true;
     }
     return TSB_OK;
@@ -368,15 +372,15 @@ static cudaError_t forward_device_wide(tsb_session* s, ModelRt& rt, const int32_
     FW(launch_rmsnorm_rows(ctx, st, rt.h, nullptr, m->layers[0].attn_norm, rt.w_xn, none, rows, c.d_model, c.rms_eps));
     for (int L = 0; L < c.n_layers; L++) {
         const LayerW& l = m->layers[L];
-        FW(launch_gemm_wide_q4k(ctx, st, l.wqkv.data, l.wqkv.rows, l.wqkv.cols, rt.w_xn, c.d_model, rows, rt.w_qkv, qkv_dim, false, rt.w_ws));
+        FW(launch_gemm_wide_q4k(ctx, st, l.wqkv.data, l.wqkv.rows, l.wqkv.cols, rt.w_xn, c.d_model, rows, rt.w_qkv, qkv_dim, false, rt.w_ws, rt.w_part));
         FW(launch_rope_store_kv(ctx, st, rt.kv, L, rt.w_qkv, rows_dev, rows, c.n_q_heads, c.rope_theta));
         FW(launch_attn_decode_rows(ctx, st, rt.kv, L, rt.w_qkv, qkv_dim, rt.w_ao, none, rows_dev, rows, rows_per_seq, c.n_q_heads, scale,
                                    max_len, rt.attn_scratch, s->n_streams * s->max_rows));
-        FW(launch_gemm_wide_q4k(ctx, st, l.wo.data, l.wo.rows, l.wo.cols, rt.w_ao, od, rows, rt.w_o, c.d_model, false, rt.w_ws));
+        FW(launch_gemm_wide_q4k(ctx, st, l.wo.data, l.wo.rows, l.wo.cols, rt.w_ao, od, rows, rt.w_o, c.d_model, false, rt.w_ws, rt.w_part));
         FW(launch_rmsnorm_rows(ctx, st, rt.h, rt.w_o, l.ffn_norm, rt.w_xn, none, rows, c.d_model, c.rms_eps));
-        FW(launch_gemm_wide_q4k(ctx, st, l.wgu.data, l.wgu.rows, l.wgu.cols, rt.w_xn, c.d_model, rows, rt.w_gu, 2 * (int64_t)c.ffn, false, rt.w_ws));
+        FW(launch_gemm_wide_q4k(ctx, st, l.wgu.data, l.wgu.rows, l.wgu.cols, rt.w_xn, c.d_model, rows, rt.w_gu, 2 * (int64_t)c.ffn, false, rt.w_ws, rt.w_part));
         FW(launch_silu_mul(ctx, st, rt.w_gu, rt.w_gu + c.ffn, rt.w_a, none, rows, c.ffn, 2 * (int64_t)c.ffn, c.ffn));
-        FW(launch_gemm_wide_q4k(ctx, st, l.wdown.data, l.wdown.rows, l.wdown.cols, rt.w_a, c.ffn, rows, rt.w_o, c.d_model, false, rt.w_ws));
+        FW(launch_gemm_wide_q4k(ctx, st, l.wdown.data, l.wdown.rows, l.wdown.cols, rt.w_a, c.ffn, rows, rt.w_o, c.d_model, false, rt.w_ws, rt.w_part));
         const void* g = L + 1 < c.n_layers ? (const void*)m->layers[L + 1].attn_norm : (const void*)m->out_norm;
         FW(launch_rmsnorm_rows(ctx, st, rt.h, rt.w_o, g, rt.w_xn, none, rows, c.d_model, c.rms_eps));
     }
@@ -384,13 +388,13 @@ static cudaError_t forward_device_wide(tsb_session* s, ModelRt& rt, const int32_
         if (last_rows_only && rows_per_seq > 1) {
             // every row's logits into the staging buffer, then each stream's last row to its place
             FW(launch_gemm_wide_q4k(ctx, st, m->lm_head.data, m->lm_head.rows, m->lm_head.cols, rt.w_xn, c.d_model, rows, rt.w_logits, c.vocab,
-                                    false, rt.w_ws));
+                                    false, rt.w_ws, rt.w_part));
             FW(cudaMemcpy2DAsync(logits, (size_t)logits_stride * 2, rt.w_logits + (size_t)(rows_per_seq - 1) * c.vocab,
                                  (size_t)rows_per_seq * c.vocab * 2, (size_t)c.vocab * 2, (size_t)(rows / rows_per_seq),
                                  cudaMemcpyDeviceToDevice, st));
         } else {
             FW(launch_gemm_wide_q4k(ctx, st, m->lm_head.data, m->lm_head.rows, m->lm_head.cols, rt.w_xn, c.d_model, rows, logits, logits_stride,
-                                    false, rt.w_ws));
+                                    false, rt.w_ws, rt.w_part));
         }
     }
 #undef FW

@@ -47,6 +47,7 @@ struct ModelRt {
     bool wide_ok = false;
     __half *w_xn = nullptr, *w_qkv = nullptr, *w_ao = nullptr, *w_o = nullptr, *w_gu = nullptr, *w_a = nullptr, *w_logits = nullptr;
     void* w_ws = nullptr;
+    void* w_part = nullptr;  // split sums of the matmuls with few row tiles
     std::vector<std::vector<int32_t>> fed;  // per stream: tokens absorbed, by position (target only)
 };
 
