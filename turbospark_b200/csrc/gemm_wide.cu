@@ -87,6 +87,13 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "memory");
 }
 
+__device__ __forceinline__ void tc_ld4(uint32_t taddr, uint32_t (&r)[4]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr)
+                 : "memory");
+}
+
 struct WideBars {
     uint64_t raw_full[WIDE_RAW_STAGES], raw_empty[WIDE_RAW_STAGES];
     uint64_t b_full[WIDE_B_STAGES], b_empty[WIDE_B_STAGES];
@@ -252,20 +259,33 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1)
         const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
         uint32_t nraw = 0, nb = 0;
         bool ok = true;
-        const bool reads_d = 16 * g < n_pad;  // this warp's 16 accumulator columns hold token rows
+        // the accumulator columns (token rows) are dealt evenly to the four warps of a lane quadrant: n_pad / 4 each
+        const int cpw = n_pad >> 2;
         // fold block `which`'s accumulators into the registers: acc += d * D1 - dmin * D2
         auto drain = [&](uint32_t which, float d, float dmin, float (&acc)[16]) {
             if (ok) ok = mbar_wait(&bars->d_full, which & 1, err);
             if (ok) {
                 tc_fence_after();
-                if (reads_d) {
-                    uint32_t p[16], m[16];
-                    tc_ld16(tmem_d1 + lane_base + 16 * g, p);
-                    tc_ld16(tmem_d2 + lane_base + 16 * g, m);
-                    tc_wait_ld();
+                // eight columns per round trip keeps the loaded values in sixteen registers
 #pragma unroll
-                    for (int i = 0; i < 16; i++) acc[i] = fmaf(d, __uint_as_float(p[i]), fmaf(-dmin, __uint_as_float(m[i]), acc[i]));
-                }
+                for (int h = 0; h < 2; h++)
+                    if (8 * h < cpw) {
+                        uint32_t a4[2][4], b4[2][4];
+#pragma unroll
+                        for (int q = 0; q < 2; q++)
+                            if (8 * h + 4 * q < cpw) {
+                                tc_ld4(tmem_d1 + lane_base + g * cpw + 8 * h + 4 * q, a4[q]);
+                                tc_ld4(tmem_d2 + lane_base + g * cpw + 8 * h + 4 * q, b4[q]);
+                            }
+                        tc_wait_ld();
+#pragma unroll
+                        for (int q = 0; q < 2; q++)
+                            if (8 * h + 4 * q < cpw) {
+#pragma unroll
+                                for (int i = 0; i < 4; i++)
+                                    acc[8 * h + 4 * q + i] = fmaf(d, __uint_as_float(a4[q][i]), fmaf(-dmin, __uint_as_float(b4[q][i]), acc[8 * h + 4 * q + i]));
+                            }
+                    }
                 tc_fence_before();
             }
             __syncwarp();
@@ -297,20 +317,18 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1)
                         const uint4 qb = *reinterpret_cast<const uint4*>(bp + 32 + 32 * g);
                         const __half2 dd = *reinterpret_cast<const __half2*>(&hdr.x);
                         d = __low2float(dd), dmin = __high2float(dd);
-                        // 6-bit scale / min of sub-blocks 2g and 2g+1 (crates/compute/src/quant_gguf/q4_k.rs:43-54)
-                        auto sbyte = [&](int k) -> uint32_t {
-                            const uint32_t w = k < 4 ? hdr.y : (k < 8 ? hdr.z : hdr.w);
-                            return (w >> (8 * (k & 3))) & 0xFFu;
-                        };
+                        // 6-bit scale / min of sub-blocks j = 2g and 2g+1 (crates/compute/src/quant_gguf/q4_k.rs:43-54): byte
+                        // j & 3 of the scale word (j < 4) or of the high word combined with two bits of the low words (j >= 4)
                         uint32_t scv[2], mv[2];
 #pragma unroll
                         for (int h = 0; h < 2; h++) {
-                            const int j = 2 * g + h;
-                            if (j < 4) {
-                                scv[h] = sbyte(j) & 63u, mv[h] = sbyte(j + 4) & 63u;
+                            const int sh = 16 * (g & 1) + 8 * h;
+                            const uint32_t y = hdr.y >> sh, z = hdr.z >> sh, w = hdr.w >> sh;
+                            if (g < 2) {
+                                scv[h] = y & 63u, mv[h] = z & 63u;
                             } else {
-                                scv[h] = (sbyte(j + 4) & 0xFu) | ((sbyte(j - 4) >> 6) << 4);
-                                mv[h] = (sbyte(j + 4) >> 4) | ((sbyte(j) >> 6) << 4);
+                                scv[h] = (w & 0xFu) | ((y >> 2) & 0x30u);
+                                mv[h] = ((w >> 4) & 0xFu) | ((z >> 2) & 0x30u);
                             }
                         }
                         // integers up to 63 as f16 pairs: (0x6400 | v) is 1024 + v
@@ -348,12 +366,12 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1)
                 if (lane == 0 && ok) mbar_arrive(&bars->raw_empty[s]);
             }
             if (nblk > 0) drain(nb - 1, d_prev, dmin_prev, acc);  // the item's last block
-            if (ok && reads_d) {
+            if (ok) {
                 const int64_t orow = (int64_t)tile * WM + row;
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
-                    const int n = 16 * g + i;
-                    if (n < tokens) {
+                    const int n = g * cpw + i;
+                    if (i < cpw && n < tokens) {
                         if (ksplit > 1)
                             part[((size_t)ks * tokens + n) * rows + orow] = acc[i];
                         else if (y_f32)
