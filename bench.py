@@ -58,7 +58,13 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append([c.strip() for c in line.split(",")] + [time.time()])
+
+    def window(self, t0, t1):
+        """Keep the samples taken between t0 and t1 (host clock); all of them when none fell inside."""
+        inside = [r for r in self.rows if t0 <= r[-1] <= t1]
+        if inside:
+            self.rows = inside
 
     def stop(self):
         if not self.proc:
@@ -68,7 +74,8 @@ class ClockSampler:
         sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
         mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower().startswith("active") for r in self.rows)]
+        reasons = [n for i, n in enumerate(names)
+                   if any(len(r) > 3 + i and str(r[2 + i]).lower().startswith("active") for r in self.rows)]
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
                 "samples": len(sm)}
 
@@ -157,6 +164,10 @@ def run_ours(args, rank, world, local_rank):
     ctx = tsb.Ctx(local_rank)
     S, K = args.streams, BLOCK
     max_ctx = CONTEXT + (args.steps + args.warmup + 8) * (K + 1) + 64
+    # the sampler starts before the set-up (nvidia-smi takes a while to come up on a box with eight GPUs); only the
+    # samples that fall inside the timed region are reported
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     target = tsb.Model(ctx, tsb.config_8b_target(max_ctx))
     target.fill_synthetic(tsb.Q4_K, seed=1)
     draft = tsb.Model(ctx, tsb.config_8b_draft(max_ctx))
@@ -178,8 +189,7 @@ def run_ours(args, rank, world, local_rank):
     for _ in range(args.warmup):
         sess.round(rc, nxt, steps_ctr)
     barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    t_begin = time.time()
     launches0 = ctx.launches
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     committed = accepted = 0
@@ -192,6 +202,7 @@ def run_ours(args, rank, world, local_rank):
         dev_ms += sess.round_times()[3]   # device time of the round: inputs resident, no host gaps
     e1.record(stream)
     barrier()
+    sampler.window(t_begin, time.time())
     clocks = sampler.stop()
     launches = ctx.launches - launches0
     e2e_ms = e0.elapsed_time(e1)          # whole loop: host staging, H2D, kernels, D2H, host commit
