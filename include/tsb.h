@@ -425,6 +425,12 @@ TSB_API int32_t tsb_sequential_run(tsb_session* s, int32_t stream, const int32_t
  * Streams must have equal cursors in the target and draft caches (lockstep). */
 TSB_API int32_t tsb_session_round(tsb_session* s, const tsb_run_config* cfg, int32_t* next_tokens_host,
                                   int32_t* accepted_host, uint64_t* draw_step_inout);
+/* The same round, also returning what each stream committed: tokens_out[stream * 16 + i] for i < accepted is the
+ * i-th accepted proposal, tokens_out[stream * 16 + accepted] the corrected / bonus token (the same value that lands
+ * in next_tokens_host).  A serving loop appends the confirmed token that entered the round, then the accepted ones
+ * (crates/runtime/src/speculative.rs:861-905). */
+TSB_API int32_t tsb_session_round_tokens(tsb_session* s, const tsb_run_config* cfg, int32_t* next_tokens_host,
+                                         int32_t* accepted_host, int32_t* tokens_out, uint64_t* draw_step_inout);
 /* Rounds run as one CUDA graph after the first (copies, kernels); 0 switches to plain launches, which is what
  * makes the per-phase timings below available.  Env TSB_GRAPH=0 does the same at session creation. */
 TSB_API int32_t tsb_session_set_graph(tsb_session* s, int32_t enabled);

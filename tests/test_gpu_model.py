@@ -271,3 +271,35 @@ def test_many_row_passes_match_the_oracle_forward(rig, oracle):
     want_t = ost.forward(tfeed, base, parent=parent)
     _close(oracle, got_t, want_t, rel=4e-3, abs_=4e-3)
     sess.close()
+
+
+def test_lockstep_rounds_over_three_streams_equal_three_single_stream_runs(rig, oracle):
+    """Independent streams in one session: every stream's greedy output from lockstep rounds equals its own
+    single-stream sequential run (streams of different lengths, different prompts)."""
+    tsb = rig["tsb"]
+    S, K, NEW = 3, 3, 20
+    sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], S, K + 1)
+    solo = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 8)
+    rng = np.random.default_rng(33)
+    prompts = [rng.integers(0, rig["cfg"].vocab, size=n).astype(np.int32) for n in (9, 21, 14)]
+    rc = tsb.run_config(tsb.shaping(temperature=0.0), 1 << 20, K)
+    want = [solo.sequential_run(p, tsb.run_config(tsb.shaping(temperature=0.0), NEW, K))[1] for p in prompts]
+    nxt = np.zeros(S, dtype=np.int32)
+    for q, p in enumerate(prompts):
+        for i, t in enumerate(p[:-1]):
+            sess.produce_prefill(int(t), i, stream=q)
+        lg = oracle.f16_bits_to_f32(sess.produce(int(p[-1]), len(p) - 1, stream=q))
+        nxt[q] = int(np.argmax(lg))
+        sess.prime_drafter(int(p[-1]), len(p) - 2, stream=q)
+    out = [[] for _ in range(S)]
+    steps = np.zeros(S, dtype=np.uint64)
+    for _ in range(NEW):
+        confirmed = nxt.copy()
+        acc, toks = sess.round_tokens(rc, nxt, steps)
+        for q in range(S):
+            out[q].append(int(confirmed[q]))
+            out[q].extend(int(t) for t in toks[q, :acc[q]])
+            assert toks[q, acc[q]] == nxt[q]
+    for q in range(S):
+        assert out[q][:NEW] == list(want[q][:NEW]), (q, out[q][:NEW], list(want[q][:NEW]))
+    sess.close(), solo.close()

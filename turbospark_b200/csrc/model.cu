@@ -1134,6 +1134,16 @@ int32_t tsb_session_round(tsb_session* s, const tsb_run_config* cfg, int32_t* ne
                                  nullptr, draw_step_inout);
 }
 
+int32_t tsb_session_round_tokens(tsb_session* s, const tsb_run_config* cfg, int32_t* next_tokens_host, int32_t* accepted_host,
+                                 int32_t* tokens_out, uint64_t* draw_step_inout) {
+    if (!s || !cfg || !next_tokens_host || !accepted_host || !tokens_out || !draw_step_inout) return TSB_ERR_INVALID;
+    DeviceGuard g(s->ctx);
+    std::vector<int32_t> streams(s->n_streams);
+    for (int q = 0; q < s->n_streams; q++) streams[q] = q;
+    return session_round_streams(s, streams.data(), s->n_streams, cfg->block, cfg, next_tokens_host, accepted_host, tokens_out,
+                                 nullptr, draw_step_inout);
+}
+
 void* tsb_session_stream(tsb_session* s) { return s ? (void*)s->stream : nullptr; }
 
 int32_t tsb_session_set_graph(tsb_session* s, int32_t enabled) {

@@ -185,6 +185,15 @@ class Session:
                                                accepted.ctypes.data_as(C.c_void_p), draw_steps.ctypes.data_as(C.c_void_p)))
         return accepted
 
+    def round_tokens(self, rc, next_tokens, draw_steps):
+        """round() that also returns the committed tokens: (accepted[n_streams], tokens[n_streams, 16])."""
+        accepted = np.zeros(self.n_streams, dtype=np.int32)
+        toks = np.full((self.n_streams, 16), -1, dtype=np.int32)
+        self.ctx.check(lib().tsb_session_round_tokens(self.h, C.byref(rc), next_tokens.ctypes.data_as(C.c_void_p),
+                                                      accepted.ctypes.data_as(C.c_void_p), toks.ctypes.data_as(C.c_void_p),
+                                                      draw_steps.ctypes.data_as(C.c_void_p)))
+        return accepted, toks
+
     def set_graph(self, enabled):
         self.ctx.check(lib().tsb_session_set_graph(self.h, C.c_int32(int(enabled))))
 
