@@ -603,22 +603,28 @@ __global__ void __launch_bounds__(ACC_THREADS)
         const double dmx = (double)mx, inv_t = 1.0 / temperature;
         const bool unit_t = temperature == 1.0;
         const bool truncating = (tr.top_k > 0 && tr.top_k < (unsigned)vocab) || tr.top_p > 0.0 || tr.min_p > 0.0;
-        // e = exp(l - max) and its sum
+        // e = exp(l - max) and its sum (and, when every entry survives, the last entry in rank order on the way)
         double acc = 0.0;
+        unsigned long long best = ~0ull;
+        unsigned int best_i = 0;
         for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
             const double e = exp((double)__half2float(row[sl.lo + j]) - dmx);
             ecache[j] = e;
             acc += e;
+            const unsigned long long eb = (unsigned long long)__double_as_longlong(e);
+            if (eb <= best) best = eb, best_i = (unsigned int)(sl.lo + j);  // indices grow with j
         }
         const double sum = cluster_sum_f64(cluster, &c.xch, 0, block_sum_f64(acc, c.red));
         const double top = 1.0 / sum;
         RowStats st;
         st.has_cut = 0, st.cut_key = 0xFFFFu, st.cut_idx = 0x7fffffff, st.min_e = 0.0;
         if (truncating) cluster_find_cut(cluster, c, ecache, sum, row, sl, vocab, tr, &st);
-        // weights of the survivors, their total, and the last survivor in rank order (smallest e, then the largest index)
+        // weights of the survivors, their total, and the last survivor in rank order (smallest e, then the largest index);
+        // at temperature 1 without truncation the weights are the exps themselves and the total is their sum
+        double total = sum;
+        if (truncating || !unit_t) {
         acc = 0.0;
-        unsigned long long best = ~0ull;
-        unsigned int best_i = 0;
+        best = ~0ull, best_i = 0;
         for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
             const double e = ecache[j];
             if (truncating && !survives(st, row[sl.lo + j], sl.lo + j, e)) {
@@ -634,7 +640,8 @@ __global__ void __launch_bounds__(ACC_THREADS)
             const unsigned long long eb = (unsigned long long)__double_as_longlong(e);
             if (eb <= best) best = eb, best_i = (unsigned int)(sl.lo + j);  // indices grow with j
         }
-        const double total = cluster_sum_f64(cluster, &c.xch, 1, block_sum_f64(acc, c.red));
+        total = cluster_sum_f64(cluster, &c.xch, 1, block_sum_f64(acc, c.red));
+        }
         if (threadIdx.x == 0) c.best_exp = ~0ull, c.best_idx = 0;
         __syncthreads();
         atomicMin(&c.best_exp, best);

@@ -390,9 +390,13 @@ __global__ void __maxnreg__(136)
             if (part == 0) part_ml[pi] = make_float2(m, den);
         }
     }
-    // nobody may leave while a neighbour still reads its shared memory
-    if (cluster_size > 1) cluster.sync();
-    if (n_clusters == 1) return;
+    // nobody may leave while a neighbour still reads its shared memory: arrive now, wait just before leaving, so the
+    // barrier's latency hides behind the ticket and the last merge
+    if (cluster_size > 1) cluster.barrier_arrive();
+    if (n_clusters == 1) {
+        if (cluster_size > 1) cluster.barrier_wait();
+        return;
+    }
 
     // ---- the last CTA to finish among all clusters of this (stream, kv head, query tile) merges the clusters'
     // shares.  A ticket counter decides who is last; nobody waits on anybody.
@@ -405,7 +409,10 @@ __global__ void __maxnreg__(136)
         if (s_last) tickets[ticket_id] = 0;  // ready for the next launch
     }
     __syncthreads();
-    if (!s_last) return;
+    if (!s_last) {
+        if (cluster_size > 1) cluster.barrier_wait();
+        return;
+    }
     __threadfence();
     for (int ql0 = 0; ql0 < QT; ql0 += QPP) {
         const int ql = ql0 + threadIdx.x / TPH;
@@ -443,6 +450,7 @@ __global__ void __maxnreg__(136)
         }
         if (act.xp) act_store8(accv, act.xp, act.xs, row, e0, (n_q_heads * HD) >> 8, active);
     }
+    if (cluster_size > 1) cluster.barrier_wait();
 }
 
 }  // namespace
