@@ -303,3 +303,21 @@ def test_lockstep_rounds_over_three_streams_equal_three_single_stream_runs(rig, 
     for q in range(S):
         assert out[q][:NEW] == list(want[q][:NEW]), (q, out[q][:NEW], list(want[q][:NEW]))
     sess.close(), solo.close()
+
+
+def test_adaptive_depth_changes_the_round_shape_not_the_output(rig, oracle):
+    """AdaptiveDepth (crates/runtime/src/speculative_adaptive.rs:104-225) only picks how many proposals a round offers:
+    greedy output stays token-identical to the sequential loop, and a run that starts at the floor offers less per
+    round than a fixed-depth run."""
+    tsb = rig["tsb"]
+    sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 16)
+    rng = np.random.default_rng(44)
+    prompt = rng.integers(0, rig["cfg"].vocab, size=20).astype(np.int32)
+    fixed = tsb.run_config(tsb.shaping(temperature=0.0), 48, 5)
+    adaptive = tsb.run_config(tsb.shaping(temperature=0.0), 48, 5, adaptive=2)
+    _, seq, _ = sess.sequential_run(prompt, fixed)
+    _, e_fixed, r_fixed = sess.spec_run(prompt, fixed)
+    _, e_adapt, r_adapt = sess.spec_run(prompt, adaptive)
+    assert np.array_equal(seq, e_fixed) and np.array_equal(seq, e_adapt)
+    assert r_adapt.new_tokens == 48 and r_adapt.rounds >= r_fixed.rounds
+    sess.close()
