@@ -320,8 +320,9 @@ enum { TSB_N_ATTN = 0, TSB_N_FFN, TSB_N_OUT };
 
 TSB_API int32_t tsb_model_create(tsb_ctx* ctx, const tsb_model_config* cfg, tsb_model** out);
 TSB_API void tsb_model_destroy(tsb_model* m);
-/* Upload one matrix as verbatim block rows (rows x cols, row-major rows of blocks).  q, k and v of a
- * layer must share a format, as must gate and up: they are laid out back to back and run as one matmul.
+/* Upload one matrix as verbatim block rows (rows x cols, row-major rows of blocks).  q and k of a layer
+ * must share a format, as must gate and up: they are laid out back to back and run as one matmul.  v joins
+ * q and k when its format is theirs; otherwise (mixed recipes keep v in Q6_K) it runs as a launch of its own.
  * layer is ignored for TSB_W_EMBED / TSB_W_LM_HEAD.  A model may point its embedding and head at another
  * model's tensors with tsb_model_share (a drafter sharing the trunk's tables). */
 TSB_API int32_t tsb_model_set_matrix(tsb_model* m, int32_t layer, int32_t which, int32_t qtype,

@@ -321,3 +321,37 @@ def test_adaptive_depth_changes_the_round_shape_not_the_output(rig, oracle):
     assert np.array_equal(seq, e_fixed) and np.array_equal(seq, e_adapt)
     assert r_adapt.new_tokens == 48 and r_adapt.rounds >= r_fixed.rounds
     sess.close()
+
+
+@pytest.mark.parametrize("order", [None, "v_first"])
+def test_mixed_recipe_layers_v_and_down_in_q6k_match_the_oracle(oracle, order):
+    """The common mixed recipe: q, k, o, gate, up in Q4_K; v, down and the head in Q6_K.  v sits in its own matrix
+    and runs as a second launch; the logits must match the oracle's forward pass over the same blocks, whichever of
+    q, k, v is uploaded first."""
+    import turbospark_b200 as tsb
+    from turbospark_b200.model import W_Q, W_V, W_DOWN, W_EMBED, W_LM_HEAD
+    ctx = tsb.Ctx(0)
+    cfg = tsb.config_tiny(max_context=256)
+    recipe = {W_V: tsb.Q6_K, W_DOWN: tsb.Q6_K, W_LM_HEAD: tsb.Q6_K}
+    mats, norms = tsb.random_weights(cfg, 5, oracle, real_ffn=1408, qtype_of=recipe)
+    target = tsb.Model(ctx, cfg)
+    tsb.load_weights(target, mats, norms, order=[W_V] if order else None)
+    assert target.weight_bytes == sum(b.size for (l, w), (b, _, _, _) in mats.items() if w != W_EMBED)
+    ocfg = oracle.ModelCfg(cfg.n_layers, cfg.d_model, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.vocab,
+                           cfg.max_context, cfg.rms_eps, cfg.rope_theta)
+    ot = oracle.Model(ocfg, threads=8)
+    tsb.load_weights(ot, mats, norms)
+    sess = tsb.Session(ctx, target, None, 1, 8)
+    ost = oracle.State(ot)
+    rng = np.random.default_rng(9)
+    prompt = rng.integers(0, cfg.vocab, size=10).astype(np.int32)
+    for i, t in enumerate(prompt):
+        _close(oracle, sess.produce(int(t), i), ost.forward([int(t)], i)[0], rel=4e-3, abs_=4e-3)
+    feed = rng.integers(0, cfg.vocab, size=6).astype(np.int32)
+    point = sess.checkpoint()
+    _close(oracle, sess.verify(feed, point), ost.forward(feed, point), rel=4e-3, abs_=4e-3)
+    # q in a format other than k is still refused
+    with pytest.raises(tsb.TsbError):
+        qb = oracle.quantize(tsb.Q6_K, np.zeros((cfg.n_q_heads * cfg.head_dim, cfg.d_model), np.float32))
+        target.set_matrix(0, W_Q, tsb.Q6_K, qb, cfg.n_q_heads * cfg.head_dim, cfg.d_model)
+    sess.close(), target.close(), ctx.close()

@@ -389,7 +389,7 @@ __device__ __forceinline__ int num_groups(int n_tiles, const EpiArgs& e) {
     if (EPI == EPI_SILU || EPI == EPI_MOE_ACT) return n_tiles / 2;
     if (EPI == EPI_ROPE_STORE) {
         const int tph = e.head_dim / 16;  // tiles per head
-        return (e.n_q_heads + e.n_kv_heads) * (tph / 2) + e.n_kv_heads * tph;
+        return (e.n_q_heads + e.n_kv_heads) * (tph / 2) + (e.n_v_heads < 0 ? e.n_kv_heads : e.n_v_heads) * tph;
     }
     return n_tiles;
 }
@@ -755,7 +755,7 @@ cudaError_t launch_one(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t 
     if (EPI == EPI_SILU || EPI == EPI_MOE_ACT) groups = n_tiles / 2;
     if (EPI == EPI_ROPE_STORE) {
         const int tph = args.head_dim / 16;
-        groups = (args.n_q_heads + args.n_kv_heads) * (tph / 2) + args.n_kv_heads * tph;
+        groups = (args.n_q_heads + args.n_kv_heads) * (tph / 2) + (args.n_v_heads < 0 ? args.n_kv_heads : args.n_v_heads) * tph;
     }
     const int per_sm = NT <= 2 ? 2 : 1;
     dim3 grid((unsigned)min(groups, ctx->sm_count * per_sm));

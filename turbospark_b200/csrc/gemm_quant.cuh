@@ -77,6 +77,7 @@ struct EpiArgs {
     const float* cs = nullptr;  // [tokens][head_dim]: cos[0..hd/2) then sin[0..hd/2) of the row's position
     __half* q_out = nullptr;    // [tokens, n_q_heads * head_dim]
     int n_q_heads = 0, n_kv_heads = 0, head_dim = 0;
+    int n_v_heads = -1;  // v heads among the rows; negative: as many as k heads.  q|k only: 0.  v only: n_q = n_kv = 0.
 };
 
 // x [tokens, cols] f16 natural order -> ActOperand buffers.

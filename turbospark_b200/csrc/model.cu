@@ -84,6 +84,8 @@ static void mat_free(tsb_ctx* ctx, Mat& m) {
     m = Mat();
 }
 
+static int64_t rows_of_v(const tsb_model_config& c) { return (int64_t)c.n_kv_heads * c.head_dim; }
+
 static Mat* fused_slot(tsb_model* m, int layer, int which, int64_t* row_off, int64_t* total_rows, int64_t* want_rows,
                        int64_t* want_cols) {
     const tsb_model_config& c = m->cfg;
@@ -137,7 +139,7 @@ void tsb_model_destroy(tsb_model* m) {
     DeviceGuard g(m->ctx);
     cudaDeviceSynchronize();
     for (auto& l : m->layers) {
-        mat_free(m->ctx, l.wqkv), mat_free(m->ctx, l.wo), mat_free(m->ctx, l.wgu), mat_free(m->ctx, l.wdown);
+        mat_free(m->ctx, l.wqkv), mat_free(m->ctx, l.wv), mat_free(m->ctx, l.wo), mat_free(m->ctx, l.wgu), mat_free(m->ctx, l.wdown);
         if (l.norms_owned) {
             if (l.attn_norm) tsb_free(m->ctx, l.attn_norm);
             if (l.ffn_norm) tsb_free(m->ctx, l.ffn_norm);
@@ -160,13 +162,42 @@ int32_t tsb_model_set_matrix(tsb_model* m, int32_t layer, int32_t which, int32_t
     TSB_REQUIRE(ctx, rows == wr && cols == wc, "tensor %d of layer %d must be %lld x %lld, got %lld x %lld", which, layer,
                 (long long)wr, (long long)wc, (long long)rows, (long long)cols);
     DeviceGuard g(ctx);
+    const int64_t rb = tsb_row_bytes(qtype, cols);
+    if (which == TSB_W_Q || which == TSB_W_K || which == TSB_W_V) {
+        // Files quantized with mixed recipes keep v in a wider format than q and k: v then lives in its own matrix
+        // and the pass runs the q|k rows and the v rows as two launches.
+        LayerW& l = m->layers[layer];
+        const int64_t qk_rows = total - rows_of_v(m->cfg);
+        if (which == TSB_W_V && (l.wv.data || (l.wqkv.data && l.wqkv.qtype != qtype))) {
+            if (l.wv.data && l.wv.qtype != qtype) mat_free(ctx, l.wv);
+            if (!l.wv.data) {
+                int32_t rc = mat_alloc(ctx, l.wv, qtype, rows, cols);
+                if (rc) return rc;
+            }
+            if (l.wqkv.data) l.wqkv.rows = qk_rows;
+            TSB_CUDA(ctx, cudaMemcpy(l.wv.data, host_blocks, (size_t)(rows * rb), cudaMemcpyHostToDevice));
+            l.qkv_set |= 4;
+            return TSB_OK;
+        }
+        if (which != TSB_W_V && l.wqkv.data && l.wqkv.qtype != qtype) {
+            if (l.qkv_set != 4 || l.wv.data || !l.wqkv.owned)
+                return tsb_fail(ctx, TSB_ERR_UNSUPPORTED, "q and k of a layer must share one block format");
+            // only v has arrived so far: it moves to its own matrix and q|k start over in the new format
+            const int64_t vb = tsb_row_bytes(l.wqkv.qtype, cols);
+            int32_t rc = mat_alloc(ctx, l.wv, l.wqkv.qtype, rows_of_v(m->cfg), cols);
+            if (rc) return rc;
+            TSB_CUDA(ctx, cudaMemcpy(l.wv.data, l.wqkv.data + qk_rows * vb, (size_t)(rows_of_v(m->cfg) * vb), cudaMemcpyDeviceToDevice));
+            mat_free(ctx, l.wqkv);
+            if ((rc = mat_alloc(ctx, l.wqkv, qtype, qk_rows, cols))) return rc;
+        }
+        l.qkv_set |= which == TSB_W_Q ? 1 : (which == TSB_W_K ? 2 : 4);
+    }
     if (!slot->data) {
         int32_t rc = mat_alloc(ctx, *slot, qtype, total, cols);
         if (rc) return rc;
     } else if (slot->qtype != qtype) {
-        return tsb_fail(ctx, TSB_ERR_UNSUPPORTED, "q/k/v (and gate/up) of a layer must share one block format");
+        return tsb_fail(ctx, TSB_ERR_UNSUPPORTED, "gate and up of a layer must share one block format");
     }
-    const int64_t rb = tsb_row_bytes(qtype, cols);
     TSB_CUDA(ctx, cudaMemcpy(slot->data + off * rb, host_blocks, (size_t)(rows * rb), cudaMemcpyHostToDevice));
     return TSB_OK;
 }
@@ -214,7 +245,8 @@ int32_t tsb_model_share(tsb_model* dst, int32_t dst_layer, const tsb_model* src,
                 "layer shapes differ");
     LayerW& d = dst->layers[dst_layer];
     const LayerW& s = src->layers[src_layer];
-    borrow(d.wqkv, s.wqkv), borrow(d.wo, s.wo), borrow(d.wgu, s.wgu), borrow(d.wdown, s.wdown);
+    borrow(d.wqkv, s.wqkv), borrow(d.wv, s.wv), borrow(d.wo, s.wo), borrow(d.wgu, s.wgu), borrow(d.wdown, s.wdown);
+    d.qkv_set = s.qkv_set;
     d.attn_norm = s.attn_norm, d.ffn_norm = s.ffn_norm, d.norms_owned = false;
     return TSB_OK;
 }
@@ -267,7 +299,7 @@ int32_t tsb_model_fill_synthetic(tsb_model* m, int32_t qtype, int32_t lm_head_qt
 int64_t tsb_model_weight_bytes(const tsb_model* m) {
     if (!m) return 0;
     int64_t t = mat_bytes(m->lm_head);
-    for (auto& l : m->layers) t += mat_bytes(l.wqkv) + mat_bytes(l.wo) + mat_bytes(l.wgu) + mat_bytes(l.wdown);
+    for (auto& l : m->layers) t += mat_bytes(l.wqkv) + mat_bytes(l.wv) + mat_bytes(l.wo) + mat_bytes(l.wgu) + mat_bytes(l.wdown);
     return t;
 }
 
@@ -281,6 +313,7 @@ static int32_t model_complete(const tsb_model* m) {
         const LayerW& l = m->layers[i];
         TSB_REQUIRE(ctx, l.wqkv.data && l.wo.data && l.wgu.data && l.wdown.data && l.attn_norm && l.ffn_norm,
                     "layer %zu is missing a tensor", i);
+        TSB_REQUIRE(ctx, l.qkv_set == 0 || l.qkv_set == 7, "layer %zu is missing one of q, k, v", i);
     }
     TSB_REQUIRE(ctx, m->embed.data && m->lm_head.data && m->out_norm, "embedding, head or final norm missing");
     return TSB_OK;
@@ -327,7 +360,7 @@ static int32_t runtime_init(tsb_session* s, ModelRt& rt, const tsb_model* model,
     // the many-row path: only when the session can hold that many rows and every matrix suits the kernel
     bool wide = R >= WIDE_MIN_ROWS && gemm_wide_supported(model->lm_head.qtype, model->lm_head.rows, model->lm_head.cols, R);
     for (const LayerW& l : model->layers)
-        wide = wide && gemm_wide_supported(l.wqkv.qtype, l.wqkv.rows, l.wqkv.cols, R) && gemm_wide_supported(l.wo.qtype, l.wo.rows, l.wo.cols, R) &&
+        wide = wide && !l.wv.data && gemm_wide_supported(l.wqkv.qtype, l.wqkv.rows, l.wqkv.cols, R) && gemm_wide_supported(l.wo.qtype, l.wo.rows, l.wo.cols, R) &&
                gemm_wide_supported(l.wgu.qtype, l.wgu.rows, l.wgu.cols, R) && gemm_wide_supported(l.wdown.qtype, l.wdown.rows, l.wdown.cols, R);
     {
         const char* env = getenv("TSB_WIDE_FORWARD");
@@ -437,7 +470,12 @@ static cudaError_t forward_device(tsb_session* s, ModelRt& rt, const int32_t* to
             a.ss_in = ss_slot(2 * L), a.ss_parts = L == 0 ? 1 : parts, a.d_in = c.d_model, a.eps = c.rms_eps;
             a.kv = rt.kv->view, a.layer = L, a.row_desc = rows_dev, a.cs = rt.cs, a.q_out = rt.q;
             a.n_q_heads = c.n_q_heads, a.n_kv_heads = c.n_kv_heads, a.head_dim = c.head_dim;
+            if (l.wv.data) a.n_v_heads = 0;
             FW(launch_gemm_fused(ctx, st, l.wqkv.qtype, l.wqkv.data, l.wqkv.rows, l.wqkv.cols, in_d, rows, EPI_ROPE_STORE, a));
+            if (l.wv.data) {  // v in its own block format: the v rows as a second launch, every tile a v tile
+                a.n_q_heads = 0, a.n_kv_heads = 0, a.n_v_heads = c.n_kv_heads;
+                FW(launch_gemm_fused(ctx, st, l.wv.qtype, l.wv.data, l.wv.rows, l.wv.cols, in_d, rows, EPI_ROPE_STORE, a));
+            }
         }
         FW(launch_attn_decode_rows(ctx, st, rt.kv, L, rt.q, (int64_t)c.n_q_heads * c.head_dim, nullptr, out_o, rows_dev, rows,
                                    rows_per_seq, c.n_q_heads, scale, max_len, rt.attn_scratch, s->n_streams * s->max_rows));
@@ -1173,12 +1211,13 @@ int32_t tsb_session_time_matmuls(tsb_session* s, int32_t rows, int32_t iters, fl
         for (int L = 0; L < c.n_layers; L++) {
             const LayerW& l = m->layers[L];
             TSB_CUDA(ctx, launch_gemm_quant(ctx, st, l.wqkv.qtype, l.wqkv.data, l.wqkv.rows, l.wqkv.cols, in_d, sink, qkv_dim, rows, false));
+            if (l.wv.data) TSB_CUDA(ctx, launch_gemm_quant(ctx, st, l.wv.qtype, l.wv.data, l.wv.rows, l.wv.cols, in_d, sink, qkv_dim, rows, false));
             TSB_CUDA(ctx, launch_gemm_quant(ctx, st, l.wo.qtype, l.wo.data, l.wo.rows, l.wo.cols, in_o, sink, c.d_model, rows, false));
             TSB_CUDA(ctx, launch_gemm_quant(ctx, st, l.wgu.qtype, l.wgu.data, l.wgu.rows, l.wgu.cols, in_d, sink, 2 * (int64_t)c.ffn, rows, false));
             TSB_CUDA(ctx, launch_gemm_quant(ctx, st, l.wdown.qtype, l.wdown.data, l.wdown.rows, l.wdown.cols, in_f, sink, c.d_model, rows, false));
             if (it == 0) {
-                bytes += mat_bytes(l.wqkv) + mat_bytes(l.wo) + mat_bytes(l.wgu) + mat_bytes(l.wdown);
-                launches += 4 * ((rows + 63) / 64);
+                bytes += mat_bytes(l.wqkv) + mat_bytes(l.wv) + mat_bytes(l.wo) + mat_bytes(l.wgu) + mat_bytes(l.wdown);
+                launches += (l.wv.data ? 5 : 4) * ((rows + 63) / 64);
             }
         }
     }

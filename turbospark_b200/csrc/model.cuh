@@ -14,6 +14,8 @@ struct Mat {
 
 struct LayerW {
     Mat wqkv, wo, wgu, wdown;  // q|k|v rows back to back; gate|up rows back to back
+    Mat wv;                    // v rows on their own when their block format differs from q and k (wqkv is then q|k)
+    uint8_t qkv_set = 0;       // which of q (1), k (2), v (4) have been uploaded
     uint16_t* attn_norm = nullptr;
     uint16_t* ffn_norm = nullptr;
     bool norms_owned = false;

@@ -228,46 +228,52 @@ class Session:
             self.h = None
 
 
-def random_weights(cfg, seed, oracle, qtype=capi.Q4_K, std=0.02, real_ffn=None):
+def random_weights(cfg, seed, oracle, qtype=capi.Q4_K, std=0.02, real_ffn=None, qtype_of=None):
     """Seeded N(0, std) weights quantized by the oracle's encoder (test / small-model set-up).  Returns a dict
-    (layer, which) -> (blocks uint8 [rows, row_bytes], rows, cols) and norms (layer, which) -> bf16 bits.
-    real_ffn < cfg.ffn zero-pads the FFN (rows of gate/up and columns of down beyond real_ffn are zero)."""
+    (layer, which) -> (blocks uint8 [rows, row_bytes], rows, cols, qtype) and norms (layer, which) -> bf16 bits.
+    real_ffn < cfg.ffn zero-pads the FFN (rows of gate/up and columns of down beyond real_ffn are zero).
+    qtype_of maps a tensor kind (W_V, W_DOWN, ...) to a block format other than `qtype`, as mixed recipes do."""
     rng = np.random.default_rng(seed)
     qd, kd, d, f = cfg.n_q_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim, cfg.d_model, cfg.ffn
     rf = real_ffn or f
     mats, norms = {}, {}
 
-    def mk(rows, cols, zero_rows_from=None, zero_cols_from=None):
+    def mk(rows, cols, zero_rows_from=None, zero_cols_from=None, which=None):
+        qt = (qtype_of or {}).get(which, qtype)
         w = (rng.standard_normal((rows, cols)) * std).astype(np.float32)
         if zero_rows_from is not None:
             w[zero_rows_from:] = 0
         if zero_cols_from is not None:
             w[:, zero_cols_from:] = 0
-        return oracle.quantize(qtype, w), rows, cols
+        return oracle.quantize(qt, w), rows, cols, qt
 
-    mats[(-1, W_EMBED)] = mk(cfg.vocab, d)
+    mats[(-1, W_EMBED)] = mk(cfg.vocab, d, which=W_EMBED)
     for l in range(cfg.n_layers):
-        mats[(l, W_Q)] = mk(qd, d)
-        mats[(l, W_K)] = mk(kd, d)
-        mats[(l, W_V)] = mk(kd, d)
-        mats[(l, W_O)] = mk(d, qd)
-        mats[(l, W_GATE)] = mk(f, d, zero_rows_from=rf)
-        mats[(l, W_UP)] = mk(f, d, zero_rows_from=rf)
-        mats[(l, W_DOWN)] = mk(d, f, zero_cols_from=rf)
+        mats[(l, W_Q)] = mk(qd, d, which=W_Q)
+        mats[(l, W_K)] = mk(kd, d, which=W_K)
+        mats[(l, W_V)] = mk(kd, d, which=W_V)
+        mats[(l, W_O)] = mk(d, qd, which=W_O)
+        mats[(l, W_GATE)] = mk(f, d, zero_rows_from=rf, which=W_GATE)
+        mats[(l, W_UP)] = mk(f, d, zero_rows_from=rf, which=W_UP)
+        mats[(l, W_DOWN)] = mk(d, f, zero_cols_from=rf, which=W_DOWN)
         for which in (N_ATTN, N_FFN):
             norms[(l, which)] = np.array([oracle.lib().tso_f32_to_bf16(float(v)) for v in 1.0 + 0.05 * rng.standard_normal(d)], dtype=np.uint16)
-    mats[(-1, W_LM_HEAD)] = mk(cfg.vocab, d)
+    mats[(-1, W_LM_HEAD)] = mk(cfg.vocab, d, which=W_LM_HEAD)
     norms[(-1, N_OUT)] = np.array([oracle.lib().tso_f32_to_bf16(float(v)) for v in 1.0 + 0.05 * rng.standard_normal(d)], dtype=np.uint16)
     return mats, norms
 
 
-def load_weights(model, mats, norms, qtype=capi.Q4_K, layers=None):
-    """Push a random_weights() set into a tsb Model or an oracle Model (same builder interface)."""
+def load_weights(model, mats, norms, qtype=None, layers=None, order=None):
+    """Push a random_weights() set into a tsb Model or an oracle Model (same builder interface).  Each matrix goes
+    up in the format it was quantized in (`qtype` overrides it); `order` lists tensor kinds to upload first."""
     n_layers = model.cfg.n_layers if layers is None else layers
-    for (l, which), (blocks, rows, cols) in mats.items():
+    first = list(order or [])
+    keys = sorted(mats, key=lambda k: first.index(k[1]) if k[1] in first else len(first))  # stable: the rest keep their order
+    for (l, which) in keys:
+        blocks, rows, cols, qt = mats[(l, which)]
         if l >= n_layers:
             continue
-        model.set_matrix(max(l, 0), which, qtype, blocks, rows, cols)
+        model.set_matrix(max(l, 0), which, qt if qtype is None else qtype, blocks, rows, cols)
     for (l, which), bits in norms.items():
         if l >= n_layers:
             continue
