@@ -61,8 +61,11 @@ typedef enum tsb_status {
 typedef enum tsb_qtype {
     TSB_Q4_K = 0, /* (7)  256 elements / 144 bytes: crates/compute/src/quant_gguf/q4_k.rs */
     TSB_Q6_K = 1, /* (8)  256 elements / 210 bytes: crates/compute/src/quant_gguf/q6_k.rs */
-    TSB_MXFP4 = 2 /* (14) 32 elements / 17 bytes:   crates/compute/src/quant_gguf_mxfp4.rs */
+    TSB_MXFP4 = 2, /* (14) 32 elements / 17 bytes:  crates/compute/src/quant_gguf_mxfp4.rs */
+    TSB_Q5_K = 3, /* 256 elements / 176 bytes: crates/compute/src/quant_gguf/q5_k.rs (cols a multiple of 256) */
+    TSB_Q8_0 = 4  /* 32 elements / 34 bytes:   crates/compute/src/quant_gguf/q8_0.rs (cols a multiple of 256 here) */
 } tsb_qtype;
+#define TSB_QTYPE_LAST TSB_Q8_0
 
 /* ------------------------------------------------------------------ context */
 

@@ -12,7 +12,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "libtsb_oracle.so")
 
-Q4K, Q6K, MXFP4 = 0, 1, 2
+Q4K, Q6K, MXFP4, Q5K, Q8_0 = 0, 1, 2, 3, 4
 W_Q, W_K, W_V, W_O, W_GATE, W_UP, W_DOWN, W_EMBED, W_LM_HEAD = range(9)
 N_ATTN, N_FFN, N_OUT = range(3)
 
@@ -123,8 +123,10 @@ def row_bytes(kind, cols):
     return int(lib().tso_row_bytes(kind, cols))
 
 
-_QUANT = {Q4K: "tso_quantize_q4k", Q6K: "tso_quantize_q6k", MXFP4: "tso_quantize_mxfp4"}
-_DEQUANT = {Q4K: "tso_dequantize_q4k", Q6K: "tso_dequantize_q6k", MXFP4: "tso_dequantize_mxfp4"}
+_QUANT = {Q4K: "tso_quantize_q4k", Q6K: "tso_quantize_q6k", MXFP4: "tso_quantize_mxfp4", Q5K: "tso_quantize_q5k",
+          Q8_0: "tso_quantize_q8_0"}
+_DEQUANT = {Q4K: "tso_dequantize_q4k", Q6K: "tso_dequantize_q6k", MXFP4: "tso_dequantize_mxfp4", Q5K: "tso_dequantize_q5k",
+            Q8_0: "tso_dequantize_q8_0"}
 
 
 def quantize(kind, w):
@@ -133,7 +135,7 @@ def quantize(kind, w):
     rows, cols = w.shape
     rb = row_bytes(kind, cols)
     out = np.zeros((rows, rb), dtype=np.uint8)
-    assert cols % (32 if kind == MXFP4 else 256) == 0, "row is not a whole number of blocks"
+    assert cols % (32 if kind in (MXFP4, Q8_0) else 256) == 0, "row is not a whole number of blocks"
     # rows are contiguous block runs, so the whole matrix quantizes as one long row
     getattr(lib(), _QUANT[kind])(_p(w), C.c_int64(rows * cols), _p(out))
     return out

@@ -409,16 +409,142 @@ TSO_API void tso_dequantize_mxfp4(const uint8_t* blocks, int64_t n, float* out) 
 TSO_API void tso_quantize_mxfp4(const float* row, int64_t n, uint8_t* out) { quantize_mxfp4(row, n, out); }
 
 // ---------------------------------------------------------------------------
+// Q5_K  (crates/compute/src/quant_gguf/q5_k.rs) and Q8_0 (crates/compute/src/quant_gguf/q8_0.rs)
+// ---------------------------------------------------------------------------
+
+static const int Q5K_ELEMS = 256, Q5K_BYTES = 176, Q5K_QH_AT = 16, Q5K_QL_AT = 48;
+static const int Q80_ELEMS = 32, Q80_BYTES = 34;
+
+// q5_k.rs:43-100 — Q4_K's scales and mins; the fifth bit of element (group g, half h, byte l) is bit 2g+h of qh[l].
+static void dequantize_q5k(const uint8_t* blocks, int64_t n, float* out) {
+    for (int64_t b = 0; b < n / Q5K_ELEMS; b++) {
+        const uint8_t* blk = blocks + b * Q5K_BYTES;
+        float d = f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+        float dmin = f16_to_f32((uint16_t)(blk[2] | (blk[3] << 8)));
+        const uint8_t* packed = blk + 4;
+        const uint8_t* qh = blk + Q5K_QH_AT;
+        const uint8_t* ql = blk + Q5K_QL_AT;
+        for (int g = 0; g < 4; g++) {
+            uint8_t sc_lo, m_lo, sc_hi, m_hi;
+            q4k_scale_min(2 * g, packed, &sc_lo, &m_lo);
+            q4k_scale_min(2 * g + 1, packed, &sc_hi, &m_hi);
+            float d_lo = d * (float)sc_lo, min_lo = dmin * (float)m_lo;
+            float d_hi = d * (float)sc_hi, min_hi = dmin * (float)m_hi;
+            int64_t at = b * Q5K_ELEMS + g * 64;
+            for (int l = 0; l < 32; l++) {
+                uint8_t byte = ql[g * 32 + l], hb = qh[l];
+                int q_lo = (byte & 0xF) + (((hb >> (2 * g)) & 1) << 4);
+                int q_hi = (byte >> 4) + (((hb >> (2 * g + 1)) & 1) << 4);
+                out[at + l] = d_lo * (float)q_lo - min_lo;
+                out[at + 32 + l] = d_hi * (float)q_hi - min_hi;
+            }
+        }
+    }
+}
+
+// The reference carries no Q5_K encoder (its bytes always arrive quantized).  This one exists so tests have
+// arbitrary weights in the format: the Q4_K min/max fit above with 31 steps per sub-block instead of 15.
+static void quantize_q5k(const float* row, int64_t n, uint8_t* out) {
+    for (int64_t b = 0; b < n / Q5K_ELEMS; b++) {
+        const float* block = row + b * Q5K_ELEMS;
+        float scales[8], mins[8];
+        for (int j = 0; j < 8; j++) {
+            const float* sub = block + j * 32;
+            float lo = 0.f;
+            for (int i = 0; i < 32; i++) lo = std::fmin(lo, sub[i]);
+            float hi = lo;
+            for (int i = 0; i < 32; i++) hi = std::fmax(hi, sub[i]);
+            scales[j] = (hi - lo) / 31.0f;
+            mins[j] = -lo;
+        }
+        float max_scale = 0.f, max_min = 0.f;
+        for (int j = 0; j < 8; j++) {
+            max_scale = std::fmax(max_scale, scales[j]);
+            max_min = std::fmax(max_min, mins[j]);
+        }
+        float inv_scale = max_scale > 0.f ? 63.0f / max_scale : 0.f;
+        float inv_min = max_min > 0.f ? 63.0f / max_min : 0.f;
+        uint8_t packed[12] = {0};
+        for (int j = 0; j < 8; j++) {
+            uint8_t ls = (uint8_t)clampf(std::round(scales[j] * inv_scale), 0.f, 63.f);
+            uint8_t lm = (uint8_t)clampf(std::round(mins[j] * inv_min), 0.f, 63.f);
+            if (j < 4) {
+                packed[j] |= ls;
+                packed[j + 4] |= lm;
+            } else {
+                packed[j + 4] = (uint8_t)((ls & 0xF) | ((lm & 0xF) << 4));
+                packed[j - 4] |= (uint8_t)((ls >> 4) << 6);
+                packed[j] |= (uint8_t)((lm >> 4) << 6);
+            }
+        }
+        uint16_t d = f32_to_f16(max_scale / 63.0f);
+        uint16_t dmin = f32_to_f16(max_min / 63.0f);
+        uint8_t* o = out + b * Q5K_BYTES;
+        std::memset(o, 0, Q5K_BYTES);
+        o[0] = (uint8_t)(d & 0xFF), o[1] = (uint8_t)(d >> 8), o[2] = (uint8_t)(dmin & 0xFF), o[3] = (uint8_t)(dmin >> 8);
+        std::memcpy(o + 4, packed, 12);
+        for (int j = 0; j < 8; j++) {
+            uint8_t sc, m;
+            q4k_scale_min(j, packed, &sc, &m);
+            float step = f16_to_f32(d) * (float)sc;
+            if (step == 0.f) continue;
+            float bias = f16_to_f32(dmin) * (float)m;
+            const int g = j >> 1, h = j & 1;
+            for (int l = 0; l < 32; l++) {
+                int q = (int)clampf(std::round((block[j * 32 + l] + bias) / step), 0.f, 31.f);
+                o[Q5K_QL_AT + g * 32 + l] |= (uint8_t)((q & 0xF) << (4 * h));
+                o[Q5K_QH_AT + l] |= (uint8_t)((q >> 4) << (2 * g + h));
+            }
+        }
+    }
+}
+
+// q8_0.rs:20-47 — f16 scale, 32 SIGNED weights; out = q * d.
+static void dequantize_q8_0(const uint8_t* blocks, int64_t n, float* out) {
+    for (int64_t b = 0; b < n / Q80_ELEMS; b++) {
+        const uint8_t* blk = blocks + b * Q80_BYTES;
+        float d = f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+        for (int k = 0; k < Q80_ELEMS; k++) out[b * Q80_ELEMS + k] = (float)(int8_t)blk[2 + k] * d;
+    }
+}
+
+// q8_0.rs:56-79 — the scale is rounded through f16 before the weights are quantized against it.
+static void quantize_q8_0(const float* row, int64_t n, uint8_t* out) {
+    for (int64_t b = 0; b < n / Q80_ELEMS; b++) {
+        const float* block = row + b * Q80_ELEMS;
+        float amax = 0.f;
+        for (int k = 0; k < Q80_ELEMS; k++) amax = std::fmax(amax, std::fabs(block[k]));
+        uint16_t d = f32_to_f16(amax / 127.0f);
+        float df = f16_to_f32(d);
+        float inv = df == 0.f ? 0.f : 1.0f / df;
+        uint8_t* o = out + b * Q80_BYTES;
+        o[0] = (uint8_t)(d & 0xFF), o[1] = (uint8_t)(d >> 8);
+        for (int k = 0; k < Q80_ELEMS; k++) {
+            int q = (int)std::round(block[k] * inv);  // round half away from zero, as f32::round
+            q = q < -127 ? -127 : (q > 127 ? 127 : q);
+            o[2 + k] = (uint8_t)(int8_t)q;
+        }
+    }
+}
+
+TSO_API void tso_dequantize_q5k(const uint8_t* blocks, int64_t n, float* out) { dequantize_q5k(blocks, n, out); }
+TSO_API void tso_quantize_q5k(const float* row, int64_t n, uint8_t* out) { quantize_q5k(row, n, out); }
+TSO_API void tso_dequantize_q8_0(const uint8_t* blocks, int64_t n, float* out) { dequantize_q8_0(blocks, n, out); }
+TSO_API void tso_quantize_q8_0(const float* row, int64_t n, uint8_t* out) { quantize_q8_0(row, n, out); }
+
+// ---------------------------------------------------------------------------
 // GEMV / small-M GEMM over quantized rows
 // q4_k.rs:207-220, q6_k.rs:183-198, quant_gguf_mxfp4.rs:149-162:
 // y[r] = sum over the dequantized row times x, sequential f32 in index order.
-// kind: 0 = Q4_K, 1 = Q6_K, 2 = MXFP4.
+// kind: 0 = Q4_K, 1 = Q6_K, 2 = MXFP4, 3 = Q5_K, 4 = Q8_0 (q5_k.rs:104-118, q8_0.rs:82-96).
 // ---------------------------------------------------------------------------
 
 static int64_t row_bytes_of(int kind, int64_t cols) {
     switch (kind) {
         case 0: return cols / Q4K_ELEMS * Q4K_BYTES;
         case 1: return cols / Q6K_ELEMS * Q6K_BYTES;
+        case 3: return cols / Q5K_ELEMS * Q5K_BYTES;
+        case 4: return cols / Q80_ELEMS * Q80_BYTES;
         default: return (cols + MX_ELEMS - 1) / MX_ELEMS * MX_BYTES;
     }
 }
@@ -427,6 +553,8 @@ static void dequant_row(int kind, const uint8_t* row, int64_t cols, float* out) 
     switch (kind) {
         case 0: dequantize_q4k(row, cols, out); break;
         case 1: dequantize_q6k(row, cols, out); break;
+        case 3: dequantize_q5k(row, cols, out); break;
+        case 4: dequantize_q8_0(row, cols, out); break;
         default: dequantize_mxfp4(row, cols, out); break;
     }
 }

@@ -60,6 +60,8 @@ def test_struct_layouts_match_the_header():
     assert C.sizeof(tsb.RunConfig) == 64 + 4 * 4 + 32 + 4 + 2 * 4 + 32 + 4
     assert tsb.lib().tsb_row_bytes(0, 4096) == 2304 and tsb.lib().tsb_row_bytes(1, 4096) == 3360
     assert tsb.lib().tsb_row_bytes(2, 4096) == 2176
+    assert tsb.lib().tsb_row_bytes(3, 4096) == 16 * 176 and tsb.lib().tsb_row_bytes(4, 4096) == 128 * 34
+    assert tsb.lib().tsb_row_bytes(5, 4096) == -1
 
 
 def test_uniform_sources_match_the_oracle(oracle):

@@ -30,7 +30,7 @@ def _check(got, want):
                                                                  want.flat[err.argmax()])
 
 
-@pytest.mark.parametrize("kind", [0, 1, 2])
+@pytest.mark.parametrize("kind", [0, 1, 2, 3, 4])
 @pytest.mark.parametrize("rows,cols,tokens", [(64, 512, 1), (48, 2048, 6), (40, 4096, 3), (16, 14336, 6), (100, 1536, 8)])
 def test_gemm_matches_oracle(ctx, oracle, kind, rows, cols, tokens):
     q = _weights(oracle, kind, rows, cols, 3)
@@ -77,7 +77,7 @@ def test_many_token_rows_take_the_tensor_memory_path_and_match_the_oracle(ctx, o
     assert np.array_equal(y2.download(np.float32, 24 * rows).reshape(24, rows), got[:24])
 
 
-@pytest.mark.parametrize("kind", [0, 1, 2])
+@pytest.mark.parametrize("kind", [0, 1, 2, 3, 4])
 def test_a_tokens_result_does_not_depend_on_the_batch(ctx, oracle, kind):
     # the verify batch must reproduce the decode step bit for bit, at every width
     rows, cols = 96, 4096
@@ -133,7 +133,7 @@ def test_gemm_refuses_bad_shapes(ctx, oracle):
         ctx.gemm_quant(0, w, 16, 256, xd, yd, 0)
 
 
-@pytest.mark.parametrize("kind", [0, 1, 2])
+@pytest.mark.parametrize("kind", [0, 1, 2, 3, 4])
 def test_dequant_rows_is_bit_exact(ctx, oracle, kind):
     rows, cols = 24, 1024
     q = _weights(oracle, kind, rows, cols, 9)
@@ -146,6 +146,24 @@ def test_dequant_rows_is_bit_exact(ctx, oracle, kind):
     for i, r in enumerate(ids):
         want = oracle.dequantize(kind, q[r], cols)
         assert np.array_equal(got[i], want.view(np.uint32)), (kind, r)
+
+
+def test_q5k_dequant_matches_ggml_golden_on_device(ctx, oracle):
+    import json, os
+    g = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "q5k_ggml.json")))
+    w = ctx.upload_weights(np.array(g["bytes"], dtype=np.uint8))
+    out = ctx.alloc(512 * 4)
+    ctx.dequant_rows(3, w, 512, None, 1, out)
+    assert np.array_equal(out.download(np.uint32, 512), np.array(g["floats"], dtype=np.float32).view(np.uint32))
+    # and the matmul over the same two superblocks against the decoded floats
+    rng = np.random.default_rng(2)
+    x16 = oracle.f32_to_f16_bits(rng.standard_normal((3, 512)).astype(np.float32))
+    want = oracle.f16_bits_to_f32(x16) @ np.array(g["floats"], dtype=np.float32)
+    rows16 = ctx.upload_weights(np.tile(np.array(g["bytes"], dtype=np.uint8), 16))
+    yd = ctx.alloc(3 * 16 * 4)
+    ctx.gemm_quant(3, rows16, 16, 512, ctx.to_device(x16), yd, 3, y_f32=True)
+    got = yd.download(np.float32, 48).reshape(3, 16)
+    _check(got, np.repeat(want[:, None], 16, axis=1))
 
 
 def test_mxfp4_dequant_matches_ggml_golden_on_device(ctx, oracle):

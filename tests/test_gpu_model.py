@@ -323,17 +323,21 @@ def test_adaptive_depth_changes_the_round_shape_not_the_output(rig, oracle):
     sess.close()
 
 
-@pytest.mark.parametrize("order", [None, "v_first"])
-def test_mixed_recipe_layers_v_and_down_in_q6k_match_the_oracle(oracle, order):
-    """The common mixed recipe: q, k, o, gate, up in Q4_K; v, down and the head in Q6_K.  v sits in its own matrix
-    and runs as a second launch; the logits must match the oracle's forward pass over the same blocks, whichever of
-    q, k, v is uploaded first."""
+@pytest.mark.parametrize("order,recipe_name", [(None, "q4_k_m"), ("v_first", "q4_k_m"), (None, "q5_k_m")])
+def test_mixed_recipe_layers_match_the_oracle(oracle, order, recipe_name):
+    """Mixed recipes.  q4_k_m: q, k, o, gate, up in Q4_K; v, down and the head in Q6_K.  q5_k_m: Q5_K in place of
+    Q4_K and a Q8_0 embedding table.  v sits in its own matrix and runs as a second launch; the logits must match
+    the oracle's forward pass over the same blocks, whichever of q, k, v is uploaded first."""
     import turbospark_b200 as tsb
     from turbospark_b200.model import W_Q, W_V, W_DOWN, W_EMBED, W_LM_HEAD
     ctx = tsb.Ctx(0)
     cfg = tsb.config_tiny(max_context=256)
     recipe = {W_V: tsb.Q6_K, W_DOWN: tsb.Q6_K, W_LM_HEAD: tsb.Q6_K}
-    mats, norms = tsb.random_weights(cfg, 5, oracle, real_ffn=1408, qtype_of=recipe)
+    base = tsb.Q4_K
+    if recipe_name == "q5_k_m":
+        recipe[W_EMBED] = tsb.Q8_0
+        base = tsb.Q5_K
+    mats, norms = tsb.random_weights(cfg, 5, oracle, qtype=base, real_ffn=1408, qtype_of=recipe)
     target = tsb.Model(ctx, cfg)
     tsb.load_weights(target, mats, norms, order=[W_V] if order else None)
     assert target.weight_bytes == sum(b.size for (l, w), (b, _, _, _) in mats.items() if w != W_EMBED)

@@ -126,3 +126,75 @@ def test_f16_conversion_matches_numpy(oracle):
     back = oracle.f16_bits_to_f32(allbits)
     ref = allbits.view(np.float16).astype(np.float32)
     assert np.array_equal(back.view(np.uint32)[~np.isnan(ref)], ref.view(np.uint32)[~np.isnan(ref)])
+
+
+def ref_weights(n, seed):
+    """The reference tests' own weight generator (crates/compute/tests/quant_gguf.rs:24-33): 32-bit LCG, values in [-1, 1)."""
+    s = (seed * 2654435761 + 1) & 0xFFFFFFFF
+    out = np.empty(n, dtype=np.float32)
+    for i in range(n):
+        s = (s * 1664525 + 1013904223) & 0xFFFFFFFF
+        out[i] = np.float32(np.float32(s >> 8) / np.float32(1 << 23)) - np.float32(1.0)
+    return out
+
+
+def test_q5k_decodes_exactly_what_ggml_decodes(oracle):
+    # crates/compute/tests/quant_gguf.rs:548-555: compared with ==, two superblocks
+    g = json.load(open(os.path.join(GOLD, "q5k_ggml.json")))
+    raw = np.array(g["bytes"], dtype=np.uint8)
+    assert raw.size == 2 * 176 and oracle.row_bytes(oracle.Q5K, 512) == raw.size
+    got = oracle.dequantize(oracle.Q5K, raw, 512)
+    want = np.array(g["floats"], dtype=np.float32)
+    assert np.array_equal(got, want)
+    assert (got < 0).any() and (got > 0).any()                      # :592-597 the min term carries the sign
+    stripped = raw.copy()                                           # :575-590 the fifth bit matters and only lowers
+    for b in range(2):
+        stripped[b * 176 + 16:b * 176 + 48] = 0
+    without = oracle.dequantize(oracle.Q5K, stripped, 512)
+    assert not np.array_equal(got, without) and np.all(got >= without)
+
+
+def test_q5k_own_encoder_round_trips_inside_one_step(oracle):
+    w = (ref_weights(1024, 9) * 0.05).reshape(2, 512)
+    q = oracle.quantize(oracle.Q5K, w)
+    assert q.shape == (2, 2 * 176)
+    back = oracle.dequantize(oracle.Q5K, q, 1024).reshape(2, 512)
+    for sub in range(1024 // 32):
+        blk = w.reshape(-1, 32)[sub]
+        step = (max(blk.max(), 0) - min(blk.min(), 0)) / 31.0
+        assert np.abs(back.reshape(-1, 32)[sub] - blk).max() <= step * 1.1 + 1e-4
+    assert np.array_equal(oracle.dequantize(oracle.Q5K, oracle.quantize(oracle.Q5K, np.zeros((1, 256), np.float32)), 256), np.zeros(256, np.float32))
+
+
+def test_q8_0_block_shape_round_trip_idempotence_signs_and_zeros(oracle):
+    # crates/compute/tests/quant_gguf.rs:36-42, 93-155
+    assert oracle.row_bytes(oracle.Q8_0, 96) == 3 * 34
+    w = ref_weights(256, 11)
+    out = oracle.dequantize(oracle.Q8_0, oracle.quantize(oracle.Q8_0, w.reshape(1, -1)), 256)
+    for b in range(8):
+        blk = w[b * 32:(b + 1) * 32]
+        amax = np.abs(blk).max()
+        assert np.abs(out[b * 32:(b + 1) * 32] - blk).max() <= amax / 127.0 * 0.5 + amax * 1e-3
+    once = oracle.quantize(oracle.Q8_0, ref_weights(512, 3).reshape(1, -1))
+    twice = oracle.quantize(oracle.Q8_0, oracle.dequantize(oracle.Q8_0, once, 512).reshape(1, -1))
+    assert np.array_equal(once, twice)
+    w = np.array([-1.0 if i % 2 == 0 else 0.5 for i in range(32)], dtype=np.float32)
+    out = oracle.dequantize(oracle.Q8_0, oracle.quantize(oracle.Q8_0, w.reshape(1, -1)), 32)
+    assert np.array_equal(out < 0, w < 0) and np.abs(out - w).max() < 0.02
+    z = oracle.dequantize(oracle.Q8_0, oracle.quantize(oracle.Q8_0, np.zeros((1, 64), np.float32)), 64)
+    assert np.all(z == 0.0)
+
+
+def test_q5k_q8_0_gemv_is_dequantize_then_multiply_in_index_order(oracle):
+    # crates/compute/src/quant_gguf/q5_k.rs:104-118, q8_0.rs:82-96
+    for kind, n in ((oracle.Q5K, 512), (oracle.Q8_0, 128)):
+        x = ref_weights(n, 5)
+        w = np.stack([ref_weights(n, 20 + r) for r in range(4)])
+        q = oracle.quantize(kind, w)
+        got = oracle.gemm_quant(kind, q.reshape(-1), 4, n, x.reshape(1, n))[0]
+        for r in range(4):
+            deq = oracle.dequantize(kind, q[r], n)
+            acc = np.float32(0)
+            for c in range(n):
+                acc = np.float32(acc + np.float32(deq[c] * x[c]))
+            assert got[r] == acc

@@ -5,7 +5,7 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-Q4_K, Q6_K, MXFP4 = 0, 1, 2
+Q4_K, Q6_K, MXFP4, Q5_K, Q8_0 = 0, 1, 2, 3, 4
 
 _lib = None
 

@@ -124,6 +124,8 @@ int64_t tsb_row_bytes(int32_t qtype, int64_t cols) {
         case TSB_Q4_K: return cols / 256 * 144;
         case TSB_Q6_K: return cols / 256 * 210;
         case TSB_MXFP4: return (cols + 31) / 32 * 17;
+        case TSB_Q5_K: return cols / 256 * 176;
+        case TSB_Q8_0: return cols / 32 * 34;
         default: return -1;
     }
 }

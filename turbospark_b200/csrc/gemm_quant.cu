@@ -52,6 +52,14 @@ template <>
 struct Fmt<TSB_MXFP4> {
     static constexpr int UNIT_BYTES = 136;  // eight 17-byte blocks
 };
+template <>
+struct Fmt<TSB_Q5_K> {
+    static constexpr int UNIT_BYTES = 176;
+};
+template <>
+struct Fmt<TSB_Q8_0> {
+    static constexpr int UNIT_BYTES = 272;  // eight 34-byte blocks
+};
 
 __device__ __forceinline__ uint32_t lds_u32_unaligned(const uint8_t* p) {
     uint32_t a = smem_u32(p);
@@ -373,6 +381,132 @@ __device__ __forceinline__ void q6k_block(const uint8_t* rA, const uint8_t* rB, 
         acc[nt][1] += dA * blkacc[nt][1];
         acc[nt][2] += dB * blkacc[nt][2];
         acc[nt][3] += dB * blkacc[nt][3];
+    }
+}
+
+// ---- Q5_K: one 176-byte superblock for rows (gid, gid+8) -------------------
+// Layout (crates/compute/src/quant_gguf/q5_k.rs:12-24,43-100): f16 d, f16 dmin, Q4_K's 12 packed scale/min
+// bytes, qh[32], ql[128]; element (group g, half hi, byte l) = 64g + 32hi + l takes its low four bits from
+// nibble hi of ql[32g + l] and its fifth from bit 2g+hi of qh[l]; w = d*sc*q - dmin*m with q in 0..31.
+// One mma covers 16 elements of one sub-block with the exact integers q as the A operand; a second mma with
+// an all-ones A operand yields the activation sum the sub-block's min multiplies.
+__device__ __forceinline__ void q4k_scale_min_smem(int j, const uint8_t* p, float& sc, float& m) {
+    // crates/compute/src/quant_gguf/q4_k.rs:43-54
+    uint32_t s, mm;
+    if (j < 4) {
+        s = p[j] & 63u, mm = p[j + 4] & 63u;
+    } else {
+        s = (p[j + 4] & 0xFu) | ((uint32_t)(p[j - 4] >> 6) << 4);
+        mm = (uint32_t)(p[j + 4] >> 4) | ((uint32_t)(p[j] >> 6) << 4);
+    }
+    sc = (float)s, m = (float)mm;
+}
+
+template <int NT>
+__device__ __forceinline__ void q5k_block(const uint8_t* rA, const uint8_t* rB, const ActOperand& act, int nblk,
+                                          int blk, int gid, int tig, float (&acc)[NT][4]) {
+    float bq[NT][4], bm[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) bq[nt][i] = 0.f, bm[nt][i] = 0.f;
+    const uint32_t k1024 = 0x64006400u, kOne = 0x3C003C00u;
+    const uint32_t ones[4] = {kOne, kOne, kOne, kOne};
+#pragma unroll 1
+    for (int j = 0; j < 8; j++) {  // sub-block j = 2g + hi
+        const int g = j >> 1, hi = j & 1;
+        float scA, mA, scB, mB;
+        q4k_scale_min_smem(j, rA + 4, scA, mA);
+        q4k_scale_min_smem(j, rB + 4, scB, mB);
+        float cq[NT][4], cs[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) cq[nt][i] = 0.f, cs[nt][i] = 0.f;
+#pragma unroll
+        for (int m = 0; m < 2; m++) {
+            const int l = 16 * m + 4 * tig;
+            const uint32_t qlA = *reinterpret_cast<const uint32_t*>(rA + 48 + 32 * g + l);
+            const uint32_t qlB = *reinterpret_cast<const uint32_t*>(rB + 48 + 32 * g + l);
+            const uint32_t qhA = *reinterpret_cast<const uint32_t*>(rA + 16 + l);
+            const uint32_t qhB = *reinterpret_cast<const uint32_t*>(rB + 16 + l);
+            const uint32_t vA = ((qlA >> (4 * hi)) & 0x0F0F0F0Fu) | (((qhA >> j) & 0x01010101u) << 4);
+            const uint32_t vB = ((qlB >> (4 * hi)) & 0x0F0F0F0Fu) | (((qhB >> j) & 0x01010101u) << 4);
+            uint32_t a[4];
+            a[0] = hsub2_u32(lop3_and_or(vA, 0x00FF00FFu, k1024), k1024);
+            a[1] = hsub2_u32(lop3_and_or(vB, 0x00FF00FFu, k1024), k1024);
+            a[2] = hsub2_u32(lop3_and_or(vA >> 8, 0x00FF00FFu, k1024), k1024);
+            a[3] = hsub2_u32(lop3_and_or(vB >> 8, 0x00FF00FFu, k1024), k1024);
+            const int k0 = blk * 256 + 32 * j + l;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const __half* xh16 = reinterpret_cast<const __half*>(act.xp);
+                const uint2 x = __ldg(reinterpret_cast<const uint2*>(xh16 + act_xp_half_index(nt * 8 + gid, k0, nblk)));
+                const uint32_t bb[2] = {x.x, x.y};
+                mma_16816(cq[nt], a, bb);
+                mma_16816(cs[nt], ones, bb);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            bq[nt][0] += scA * cq[nt][0], bq[nt][1] += scA * cq[nt][1];
+            bq[nt][2] += scB * cq[nt][2], bq[nt][3] += scB * cq[nt][3];
+            bm[nt][0] += mA * cs[nt][0], bm[nt][1] += mA * cs[nt][1];
+            bm[nt][2] += mB * cs[nt][2], bm[nt][3] += mB * cs[nt][3];
+        }
+    }
+    const __half2 ddA = *reinterpret_cast<const __half2*>(rA), ddB = *reinterpret_cast<const __half2*>(rB);
+    const float dA = __low2float(ddA), dminA = __high2float(ddA), dB = __low2float(ddB), dminB = __high2float(ddB);
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        acc[nt][0] += dA * bq[nt][0] - dminA * bm[nt][0];
+        acc[nt][1] += dA * bq[nt][1] - dminA * bm[nt][1];
+        acc[nt][2] += dB * bq[nt][2] - dminB * bm[nt][2];
+        acc[nt][3] += dB * bq[nt][3] - dminB * bm[nt][3];
+    }
+}
+
+// ---- Q8_0: eight 34-byte blocks (256 columns) for rows (gid, gid+8) --------
+// Block (crates/compute/src/quant_gguf/q8_0.rs:5-47): f16 d, 32 signed bytes; w = q * d.  A signed byte b
+// becomes the f16 integer b through the bit pattern 0x6400 | (b ^ 0x80) = 1024 + 128 + b, minus 1152.
+template <int NT>
+__device__ __forceinline__ void q8_0_unit(const uint8_t* rA, const uint8_t* rB, const ActOperand& act, int nblk,
+                                          int unit, int gid, int tig, float (&acc)[NT][4]) {
+    const uint32_t k1152 = 0x64806480u;
+#pragma unroll 2
+    for (int b = 0; b < 8; b++) {
+        const uint8_t* pA = rA + b * 34;
+        const uint8_t* pB = rB + b * 34;
+        const float dA = __half2float(*reinterpret_cast<const __half*>(pA));
+        const float dB = __half2float(*reinterpret_cast<const __half*>(pB));
+        float c[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) c[nt][i] = 0.f;
+#pragma unroll
+        for (int sgrp = 0; sgrp < 2; sgrp++) {
+            const uint32_t wA = lds_u32_unaligned(pA + 2 + 16 * sgrp + 4 * tig) ^ 0x80808080u;
+            const uint32_t wB = lds_u32_unaligned(pB + 2 + 16 * sgrp + 4 * tig) ^ 0x80808080u;
+            uint32_t a[4];
+            a[0] = hsub2_u32(__byte_perm(wA, 0x64646464u, 0x4240), k1152);  // elements (0, 2) of the lane's four
+            a[1] = hsub2_u32(__byte_perm(wB, 0x64646464u, 0x4240), k1152);
+            a[2] = hsub2_u32(__byte_perm(wA, 0x64646464u, 0x4341), k1152);  // elements (1, 3)
+            a[3] = hsub2_u32(__byte_perm(wB, 0x64646464u, 0x4341), k1152);
+            const int k0 = unit * 256 + b * 32 + 16 * sgrp + 4 * tig;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const __half* xh16 = reinterpret_cast<const __half*>(act.xp);
+                const uint2 x = __ldg(reinterpret_cast<const uint2*>(xh16 + act_xp_half_index(nt * 8 + gid, k0, nblk)));
+                const uint32_t bb[2] = {x.x, x.y};
+                mma_16816(c[nt], a, bb);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            acc[nt][0] += dA * c[nt][0], acc[nt][1] += dA * c[nt][1];
+            acc[nt][2] += dB * c[nt][2], acc[nt][3] += dB * c[nt][3];
+        }
     }
 }
 
@@ -700,6 +834,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
                         q4k_block<NT>(reinterpret_cast<const uint4*>(rA), reinterpret_cast<const uint4*>(rB), la, unit, tig, acc);
                     if constexpr (QT == TSB_MXFP4) mxfp4_unit<NT>(rA, rB, act, units, unit, gid, tig, acc);
                     if constexpr (QT == TSB_Q6_K) q6k_block<NT>(rA, rB, act, units, unit, gid, tig, acc);
+                    if constexpr (QT == TSB_Q5_K) q5k_block<NT>(rA, rB, act, units, unit, gid, tig, acc);
+                    if constexpr (QT == TSB_Q8_0) q8_0_unit<NT>(rA, rB, act, units, unit, gid, tig, acc);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
@@ -839,6 +975,8 @@ cudaError_t launch_gemm_fused(tsb_ctx* ctx, cudaStream_t st, int qtype, const ui
             case TSB_Q4_K: e = launch_epi<TSB_Q4_K>(ctx, st, w, rows, units, a, nt, t0, epi, args); break;
             case TSB_Q6_K: e = launch_epi<TSB_Q6_K>(ctx, st, w, rows, units, a, nt, t0, epi, args); break;
             case TSB_MXFP4: e = launch_epi<TSB_MXFP4>(ctx, st, w, rows, units, a, nt, t0, epi, args); break;
+            case TSB_Q5_K: e = launch_epi<TSB_Q5_K>(ctx, st, w, rows, units, a, nt, t0, epi, args); break;
+            case TSB_Q8_0: e = launch_epi<TSB_Q8_0>(ctx, st, w, rows, units, a, nt, t0, epi, args); break;
             default: return cudaErrorInvalidValue;
         }
         if (e != cudaSuccess) return e;
@@ -860,14 +998,14 @@ int32_t tsb_gemm_quant(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* re
                        int64_t cols, const void* x_f16, void* y, int32_t tokens, int32_t y_f32) {
     if (!ctx) return TSB_ERR_INVALID;
     TSB_REQUIRE(ctx, region && x_f16 && y, "null buffer");
-    TSB_REQUIRE(ctx, qtype == TSB_Q4_K || qtype == TSB_Q6_K || qtype == TSB_MXFP4, "unknown block format %d", qtype);
+    TSB_REQUIRE(ctx, qtype >= TSB_Q4_K && qtype <= TSB_QTYPE_LAST, "unknown block format %d", qtype);
     TSB_REQUIRE(ctx, rows > 0 && cols > 0 && tokens > 0, "rows, cols and tokens must be positive");
     if (cols % 256 != 0)
         return tsb_fail(ctx, TSB_ERR_UNSUPPORTED,
                         "cols (%lld) is not a whole number of 256-element superblocks", (long long)cols);
     TSB_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(x_f16) & 15u) == 0, "x must be 16-byte aligned");
-    if (qtype == TSB_Q4_K) TSB_REQUIRE(ctx, ((reinterpret_cast<uintptr_t>(region) + w_off) & 15u) == 0,
-                                       "Q4_K rows must start on a 16-byte boundary");
+    if (qtype == TSB_Q4_K || qtype == TSB_Q5_K || qtype == TSB_Q8_0)  // formats whose 256-column units are 16-byte multiples
+        TSB_REQUIRE(ctx, ((reinterpret_cast<uintptr_t>(region) + w_off) & 15u) == 0, "rows of this format must start on a 16-byte boundary");
     DeviceGuard g(ctx);
     cudaStream_t st = (cudaStream_t)s;
     {

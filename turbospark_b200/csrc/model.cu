@@ -33,8 +33,12 @@ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
 
 // Seeded synthetic blocks: every byte pseudo-random, then the scale fields are overwritten so the
 // dequantised weights are finite, zero-mean and of standard deviation about 0.02.
+__host__ __device__ inline int block_bytes_of(int qtype) {
+    return qtype == TSB_Q4_K ? 144 : qtype == TSB_Q6_K ? 210 : qtype == TSB_Q5_K ? 176 : qtype == TSB_Q8_0 ? 34 : 17;
+}
+
 __global__ void fill_blocks_kernel(uint8_t* __restrict__ data, int64_t n_blocks, int qtype, uint32_t seed) {
-    const int bb = qtype == TSB_Q4_K ? 144 : (qtype == TSB_Q6_K ? 210 : 17);
+    const int bb = block_bytes_of(qtype);
     for (int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b < n_blocks; b += (int64_t)gridDim.x * blockDim.x) {
         uint8_t* p = data + b * bb;
         uint32_t h = mix32((uint32_t)b * 0x9E3779B9u + seed) ^ mix32((uint32_t)(b >> 32) + seed * 31u);
@@ -51,6 +55,14 @@ __global__ void fill_blocks_kernel(uint8_t* __restrict__ data, int64_t n_blocks,
         } else if (qtype == TSB_Q6_K) {
             const unsigned short db = __half_as_ushort(__float2half_rn(1.46e-5f * (0.5f + u)));
             p[208] = db & 0xFF, p[209] = db >> 8;
+        } else if (qtype == TSB_Q5_K) {
+            // E[sc*q] = 31.5*15.5 cancelled by dmin*E[m] with dmin = 15.5 d
+            const __half d = __float2half_rn(3.7e-5f * (0.5f + u)), dm = __float2half_rn(15.5f * 3.7e-5f * (0.5f + u));
+            const unsigned short db = __half_as_ushort(d), mb = __half_as_ushort(dm);
+            p[0] = db & 0xFF, p[1] = db >> 8, p[2] = mb & 0xFF, p[3] = mb >> 8;
+        } else if (qtype == TSB_Q8_0) {
+            const unsigned short db = __half_as_ushort(__float2half_rn(2.7e-4f * (0.5f + u)));
+            p[0] = db & 0xFF, p[1] = db >> 8;
         } else {
             p[0] = (uint8_t)(119 + (h & 1));
         }
@@ -155,7 +167,7 @@ int32_t tsb_model_set_matrix(tsb_model* m, int32_t layer, int32_t which, int32_t
     if (!m) return TSB_ERR_INVALID;
     tsb_ctx* ctx = m->ctx;
     TSB_REQUIRE(ctx, host_blocks, "null data");
-    TSB_REQUIRE(ctx, qtype >= TSB_Q4_K && qtype <= TSB_MXFP4, "unknown block format %d", qtype);
+    TSB_REQUIRE(ctx, qtype >= TSB_Q4_K && qtype <= TSB_QTYPE_LAST, "unknown block format %d", qtype);
     int64_t off, total, wr, wc;
     Mat* slot = fused_slot(m, layer, which, &off, &total, &wr, &wc);
     TSB_REQUIRE(ctx, slot, "no such tensor (layer %d, which %d)", layer, which);
@@ -254,7 +266,7 @@ int32_t tsb_model_share(tsb_model* dst, int32_t dst_layer, const tsb_model* src,
 int32_t tsb_model_fill_synthetic(tsb_model* m, int32_t qtype, int32_t lm_head_qtype, uint64_t seed) {
     if (!m) return TSB_ERR_INVALID;
     tsb_ctx* ctx = m->ctx;
-    TSB_REQUIRE(ctx, qtype >= TSB_Q4_K && qtype <= TSB_MXFP4 && lm_head_qtype >= TSB_Q4_K && lm_head_qtype <= TSB_MXFP4, "bad format");
+    TSB_REQUIRE(ctx, qtype >= TSB_Q4_K && qtype <= TSB_QTYPE_LAST && lm_head_qtype >= TSB_Q4_K && lm_head_qtype <= TSB_QTYPE_LAST, "bad format");
     DeviceGuard g(ctx);
     const tsb_model_config& c = m->cfg;
     const int64_t qd = (int64_t)c.n_q_heads * c.head_dim, kd = (int64_t)c.n_kv_heads * c.head_dim;
@@ -264,7 +276,7 @@ int32_t tsb_model_fill_synthetic(tsb_model* m, int32_t qtype, int32_t lm_head_qt
             int32_t rc = mat_alloc(ctx, t, qt, rows, cols);
             if (rc) return rc;
         }
-        const int64_t nb = mat_bytes(t) / (qt == TSB_Q4_K ? 144 : (qt == TSB_Q6_K ? 210 : 17));
+        const int64_t nb = mat_bytes(t) / block_bytes_of(qt);
         fill_blocks_kernel<<<1024, 256>>>(t.data, nb, qt, sd);
         sd = sd * 1664525u + 1013904223u;
         return TSB_OK;

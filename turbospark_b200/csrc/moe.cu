@@ -103,7 +103,7 @@ int32_t tsb_moe_ffn(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* gate_
                     int32_t k, void* y_f16) {
     if (!ctx) return TSB_ERR_INVALID;
     TSB_REQUIRE(ctx, gate_up_region && down_region && x_f16 && residual_f16 && ids_dev && weights_f16_dev && y_f16, "null buffer");
-    TSB_REQUIRE(ctx, qtype == TSB_Q4_K || qtype == TSB_Q6_K || qtype == TSB_MXFP4, "unknown block format %d", qtype);
+    TSB_REQUIRE(ctx, qtype >= TSB_Q4_K && qtype <= TSB_QTYPE_LAST, "unknown block format %d", qtype);
     TSB_REQUIRE(ctx, tokens > 0 && tokens <= 4096 && k >= 1 && k <= 8 && n_experts >= k, "bad token / expert counts");
     TSB_REQUIRE(ctx, d_model > 0 && d_model % 256 == 0 && ffn > 0 && ffn % 256 == 0, "d_model and the expert width must be multiples of 256");
     DeviceGuard g(ctx);

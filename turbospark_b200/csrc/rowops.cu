@@ -51,6 +51,22 @@ __device__ __forceinline__ float dequant_elem(const uint8_t* row, int e) {
         const int sc = (int)(int8_t)blk[192 + h * 8 + (l >> 4) + 2 * k];
         const float d = __half2float(__ushort_as_half((unsigned short)(blk[208] | (blk[209] << 8))));
         return __fmul_rn(__fmul_rn(d, (float)sc), (float)q);
+    } else if constexpr (QT == TSB_Q5_K) {
+        // q5_k.rs:43-100: Q4_K's scales; fifth bit of (group g, half hi, byte l) is bit 2g+hi of qh[l]
+        const uint8_t* blk = row + (size_t)(e >> 8) * 176;
+        const int ie = e & 255, g = ie >> 6, within = ie & 63, l = within & 31, hi = within >> 5;
+        const float d = __half2float(__ushort_as_half((unsigned short)(blk[0] | (blk[1] << 8))));
+        const float dmin = __half2float(__ushort_as_half((unsigned short)(blk[2] | (blk[3] << 8))));
+        uint32_t sc, m;
+        q4k_scale_min_dev(2 * g + hi, blk + 4, sc, m);
+        const uint32_t byte = blk[48 + g * 32 + l];
+        const uint32_t q = (hi ? (byte >> 4) : (byte & 0xFu)) + ((((uint32_t)blk[16 + l] >> (2 * g + hi)) & 1u) << 4);
+        return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)q), __fmul_rn(dmin, (float)m));
+    } else if constexpr (QT == TSB_Q8_0) {
+        // q8_0.rs:20-47: out = q * d, q signed
+        const uint8_t* blk = row + (size_t)(e >> 5) * 34;
+        const float d = __half2float(__ushort_as_half((unsigned short)(blk[0] | (blk[1] << 8))));
+        return __fmul_rn((float)(int8_t)blk[2 + (e & 31)], d);
     } else {
         // quant_gguf_mxfp4.rs:114-141
         const uint8_t* blk = row + (size_t)(e >> 5) * 17;
@@ -319,6 +335,12 @@ cudaError_t launch_dequant(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8
         case TSB_Q6_K:
             return tsb_launch(ctx, dequant_rows_kernel<TSB_Q6_K, F16>, grid, dim3(256), 0, st, true, w, rb, table_rows,
                               cols, ids, id_stride, n, out, scale, ctx->dev_error);
+        case TSB_Q5_K:
+            return tsb_launch(ctx, dequant_rows_kernel<TSB_Q5_K, F16>, grid, dim3(256), 0, st, true, w, rb, table_rows,
+                              cols, ids, id_stride, n, out, scale, ctx->dev_error);
+        case TSB_Q8_0:
+            return tsb_launch(ctx, dequant_rows_kernel<TSB_Q8_0, F16>, grid, dim3(256), 0, st, true, w, rb, table_rows,
+                              cols, ids, id_stride, n, out, scale, ctx->dev_error);
         default:
             return tsb_launch(ctx, dequant_rows_kernel<TSB_MXFP4, F16>, grid, dim3(256), 0, st, true, w, rb, table_rows,
                               cols, ids, id_stride, n, out, scale, ctx->dev_error);
@@ -343,6 +365,12 @@ cudaError_t launch_embed_norm(tsb_ctx* ctx, cudaStream_t st, int qtype, const ui
                               id_stride, h, (const uint16_t*)g_bf16, act, ss_out, cs, rows, head_dim, lt, ctx->dev_error);
         case TSB_Q6_K:
             return tsb_launch(ctx, embed_norm_kernel<TSB_Q6_K>, dim3((unsigned)n), dim3(256), 0, st, true, w, rb, vocab_rows, d, ids,
+                              id_stride, h, (const uint16_t*)g_bf16, act, ss_out, cs, rows, head_dim, lt, ctx->dev_error);
+        case TSB_Q5_K:
+            return tsb_launch(ctx, embed_norm_kernel<TSB_Q5_K>, dim3((unsigned)n), dim3(256), 0, st, true, w, rb, vocab_rows, d, ids,
+                              id_stride, h, (const uint16_t*)g_bf16, act, ss_out, cs, rows, head_dim, lt, ctx->dev_error);
+        case TSB_Q8_0:
+            return tsb_launch(ctx, embed_norm_kernel<TSB_Q8_0>, dim3((unsigned)n), dim3(256), 0, st, true, w, rb, vocab_rows, d, ids,
                               id_stride, h, (const uint16_t*)g_bf16, act, ss_out, cs, rows, head_dim, lt, ctx->dev_error);
         default:
             return tsb_launch(ctx, embed_norm_kernel<TSB_MXFP4>, dim3((unsigned)n), dim3(256), 0, st, true, w, rb, vocab_rows, d, ids,
@@ -369,8 +397,8 @@ int32_t tsb_dequant_rows(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* 
                          const int32_t* row_ids, int32_t n_rows, float* out_f32) {
     if (!ctx) return TSB_ERR_INVALID;
     TSB_REQUIRE(ctx, region && out_f32 && n_rows > 0 && cols > 0, "bad arguments");
-    TSB_REQUIRE(ctx, qtype >= TSB_Q4_K && qtype <= TSB_MXFP4, "unknown block format %d", qtype);
-    TSB_REQUIRE(ctx, cols % (qtype == TSB_MXFP4 ? 32 : 256) == 0, "cols is not a whole number of blocks");
+    TSB_REQUIRE(ctx, qtype >= TSB_Q4_K && qtype <= TSB_QTYPE_LAST, "unknown block format %d", qtype);
+    TSB_REQUIRE(ctx, cols % ((qtype == TSB_MXFP4 || qtype == TSB_Q8_0) ? 32 : 256) == 0, "cols is not a whole number of blocks");
     DeviceGuard g(ctx);
     TSB_CUDA(ctx, launch_dequant<false>(ctx, (cudaStream_t)s, qtype, (const uint8_t*)region + w_off, INT64_MAX,
                                         (int)cols, row_ids, 1, n_rows, out_f32, 1.0f));
@@ -382,8 +410,8 @@ int32_t tsb_embed_rows(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* re
                        float out_scale) {
     if (!ctx) return TSB_ERR_INVALID;
     TSB_REQUIRE(ctx, region && out_f16 && token_ids && n > 0 && cols > 0 && vocab_rows > 0, "bad arguments");
-    TSB_REQUIRE(ctx, qtype >= TSB_Q4_K && qtype <= TSB_MXFP4, "unknown block format %d", qtype);
-    TSB_REQUIRE(ctx, cols % (qtype == TSB_MXFP4 ? 32 : 256) == 0, "cols is not a whole number of blocks");
+    TSB_REQUIRE(ctx, qtype >= TSB_Q4_K && qtype <= TSB_QTYPE_LAST, "unknown block format %d", qtype);
+    TSB_REQUIRE(ctx, cols % ((qtype == TSB_MXFP4 || qtype == TSB_Q8_0) ? 32 : 256) == 0, "cols is not a whole number of blocks");
     DeviceGuard g(ctx);
     TSB_CUDA(ctx, launch_embed_rows(ctx, (cudaStream_t)s, qtype, (const uint8_t*)region + w_off, vocab_rows, (int)cols,
                                     token_ids, 1, n, (__half*)out_f16, out_scale));

@@ -17,7 +17,7 @@ import numpy as np
 
 from . import capi
 
-QTYPES = {"q4k": (0, 256, 144), "q6k": (1, 256, 210), "mxfp4": (2, 32, 17)}
+QTYPES = {"q4k": (0, 256, 144), "q6k": (1, 256, 210), "mxfp4": (2, 32, 17), "q5k": (3, 256, 176), "q8_0": (4, 32, 34)}
 L2_BYTES = 126 << 20
 
 
@@ -32,6 +32,11 @@ def random_blocks(qtype, rows, cols, rng):
         b[:, :, 2:4] = np.frombuffer(np.float16(5.8e-4).tobytes(), np.uint8)
     elif qtype == "q6k":
         b[:, :, 208:210] = np.frombuffer(np.float16(1.5e-5).tobytes(), np.uint8)
+    elif qtype == "q5k":
+        b[:, :, 0:2] = np.frombuffer(np.float16(3.7e-5).tobytes(), np.uint8)
+        b[:, :, 2:4] = np.frombuffer(np.float16(5.7e-4).tobytes(), np.uint8)
+    elif qtype == "q8_0":
+        b[:, :, 0:2] = np.frombuffer(np.float16(2.7e-4).tobytes(), np.uint8)
     else:
         b[:, :, 0] = 119
     flat = b.reshape(base_rows, nb * nbytes)
