@@ -339,6 +339,39 @@ TSB_API int32_t tsb_model_share(tsb_model* dst, int32_t dst_layer, const tsb_mod
 TSB_API int32_t tsb_model_fill_synthetic(tsb_model* m, int32_t qtype, int32_t lm_head_qtype, uint64_t seed);
 TSB_API int64_t tsb_model_weight_bytes(const tsb_model* m);
 
+/* ------------------------------------------------------------------ resident weight file
+ * The leading index region of the reference's resident weight file: 24-byte header, 72-byte entries, string
+ * table, optional "GTURBIDX" format trailer (crates/model-io/src/resident_index.rs:19-67, load at :131-283,
+ * trailer check at :289-317; written by crates/repack/src/resident_writer.rs:375-470).  Host code only: these
+ * calls need no device.  Errors go to tsb_resident_last_error() (per thread): a malformed index answers
+ * TSB_ERR_INVALID with "index corrupt: ..." (ModelError::IndexCorrupt), a trailer naming another format version
+ * answers TSB_ERR_UNSUPPORTED (ModelError::UnsupportedIndexFormat). */
+typedef struct tsb_resident tsb_resident;
+typedef struct tsb_resident_entry { /* ResidentIndexEntry, resident_index.rs:47-66 */
+    uint8_t dtype;                  /* dtype tag byte (crates/repack/src/resident_writer.rs:80-162) */
+    uint8_t _pad[3];
+    uint32_t shape[4];              /* rank padded to 4 */
+    uint64_t file_offset;           /* absolute file offset of the payload (>= index size) */
+    uint64_t size_bytes;
+    uint64_t scale_offset, scale_size, bias_offset, bias_size; /* zero for the block formats */
+} tsb_resident_entry;
+TSB_API int32_t tsb_resident_open(const char* path, tsb_resident** out);
+TSB_API void tsb_resident_close(tsb_resident* idx);
+TSB_API const char* tsb_resident_last_error(void);
+TSB_API int64_t tsb_resident_count(const tsb_resident* idx);
+TSB_API uint64_t tsb_resident_index_size(const tsb_resident* idx); /* tensor bytes start here */
+TSB_API uint64_t tsb_resident_data_size(const tsb_resident* idx);
+TSB_API int32_t tsb_resident_entry_at(const tsb_resident* idx, int64_t i, tsb_resident_entry* out, char* name_buf, int32_t name_cap);
+TSB_API int32_t tsb_resident_find(const tsb_resident* idx, const char* name, tsb_resident_entry* out);
+/* dtype tag -> tsb_qtype (7 Q4_K, 8 Q6_K, 14 MXFP4, 13 Q5_K, 6 Q8_0), -1 for anything else */
+TSB_API int32_t tsb_resident_qtype_of(int32_t dtype_tag);
+/* Upload the Llama-family tensor set the reference's runner looks up by name (embed_tokens, per layer
+ * input_layernorm / self_attn.{q,k,v,o}_proj / post_attention_layernorm / mlp.{gate,up,down}_proj, model.norm,
+ * lm_head or the embedding again when tied: crates/runtime/src/families/llama/mod.rs:49-51,99,371-386) from the
+ * file into `m`, blocks verbatim.  A tensor whose byte count does not match its format and the model's shape
+ * is refused (real_forward_dispatch.rs:1008-1016), as is a dtype outside the block formats. */
+TSB_API int32_t tsb_model_load_resident(tsb_model* m, const tsb_resident* idx, int32_t tie_word_embeddings);
+
 /* A session = the producer: a target model, an optional stand-alone draft model, paged K/V caches for
  * `n_streams` independent request streams, and every activation / logits / scratch buffer a round
  * needs for up to `max_rows` rows per stream.  Mirrors what RealForwardRunner owns

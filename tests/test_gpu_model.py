@@ -359,3 +359,43 @@ def test_mixed_recipe_layers_match_the_oracle(oracle, order, recipe_name):
         qb = oracle.quantize(tsb.Q6_K, np.zeros((cfg.n_q_heads * cfg.head_dim, cfg.d_model), np.float32))
         target.set_matrix(0, W_Q, tsb.Q6_K, qb, cfg.n_q_heads * cfg.head_dim, cfg.d_model)
     sess.close(), target.close(), ctx.close()
+
+
+def test_a_model_loaded_from_a_resident_weight_file_gives_the_same_logits(oracle, tmp_path):
+    """The install-side path: a mixed-recipe tensor set written in the resident file layout under the names the
+    reference's Llama runner looks up, read back through the index and uploaded verbatim."""
+    import turbospark_b200 as tsb
+    from turbospark_b200 import resident
+    from turbospark_b200.model import W_V, W_DOWN, W_LM_HEAD, W_Q
+    ctx = tsb.Ctx(0)
+    cfg = tsb.config_tiny(max_context=256)
+    mats, norms = tsb.random_weights(cfg, 6, oracle, real_ffn=1408, qtype_of={W_V: tsb.Q6_K, W_DOWN: tsb.Q6_K, W_LM_HEAD: tsb.Q6_K})
+    direct = tsb.Model(ctx, cfg)
+    tsb.load_weights(direct, mats, norms)
+    path = tmp_path / "model_weights.bin"
+    path.write_bytes(resident.build_resident_file(resident.llama_tensor_list(cfg, mats, norms)))
+    idx = resident.ResidentIndex(path)
+    assert len(idx) == 2 + cfg.n_layers * 9 + 1
+    loaded = tsb.Model(ctx, cfg)
+    idx.load_into(loaded)
+    assert loaded.weight_bytes == direct.weight_bytes
+    rng = np.random.default_rng(3)
+    feed = rng.integers(0, cfg.vocab, size=6).astype(np.int32)
+    outs = []
+    for m in (direct, loaded):
+        sess = tsb.Session(ctx, m, None, 1, 8)
+        outs.append(sess.verify(feed, 0).copy())
+        sess.close()
+    assert np.array_equal(outs[0], outs[1])
+    # a tensor whose byte count does not fit the model's shape is refused, as is a non-block dtype
+    wrong = tsb.Model(ctx, tsb.ModelConfig(cfg.n_layers, cfg.d_model, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn,
+                                           cfg.vocab * 2, cfg.max_context, cfg.rms_eps, cfg.rope_theta))
+    with pytest.raises(tsb.TsbError, match="does not match"):
+        idx.load_into(wrong)
+    tensors = resident.llama_tensor_list(cfg, mats, norms)
+    tensors[2] = (tensors[2][0], 1, tensors[2][2], tensors[2][3])      # layer 0 q_proj tagged BF16
+    bad = tmp_path / "bad.bin"
+    bad.write_bytes(resident.build_resident_file(tensors))
+    with pytest.raises(tsb.TsbError, match="dtype tag"):
+        resident.ResidentIndex(bad).load_into(tsb.Model(ctx, cfg))
+    idx.close(), direct.close(), loaded.close(), wrong.close(), ctx.close()
