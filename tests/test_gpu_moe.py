@@ -37,7 +37,8 @@ def test_routing_matches_the_oracle_bit_for_bit(ctx, oracle, tokens, experts, k)
     assert got_ids[0, 0] == min(3, experts - 1)
 
 
-@pytest.mark.parametrize("kind,tokens,experts,k,d,f", [(2, 5, 16, 4, 512, 256), (2, 6, 128, 8, 2048, 768), (0, 3, 8, 2, 512, 512)])
+@pytest.mark.parametrize("kind,tokens,experts,k,d,f", [(2, 5, 16, 4, 512, 256), (2, 6, 128, 8, 2048, 768), (0, 3, 8, 2, 512, 512),
+                                                   (2, 150, 4, 2, 512, 256), (0, 40, 16, 4, 256, 256)])
 def test_routed_feed_forward_matches_the_oracle(ctx, oracle, kind, tokens, experts, k, d, f):
     rng = np.random.default_rng(100 + tokens)
     gu = np.concatenate([oracle.quantize(kind, (rng.standard_normal((2 * f, d)) * 0.05).astype(np.float32)) for _ in range(experts)])
@@ -55,3 +56,19 @@ def test_routed_feed_forward_matches_the_oracle(ctx, oracle, kind, tokens, exper
     assert not np.isnan(got).any()
     err = np.abs(got - want)
     assert np.all(err <= ABS + REL * np.abs(want)), float(err.max())
+
+
+def test_routed_feed_forward_flags_an_expert_id_outside_the_table(ctx, oracle):
+    import turbospark_b200 as tsb
+    d, f, experts = 256, 256, 4
+    rng = np.random.default_rng(1)
+    gu = np.concatenate([oracle.quantize(0, (rng.standard_normal((2 * f, d)) * 0.05).astype(np.float32)) for _ in range(experts)])
+    dn = np.concatenate([oracle.quantize(0, (rng.standard_normal((d, f)) * 0.05).astype(np.float32)) for _ in range(experts)])
+    x16 = oracle.f32_to_f16_bits(rng.standard_normal((2, d)).astype(np.float32))
+    ids = np.array([[0, 9], [1, 2]], dtype=np.int32)
+    w16 = oracle.f32_to_f16_bits(np.full((2, 2), 0.5, np.float32))
+    y = ctx.alloc(2 * d * 2)
+    ctx.moe_ffn(0, ctx.upload_weights(gu), ctx.upload_weights(dn), experts, d, f, ctx.to_device(x16), ctx.to_device(x16),
+                ctx.to_device(ids), ctx.to_device(w16), 2, 2, y)
+    with pytest.raises(tsb.TsbError):
+        ctx.sync()

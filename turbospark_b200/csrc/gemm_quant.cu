@@ -693,10 +693,23 @@ __device__ __forceinline__ void run_epilogue(const EpiArgs& e, const Group& gr, 
     }
 }
 
-template <int QT, int NT, int EPI>
+// GROUPED: one launch over many matrices of one shape (the experts of a routed feed-forward).  Work item =
+// (matrix m, row group g); matrix m sits at W + m * w_stride, multiplies count[m] token rows whose operand tiles
+// start at tile tile_start[m] of `act`, and its outputs are indexed from token tile_start[m] * 8.  A launch covers
+// token rows [chunk0, chunk0 + 8 NT) of every matrix; matrices with fewer rows are skipped.  Producer and consumers
+// read the same counts, so they skip the same items and the stage ring stays in step.
+struct GroupedArgs {
+    const int32_t* count = nullptr;
+    const int32_t* tile_start = nullptr;
+    int n_mats = 0;
+    int chunk0 = 0;
+    int64_t w_stride = 0;
+};
+
+template <int QT, int NT, int EPI, bool GROUPED = false>
 __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
-    gemm_quant_kernel(const uint8_t* __restrict__ W, int64_t rows, int units /*256-col units per row*/,
-                      ActOperand act, int tokens, int tok0, EpiArgs epi, uint32_t* __restrict__ err) {
+    gemm_quant_kernel(const uint8_t* __restrict__ W0, int64_t rows, int units /*256-col units per row*/,
+                      ActOperand act, int tokens, int tok0, EpiArgs epi, uint32_t* __restrict__ err, GroupedArgs grp) {
     constexpr int UB = Fmt<QT>::UNIT_BYTES;
     constexpr int ROW_STRIDE = row_stride_for(UB);
     constexpr int STAGE_BYTES = TILE_ROWS * ROW_STRIDE;
@@ -713,6 +726,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = (int)((rows + TILE_ROWS - 1) / TILE_ROWS);
     const int n_groups = num_groups<EPI>(n_tiles, epi);
+    const int n_items = GROUPED ? n_groups * grp.n_mats : n_groups;
     const int iters = (units + STAGE_UNITS - 1) / STAGE_UNITS;  // stages per row tile
     const int64_t row_bytes = (int64_t)units * UB;
 
@@ -732,7 +746,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
         // rows are not 16-byte multiples) and the consumer skips the same slack.
         uint32_t n = 0;
         bool inv_done = !NEEDS_INV;
-        for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+            int g = item;
+            const uint8_t* W = W0;
+            if constexpr (GROUPED) {
+                const int mat = item / n_groups;
+                g = item - mat * n_groups;
+                if (grp.count[mat] <= grp.chunk0) continue;
+                W = W0 + (int64_t)mat * grp.w_stride;
+            }
             const Group gr = group_of<EPI>(g, n_tiles, epi);
             for (int ti = 0; ti < gr.n; ti++) {
                 const int64_t row0 = (int64_t)(ti ? gr.tile1 : gr.tile0) * TILE_ROWS;
@@ -801,12 +823,31 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
         la.xs[nt] = act.xs + (size_t)nt * units * 32 + lane;
     }
     pdl_wait();  // activations come from the previous kernel
+    const ActOperand act0 = act;
 
     bool ok = true, have_inv = !NEEDS_INV;
     uint32_t n = 0;
-    for (int g = blockIdx.x; g < n_groups; g += gridDim.x) {
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+        if (item + (int)gridDim.x >= n_items) pdl_launch_dependents();  // last item of this CTA
+        int g = item;
+        const uint8_t* W = W0;
+        if constexpr (GROUPED) {
+            const int mat = item / n_groups;
+            g = item - mat * n_groups;
+            const int cnt = grp.count[mat];
+            if (cnt <= grp.chunk0) continue;
+            W = W0 + (int64_t)mat * grp.w_stride;
+            const int tile0 = grp.tile_start[mat] + grp.chunk0 / 8;
+            tokens = min(NT * 8, cnt - grp.chunk0);
+            tok0 = tile0 * 8;
+            act.xp = act0.xp + (size_t)tile0 * units * 256;
+            act.xs = act0.xs + (size_t)tile0 * units * 32;
+            for (int nt = 0; nt < NT; nt++) {
+                la.xp[nt] = act.xp + (size_t)nt * units * 256 + lane;
+                la.xs[nt] = act.xs + (size_t)nt * units * 32 + lane;
+            }
+        }
         const Group gr = group_of<EPI>(g, n_tiles, epi);
-        if (g + (int)gridDim.x >= n_groups) pdl_launch_dependents();  // last group of this CTA
         for (int ti = 0; ti < gr.n; ti++) {
             const int64_t row0 = (int64_t)(ti ? gr.tile1 : gr.tile0) * TILE_ROWS;
             float acc[NT][4];
@@ -875,10 +916,10 @@ constexpr size_t gemm_smem_bytes() {
            (size_t)NUM_STAGES * TILE_ROWS * row_stride_for(Fmt<QT>::UNIT_BYTES) + 128;
 }
 
-template <int QT, int NT, int EPI>
+template <int QT, int NT, int EPI, bool GROUPED = false>
 cudaError_t launch_one(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t rows, int units, ActOperand act, int tokens,
-                       int tok0, const EpiArgs& args) {
-    auto kern = gemm_quant_kernel<QT, NT, EPI>;
+                       int tok0, const EpiArgs& args, const GroupedArgs& grp = GroupedArgs()) {
+    auto kern = gemm_quant_kernel<QT, NT, EPI, GROUPED>;
     static bool configured = false;  // per instantiation; the attribute belongs to the device function
     constexpr size_t smem = gemm_smem_bytes<QT, NT>();
     if (!configured) {
@@ -894,8 +935,26 @@ cudaError_t launch_one(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t 
         groups = (args.n_q_heads + args.n_kv_heads) * (tph / 2) + (args.n_v_heads < 0 ? args.n_kv_heads : args.n_v_heads) * tph;
     }
     const int per_sm = NT <= 2 ? 2 : 1;
+    if (GROUPED) groups *= grp.n_mats;
     dim3 grid((unsigned)min(groups, ctx->sm_count * per_sm));
-    return tsb_launch(ctx, kern, grid, dim3(GEMM_THREADS), smem, st, true, w, rows, units, act, tokens, tok0, args, ctx->dev_error);
+    return tsb_launch(ctx, kern, grid, dim3(GEMM_THREADS), smem, st, true, w, rows, units, act, tokens, tok0, args, ctx->dev_error, grp);
+}
+
+template <int QT, int EPI>
+cudaError_t launch_grouped_nt(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t rows, int units, ActOperand act, int tokens,
+                              const EpiArgs& args, const GroupedArgs& grp) {
+    if (tokens <= 8) return launch_one<QT, 1, EPI, true>(ctx, st, w, rows, units, act, tokens, 0, args, grp);
+    if (tokens <= 16) return launch_one<QT, 2, EPI, true>(ctx, st, w, rows, units, act, tokens, 0, args, grp);
+    if (tokens <= 32) return launch_one<QT, 4, EPI, true>(ctx, st, w, rows, units, act, tokens, 0, args, grp);
+    return launch_one<QT, 8, EPI, true>(ctx, st, w, rows, units, act, tokens, 0, args, grp);
+}
+
+template <int QT>
+cudaError_t launch_grouped_epi(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t rows, int units, ActOperand act, int tokens,
+                               int epi, const EpiArgs& args, const GroupedArgs& grp) {
+    if (epi == EPI_MOE_ACT) return launch_grouped_nt<QT, EPI_MOE_ACT>(ctx, st, w, rows, units, act, tokens, args, grp);
+    if (epi == EPI_PLAIN) return launch_grouped_nt<QT, EPI_PLAIN>(ctx, st, w, rows, units, act, tokens, args, grp);
+    return cudaErrorInvalidValue;
 }
 
 template <int QT, int EPI>
@@ -936,10 +995,12 @@ __global__ void act_prepare_kernel(const __half* __restrict__ x, int64_t x_strid
     for (int i = 0; i < 8; i++) v[i] = 0.f;
     if (active && t < tokens) {
         const int src = src_rows ? src_rows[t] : t;
-        const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)src * x_stride + e0);
-        const __half* hp = reinterpret_cast<const __half*>(&raw);
+        if (src >= 0) {  // a negative source row is a padding slot: zeros
+            const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)src * x_stride + e0);
+            const __half* hp = reinterpret_cast<const __half*>(&raw);
 #pragma unroll
-        for (int i = 0; i < 8; i++) v[i] = __half2float(hp[i]);
+            for (int i = 0; i < 8; i++) v[i] = __half2float(hp[i]);
+        }
     }
     pdl_launch_dependents();
     act_store8(v, xp, xs, t, e0, cols >> 8, active);
@@ -977,6 +1038,28 @@ cudaError_t launch_gemm_fused(tsb_ctx* ctx, cudaStream_t st, int qtype, const ui
             case TSB_MXFP4: e = launch_epi<TSB_MXFP4>(ctx, st, w, rows, units, a, nt, t0, epi, args); break;
             case TSB_Q5_K: e = launch_epi<TSB_Q5_K>(ctx, st, w, rows, units, a, nt, t0, epi, args); break;
             case TSB_Q8_0: e = launch_epi<TSB_Q8_0>(ctx, st, w, rows, units, a, nt, t0, epi, args); break;
+            default: return cudaErrorInvalidValue;
+        }
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+cudaError_t launch_gemm_grouped(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t w_stride, int n_mats,
+                                int64_t rows, int64_t cols, ActOperand act, const int32_t* count, const int32_t* tile_start,
+                                int max_tokens, int epi, const EpiArgs& args) {
+    const int units = (int)(cols / 256);
+    for (int t0 = 0; t0 < max_tokens; t0 += 64) {
+        GroupedArgs grp;
+        grp.count = count, grp.tile_start = tile_start, grp.n_mats = n_mats, grp.chunk0 = t0, grp.w_stride = w_stride;
+        const int nt = min(64, max_tokens - t0);
+        cudaError_t e;
+        switch (qtype) {
+            case TSB_Q4_K: e = launch_grouped_epi<TSB_Q4_K>(ctx, st, w, rows, units, act, nt, epi, args, grp); break;
+            case TSB_Q6_K: e = launch_grouped_epi<TSB_Q6_K>(ctx, st, w, rows, units, act, nt, epi, args, grp); break;
+            case TSB_MXFP4: e = launch_grouped_epi<TSB_MXFP4>(ctx, st, w, rows, units, act, nt, epi, args, grp); break;
+            case TSB_Q5_K: e = launch_grouped_epi<TSB_Q5_K>(ctx, st, w, rows, units, act, nt, epi, args, grp); break;
+            case TSB_Q8_0: e = launch_grouped_epi<TSB_Q8_0>(ctx, st, w, rows, units, act, nt, epi, args, grp); break;
             default: return cudaErrorInvalidValue;
         }
         if (e != cudaSuccess) return e;

@@ -91,9 +91,22 @@ cudaError_t launch_act_prepare_gather(tsb_ctx* ctx, cudaStream_t st, const __hal
 // up halves back to back; for EPI_ROPE_STORE q heads, k heads, v heads back to back).
 cudaError_t launch_gemm_fused(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t rows, int64_t cols,
                               ActOperand act, int tokens, int epi, const EpiArgs& args);
+// One launch (per 64 token rows) over n_mats matrices of one shape, w_stride bytes apart: matrix m multiplies
+// count[m] token rows (device array) whose operand tiles start at tile tile_start[m] (device array) of `act`;
+// outputs are indexed from token tile_start[m] * 8.  max_tokens bounds every count.  Epilogues: EPI_MOE_ACT, EPI_PLAIN.
+cudaError_t launch_gemm_grouped(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t w_stride, int n_mats,
+                                int64_t rows, int64_t cols, ActOperand act, const int32_t* count, const int32_t* tile_start,
+                                int max_tokens, int epi, const EpiArgs& args);
 // y[t, r] = W[r,:] . x[t,:]; y f16 or f32, [tokens, rows] with row stride y_stride (elements).
 cudaError_t launch_gemm_quant(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t rows, int64_t cols,
                               ActOperand act, void* y, int64_t y_stride, int tokens, bool y_f32);
+
+// The routed feed-forward (csrc/moe.cu): y = half(residual + sum over slots of w * down_e(act(gate_e x) * up_e x)).
+// x rows have stride x_stride; ids / weights are [tokens, k]; workspace holds moe_ffn_workspace_bytes(...) bytes.
+size_t moe_ffn_workspace_bytes(int tokens, int k, int n_experts, int d_model, int ffn);
+cudaError_t launch_moe_ffn(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* gate_up, const uint8_t* down, int n_experts,
+                           int d_model, int ffn, const __half* x, int64_t x_stride, const __half* residual, const int32_t* ids,
+                           const __half* weights, int tokens, int k, __half* y, void* workspace);
 
 // The tensor-memory (tcgen05) path for many token rows: Q4_K, rows a multiple of 128.  x is natural f16.
 bool gemm_wide_supported(int qtype, int64_t rows, int64_t cols, int tokens);

@@ -11,12 +11,14 @@
 //
 // The expert matrices are verbatim block rows (any format the matmul kernel reads; the benchmark shape uses
 // MXFP4), laid out per expert as gate rows then up rows [2F, D], and down rows [D, F].  Token rows routed to the
-// same expert are gathered and run through the fused matmul kernel once per expert; the dispatch lists are built
-// on the host from the device's routing result (one small readback per call).
+// same expert are gathered into that expert's tiles of a padded token space (dispatch lists built on the device)
+// and each phase is one grouped launch of the matmul kernel over all experts: no host round trip.
 #include <algorithm>
 #include <vector>
 
 #include "gemm_quant.cuh"
+
+constexpr int MOE_MAX_EXPERTS = 512;
 
 namespace {
 
@@ -80,6 +82,116 @@ __global__ void moe_combine_kernel(const __half* __restrict__ residual, const fl
     y[idx] = __float2half_rn(acc);
 }
 
+
+// Dispatch lists on the device.  Every expert's rows are laid out in a padded token space: expert e owns the
+// token tiles [tile_start[e], tile_start[e] + ceil(count[e] / 8)), so each expert's operand starts on a tile
+// boundary.  src_pad[p] = source token of padded slot p (or -1), dst_pad[p] = its (token, slot) pair (or -1).
+// One CTA; the slot order inside an expert comes from an atomic counter, which is harmless: a row's result does
+// not depend on its batch mates.
+__global__ void __launch_bounds__(1024)
+    moe_dispatch_kernel(const int32_t* __restrict__ ids, int P, int k, int n_experts, int32_t* __restrict__ count,
+                        int32_t* __restrict__ tile_start, int32_t* __restrict__ src_pad, int32_t* __restrict__ dst_pad, int pad_slots,
+                        uint32_t* __restrict__ err) {
+    __shared__ int cnt[MOE_MAX_EXPERTS], fill[MOE_MAX_EXPERTS], tstart[MOE_MAX_EXPERTS];
+    pdl_wait();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) cnt[e] = 0, fill[e] = 0;
+    for (int p = threadIdx.x; p < pad_slots; p += blockDim.x) src_pad[p] = -1, dst_pad[p] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < P; i += blockDim.x) {
+        int e = ids[i];
+        if (e < 0 || e >= n_experts) {
+            atomicCAS(err, 0u, (uint32_t)TSB_DEV_BAD_INDEX);
+            e = 0;
+        }
+        atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int e = 0; e < n_experts; e++) {
+            tstart[e] = t;
+            t += (cnt[e] + 7) >> 3;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < P; i += blockDim.x) {
+        int e = ids[i];
+        if (e < 0 || e >= n_experts) e = 0;
+        const int p = tstart[e] * 8 + atomicAdd(&fill[e], 1);
+        src_pad[p] = i / k, dst_pad[p] = i;
+    }
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) count[e] = cnt[e], tile_start[e] = tstart[e];
+    pdl_launch_dependents();
+}
+
+struct MoeLayout {
+    int pad_tiles;  // tiles of the padded token space, with eight spare tiles the widest launch may read past the last expert
+    size_t off_count, off_tstart, off_src, off_dst, off_xin_p, off_xin_s, off_act_p, off_act_s, off_values, total;
+};
+
+MoeLayout moe_layout(int tokens, int k, int n_experts, int d_model, int ffn) {
+    MoeLayout L;
+    const int P = tokens * k;
+    L.pad_tiles = (P + 7) / 8 + std::min(P, n_experts) + 8;
+    const int slots = L.pad_tiles * 8;
+    auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    size_t o = 0;
+    L.off_count = o, o += up((size_t)n_experts * 4);
+    L.off_tstart = o, o += up((size_t)n_experts * 4);
+    L.off_src = o, o += up((size_t)slots * 4);
+    L.off_dst = o, o += up((size_t)slots * 4);
+    L.off_xin_p = o, o += up(act_xp_bytes(slots, d_model));
+    L.off_xin_s = o, o += up(act_xs_bytes(slots, d_model));
+    L.off_act_p = o, o += up(act_xp_bytes(slots, ffn));
+    L.off_act_s = o, o += up(act_xs_bytes(slots, ffn));
+    L.off_values = o, o += up((size_t)P * d_model * sizeof(float));
+    L.total = o;
+    return L;
+}
+
+}  // namespace
+
+size_t moe_ffn_workspace_bytes(int tokens, int k, int n_experts, int d_model, int ffn) {
+    return moe_layout(tokens, k, n_experts, d_model, ffn).total;
+}
+
+// The routed feed-forward without a host round trip: dispatch on the device, one gather, one grouped launch per
+// phase (per 64 rows of the fullest expert's possible load), the slot-ordered combine.  Graph-capturable.
+cudaError_t launch_moe_ffn(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* gate_up, const uint8_t* down, int n_experts,
+                           int d_model, int ffn, const __half* x, int64_t x_stride, const __half* residual, const int32_t* ids,
+                           const __half* weights, int tokens, int k, __half* y, void* workspace) {
+    const MoeLayout L = moe_layout(tokens, k, n_experts, d_model, ffn);
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    int32_t* count = reinterpret_cast<int32_t*>(ws + L.off_count);
+    int32_t* tstart = reinterpret_cast<int32_t*>(ws + L.off_tstart);
+    int32_t* src_pad = reinterpret_cast<int32_t*>(ws + L.off_src);
+    int32_t* dst_pad = reinterpret_cast<int32_t*>(ws + L.off_dst);
+    const ActOut xin_w{reinterpret_cast<uint4*>(ws + L.off_xin_p), reinterpret_cast<uint4*>(ws + L.off_xin_s)};
+    const ActOut act_w{reinterpret_cast<uint4*>(ws + L.off_act_p), reinterpret_cast<uint4*>(ws + L.off_act_s)};
+    const ActOperand xin{xin_w.xp, xin_w.xs}, act{act_w.xp, act_w.xs};
+    float* values = reinterpret_cast<float*>(ws + L.off_values);
+    const int P = tokens * k, slots = L.pad_tiles * 8;
+    cudaError_t e = tsb_launch(ctx, moe_dispatch_kernel, dim3(1), dim3(1024), 0, st, true, ids, P, k, n_experts, count, tstart, src_pad,
+                               dst_pad, slots, ctx->dev_error);
+    if (e != cudaSuccess) return e;
+    if ((e = launch_act_prepare_gather(ctx, st, x, x_stride, src_pad, slots, d_model, xin_w.xp, xin_w.xs)) != cudaSuccess) return e;
+    const int64_t gu_bytes = (int64_t)2 * ffn * tsb_row_bytes(qtype, d_model), down_bytes = (int64_t)d_model * tsb_row_bytes(qtype, ffn);
+    EpiArgs a1;
+    a1.out = act_w;
+    if ((e = launch_gemm_grouped(ctx, st, qtype, gate_up, gu_bytes, n_experts, 2 * ffn, d_model, xin, count, tstart, tokens, EPI_MOE_ACT, a1)) !=
+        cudaSuccess)
+        return e;
+    EpiArgs a2;
+    a2.y = values, a2.y_stride = d_model, a2.y_f32 = 1, a2.y_rows = dst_pad;
+    if ((e = launch_gemm_grouped(ctx, st, qtype, down, down_bytes, n_experts, d_model, ffn, act, count, tstart, tokens, EPI_PLAIN, a2)) !=
+        cudaSuccess)
+        return e;
+    const int64_t total = (int64_t)tokens * d_model;
+    return tsb_launch(ctx, moe_combine_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, true, residual,
+                      (const float*)values, weights, (int)k, (int)d_model, (int)tokens, y);
+}
+
+namespace {
 }  // namespace
 
 extern "C" {
@@ -104,70 +216,17 @@ int32_t tsb_moe_ffn(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* gate_
     if (!ctx) return TSB_ERR_INVALID;
     TSB_REQUIRE(ctx, gate_up_region && down_region && x_f16 && residual_f16 && ids_dev && weights_f16_dev && y_f16, "null buffer");
     TSB_REQUIRE(ctx, qtype >= TSB_Q4_K && qtype <= TSB_QTYPE_LAST, "unknown block format %d", qtype);
-    TSB_REQUIRE(ctx, tokens > 0 && tokens <= 4096 && k >= 1 && k <= 8 && n_experts >= k, "bad token / expert counts");
+    TSB_REQUIRE(ctx, tokens > 0 && tokens <= 4096 && k >= 1 && k <= 8 && n_experts >= k && n_experts <= MOE_MAX_EXPERTS,
+                "bad token / expert counts");
     TSB_REQUIRE(ctx, d_model > 0 && d_model % 256 == 0 && ffn > 0 && ffn % 256 == 0, "d_model and the expert width must be multiples of 256");
     DeviceGuard g(ctx);
     cudaStream_t st = (cudaStream_t)s;
-    const int P = tokens * k;
-    // routing result to the host: the dispatch lists are built here
-    std::vector<int32_t> ids(P);
-    TSB_CUDA(ctx, cudaMemcpyAsync(ids.data(), ids_dev, (size_t)P * sizeof(int32_t), cudaMemcpyDeviceToHost, st));
-    TSB_CUDA(ctx, cudaStreamSynchronize(st));
-    std::vector<int> count(n_experts, 0), start(n_experts + 1, 0);
-    for (int i = 0; i < P; i++) {
-        if (ids[i] < 0 || ids[i] >= n_experts) return tsb_fail(ctx, TSB_ERR_INVALID, "expert id %d outside 0..%d", ids[i], n_experts);
-        count[ids[i]]++;
-    }
-    for (int e = 0; e < n_experts; e++) start[e + 1] = start[e] + count[e];
-    std::vector<int32_t> src(P), dst(P);  // per dispatch row: source token, (token, slot) row of the value matrix
-    {
-        std::vector<int> fill(start.begin(), start.end() - 1);
-        for (int i = 0; i < P; i++) {
-            const int at = fill[ids[i]]++;
-            src[at] = i / k, dst[at] = i;
-        }
-    }
-    int max_n = 1;
-    for (int e = 0; e < n_experts; e++) max_n = std::max(max_n, count[e]);
-    // scratch, stream-ordered: dispatch lists, the gathered operand, the activation operand, the per-slot values
-    const size_t lists_b = ((size_t)2 * P * sizeof(int32_t) + 255) & ~(size_t)255;
-    const size_t xin_b = ((act_xp_bytes(max_n, d_model) + 255) & ~(size_t)255) + ((act_xs_bytes(max_n, d_model) + 255) & ~(size_t)255);
-    const size_t act_b = ((act_xp_bytes(max_n, ffn) + 255) & ~(size_t)255) + ((act_xs_bytes(max_n, ffn) + 255) & ~(size_t)255);
-    const size_t val_b = (size_t)P * d_model * sizeof(float);
-    uint8_t* scratch = nullptr;
-    TSB_CUDA(ctx, cudaMallocAsync((void**)&scratch, lists_b + xin_b + act_b + val_b, st));
-    int32_t* src_dev = reinterpret_cast<int32_t*>(scratch);
-    int32_t* dst_dev = src_dev + P;
-    uint4* xin_p = reinterpret_cast<uint4*>(scratch + lists_b);
-    uint4* xin_s = reinterpret_cast<uint4*>(scratch + lists_b + ((act_xp_bytes(max_n, d_model) + 255) & ~(size_t)255));
-    uint4* act_p = reinterpret_cast<uint4*>(scratch + lists_b + xin_b);
-    uint4* act_s = reinterpret_cast<uint4*>(scratch + lists_b + xin_b + ((act_xp_bytes(max_n, ffn) + 255) & ~(size_t)255));
-    float* values = reinterpret_cast<float*>(scratch + lists_b + xin_b + act_b);
-    cudaError_t e = cudaMemcpyAsync(src_dev, src.data(), (size_t)P * sizeof(int32_t), cudaMemcpyHostToDevice, st);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(dst_dev, dst.data(), (size_t)P * sizeof(int32_t), cudaMemcpyHostToDevice, st);
-    const int64_t gu_bytes = (int64_t)2 * ffn * tsb_row_bytes(qtype, d_model), down_bytes = (int64_t)d_model * tsb_row_bytes(qtype, ffn);
-    const uint8_t* gu0 = static_cast<const uint8_t*>(gate_up_region) + gate_up_off;
-    const uint8_t* dn0 = static_cast<const uint8_t*>(down_region) + down_off;
-    for (int ex = 0; ex < n_experts && e == cudaSuccess; ex++) {
-        const int n = count[ex];
-        if (!n) continue;
-        e = launch_act_prepare_gather(ctx, st, (const __half*)x_f16, d_model, src_dev + start[ex], n, d_model, xin_p, xin_s);
-        if (e != cudaSuccess) break;
-        EpiArgs a1;
-        a1.out = ActOut{act_p, act_s};
-        e = launch_gemm_fused(ctx, st, qtype, gu0 + (int64_t)ex * gu_bytes, 2 * ffn, d_model, ActOperand{xin_p, xin_s}, n, EPI_MOE_ACT, a1);
-        if (e != cudaSuccess) break;
-        EpiArgs a2;
-        a2.y = values, a2.y_stride = d_model, a2.y_f32 = 1, a2.y_rows = dst_dev + start[ex];
-        e = launch_gemm_fused(ctx, st, qtype, dn0 + (int64_t)ex * down_bytes, d_model, ffn, ActOperand{act_p, act_s}, n, EPI_PLAIN, a2);
-    }
-    if (e == cudaSuccess) {
-        const int64_t total = (int64_t)tokens * d_model;
-        e = tsb_launch(ctx, moe_combine_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, true,
-                       (const __half*)residual_f16, (const float*)values, (const __half*)weights_f16_dev, (int)k, (int)d_model,
-                       (int)tokens, (__half*)y_f16);
-    }
-    cudaFreeAsync(scratch, st);
+    void* ws = nullptr;
+    TSB_CUDA(ctx, cudaMallocAsync(&ws, moe_ffn_workspace_bytes(tokens, k, n_experts, d_model, ffn), st));
+    cudaError_t e = launch_moe_ffn(ctx, st, qtype, static_cast<const uint8_t*>(gate_up_region) + gate_up_off,
+                                   static_cast<const uint8_t*>(down_region) + down_off, n_experts, d_model, ffn, (const __half*)x_f16, d_model,
+                                   (const __half*)residual_f16, ids_dev, (const __half*)weights_f16_dev, tokens, k, (__half*)y_f16, ws);
+    cudaFreeAsync(ws, st);
     TSB_CUDA(ctx, e);
     return TSB_OK;
 }
