@@ -338,6 +338,20 @@ TSB_API int32_t tsb_model_share(tsb_model* dst, int32_t dst_layer, const tsb_mod
  * right shapes and formats without a host copy; values are valid blocks with small scales). */
 TSB_API int32_t tsb_model_fill_synthetic(tsb_model* m, int32_t qtype, int32_t lm_head_qtype, uint64_t seed);
 TSB_API int64_t tsb_model_weight_bytes(const tsb_model* m);
+/* Routed feed-forward (the llama family's MoE layers: crates/runtime/src/families/llama/moe.rs:36-221, router
+ * families/llama/router.rs:12-66).  tsb_model_set_moe, called before any tensor is uploaded, makes every layer's
+ * feed-forward routed: n_experts experts of width moe_ffn, top_k per token (the config's dense `ffn` is then
+ * unused and gate / up / down are not uploaded).  The router is the reference's 8-bit affine matrix: u8
+ * [n_experts, d_model] with bf16 scale and bias per 64 columns (dtype tag 5); experts are verbatim block rows,
+ * per expert gate rows then up rows [2 moe_ffn, d_model], and down rows [d_model, moe_ffn]. */
+TSB_API int32_t tsb_model_set_moe(tsb_model* m, int32_t n_experts, int32_t top_k, int32_t moe_ffn);
+TSB_API int32_t tsb_model_set_router(tsb_model* m, int32_t layer, const void* q_u8, const void* scale_bf16, const void* bias_bf16);
+TSB_API int32_t tsb_model_set_experts(tsb_model* m, int32_t layer, int32_t qtype, const void* gate_up_blocks,
+                                      const void* down_blocks);
+/* router_gemv_gemma4 (crates/gpu/src/moe_decode.rs:491-530, shaders/moe.metal:107-145) with the all-ones
+ * effective scale: logits[t, e] = sum over 64-column groups of fma(s, q.x, .) and fma(b, sum x, .), f32. */
+TSB_API int32_t tsb_router_logits(tsb_ctx* ctx, tsb_stream s, const void* q_u8, const void* scale_bf16, const void* bias_bf16,
+                                  const void* x_f16, int32_t tokens, int32_t n_experts, int32_t d_model, float* logits_out);
 
 /* ------------------------------------------------------------------ resident weight file
  * The leading index region of the reference's resident weight file: 24-byte header, 72-byte entries, string

@@ -357,8 +357,19 @@ def gather_rows_inplace(rows_u16, map_):
     return int(lib().tso_gather_rows_inplace(_p(rows_u16), C.c_int64(rows_u16.shape[1]), _p(m), C.c_int(m.size)))
 
 
+def router_logits(q_u8, scale_bf16, bias_bf16, x16, experts):
+    """router_gemv_gemma4 with the all-ones effective scale: [tokens, experts] f32."""
+    x = np.ascontiguousarray(x16, dtype=np.uint16)
+    tokens, d = x.shape
+    q = np.ascontiguousarray(q_u8, dtype=np.uint8)
+    sc, bi = np.ascontiguousarray(scale_bf16, dtype=np.uint16), np.ascontiguousarray(bias_bf16, dtype=np.uint16)
+    out = np.empty((tokens, experts), dtype=np.float32)
+    lib().tso_router_logits(_p(q), _p(sc), _p(bi), _p(x), C.c_int64(tokens), C.c_int64(experts), C.c_int64(d), _p(out))
+    return out
+
+
 class Model:
-    """CPU model: dense Llama-style decoder over quantized matrices."""
+    """CPU model: Llama-style decoder over quantized matrices, dense or with a routed feed-forward."""
 
     def __init__(self, cfg: ModelCfg, threads=1):
         self.cfg = cfg
@@ -373,6 +384,23 @@ class Model:
     def set_norm(self, layer, which, bf16):
         bf16 = np.ascontiguousarray(bf16, dtype=np.uint16)
         lib().tso_model_set_norm(self.h, C.c_int(layer), C.c_int(which), _p(bf16), C.c_int64(bf16.size))
+
+    def set_moe(self, n_experts, top_k, moe_ffn):
+        """Every layer's feed-forward becomes routed (families/llama/moe.rs)."""
+        self.n_experts, self.top_k, self.moe_ffn = n_experts, top_k, moe_ffn
+        lib().tso_model_set_moe(self.h, C.c_int(n_experts), C.c_int(top_k), C.c_int(moe_ffn))
+
+    def set_router(self, layer, q_u8, scale_bf16, bias_bf16):
+        q = np.ascontiguousarray(q_u8, dtype=np.uint8)
+        sc, bi = np.ascontiguousarray(scale_bf16, dtype=np.uint16), np.ascontiguousarray(bias_bf16, dtype=np.uint16)
+        assert q.size == self.n_experts * self.cfg.d_model and sc.size == q.size // 64 == bi.size
+        lib().tso_model_set_router(self.h, C.c_int(layer), _p(q), _p(sc), _p(bi))
+
+    def set_experts(self, layer, kind, gate_up, down):
+        gu, dn = np.ascontiguousarray(gate_up, dtype=np.uint8), np.ascontiguousarray(down, dtype=np.uint8)
+        assert gu.size == self.n_experts * 2 * self.moe_ffn * row_bytes(kind, self.cfg.d_model)
+        assert dn.size == self.n_experts * self.cfg.d_model * row_bytes(kind, self.moe_ffn)
+        lib().tso_model_set_experts(self.h, C.c_int(layer), C.c_int(kind), _p(gu), _p(dn))
 
     def __del__(self):
         if getattr(self, "h", None):

@@ -229,6 +229,10 @@ class Ctx:
         self.check(lib().tsb_moe_route(self.h, stream, _vp(router_logits), C.c_int32(tokens), C.c_int32(n_experts), C.c_int32(k),
                                        _vp(scale) if scale is not None else None, _vp(ids_out), _vp(weights_out)))
 
+    def router_logits(self, q_u8, scale_bf16, bias_bf16, x, tokens, n_experts, d_model, logits_out, stream=None):
+        self.check(lib().tsb_router_logits(self.h, stream, _vp(q_u8), _vp(scale_bf16), _vp(bias_bf16), _vp(x), C.c_int32(tokens),
+                                           C.c_int32(n_experts), C.c_int32(d_model), _vp(logits_out)))
+
     def moe_ffn(self, qtype, gate_up, down, n_experts, d_model, ffn, x, residual, ids, weights, tokens, k, y, stream=None):
         self.check(lib().tsb_moe_ffn(self.h, stream, C.c_int32(qtype), _vp(gate_up), C.c_uint64(0), _vp(down), C.c_uint64(0),
                                      C.c_int32(n_experts), C.c_int32(d_model), C.c_int32(ffn), _vp(x), _vp(residual), _vp(ids),

@@ -156,6 +156,9 @@ void tsb_model_destroy(tsb_model* m) {
             if (l.attn_norm) tsb_free(m->ctx, l.attn_norm);
             if (l.ffn_norm) tsb_free(m->ctx, l.ffn_norm);
         }
+        if (l.moe_owned)
+            for (void* p : {(void*)l.router_q, (void*)l.router_scale, (void*)l.router_bias, (void*)l.experts_gate_up, (void*)l.experts_down})
+                if (p) tsb_free(m->ctx, p);
     }
     mat_free(m->ctx, m->embed), mat_free(m->ctx, m->lm_head);
     if (m->out_norm_owned && m->out_norm) tsb_free(m->ctx, m->out_norm);
@@ -214,6 +217,61 @@ int32_t tsb_model_set_matrix(tsb_model* m, int32_t layer, int32_t which, int32_t
     return TSB_OK;
 }
 
+int32_t tsb_model_set_moe(tsb_model* m, int32_t n_experts, int32_t top_k, int32_t moe_ffn) {
+    if (!m) return TSB_ERR_INVALID;
+    tsb_ctx* ctx = m->ctx;
+    TSB_REQUIRE(ctx, n_experts >= 1 && n_experts <= 512 && top_k >= 1 && top_k <= 8 && top_k <= n_experts, "need 1 <= top_k <= min(8, experts) and at most 512 experts");
+    TSB_REQUIRE(ctx, moe_ffn > 0 && moe_ffn % 256 == 0, "the expert width must be a multiple of 256");
+    for (const LayerW& l : m->layers) TSB_REQUIRE(ctx, !l.wgu.data && !l.wdown.data, "set_moe comes before the tensors");
+    m->n_experts = n_experts, m->top_k = top_k, m->moe_ffn = moe_ffn;
+    return TSB_OK;
+}
+
+static int32_t upload(tsb_ctx* ctx, void** slot, const void* host, size_t bytes) {
+    if (!*slot) {
+        // spare bytes for the bulk-copy path's 16-byte granules, as for the dense matrices
+        int32_t rc = tsb_alloc(ctx, bytes + 256, slot);
+        if (rc) return rc;
+        cudaMemset((uint8_t*)*slot + bytes, 0, 256);
+    }
+    TSB_CUDA(ctx, cudaMemcpy(*slot, host, bytes, cudaMemcpyHostToDevice));
+    return TSB_OK;
+}
+
+int32_t tsb_model_set_router(tsb_model* m, int32_t layer, const void* q_u8, const void* scale_bf16, const void* bias_bf16) {
+    if (!m) return TSB_ERR_INVALID;
+    tsb_ctx* ctx = m->ctx;
+    TSB_REQUIRE(ctx, m->n_experts > 0, "the model has no experts (tsb_model_set_moe first)");
+    TSB_REQUIRE(ctx, layer >= 0 && layer < m->cfg.n_layers && q_u8 && scale_bf16 && bias_bf16, "bad layer or null data");
+    TSB_REQUIRE(ctx, m->cfg.d_model % 64 == 0, "d_model must be a multiple of the router's 64-column group");
+    DeviceGuard g(ctx);
+    LayerW& l = m->layers[layer];
+    l.moe_owned = true;
+    const size_t n = (size_t)m->n_experts * m->cfg.d_model;
+    int32_t rc;
+    if ((rc = upload(ctx, (void**)&l.router_q, q_u8, n)) || (rc = upload(ctx, (void**)&l.router_scale, scale_bf16, n / 64 * 2)) ||
+        (rc = upload(ctx, (void**)&l.router_bias, bias_bf16, n / 64 * 2)))
+        return rc;
+    return TSB_OK;
+}
+
+int32_t tsb_model_set_experts(tsb_model* m, int32_t layer, int32_t qtype, const void* gate_up_blocks, const void* down_blocks) {
+    if (!m) return TSB_ERR_INVALID;
+    tsb_ctx* ctx = m->ctx;
+    TSB_REQUIRE(ctx, m->n_experts > 0, "the model has no experts (tsb_model_set_moe first)");
+    TSB_REQUIRE(ctx, layer >= 0 && layer < m->cfg.n_layers && gate_up_blocks && down_blocks, "bad layer or null data");
+    TSB_REQUIRE(ctx, qtype >= TSB_Q4_K && qtype <= TSB_QTYPE_LAST, "unknown block format %d", qtype);
+    DeviceGuard g(ctx);
+    LayerW& l = m->layers[layer];
+    l.moe_owned = true;
+    l.experts_qtype = qtype;
+    const size_t gu = (size_t)m->n_experts * 2 * m->moe_ffn * tsb_row_bytes(qtype, m->cfg.d_model);
+    const size_t dn = (size_t)m->n_experts * m->cfg.d_model * tsb_row_bytes(qtype, m->moe_ffn);
+    int32_t rc;
+    if ((rc = upload(ctx, (void**)&l.experts_gate_up, gate_up_blocks, gu)) || (rc = upload(ctx, (void**)&l.experts_down, down_blocks, dn))) return rc;
+    return TSB_OK;
+}
+
 int32_t tsb_model_set_norm(tsb_model* m, int32_t layer, int32_t which, const void* host_bf16, int32_t n) {
     if (!m) return TSB_ERR_INVALID;
     tsb_ctx* ctx = m->ctx;
@@ -259,6 +317,8 @@ int32_t tsb_model_share(tsb_model* dst, int32_t dst_layer, const tsb_model* src,
     const LayerW& s = src->layers[src_layer];
     borrow(d.wqkv, s.wqkv), borrow(d.wv, s.wv), borrow(d.wo, s.wo), borrow(d.wgu, s.wgu), borrow(d.wdown, s.wdown);
     d.qkv_set = s.qkv_set;
+    d.router_q = s.router_q, d.router_scale = s.router_scale, d.router_bias = s.router_bias;
+    d.experts_gate_up = s.experts_gate_up, d.experts_down = s.experts_down, d.experts_qtype = s.experts_qtype, d.moe_owned = false;
     d.attn_norm = s.attn_norm, d.ffn_norm = s.ffn_norm, d.norms_owned = false;
     return TSB_OK;
 }
@@ -312,6 +372,11 @@ int64_t tsb_model_weight_bytes(const tsb_model* m) {
     if (!m) return 0;
     int64_t t = mat_bytes(m->lm_head);
     for (auto& l : m->layers) t += mat_bytes(l.wqkv) + mat_bytes(l.wv) + mat_bytes(l.wo) + mat_bytes(l.wgu) + mat_bytes(l.wdown);
+    if (m->n_experts > 0)  // every expert, although a pass reads only the routed ones
+        for (auto& l : m->layers)
+            t += (int64_t)m->n_experts * (2 * m->moe_ffn * tsb_row_bytes(l.experts_qtype, m->cfg.d_model) +
+                                          m->cfg.d_model * tsb_row_bytes(l.experts_qtype, m->moe_ffn)) +
+                 (int64_t)m->n_experts * m->cfg.d_model;
     return t;
 }
 
@@ -323,8 +388,12 @@ static int32_t model_complete(const tsb_model* m) {
     tsb_ctx* ctx = m->ctx;
     for (size_t i = 0; i < m->layers.size(); i++) {
         const LayerW& l = m->layers[i];
-        TSB_REQUIRE(ctx, l.wqkv.data && l.wo.data && l.wgu.data && l.wdown.data && l.attn_norm && l.ffn_norm,
-                    "layer %zu is missing a tensor", i);
+        if (m->n_experts > 0)
+            TSB_REQUIRE(ctx, l.wqkv.data && l.wo.data && l.attn_norm && l.ffn_norm && l.router_q && l.experts_gate_up && l.experts_down,
+                        "layer %zu is missing a tensor (attention, norms, router or experts)", i);
+        else
+            TSB_REQUIRE(ctx, l.wqkv.data && l.wo.data && l.wgu.data && l.wdown.data && l.attn_norm && l.ffn_norm,
+                        "layer %zu is missing a tensor", i);
         TSB_REQUIRE(ctx, l.qkv_set == 0 || l.qkv_set == 7, "layer %zu is missing one of q, k, v", i);
     }
     TSB_REQUIRE(ctx, m->embed.data && m->lm_head.data && m->out_norm, "embedding, head or final norm missing");
@@ -370,6 +439,17 @@ static int32_t runtime_init(tsb_session* s, ModelRt& rt, const tsb_model* model,
     cudaMemset(rt.attn_scratch, 0, rt.attn_scratch_bytes);  // the ticket words start at zero
     rt.fed.assign(n_streams, std::vector<int32_t>());
     // the many-row path: only when the session can hold that many rows and every matrix suits the kernel
+    if (model->n_experts > 0) {
+        // routed feed-forward: natural-layout rows around the router and the experts
+        if ((rc = A((size_t)R * c.d_model * 2, (void**)&rt.w_xn)) || (rc = A((size_t)R * qkv_dim * 2, (void**)&rt.w_qkv)) ||
+            (rc = A((size_t)R * c.d_model * 2, (void**)&rt.w_o)) || (rc = A((size_t)R * model->n_experts * sizeof(float), (void**)&rt.moe_logits)) ||
+            (rc = A((size_t)R * model->top_k * sizeof(int32_t), (void**)&rt.moe_ids)) || (rc = A((size_t)R * model->top_k * 2, (void**)&rt.moe_w)) ||
+            (rc = A((size_t)R * c.d_model * 2, (void**)&rt.moe_zero)) ||
+            (rc = A(moe_ffn_workspace_bytes(R, model->top_k, model->n_experts, c.d_model, model->moe_ffn), &rt.moe_ws)))
+            return rc;
+        cudaMemset(rt.moe_zero, 0, (size_t)R * c.d_model * 2);
+        return TSB_OK;
+    }
     bool wide = R >= WIDE_MIN_ROWS && gemm_wide_supported(model->lm_head.qtype, model->lm_head.rows, model->lm_head.cols, R);
     for (const LayerW& l : model->layers)
         wide = wide && !l.wv.data && gemm_wide_supported(l.wqkv.qtype, l.wqkv.rows, l.wqkv.cols, R) && gemm_wide_supported(l.wo.qtype, l.wo.rows, l.wo.cols, R) &&
@@ -446,12 +526,63 @@ static cudaError_t forward_device_wide(tsb_session* s, ModelRt& rt, const int32_
     return cudaSuccess;
 }
 
+// The pass of a model whose feed-forward is routed (crates/runtime/src/families/llama/mod.rs:205-291 with the
+// feed-forward of families/llama/moe.rs:36-221): unfused operators on natural-layout f16 rows with the reference's
+// rounding points; the routed sum is formed over a zero residual and added to the stream afterwards.
+static cudaError_t forward_device_moe(tsb_session* s, ModelRt& rt, const int32_t* tokens_dev, int token_stride,
+                                      const tsb_row_desc* rows_dev, int rows, int rows_per_seq, int max_len, __half* logits,
+                                      int64_t logits_stride, bool last_rows_only) {
+    tsb_ctx* ctx = s->ctx;
+    cudaStream_t st = s->stream;
+    const tsb_model* m = rt.model;
+    const tsb_model_config& c = m->cfg;
+    const float scale = 1.0f / sqrtf((float)c.head_dim);
+    const int64_t qd = (int64_t)c.n_q_heads * c.head_dim, kd = (int64_t)c.n_kv_heads * c.head_dim, qkv_dim = qd + 2 * kd;
+    const ActOut none{nullptr, nullptr}, out_d{rt.act_d.xp, rt.act_d.xs}, out_o{rt.act_o.xp, rt.act_o.xs};
+    const ActOperand in_d{rt.act_d.xp, rt.act_d.xs}, in_o{rt.act_o.xp, rt.act_o.xs};
+    cudaError_t e;
+#define FW(x)                           \
+    do {                                \
+        e = (x);                        \
+        if (e != cudaSuccess) return e; \
+    } while (0)
+    FW(launch_embed_rows(ctx, st, m->embed.qtype, m->embed.data, c.vocab, c.d_model, tokens_dev, token_stride, rows, rt.h, 1.0f));
+    FW(launch_rmsnorm_rows(ctx, st, rt.h, nullptr, m->layers[0].attn_norm, rt.w_xn, out_d, rows, c.d_model, c.rms_eps));
+    for (int L = 0; L < c.n_layers; L++) {
+        const LayerW& l = m->layers[L];
+        FW(launch_gemm_quant(ctx, st, l.wqkv.qtype, l.wqkv.data, l.wqkv.rows, l.wqkv.cols, in_d, rt.w_qkv, qkv_dim, rows, false));
+        if (l.wv.data) FW(launch_gemm_quant(ctx, st, l.wv.qtype, l.wv.data, l.wv.rows, l.wv.cols, in_d, rt.w_qkv + qd + kd, qkv_dim, rows, false));
+        FW(launch_rope_store_kv(ctx, st, rt.kv, L, rt.w_qkv, rows_dev, rows, c.n_q_heads, c.rope_theta));
+        FW(launch_attn_decode_rows(ctx, st, rt.kv, L, rt.w_qkv, qkv_dim, nullptr, out_o, rows_dev, rows, rows_per_seq, c.n_q_heads, scale,
+                                   max_len, rt.attn_scratch, s->n_streams * s->max_rows));
+        FW(launch_gemm_quant(ctx, st, l.wo.qtype, l.wo.data, l.wo.rows, l.wo.cols, in_o, rt.w_o, c.d_model, rows, false));
+        FW(launch_rmsnorm_rows(ctx, st, rt.h, rt.w_o, l.ffn_norm, rt.w_xn, none, rows, c.d_model, c.rms_eps));
+        FW(launch_router_logits(ctx, st, l.router_q, l.router_scale, l.router_bias, rt.w_xn, c.d_model, rows, m->n_experts, c.d_model, rt.moe_logits));
+        FW(launch_moe_route(ctx, st, rt.moe_logits, rows, m->n_experts, m->top_k, rt.moe_ids, rt.moe_w));
+        FW(launch_moe_ffn(ctx, st, l.experts_qtype, l.experts_gate_up, l.experts_down, m->n_experts, c.d_model, m->moe_ffn, rt.w_xn, c.d_model,
+                          rt.moe_zero, rt.moe_ids, rt.moe_w, rows, m->top_k, rt.w_o, rt.moe_ws));
+        const void* g = L + 1 < c.n_layers ? (const void*)m->layers[L + 1].attn_norm : (const void*)m->out_norm;
+        FW(launch_rmsnorm_rows(ctx, st, rt.h, rt.w_o, g, rt.w_xn, out_d, rows, c.d_model, c.rms_eps));
+    }
+    if (logits) {
+        EpiArgs a;
+        a.y = logits, a.y_stride = logits_stride, a.y_f32 = 0;
+        a.y_every = last_rows_only ? rows_per_seq : 0;
+        FW(launch_gemm_fused(ctx, st, m->lm_head.qtype, m->lm_head.data, m->lm_head.rows, m->lm_head.cols, in_d, rows, EPI_PLAIN, a));
+    }
+#undef FW
+    return cudaSuccess;
+}
+
 // One forward pass over `rows` rows (rows_per_seq per stream).  Row descriptors and token ids are
 // already on the device.  Cursors are not touched here.
 static cudaError_t forward_device(tsb_session* s, ModelRt& rt, const int32_t* tokens_dev, int token_stride,
                                   const tsb_row_desc* rows_dev, int rows, int rows_per_seq, int max_len, __half* logits,
                                   int64_t logits_stride, bool last_rows_only = false) {
     if (s->replay) return cudaSuccess;  // the captured graph already holds this work
+    if (rt.model->n_experts > 0)
+        return forward_device_moe(s, rt, tokens_dev, token_stride, rows_dev, rows, rows_per_seq, (max_len + 511) / 512 * 512, logits,
+                                  logits_stride, last_rows_only);
     if (rt.wide_ok && rows >= WIDE_MIN_ROWS)
         return forward_device_wide(s, rt, tokens_dev, token_stride, rows_dev, rows, rows_per_seq, (max_len + 511) / 512 * 512, logits,
                                    logits_stride, last_rows_only);

@@ -19,6 +19,13 @@ struct LayerW {
     uint16_t* attn_norm = nullptr;
     uint16_t* ffn_norm = nullptr;
     bool norms_owned = false;
+    // routed feed-forward (when the model has experts): 8-bit affine router [E, d] with bf16 scale / bias per
+    // 64 columns, expert matrices as verbatim block rows [E][2F, d] (gate then up) and [E][d, F]
+    uint8_t* router_q = nullptr;
+    uint16_t *router_scale = nullptr, *router_bias = nullptr;
+    uint8_t *experts_gate_up = nullptr, *experts_down = nullptr;
+    int experts_qtype = 0;
+    bool moe_owned = false;
 };
 
 struct tsb_model {
@@ -28,6 +35,7 @@ struct tsb_model {
     Mat embed, lm_head;
     uint16_t* out_norm = nullptr;
     bool out_norm_owned = false;
+    int n_experts = 0, top_k = 0, moe_ffn = 0;  // n_experts > 0: every layer's feed-forward is routed
 };
 
 struct ActBuf {
@@ -50,6 +58,11 @@ struct ModelRt {
     __half *w_xn = nullptr, *w_qkv = nullptr, *w_ao = nullptr, *w_o = nullptr, *w_gu = nullptr, *w_a = nullptr, *w_logits = nullptr;
     void* w_ws = nullptr;
     void* w_part = nullptr;  // split sums of the matmuls with few row tiles
+    // routed feed-forward: router logits [R, E] f32, picks [R, k], weights [R, k] f16, a zero residual, workspace
+    float* moe_logits = nullptr;
+    int32_t* moe_ids = nullptr;
+    __half *moe_w = nullptr, *moe_zero = nullptr;
+    void* moe_ws = nullptr;
     std::vector<std::vector<int32_t>> fed;  // per stream: tokens absorbed, by position (target only)
 };
 

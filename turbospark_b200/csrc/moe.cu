@@ -69,6 +69,35 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int n_experts
     }
 }
 
+// One warp per (token, expert): lane l takes columns 2l, 2l+1 of every 64-column group, as the reference's
+// kernel does (shaders/moe.metal:131-144), effective scale all ones.
+__global__ void router_logits_kernel(const uint8_t* __restrict__ q, const uint16_t* __restrict__ scale, const uint16_t* __restrict__ bias,
+                                     const __half* __restrict__ x, int64_t x_stride, int tokens, int n_experts, int d,
+                                     float* __restrict__ out) {
+    pdl_wait();
+    const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (w >= (int64_t)tokens * n_experts) return;
+    const int t = (int)(w / n_experts), e = (int)(w % n_experts);
+    const int groups = d / 64;
+    const uint8_t* qr = q + (size_t)e * d;
+    const __half* xr = x + (size_t)t * x_stride;
+    float acc = 0.f;
+    for (int g = 0; g < groups; g++) {
+        const float s = __uint_as_float((uint32_t)scale[(size_t)e * groups + g] << 16);
+        const float b = __uint_as_float((uint32_t)bias[(size_t)e * groups + g] << 16);
+        const int idx = g * 64 + lane * 2;
+        const float q0 = (float)qr[idx], q1 = (float)qr[idx + 1];
+        const float x0 = __half2float(xr[idx]), x1 = __half2float(xr[idx + 1]);
+        acc = __fmaf_rn(s, __fadd_rn(__fmul_rn(q0, x0), __fmul_rn(q1, x1)), acc);
+        acc = __fmaf_rn(b, __fadd_rn(x0, x1), acc);
+    }
+    // the lanes in index order, as the CPU restatement adds them
+    float total = 0.f;
+    for (int l = 0; l < 32; l++) total = __fadd_rn(total, __shfl_sync(0xffffffffu, acc, l));
+    if (lane == 0) out[w] = total;
+}
+
 // y[t][d] = half(float(residual[t][d]) + sum_s float(w[t][s]) * values[t*k+s][d]), slots in order.
 __global__ void moe_combine_kernel(const __half* __restrict__ residual, const float* __restrict__ values,
                                    const __half* __restrict__ weights, int k, int d_model, int tokens, __half* __restrict__ y) {
@@ -151,6 +180,20 @@ MoeLayout moe_layout(int tokens, int k, int n_experts, int d_model, int ffn) {
 
 }  // namespace
 
+cudaError_t launch_router_logits(tsb_ctx* ctx, cudaStream_t st, const uint8_t* q, const uint16_t* scale, const uint16_t* bias,
+                                 const __half* x, int64_t x_stride, int tokens, int n_experts, int d, float* out) {
+    const int64_t warps = (int64_t)tokens * n_experts;
+    return tsb_launch(ctx, router_logits_kernel, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0, st, true, q, scale, bias, x, x_stride,
+                      tokens, n_experts, d, out);
+}
+
+cudaError_t launch_moe_route(tsb_ctx* ctx, cudaStream_t st, const float* logits, int tokens, int n_experts, int k, int32_t* ids,
+                             __half* weights) {
+    const int wpb = 4;
+    return tsb_launch(ctx, moe_route_kernel, dim3((unsigned)((tokens + wpb - 1) / wpb)), dim3(wpb * 32), 0, st, true, logits, n_experts, k,
+                      (const float*)nullptr, ids, weights, tokens, ctx->dev_error);
+}
+
 size_t moe_ffn_workspace_bytes(int tokens, int k, int n_experts, int d_model, int ffn) {
     return moe_layout(tokens, k, n_experts, d_model, ffn).total;
 }
@@ -206,6 +249,17 @@ int32_t tsb_moe_route(tsb_ctx* ctx, tsb_stream s, const float* router_logits_f32
     TSB_CUDA(ctx, tsb_launch(ctx, moe_route_kernel, dim3((unsigned)((tokens + wpb - 1) / wpb)), dim3(wpb * 32), 0, (cudaStream_t)s,
                              true, router_logits_f32, (int)n_experts, (int)k, per_expert_scale, ids_out,
                              (__half*)weights_f16_out, (int)tokens, ctx->dev_error));
+    return TSB_OK;
+}
+
+int32_t tsb_router_logits(tsb_ctx* ctx, tsb_stream s, const void* q_u8, const void* scale_bf16, const void* bias_bf16,
+                          const void* x_f16, int32_t tokens, int32_t n_experts, int32_t d_model, float* logits_out) {
+    if (!ctx) return TSB_ERR_INVALID;
+    TSB_REQUIRE(ctx, q_u8 && scale_bf16 && bias_bf16 && x_f16 && logits_out, "null buffer");
+    TSB_REQUIRE(ctx, tokens > 0 && n_experts > 0 && d_model > 0 && d_model % 64 == 0, "d_model must be a multiple of the 64-column group");
+    DeviceGuard g(ctx);
+    TSB_CUDA(ctx, launch_router_logits(ctx, (cudaStream_t)s, (const uint8_t*)q_u8, (const uint16_t*)scale_bf16, (const uint16_t*)bias_bf16,
+                                       (const __half*)x_f16, d_model, tokens, n_experts, d_model, logits_out));
     return TSB_OK;
 }
 

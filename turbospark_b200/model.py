@@ -76,6 +76,23 @@ class Model:
         self.ctx.check(lib().tsb_model_set_norm(self.h, C.c_int32(layer), C.c_int32(which),
                                                 bf16.ctypes.data_as(C.c_void_p), C.c_int32(bf16.size)))
 
+    def set_moe(self, n_experts, top_k, moe_ffn):
+        """Every layer's feed-forward becomes routed; call before uploading tensors."""
+        self.n_experts, self.top_k, self.moe_ffn = n_experts, top_k, moe_ffn
+        self.ctx.check(lib().tsb_model_set_moe(self.h, C.c_int32(n_experts), C.c_int32(top_k), C.c_int32(moe_ffn)))
+
+    def set_router(self, layer, q_u8, scale_bf16, bias_bf16):
+        q = np.ascontiguousarray(q_u8, dtype=np.uint8)
+        sc, bi = np.ascontiguousarray(scale_bf16, dtype=np.uint16), np.ascontiguousarray(bias_bf16, dtype=np.uint16)
+        assert q.size == self.n_experts * self.cfg.d_model and sc.size == q.size // 64 == bi.size
+        self.ctx.check(lib().tsb_model_set_router(self.h, C.c_int32(layer), q.ctypes.data_as(C.c_void_p),
+                                                  sc.ctypes.data_as(C.c_void_p), bi.ctypes.data_as(C.c_void_p)))
+
+    def set_experts(self, layer, qtype, gate_up, down):
+        gu, dn = np.ascontiguousarray(gate_up, dtype=np.uint8), np.ascontiguousarray(down, dtype=np.uint8)
+        self.ctx.check(lib().tsb_model_set_experts(self.h, C.c_int32(layer), C.c_int32(qtype), gu.ctypes.data_as(C.c_void_p),
+                                                   dn.ctypes.data_as(C.c_void_p)))
+
     def share(self, dst_layer, src, src_layer):
         self.ctx.check(lib().tsb_model_share(self.h, C.c_int32(dst_layer), src.h, C.c_int32(src_layer)))
 
@@ -263,7 +280,10 @@ def random_weights(cfg, seed, oracle, qtype=capi.Q4_K, std=0.02, real_ffn=None, 
     return mats, norms
 
 
-def load_weights(model, mats, norms, qtype=None, layers=None, order=None):
+DENSE_FFN = (W_GATE, W_UP, W_DOWN)
+
+
+def load_weights(model, mats, norms, qtype=None, layers=None, order=None, skip=()):
     """Push a random_weights() set into a tsb Model or an oracle Model (same builder interface).  Each matrix goes
     up in the format it was quantized in (`qtype` overrides it); `order` lists tensor kinds to upload first."""
     n_layers = model.cfg.n_layers if layers is None else layers
@@ -271,10 +291,34 @@ def load_weights(model, mats, norms, qtype=None, layers=None, order=None):
     keys = sorted(mats, key=lambda k: first.index(k[1]) if k[1] in first else len(first))  # stable: the rest keep their order
     for (l, which) in keys:
         blocks, rows, cols, qt = mats[(l, which)]
-        if l >= n_layers:
+        if l >= n_layers or which in skip:
             continue
         model.set_matrix(max(l, 0), which, qt if qtype is None else qtype, blocks, rows, cols)
     for (l, which), bits in norms.items():
         if l >= n_layers:
             continue
         model.set_norm(max(l, 0), which, bits)
+
+
+def random_moe_weights(cfg, n_experts, moe_ffn, seed, oracle, qtype=capi.MXFP4, std=0.05):
+    """Seeded routers (8-bit affine: u8 [E, d], bf16 scale and bias per 64 columns) and experts (block rows, per
+    expert gate then up [2F, d], and down [d, F]) for every layer: {layer: (q, scale, bias, gate_up, down)}."""
+    rng = np.random.default_rng(seed)
+    d = cfg.d_model
+    bf16 = np.vectorize(lambda v: oracle.lib().tso_f32_to_bf16(float(v)), otypes=[np.uint16])
+    out = {}
+    for l in range(cfg.n_layers):
+        q = rng.integers(0, 256, size=(n_experts, d), dtype=np.uint8)
+        sc = bf16(0.004 * (0.5 + rng.random((n_experts, d // 64))))
+        bi = bf16(-0.5 * (0.5 + rng.random((n_experts, d // 64))))   # about -128 * scale: zero-mean weights
+        gu = np.concatenate([oracle.quantize(qtype, (rng.standard_normal((2 * moe_ffn, d)) * std).astype(np.float32)) for _ in range(n_experts)])
+        dn = np.concatenate([oracle.quantize(qtype, (rng.standard_normal((d, moe_ffn)) * std).astype(np.float32)) for _ in range(n_experts)])
+        out[l] = (q, sc, bi, gu, dn)
+    return out
+
+
+def load_moe_weights(model, moe, qtype=capi.MXFP4):
+    """Push a random_moe_weights() set into a tsb Model or an oracle Model (set_moe must have been called)."""
+    for l, (q, sc, bi, gu, dn) in moe.items():
+        model.set_router(l, q, sc, bi)
+        model.set_experts(l, qtype, gu, dn)
