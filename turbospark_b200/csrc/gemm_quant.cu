@@ -260,50 +260,57 @@ __device__ __forceinline__ float mxfp4_scale_dev(uint32_t e) {
     return __uint_as_float(e < 2 ? (0x00200000u << e) : ((e - 1u) << 23));
 }
 
+// e2m1 code n = s e1 e0 m  ->  f16 bits (n & 7) << 9 | (n & 8) << 12: exponent field e1e0, top mantissa bit m.  That
+// f16 is the e2m1 value times 2^-14 exactly (a subnormal for the codes below 1.0); the fp32 partial sum is scaled by
+// 2^15 before the block scale (crates/compute/src/quant_gguf_mxfp4.rs:76-78: the table holds 2 * e2m1).
+// v carries four codes in the low nibbles of its bytes (the high nibbles are ignored): elements (0,2) and (1,3).
+__device__ __forceinline__ void e2m1_pairs(uint32_t v, uint32_t& p02, uint32_t& p13) {
+    constexpr uint32_t M = 0x0E000E00u, S = 0x80008000u;
+    p02 = lop3_and_or(v << 9, M, (v << 12) & S);
+    p13 = lop3_and_or(v << 1, M, (v << 4) & S);
+}
+
+// One 256-column unit = eight 17-byte blocks.  One mma must stay inside one block, because the block scale
+// multiplies its fp32 sum: lane tig takes code bytes 4tig..4tig+3 of every block (elements 4tig..4tig+3 from the low
+// nibbles, 16+4tig.. from the high ones), whose activations are the halves (tig & 1) of two adjacent uint4 slots of
+// the operand; with b unrolled every offset is an immediate: uint4 index ((b/4)*4 + (b&1))*32 + ((b/2)&1)*2 past
+// the lane's base.  Rows start on a 4-byte boundary (checked where the weights come in) and a unit is 136 bytes, so
+// the lane's code word of block b, bytes 17b + 1 + 4tig .. +3, is a funnel shift by an immediate over two aligned words.
 template <int NT>
 __device__ __forceinline__ void mxfp4_unit(const uint8_t* rA, const uint8_t* rB, const ActOperand& act, int nblk,
                                            int unit, int gid, int tig, float (&acc)[NT][4]) {
-#pragma unroll 2
+    const uint2* xb[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+        xb[nt] = reinterpret_cast<const uint2*>(act.xp + ((size_t)nt * nblk + unit) * 256 + (tig >> 1) * 64 + gid * 4) + (tig & 1);
+    const uint32_t* wA = reinterpret_cast<const uint32_t*>(rA) + tig;
+    const uint32_t* wB = reinterpret_cast<const uint32_t*>(rB) + tig;
+#pragma unroll
     for (int b = 0; b < 8; b++) {
-        const uint8_t* pA = rA + b * 17;
-        const uint8_t* pB = rB + b * 17;
-        const float sA = mxfp4_scale_dev(pA[0]);
-        const float sB = mxfp4_scale_dev(pB[0]);
-        const uint32_t wA = lds_u32_unaligned(pA + 1 + 4 * tig);
-        const uint32_t wB = lds_u32_unaligned(pB + 1 + 4 * tig);
-        uint32_t cA[4], cB[4];
-        cvt_e2m1x4(wA, cA);
-        cvt_e2m1x4(wB, cB);
-        // byte i of the word is element 4tig+i (low) and 16+4tig+i (high); the
-        // swizzled activation row stores (x0,x2),(x1,x3), so pair bytes (0,2),(1,3).
+        const int o = 17 * b + 1;  // byte offset of the block's code bytes in the row
+        const float scA = mxfp4_scale_dev(rA[o - 1]), scB = mxfp4_scale_dev(rB[o - 1]);
+        uint32_t cwA = wA[o >> 2], cwB = wB[o >> 2];
+        if ((o & 3) != 0) {
+            cwA = __funnelshift_r(cwA, wA[(o >> 2) + 1], (o & 3) * 8);
+            cwB = __funnelshift_r(cwB, wB[(o >> 2) + 1], (o & 3) * 8);
+        }
         uint32_t alo[4], ahi[4];
-        alo[0] = __byte_perm(cA[0], cA[2], 0x5410);
-        alo[1] = __byte_perm(cB[0], cB[2], 0x5410);
-        alo[2] = __byte_perm(cA[1], cA[3], 0x5410);
-        alo[3] = __byte_perm(cB[1], cB[3], 0x5410);
-        ahi[0] = __byte_perm(cA[0], cA[2], 0x7632);
-        ahi[1] = __byte_perm(cB[0], cB[2], 0x7632);
-        ahi[2] = __byte_perm(cA[1], cA[3], 0x7632);
-        ahi[3] = __byte_perm(cB[1], cB[3], 0x7632);
-        const int k0 = unit * 256 + b * 32 + 4 * tig;
+        e2m1_pairs(cwA, alo[0], alo[2]);
+        e2m1_pairs(cwB, alo[1], alo[3]);
+        e2m1_pairs(cwA >> 4, ahi[0], ahi[2]);
+        e2m1_pairs(cwB >> 4, ahi[1], ahi[3]);
+        const int u4 = (((b >> 2) * 4 + (b & 1)) * 32 + ((b >> 1) & 1) * 2) * 2;  // in uint2 units
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
-            const int token = nt * 8 + gid;
-            float c[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t bl[2], bh[2];
-            {
-                const __half* xh16 = reinterpret_cast<const __half*>(act.xp);
-                const uint2 l = __ldg(reinterpret_cast<const uint2*>(xh16 + act_xp_half_index(token, k0, nblk)));
-                const uint2 hh = __ldg(reinterpret_cast<const uint2*>(xh16 + act_xp_half_index(token, k0 + 16, nblk)));
-                bl[0] = l.x, bl[1] = l.y, bh[0] = hh.x, bh[1] = hh.y;
-            }
-            mma_16816(c, alo, bl);
+            const uint2 l = __ldg(xb[nt] + u4), hh = __ldg(xb[nt] + u4 + 2);
+            const uint32_t bl[2] = {l.x, l.y}, bh[2] = {hh.x, hh.y};
+            float c[4];
+            mma_16816_first(c, alo, bl);
             mma_16816(c, ahi, bh);
-            // the hardware conversion yields e2m1 = LUT / 2, so the sum is doubled (exactly)
-            acc[nt][0] += sA * (c[0] + c[0]);
-            acc[nt][1] += sA * (c[1] + c[1]);
-            acc[nt][2] += sB * (c[2] + c[2]);
-            acc[nt][3] += sB * (c[3] + c[3]);
+            acc[nt][0] += scA * (c[0] * 32768.f);
+            acc[nt][1] += scA * (c[1] * 32768.f);
+            acc[nt][2] += scB * (c[2] * 32768.f);
+            acc[nt][3] += scB * (c[3] * 32768.f);
         }
     }
 }
@@ -697,12 +704,15 @@ __device__ __forceinline__ void run_epilogue(const EpiArgs& e, const Group& gr, 
 // (matrix m, row group g); matrix m sits at W + m * w_stride, multiplies count[m] token rows whose operand tiles
 // start at tile tile_start[m] of `act`, and its outputs are indexed from token tile_start[m] * 8.  A launch covers
 // token rows [chunk0, chunk0 + 8 NT) of every matrix; matrices with fewer rows are skipped.  Producer and consumers
-// read the same counts, so they skip the same items and the stage ring stays in step.
+// walk the same compacted list, so the stage ring stays in step.  The token-tile width of a
+// launch is fixed (8 NT): `tokens` is recomputed per matrix as min(8 NT, count - chunk0).
+constexpr int GROUPED_MAX_MATS = 512;
 struct GroupedArgs {
     const int32_t* count = nullptr;
     const int32_t* tile_start = nullptr;
     int n_mats = 0;
     int chunk0 = 0;
+    int lo = 0, hi = 0x7fffffff;  // only matrices with lo < count <= hi take part in this launch
     int64_t w_stride = 0;
 };
 
@@ -726,7 +736,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = (int)((rows + TILE_ROWS - 1) / TILE_ROWS);
     const int n_groups = num_groups<EPI>(n_tiles, epi);
-    const int n_items = GROUPED ? n_groups * grp.n_mats : n_groups;
     const int iters = (units + STAGE_UNITS - 1) / STAGE_UNITS;  // stages per row tile
     const int64_t row_bytes = (int64_t)units * UB;
 
@@ -737,7 +746,29 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
         }
         mbar_fence_init();
     }
+    // GROUPED: the matrices that take part in this launch, compacted once per CTA (index, row count, first tile), so
+    // the item walk touches no global memory and the items spread evenly over the CTAs
+    __shared__ int grp_mat[GROUPED ? GROUPED_MAX_MATS : 1], grp_cnt[GROUPED ? GROUPED_MAX_MATS : 1], grp_tile[GROUPED ? GROUPED_MAX_MATS : 1];
+    __shared__ int grp_active;
+    if constexpr (GROUPED) {
+        if (warp == 0) {
+            int base = 0;
+            for (int c = 0; c < grp.n_mats; c += 32) {
+                const int mt = c + lane;
+                const int cnt = mt < grp.n_mats ? grp.count[mt] : 0;
+                const bool on = cnt > grp.lo && cnt <= grp.hi && cnt > grp.chunk0;
+                const uint32_t mask = __ballot_sync(0xffffffffu, on);
+                if (on) {
+                    const int at = base + __popc(mask & ((1u << lane) - 1u));
+                    grp_mat[at] = mt, grp_cnt[at] = cnt, grp_tile[at] = grp.tile_start[mt];
+                }
+                base += __popc(mask);
+            }
+            if (lane == 0) grp_active = base;
+        }
+    }
     __syncthreads();
+    const int n_items = GROUPED ? n_groups * grp_active : n_groups;
 
     // The CTA is persistent: it walks groups blockIdx.x, +gridDim.x, ... and the stage ring runs on across
     // tile boundaries, so weight bytes stay in flight while the consumers reduce and store a finished tile.
@@ -750,10 +781,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
             int g = item;
             const uint8_t* W = W0;
             if constexpr (GROUPED) {
-                const int mat = item / n_groups;
-                g = item - mat * n_groups;
-                if (grp.count[mat] <= grp.chunk0) continue;
-                W = W0 + (int64_t)mat * grp.w_stride;
+                const int a = item / n_groups;
+                g = item - a * n_groups;
+                W = W0 + (int64_t)grp_mat[a] * grp.w_stride;
             }
             const Group gr = group_of<EPI>(g, n_tiles, epi);
             for (int ti = 0; ti < gr.n; ti++) {
@@ -832,12 +862,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
         int g = item;
         const uint8_t* W = W0;
         if constexpr (GROUPED) {
-            const int mat = item / n_groups;
-            g = item - mat * n_groups;
-            const int cnt = grp.count[mat];
-            if (cnt <= grp.chunk0) continue;
-            W = W0 + (int64_t)mat * grp.w_stride;
-            const int tile0 = grp.tile_start[mat] + grp.chunk0 / 8;
+            const int a = item / n_groups;
+            g = item - a * n_groups;
+            const int cnt = grp_cnt[a];
+            W = W0 + (int64_t)grp_mat[a] * grp.w_stride;
+            const int tile0 = grp_tile[a] + grp.chunk0 / 8;
             tokens = min(NT * 8, cnt - grp.chunk0);
             tok0 = tile0 * 8;
             act.xp = act0.xp + (size_t)tile0 * units * 256;
@@ -940,13 +969,24 @@ cudaError_t launch_one(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t 
     return tsb_launch(ctx, kern, grid, dim3(GEMM_THREADS), smem, st, true, w, rows, units, act, tokens, tok0, args, ctx->dev_error, grp);
 }
 
+// The matrices are binned by their row count, one launch per bin with the token-tile width that fits it: a matrix
+// with three rows is not run through the 64-column variant because another one has forty.
 template <int QT, int EPI>
-cudaError_t launch_grouped_nt(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t rows, int units, ActOperand act, int tokens,
-                              const EpiArgs& args, const GroupedArgs& grp) {
-    if (tokens <= 8) return launch_one<QT, 1, EPI, true>(ctx, st, w, rows, units, act, tokens, 0, args, grp);
-    if (tokens <= 16) return launch_one<QT, 2, EPI, true>(ctx, st, w, rows, units, act, tokens, 0, args, grp);
-    if (tokens <= 32) return launch_one<QT, 4, EPI, true>(ctx, st, w, rows, units, act, tokens, 0, args, grp);
-    return launch_one<QT, 8, EPI, true>(ctx, st, w, rows, units, act, tokens, 0, args, grp);
+cudaError_t launch_grouped_nt(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t rows, int units, ActOperand act, int max_tokens,
+                              const EpiArgs& args, GroupedArgs grp) {
+    cudaError_t e;
+    grp.chunk0 = 0, grp.lo = 0, grp.hi = 8;
+    if ((e = launch_one<QT, 1, EPI, true>(ctx, st, w, rows, units, act, 8, 0, args, grp)) != cudaSuccess || max_tokens <= 8) return e;
+    grp.lo = 8, grp.hi = 16;
+    if ((e = launch_one<QT, 2, EPI, true>(ctx, st, w, rows, units, act, 16, 0, args, grp)) != cudaSuccess || max_tokens <= 16) return e;
+    grp.lo = 16, grp.hi = 32;
+    if ((e = launch_one<QT, 4, EPI, true>(ctx, st, w, rows, units, act, 32, 0, args, grp)) != cudaSuccess || max_tokens <= 32) return e;
+    grp.lo = 32, grp.hi = 0x7fffffff;
+    for (int t0 = 0; t0 < max_tokens; t0 += 64) {
+        grp.chunk0 = t0;
+        if ((e = launch_one<QT, 8, EPI, true>(ctx, st, w, rows, units, act, 64, 0, args, grp)) != cudaSuccess) return e;
+    }
+    return cudaSuccess;
 }
 
 template <int QT>
@@ -1049,22 +1089,16 @@ cudaError_t launch_gemm_grouped(tsb_ctx* ctx, cudaStream_t st, int qtype, const 
                                 int64_t rows, int64_t cols, ActOperand act, const int32_t* count, const int32_t* tile_start,
                                 int max_tokens, int epi, const EpiArgs& args) {
     const int units = (int)(cols / 256);
-    for (int t0 = 0; t0 < max_tokens; t0 += 64) {
-        GroupedArgs grp;
-        grp.count = count, grp.tile_start = tile_start, grp.n_mats = n_mats, grp.chunk0 = t0, grp.w_stride = w_stride;
-        const int nt = min(64, max_tokens - t0);
-        cudaError_t e;
-        switch (qtype) {
-            case TSB_Q4_K: e = launch_grouped_epi<TSB_Q4_K>(ctx, st, w, rows, units, act, nt, epi, args, grp); break;
-            case TSB_Q6_K: e = launch_grouped_epi<TSB_Q6_K>(ctx, st, w, rows, units, act, nt, epi, args, grp); break;
-            case TSB_MXFP4: e = launch_grouped_epi<TSB_MXFP4>(ctx, st, w, rows, units, act, nt, epi, args, grp); break;
-            case TSB_Q5_K: e = launch_grouped_epi<TSB_Q5_K>(ctx, st, w, rows, units, act, nt, epi, args, grp); break;
-            case TSB_Q8_0: e = launch_grouped_epi<TSB_Q8_0>(ctx, st, w, rows, units, act, nt, epi, args, grp); break;
-            default: return cudaErrorInvalidValue;
-        }
-        if (e != cudaSuccess) return e;
+    GroupedArgs grp;
+    grp.count = count, grp.tile_start = tile_start, grp.n_mats = n_mats, grp.w_stride = w_stride;
+    switch (qtype) {
+        case TSB_Q4_K: return launch_grouped_epi<TSB_Q4_K>(ctx, st, w, rows, units, act, max_tokens, epi, args, grp);
+        case TSB_Q6_K: return launch_grouped_epi<TSB_Q6_K>(ctx, st, w, rows, units, act, max_tokens, epi, args, grp);
+        case TSB_MXFP4: return launch_grouped_epi<TSB_MXFP4>(ctx, st, w, rows, units, act, max_tokens, epi, args, grp);
+        case TSB_Q5_K: return launch_grouped_epi<TSB_Q5_K>(ctx, st, w, rows, units, act, max_tokens, epi, args, grp);
+        case TSB_Q8_0: return launch_grouped_epi<TSB_Q8_0>(ctx, st, w, rows, units, act, max_tokens, epi, args, grp);
+        default: return cudaErrorInvalidValue;
     }
-    return cudaSuccess;
 }
 
 cudaError_t launch_gemm_quant(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* w, int64_t rows, int64_t cols,
@@ -1089,6 +1123,8 @@ int32_t tsb_gemm_quant(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* re
     TSB_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(x_f16) & 15u) == 0, "x must be 16-byte aligned");
     if (qtype == TSB_Q4_K || qtype == TSB_Q5_K || qtype == TSB_Q8_0)  // formats whose 256-column units are 16-byte multiples
         TSB_REQUIRE(ctx, ((reinterpret_cast<uintptr_t>(region) + w_off) & 15u) == 0, "rows of this format must start on a 16-byte boundary");
+    if (qtype == TSB_MXFP4)  // the resident file aligns every tensor to 4 bytes (crates/repack/src/resident_writer.rs:401-405)
+        TSB_REQUIRE(ctx, ((reinterpret_cast<uintptr_t>(region) + w_off) & 3u) == 0, "MXFP4 rows must start on a 4-byte boundary");
     DeviceGuard g(ctx);
     cudaStream_t st = (cudaStream_t)s;
     {

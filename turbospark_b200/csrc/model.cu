@@ -355,8 +355,36 @@ int32_t tsb_model_fill_synthetic(tsb_model* m, int32_t qtype, int32_t lm_head_qt
     for (auto& l : m->layers) {
         if ((rc = fill(l.wqkv, qtype, qd + 2 * kd, c.d_model))) return rc;
         if ((rc = fill(l.wo, qtype, c.d_model, qd))) return rc;
-        if ((rc = fill(l.wgu, qtype, 2 * (int64_t)c.ffn, c.d_model))) return rc;
-        if ((rc = fill(l.wdown, qtype, c.d_model, c.ffn))) return rc;
+        if (m->n_experts > 0) {
+            // routed layers: random 8-bit router with scale 0.004 / bias -0.5 (zero-mean weights), experts as blocks
+            const size_t rn = (size_t)m->n_experts * c.d_model, rg = rn / 64;
+            const int64_t gu_b = (int64_t)m->n_experts * 2 * m->moe_ffn * tsb_row_bytes(qtype, c.d_model);
+            const int64_t dn_b = (int64_t)m->n_experts * c.d_model * tsb_row_bytes(qtype, m->moe_ffn);
+            l.moe_owned = true, l.experts_qtype = qtype;
+            void* p;
+            if (!l.router_q) {
+                if ((rc = tsb_alloc(ctx, rn + 256, &p))) return rc;
+                l.router_q = (uint8_t*)p;
+                if ((rc = tsb_alloc(ctx, rg * 2, &p))) return rc;
+                l.router_scale = (uint16_t*)p;
+                if ((rc = tsb_alloc(ctx, rg * 2, &p))) return rc;
+                l.router_bias = (uint16_t*)p;
+                if ((rc = tsb_alloc(ctx, (size_t)gu_b + 256, &p))) return rc;
+                l.experts_gate_up = (uint8_t*)p;
+                if ((rc = tsb_alloc(ctx, (size_t)dn_b + 256, &p))) return rc;
+                l.experts_down = (uint8_t*)p;
+                cudaMemset(l.experts_gate_up + gu_b, 0, 256), cudaMemset(l.experts_down + dn_b, 0, 256);
+            }
+            fill_blocks_kernel<<<64, 256>>>(l.router_q, (int64_t)(rn / 17), TSB_MXFP4, sd);  // any bytes do for the 8-bit weights
+            fill_u16_kernel<<<32, 256>>>(l.router_scale, (int64_t)rg, (uint16_t)0x3B83);      // bf16 0.004
+            fill_u16_kernel<<<32, 256>>>(l.router_bias, (int64_t)rg, (uint16_t)0xBF00);       // bf16 -0.5
+            fill_blocks_kernel<<<1024, 256>>>(l.experts_gate_up, gu_b / block_bytes_of(qtype), qtype, sd + 1);
+            fill_blocks_kernel<<<1024, 256>>>(l.experts_down, dn_b / block_bytes_of(qtype), qtype, sd + 2);
+            sd = sd * 1664525u + 1013904223u;
+        } else {
+            if ((rc = fill(l.wgu, qtype, 2 * (int64_t)c.ffn, c.d_model))) return rc;
+            if ((rc = fill(l.wdown, qtype, c.d_model, c.ffn))) return rc;
+        }
         l.norms_owned = true;
         if ((rc = ones(&l.attn_norm)) || (rc = ones(&l.ffn_norm))) return rc;
     }

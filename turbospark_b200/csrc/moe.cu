@@ -22,23 +22,28 @@ constexpr int MOE_MAX_EXPERTS = 512;
 
 namespace {
 
-// One warp per token: k rounds of arg-max over the logits (ties to the lower index), then the softmax over the picks.
-__global__ void moe_route_kernel(const float* __restrict__ logits, int n_experts, int k, const float* __restrict__ scale,
-                                 int32_t* __restrict__ ids, __half* __restrict__ weights, int tokens, uint32_t* __restrict__ err) {
-    pdl_wait();
-    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (t >= tokens) return;
-    const float* row = logits + (size_t)t * n_experts;
+constexpr int ROUTER_MAX_EXPERTS = 512;
+
+// One warp routes one token: k rounds of arg-max over the logits (ties to the lower index), then the softmax over
+// the picks.  `row` may live in shared or global memory.
+__device__ __forceinline__ void route_row(const float* row, int n_experts, int k, const float* __restrict__ scale,
+                                          int32_t* __restrict__ ids, __half* __restrict__ weights, int lane, uint32_t* __restrict__ err) {
     int picked[8];
     float pv[8];
+    float held[ROUTER_MAX_EXPERTS / 32];  // this lane's logits, read once
+#pragma unroll
+    for (int i = 0; i < ROUTER_MAX_EXPERTS / 32; i++) held[i] = lane + 32 * i < n_experts ? row[lane + 32 * i] : 0.f;
     for (int r = 0; r < k; r++) {
         float best = 0.f;
         int bi = 0x7fffffff;
-        for (int e = lane; e < n_experts; e += 32) {
+#pragma unroll
+        for (int i = 0; i < ROUTER_MAX_EXPERTS / 32; i++) {
+            const int e = lane + 32 * i;
+            if (e >= n_experts) continue;
             bool taken = false;
             for (int c = 0; c < r; c++) taken |= picked[c] == e;
             if (taken) continue;
-            const float v = row[e];
+            const float v = held[i];
             // total order of f32::total_cmp on the values a router emits (finite): larger first, then lower index
             if (bi == 0x7fffffff || v > best || (v == best && e < bi)) best = v, bi = e;
         }
@@ -63,14 +68,42 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int n_experts
         for (int r = 0; r < k; r++) {
             const int e = bad ? 0 : picked[r];
             const float sc = scale ? scale[e] : 1.0f;
-            ids[(size_t)t * k + r] = e;
-            weights[(size_t)t * k + r] = __float2half_rn(__fmul_rn(__fdiv_rn(ex[r], sum), sc));
+            ids[r] = e;
+            weights[r] = __float2half_rn(__fmul_rn(__fdiv_rn(ex[r], sum), sc));
         }
     }
 }
 
-// One warp per (token, expert): lane l takes columns 2l, 2l+1 of every 64-column group, as the reference's
-// kernel does (shaders/moe.metal:131-144), effective scale all ones.
+__global__ void moe_route_kernel(const float* __restrict__ logits, int n_experts, int k, const float* __restrict__ scale,
+                                 int32_t* __restrict__ ids, __half* __restrict__ weights, int tokens, uint32_t* __restrict__ err) {
+    pdl_wait();
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= tokens) return;
+    route_row(logits + (size_t)t * n_experts, n_experts, k, scale, ids + (size_t)t * k, weights + (size_t)t * k, lane, err);
+}
+
+// One (token, expert) router logit by one warp: lane l takes columns 2l, 2l+1 of every 64-column group, as the
+// reference's kernel does (shaders/moe.metal:131-144), effective scale all ones; the lanes are then added as a
+// butterfly (partners 16, 8, 4, 2, 1 apart), which is also how the CPU restatement adds them.
+__device__ __forceinline__ float router_logit(const uint8_t* __restrict__ qr, const uint16_t* __restrict__ sr, const uint16_t* __restrict__ br,
+                                              const __half* __restrict__ xr, int groups, int lane) {
+    float acc = 0.f;
+#pragma unroll 8
+    for (int g = 0; g < groups; g++) {
+        const float s = __uint_as_float((uint32_t)sr[g] << 16);
+        const float b = __uint_as_float((uint32_t)br[g] << 16);
+        const int idx = g * 64 + lane * 2;
+        const uint32_t qq = *reinterpret_cast<const uint16_t*>(qr + idx);
+        const float2 xx = __half22float2(*reinterpret_cast<const __half2*>(xr + idx));
+        const float q0 = (float)(qq & 0xFFu), q1 = (float)(qq >> 8);
+        acc = __fmaf_rn(s, __fadd_rn(__fmul_rn(q0, xx.x), __fmul_rn(q1, xx.y)), acc);
+        acc = __fmaf_rn(b, __fadd_rn(xx.x, xx.y), acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
+    return acc;
+}
+
 __global__ void router_logits_kernel(const uint8_t* __restrict__ q, const uint16_t* __restrict__ scale, const uint16_t* __restrict__ bias,
                                      const __half* __restrict__ x, int64_t x_stride, int tokens, int n_experts, int d,
                                      float* __restrict__ out) {
@@ -80,21 +113,7 @@ __global__ void router_logits_kernel(const uint8_t* __restrict__ q, const uint16
     if (w >= (int64_t)tokens * n_experts) return;
     const int t = (int)(w / n_experts), e = (int)(w % n_experts);
     const int groups = d / 64;
-    const uint8_t* qr = q + (size_t)e * d;
-    const __half* xr = x + (size_t)t * x_stride;
-    float acc = 0.f;
-    for (int g = 0; g < groups; g++) {
-        const float s = __uint_as_float((uint32_t)scale[(size_t)e * groups + g] << 16);
-        const float b = __uint_as_float((uint32_t)bias[(size_t)e * groups + g] << 16);
-        const int idx = g * 64 + lane * 2;
-        const float q0 = (float)qr[idx], q1 = (float)qr[idx + 1];
-        const float x0 = __half2float(xr[idx]), x1 = __half2float(xr[idx + 1]);
-        acc = __fmaf_rn(s, __fadd_rn(__fmul_rn(q0, x0), __fmul_rn(q1, x1)), acc);
-        acc = __fmaf_rn(b, __fadd_rn(x0, x1), acc);
-    }
-    // the lanes in index order, as the CPU restatement adds them
-    float total = 0.f;
-    for (int l = 0; l < 32; l++) total = __fadd_rn(total, __shfl_sync(0xffffffffu, acc, l));
+    const float total = router_logit(q + (size_t)e * d, scale + (size_t)e * groups, bias + (size_t)e * groups, x + (size_t)t * x_stride, groups, lane);
     if (lane == 0) out[w] = total;
 }
 
@@ -189,6 +208,7 @@ cudaError_t launch_router_logits(tsb_ctx* ctx, cudaStream_t st, const uint8_t* q
 
 cudaError_t launch_moe_route(tsb_ctx* ctx, cudaStream_t st, const float* logits, int tokens, int n_experts, int k, int32_t* ids,
                              __half* weights) {
+    if (n_experts > ROUTER_MAX_EXPERTS) return cudaErrorInvalidValue;
     const int wpb = 4;
     return tsb_launch(ctx, moe_route_kernel, dim3((unsigned)((tokens + wpb - 1) / wpb)), dim3(wpb * 32), 0, st, true, logits, n_experts, k,
                       (const float*)nullptr, ids, weights, tokens, ctx->dev_error);
@@ -243,7 +263,8 @@ int32_t tsb_moe_route(tsb_ctx* ctx, tsb_stream s, const float* router_logits_f32
                       const float* per_expert_scale, int32_t* ids_out, void* weights_f16_out) {
     if (!ctx) return TSB_ERR_INVALID;
     TSB_REQUIRE(ctx, router_logits_f32 && ids_out && weights_f16_out, "null buffer");
-    TSB_REQUIRE(ctx, tokens > 0 && n_experts > 0 && k >= 1 && k <= 8 && k <= n_experts, "need 1 <= k <= min(8, experts)");
+    TSB_REQUIRE(ctx, tokens > 0 && n_experts > 0 && n_experts <= ROUTER_MAX_EXPERTS && k >= 1 && k <= 8 && k <= n_experts,
+                "need 1 <= k <= min(8, experts) and at most 512 experts");
     DeviceGuard g(ctx);
     const int wpb = 4;
     TSB_CUDA(ctx, tsb_launch(ctx, moe_route_kernel, dim3((unsigned)((tokens + wpb - 1) / wpb)), dim3(wpb * 32), 0, (cudaStream_t)s,
@@ -273,6 +294,8 @@ int32_t tsb_moe_ffn(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* gate_
     TSB_REQUIRE(ctx, tokens > 0 && tokens <= 4096 && k >= 1 && k <= 8 && n_experts >= k && n_experts <= MOE_MAX_EXPERTS,
                 "bad token / expert counts");
     TSB_REQUIRE(ctx, d_model > 0 && d_model % 256 == 0 && ffn > 0 && ffn % 256 == 0, "d_model and the expert width must be multiples of 256");
+    TSB_REQUIRE(ctx, ((reinterpret_cast<uintptr_t>(gate_up_region) + gate_up_off) & 15u) == 0 && ((reinterpret_cast<uintptr_t>(down_region) + down_off) & 15u) == 0,
+                "expert matrices must start on a 16-byte boundary");
     DeviceGuard g(ctx);
     cudaStream_t st = (cudaStream_t)s;
     void* ws = nullptr;
