@@ -28,49 +28,57 @@ constexpr int ROUTER_MAX_EXPERTS = 512;
 // the picks.  `row` may live in shared or global memory.
 __device__ __forceinline__ void route_row(const float* row, int n_experts, int k, const float* __restrict__ scale,
                                           int32_t* __restrict__ ids, __half* __restrict__ weights, int lane, uint32_t* __restrict__ err) {
-    int picked[8];
-    float pv[8];
     float held[ROUTER_MAX_EXPERTS / 32];  // this lane's logits, read once
+    uint32_t alive = 0;                   // bit i: expert lane + 32 i is still to be picked
 #pragma unroll
-    for (int i = 0; i < ROUTER_MAX_EXPERTS / 32; i++) held[i] = lane + 32 * i < n_experts ? row[lane + 32 * i] : 0.f;
-    for (int r = 0; r < k; r++) {
-        float best = 0.f;
-        int bi = 0x7fffffff;
-#pragma unroll
-        for (int i = 0; i < ROUTER_MAX_EXPERTS / 32; i++) {
-            const int e = lane + 32 * i;
-            if (e >= n_experts) continue;
-            bool taken = false;
-            for (int c = 0; c < r; c++) taken |= picked[c] == e;
-            if (taken) continue;
-            const float v = held[i];
-            // total order of f32::total_cmp on the values a router emits (finite): larger first, then lower index
-            if (bi == 0x7fffffff || v > best || (v == best && e < bi)) best = v, bi = e;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (oi != 0x7fffffff && (bi == 0x7fffffff || ob > best || (ob == best && oi < bi))) best = ob, bi = oi;
-        }
-        picked[r] = bi, pv[r] = best;
+    for (int i = 0; i < ROUTER_MAX_EXPERTS / 32; i++) {
+        const bool in = lane + 32 * i < n_experts;
+        held[i] = in ? row[lane + 32 * i] : 0.f;
+        alive |= in ? (1u << i) : 0u;
     }
-    if (lane == 0) {
-        bool bad = false;
-        for (int r = 0; r < k; r++) bad |= picked[r] == 0x7fffffff || !isfinite(pv[r]);
-        if (bad) atomicCAS(err, 0u, (uint32_t)TSB_DEV_NONFINITE);
-        const float mx = pv[0];
-        float ex[8], sum = 0.f;
-        for (int r = 0; r < k; r++) {
-            ex[r] = (float)exp((double)(pv[r] - mx));  // correctly rounded f32 exp
-            sum += ex[r];
+    // lane r keeps pick r
+    int my_pick = 0x7fffffff;
+    float my_val = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+        if (r < k) {
+            float best = 0.f;
+            int bi = 0x7fffffff;
+#pragma unroll
+            for (int i = 0; i < ROUTER_MAX_EXPERTS / 32; i++) {
+                const float v = held[i];
+                // total order of f32::total_cmp on the values a router emits (finite): larger first, then lower index;
+                // within a lane the candidates come in ascending index order, so a strict compare keeps the lower one
+                if (((alive >> i) & 1u) && (bi == 0x7fffffff || v > best)) best = v, bi = lane + 32 * i;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (oi != 0x7fffffff && (bi == 0x7fffffff || ob > best || (ob == best && oi < bi))) best = ob, bi = oi;
+            }
+            if (bi != 0x7fffffff && (bi & 31) == lane) alive &= ~(1u << (bi >> 5));
+            if (lane == r) my_pick = bi, my_val = best;
         }
-        for (int r = 0; r < k; r++) {
-            const int e = bad ? 0 : picked[r];
-            const float sc = scale ? scale[e] : 1.0f;
-            ids[r] = e;
-            weights[r] = __float2half_rn(__fmul_rn(__fdiv_rn(ex[r], sum), sc));
-        }
+    }
+    // softmax over the picks: max = the first pick, exp per lane, the sum in pick order
+    const float mx = __shfl_sync(0xffffffffu, my_val, 0);
+    const bool mine = lane < k;
+    const float ex = mine ? (float)exp((double)(my_val - mx)) : 0.f;  // correctly rounded f32 exp
+    float sum = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+        const float er = __shfl_sync(0xffffffffu, ex, r);
+        if (r < k) sum = __fadd_rn(sum, er);
+    }
+    const bool bad_lane = mine && (my_pick == 0x7fffffff || !isfinite(my_val));
+    const bool bad = __any_sync(0xffffffffu, bad_lane);
+    if (bad && lane == 0) atomicCAS(err, 0u, (uint32_t)TSB_DEV_NONFINITE);
+    if (mine) {
+        const int e = bad ? 0 : my_pick;
+        const float sc = scale ? scale[e] : 1.0f;
+        ids[lane] = e;
+        weights[lane] = __float2half_rn(__fmul_rn(__fdiv_rn(ex, sum), sc));
     }
 }
 
@@ -88,16 +96,30 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int n_experts
 __device__ __forceinline__ float router_logit(const uint8_t* __restrict__ qr, const uint16_t* __restrict__ sr, const uint16_t* __restrict__ br,
                                               const __half* __restrict__ xr, int groups, int lane) {
     float acc = 0.f;
-#pragma unroll 8
-    for (int g = 0; g < groups; g++) {
-        const float s = __uint_as_float((uint32_t)sr[g] << 16);
-        const float b = __uint_as_float((uint32_t)br[g] << 16);
-        const int idx = g * 64 + lane * 2;
-        const uint32_t qq = *reinterpret_cast<const uint16_t*>(qr + idx);
-        const float2 xx = __half22float2(*reinterpret_cast<const __half2*>(xr + idx));
-        const float q0 = (float)(qq & 0xFFu), q1 = (float)(qq >> 8);
-        acc = __fmaf_rn(s, __fadd_rn(__fmul_rn(q0, xx.x), __fmul_rn(q1, xx.y)), acc);
-        acc = __fmaf_rn(b, __fadd_rn(xx.x, xx.y), acc);
+    for (int g0 = 0; g0 < groups; g0 += 32) {
+        // every load of the next 32 groups first (one latency), then the sums in group order
+        uint32_t qq[32], ss[32], bb[32];
+        __half2 xx[32];
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+            const int g = g0 + i;
+            const bool in = g < groups;
+            const int idx = (in ? g : g0) * 64 + lane * 2;
+            qq[i] = *reinterpret_cast<const uint16_t*>(qr + idx);
+            xx[i] = *reinterpret_cast<const __half2*>(xr + idx);
+            ss[i] = sr[in ? g : g0];
+            bb[i] = br[in ? g : g0];
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+            if (g0 + i < groups) {
+                const float s = __uint_as_float(ss[i] << 16), b = __uint_as_float(bb[i] << 16);
+                const float2 x = __half22float2(xx[i]);
+                const float q0 = (float)(qq[i] & 0xFFu), q1 = (float)(qq[i] >> 8);
+                acc = __fmaf_rn(s, __fadd_rn(__fmul_rn(q0, x.x), __fmul_rn(q1, x.y)), acc);
+                acc = __fmaf_rn(b, __fadd_rn(x.x, x.y), acc);
+            }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
