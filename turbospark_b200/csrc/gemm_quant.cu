@@ -239,22 +239,7 @@ __device__ __forceinline__ void q4k_block(const uint4* __restrict__ rowA, const 
 // ---- MXFP4: eight 17-byte blocks (256 columns) for rows (gid, gid+8) -------
 // Block (crates/compute/src/quant_gguf_mxfp4.rs:60-78): e8m0 byte, 16 nibble
 // bytes; byte j = element j (low) and j+16 (high); w = LUT[code] * 2^(e-128)
-// with LUT = 2 * e2m1.  The hardware e2m1x2 -> f16x2 conversion yields the
-// e2m1 value, so the fp32 partial sum is doubled before the block scale 2^(e-128) multiplies it.
-__device__ __forceinline__ void cvt_e2m1x4(uint32_t w, uint32_t (&out)[4]) {
-    // out[i] = half2( e2m1(byte i low nibble), e2m1(byte i high nibble) )
-    asm volatile(
-        "{\n"
-        ".reg .b8 b0, b1, b2, b3;\n"
-        "mov.b32 {b0, b1, b2, b3}, %4;\n"
-        "cvt.rn.f16x2.e2m1x2 %0, b0;\n"
-        "cvt.rn.f16x2.e2m1x2 %1, b1;\n"
-        "cvt.rn.f16x2.e2m1x2 %2, b2;\n"
-        "cvt.rn.f16x2.e2m1x2 %3, b3;\n"
-        "}\n"
-        : "=r"(out[0]), "=r"(out[1]), "=r"(out[2]), "=r"(out[3])
-        : "r"(w));
-}
+// with LUT = 2 * e2m1.
 __device__ __forceinline__ float mxfp4_scale_dev(uint32_t e) {
     // crates/compute/src/quant_gguf_mxfp4.rs:95-102: 2^(e-128), subnormal for e < 2.
     return __uint_as_float(e < 2 ? (0x00200000u << e) : ((e - 1u) << 23));

@@ -476,6 +476,11 @@ static int32_t runtime_init(tsb_session* s, ModelRt& rt, const tsb_model* model,
             (rc = A(moe_ffn_workspace_bytes(R, model->top_k, model->n_experts, c.d_model, model->moe_ffn), &rt.moe_ws)))
             return rc;
         cudaMemset(rt.moe_zero, 0, (size_t)R * c.d_model * 2);
+        if ((rc = A((size_t)R * sizeof(float), (void**)&rt.moe_unit_ss))) return rc;
+        {
+            std::vector<float> unit((size_t)R, (float)c.d_model);  // sum / d_model = 1 and eps = 0: 1/rms = 1 exactly
+            TSB_CUDA(ctx, cudaMemcpy(rt.moe_unit_ss, unit.data(), unit.size() * sizeof(float), cudaMemcpyHostToDevice));
+        }
         return TSB_OK;
     }
     bool wide = R >= WIDE_MIN_ROWS && gemm_wide_supported(model->lm_head.qtype, model->lm_head.rows, model->lm_head.cols, R);
@@ -574,14 +579,26 @@ static cudaError_t forward_device_moe(tsb_session* s, ModelRt& rt, const int32_t
         e = (x);                        \
         if (e != cudaSuccess) return e; \
     } while (0)
-    FW(launch_embed_rows(ctx, st, m->embed.qtype, m->embed.data, c.vocab, c.d_model, tokens_dev, token_stride, rows, rt.h, 1.0f));
+    // embedding rows into the residual stream plus the RoPE table of the rows' positions (the operand and the sums
+    // this kernel also writes are replaced by the norm that follows)
+    FW(launch_embed_norm(ctx, st, m->embed.qtype, m->embed.data, c.vocab, c.d_model, tokens_dev, token_stride, rows, rt.h,
+                         m->layers[0].attn_norm, out_d, rt.ss, rt.cs, rows_dev, c.head_dim, c.rope_theta));
     FW(launch_rmsnorm_rows(ctx, st, rt.h, nullptr, m->layers[0].attn_norm, rt.w_xn, out_d, rows, c.d_model, c.rms_eps));
     for (int L = 0; L < c.n_layers; L++) {
         const LayerW& l = m->layers[L];
-        FW(launch_gemm_quant(ctx, st, l.wqkv.qtype, l.wqkv.data, l.wqkv.rows, l.wqkv.cols, in_d, rt.w_qkv, qkv_dim, rows, false));
-        if (l.wv.data) FW(launch_gemm_quant(ctx, st, l.wv.qtype, l.wv.data, l.wv.rows, l.wv.cols, in_d, rt.w_qkv + qd + kd, qkv_dim, rows, false));
-        FW(launch_rope_store_kv(ctx, st, rt.kv, L, rt.w_qkv, rows_dev, rows, c.n_q_heads, c.rope_theta));
-        FW(launch_attn_decode_rows(ctx, st, rt.kv, L, rt.w_qkv, qkv_dim, nullptr, out_o, rows_dev, rows, rows_per_seq, c.n_q_heads, scale,
+        {   // q|k|v over the normed operand; epilogue: f16 rounding, RoPE, q -> buffer, k and v -> cache slots
+            EpiArgs a;
+            a.ss_in = rt.moe_unit_ss, a.ss_parts = 1, a.d_in = c.d_model, a.eps = 0.f;
+            a.kv = rt.kv->view, a.layer = L, a.row_desc = rows_dev, a.cs = rt.cs, a.q_out = rt.q;
+            a.n_q_heads = c.n_q_heads, a.n_kv_heads = c.n_kv_heads, a.head_dim = c.head_dim;
+            if (l.wv.data) a.n_v_heads = 0;
+            FW(launch_gemm_fused(ctx, st, l.wqkv.qtype, l.wqkv.data, l.wqkv.rows, l.wqkv.cols, in_d, rows, EPI_ROPE_STORE, a));
+            if (l.wv.data) {
+                a.n_q_heads = 0, a.n_kv_heads = 0, a.n_v_heads = c.n_kv_heads;
+                FW(launch_gemm_fused(ctx, st, l.wv.qtype, l.wv.data, l.wv.rows, l.wv.cols, in_d, rows, EPI_ROPE_STORE, a));
+            }
+        }
+        FW(launch_attn_decode_rows(ctx, st, rt.kv, L, rt.q, qd, nullptr, out_o, rows_dev, rows, rows_per_seq, c.n_q_heads, scale,
                                    max_len, rt.attn_scratch, s->n_streams * s->max_rows));
         FW(launch_gemm_quant(ctx, st, l.wo.qtype, l.wo.data, l.wo.rows, l.wo.cols, in_o, rt.w_o, c.d_model, rows, false));
         FW(launch_rmsnorm_rows(ctx, st, rt.h, rt.w_o, l.ffn_norm, rt.w_xn, none, rows, c.d_model, c.rms_eps));

@@ -62,6 +62,7 @@ struct ModelRt {
     float* moe_logits = nullptr;
     int32_t* moe_ids = nullptr;
     __half *moe_w = nullptr, *moe_zero = nullptr;
+    float* moe_unit_ss = nullptr;  // [R] sums of squares that make the q|k|v epilogue's 1/rms exactly one (the operand is already normed)
     void* moe_ws = nullptr;
     std::vector<std::vector<int32_t>> fed;  // per stream: tokens absorbed, by position (target only)
 };
