@@ -546,6 +546,7 @@ __device__ __forceinline__ void run_epilogue(const EpiArgs& e, const Group& gr, 
     constexpr int NTOK = NT * 8;
     const int tid = threadIdx.x;
     if constexpr (EPI == EPI_PLAIN || EPI == EPI_SCALE) {
+        // (these two epilogues are elementwise and normally run straight out of the reduction: store_plain below)
         const int64_t row0 = (int64_t)gr.tile0 * TILE_ROWS;
         for (int idx = tid; idx < NTOK * 16; idx += CONSUMER_WARPS * 32) {
             const int tok = idx >> 4, row = idx & 15;
@@ -713,9 +714,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + NUM_STAGES;
     float* inv_rms = reinterpret_cast<float*>(smem + 64);                                  // [NTOK] (<= 64 floats)
-    float* red = reinterpret_cast<float*>(smem + 64 + 256);                                // [8 warps][NT][4][32]
-    float* tile_out = red + CONSUMER_WARPS * NT * 4 * 32;                                  // [2][NTOK][16]
-    uint8_t* stages = reinterpret_cast<uint8_t*>(tile_out + 2 * NTOK * 16);
+    float* red = reinterpret_cast<float*>(smem + 64 + 256);                                // [2][8 warps][NT][4][32]
+    float* tile_out0 = red + 2 * CONSUMER_WARPS * NT * 4 * 32;                             // [2 groups in turn][2][NTOK][16]
+    // The plain and the scaling epilogue are elementwise: the thread that sums an output element also stores it, so
+    // those kernels alternate between two reduction buffers and keep one barrier per tile instead of three.
+    constexpr bool ELEMWISE = EPI == EPI_PLAIN || EPI == EPI_SCALE;
+    uint8_t* stages = reinterpret_cast<uint8_t*>(tile_out0 + 4 * NTOK * 16);
     constexpr bool NEEDS_INV = EPI == EPI_SCALE || EPI == EPI_SILU || EPI == EPI_ROPE_STORE;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -841,7 +845,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
     const ActOperand act0 = act;
 
     bool ok = true, have_inv = !NEEDS_INV;
-    uint32_t n = 0;
+    uint32_t n = 0, tile_no = 0, group_no = 0;
     for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
         if (item + (int)gridDim.x >= n_items) pdl_launch_dependents();  // last item of this CTA
         int g = item;
@@ -862,6 +866,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
             }
         }
         const Group gr = group_of<EPI>(g, n_tiles, epi);
+        // finished tiles alternate between two buffers, so a group's epilogue may still be reading its tiles while
+        // the next group's sums are written: no barrier after the epilogue
+        float* tile_out = tile_out0 + (group_no++ & 1u) * (2 * NTOK * 16);
         for (int ti = 0; ti < gr.n; ti++) {
             const int64_t row0 = (int64_t)(ti ? gr.tile1 : gr.tile0) * TILE_ROWS;
             float acc[NT][4];
@@ -897,10 +904,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
             }
 
             // ---- fixed-order reduction over the eight consumer warps into tile_out[ti]
+            float* redb = red + (ELEMWISE ? (tile_no++ & 1u) * (CONSUMER_WARPS * NT * 4 * 32) : 0);
 #pragma unroll
             for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-                for (int i = 0; i < 4; i++) red[((warp * NT + nt) * 4 + i) * 32 + lane] = acc[nt][i];
+                for (int i = 0; i < 4; i++) redb[((warp * NT + nt) * 4 + i) * 32 + lane] = acc[nt][i];
             asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
             for (int idx = threadIdx.x; idx < NTOK * 16; idx += CONSUMER_WARPS * 32) {
                 const int tok = idx >> 4, row = idx & 15;
@@ -909,24 +917,25 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
                 const int i = ((row >> 3) << 1) | (nn & 1);
                 float sum = 0.f;
 #pragma unroll
-                for (int w = 0; w < CONSUMER_WARPS; w++) sum += red[((w * NT + nt) * 4 + i) * 32 + src_lane];
+                for (int w = 0; w < CONSUMER_WARPS; w++) sum += redb[((w * NT + nt) * 4 + i) * 32 + src_lane];
                 tile_out[ti * NTOK * 16 + idx] = sum;
             }
-            asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");  // tile_out complete, red reusable
+            if constexpr (!ELEMWISE)
+                asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");  // tile_out complete, red reusable
         }
         if (!have_inv) {
             asm volatile("bar.sync 2, %0;" ::"n"(GEMM_THREADS) : "memory");  // 1/rms per token from the producer warp
             have_inv = true;
         }
+        // (elementwise epilogues: run_epilogue reads tile_out[idx] with the same idx -> thread mapping as the sum loop)
         if (ok) run_epilogue<EPI, NT>(epi, gr, tile_out, inv_rms, rows, tokens, tok0, err);
-        asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");  // tile_out is reused by the next group
     }
     if (!have_inv) asm volatile("bar.sync 2, %0;" ::"n"(GEMM_THREADS) : "memory");
 }
 
 template <int QT, int NT>
 constexpr size_t gemm_smem_bytes() {
-    return 64 + 256 + (size_t)CONSUMER_WARPS * NT * 4 * 32 * sizeof(float) + (size_t)2 * NT * 8 * 16 * sizeof(float) +
+    return 64 + 256 + (size_t)2 * CONSUMER_WARPS * NT * 4 * 32 * sizeof(float) + (size_t)4 * NT * 8 * 16 * sizeof(float) +
            (size_t)NUM_STAGES * TILE_ROWS * row_stride_for(Fmt<QT>::UNIT_BYTES) + 128;
 }
 
