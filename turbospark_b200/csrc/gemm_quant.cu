@@ -903,22 +903,29 @@ __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
                 if (lane == 0) mbar_arrive(&empty[s]);
             }
 
-            // ---- fixed-order reduction over the eight consumer warps into tile_out[ti]
-            float* redb = red + (ELEMWISE ? (tile_no++ & 1u) * (CONSUMER_WARPS * NT * 4 * 32) : 0);
+            // ---- fixed-order reduction over the eight consumer warps into tile_out[ti].  Elementwise epilogues take
+            // the two reduction buffers in turn (one barrier per tile); the paired ones park the first tile's partial
+            // sums in buffer 0, the second's in buffer 1, and reduce both behind one pair of barriers.
+            constexpr int RED_FLOATS = CONSUMER_WARPS * NT * 4 * 32;
+            float* redb = red + (ELEMWISE ? (tile_no++ & 1u) : (uint32_t)ti) * RED_FLOATS;
 #pragma unroll
             for (int nt = 0; nt < NT; nt++)
 #pragma unroll
                 for (int i = 0; i < 4; i++) redb[((warp * NT + nt) * 4 + i) * 32 + lane] = acc[nt][i];
+            if (!ELEMWISE && ti + 1 < gr.n) continue;  // the pair's second tile first
             asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
-            for (int idx = threadIdx.x; idx < NTOK * 16; idx += CONSUMER_WARPS * 32) {
-                const int tok = idx >> 4, row = idx & 15;
-                const int nt = tok >> 3, nn = tok & 7;
-                const int src_lane = (row & 7) * 4 + (nn >> 1);
-                const int i = ((row >> 3) << 1) | (nn & 1);
-                float sum = 0.f;
+            for (int t2 = ELEMWISE ? ti : 0; t2 <= ti; t2++) {
+                const float* rsrc = ELEMWISE ? redb : red + t2 * RED_FLOATS;
+                for (int idx = threadIdx.x; idx < NTOK * 16; idx += CONSUMER_WARPS * 32) {
+                    const int tok = idx >> 4, row = idx & 15;
+                    const int nt = tok >> 3, nn = tok & 7;
+                    const int src_lane = (row & 7) * 4 + (nn >> 1);
+                    const int i = ((row >> 3) << 1) | (nn & 1);
+                    float sum = 0.f;
 #pragma unroll
-                for (int w = 0; w < CONSUMER_WARPS; w++) sum += redb[((w * NT + nt) * 4 + i) * 32 + src_lane];
-                tile_out[ti * NTOK * 16 + idx] = sum;
+                    for (int w = 0; w < CONSUMER_WARPS; w++) sum += rsrc[((w * NT + nt) * 4 + i) * 32 + src_lane];
+                    tile_out[t2 * NTOK * 16 + idx] = sum;
+                }
             }
             if constexpr (!ELEMWISE)
                 asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");  // tile_out complete, red reusable
