@@ -104,6 +104,9 @@ cudaError_t launch_gemm_quant(tsb_ctx* ctx, cudaStream_t st, int qtype, const ui
 // The routed feed-forward (csrc/moe.cu): y = half(residual + sum over slots of w * down_e(act(gate_e x) * up_e x)).
 // x rows have stride x_stride; ids / weights are [tokens, k]; workspace holds moe_ffn_workspace_bytes(...) bytes.
 size_t moe_ffn_workspace_bytes(int tokens, int k, int n_experts, int d_model, int ffn);
+// With y == nullptr launch_moe_ffn stops before the combine step and leaves the per-(row, slot) expert outputs,
+// f32 [tokens * k, d_model], at this address inside the workspace.
+const float* moe_ffn_values(const void* workspace, int tokens, int k, int n_experts, int d_model, int ffn);
 cudaError_t launch_router_logits(tsb_ctx* ctx, cudaStream_t st, const uint8_t* q, const uint16_t* scale, const uint16_t* bias,
                                  const __half* x, int64_t x_stride, int tokens, int n_experts, int d, float* out);
 cudaError_t launch_moe_route(tsb_ctx* ctx, cudaStream_t st, const float* logits, int tokens, int n_experts, int k, int32_t* ids,

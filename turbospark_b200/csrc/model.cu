@@ -605,9 +605,11 @@ static cudaError_t forward_device_moe(tsb_session* s, ModelRt& rt, const int32_t
         FW(launch_router_logits(ctx, st, l.router_q, l.router_scale, l.router_bias, rt.w_xn, c.d_model, rows, m->n_experts, c.d_model, rt.moe_logits));
         FW(launch_moe_route(ctx, st, rt.moe_logits, rows, m->n_experts, m->top_k, rt.moe_ids, rt.moe_w));
         FW(launch_moe_ffn(ctx, st, l.experts_qtype, l.experts_gate_up, l.experts_down, m->n_experts, c.d_model, m->moe_ffn, rt.w_xn, c.d_model,
-                          rt.moe_zero, rt.moe_ids, rt.moe_w, rows, m->top_k, rt.w_o, rt.moe_ws));
+                          rt.moe_zero, rt.moe_ids, rt.moe_w, rows, m->top_k, nullptr, rt.moe_ws));
+        // the slot-ordered weighted sum (over a zero residual, rounded to f16), its add onto the stream and the next norm
         const void* g = L + 1 < c.n_layers ? (const void*)m->layers[L + 1].attn_norm : (const void*)m->out_norm;
-        FW(launch_rmsnorm_rows(ctx, st, rt.h, rt.w_o, g, rt.w_xn, out_d, rows, c.d_model, c.rms_eps));
+        FW(launch_combine_norm_rows(ctx, st, rt.h, moe_ffn_values(rt.moe_ws, rows, m->top_k, m->n_experts, c.d_model, m->moe_ffn), rt.moe_w,
+                                    m->top_k, g, rt.w_xn, out_d, rows, c.d_model, c.rms_eps));
     }
     if (logits) {
         EpiArgs a;

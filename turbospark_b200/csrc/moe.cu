@@ -236,6 +236,10 @@ cudaError_t launch_moe_route(tsb_ctx* ctx, cudaStream_t st, const float* logits,
                       (const float*)nullptr, ids, weights, tokens, ctx->dev_error);
 }
 
+const float* moe_ffn_values(const void* workspace, int tokens, int k, int n_experts, int d_model, int ffn) {
+    return reinterpret_cast<const float*>(static_cast<const uint8_t*>(workspace) + moe_layout(tokens, k, n_experts, d_model, ffn).off_values);
+}
+
 size_t moe_ffn_workspace_bytes(int tokens, int k, int n_experts, int d_model, int ffn) {
     return moe_layout(tokens, k, n_experts, d_model, ffn).total;
 }
@@ -271,6 +275,7 @@ cudaError_t launch_moe_ffn(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8
     if ((e = launch_gemm_grouped(ctx, st, qtype, down, down_bytes, n_experts, d_model, ffn, act, count, tstart, tokens, EPI_PLAIN, a2)) !=
         cudaSuccess)
         return e;
+    if (!y) return cudaSuccess;  // the caller combines (moe_ffn_values) together with its next operator
     const int64_t total = (int64_t)tokens * d_model;
     return tsb_launch(ctx, moe_combine_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, true, residual,
                       (const float*)values, weights, (int)k, (int)d_model, (int)tokens, y);

@@ -104,9 +104,14 @@ __global__ void dequant_rows_kernel(const uint8_t* __restrict__ w, int64_t row_b
 constexpr int NORM_THREADS = 256;
 constexpr int NORM_MAX_ITERS = 8;  // d <= 256 * 8 * 8 = 16384
 
+// MIX: the residual row is not read but formed here as the routed experts' weighted sum,
+// half(sum over slots in slot order of float(w[r, s]) * values[r * k + s][.]) (the routed layer's combine step,
+// crates/gpu/src/shaders/moe_gguf.metal:625-678 over a zero residual).
+template <bool MIX>
 __global__ void __launch_bounds__(NORM_THREADS)
     rmsnorm_rows_kernel(__half* __restrict__ x, const __half* __restrict__ residual, const uint16_t* __restrict__ w_bf16,
-                        __half* __restrict__ out, ActOut act, int d, float eps) {
+                        __half* __restrict__ out, ActOut act, int d, float eps, const float* __restrict__ mix_values,
+                        const __half* __restrict__ mix_weights, int mix_k) {
     __shared__ float warp_sums[NORM_THREADS / 32];
     pdl_wait();
     const int r = blockIdx.x;
@@ -119,8 +124,26 @@ __global__ void __launch_bounds__(NORM_THREADS)
         if (e0 < d) {
             uint4 raw = *reinterpret_cast<const uint4*>(xr + e0);
             const __half* hp = reinterpret_cast<const __half*>(&raw);
-            if (residual) {
-                const uint4 rr = *reinterpret_cast<const uint4*>(residual + (size_t)r * d + e0);
+            if (MIX || residual) {
+                uint4 rr;
+                if constexpr (MIX) {
+                    float a8[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) a8[i] = 0.f;
+                    for (int sl = 0; sl < mix_k; sl++) {
+                        const float wgt = __half2float(mix_weights[(size_t)r * mix_k + sl]);
+                        const float4* vp = reinterpret_cast<const float4*>(mix_values + ((size_t)r * mix_k + sl) * d + e0);
+                        const float4 v0 = vp[0], v1 = vp[1];
+                        const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+                        for (int i = 0; i < 8; i++) a8[i] = __fadd_rn(a8[i], __fmul_rn(wgt, vv[i]));
+                    }
+                    __half* rw = reinterpret_cast<__half*>(&rr);
+#pragma unroll
+                    for (int i = 0; i < 8; i++) rw[i] = __float2half_rn(a8[i]);
+                } else {
+                    rr = *reinterpret_cast<const uint4*>(residual + (size_t)r * d + e0);
+                }
                 const __half* rp = reinterpret_cast<const __half*>(&rr);
                 uint4 upd;
                 __half* up = reinterpret_cast<__half*>(&upd);
@@ -380,8 +403,14 @@ cudaError_t launch_embed_norm(tsb_ctx* ctx, cudaStream_t st, int qtype, const ui
 
 cudaError_t launch_rmsnorm_rows(tsb_ctx* ctx, cudaStream_t st, __half* x, const __half* residual, const void* w_bf16,
                                 __half* out, ActOut act, int rows, int d, float eps) {
-    return tsb_launch(ctx, rmsnorm_rows_kernel, dim3((unsigned)rows), dim3(NORM_THREADS), 0, st, true, x, residual,
-                      (const uint16_t*)w_bf16, out, act, d, eps);
+    return tsb_launch(ctx, rmsnorm_rows_kernel<false>, dim3((unsigned)rows), dim3(NORM_THREADS), 0, st, true, x, residual,
+                      (const uint16_t*)w_bf16, out, act, d, eps, (const float*)nullptr, (const __half*)nullptr, 0);
+}
+
+cudaError_t launch_combine_norm_rows(tsb_ctx* ctx, cudaStream_t st, __half* x, const float* values, const __half* weights, int k,
+                                     const void* w_bf16, __half* out, ActOut act, int rows, int d, float eps) {
+    return tsb_launch(ctx, rmsnorm_rows_kernel<true>, dim3((unsigned)rows), dim3(NORM_THREADS), 0, st, true, x, (const __half*)nullptr,
+                      (const uint16_t*)w_bf16, out, act, d, eps, values, weights, k);
 }
 
 cudaError_t launch_silu_mul(tsb_ctx* ctx, cudaStream_t st, const __half* gate, const __half* up, __half* out, ActOut act,
