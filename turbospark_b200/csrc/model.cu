@@ -1385,6 +1385,7 @@ int32_t tsb_session_time_matmuls(tsb_session* s, int32_t rows, int32_t iters, fl
     if (!s || !out_ms) return TSB_ERR_INVALID;
     tsb_ctx* ctx = s->ctx;
     TSB_REQUIRE(ctx, rows > 0 && rows <= s->n_streams * s->max_rows && iters > 0, "bad rows / iters");
+    if (s->target.model->n_experts > 0) return tsb_fail(ctx, TSB_ERR_UNSUPPORTED, "the matmul timing covers dense layers only");
     DeviceGuard g(ctx);
     ModelRt& rt = s->target;
     const tsb_model* m = rt.model;
