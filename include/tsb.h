@@ -85,6 +85,15 @@ TSB_API int32_t tsb_memcpy_d2h(tsb_ctx* ctx, tsb_stream s, void* host, const voi
 /* Replaces PassEncoder commit_and_wait_checked (crates/gpu/src/context/pass.rs:180): waits, then
  * surfaces both CUDA errors and the kernels' own error word. */
 TSB_API int32_t tsb_stream_sync(tsb_ctx* ctx, tsb_stream s);
+/* Every wait inside a kernel (on a copy's arrival barrier, on the grid barrier of a cooperative kernel) is bounded by
+ * time: when the limit runs out the kernel records TSB_ERR_DEVICE's "bounded barrier wait gave up" word, drains and
+ * returns, and the context stays usable.  Default 1 s.  Synchronises the device.  (The reference's Metal passes have
+ * no device-side waits; its host-side equivalent is the command-buffer status check of
+ * crates/gpu/src/context/pass.rs:180.) */
+TSB_API int32_t tsb_ctx_set_wait_limit_us(tsb_ctx* ctx, uint32_t microseconds);
+/* Test hook: one CTA waits on a barrier nobody arrives on, so the bounded wait runs out.  out_u32_dev receives
+ * 1 if the wait reported success (it must not), 0 otherwise; the following tsb_stream_sync returns TSB_ERR_DEVICE. */
+TSB_API int32_t tsb_debug_wait_nobody(tsb_ctx* ctx, tsb_stream s, void* out_u32_dev);
 /* Bytes one row of `cols` elements occupies in the given format. */
 TSB_API int64_t tsb_row_bytes(int32_t qtype, int64_t cols);
 /* Number of kernel launches this ctx has enqueued since creation. */

@@ -212,6 +212,28 @@ def test_q4k_hand_packed_superblock_on_device(ctx, oracle):
         assert y[t] == got[t * 37 % 256]
 
 
+def test_q6k_hand_packed_superblock_on_device(ctx, oracle):
+    import json, os
+    from tests.test_oracle_quant import q6k_hand_packed_block
+    g = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "q6k_handpacked.json")))
+    block, want = q6k_hand_packed_block(g)
+    w = ctx.upload_weights(block)
+    out = ctx.alloc(256 * 4)
+    ctx.dequant_rows(1, w, 256, None, 1, out)
+    got = out.download(np.float32, 256)
+    assert np.array_equal(got, want)
+    # through the matmul: one-hot activations pick single weights out exactly
+    x = np.zeros((8, 256), dtype=np.float32)
+    for t in range(8):
+        x[t, (t * 37 + 5) % 256] = 1.0
+    xd = ctx.to_device(oracle.f32_to_f16_bits(x))
+    yd = ctx.alloc(8 * 4)
+    ctx.gemm_quant(1, w, 1, 256, xd, yd, 8, y_f32=True)
+    y = yd.download(np.float32, 8)
+    for t in range(8):
+        assert y[t] == want[(t * 37 + 5) % 256]
+
+
 def test_embed_rows(ctx, oracle):
     vocab, d = 50, 512
     q = _weights(oracle, 0, vocab, d, 2)
@@ -265,3 +287,29 @@ def test_rmsnorm_rope_silu_residual(ctx, oracle):
     a = ctx.to_device(x)
     ctx.residual_add(a, ctx.to_device(res), rows * d)
     assert np.array_equal(a.download(np.uint16, rows * d).reshape(rows, d), summed)
+
+
+def test_a_wait_nobody_answers_gives_up_reports_and_leaves_the_context_usable(oracle):
+    """Every device-side wait is bounded by time.  A barrier nobody arrives on makes the bound run out: the kernel
+    returns, the next synchronisation reports the device error word, and the same context still computes."""
+    import turbospark_b200 as tsb
+    c = tsb.Ctx(0)
+    try:
+        c.set_wait_limit_us(2000)
+        flag = c.to_device(np.array([7], dtype=np.uint32))
+        c.debug_wait_nobody(flag)
+        with pytest.raises(tsb.TsbError) as ei:
+            c.sync()
+        assert "wait gave up" in str(ei.value)
+        assert flag.download(np.uint32, 1)[0] == 0  # the wait did not claim success
+        c.set_wait_limit_us(1000000)
+        rows, cols = 32, 4096
+        q = _weights(oracle, 0, rows, cols, 1)
+        x16 = oracle.f32_to_f16_bits(np.random.default_rng(1).standard_normal((2, cols)).astype(np.float32))
+        yd = c.alloc(2 * rows * 4)
+        c.gemm_quant(0, c.upload_weights(q), rows, cols, c.to_device(x16), yd, 2, y_f32=True)
+        c.sync()
+        _check(yd.download(np.float32, 2 * rows).reshape(2, rows),
+               oracle.gemm_quant(0, q, rows, cols, oracle.f16_bits_to_f32(x16)))
+    finally:
+        c.close()

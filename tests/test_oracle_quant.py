@@ -70,6 +70,27 @@ def test_q6k_round_trip(oracle):
     assert np.all(z == 0)
 
 
+def q6k_hand_packed_block(g):
+    """The literal superblock of crates/compute/tests/quant_gguf.rs:390-445 and the values its formula gives."""
+    block = bytes([g["ql_byte"]] * 128 + [g["qh_byte"]] * 64 + [s & 0xFF for s in g["scales"]]) + int(g["d_bits"]).to_bytes(2, "little")
+    assert len(block) == 210
+    want = np.empty(256, dtype=np.float32)
+    for h in range(2):
+        for k in range(4):
+            for l in range(32):
+                want[h * 128 + k * 32 + l] = np.float32(g["d"]) * np.float32(g["scales"][h * 8 + l // 16 + 2 * k]) * np.float32(g["quants"][k])
+    return np.frombuffer(block, dtype=np.uint8), want
+
+
+def test_q6k_hand_packed_superblock_decodes_to_the_documented_formula(oracle):
+    # split 6-bit levels, the bias of 32, signed scales, the scale index striding by 2, the 32-element spacing
+    g = json.load(open(os.path.join(GOLD, "q6k_handpacked.json")))
+    block, want = q6k_hand_packed_block(g)
+    got = oracle.dequantize(oracle.Q6K, block, 256)
+    assert np.array_equal(got, want)
+    assert got[0] == np.float32(g["spot"]["0"]) and got[176] == np.float32(g["spot"]["176"])
+
+
 def test_mxfp4_decoder_matches_ggml_bytes_floats_codebook_and_exponents(oracle):
     g = json.load(open(os.path.join(GOLD, "mxfp4_ggml.json")))
     got = oracle.dequantize(oracle.MXFP4, np.array(g["bytes"], dtype=np.uint8), 128)

@@ -13,8 +13,9 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-OUT = os.path.join(HERE, "_build")
-LIB = os.path.join(HERE, "libtsb.so")
+# TSB_BUILD_DIR redirects objects and the library (a scratch build that leaves the in-tree library alone)
+OUT = os.path.join(os.environ["TSB_BUILD_DIR"], "obj") if os.environ.get("TSB_BUILD_DIR") else os.path.join(HERE, "_build")
+LIB = os.path.join(os.environ["TSB_BUILD_DIR"], "libtsb.so") if os.environ.get("TSB_BUILD_DIR") else os.path.join(HERE, "libtsb.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")

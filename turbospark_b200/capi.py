@@ -163,6 +163,13 @@ class Ctx:
     def launches(self):
         return int(lib().tsb_launch_count(self.h))
 
+    def set_wait_limit_us(self, microseconds):
+        """Bound of every wait inside a kernel; when it runs out the kernel reports an error and returns."""
+        self.check(lib().tsb_ctx_set_wait_limit_us(self.h, C.c_uint32(microseconds)))
+
+    def debug_wait_nobody(self, out_u32, stream=None):
+        self.check(lib().tsb_debug_wait_nobody(self.h, stream, _vp(out_u32)))
+
     # ---- operators
     def gemm_quant(self, qtype, w, rows, cols, x, y, tokens, y_f32=False, w_off=0, stream=None):
         self.check(lib().tsb_gemm_quant(self.h, stream, C.c_int32(qtype), _vp(w), C.c_uint64(w_off), C.c_int64(rows),

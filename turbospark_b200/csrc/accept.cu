@@ -727,9 +727,13 @@ int32_t check_shaping(tsb_ctx* ctx, const tsb_shaping* sh) {
 
 size_t slice_smem(int vocab) { return (size_t)(((vocab + CL - 1) / CL + 1) & ~1) * sizeof(unsigned long long); }
 
-template <typename K>
-cudaError_t ensure_smem(K kernel, size_t bytes) {
-    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+// the three cluster kernels keep a vocabulary slice in dynamic shared memory (opt-in per device)
+cudaError_t configure_kernels(const tsb_ctx* ctx) {
+    static SmemOptIn stats_done, decide_done, sample_done;
+    cudaError_t e = tsb_opt_in_smem(ctx, accept_stats_kernel, (size_t)SLICE_MAX * 8, stats_done);
+    if (e == cudaSuccess) e = tsb_opt_in_smem(ctx, accept_decide_kernel, (size_t)SLICE_MAX * 8, decide_done);
+    if (e == cudaSuccess) e = tsb_opt_in_smem(ctx, sample_kernel, (size_t)SLICE_MAX * 8, sample_done);
+    return e;
 }
 
 }  // namespace
@@ -747,14 +751,7 @@ cudaError_t launch_accept(tsb_ctx* ctx, cudaStream_t st, const __half* target, c
     RowStats* stats = reinterpret_cast<RowStats*>(scratch);
     const int rps = 2 * k + 1;
     const size_t smem = slice_smem(vocab);
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = ensure_smem(accept_stats_kernel, (size_t)SLICE_MAX * 8);
-        if (e == cudaSuccess) e = ensure_smem(accept_decide_kernel, (size_t)SLICE_MAX * 8);
-        if (e == cudaSuccess) e = ensure_smem(sample_kernel, (size_t)SLICE_MAX * 8);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    if (cudaError_t e = configure_kernels(ctx); e != cudaSuccess) return e;
     const TruncShape tr{shape.top_k, shape.top_p, shape.min_p};
     const double temperature = shape.temperature;
     cudaError_t e = tsb_launch_cluster(ctx, accept_stats_kernel, dim3((unsigned)(batch * rps * CL)), dim3(ACC_THREADS), smem, st,
@@ -772,14 +769,7 @@ cudaError_t launch_sample(tsb_ctx* ctx, cudaStream_t st, const __half* logits, i
     const TruncShape tr{shape.top_k, shape.top_p, shape.min_p};
     const double temperature = shape.temperature;
     const size_t smem = slice_smem(vocab);
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = ensure_smem(accept_stats_kernel, (size_t)SLICE_MAX * 8);
-        if (e == cudaSuccess) e = ensure_smem(accept_decide_kernel, (size_t)SLICE_MAX * 8);
-        if (e == cudaSuccess) e = ensure_smem(sample_kernel, (size_t)SLICE_MAX * 8);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    if (cudaError_t e = configure_kernels(ctx); e != cudaSuccess) return e;
     return tsb_launch_cluster(ctx, sample_kernel, dim3((unsigned)(batch * CL)), dim3(ACC_THREADS), smem, st, true, (unsigned)CL,
                               logits, logits_stride, uniforms, uni_stride, vocab, temperature, tr, tokens_dev, token_stride,
                               margins_dev, ctx->dev_error);
@@ -794,8 +784,7 @@ cudaError_t launch_argmax_rows(tsb_ctx* ctx, cudaStream_t st, const __half* logi
     // the statistics kernel at temperature 0: max, first argmax and finiteness of every row (rows are "target rows")
     RowStats* stats = reinterpret_cast<RowStats*>(scratch);
     const size_t smem = slice_smem(vocab);
-    cudaError_t e = ensure_smem(accept_stats_kernel, (size_t)SLICE_MAX * 8);
-    if (e != cudaSuccess) return e;
+    if (cudaError_t e = configure_kernels(ctx); e != cudaSuccess) return e;
     return tsb_launch_cluster(ctx, accept_stats_kernel, dim3((unsigned)(n_rows * CL)), dim3(ACC_THREADS), smem, st, true,
                               (unsigned)CL, logits, (const __half*)nullptr, n_rows - 1, vocab, 0.0, TruncShape{0u, 0.0, 0.0}, stats, n_rows,
                               (int64_t)0);

@@ -560,12 +560,8 @@ static cudaError_t launch_attn_t(tsb_ctx* ctx, cudaStream_t st, const AttnPlan& 
                                  const __half* q, int64_t q_stride, const tsb_row_desc* rows_dev, int rows_per_seq,
                                  int n_q_heads, float scale_log2e, float* part_o, float2* part_ml, uint32_t* tickets,
                                  __half* out, ActOut act) {
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<HD, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static SmemOptIn configured;
+    if (cudaError_t e = tsb_opt_in_smem(ctx, attn_partial_kernel<HD, MT>, smem, configured); e != cudaSuccess) return e;
     return tsb_launch_cluster(ctx, attn_partial_kernel<HD, MT>, grid, dim3(ATT_THREADS * MT), smem, st, true,
                               (unsigned)p.cluster_size, view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
                               scale_log2e, p.chunk, p.cluster_size, part_o, part_ml, tickets, out, act, ctx->dev_error);

@@ -18,12 +18,19 @@ struct tsb_ctx {
     int sm_count = 148;
     std::string last_error;
     uint64_t launches = 0;
-    // One device word any kernel may set instead of trapping: 0 = fine.
-    // Read back by tsb_stream_sync.
+    // A small device area every kernel gets a pointer to (TsbDevState below).  Word 0 is the error word any kernel
+    // may set instead of trapping: 0 = fine.  Read back by tsb_stream_sync.
     uint32_t* dev_error = nullptr;
     uint32_t* host_error = nullptr;  // pinned mirror
+    uint32_t wait_limit_us = 1000000;  // bound of every device-side wait (mirrored in word 1 of the device area)
     bool pdl = true;                 // programmatic dependent launch between this ctx's kernels
 };
+
+// Layout of the device area behind tsb_ctx::dev_error (64 bytes, zeroed at creation).
+//   word 0        error word (first writer wins)
+//   word 1        bound of a device-side wait, in microseconds
+//   bytes 8..15   arrival counter of the grid-wide barrier of cooperative kernels (monotonic, 64 bits)
+constexpr size_t TSB_DEV_STATE_BYTES = 64;
 
 // Error words kernels may write (first writer wins).
 enum : uint32_t {
@@ -70,6 +77,22 @@ struct DeviceGuard {
         if (prev >= 0) cudaSetDevice(prev);
     }
 };
+
+// A kernel's opt-in to more than 48 KB of dynamic shared memory is a property of the (device, function) pair:
+// `done` is the call site's table of devices already configured (one per kernel instantiation).  Two host
+// threads racing here both set the same value, which is harmless.
+constexpr int TSB_MAX_DEVICES = 64;
+struct SmemOptIn {
+    bool done[TSB_MAX_DEVICES] = {};
+};
+template <typename Kern>
+inline cudaError_t tsb_opt_in_smem(const tsb_ctx* ctx, Kern kern, size_t bytes, SmemOptIn& table) {
+    const int dev = ctx->device;
+    if (dev >= 0 && dev < TSB_MAX_DEVICES && table.done[dev]) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess && dev >= 0 && dev < TSB_MAX_DEVICES) table.done[dev] = true;
+    return e;
+}
 
 // Launch helper: every kernel of this library goes through here so launches are
 // counted and may carry the programmatic-dependent-launch attribute, which lets
@@ -141,11 +164,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after ~2^26 polls, records why, and lets the caller
-// bail out so the context stays usable.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: bounded by time, not by polls.  The limit (microseconds) sits in the word after the error word;
+// when it runs out the wait records why and returns false, so the caller can drain and leave and the context
+// stays usable.  The clock is read only every 64 failed polls, so a wait that succeeds quickly never touches it.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* err_word) {
-    for (uint32_t i = 0; i < (1u << 26); i++) {
+    unsigned long long t0 = 0, limit_ns = 0;
+    for (uint32_t i = 1;; i++) {
         if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 0) {
+            const unsigned long long now = global_timer_ns();
+            if (t0 == 0) {
+                t0 = now;
+                const uint32_t us = err_word ? *reinterpret_cast<volatile uint32_t*>(err_word + 1) : 0u;
+                limit_ns = (unsigned long long)(us ? us : 1000000u) * 1000ull;
+            } else if (now - t0 > limit_ns) {
+                break;
+            }
+        }
     }
     if (err_word) atomicCAS(err_word, 0u, (uint32_t)TSB_DEV_BARRIER_TIMEOUT);
     return false;

@@ -27,9 +27,10 @@ int32_t tsb_ctx_create(int32_t device_ordinal, tsb_ctx** out) {
     }
     if (e == cudaSuccess) {
         ctx->sm_count = prop.multiProcessorCount;
-        e = cudaMalloc((void**)&ctx->dev_error, sizeof(uint32_t));
+        e = cudaMalloc((void**)&ctx->dev_error, TSB_DEV_STATE_BYTES);
     }
-    if (e == cudaSuccess) e = cudaMemset(ctx->dev_error, 0, sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(ctx->dev_error, 0, TSB_DEV_STATE_BYTES);
+    if (e == cudaSuccess) e = cudaMemcpy(ctx->dev_error + 1, &ctx->wait_limit_us, sizeof(uint32_t), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMallocHost((void**)&ctx->host_error, sizeof(uint32_t));
     if (prev >= 0) cudaSetDevice(prev);
     if (e != cudaSuccess) {
@@ -110,12 +111,44 @@ int32_t tsb_stream_sync(tsb_ctx* ctx, tsb_stream s) {
     TSB_CUDA(ctx, cudaStreamSynchronize((cudaStream_t)s));
     uint32_t w = *ctx->host_error;
     if (w != TSB_DEV_OK) {
+        // the error word, and the grid barrier's arrival counter (a kernel that gave up left it mid-count)
         cudaMemsetAsync(ctx->dev_error, 0, sizeof(uint32_t), (cudaStream_t)s);
+        cudaMemsetAsync(ctx->dev_error + 2, 0, sizeof(unsigned long long), (cudaStream_t)s);
         return tsb_fail(ctx, TSB_ERR_DEVICE, "a kernel reported error word %u (%s)", w,
                         w == TSB_DEV_BARRIER_TIMEOUT ? "bounded barrier wait gave up"
                         : w == TSB_DEV_BAD_INDEX     ? "index outside its table"
                                                      : "non-finite value");
     }
+    return TSB_OK;
+}
+
+int32_t tsb_ctx_set_wait_limit_us(tsb_ctx* ctx, uint32_t microseconds) {
+    if (!ctx) return TSB_ERR_INVALID;
+    TSB_REQUIRE(ctx, microseconds >= 1, "the limit must be at least one microsecond");
+    DeviceGuard g(ctx);
+    TSB_CUDA(ctx, cudaDeviceSynchronize());
+    ctx->wait_limit_us = microseconds;
+    TSB_CUDA(ctx, cudaMemcpy(ctx->dev_error + 1, &ctx->wait_limit_us, sizeof(uint32_t), cudaMemcpyHostToDevice));
+    return TSB_OK;
+}
+
+namespace {
+// One CTA waits on an mbarrier nobody arrives on; the bounded wait must give up, record why and return.
+__global__ void wait_nobody_kernel(uint32_t* err, uint32_t* waited_ok) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *waited_ok = mbar_wait(&bar, 0, err) ? 1u : 0u;
+}
+}  // namespace
+
+int32_t tsb_debug_wait_nobody(tsb_ctx* ctx, tsb_stream s, void* out_u32_dev) {
+    if (!ctx || !out_u32_dev) return TSB_ERR_INVALID;
+    DeviceGuard g(ctx);
+    TSB_CUDA(ctx, tsb_launch(ctx, wait_nobody_kernel, dim3(1), dim3(32), 0, (cudaStream_t)s, false, ctx->dev_error, (uint32_t*)out_u32_dev));
     return TSB_OK;
 }
 

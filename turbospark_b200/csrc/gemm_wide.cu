@@ -433,13 +433,9 @@ cudaError_t launch_gemm_wide_q4k(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w
                                  int64_t x_stride, int tokens, void* y, int64_t y_stride, bool y_f32, void* workspace, void* partials) {
     const int units = (int)(cols / 256);
     const int ksplit = wide_ksplit(ctx, rows, units);
-    static bool configured = false;
+    static SmemOptIn configured;
     const size_t smem_max = 1024 + (size_t)WIDE_RAW_STAGES * WIDE_RAW_BYTES + (size_t)WIDE_B_STAGES * WIDE_CHUNKS * WIDE_NMAX * 16;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_wide_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    if (cudaError_t e = tsb_opt_in_smem(ctx, gemm_wide_q4k_kernel, smem_max, configured); e != cudaSuccess) return e;
     for (int t0 = 0; t0 < tokens; t0 += WIDE_NMAX) {
         const int nt = min(WIDE_NMAX, tokens - t0);
         const int n_pad = (nt + 15) / 16 * 16;
