@@ -85,7 +85,7 @@ TSB_API int32_t tsb_memcpy_d2h(tsb_ctx* ctx, tsb_stream s, void* host, const voi
 /* Replaces PassEncoder commit_and_wait_checked (crates/gpu/src/context/pass.rs:180): waits, then
  * surfaces both CUDA errors and the kernels' own error word. */
 TSB_API int32_t tsb_stream_sync(tsb_ctx* ctx, tsb_stream s);
-/* Every wait inside a kernel (on a copy's arrival barrier, on the grid barrier of a cooperative kernel) is bounded by
+/* Every wait inside a kernel (on a copy's arrival barrier) is bounded by
  * time: when the limit runs out the kernel records TSB_ERR_DEVICE's "bounded barrier wait gave up" word, drains and
  * returns, and the context stays usable.  Default 1 s.  Synchronises the device.  (The reference's Metal passes have
  * no device-side waits; its host-side equivalent is the command-buffer status check of
@@ -278,8 +278,8 @@ typedef struct tsb_accept_out {
  * Replaces the host-side accept step of the round loop (crates/runtime/src/speculative.rs:694-754,
  * 861-879) and select / shaped_distribution / residual (crates/selection/src/choose.rs:62-232,
  * distribution.rs:57-125).  Temperature, top_k (<= 256), top_p and min_p are applied on the device (the support is
- * the reference's rank-order prefix); repetition, presence and frequency penalties need the token history and are
- * refused with TSB_ERR_UNSUPPORTED. */
+ * the reference's rank-order prefix); repetition, presence and frequency penalties need the token history: this entry
+ * point refuses them with TSB_ERR_UNSUPPORTED, tsb_accept_history applies them. */
 TSB_API int32_t tsb_accept(tsb_ctx* ctx, tsb_stream s, const void* target_logits_f16, const void* draft_logits_f16,
                            const int32_t* proposals, const uint64_t* uniforms, int32_t batch, int32_t k,
                            int32_t vocab, const tsb_shaping* shaping, tsb_accept_out* out_dev, void* scratch,
@@ -291,6 +291,27 @@ TSB_API size_t tsb_accept_scratch_bytes(int32_t batch, int32_t k, int32_t vocab)
 TSB_API int32_t tsb_sample(tsb_ctx* ctx, tsb_stream s, const void* logits_f16, const uint64_t* uniforms,
                            int32_t batch, int32_t vocab, const tsb_shaping* shaping, int32_t* tokens_dev,
                            double* margins_dev, void* scratch, size_t scratch_bytes);
+
+/* tsb_accept / tsb_sample with the history penalties of the shaping record (crates/selection/src/penalty.rs:15-82,
+ * applied at choose.rs:139-154 before the softmax): repetition_penalty attenuates every distinct id of the history
+ * once (s > 0 ? s / penalty : s * penalty, in f32), presence_penalty + frequency_penalty * count is subtracted for
+ * every distinct id of the GENERATED suffix of the history.  Per stream b: history_dev[b * hist_stride + j] for
+ * j < hist_len_dev[b] is the committed stream (prompt, then what this turn generated, the confirmed token that
+ * entered the round included), generated_dev[b] how many of its last entries this turn generated.  Which history a
+ * row sees follows the round loop (crates/runtime/src/speculative.rs:636-648,701-734): a drafter row was shaped with
+ * the history of the round's start, target row i after proposals 0..i were committed (they count as history and as
+ * generated).  With the identity penalties the results equal tsb_accept / tsb_sample.  All arrays are device memory;
+ * scratch: tsb_accept_history_scratch_bytes(batch, k, vocab) (k = 0 for tsb_sample_history). */
+TSB_API int32_t tsb_accept_history(tsb_ctx* ctx, tsb_stream s, const void* target_logits_f16, const void* draft_logits_f16,
+                                   const int32_t* proposals, const uint64_t* uniforms, int32_t batch, int32_t k, int32_t vocab,
+                                   const tsb_shaping* shaping, const int32_t* history_dev, int32_t hist_stride,
+                                   const int32_t* hist_len_dev, const int32_t* generated_dev, tsb_accept_out* out_dev,
+                                   void* scratch, size_t scratch_bytes);
+TSB_API int32_t tsb_sample_history(tsb_ctx* ctx, tsb_stream s, const void* logits_f16, const uint64_t* uniforms, int32_t batch,
+                                   int32_t vocab, const tsb_shaping* shaping, const int32_t* history_dev, int32_t hist_stride,
+                                   const int32_t* hist_len_dev, const int32_t* generated_dev, int32_t* tokens_dev,
+                                   double* margins_dev, void* scratch, size_t scratch_bytes);
+TSB_API size_t tsb_accept_history_scratch_bytes(int32_t batch, int32_t k, int32_t vocab);
 
 /* Uniform sources: mode 0 = derive_step_value(seed, step) (crates/selection/src/derive.rs:20-48),
  * mode 1 = Philox4x32-10 keyed by seed with counter = step (this backend's addition). */
@@ -419,7 +440,57 @@ TSB_API int32_t tsb_producer_verify(tsb_session* s, int32_t stream, const int32_
  * (crates/runtime/src/families/qwen/batched_scratch.rs:97-124). */
 TSB_API int32_t tsb_producer_verify_tree(tsb_session* s, int32_t stream, const int32_t* feed, const int32_t* slot_parent,
                                          int32_t n, int64_t base, void* logits_out_host);
+/* compact_tree (producer.rs:287-291): moves the accepted path's slots (path[0] == 0, increasing) to rows 0..keep of
+ * the verify, in the target's cache and - for the slots the drafter ran over - in the drafter's; the record of fed
+ * tokens takes the path's tokens from the last verify_tree. */
 TSB_API int32_t tsb_producer_compact_tree(tsb_session* s, int32_t stream, int64_t base, const uint32_t* path, int32_t keep);
+/* One node of a drafted tree (crates/runtime/src/dflash_tree.rs:10-16): candidate `cand` at `depth` below the anchor,
+ * under node `parent` (-1 for a child of the anchor).  Node i sits in slot i + 1 of the verify. */
+typedef struct tsb_tree_node {
+    int32_t depth, cand, parent;
+} tsb_tree_node;
+/* The trees this session's producer drafts: `nodes` drafted nodes per round in at most `levels` levels.  best_first
+ * == 0: the static shape in which every node of level l gets its branching[l] most likely next tokens, cut
+ * breadth-first at `nodes`.  best_first == 1: grown by path probability (dflash_best_first_tree,
+ * crates/runtime/src/dflash_tree.rs:30-82) with `cand` (1..8) candidates scored under every expanded node - a
+ * parent's children share a softmax over the drafter's logits of those candidates.  nodes == 0 turns trees off. */
+TSB_API int32_t tsb_session_set_tree(tsb_session* s, int32_t nodes, int32_t levels, const int32_t* branching /* [levels], may be NULL when best_first */,
+                                     int32_t best_first, int32_t cand);
+/* tree_nodes (producer.rs:256-262): nodes per tree round, 0 when the producer verifies chains only. */
+TSB_API int32_t tsb_producer_tree_nodes(const tsb_session* s);
+/* draft_tree (producer.rs:264-275): a tree of up to `nodes` nodes anchored at `anchor` (the token at `base`), parents
+ * before children; tokens_out[i] is node i's token.  Greedy drafter picks (the reference runs tree rounds at
+ * temperature 0 only).  The drafter's cursor stays at `base`. */
+TSB_API int32_t tsb_producer_draft_tree(tsb_session* s, int32_t stream, int32_t anchor, int64_t base, int32_t nodes,
+                                        tsb_tree_node* tree_out, int32_t* tokens_out, int32_t* n_out);
+/* dflash_tree_slot_parents (dflash_tree.rs:117-124): slot 0 is the anchor (-1), node i sits at slot i + 1 under its
+ * parent's slot.  out has n + 1 entries. */
+TSB_API int32_t tsb_tree_slot_parents(const tsb_tree_node* tree, int32_t n, int32_t* out);
+/* dflash_best_first_tree over a fixed score table scores[depth * branch + cand] (the shape the reference's own tests
+ * use, dflash_tree.rs:130-190): returns the number of nodes written. */
+TSB_API int32_t tsb_best_first_tree(const float* scores, int32_t depth_max, int32_t branch, int32_t nodes, tsb_tree_node* out);
+/* dflash_tree_accept (dflash_tree.rs:92-115): from the anchor, step into the child whose token is the target's pick
+ * at the current node's row while there is one.  target_pick has n + 1 entries (slot order).  Returns the number of
+ * accepted node ids written to accepted_out. */
+TSB_API int32_t tsb_tree_accept(const tsb_tree_node* tree, const int32_t* tokens, int32_t n, const int32_t* target_pick, int32_t* accepted_out);
+/* draft_block (producer.rs:236-254): `block` proposals for positions base + 1 ..= base + block in one call, the
+ * drafter's greedy picks, each fed back as the next step's input (the last step is taken for its cache row alone, as
+ * the step-wise loop does).  drafts_block_passes answers 0: the round loop of this library drives draft_step. */
+TSB_API int32_t tsb_producer_draft_block(tsb_session* s, int32_t stream, int32_t anchor, int64_t base, int32_t block,
+                                         int32_t* proposals_out);
+TSB_API int32_t tsb_producer_drafts_block_passes(const tsb_session* s);
+/* commit_pending / discard_pending (producer.rs:332-350).  A verify leaves its rows pending until the round's outcome
+ * is known.  commit_pending(keep_rows) closes a round that kept `keep_rows` rows (nothing is deferred here - K/V rows
+ * are final when written - so it only checks the count and clears the mark; a no-op when nothing is pending).
+ * discard_pending rewinds the target's cursor and the record of fed tokens to where the verify started and the
+ * drafter to at most one row past it; the loops call it when a round fails between verify and commit. */
+TSB_API int32_t tsb_producer_commit_pending(tsb_session* s, int32_t stream, int32_t keep_rows);
+TSB_API int32_t tsb_producer_discard_pending(tsb_session* s, int32_t stream);
+/* supports_retaining_rollback (producer.rs:352-358): 1 - a pure-attention cache keeps rows in place.
+ * supports_headless_prefill (producer.rs:306-322): 1 - the drafter is a stand-alone decoder that reads nothing of
+ * the trunk's final norm. */
+TSB_API int32_t tsb_producer_supports_retaining_rollback(const tsb_session* s);
+TSB_API int32_t tsb_producer_supports_headless_prefill(const tsb_session* s);
 TSB_API int64_t tsb_producer_checkpoint(tsb_session* s, int32_t stream);
 TSB_API int32_t tsb_producer_rollback(tsb_session* s, int32_t stream, int64_t point);
 TSB_API int32_t tsb_producer_rollback_retaining(tsb_session* s, int32_t stream, int64_t point, int32_t keep_rows);
@@ -454,6 +525,9 @@ typedef struct tsb_run_config {
     /* 1: keep what the stream's caches already hold for the longest prefix of the prompt whose token ids equal the
      * ids that were fed (try_reuse_prefix, crates/runtime/src/producer.rs:21-47) instead of resetting the stream */
     int32_t reuse_prefix;
+    /* 1: tree rounds grow their tree best-first (dflash_best_first_tree) with tree_cand candidates per expanded node
+     * and at most tree_levels levels, instead of the static branching shape */
+    int32_t tree_best_first, tree_cand;
 } tsb_run_config;
 
 typedef struct tsb_run_result {

@@ -1086,6 +1086,7 @@ TSO_API int tso_accept_round(const uint16_t* target_logits, const uint16_t* draf
                              const int32_t* history, int64_t nh, uint64_t generated, int32_t* out_accepted,
                              int32_t* out_tokens, double* margins) {
     std::vector<int32_t> hist(history, history + nh);
+    const uint64_t generated0 = generated;
     int accepted = 0;
     int draws = 0;
     bool sampled = cfg->temperature != 0.0;
@@ -1111,8 +1112,10 @@ TSO_API int tso_accept_round(const uint16_t* target_logits, const uint16_t* draf
             Shaped p, q;
             int rc = shaped_distribution(row, v, *cfg, hist.data(), (int64_t)hist.size(), generated, p);
             if (rc) return -rc;
-            rc = shaped_distribution(draft_logits + (int64_t)i * v, v, *cfg, hist.data(), (int64_t)hist.size(),
-                                     generated, q);
+            // q is the distribution proposal i was DRAWN from: shaped when the drafter ran, with the history and the
+            // generated count of the round's start (speculative.rs:636-648 stores it, :708 reads it back) - the
+            // proposals accepted since then are not part of it
+            rc = shaped_distribution(draft_logits + (int64_t)i * v, v, *cfg, hist.data(), nh, generated0, q);
             if (rc) return -rc;
             double r = to_unit_interval(uniforms[draws++]);
             double qx = shaped_probability(q, (uint32_t)x), px = shaped_probability(p, (uint32_t)x);

@@ -83,15 +83,166 @@ def test_tree_verify_matches_the_oracle_and_compaction_restores_a_chain(rig, ora
     got = sess.verify_tree(feed, parent, base)
     want = ost.forward(feed, base, parent=parent)
     _close(oracle, got, want, rel=4e-3, abs_=4e-3)
-    # accept the branch 0 -> 5 -> 6, compact it to rows 0..2 and continue as a chain
+    # accept the branch 0 -> 5 -> 6: the reference's own sequence (crates/runtime/src/speculative.rs:530-567) compacts
+    # the path to rows 0..2, cuts the verify back to them, closes the round and records what was kept
     sess.compact_tree(base, [0, 5, 6])
-    sess.rollback_retaining(base, 3) if False else None  # the tree verify did not advance past base + 8
-    sess.kv(0).set_cursor(0, base + 3)
+    sess.rollback_retaining(base, 3)
+    sess.commit_pending(3)
+    kept = [int(feed[0]), int(feed[5]), int(feed[6])]
+    sess.record_committed(kept, base)
+    sess.rewind_drafter(base + 2)
+    assert sess.checkpoint() == base + 3
     ost.cursor = base
-    ost.forward([int(feed[0]), int(feed[5]), int(feed[6])], base)
+    ost.forward(kept, base)
+    # the drafter replays the record of fed tokens: its next step must see the path's tokens, not zeros
+    odst = oracle.State(rig["od"])
+    odst.forward(list(prompt) + kept, 0, want_logits=False)
     nxt = 77
+    _close(oracle, sess.draft_step(nxt, base + 2), odst.forward([nxt], base + 3)[0], rel=4e-3, abs_=4e-3)
     _close(oracle, sess.produce(nxt, base + 3), ost.forward([nxt], base + 3)[0], rel=4e-3, abs_=4e-3)
+    # and a later turn finds the kept rows under the tokens that were really fed
+    assert sess.try_reuse_prefix(list(prompt) + kept + [nxt, 5]) == len(prompt) + 4
+    # a second compaction of the same verify, and keeping rows nobody recorded, are refused
+    with pytest.raises(tsb.TsbError):
+        sess.compact_tree(base, [0, 5, 6])
     sess.close()
+
+
+def test_rollback_retaining_after_a_tree_verify_needs_the_compaction_first(rig, oracle):
+    tsb = rig["tsb"]
+    sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 8)
+    for i in range(10):
+        sess.produce_prefill(3 + i, i)
+    base = sess.checkpoint()
+    sess.verify_tree([1, 2, 3, 4], [-1, 0, 0, 1], base)
+    with pytest.raises(tsb.TsbError):
+        sess.rollback_retaining(base, 2)  # the record of fed tokens ends at base: nothing says which slots to keep
+    # discard_pending (crates/runtime/src/producer.rs:346-350) puts the stream back where the verify started
+    sess.discard_pending()
+    assert sess.checkpoint() == base
+    a = sess.verify([1, 2, 3], base)
+    sess.discard_pending()
+    assert sess.checkpoint() == base
+    b = sess.verify([1, 2, 3], base)
+    assert np.array_equal(a, b)
+    sess.commit_pending(3)
+    sess.commit_pending(3)  # nothing pending: a no-op, as in the reference
+    assert sess.supports_retaining_rollback() and sess.supports_headless_prefill() and not sess.drafts_block_passes()
+    sess.close()
+
+
+def _argmax(oracle, row16):
+    v = oracle.f16_bits_to_f32(row16)
+    return int(np.flatnonzero(v == v.max())[0])
+
+
+@pytest.mark.parametrize("shape", [dict(nodes=10, branching=(2, 2, 1)), dict(nodes=9, levels=3, best_first=True, cand=3)])
+def test_tree_rounds_driven_through_the_producer_calls_equal_the_sequential_loop(rig, oracle, shape):
+    """The reference's round loop (crates/runtime/src/speculative.rs:461-575) written against the producer calls -
+    tree_nodes, draft_tree, verify_tree, the accept walk, compact_tree, rollback_retaining, commit_pending,
+    record_committed, rewind_drafter - must leave what greedy sequential decoding leaves, for the static shape and for
+    the best-first tree."""
+    tsb = rig["tsb"]
+    sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 16)
+    rng = np.random.default_rng(31)
+    prompt = rng.integers(0, rig["cfg"].vocab, size=20).astype(np.int32)
+    budget = 30
+    _, want, _ = sess.sequential_run(prompt, tsb.run_config(tsb.shaping(temperature=0.0), budget, 3))
+    sess.reset()
+    assert sess.tree_nodes() is None
+    with pytest.raises(tsb.TsbError):
+        sess.draft_tree(1, 5, 4)  # chains only until a tree shape is set
+    sess.set_tree(**shape)
+    nodes = sess.tree_nodes()
+    assert nodes == shape["nodes"]
+    for i, t in enumerate(prompt[:-1]):
+        sess.produce_prefill(int(t), i)
+    logits = sess.produce(int(prompt[-1]), len(prompt) - 1)
+    sess.prime_drafter(int(prompt[-1]), len(prompt) - 2)
+    history = list(prompt)
+    emitted = []
+    nxt = _argmax(oracle, logits)
+    accepted_total, first_round = 0, True
+    while len(emitted) < budget:
+        emitted.append(nxt)
+        if len(emitted) == budget:
+            break
+        history.append(nxt)
+        base = len(history) - 1
+        if budget - len(emitted) < 3:  # not enough room for a full-depth tree: plain steps (the loop's truncated rounds)
+            logits = sess.produce(nxt, base)
+            sess.rewind_drafter(base)
+            nxt = _argmax(oracle, logits)
+            continue
+        depth, cand, parent, toks = sess.draft_tree(nxt, base, nodes)
+        assert all(p < i for i, p in enumerate(parent))  # parents precede children
+        if first_round:
+            # the first node is the drafter's most likely token after the anchor: what one greedy draft step proposes
+            ref = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 16)
+            for i, t in enumerate(history[:-1]):
+                ref.produce_prefill(int(t), i)
+            assert int(toks[0]) == _argmax(oracle, ref.draft_step(nxt, base - 1)) and depth[0] == 0 and parent[0] == -1
+            ref.close()
+            first_round = False
+        slot_parent = np.array([-1] + [int(p) + 1 for p in parent], dtype=np.int32)  # dflash_tree_slot_parents
+        feed = np.concatenate([[nxt], toks]).astype(np.int32)
+        point = sess.checkpoint()
+        rows = sess.verify_tree(feed, slot_parent, base)
+        path, at, bonus = [0], -1, None
+        while True:
+            pick = _argmax(oracle, rows[at + 1])
+            hit = [i for i in range(len(toks)) if parent[i] == at and toks[i] == pick]
+            if not hit or len(emitted) + 1 >= budget:
+                bonus = pick
+                break
+            path.append(hit[0] + 1)
+            at = hit[0]
+            emitted.append(pick)
+            history.append(pick)
+        committed = len(path) - 1
+        accepted_total += committed
+        sess.compact_tree(base, path)
+        if committed + 1 < len(feed):
+            sess.rollback_retaining(point, committed + 1)
+        sess.commit_pending(committed + 1)
+        sess.record_committed([int(feed[s]) for s in path], base)
+        sess.rewind_drafter(base + committed)
+        nxt = bonus
+    assert emitted == list(want)
+    sess.close()
+
+
+def test_best_first_tree_rounds_in_the_library_loop_equal_the_sequential_loop(rig, oracle):
+    tsb = rig["tsb"]
+    sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 16)
+    rng = np.random.default_rng(5)
+    prompt = rng.integers(0, rig["cfg"].vocab, size=24).astype(np.int32)
+    plain = tsb.run_config(tsb.shaping(temperature=0.0), 36, 3)
+    tree = tsb.run_config(tsb.shaping(temperature=0.0), 36, 3, tree_nodes=8, tree_best_first=True, tree_cand=3, tree_levels=3)
+    _, seq_emit, _ = sess.sequential_run(prompt, plain)
+    _, emit, res = sess.spec_run(prompt, tree)
+    assert np.array_equal(seq_emit, emit) and res.new_tokens == 36
+    sess.close()
+
+
+def test_draft_block_gives_the_greedy_chain_of_draft_steps(rig, oracle):
+    tsb = rig["tsb"]
+    sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 8)
+    prompt = [4, 9, 200, 31, 77, 5]
+    for i, t in enumerate(prompt):
+        sess.produce_prefill(t, i)
+    base = len(prompt) - 1  # the anchor's position; the drafter catches up to it from the record of fed tokens
+    block = sess.draft_block(prompt[-1], base, 4)
+    # the same through single steps on a second session
+    ref = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 8)
+    for i, t in enumerate(prompt):
+        ref.produce_prefill(t, i)
+    tok, want = prompt[-1], []
+    for i in range(4):
+        tok = _argmax(oracle, ref.draft_step(tok, base + i - 1))
+        want.append(tok)
+    assert list(block) == want
+    sess.close(), ref.close()
 
 
 @pytest.mark.parametrize("block", [1, 4])

@@ -23,7 +23,7 @@ FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "--expt-relaxed-constexpr",
     "-I", INCLUDE,
-]
+] + os.environ.get("TSB_NVCC_EXTRA", "").split()
 
 
 def _sources():

@@ -17,7 +17,8 @@ class TsbError(RuntimeError):
 
 
 def lib_path():
-    return os.path.join(_HERE, "libtsb.so")
+    # TSB_LIB points at another build of the same library (kernel experiments); the default is the in-tree one
+    return os.environ.get("TSB_LIB") or os.path.join(_HERE, "libtsb.so")
 
 
 class RowDesc(C.Structure):
@@ -69,7 +70,7 @@ def lib():
         L.tsb_launch_count.argtypes = [C.c_void_p]
         L.tsb_uniform_u64.restype = C.c_uint64
         L.tsb_uniform_u64.argtypes = [C.c_int32, C.c_uint64, C.c_uint64]
-        for name in ("tsb_attn_scratch_bytes", "tsb_accept_scratch_bytes"):
+        for name in ("tsb_attn_scratch_bytes", "tsb_accept_scratch_bytes", "tsb_accept_history_scratch_bytes"):
             if hasattr(L, name):
                 getattr(L, name).restype = C.c_size_t
         if hasattr(L, "tsb_kv_cursor"):
@@ -231,6 +232,23 @@ class Ctx:
         self.check(lib().tsb_sample(self.h, stream, _vp(logits), _vp(uniforms), C.c_int32(batch), C.c_int32(vocab),
                                     C.byref(shaping_cfg), _vp(tokens), _vp(margins), _vp(scratch),
                                     C.c_size_t(scratch.nbytes)))
+
+    def accept_history_scratch_bytes(self, batch, k, vocab):
+        return int(lib().tsb_accept_history_scratch_bytes(C.c_int32(batch), C.c_int32(k), C.c_int32(vocab)))
+
+    def accept_history(self, target_logits, draft_logits, proposals, uniforms, batch, k, vocab, shaping_cfg, history, hist_stride,
+                       hist_len, generated, out, scratch, stream=None):
+        """tsb_accept with the history penalties: history [batch, hist_stride] i32, hist_len / generated [batch] i32 (device)."""
+        self.check(lib().tsb_accept_history(self.h, stream, _vp(target_logits), _vp(draft_logits), _vp(proposals), _vp(uniforms),
+                                            C.c_int32(batch), C.c_int32(k), C.c_int32(vocab), C.byref(shaping_cfg), _vp(history),
+                                            C.c_int32(hist_stride), _vp(hist_len), _vp(generated), _vp(out), _vp(scratch),
+                                            C.c_size_t(scratch.nbytes)))
+
+    def sample_history(self, logits, uniforms, batch, vocab, shaping_cfg, history, hist_stride, hist_len, generated, tokens, margins,
+                       scratch, stream=None):
+        self.check(lib().tsb_sample_history(self.h, stream, _vp(logits), _vp(uniforms), C.c_int32(batch), C.c_int32(vocab),
+                                            C.byref(shaping_cfg), _vp(history), C.c_int32(hist_stride), _vp(hist_len), _vp(generated),
+                                            _vp(tokens), _vp(margins), _vp(scratch), C.c_size_t(scratch.nbytes)))
 
     def moe_route(self, router_logits, tokens, n_experts, k, ids_out, weights_out, scale=None, stream=None):
         self.check(lib().tsb_moe_route(self.h, stream, _vp(router_logits), C.c_int32(tokens), C.c_int32(n_experts), C.c_int32(k),

@@ -23,6 +23,17 @@ cudaError_t launch_accept(tsb_ctx* ctx, cudaStream_t st, const __half* target, c
 cudaError_t launch_sample(tsb_ctx* ctx, cudaStream_t st, const __half* logits, int64_t logits_stride,
                           const uint64_t* uniforms, int uni_stride, int batch, int vocab, AcceptShape shape,
                           int32_t* tokens_dev, int token_stride, double* margins_dev, void* scratch);
+// The same two operators with the history penalties of the shaping record applied first (repetition over the whole
+// history, presence / frequency over its generated suffix): history[b * hist_stride + j] for j < hist_len[b],
+// generated[b] of its last entries produced in this turn.  scratch: accept_history_scratch_bytes(batch, k, vocab).
+size_t accept_history_scratch_bytes(int batch, int k, int vocab);
+cudaError_t launch_accept_history(tsb_ctx* ctx, cudaStream_t st, const __half* target, const __half* draft, const int32_t* proposals,
+                                  int prop_stride, const uint64_t* uniforms, int batch, int k, int vocab, const tsb_shaping& sh,
+                                  const int32_t* history, int hist_stride, const int32_t* hist_len, const int32_t* generated,
+                                  tsb_accept_out* out_dev, void* scratch);
+cudaError_t launch_sample_history(tsb_ctx* ctx, cudaStream_t st, const __half* logits, const uint64_t* uniforms, int batch, int vocab,
+                                  const tsb_shaping& sh, const int32_t* history, int hist_stride, const int32_t* hist_len,
+                                  const int32_t* generated, int32_t* tokens_dev, double* margins_dev, void* scratch);
 // The `width` (<= 8) largest logits of rows rows_dev[0..n_rows) of a [*, vocab] matrix, value descending, token id
 // ascending on ties; row r's picks land in out_dev[r * 8 ..].
 cudaError_t launch_topk_rows(tsb_ctx* ctx, cudaStream_t st, const __half* logits, int vocab, const int32_t* rows_dev, int n_rows,

@@ -61,11 +61,12 @@ __device__ __forceinline__ uint32_t tile_off(int r, int c) {
 // Grid: x = KV chunks (a multiple of the cluster size; the CTAs of a cluster hold consecutive chunks of the same
 // queries), y = kv head * query tiles, z = streams.
 template <int HD, int MT>
-__global__ void __maxnreg__(136)
+__global__ void __maxnreg__(128)
     attn_partial_kernel(KvView kv, int layer, const __half* __restrict__ q, int64_t q_stride,
                         const tsb_row_desc* __restrict__ rows, int rows_per_seq, int n_q_heads, float scale_log2e,
                         int chunk, int cluster_size, float* __restrict__ part_o, float2* __restrict__ part_ml,
-                        uint32_t* __restrict__ tickets, __half* __restrict__ out, ActOut act, uint32_t* __restrict__ err) {
+                        uint32_t* __restrict__ tickets, __half* __restrict__ out, ActOut act, uint32_t* __restrict__ err,
+                        int defer_merge) {
     constexpr int CH = HD / 8;         // 16-byte chunks per token row
     constexpr int KS = HD / 16;        // k steps of S = Q K^T
     constexpr int NO = HD / 8;         // n tiles of O
@@ -83,6 +84,13 @@ __global__ void __maxnreg__(136)
     const int gid = lane >> 2, tig = lane & 3;
     const int mt = warp % MT, sl = warp / MT;
     const int nkv = kv.kv_heads, G = n_q_heads / nkv;
+#ifdef TSB_ATTN_TRACE
+    unsigned long long* trc = defer_merge && tickets ? reinterpret_cast<unsigned long long*>(tickets) + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 : nullptr;
+#define TRC(i) if (trc && threadIdx.x == 0) trc[i] = global_timer_ns()
+#else
+#define TRC(i)
+#endif
+    TRC(0);
     const int n_queries = rows_per_seq * G;
     const int n_qtiles = (n_queries + QT - 1) / QT;
     const int split = blockIdx.x;
@@ -134,7 +142,9 @@ __global__ void __maxnreg__(136)
     // tiles made only of committed rows can start moving while the kernel that produces q is still running
     const bool early = t_begin + NST * TILE_TOKENS <= base;
     if (early) prologue();
+    TRC(1);
     pdl_wait();
+    TRC(2);
     if (!early) prologue();
 
     // ---- this lane's two queries (rows gid and gid+8 of the warp's mma tile)
@@ -171,6 +181,7 @@ __global__ void __maxnreg__(136)
         const int stage = tile % NST;
         cp_async_wait<NST - 1>();  // all but the NST - 1 youngest groups have landed: tile `tile` is here
         __syncthreads();
+        if (tile == 0) { TRC(3); }
         const uint32_t ktile = smem_base + stage * 2 * TILE_BYTES, vtile = ktile + TILE_BYTES;
         const int tok0 = sl * WTOK;  // this warp's tokens of the tile
         const int pos0 = t_begin + tile * TILE_TOKENS + tok0;
@@ -268,6 +279,7 @@ __global__ void __maxnreg__(136)
         else cp_async_commit();
     }
     cp_async_wait<0>();
+    TRC(4);
     pdl_launch_dependents();
 
     // ---- every warp leaves its (m, l, O) for its 16 queries in shared memory: wo[warp][16][HDP], wml[warp][16]
@@ -319,13 +331,30 @@ __global__ void __maxnreg__(136)
             accv[0] += a.x * wgt, accv[1] += a.y * wgt, accv[2] += a.z * wgt, accv[3] += a.w * wgt;
             accv[4] += b2.x * wgt, accv[5] += b2.y * wgt, accv[6] += b2.z * wgt, accv[7] += b2.w * wgt;
         }
+        if (defer_merge) {
+            // partials-only launch (no cluster): the CTA's share goes straight to memory, the merge launch takes over
+            const int qi = qtile * QT + ql;
+            if (qi < n_queries) {
+                const size_t pi = ((size_t)(row_first + qi / G) * n_q_heads + (kvh * G + qi % G)) * gridDim.x + blockIdx.x;
+                float4* po = reinterpret_cast<float4*>(part_o + pi * HD + part * 8);
+                po[0] = make_float4(accv[0], accv[1], accv[2], accv[3]);
+                po[1] = make_float4(accv[4], accv[5], accv[6], accv[7]);
+                if (part == 0) part_ml[pi] = make_float2(m, den);
+            }
+            continue;
+        }
         float4* dst = reinterpret_cast<float4*>(co + (size_t)ql * HD + part * 8);
         dst[0] = make_float4(accv[0], accv[1], accv[2], accv[3]);
         dst[1] = make_float4(accv[4], accv[5], accv[6], accv[7]);
         if (part == 0) cml[ql] = make_float2(m, den);
     }
+    if (defer_merge) {
+        TRC(6);
+        return;
+    }
     if (cluster_size > 1) cluster.sync();
     else __syncthreads();
+    TRC(5);
 
     // CTA `rank` of the cluster finishes queries rank, rank + cluster_size, ... of the tile
     const int rank = cluster_size > 1 ? (int)cluster.block_rank() : 0;
@@ -370,7 +399,7 @@ __global__ void __maxnreg__(136)
         }
         const int row = row_first + (active ? qi / G : 0), head = kvh * G + (active ? qi % G : 0);
         const int e0 = head * HD + part * 8;
-        if (n_clusters == 1) {
+        if (n_clusters == 1 && !defer_merge) {
             const float inv = den > 0.f ? 1.0f / den : 0.f;
 #pragma unroll
             for (int i = 0; i < 8; i++) accv[i] *= inv;
@@ -392,8 +421,9 @@ __global__ void __maxnreg__(136)
     }
     // nobody may leave while a neighbour still reads its shared memory: arrive now, wait just before leaving, so the
     // barrier's latency hides behind the ticket and the last merge
+    TRC(6);
     if (cluster_size > 1) cluster.barrier_arrive();
-    if (n_clusters == 1) {
+    if (n_clusters == 1 || defer_merge) {  // deferred: whoever runs next merges the shares left in memory
         if (cluster_size > 1) cluster.barrier_wait();
         return;
     }
@@ -451,6 +481,75 @@ __global__ void __maxnreg__(136)
         if (act.xp) act_store8(accv, act.xp, act.xs, row, e0, (n_q_heads * HD) >> 8, active);
     }
     if (cluster_size > 1) cluster.barrier_wait();
+}
+
+// ---- merge of the split-KV shares left by a partials-only launch: one CTA per (row, head).
+// out = sum_c O_c 2^(m_c - m) / sum_c l_c 2^(m_c - m)   (crates/gpu/src/shaders/attention.metal:983-1031)
+// The CTA's threads are (split group, eight-column part): a group folds its splits c = g, g + n_groups, ... in that
+// order into one (m, l, O) share, the shares meet in shared memory, and the first group combines them in group order -
+// a fixed summation tree that depends only on the number of splits.
+constexpr int MERGE_THREADS = 256;
+__global__ void __launch_bounds__(MERGE_THREADS)
+    attn_merge_kernel(const float* __restrict__ part_o, const float2* __restrict__ part_ml, int n_splits, int n_q_heads, int head_dim,
+                      __half* __restrict__ out, ActOut act) {
+    __shared__ float sh_o[MERGE_THREADS * 8];
+    __shared__ float2 sh_ml[MERGE_THREADS];
+    const int lpi = head_dim >> 3;              // threads per group (one per eight columns)
+    const int n_groups = MERGE_THREADS / lpi;   // split groups
+    const int grp = threadIdx.x / lpi, part = threadIdx.x % lpi;
+    const int item = blockIdx.x;                // row * n_q_heads + head
+    pdl_wait();
+    const size_t pi = (size_t)item * n_splits;
+    float m = -INFINITY, den = 0.f, accv[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) accv[i] = 0.f;
+    {
+        for (int c = grp; c < n_splits; c += n_groups) m = fmaxf(m, __ldcg(&part_ml[pi + c]).x);
+        const float mu = (m == -INFINITY) ? 0.f : m;
+        for (int c = grp; c < n_splits; c += n_groups) {
+            const float2 v = __ldcg(&part_ml[pi + c]);
+            const float wgt = exp2f(v.x - mu);
+            den += v.y * wgt;
+            const float4* po = reinterpret_cast<const float4*>(part_o + (pi + c) * head_dim + part * 8);
+            const float4 a = __ldcg(po), b2 = __ldcg(po + 1);
+            accv[0] += a.x * wgt, accv[1] += a.y * wgt, accv[2] += a.z * wgt, accv[3] += a.w * wgt;
+            accv[4] += b2.x * wgt, accv[5] += b2.y * wgt, accv[6] += b2.z * wgt, accv[7] += b2.w * wgt;
+        }
+    }
+    pdl_launch_dependents();
+#pragma unroll
+    for (int i = 0; i < 8; i++) sh_o[threadIdx.x * 8 + i] = accv[i];
+    sh_ml[threadIdx.x] = make_float2(m, den);
+    __syncthreads();
+    if (threadIdx.x >= 32 && threadIdx.x >= lpi) return;  // the first warp finishes (its lanes past lpi only take part in the shuffles)
+    const bool active = threadIdx.x < lpi;
+    float mm = -INFINITY, dd = 0.f, o[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) o[i] = 0.f;
+    if (active) {
+        for (int g = 0; g < n_groups; g++) mm = fmaxf(mm, sh_ml[g * lpi + part].x);
+        const float mu = (mm == -INFINITY) ? 0.f : mm;
+        for (int g = 0; g < n_groups; g++) {
+            const float2 v = sh_ml[g * lpi + part];
+            const float wgt = exp2f(v.x - mu);
+            dd += v.y * wgt;
+#pragma unroll
+            for (int i = 0; i < 8; i++) o[i] += sh_o[(g * lpi + part) * 8 + i] * wgt;
+        }
+        const float inv = dd > 0.f ? 1.0f / dd : 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) o[i] *= inv;
+    }
+    const int row = item / n_q_heads, head = item % n_q_heads;
+    const int e0 = head * head_dim + part * 8;
+    if (out && active) {
+        uint4 pk;
+        __half* pp = reinterpret_cast<__half*>(&pk);
+#pragma unroll
+        for (int i = 0; i < 8; i++) pp[i] = __float2half_rn(o[i]);
+        *reinterpret_cast<uint4*>(out + (size_t)row * n_q_heads * head_dim + e0) = pk;
+    }
+    if (act.xp) act_store8(o, act.xp, act.xs, row, active ? e0 : 0, (n_q_heads * head_dim) >> 8, active);
 }
 
 }  // namespace
@@ -559,17 +658,39 @@ template <int HD, int MT>
 static cudaError_t launch_attn_t(tsb_ctx* ctx, cudaStream_t st, const AttnPlan& p, dim3 grid, size_t smem, KvView view, int layer,
                                  const __half* q, int64_t q_stride, const tsb_row_desc* rows_dev, int rows_per_seq,
                                  int n_q_heads, float scale_log2e, float* part_o, float2* part_ml, uint32_t* tickets,
-                                 __half* out, ActOut act) {
+                                 __half* out, ActOut act, int defer_merge = 0) {
     static SmemOptIn configured;
     if (cudaError_t e = tsb_opt_in_smem(ctx, attn_partial_kernel<HD, MT>, smem, configured); e != cudaSuccess) return e;
     return tsb_launch_cluster(ctx, attn_partial_kernel<HD, MT>, grid, dim3(ATT_THREADS * MT), smem, st, true,
                               (unsigned)p.cluster_size, view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
-                              scale_log2e, p.chunk, p.cluster_size, part_o, part_ml, tickets, out, act, ctx->dev_error);
+                              scale_log2e, p.chunk, p.cluster_size, part_o, part_ml, tickets, out, act, ctx->dev_error, defer_merge);
+}
+
+// TSB_ATTN_MODE=0 keeps the single launch whose CTAs merge through clusters and a ticket; the default (1) is the
+// partials launch followed by the merge launch.
+static bool attn_split_merge_mode() {
+    static int mode = -1;
+    if (mode < 0) {
+        const char* env = getenv("TSB_ATTN_MODE");
+        mode = env ? atoi(env) : 1;
+    }
+    return mode == 1;
 }
 
 cudaError_t launch_attn_decode_rows(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, int layer, const __half* q, int64_t q_stride,
                                     __half* out, ActOut act, const tsb_row_desc* rows_dev, int rows, int rows_per_seq,
                                     int n_q_heads, float scale, int max_len, void* scratch, int rows_cap) {
+    if (attn_split_merge_mode()) {
+        // every chunk CTA leaves its share in memory and a second, wide launch merges them (one CTA per row and head)
+        const float* part_o;
+        const float2* part_ml;
+        int n_splits;
+        cudaError_t e = launch_attn_partials(ctx, st, kv, layer, q, q_stride, rows_dev, rows, rows_per_seq, n_q_heads, scale, max_len, scratch,
+                                             &part_o, &part_ml, &n_splits);
+        if (e != cudaSuccess) return e;
+        return tsb_launch(ctx, attn_merge_kernel, dim3((unsigned)(rows * n_q_heads)), dim3(MERGE_THREADS), 0, st, true, part_o, part_ml, n_splits,
+                          n_q_heads, kv->view.head_dim, out, act);
+    }
     const AttnPlan p = attn_plan(ctx, kv, rows, rows_per_seq, n_q_heads, max_len);
     const int hd = kv->view.head_dim;
     const int n_clusters = p.n_splits / p.cluster_size;
@@ -593,6 +714,68 @@ cudaError_t launch_attn_decode_rows(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, i
                                     scale_log2e, part_o, part_ml, tickets, out, act);
     return launch_attn_t<64, 1>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
                                 scale_log2e, part_o, part_ml, tickets, out, act);
+}
+
+// The split plan of the partials-only launch: no clusters, as many KV chunks per (stream, kv head, query tile) as
+// the device holds CTAs at once, up to two per SM (at most MAX_SPLITS): one wave, and with two tiles or fewer per
+// CTA every K/V byte of a chunk is in flight from the first instruction.  Like attn_plan it is made for the length rounded up
+// to 512 and does not depend on the row count while the queries fit one tile, so a row gets the same chunks - and
+// the same sums - whether it is verified in a batch or decoded alone.
+static AttnPlan attn_plan_partials(const tsb_ctx* ctx, const tsb_kv* kv, int rows, int rows_per_seq, int n_q_heads, int max_len) {
+    AttnPlan p;
+    const int G = n_q_heads / kv->view.kv_heads;
+    const int n_queries = rows_per_seq * G;
+    p.mt = n_queries <= 16 ? 1 : 2;
+    p.n_qtiles = (n_queries + 16 * p.mt - 1) / (16 * p.mt);
+    p.groups = rows / rows_per_seq;
+    p.cluster_size = 1;
+    const int planned = max_len > 0 ? (max_len + 511) / 512 * 512 : 512;
+    const int tiles_total = planned / TILE_TOKENS;
+    const int base_ctas = p.groups * kv->view.kv_heads * p.n_qtiles;
+    int resident = max_clusters(ctx->device, kv->view.head_dim, p.mt, 1);  // CTAs the device holds at once
+    if (resident > ctx->sm_count * 2) resident = ctx->sm_count * 2;
+    if (resident < 1) resident = ctx->sm_count;
+    int splits = resident / (base_ctas > 0 ? base_ctas : 1);
+    if (splits < 1) splits = 1;
+    if (splits > MAX_SPLITS) splits = MAX_SPLITS;
+    if (splits > tiles_total) splits = tiles_total;
+    const int tiles_per = (tiles_total + splits - 1) / splits;
+    p.chunk = tiles_per * TILE_TOKENS;
+    p.n_splits = (tiles_total + tiles_per - 1) / tiles_per;
+    return p;
+}
+
+#ifdef TSB_ATTN_TRACE
+static uint32_t* g_attn_trace = nullptr;
+extern "C" __attribute__((visibility("default"))) void tsb_debug_set_attn_trace(void* p) { g_attn_trace = (uint32_t*)p; }
+#define ATTN_TICKETS g_attn_trace
+#else
+#define ATTN_TICKETS nullptr
+#endif
+cudaError_t launch_attn_partials(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, int layer, const __half* q, int64_t q_stride,
+                                 const tsb_row_desc* rows_dev, int rows, int rows_per_seq, int n_q_heads, float scale, int max_len,
+                                 void* scratch, const float** part_o_out, const float2** part_ml_out, int* n_splits_out) {
+    const AttnPlan p = attn_plan_partials(ctx, kv, rows, rows_per_seq, n_q_heads, max_len);
+    const int hd = kv->view.head_dim;
+    float* part_o = reinterpret_cast<float*>(scratch);
+    float2* part_ml = reinterpret_cast<float2*>(part_o + (size_t)rows * n_q_heads * p.n_splits * hd);
+    *part_o_out = part_o, *part_ml_out = part_ml, *n_splits_out = p.n_splits;
+    const float scale_log2e = scale * 1.4426950408889634f;
+    dim3 grid((unsigned)p.n_splits, (unsigned)(kv->view.kv_heads * p.n_qtiles), (unsigned)p.groups);
+    const size_t smem = (size_t)NST * 2 * TILE_TOKENS * hd * sizeof(__half);
+    const ActOut none{nullptr, nullptr};
+    if (hd == 128) {
+        if (p.mt == 2)
+            return launch_attn_t<128, 2>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
+                                         scale_log2e, part_o, part_ml, ATTN_TICKETS, nullptr, none, 1);
+        return launch_attn_t<128, 1>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
+                                     scale_log2e, part_o, part_ml, ATTN_TICKETS, nullptr, none, 1);
+    }
+    if (p.mt == 2)
+        return launch_attn_t<64, 2>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
+                                    scale_log2e, part_o, part_ml, ATTN_TICKETS, nullptr, none, 1);
+    return launch_attn_t<64, 1>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
+                                scale_log2e, part_o, part_ml, ATTN_TICKETS, nullptr, none, 1);
 }
 
 extern "C" {

@@ -22,14 +22,16 @@ struct tsb_ctx {
     // may set instead of trapping: 0 = fine.  Read back by tsb_stream_sync.
     uint32_t* dev_error = nullptr;
     uint32_t* host_error = nullptr;  // pinned mirror
-    uint32_t wait_limit_us = 1000000;  // bound of every device-side wait (mirrored in word 1 of the device area)
+    uint32_t wait_limit_us = 1000000;
+    // diagnostics of the fused matmul chain (tsb_debug_chain_trace): device buffer of nanosecond stamps
+    unsigned long long* chain_trace = nullptr;
+    size_t chain_trace_cap = 0, chain_trace_used = 0;  // in stamps / in launches  // bound of every device-side wait (mirrored in word 1 of the device area)
     bool pdl = true;                 // programmatic dependent launch between this ctx's kernels
 };
 
 // Layout of the device area behind tsb_ctx::dev_error (64 bytes, zeroed at creation).
 //   word 0        error word (first writer wins)
 //   word 1        bound of a device-side wait, in microseconds
-//   bytes 8..15   arrival counter of the grid-wide barrier of cooperative kernels (monotonic, 64 bits)
 constexpr size_t TSB_DEV_STATE_BYTES = 64;
 
 // Error words kernels may write (first writer wins).

@@ -111,9 +111,7 @@ int32_t tsb_stream_sync(tsb_ctx* ctx, tsb_stream s) {
     TSB_CUDA(ctx, cudaStreamSynchronize((cudaStream_t)s));
     uint32_t w = *ctx->host_error;
     if (w != TSB_DEV_OK) {
-        // the error word, and the grid barrier's arrival counter (a kernel that gave up left it mid-count)
         cudaMemsetAsync(ctx->dev_error, 0, sizeof(uint32_t), (cudaStream_t)s);
-        cudaMemsetAsync(ctx->dev_error + 2, 0, sizeof(unsigned long long), (cudaStream_t)s);
         return tsb_fail(ctx, TSB_ERR_DEVICE, "a kernel reported error word %u (%s)", w,
                         w == TSB_DEV_BARRIER_TIMEOUT ? "bounded barrier wait gave up"
                         : w == TSB_DEV_BAD_INDEX     ? "index outside its table"

@@ -1,6 +1,6 @@
 // Device code shared by the quantized-matmul kernels: the per-format block routines (weights of one 256-column
 // unit of two rows against the fragment-major activation operand), the work decomposition into groups of row
-// tiles, and the epilogues.  Included by the stand-alone matmul kernel and by the fused chain kernel.
+// tiles, and the epilogues.  Included by the matmul kernel's translation unit.
 #pragma once
 #include "gemm_quant.cuh"
 
@@ -94,23 +94,9 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
     return r;
 }
 
-// Activation loads.  NC: through the read-only path (the operand was written by an earlier launch).  Otherwise a
-// plain load: the operand was written by other CTAs of the SAME launch before a grid-wide barrier, and the
-// read-only path is not coherent with such writes.
-template <bool NC>
-__device__ __forceinline__ uint4 ld_act(const uint4* p) {
-    if constexpr (NC) {
-        return __ldg(p);
-    } else {
-        uint4 v;
-        asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-        return v;
-    }
-}
-
 // rowA/rowB: the 144-byte superblock of rows gid and gid+8 in shared memory.
 // blk: index of the 256-column block (for the activation offsets).
-template <int NT, bool NC = true>
+template <int NT>
 __device__ __forceinline__ void q4k_block(const uint4* __restrict__ rowA, const uint4* __restrict__ rowB,
                                           const LaneAct<NT>& la, int blk, int tig, float (&acc)[NT][4]) {
     // all activation loads of the block first: one scoreboard wait, hidden behind the scale decode
@@ -123,10 +109,10 @@ __device__ __forceinline__ void q4k_block(const uint4* __restrict__ rowA, const 
         for (int r = 0; r < 2; r++)
 #pragma unroll
             for (int jj = 0; jj < 2; jj++) {
-                xl[r][jj][nt] = ld_act<NC>(p + ((r * 2 + jj) * 2) * 32);
-                xh[r][jj][nt] = ld_act<NC>(p + ((r * 2 + jj) * 2 + 1) * 32);  // sub-block 2g+1
+                xl[r][jj][nt] = __ldg(p + ((r * 2 + jj) * 2) * 32);
+                xh[r][jj][nt] = __ldg(p + ((r * 2 + jj) * 2 + 1) * 32);  // sub-block 2g+1
             }
-        xsum[nt] = ld_act<NC>(la.xs[nt] + blk * 32);
+        xsum[nt] = __ldg(la.xs[nt] + blk * 32);
     }
     const uint4 hA = rowA[0];
     const uint4 hB = rowB[0];

@@ -40,8 +40,17 @@ struct GroupedArgs {
     int64_t w_stride = 0;
 };
 
+// Resident CTAs per SM the kernel is compiled for (register cap) and launched with.
+#ifndef TSB_GEMM_CTAS_NT1
+#define TSB_GEMM_CTAS_NT1 2
+#endif
+template <int QT, int NT>
+constexpr int gemm_ctas_per_sm() {
+    return NT == 1 && QT == TSB_Q4_K ? TSB_GEMM_CTAS_NT1 : (NT <= 2 ? 2 : 1);
+}
+
 template <int QT, int NT, int EPI, bool GROUPED = false>
-__global__ void __launch_bounds__(GEMM_THREADS, (NT <= 2 ? 2 : 1))
+__global__ void __launch_bounds__(GEMM_THREADS, (gemm_ctas_per_sm<QT, NT>()))
     gemm_quant_kernel(const uint8_t* __restrict__ W0, int64_t rows, int units /*256-col units per row*/,
                       ActOperand act, int tokens, int tok0, EpiArgs epi, uint32_t* __restrict__ err, GroupedArgs grp) {
     constexpr int UB = Fmt<QT>::UNIT_BYTES;
@@ -298,7 +307,7 @@ cudaError_t launch_one(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t 
         const int tph = args.head_dim / 16;
         groups = (args.n_q_heads + args.n_kv_heads) * (tph / 2) + (args.n_v_heads < 0 ? args.n_kv_heads : args.n_v_heads) * tph;
     }
-    const int per_sm = NT <= 2 ? 2 : 1;
+    const int per_sm = gemm_ctas_per_sm<QT, NT>();
     if (GROUPED) groups *= grp.n_mats;
     dim3 grid((unsigned)min(groups, ctx->sm_count * per_sm));
     return tsb_launch(ctx, kern, grid, dim3(GEMM_THREADS), smem, st, true, w, rows, units, act, tokens, tok0, args, ctx->dev_error, grp);

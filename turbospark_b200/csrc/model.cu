@@ -466,6 +466,7 @@ static int32_t runtime_init(tsb_session* s, ModelRt& rt, const tsb_model* model,
     if ((rc = A(rt.attn_scratch_bytes, &rt.attn_scratch))) return rc;
     cudaMemset(rt.attn_scratch, 0, rt.attn_scratch_bytes);  // the ticket words start at zero
     rt.fed.assign(n_streams, std::vector<int32_t>());
+    rt.pending.assign(n_streams, PendingVerify());
     // the many-row path: only when the session can hold that many rows and every matrix suits the kernel
     if (model->n_experts > 0) {
         // routed feed-forward: natural-layout rows around the router and the experts
@@ -708,7 +709,7 @@ static int32_t stage_rows(tsb_session* s, ModelRt& rt, const int32_t* streams, i
     TSB_REQUIRE(ctx, rows <= s->n_streams * s->max_rows, "%d rows exceed the session's %d", rows, s->n_streams * s->max_rows);
     TSB_REQUIRE(ctx, rows_per_seq <= 128, "at most 128 in-flight rows per stream");
     if (s->stage_used + rows > s->stage_cap) {
-        if (s->replay) return tsb_fail(ctx, TSB_ERR_STATE, "staging ring overflow inside a captured round");
+        if (s->replay || s->capturing) return tsb_fail(ctx, TSB_ERR_STATE, "staging ring overflow inside a captured round");
         // the ring is reused only after the work that read it has finished
         TSB_CUDA(ctx, cudaStreamSynchronize(s->stream));
         s->stage_used = 0;
@@ -874,6 +875,7 @@ int32_t tsb_producer_reset(tsb_session* s, int32_t stream) {
     int32_t rc = tsb_kv_reset(s->target.kv, stream);
     if (rc) return rc;
     s->target.fed[stream].clear();
+    s->target.pending[stream] = PendingVerify();
     if (s->has_draft) {
         if ((rc = tsb_kv_reset(s->draft.kv, stream))) return rc;
     }
@@ -955,6 +957,8 @@ int32_t tsb_producer_verify(tsb_session* s, int32_t stream, const int32_t* feed,
     int32_t rc = check_position(s, s->target, stream, base);
     if (rc) return rc;
     record_fed(s->target, stream, base, feed, n);
+    PendingVerify& pv = s->target.pending[stream];
+    pv.active = true, pv.tree = false, pv.base = base, pv.rows = n, pv.feed.clear(), pv.drafter_rows = 0;
     return forward_stream(s, s->target, stream, feed, n, nullptr, s->logits_target, logits_out_host);
 }
 
@@ -965,13 +969,42 @@ int32_t tsb_producer_verify_tree(tsb_session* s, int32_t stream, const int32_t* 
     DeviceGuard g(s->ctx);
     int32_t rc = check_position(s, s->target, stream, base);
     if (rc) return rc;
+    // the slots' tokens are kept until compact_tree says which of them form the accepted path
+    PendingVerify& pv = s->target.pending[stream];
+    const int drafted = pv.active && pv.tree && pv.base == base && pv.rows == 0 ? pv.drafter_rows : 0;  // left by draft_tree
+    pv.active = true, pv.tree = true, pv.base = base, pv.rows = n, pv.feed.assign(feed, feed + n), pv.drafter_rows = drafted;
     return forward_stream(s, s->target, stream, feed, n, slot_parent, s->logits_target, logits_out_host);
 }
 
 int32_t tsb_producer_compact_tree(tsb_session* s, int32_t stream, int64_t base, const uint32_t* path, int32_t keep) {
     if (!s) return TSB_ERR_INVALID;
-    DeviceGuard g(s->ctx);
-    return tsb_kv_commit_path(s->ctx, s->stream, s->target.kv, stream, base, path, keep);
+    tsb_ctx* ctx = s->ctx;
+    TSB_REQUIRE(ctx, stream >= 0 && stream < s->n_streams, "stream %d outside the session", stream);
+    PendingVerify& pv = s->target.pending[stream];
+    if (!pv.active || !pv.tree || pv.base != base)
+        return tsb_fail(ctx, TSB_ERR_STATE, "compact_tree at %lld has no tree verify to compact", (long long)base);
+    TSB_REQUIRE(ctx, path && keep >= 1 && keep <= pv.rows && path[0] == 0, "the path starts at slot 0 and has 1..%d entries", pv.rows);
+    for (int r = 1; r < keep; r++) TSB_REQUIRE(ctx, path[r] > path[r - 1] && (int)path[r] < pv.rows, "path entries increase and stay inside the verify");
+    DeviceGuard g(ctx);
+    int32_t rc = tsb_kv_commit_path(ctx, s->stream, s->target.kv, stream, base, path, keep);
+    if (rc) return rc;
+    // the drafter holds rows only for the slots it was run over: the part of the path it has is compacted too, the
+    // rest is replayed from the record of fed tokens before its next step
+    int dkeep = 0;
+    if (s->has_draft && pv.drafter_rows > 0 && tsb_kv_cursor(s->draft.kv, stream) == base) {
+        while (dkeep < keep && (int)path[dkeep] < pv.drafter_rows) dkeep++;
+        if (dkeep > 0 && (rc = tsb_kv_commit_path(ctx, s->stream, s->draft.kv, stream, base, path, dkeep))) return rc;
+    }
+    if ((rc = tsb_stream_sync(ctx, s->stream))) return rc;
+    // the verify left the cursor past every slot; the kept rows now sit at base .. base + keep
+    if (dkeep > 0) tsb_kv_set_cursor(s->draft.kv, stream, base + dkeep);
+    auto& fed = s->target.fed[stream];
+    if ((int64_t)fed.size() < base) return tsb_fail(ctx, TSB_ERR_STATE, "the record of fed tokens ends before %lld", (long long)base);
+    fed.resize((size_t)base);
+    for (int r = 0; r < keep; r++) fed.push_back(pv.feed[path[r]]);
+    // the slots past the path are dropped from the record; their cache rows are cut by rollback_retaining
+    pv.tree = false, pv.feed.clear();  // compacted: what remains pending is a chain of pv.rows rows, of which `keep` matter
+    return TSB_OK;
 }
 
 int64_t tsb_producer_checkpoint(tsb_session* s, int32_t stream) { return s ? tsb_kv_cursor(s->target.kv, stream) : -1; }
@@ -988,9 +1021,156 @@ int32_t tsb_producer_rollback_retaining(tsb_session* s, int32_t stream, int64_t 
     if (point < 0 || keep_rows < 0 || point + keep_rows > cur)
         return tsb_fail(s->ctx, TSB_ERR_STATE, "cannot keep %d rows after %lld: the cursor is %lld", keep_rows, (long long)point,
                         (long long)cur);
+    // the record of fed tokens is only ever cut here: rows nobody recorded cannot be kept
+    if ((int64_t)s->target.fed[stream].size() < point + keep_rows)
+        return tsb_fail(s->ctx, TSB_ERR_STATE, "the record of fed tokens holds %zu entries, fewer than the %lld rows to keep "
+                        "(after verify_tree, compact_tree comes first)", s->target.fed[stream].size(), (long long)(point + keep_rows));
     int32_t rc = tsb_kv_set_cursor(s->target.kv, stream, point + keep_rows);
     if (rc) return rc;
     s->target.fed[stream].resize((size_t)(point + keep_rows));
+    return TSB_OK;
+}
+
+int32_t tsb_producer_commit_pending(tsb_session* s, int32_t stream, int32_t keep_rows) {
+    if (!s) return TSB_ERR_INVALID;
+    TSB_REQUIRE(s->ctx, stream >= 0 && stream < s->n_streams, "stream %d outside the session", stream);
+    PendingVerify& pv = s->target.pending[stream];
+    if (!pv.active) return TSB_OK;
+    if (keep_rows < 0 || keep_rows > pv.rows)
+        return tsb_fail(s->ctx, TSB_ERR_STATE, "commit_pending(%d): the last verify fed %d rows", keep_rows, pv.rows);
+    pv = PendingVerify();
+    return TSB_OK;
+}
+
+int32_t tsb_producer_discard_pending(tsb_session* s, int32_t stream) {
+    if (!s) return TSB_ERR_INVALID;
+    TSB_REQUIRE(s->ctx, stream >= 0 && stream < s->n_streams, "stream %d outside the session", stream);
+    PendingVerify& pv = s->target.pending[stream];
+    if (!pv.active) return TSB_OK;
+    DeviceGuard g(s->ctx);
+    cudaStreamSynchronize(s->stream);  // whatever the failed round enqueued is over before the cursors move
+    const int64_t base = pv.base;
+    pv = PendingVerify();
+    if (tsb_kv_cursor(s->target.kv, stream) > base) tsb_kv_set_cursor(s->target.kv, stream, base);
+    if (s->target.fed[stream].size() > (size_t)base) s->target.fed[stream].resize((size_t)base);
+    if (s->has_draft && tsb_kv_cursor(s->draft.kv, stream) > base + 1) tsb_kv_set_cursor(s->draft.kv, stream, base + 1);
+    return TSB_OK;
+}
+
+int32_t tsb_producer_supports_retaining_rollback(const tsb_session* s) { return s ? 1 : 0; }
+int32_t tsb_producer_supports_headless_prefill(const tsb_session* s) { return s ? 1 : 0; }
+int32_t tsb_producer_drafts_block_passes(const tsb_session* s) {
+    (void)s;
+    return 0;
+}
+
+int32_t tsb_session_set_tree(tsb_session* s, int32_t nodes, int32_t levels, const int32_t* branching, int32_t best_first, int32_t cand) {
+    if (!s) return TSB_ERR_INVALID;
+    tsb_ctx* ctx = s->ctx;
+    TreeShape t;
+    if (nodes == 0) {
+        s->tree = t;
+        return TSB_OK;
+    }
+    TSB_REQUIRE(ctx, nodes >= 1 && nodes + 1 <= s->max_rows && nodes + 1 <= 128, "a tree of %d nodes plus the anchor exceeds the session's %d rows", nodes, s->max_rows);
+    TSB_REQUIRE(ctx, levels >= 1 && levels <= 8, "levels must be 1..8");
+    t.nodes = nodes, t.levels = levels, t.best_first = best_first ? 1 : 0, t.cand = cand;
+    if (best_first) {
+        TSB_REQUIRE(ctx, cand >= 1 && cand <= 8, "cand must be 1..8");
+    } else {
+        TSB_REQUIRE(ctx, branching != nullptr, "a static tree needs its branching list");
+        for (int l = 0; l < levels; l++) {
+            TSB_REQUIRE(ctx, branching[l] >= 1 && branching[l] <= 8, "branching must be 1..8");
+            t.branching[l] = branching[l];
+        }
+    }
+    s->tree = t;
+    return TSB_OK;
+}
+
+int32_t tsb_producer_tree_nodes(const tsb_session* s) { return s ? s->tree.nodes : 0; }
+
+int32_t tsb_tree_slot_parents(const tsb_tree_node* tree, int32_t n, int32_t* out) {
+    if ((!tree && n) || !out || n < 0) return TSB_ERR_INVALID;
+    out[0] = -1;
+    for (int i = 0; i < n; i++) out[i + 1] = tree[i].parent < 0 ? 0 : tree[i].parent + 1;
+    return TSB_OK;
+}
+
+int32_t tsb_best_first_tree(const float* scores, int32_t depth_max, int32_t branch, int32_t nodes, tsb_tree_node* out) {
+    if (!scores || !out || branch <= 0) return 0;
+    std::vector<tsb_tree_node> t;
+    best_first_tree(depth_max, nodes, branch,
+                    [&](int depth, int /*parent*/, float* sc) -> int32_t {
+                        for (int c = 0; c < branch; c++) sc[c] = scores[(size_t)depth * branch + c];
+                        return 0;
+                    },
+                    t);
+    std::copy(t.begin(), t.end(), out);
+    return (int32_t)t.size();
+}
+
+int32_t tsb_tree_accept(const tsb_tree_node* tree, const int32_t* tokens, int32_t n, const int32_t* target_pick, int32_t* accepted_out) {
+    if ((!tree && n) || (!tokens && n) || !target_pick || !accepted_out || n < 0) return 0;
+    int at = -1, k = 0;
+    for (;;) {
+        const int32_t want = target_pick[at + 1];
+        int hit = -1;
+        for (int id = 0; id < n && hit < 0; id++)
+            if (tree[id].parent == at && tokens[id] == want) hit = id;
+        if (hit < 0) return k;
+        accepted_out[k++] = hit;
+        at = hit;
+    }
+}
+
+int32_t tsb_producer_draft_tree(tsb_session* s, int32_t stream, int32_t anchor, int64_t base, int32_t nodes, tsb_tree_node* tree_out,
+                                int32_t* tokens_out, int32_t* n_out) {
+    if (!s || !tree_out || !tokens_out || !n_out) return TSB_ERR_INVALID;
+    tsb_ctx* ctx = s->ctx;
+    TSB_REQUIRE(ctx, stream >= 0 && stream < s->n_streams, "stream %d outside the session", stream);
+    if (s->tree.nodes == 0) return tsb_fail(ctx, TSB_ERR_STATE, "this producer verifies chains only (tsb_session_set_tree turns trees on)");
+    TSB_REQUIRE(ctx, nodes >= 1 && nodes <= s->tree.nodes, "nodes must be 1..%d", s->tree.nodes);
+    DeviceGuard g(ctx);
+    TreeShape shape = s->tree;
+    shape.nodes = nodes;
+    std::vector<int32_t> feed, parent;
+    std::vector<tsb_tree_node> tree;
+    int drafter_rows = 0;
+    int32_t rc = session_draft_tree(s, stream, shape, anchor, base, feed, parent, tree, &drafter_rows);
+    if (rc) return rc;
+    for (size_t i = 0; i < tree.size(); i++) tree_out[i] = tree[i], tokens_out[i] = feed[i + 1];
+    *n_out = (int32_t)tree.size();
+    // remembered for the verify_tree / compact_tree that follow: which slots the drafter's cache holds
+    PendingVerify& pv = s->target.pending[stream];
+    pv = PendingVerify();
+    pv.active = true, pv.tree = true, pv.base = base, pv.rows = 0, pv.drafter_rows = drafter_rows;
+    return TSB_OK;
+}
+
+int32_t tsb_producer_draft_block(tsb_session* s, int32_t stream, int32_t anchor, int64_t base, int32_t block, int32_t* proposals_out) {
+    if (!s || !proposals_out) return TSB_ERR_INVALID;
+    tsb_ctx* ctx = s->ctx;
+    if (!s->has_draft) return tsb_fail(ctx, TSB_ERR_STATE, "the session has no drafter");
+    TSB_REQUIRE(ctx, stream >= 0 && stream < s->n_streams, "stream %d outside the session", stream);
+    TSB_REQUIRE(ctx, block >= 1 && block <= 15, "block must be 1..=15");
+    DeviceGuard g(ctx);
+    const int V = s->draft.model->cfg.vocab;
+    int32_t tok = anchor;
+    for (int i = 0; i <= block; i++) {
+        // step i feeds the token at base + i; its logits give proposal i (the last step is taken for its row alone)
+        int32_t rc = drafter_step(s, stream, tok, base + i - 1, i < block, nullptr);
+        if (rc) return rc;
+        if (i == block) break;
+        TSB_CUDA(ctx, launch_argmax_rows(ctx, s->stream, s->logits_draft, 1, V, s->accept_scratch));
+        std::vector<uint8_t> stats(accept_row_stats_bytes());
+        TSB_CUDA(ctx, cudaMemcpyAsync(stats.data(), s->accept_scratch, stats.size(), cudaMemcpyDeviceToHost, s->stream));
+        if ((rc = tsb_stream_sync(ctx, s->stream))) return rc;
+        int32_t am, bad;
+        accept_row_stats_read(stats.data(), 0, &am, &bad);
+        if (bad) return tsb_fail(ctx, TSB_ERR_DEVICE, "the drafter's logits at step %d are not finite", i);
+        proposals_out[i] = tok = am;
+    }
     return TSB_OK;
 }
 
@@ -1163,12 +1343,21 @@ int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_acti
         return TSB_OK;
     };
 
+    // A round that fails part-way (a refused staging, a failed capture) must not leave the two caches out of step:
+    // the cursors the body moves are put back on any error, so the caller can call again or discard.
+    std::vector<int64_t> cur_t(S), cur_d(S);
+    for (int a = 0; a < S; a++) cur_t[a] = tsb_kv_cursor(s->target.kv, streams[a]), cur_d[a] = tsb_kv_cursor(s->draft.kv, streams[a]);
+    auto restore = [&](int32_t code) {
+        for (int a = 0; a < S; a++) tsb_kv_set_cursor(s->target.kv, streams[a], cur_t[a]), tsb_kv_set_cursor(s->draft.kv, streams[a], cur_d[a]);
+        s->stage_used = 0;
+        return code;
+    };
     const bool want_graph = s->use_graph && s->rounds_done >= 1;
     if (want_graph && s->graph && s->graph_key == key) {
         s->replay = true;  // host-side staging only: descriptors land in the pinned ring at the captured offsets
         rc = body();
         s->replay = false;
-        if (rc) return rc;
+        if (rc) return restore(rc);
         TSB_CUDA(ctx, cudaEventRecord(s->ev[0], st));
         TSB_CUDA(ctx, cudaGraphLaunch(s->graph, st));
         TSB_CUDA(ctx, cudaEventRecord(s->ev[3], st));
@@ -1185,12 +1374,15 @@ int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_acti
         cudaError_t ce = cudaStreamEndCapture(st, &g);
         if (rc) {
             if (g) cudaGraphDestroy(g);
-            return rc;
+            return restore(rc);
         }
-        TSB_CUDA(ctx, ce);
+        if (ce != cudaSuccess) return restore(tsb_fail(ctx, TSB_ERR_CUDA, "ending the capture of a round failed: %s", cudaGetErrorString(ce)));
         ce = cudaGraphInstantiate(&s->graph, g, 0);
         cudaGraphDestroy(g);
-        TSB_CUDA(ctx, ce);
+        if (ce != cudaSuccess) {
+            s->graph = nullptr;
+            return restore(tsb_fail(ctx, TSB_ERR_CUDA, "instantiating the graph of a round failed: %s", cudaGetErrorString(ce)));
+        }
         s->graph_key = key;
         s->graph_launches = ctx->launches - l0;
         TSB_CUDA(ctx, cudaEventRecord(s->ev[0], st));
@@ -1198,11 +1390,14 @@ int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_acti
         TSB_CUDA(ctx, cudaEventRecord(s->ev[3], st));
         s->last_round_graphed = true;
     } else {
-        if ((rc = body())) return rc;
+        if ((rc = body())) {
+            cudaStreamSynchronize(st);  // what was enqueued before the failure is over before the cursors move back
+            return restore(rc);
+        }
         s->last_round_graphed = false;
     }
     s->rounds_done++;
-    if ((rc = tsb_stream_sync(ctx, st))) return rc;
+    if ((rc = tsb_stream_sync(ctx, st))) return restore(rc);
     s->stage_used = 0;
     // ---- commit: cursors to the accepted prefix (rollback_retaining + rewind_drafter)
     for (int a = 0; a < S; a++) {
@@ -1239,66 +1434,169 @@ int32_t session_prefill_rows(tsb_session* s, int stream, const int32_t* tokens, 
     return TSB_OK;
 }
 
-// ---- tree round (crates/runtime/src/speculative.rs:461-560; tree shape helpers runtime/src/dflash_tree.rs:106-124)
-int32_t session_tree_round(tsb_session* s, int stream, const tsb_run_config* cfg, int32_t next, int64_t base,
-                           std::vector<int32_t>& feed, std::vector<int32_t>& slot_parent, std::vector<int32_t>& picks,
-                           int* drafter_rows) {
+// ---- tree drafting (crates/runtime/src/speculative.rs:461-560; tree shape helpers runtime/src/dflash_tree.rs)
+// The drafter runs over every slot drafted so far (tree mask) and its logits at the rows that get children give
+// those children: simple rather than fast - a level (static shape) or an expansion (best-first) costs one pass.
+static int32_t drafter_children(tsb_session* s, int stream, const std::vector<int32_t>& feed, const std::vector<int32_t>& slot_parent, int n_known,
+                                const std::vector<int32_t>& rows, int width, bool want_scores, std::vector<int32_t>& child,
+                                std::vector<float>& scores) {
+    tsb_ctx* ctx = s->ctx;
+    const int V = s->target.model->cfg.vocab;
+    const int64_t base = tsb_kv_cursor(s->draft.kv, stream);
+    int32_t rc = forward_stream(s, s->draft, stream, feed.data(), n_known, slot_parent.data(), s->logits_draft, nullptr);
+    if (rc) return rc;
+    tsb_kv_set_cursor(s->draft.kv, stream, base);
+    int32_t* rows_dev = s->tree_dev;  // row list (128 ints), then eight picks per row
+    int32_t* child_dev = s->tree_dev + 128;
+    const int nr = (int)rows.size();
+    child.assign((size_t)nr * 8, -1);
+    TSB_CUDA(ctx, cudaMemcpyAsync(rows_dev, rows.data(), nr * sizeof(int32_t), cudaMemcpyHostToDevice, s->stream));
+    TSB_CUDA(ctx, launch_topk_rows(ctx, s->stream, s->logits_draft, V, rows_dev, nr, width, child_dev));
+    TSB_CUDA(ctx, cudaMemcpyAsync(child.data(), child_dev, (size_t)nr * 8 * sizeof(int32_t), cudaMemcpyDeviceToHost, s->stream));
+    if ((rc = tsb_stream_sync(ctx, s->stream))) return rc;
+    for (int r = 0; r < nr; r++)
+        for (int c = 0; c < width; c++)
+            if (child[(size_t)r * 8 + c] < 0) return tsb_fail(ctx, TSB_ERR_DEVICE, "the drafter's logits at tree slot %d are not finite", rows[r]);
+    if (want_scores) {
+        // the picked candidates' logits, the scores the best-first builder's softmax runs over
+        std::vector<uint16_t> raw((size_t)nr * width);
+        for (int r = 0; r < nr; r++)
+            for (int c = 0; c < width; c++)
+                TSB_CUDA(ctx, cudaMemcpyAsync(&raw[(size_t)r * width + c], s->logits_draft + (size_t)rows[r] * V + child[(size_t)r * 8 + c], 2,
+                                              cudaMemcpyDeviceToHost, s->stream));
+        if ((rc = tsb_stream_sync(ctx, s->stream))) return rc;
+        scores.resize(raw.size());
+        for (size_t i = 0; i < raw.size(); i++) scores[i] = __half2float(__ushort_as_half(raw[i]));
+    }
+    return TSB_OK;
+}
+
+int32_t session_draft_tree(tsb_session* s, int stream, const TreeShape& shape, int32_t next, int64_t base, std::vector<int32_t>& feed,
+                           std::vector<int32_t>& slot_parent, std::vector<tsb_tree_node>& nodes, int* drafter_rows) {
     tsb_ctx* ctx = s->ctx;
     if (!s->has_draft) return tsb_fail(ctx, TSB_ERR_STATE, "the session has no drafter");
-    TSB_REQUIRE(ctx, cfg->shaping.temperature == 0.0, "tree rounds need temperature 0 (sampled tree acceptance is not defined)");
-    const int N = cfg->tree_nodes, LV = cfg->tree_levels;
+    const int N = shape.nodes, LV = shape.levels;
     TSB_REQUIRE(ctx, N >= 1 && N + 1 <= s->max_rows && N + 1 <= 128, "tree of %d nodes + anchor exceeds the session's %d rows", N, s->max_rows);
     TSB_REQUIRE(ctx, LV >= 1 && LV <= 8, "tree_levels must be 1..8");
-    for (int l = 0; l < LV; l++) TSB_REQUIRE(ctx, cfg->tree_branching[l] >= 1 && cfg->tree_branching[l] <= 8, "tree_branching must be 1..8");
-    const int V = s->target.model->cfg.vocab;
     int32_t rc;
     if (tsb_kv_cursor(s->draft.kv, stream) < base && (rc = drafter_catch_up(s, stream, base))) return rc;
-    if (tsb_kv_cursor(s->draft.kv, stream) != base || tsb_kv_cursor(s->target.kv, stream) != base)
-        return tsb_fail(ctx, TSB_ERR_STATE, "tree round at %lld: target cursor %lld, drafter cursor %lld", (long long)base,
-                        (long long)tsb_kv_cursor(s->target.kv, stream), (long long)tsb_kv_cursor(s->draft.kv, stream));
-    // the static shape, breadth-first, cut at N nodes: slot 0 is the anchor, node i sits in slot i + 1
+    if (tsb_kv_cursor(s->draft.kv, stream) != base)
+        return tsb_fail(ctx, TSB_ERR_STATE, "tree draft at %lld: drafter cursor %lld", (long long)base, (long long)tsb_kv_cursor(s->draft.kv, stream));
+    if (base + N + 1 > s->draft.model->cfg.max_context) return tsb_fail(ctx, TSB_ERR_STATE, "a tree of %d rows at %lld exceeds the context window", N + 1, (long long)base);
+    nodes.clear();
+    feed.assign(1, next);
     slot_parent.assign(1, -1);
+    std::vector<int32_t> child;
+    std::vector<float> sc;
+    int drafted = 0;
+    if (shape.best_first) {
+        TSB_REQUIRE(ctx, shape.cand >= 1 && shape.cand <= 8, "tree_cand must be 1..8");
+        // children of node `parent` (the anchor for -1): the drafter's `cand` most likely tokens after it, scored by
+        // their logits.  The expanded node is always the newest slot, so one pass over the slots so far gives its row.
+        std::vector<std::vector<int32_t>> cand_tokens;  // per expanded parent (index parent + 1): its candidates' tokens
+        cand_tokens.resize((size_t)N + 1);
+        std::vector<tsb_tree_node> out;
+        // best_first_tree appends a node and, when it has room, expands it at once: `out` is mirrored in feed/slot_parent
+        // inside the callback, which therefore sees every earlier node's slot already in place
+        std::vector<tsb_tree_node> seen;
+        auto on_scores = [&](int depth, int parent, float* scores_out) -> int32_t {
+            (void)depth;
+            // bring feed / slot_parent up to date with the nodes picked since the last expansion
+            return TSB_OK + 0 * (scores_out != nullptr) + 0 * parent;
+        };
+        (void)on_scores;
+        // The builder is run step by step here (instead of through the callback form) because a node's token is only
+        // known once its parent's candidates have been scored.
+        struct Front {
+            double p;
+            tsb_tree_node n;
+        };
+        std::vector<Front> frontier;
+        auto expand = [&](int depth, int parent, double path_p) -> int32_t {
+            const int n_known = (int)feed.size();
+            std::vector<int32_t> rows{parent + 1};
+            int32_t rc2 = drafter_children(s, stream, feed, slot_parent, n_known, rows, shape.cand, true, child, sc);
+            if (rc2) return rc2;
+            drafted = n_known;
+            cand_tokens[(size_t)parent + 1].assign(child.begin(), child.begin() + shape.cand);
+            float mf = -INFINITY;
+            for (int i = 0; i < shape.cand; i++) mf = fmaxf(mf, sc[i]);
+            const double m = (double)mf;
+            double e[8], z = 0.0;
+            for (int i = 0; i < shape.cand; i++) e[i] = exp((double)sc[i] - m);
+            for (int i = 0; i < shape.cand; i++) z += e[i];
+            for (int c = 0; c < shape.cand; c++) frontier.push_back({path_p * (e[c] / z), tsb_tree_node{depth, c, parent}});
+            return TSB_OK;
+        };
+        if ((rc = expand(0, -1, 1.0))) return rc;
+        while ((int)nodes.size() < N && !frontier.empty()) {
+            size_t best = 0;
+            for (size_t i = 1; i < frontier.size(); i++) {
+                const Front &f = frontier[i], &b = frontier[best];
+                if (f.p > b.p || (f.p == b.p && (f.n.depth < b.n.depth || (f.n.depth == b.n.depth && f.n.cand < b.n.cand)))) best = i;
+            }
+            const Front picked = frontier[best];
+            frontier[best] = frontier.back();
+            frontier.pop_back();
+            const int id = (int)nodes.size();
+            nodes.push_back(picked.n);
+            feed.push_back(cand_tokens[(size_t)picked.n.parent + 1][picked.n.cand]);
+            slot_parent.push_back(picked.n.parent + 1);
+            if ((int)nodes.size() < N && picked.n.depth + 1 < LV && (rc = expand(picked.n.depth + 1, id, picked.p))) return rc;
+        }
+        *drafter_rows = drafted;
+        return TSB_OK;
+    }
+    for (int l = 0; l < LV; l++) TSB_REQUIRE(ctx, shape.branching[l] >= 1 && shape.branching[l] <= 8, "tree_branching must be 1..8");
+    // the static shape, breadth-first, cut at N nodes: slot 0 is the anchor, node i sits in slot i + 1
     std::vector<int> level_begin{0, 1};  // slots of level l are [level_begin[l], level_begin[l+1])
+    std::vector<int> depth_of{0}, cand_of{0};
     for (int l = 0; l < LV && (int)slot_parent.size() < N + 1; l++) {
         const int lo = level_begin[l], hi = level_begin[l + 1];
         for (int p = lo; p < hi && (int)slot_parent.size() < N + 1; p++)
-            for (int c = 0; c < cfg->tree_branching[l] && (int)slot_parent.size() < N + 1; c++) slot_parent.push_back(p);
+            for (int c = 0; c < shape.branching[l] && (int)slot_parent.size() < N + 1; c++) {
+                slot_parent.push_back(p);
+                depth_of.push_back(l), cand_of.push_back(c);
+            }
         level_begin.push_back((int)slot_parent.size());
     }
     const int rows = (int)slot_parent.size();
     TSB_REQUIRE(ctx, rows == N + 1, "the branching list yields %d nodes, fewer than tree_nodes %d", rows - 1, N);
-    feed.assign(rows, 0);
-    feed[0] = next;
-    // ---- draft level by level: the drafter runs over every slot drafted so far (tree mask), its logits at the rows of
-    // the newest level give those nodes' children
+    feed.resize(rows, 0);
+    for (int i = 1; i < rows; i++) nodes.push_back(tsb_tree_node{depth_of[i], cand_of[i], slot_parent[i] - 1});
     const int n_levels = (int)level_begin.size() - 1;  // levels that hold slots (anchor level included)
-    int drafted = 0;
-    std::vector<int32_t> row_ids, child(8 * 128);
+    std::vector<int32_t> row_ids;
     for (int l = 0; l + 1 < n_levels; l++) {
         const int n = level_begin[l + 1];  // slots 0 .. n-1 are known
-        if ((rc = forward_stream(s, s->draft, stream, feed.data(), n, slot_parent.data(), s->logits_draft, nullptr))) return rc;
-        tsb_kv_set_cursor(s->draft.kv, stream, base);
-        drafted = n;
         const int lo = level_begin[l], hi = level_begin[l + 1];
         row_ids.resize(hi - lo);
         for (int p = lo; p < hi; p++) row_ids[p - lo] = p;
-        int32_t* rows_dev = s->tree_dev;  // row list (128 ints), then eight picks per row
-        int32_t* child_dev = s->tree_dev + 128;
-        TSB_CUDA(ctx, cudaMemcpyAsync(rows_dev, row_ids.data(), (hi - lo) * sizeof(int32_t), cudaMemcpyHostToDevice, s->stream));
-        TSB_CUDA(ctx, launch_topk_rows(ctx, s->stream, s->logits_draft, V, rows_dev, hi - lo, cfg->tree_branching[l], child_dev));
-        TSB_CUDA(ctx, cudaMemcpyAsync(child.data(), child_dev, (size_t)(hi - lo) * 8 * sizeof(int32_t), cudaMemcpyDeviceToHost, s->stream));
-        if ((rc = tsb_stream_sync(ctx, s->stream))) return rc;
-        // children of the level's nodes, in slot order
-        int slot = level_begin[l + 1];
+        if ((rc = drafter_children(s, stream, feed, slot_parent, n, row_ids, shape.branching[l], false, child, sc))) return rc;
+        drafted = n;
+        int slot = level_begin[l + 1];  // children of the level's nodes, in slot order
         for (int p = lo; p < hi; p++)
-            for (int c = 0; c < cfg->tree_branching[l] && slot < level_begin[l + 2]; c++, slot++) {
-                const int32_t t = child[(size_t)(p - lo) * 8 + c];
-                if (t < 0) return tsb_fail(ctx, TSB_ERR_DEVICE, "the drafter's logits at tree slot %d are not finite", p);
-                feed[slot] = t;
-            }
+            for (int c = 0; c < shape.branching[l] && slot < level_begin[l + 2]; c++, slot++) feed[slot] = child[(size_t)(p - lo) * 8 + c];
     }
     *drafter_rows = drafted;
-    // ---- verify: anchor + nodes in one target pass, then the target's pick at every row
+    return TSB_OK;
+}
+
+// ---- tree round: draft, then anchor + nodes in one target pass and the target's pick at every row
+int32_t session_tree_round(tsb_session* s, int stream, const tsb_run_config* cfg, int32_t next, int64_t base,
+                           std::vector<int32_t>& feed, std::vector<int32_t>& slot_parent, std::vector<int32_t>& picks,
+                           int* drafter_rows) {
+    tsb_ctx* ctx = s->ctx;
+    TSB_REQUIRE(ctx, cfg->shaping.temperature == 0.0, "tree rounds need temperature 0 (sampled tree acceptance is not defined)");
+    TreeShape shape;
+    shape.nodes = cfg->tree_nodes, shape.levels = cfg->tree_levels, shape.best_first = cfg->tree_best_first, shape.cand = cfg->tree_cand;
+    for (int l = 0; l < 8; l++) shape.branching[l] = cfg->tree_branching[l];
+    const int V = s->target.model->cfg.vocab;
+    if (tsb_kv_cursor(s->target.kv, stream) != base)
+        return tsb_fail(ctx, TSB_ERR_STATE, "tree round at %lld: target cursor %lld", (long long)base, (long long)tsb_kv_cursor(s->target.kv, stream));
+    std::vector<tsb_tree_node> nodes;
+    int32_t rc = session_draft_tree(s, stream, shape, next, base, feed, slot_parent, nodes, drafter_rows);
+    if (rc) return rc;
+    const int rows = (int)feed.size();
     if ((rc = forward_stream(s, s->target, stream, feed.data(), rows, slot_parent.data(), s->logits_target, nullptr))) return rc;
     tsb_kv_set_cursor(s->target.kv, stream, base);
     TSB_REQUIRE(ctx, (size_t)rows * accept_row_stats_bytes() <= s->accept_scratch_bytes, "tree of %d rows exceeds the acceptance scratch", rows);

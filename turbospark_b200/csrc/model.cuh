@@ -1,5 +1,6 @@
 // Model, per-model runtime state and session objects behind the opaque C handles.
 #pragma once
+#include <cmath>
 #include <vector>
 
 #include "gemm_quant.cuh"
@@ -38,6 +39,24 @@ struct tsb_model {
     int n_experts = 0, top_k = 0, moe_ffn = 0;  // n_experts > 0: every layer's feed-forward is routed
 };
 
+// Shape of the trees a session drafts (tsb_session_set_tree, or a run configuration's tree fields).
+struct TreeShape {
+    int nodes = 0;      // drafted nodes per round (the anchor row comes on top); 0: chains only
+    int levels = 0;     // longest path below the anchor
+    int branching[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // static shape: children per node of level l
+    int best_first = 0; // 1: grown best-first by path probability (crates/runtime/src/dflash_tree.rs:30-82)
+    int cand = 0;       // best-first: candidates scored per expanded node (1..8)
+};
+
+// The last verify of a stream until the round's outcome is known (commit_pending / discard_pending).
+struct PendingVerify {
+    bool active = false, tree = false;
+    int64_t base = 0;
+    int rows = 0;
+    std::vector<int32_t> feed;  // tree verifies: the token fed at every slot
+    int drafter_rows = 0;       // tree drafts: slots the drafter's cache holds rows for
+};
+
 struct ActBuf {
     uint4* xp = nullptr;
     uint4* xs = nullptr;
@@ -65,6 +84,7 @@ struct ModelRt {
     float* moe_unit_ss = nullptr;  // [R] sums of squares that make the q|k|v epilogue's 1/rms exactly one (the operand is already normed)
     void* moe_ws = nullptr;
     std::vector<std::vector<int32_t>> fed;  // per stream: tokens absorbed, by position (target only)
+    std::vector<PendingVerify> pending;     // per stream (target only)
 };
 
 struct tsb_session {
@@ -101,6 +121,7 @@ struct tsb_session {
     cudaGraphExec_t graph = nullptr;
     uint64_t graph_key = 0, graph_launches = 0;
     int rounds_done = 0;
+    TreeShape tree;  // what tsb_producer_tree_nodes / tsb_producer_draft_tree use
 };
 
 // One speculative round for the listed streams with k proposals each (model.cu).
@@ -114,6 +135,55 @@ int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_acti
 int32_t session_tree_round(tsb_session* s, int stream, const tsb_run_config* cfg, int32_t next, int64_t base,
                            std::vector<int32_t>& feed, std::vector<int32_t>& slot_parent, std::vector<int32_t>& picks,
                            int* drafter_rows);
+// The drafting half of a tree round at temperature 0: fills feed (slot 0 = the anchor token) and slot_parent, and for
+// every drafted node its depth below the anchor, its candidate rank among its parent's children and its parent
+// node (-1 under the anchor).  The drafter's cursor is left at `base`.
+int32_t session_draft_tree(tsb_session* s, int stream, const TreeShape& shape, int32_t next, int64_t base, std::vector<int32_t>& feed,
+                           std::vector<int32_t>& slot_parent, std::vector<tsb_tree_node>& nodes, int* drafter_rows);
+// The best-first builder of crates/runtime/src/dflash_tree.rs:30-82 over a callback that scores one parent's children.
+// child_scores(depth, parent_node_or_-1, scores_out[branch]) returns a status (0 = fine).  Repeatedly the frontier
+// node with the highest path probability is taken and all its children are added; a parent's children share an f64
+// softmax over its scores; ties prefer the shallower, then the lower candidate; parents precede children.
+template <typename F>
+inline int32_t best_first_tree(int depth_max, int nodes, int branch, F&& child_scores, std::vector<tsb_tree_node>& out) {
+    out.clear();
+    if (depth_max <= 0 || nodes <= 0 || branch <= 0) return 0;
+    struct Front {
+        double p;
+        tsb_tree_node n;
+    };
+    std::vector<Front> frontier;
+    std::vector<float> sc((size_t)branch);
+    auto push_children = [&](int depth, int parent, double path_p) -> int32_t {
+        int32_t rc = child_scores(depth, parent, sc.data());
+        if (rc) return rc;
+        float mf = -INFINITY;
+        for (int i = 0; i < branch; i++) mf = fmaxf(mf, sc[i]);
+        const double m = (double)mf;
+        std::vector<double> e((size_t)branch);
+        double z = 0.0;
+        for (int i = 0; i < branch; i++) e[i] = exp((double)sc[i] - m);
+        for (int i = 0; i < branch; i++) z += e[i];
+        for (int c = 0; c < branch; c++) frontier.push_back({path_p * (e[c] / z), tsb_tree_node{depth, c, parent}});
+        return 0;
+    };
+    if (int32_t rc = push_children(0, -1, 1.0)) return rc;
+    while ((int)out.size() < nodes && !frontier.empty()) {
+        size_t best = 0;
+        for (size_t i = 1; i < frontier.size(); i++) {
+            const Front &f = frontier[i], &b = frontier[best];
+            if (f.p > b.p || (f.p == b.p && (f.n.depth < b.n.depth || (f.n.depth == b.n.depth && f.n.cand < b.n.cand)))) best = i;
+        }
+        const Front picked = frontier[best];
+        frontier[best] = frontier.back();
+        frontier.pop_back();
+        const int id = (int)out.size();
+        out.push_back(picked.n);
+        if ((int)out.size() < nodes && picked.n.depth + 1 < depth_max)
+            if (int32_t rc = push_children(picked.n.depth + 1, id, picked.p)) return rc;
+    }
+    return 0;
+}
 // Keep path[0..keep) of the tree rows of both caches as a chain at base (compaction + cursors + fed-token record).
 int32_t session_tree_commit(tsb_session* s, int stream, int64_t base, const std::vector<int32_t>& feed,
                             const std::vector<uint32_t>& path, int keep, int drafter_rows);

@@ -171,7 +171,12 @@ int32_t tsb_spec_run(tsb_session* s, int32_t stream, const int32_t* prompt, int3
             // pick is accepted when a child of that node carries it (speculative.rs:494-529)
             std::vector<int32_t> feed, parent, picks;
             int drafter_rows = 0;
-            if ((rc = session_tree_round(s, stream, cfg, next, base, feed, parent, picks, &drafter_rows))) return rc;
+            if ((rc = session_tree_round(s, stream, cfg, next, base, feed, parent, picks, &drafter_rows))) {
+                // speculative.rs:551-557: a round that fails after its verify began is discarded, not half-kept
+                tsb_kv_set_cursor(s->target.kv, stream, std::min<int64_t>(tsb_kv_cursor(s->target.kv, stream), base));
+                tsb_producer_rewind_drafter(s, stream, base);
+                return rc;
+            }
             rounds++;
             std::vector<uint32_t> path{0};
             int at = 0, stopped = -1;
@@ -199,7 +204,11 @@ int32_t tsb_spec_run(tsb_session* s, int32_t stream, const int32_t* prompt, int3
             accepted_total += (int)path.size() - 1;
             const int64_t committed = (int64_t)sink.history.size() - (base + 1);
             if (committed + 1 < (int64_t)feed.size()) rollbacks++;
-            if ((rc = session_tree_commit(s, stream, base, feed, path, (int)committed + 1, drafter_rows))) return rc;
+            if ((rc = session_tree_commit(s, stream, base, feed, path, (int)committed + 1, drafter_rows))) {
+                tsb_kv_set_cursor(s->target.kv, stream, std::min<int64_t>(tsb_kv_cursor(s->target.kv, stream), base));
+                tsb_producer_rewind_drafter(s, stream, base);
+                return rc;
+            }
             position = (int64_t)sink.history.size();
             if (stopped >= 0) {
                 reason = stopped;

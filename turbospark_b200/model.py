@@ -19,7 +19,11 @@ class RunConfig(C.Structure):
     _fields_ = [("shaping", Shaping), ("max_new_tokens", C.c_int32), ("block", C.c_int32), ("uniform_mode", C.c_int32),
                 ("n_stop", C.c_int32), ("stop_tokens", C.c_int32 * 8), ("adaptive", C.c_int32),
                 ("tree_nodes", C.c_int32), ("tree_levels", C.c_int32), ("tree_branching", C.c_int32 * 8),
-                ("reuse_prefix", C.c_int32)]
+                ("reuse_prefix", C.c_int32), ("tree_best_first", C.c_int32), ("tree_cand", C.c_int32)]
+
+
+class TreeNode(C.Structure):
+    _fields_ = [("depth", C.c_int32), ("cand", C.c_int32), ("parent", C.c_int32)]
 
 
 class RunResult(C.Structure):
@@ -30,10 +34,11 @@ class RunResult(C.Structure):
 
 
 def run_config(shaping_cfg, max_new_tokens, block, uniform_mode=0, stop_tokens=(), adaptive=0, tree_nodes=0, tree_branching=(),
-               reuse_prefix=False):
+               reuse_prefix=False, tree_best_first=False, tree_cand=0, tree_levels=None):
     rc = RunConfig()
     rc.reuse_prefix = 1 if reuse_prefix else 0
-    rc.tree_nodes, rc.tree_levels = tree_nodes, len(tree_branching)
+    rc.tree_nodes, rc.tree_levels = tree_nodes, (len(tree_branching) if tree_levels is None else tree_levels)
+    rc.tree_best_first, rc.tree_cand = (1 if tree_best_first else 0), tree_cand
     for i, b in enumerate(tree_branching):
         rc.tree_branching[i] = b
     rc.shaping = shaping_cfg
@@ -176,6 +181,57 @@ class Session:
 
     def rewind_drafter(self, position, stream=0):
         self.ctx.check(lib().tsb_producer_rewind_drafter(self.h, C.c_int32(stream), C.c_int64(position)))
+
+    def set_tree(self, nodes, levels=0, branching=(), best_first=False, cand=0):
+        br = (C.c_int32 * 8)(*list(branching)[:8])
+        self.ctx.check(lib().tsb_session_set_tree(self.h, C.c_int32(nodes), C.c_int32(levels or len(branching)), br,
+                                                  C.c_int32(1 if best_first else 0), C.c_int32(cand)))
+
+    def tree_nodes(self):
+        n = int(lib().tsb_producer_tree_nodes(self.h))
+        return n or None
+
+    def draft_tree(self, anchor, base, nodes, stream=0):
+        """-> (depth, cand, parent) int arrays and the nodes' tokens; parent -1 = under the anchor."""
+        tree = (TreeNode * nodes)()
+        toks = np.zeros(nodes, dtype=np.int32)
+        n = C.c_int32()
+        self.ctx.check(lib().tsb_producer_draft_tree(self.h, C.c_int32(stream), C.c_int32(anchor), C.c_int64(base), C.c_int32(nodes),
+                                                     tree, toks.ctypes.data_as(C.c_void_p), C.byref(n)))
+        k = n.value
+        return (np.array([tree[i].depth for i in range(k)], dtype=np.int32), np.array([tree[i].cand for i in range(k)], dtype=np.int32),
+                np.array([tree[i].parent for i in range(k)], dtype=np.int32), toks[:k].copy())
+
+    def draft_block(self, anchor, base, block, stream=0):
+        out = np.zeros(block, dtype=np.int32)
+        self.ctx.check(lib().tsb_producer_draft_block(self.h, C.c_int32(stream), C.c_int32(anchor), C.c_int64(base), C.c_int32(block),
+                                                      out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def drafts_block_passes(self):
+        return bool(lib().tsb_producer_drafts_block_passes(self.h))
+
+    def commit_pending(self, keep_rows, stream=0):
+        self.ctx.check(lib().tsb_producer_commit_pending(self.h, C.c_int32(stream), C.c_int32(keep_rows)))
+
+    def discard_pending(self, stream=0):
+        self.ctx.check(lib().tsb_producer_discard_pending(self.h, C.c_int32(stream)))
+
+    def supports_retaining_rollback(self):
+        return bool(lib().tsb_producer_supports_retaining_rollback(self.h))
+
+    def supports_headless_prefill(self):
+        return bool(lib().tsb_producer_supports_headless_prefill(self.h))
+
+    def try_reuse_prefix(self, prompt, stream=0):
+        p = np.ascontiguousarray(prompt, dtype=np.int32)
+        lib().tsb_producer_try_reuse_prefix.restype = C.c_int64
+        return int(lib().tsb_producer_try_reuse_prefix(self.h, C.c_int32(stream), p.ctypes.data_as(C.c_void_p), C.c_int32(p.size)))
+
+    def record_committed(self, tokens, pos0, stream=0):
+        t = np.ascontiguousarray(tokens, dtype=np.int32)
+        self.ctx.check(lib().tsb_producer_record_committed(self.h, C.c_int32(stream), t.ctypes.data_as(C.c_void_p), C.c_int32(t.size),
+                                                           C.c_int64(pos0)))
 
     def _run(self, fn, prompt, rc, stream):
         p = np.ascontiguousarray(prompt, dtype=np.int32)
