@@ -44,6 +44,7 @@ typedef struct tsb_ctx tsb_ctx;
 typedef struct tsb_kv tsb_kv;
 typedef struct tsb_model tsb_model;
 typedef struct tsb_session tsb_session;
+typedef struct tsb_comm tsb_comm;
 typedef void* tsb_stream; /* cudaStream_t */
 
 typedef enum tsb_status {
@@ -416,6 +417,29 @@ TSB_API int32_t tsb_resident_qtype_of(int32_t dtype_tag);
  * is refused (real_forward_dispatch.rs:1008-1016), as is a dtype outside the block formats. */
 TSB_API int32_t tsb_model_load_resident(tsb_model* m, const tsb_resident* idx, int32_t tie_word_embeddings);
 
+/* ------------------------------------------------- sharding one routed model over the GPUs of a box
+ * The reference runs on one Apple GPU and has no counterpart; the shapes follow its routed layer
+ * (crates/runtime/src/families/llama/moe.rs:36-221).  One process per GPU.  Attention is tensor-parallel over heads:
+ * a rank's model is built with ITS heads only (n_q_heads / world query heads and the K/V heads they read, a K/V head
+ * being replicated where world exceeds the K/V head count), its o_proj matrix holds the matching head columns, and the
+ * partial projections are summed over the ranks (f32 all-reduce).  Experts are sharded: a rank holds experts
+ * [expert_lo, expert_lo + n_local) of every layer, computes the (row, slot) outputs routed to them and leaves zeros
+ * for the rest; the f32 all-reduce of those per-slot outputs adds only zeros to each value, so every rank then holds
+ * exactly what one GPU computes and the slot-ordered weighted sum is bit-identical on all ranks.  Router, norms,
+ * embedding and head are replicated.  The collectives are NCCL calls on the session's stream; NCCL is loaded at run
+ * time (TSB_NCCL_LIB overrides the library name). */
+/* Rank 0 makes the id, the host program hands the 128 bytes to every rank (any channel), every rank creates. */
+TSB_API int32_t tsb_comm_unique_id(tsb_ctx* ctx, void* out_128_bytes);
+TSB_API int32_t tsb_comm_create(tsb_ctx* ctx, const void* unique_id_128_bytes, int32_t rank, int32_t world, tsb_comm** out);
+TSB_API void tsb_comm_destroy(tsb_comm* c);
+/* In-place sum over the ranks of `count` f32 values (the exchange step itself, as an operator). */
+TSB_API int32_t tsb_comm_all_reduce_f32(tsb_comm* c, tsb_stream s, void* buf_f32_dev, size_t count);
+/* This rank's experts: set after tsb_model_set_moe and before the expert tensors, which then hold n_local experts. */
+TSB_API int32_t tsb_model_set_expert_shard(tsb_model* m, int32_t expert_lo, int32_t n_local);
+/* The session's passes exchange through `c` (NULL: single GPU).  Every rank must run the same passes in the same
+ * order with the same rows. */
+TSB_API int32_t tsb_session_set_comm(tsb_session* s, tsb_comm* c);
+
 /* A session = the producer: a target model, an optional stand-alone draft model, paged K/V caches for
  * `n_streams` independent request streams, and every activation / logits / scratch buffer a round
  * needs for up to `max_rows` rows per stream.  Mirrors what RealForwardRunner owns
@@ -577,9 +601,10 @@ TSB_API int32_t tsb_session_fill_context(tsb_session* s, int64_t tokens, uint64_
 
 /* The CUDA stream (cudaStream_t) the session enqueues on, so a caller can record its own events on it. */
 TSB_API void* tsb_session_stream(tsb_session* s);
-/* Measurement aid: enqueue the target's per-layer matmul sequence (qkv, o_proj, gate|up, down for every layer:
- * the kernels that dominate a verify pass) `iters` times for `rows` token rows over whatever the activation
- * buffers hold, and return the elapsed device time and the weight bytes one sequence streams. */
+/* Measurement aid: enqueue the target's layer matmuls exactly as a pass of `rows` rows launches them (q|k|v with the
+ * RoPE / K-V-store epilogue, o_proj and down with the residual + norm epilogue, gate|up with the SiLU epilogue, for
+ * every layer; no attention, embedding or head) `iters` times, over whatever the activation buffers hold and rows
+ * past the streams' cursors, and return the elapsed device time and the bytes one sequence streams. */
 TSB_API int32_t tsb_session_time_matmuls(tsb_session* s, int32_t rows, int32_t iters, float* out_ms, int64_t* out_bytes_per_iter,
                                          int32_t* out_launches_per_iter);
 

@@ -3,6 +3,8 @@ on the CPU-runnable tiny configuration: 4-layer Llama-style target, draft = its 
 import numpy as np
 import pytest
 
+from tests import weights
+
 pytestmark = pytest.mark.gpu
 REL, ABS = 2e-3, 1e-3
 
@@ -14,9 +16,9 @@ def rig(oracle):
     cfg = tsb.config_tiny(max_context=512)
     dcfg = tsb.ModelConfig(2, cfg.d_model, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.vocab, cfg.max_context,
                            cfg.rms_eps, cfg.rope_theta)
-    mats, norms = tsb.random_weights(cfg, 0, oracle, real_ffn=1408)
+    mats, norms = weights.random_weights(cfg, 0, oracle, real_ffn=1408)
     target = tsb.Model(ctx, cfg)
-    tsb.load_weights(target, mats, norms)
+    weights.load_weights(target, mats, norms)
     draft = tsb.Model(ctx, dcfg)
     for l in range(2):
         draft.share(l, target, l)
@@ -27,9 +29,9 @@ def rig(oracle):
     odcfg = oracle.ModelCfg(2, cfg.d_model, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.vocab, cfg.max_context,
                             cfg.rms_eps, cfg.rope_theta)
     ot = oracle.Model(ocfg, threads=8)
-    tsb.load_weights(ot, mats, norms)
+    weights.load_weights(ot, mats, norms)
     od = oracle.Model(odcfg, threads=8)
-    tsb.load_weights(od, mats, norms, layers=2)
+    weights.load_weights(od, mats, norms, layers=2)
     yield dict(ctx=ctx, cfg=cfg, target=target, draft=draft, ot=ot, od=od, tsb=tsb)
     target.close(), draft.close(), ctx.close()
 
@@ -424,19 +426,23 @@ def test_many_row_passes_match_the_oracle_forward(rig, oracle):
     sess.close()
 
 
-def test_lockstep_rounds_over_three_streams_equal_three_single_stream_runs(rig, oracle):
-    """Independent streams in one session: every stream's greedy output from lockstep rounds equals its own
-    single-stream sequential run (streams of different lengths, different prompts)."""
+@pytest.mark.parametrize("S,K", [(3, 3), (4, 5), (6, 5)])
+def test_lockstep_rounds_over_several_streams_equal_single_stream_runs(rig, oracle, S, K):
+    """Independent streams in one session: every stream's greedy output from lockstep rounds equals its own sequential
+    run (streams of different lengths, different prompts).  With 4 streams at K = 5 the verify pass carries 24 rows and
+    the session's target runs the tensor-memory matmul - for every pass, the single-row decodes of the sequential loop
+    included, so the two loops still agree token for token."""
     tsb = rig["tsb"]
-    S, K, NEW = 3, 3, 20
+    NEW = 20
     sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], S, K + 1)
-    solo = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 8)
+    solo = sess  # the sequential runs use the same session: one matmul path per (session, model)
     rng = np.random.default_rng(33)
-    prompts = [rng.integers(0, rig["cfg"].vocab, size=n).astype(np.int32) for n in (9, 21, 14)]
+    prompts = [rng.integers(0, rig["cfg"].vocab, size=n).astype(np.int32) for n in (9, 21, 14, 30, 12, 17)[:S]]
     rc = tsb.run_config(tsb.shaping(temperature=0.0), 1 << 20, K)
-    want = [solo.sequential_run(p, tsb.run_config(tsb.shaping(temperature=0.0), NEW, K))[1] for p in prompts]
+    want = [solo.sequential_run(p, tsb.run_config(tsb.shaping(temperature=0.0), NEW, K), stream=q)[1] for q, p in enumerate(prompts)]
     nxt = np.zeros(S, dtype=np.int32)
     for q, p in enumerate(prompts):
+        sess.reset(stream=q)
         for i, t in enumerate(p[:-1]):
             sess.produce_prefill(int(t), i, stream=q)
         lg = oracle.f16_bits_to_f32(sess.produce(int(p[-1]), len(p) - 1, stream=q))
@@ -453,7 +459,26 @@ def test_lockstep_rounds_over_three_streams_equal_three_single_stream_runs(rig, 
             assert toks[q, acc[q]] == nxt[q]
     for q in range(S):
         assert out[q][:NEW] == list(want[q][:NEW]), (q, out[q][:NEW], list(want[q][:NEW]))
-    sess.close(), solo.close()
+    sess.close()
+
+
+def test_prefix_reuse_with_a_long_prompt_equals_a_cold_run_on_the_many_row_path(rig, oracle):
+    """A session whose largest pass has 24 rows or more prefills in chunks of that size; a later turn that reuses a
+    prefix prefills in other chunk sizes.  One matmul path per (session, model) keeps the cache rows - and the
+    output - identical to a run from an empty cache."""
+    tsb = rig["tsb"]
+    sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 32)
+    rng = np.random.default_rng(41)
+    prompt = rng.integers(0, rig["cfg"].vocab, size=70).astype(np.int32)
+    rc = tsb.run_config(tsb.shaping(temperature=0.0), 16, 3)
+    h1, _, _ = sess.spec_run(prompt, rc)
+    turn2 = np.concatenate([h1, rng.integers(0, rig["cfg"].vocab, size=29).astype(np.int32)])
+    _, e2, r2 = sess.spec_run(turn2, tsb.run_config(tsb.shaping(temperature=0.0), 16, 3, reuse_prefix=True))
+    assert r2.reused_prefix == len(h1)
+    cold = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 32)
+    _, e3, _ = cold.spec_run(turn2, rc)
+    assert np.array_equal(e2, e3)
+    sess.close(), cold.close()
 
 
 def test_adaptive_depth_changes_the_round_shape_not_the_output(rig, oracle):
@@ -488,14 +513,14 @@ def test_mixed_recipe_layers_match_the_oracle(oracle, order, recipe_name):
     if recipe_name == "q5_k_m":
         recipe[W_EMBED] = tsb.Q8_0
         base = tsb.Q5_K
-    mats, norms = tsb.random_weights(cfg, 5, oracle, qtype=base, real_ffn=1408, qtype_of=recipe)
+    mats, norms = weights.random_weights(cfg, 5, oracle, qtype=base, real_ffn=1408, qtype_of=recipe)
     target = tsb.Model(ctx, cfg)
-    tsb.load_weights(target, mats, norms, order=[W_V] if order else None)
+    weights.load_weights(target, mats, norms, order=[W_V] if order else None)
     assert target.weight_bytes == sum(b.size for (l, w), (b, _, _, _) in mats.items() if w != W_EMBED)
     ocfg = oracle.ModelCfg(cfg.n_layers, cfg.d_model, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.vocab,
                            cfg.max_context, cfg.rms_eps, cfg.rope_theta)
     ot = oracle.Model(ocfg, threads=8)
-    tsb.load_weights(ot, mats, norms)
+    weights.load_weights(ot, mats, norms)
     sess = tsb.Session(ctx, target, None, 1, 8)
     ost = oracle.State(ot)
     rng = np.random.default_rng(9)
@@ -520,9 +545,9 @@ def test_a_model_loaded_from_a_resident_weight_file_gives_the_same_logits(oracle
     from turbospark_b200.model import W_V, W_DOWN, W_LM_HEAD, W_Q
     ctx = tsb.Ctx(0)
     cfg = tsb.config_tiny(max_context=256)
-    mats, norms = tsb.random_weights(cfg, 6, oracle, real_ffn=1408, qtype_of={W_V: tsb.Q6_K, W_DOWN: tsb.Q6_K, W_LM_HEAD: tsb.Q6_K})
+    mats, norms = weights.random_weights(cfg, 6, oracle, real_ffn=1408, qtype_of={W_V: tsb.Q6_K, W_DOWN: tsb.Q6_K, W_LM_HEAD: tsb.Q6_K})
     direct = tsb.Model(ctx, cfg)
-    tsb.load_weights(direct, mats, norms)
+    weights.load_weights(direct, mats, norms)
     path = tmp_path / "model_weights.bin"
     path.write_bytes(resident.build_resident_file(resident.llama_tensor_list(cfg, mats, norms)))
     idx = resident.ResidentIndex(path)

@@ -3,6 +3,8 @@ router_topk_gemma4 and the two MoE kernels (crates/gpu/src/shaders/moe_gguf.meta
 import numpy as np
 import pytest
 
+from tests import weights
+
 pytestmark = pytest.mark.gpu
 REL, ABS = 2e-3, 1e-3
 
@@ -77,7 +79,7 @@ def test_routed_feed_forward_flags_an_expert_id_outside_the_table(ctx, oracle):
 def test_router_logits_match_the_oracle(ctx, oracle):
     import turbospark_b200 as tsb
     cfg = tsb.config_tiny()
-    moe = tsb.random_moe_weights(cfg, 8, 256, 3, oracle)
+    moe = weights.random_moe_weights(cfg, 8, 256, 3, oracle)
     q, sc, bi, _, _ = moe[0]
     rng = np.random.default_rng(4)
     x16 = oracle.f32_to_f16_bits(rng.standard_normal((5, cfg.d_model)).astype(np.float32))
@@ -97,18 +99,18 @@ def test_a_model_with_a_routed_feed_forward_matches_the_oracle_forward(oracle):
     E, K, F = 8, 2, 256
     ctx = tsb.Ctx(0)
     cfg = tsb.config_tiny(max_context=256)
-    mats, norms = tsb.random_weights(cfg, 7, oracle, real_ffn=1408)
-    moe = tsb.random_moe_weights(cfg, E, F, 8, oracle)
+    mats, norms = weights.random_weights(cfg, 7, oracle, real_ffn=1408)
+    moe = weights.random_moe_weights(cfg, E, F, 8, oracle)
     target = tsb.Model(ctx, cfg)
     target.set_moe(E, K, F)
-    tsb.load_weights(target, mats, norms, skip=tsb.DENSE_FFN)
-    tsb.load_moe_weights(target, moe)
+    weights.load_weights(target, mats, norms, skip=weights.DENSE_FFN)
+    weights.load_moe_weights(target, moe)
     ocfg = oracle.ModelCfg(cfg.n_layers, cfg.d_model, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.vocab,
                            cfg.max_context, cfg.rms_eps, cfg.rope_theta)
     ot = oracle.Model(ocfg, threads=8)
     ot.set_moe(E, K, F)
-    tsb.load_weights(ot, mats, norms, skip=tsb.DENSE_FFN)
-    tsb.load_moe_weights(ot, moe)
+    weights.load_weights(ot, mats, norms, skip=weights.DENSE_FFN)
+    weights.load_moe_weights(ot, moe)
     sess = tsb.Session(ctx, target, None, 1, 8)
     ost = oracle.State(ot)
     rng = np.random.default_rng(2)

@@ -10,4 +10,4 @@ from .capi import (row_descs, shaping, Ctx, DeviceBuffer, TsbError, lib, lib_pat
 __all__ = ["row_descs", "shaping", "Ctx", "DeviceBuffer", "TsbError", "lib", "lib_path", "Q4_K", "Q6_K", "MXFP4", "Q5_K", "Q8_0", "RowDesc", "Shaping",
            "AcceptOut", "KvCache"]
 from .model import (Model, Session, ModelConfig, RunConfig, RunResult, TreeNode, run_config, config_tiny, config_8b_target,
-                    config_8b_draft, random_weights, load_weights, random_moe_weights, load_moe_weights, DENSE_FFN)
+                    config_8b_draft)

@@ -111,9 +111,13 @@ cudaError_t launch_router_logits(tsb_ctx* ctx, cudaStream_t st, const uint8_t* q
                                  const __half* x, int64_t x_stride, int tokens, int n_experts, int d, float* out);
 cudaError_t launch_moe_route(tsb_ctx* ctx, cudaStream_t st, const float* logits, int tokens, int n_experts, int k, int32_t* ids,
                              __half* weights);
+// expert_lo / n_local: the expert matrices passed hold experts [expert_lo, expert_lo + n_local) only (n_local == 0: all
+// of them); (row, slot) pairs routed elsewhere are skipped and their values are zero.
 cudaError_t launch_moe_ffn(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* gate_up, const uint8_t* down, int n_experts,
                            int d_model, int ffn, const __half* x, int64_t x_stride, const __half* residual, const int32_t* ids,
-                           const __half* weights, int tokens, int k, __half* y, void* workspace);
+                           const __half* weights, int tokens, int k, __half* y, void* workspace, int expert_lo = 0, int n_local = 0);
+// f16(x) for n f32 values (the summed o_proj shares of a tensor-parallel pass)
+cudaError_t launch_f32_to_f16(tsb_ctx* ctx, cudaStream_t st, const float* x, __half* y, int64_t n);
 
 // The tensor-memory (tcgen05) path for many token rows: Q4_K, rows a multiple of 128.  x is natural f16.
 bool gemm_wide_supported(int qtype, int64_t rows, int64_t cols, int tokens);

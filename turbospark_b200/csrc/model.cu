@@ -96,6 +96,8 @@ static void mat_free(tsb_ctx* ctx, Mat& m) {
     m = Mat();
 }
 
+static int local_experts(const tsb_model* m) { return m->n_local_experts > 0 ? m->n_local_experts : m->n_experts; }
+
 static int64_t rows_of_v(const tsb_model_config& c) { return (int64_t)c.n_kv_heads * c.head_dim; }
 
 static Mat* fused_slot(tsb_model* m, int layer, int which, int64_t* row_off, int64_t* total_rows, int64_t* want_rows,
@@ -224,6 +226,18 @@ int32_t tsb_model_set_moe(tsb_model* m, int32_t n_experts, int32_t top_k, int32_
     TSB_REQUIRE(ctx, moe_ffn > 0 && moe_ffn % 256 == 0, "the expert width must be a multiple of 256");
     for (const LayerW& l : m->layers) TSB_REQUIRE(ctx, !l.wgu.data && !l.wdown.data, "set_moe comes before the tensors");
     m->n_experts = n_experts, m->top_k = top_k, m->moe_ffn = moe_ffn;
+    m->expert_lo = 0, m->n_local_experts = 0;
+    return TSB_OK;
+}
+
+int32_t tsb_model_set_expert_shard(tsb_model* m, int32_t expert_lo, int32_t n_local) {
+    if (!m) return TSB_ERR_INVALID;
+    tsb_ctx* ctx = m->ctx;
+    TSB_REQUIRE(ctx, m->n_experts > 0, "the model has no experts (tsb_model_set_moe first)");
+    TSB_REQUIRE(ctx, expert_lo >= 0 && n_local >= 1 && expert_lo + n_local <= m->n_experts, "experts %d..%d outside the model's %d", expert_lo,
+                expert_lo + n_local, m->n_experts);
+    for (const LayerW& l : m->layers) TSB_REQUIRE(ctx, !l.experts_gate_up && !l.experts_down, "the shard comes before the expert tensors");
+    m->expert_lo = expert_lo, m->n_local_experts = n_local;
     return TSB_OK;
 }
 
@@ -265,8 +279,8 @@ int32_t tsb_model_set_experts(tsb_model* m, int32_t layer, int32_t qtype, const 
     LayerW& l = m->layers[layer];
     l.moe_owned = true;
     l.experts_qtype = qtype;
-    const size_t gu = (size_t)m->n_experts * 2 * m->moe_ffn * tsb_row_bytes(qtype, m->cfg.d_model);
-    const size_t dn = (size_t)m->n_experts * m->cfg.d_model * tsb_row_bytes(qtype, m->moe_ffn);
+    const size_t gu = (size_t)local_experts(m) * 2 * m->moe_ffn * tsb_row_bytes(qtype, m->cfg.d_model);
+    const size_t dn = (size_t)local_experts(m) * m->cfg.d_model * tsb_row_bytes(qtype, m->moe_ffn);
     int32_t rc;
     if ((rc = upload(ctx, (void**)&l.experts_gate_up, gate_up_blocks, gu)) || (rc = upload(ctx, (void**)&l.experts_down, down_blocks, dn))) return rc;
     return TSB_OK;
@@ -358,8 +372,8 @@ int32_t tsb_model_fill_synthetic(tsb_model* m, int32_t qtype, int32_t lm_head_qt
         if (m->n_experts > 0) {
             // routed layers: random 8-bit router with scale 0.004 / bias -0.5 (zero-mean weights), experts as blocks
             const size_t rn = (size_t)m->n_experts * c.d_model, rg = rn / 64;
-            const int64_t gu_b = (int64_t)m->n_experts * 2 * m->moe_ffn * tsb_row_bytes(qtype, c.d_model);
-            const int64_t dn_b = (int64_t)m->n_experts * c.d_model * tsb_row_bytes(qtype, m->moe_ffn);
+            const int64_t gu_b = (int64_t)local_experts(m) * 2 * m->moe_ffn * tsb_row_bytes(qtype, c.d_model);
+            const int64_t dn_b = (int64_t)local_experts(m) * c.d_model * tsb_row_bytes(qtype, m->moe_ffn);
             l.moe_owned = true, l.experts_qtype = qtype;
             void* p;
             if (!l.router_q) {
@@ -402,7 +416,7 @@ int64_t tsb_model_weight_bytes(const tsb_model* m) {
     for (auto& l : m->layers) t += mat_bytes(l.wqkv) + mat_bytes(l.wv) + mat_bytes(l.wo) + mat_bytes(l.wgu) + mat_bytes(l.wdown);
     if (m->n_experts > 0)  // every expert, although a pass reads only the routed ones
         for (auto& l : m->layers)
-            t += (int64_t)m->n_experts * (2 * m->moe_ffn * tsb_row_bytes(l.experts_qtype, m->cfg.d_model) +
+            t += (int64_t)local_experts(m) * (2 * m->moe_ffn * tsb_row_bytes(l.experts_qtype, m->cfg.d_model) +
                                           m->cfg.d_model * tsb_row_bytes(l.experts_qtype, m->moe_ffn)) +
                  (int64_t)m->n_experts * m->cfg.d_model;
     return t;
@@ -410,7 +424,7 @@ int64_t tsb_model_weight_bytes(const tsb_model* m) {
 
 }  // extern "C"
 
-constexpr int WIDE_MIN_ROWS = 24;  // passes of this many rows and more take the tensor-memory matmul
+constexpr int WIDE_MIN_ROWS = 24;  // a model whose largest pass has this many rows or more runs every pass on the tensor-memory matmul
 
 static int32_t model_complete(const tsb_model* m) {
     tsb_ctx* ctx = m->ctx;
@@ -436,7 +450,7 @@ static int32_t dev_alloc(tsb_ctx* ctx, std::vector<void*>& owned, size_t bytes, 
     return rc;
 }
 
-static int32_t runtime_init(tsb_session* s, ModelRt& rt, const tsb_model* model, int n_streams, int max_rows, int page_tokens) {
+static int32_t runtime_init(tsb_session* s, ModelRt& rt, const tsb_model* model, int n_streams, int max_rows, int page_tokens, bool is_draft) {
     tsb_ctx* ctx = s->ctx;
     rt.model = model;
     const tsb_model_config& c = model->cfg;
@@ -478,13 +492,20 @@ static int32_t runtime_init(tsb_session* s, ModelRt& rt, const tsb_model* model,
             return rc;
         cudaMemset(rt.moe_zero, 0, (size_t)R * c.d_model * 2);
         if ((rc = A((size_t)R * sizeof(float), (void**)&rt.moe_unit_ss))) return rc;
+        if ((rc = A((size_t)R * c.d_model * sizeof(float), (void**)&rt.tp_partial))) return rc;
         {
             std::vector<float> unit((size_t)R, (float)c.d_model);  // sum / d_model = 1 and eps = 0: 1/rms = 1 exactly
             TSB_CUDA(ctx, cudaMemcpy(rt.moe_unit_ss, unit.data(), unit.size() * sizeof(float), cudaMemcpyHostToDevice));
         }
         return TSB_OK;
     }
-    bool wide = R >= WIDE_MIN_ROWS && gemm_wide_supported(model->lm_head.qtype, model->lm_head.rows, model->lm_head.cols, R);
+    // One matmul path per (session, model), whatever a pass's row count: the register path and the tensor-memory path
+    // sum in different orders, so a model that switched between them by row count would not reproduce its own
+    // single-row results in a batch (the reference's verify runs the decode path's arithmetic).  The tensor-memory path
+    // is taken when the model's largest pass has WIDE_MIN_ROWS rows or more: the target's verify carries max_rows rows
+    // of every stream; the drafter's largest pass is two rows per stream (a round's first step) or one stream's tree.
+    const int largest_pass = is_draft ? std::max(2 * n_streams, max_rows) : R;
+    bool wide = largest_pass >= WIDE_MIN_ROWS && gemm_wide_supported(model->lm_head.qtype, model->lm_head.rows, model->lm_head.cols, R);
     for (const LayerW& l : model->layers)
         wide = wide && !l.wv.data && gemm_wide_supported(l.wqkv.qtype, l.wqkv.rows, l.wqkv.cols, R) && gemm_wide_supported(l.wo.qtype, l.wo.rows, l.wo.cols, R) &&
                gemm_wide_supported(l.wgu.qtype, l.wgu.rows, l.wgu.cols, R) && gemm_wide_supported(l.wdown.qtype, l.wdown.rows, l.wdown.cols, R);
@@ -601,12 +622,25 @@ static cudaError_t forward_device_moe(tsb_session* s, ModelRt& rt, const int32_t
         }
         FW(launch_attn_decode_rows(ctx, st, rt.kv, L, rt.q, qd, nullptr, out_o, rows_dev, rows, rows_per_seq, c.n_q_heads, scale,
                                    max_len, rt.attn_scratch, s->n_streams * s->max_rows));
-        FW(launch_gemm_quant(ctx, st, l.wo.qtype, l.wo.data, l.wo.rows, l.wo.cols, in_o, rt.w_o, c.d_model, rows, false));
+        if (comm_world(s->comm) > 1) {
+            // tensor-parallel attention: this rank's o_proj holds its heads' columns; the f32 shares are summed over the
+            // ranks, then rounded to f16 once, as the single projection is
+            FW(launch_gemm_quant(ctx, st, l.wo.qtype, l.wo.data, l.wo.rows, l.wo.cols, in_o, rt.tp_partial, c.d_model, rows, true));
+            FW(comm_all_reduce_f32(s->comm, st, rt.tp_partial, (size_t)rows * c.d_model));
+            FW(launch_f32_to_f16(ctx, st, rt.tp_partial, rt.w_o, (int64_t)rows * c.d_model));
+        } else {
+            FW(launch_gemm_quant(ctx, st, l.wo.qtype, l.wo.data, l.wo.rows, l.wo.cols, in_o, rt.w_o, c.d_model, rows, false));
+        }
         FW(launch_rmsnorm_rows(ctx, st, rt.h, rt.w_o, l.ffn_norm, rt.w_xn, none, rows, c.d_model, c.rms_eps));
         FW(launch_router_logits(ctx, st, l.router_q, l.router_scale, l.router_bias, rt.w_xn, c.d_model, rows, m->n_experts, c.d_model, rt.moe_logits));
         FW(launch_moe_route(ctx, st, rt.moe_logits, rows, m->n_experts, m->top_k, rt.moe_ids, rt.moe_w));
         FW(launch_moe_ffn(ctx, st, l.experts_qtype, l.experts_gate_up, l.experts_down, m->n_experts, c.d_model, m->moe_ffn, rt.w_xn, c.d_model,
-                          rt.moe_zero, rt.moe_ids, rt.moe_w, rows, m->top_k, nullptr, rt.moe_ws));
+                          rt.moe_zero, rt.moe_ids, rt.moe_w, rows, m->top_k, nullptr, rt.moe_ws, m->expert_lo, m->n_local_experts));
+        // sharded experts: every (row, slot) value was computed by exactly one rank, the others hold zero there - the
+        // sum over the ranks is exact, and the slot-ordered combine below sees the values of a single GPU
+        if (m->n_local_experts > 0)
+            FW(comm_all_reduce_f32(s->comm, st, const_cast<float*>(moe_ffn_values(rt.moe_ws, rows, m->top_k, m->n_experts, c.d_model, m->moe_ffn)),
+                                   (size_t)rows * m->top_k * c.d_model));
         // the slot-ordered weighted sum (over a zero residual, rounded to f16), its add onto the stream and the next norm
         const void* g = L + 1 < c.n_layers ? (const void*)m->layers[L + 1].attn_norm : (const void*)m->out_norm;
         FW(launch_combine_norm_rows(ctx, st, rt.h, moe_ffn_values(rt.moe_ws, rows, m->top_k, m->n_experts, c.d_model, m->moe_ffn), rt.moe_w,
@@ -626,12 +660,12 @@ static cudaError_t forward_device_moe(tsb_session* s, ModelRt& rt, const int32_t
 // already on the device.  Cursors are not touched here.
 static cudaError_t forward_device(tsb_session* s, ModelRt& rt, const int32_t* tokens_dev, int token_stride,
                                   const tsb_row_desc* rows_dev, int rows, int rows_per_seq, int max_len, __half* logits,
-                                  int64_t logits_stride, bool last_rows_only = false) {
+                                  int64_t logits_stride, bool last_rows_only = false, bool matmuls_only = false) {
     if (s->replay) return cudaSuccess;  // the captured graph already holds this work
     if (rt.model->n_experts > 0)
         return forward_device_moe(s, rt, tokens_dev, token_stride, rows_dev, rows, rows_per_seq, (max_len + 511) / 512 * 512, logits,
                                   logits_stride, last_rows_only);
-    if (rt.wide_ok && rows >= WIDE_MIN_ROWS)
+    if (rt.wide_ok && !matmuls_only)
         return forward_device_wide(s, rt, tokens_dev, token_stride, rows_dev, rows, rows_per_seq, (max_len + 511) / 512 * 512, logits,
                                    logits_stride, last_rows_only);
     tsb_ctx* ctx = s->ctx;
@@ -651,8 +685,9 @@ static cudaError_t forward_device(tsb_session* s, ModelRt& rt, const int32_t* to
     const int R = s->n_streams * s->max_rows;
     const int parts = c.d_model / 16;
     auto ss_slot = [&](int i) { return rt.ss + (size_t)i * R * parts; };
+    // (matmuls_only: the measurement aid - the layer matmuls with their real epilogues over whatever the buffers hold)
     // embedding: residual stream, layer 0's operand f16(h * g), sum of h^2 (one partial per row), RoPE table
-    FW(launch_embed_norm(ctx, st, m->embed.qtype, m->embed.data, c.vocab, c.d_model, tokens_dev, token_stride, rows, rt.h,
+    if (!matmuls_only) FW(launch_embed_norm(ctx, st, m->embed.qtype, m->embed.data, c.vocab, c.d_model, tokens_dev, token_stride, rows, rt.h,
                          m->layers[0].attn_norm, out_d, ss_slot(0), rt.cs, rows_dev, c.head_dim, c.rope_theta));
     for (int L = 0; L < c.n_layers; L++) {
         const LayerW& l = m->layers[L];
@@ -668,8 +703,9 @@ static cudaError_t forward_device(tsb_session* s, ModelRt& rt, const int32_t* to
                 FW(launch_gemm_fused(ctx, st, l.wv.qtype, l.wv.data, l.wv.rows, l.wv.cols, in_d, rows, EPI_ROPE_STORE, a));
             }
         }
-        FW(launch_attn_decode_rows(ctx, st, rt.kv, L, rt.q, (int64_t)c.n_q_heads * c.head_dim, nullptr, out_o, rows_dev, rows,
-                                   rows_per_seq, c.n_q_heads, scale, max_len, rt.attn_scratch, s->n_streams * s->max_rows));
+        if (!matmuls_only)
+            FW(launch_attn_decode_rows(ctx, st, rt.kv, L, rt.q, (int64_t)c.n_q_heads * c.head_dim, nullptr, out_o, rows_dev, rows,
+                                       rows_per_seq, c.n_q_heads, scale, max_len, rt.attn_scratch, s->n_streams * s->max_rows));
         {   // o_proj; epilogue: residual add, next operand f16(h * g_ffn), partial sums of h^2
             EpiArgs a;
             a.h = rt.h, a.g = l.ffn_norm, a.out = out_d, a.ss_out = ss_slot(2 * L + 1);
@@ -687,7 +723,7 @@ static cudaError_t forward_device(tsb_session* s, ModelRt& rt, const int32_t* to
             FW(launch_gemm_fused(ctx, st, l.wdown.qtype, l.wdown.data, l.wdown.rows, l.wdown.cols, in_f, rows, EPI_RESID_NORM, a));
         }
     }
-    if (logits) {
+    if (logits && !matmuls_only) {
         // head over the final-normed operand; row t of the logits sits at logits + t * logits_stride
         EpiArgs a;
         a.ss_in = ss_slot(2 * c.n_layers), a.ss_parts = parts, a.d_in = c.d_model, a.eps = c.rms_eps;
@@ -813,8 +849,8 @@ int32_t tsb_session_create(tsb_ctx* ctx, const tsb_model* target, const tsb_mode
     if (cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking) != cudaSuccess) return fail(TSB_ERR_CUDA);
     for (auto& ev : s->ev)
         if (cudaEventCreate(&ev) != cudaSuccess) return fail(TSB_ERR_CUDA);
-    if ((rc = runtime_init(s, s->target, target, n_streams, max_rows, page_tokens))) return fail(rc);
-    if (draft && (rc = runtime_init(s, s->draft, draft, n_streams, max_rows, page_tokens))) return fail(rc);
+    if ((rc = runtime_init(s, s->target, target, n_streams, max_rows, page_tokens, false))) return fail(rc);
+    if (draft && (rc = runtime_init(s, s->draft, draft, n_streams, max_rows, page_tokens, true))) return fail(rc);
     s->has_draft = draft != nullptr;
     {
         const char* env = getenv("TSB_GRAPH");
@@ -861,6 +897,15 @@ void tsb_session_destroy(tsb_session* s) {
         if (ev) cudaEventDestroy(ev);
     if (s->stream) cudaStreamDestroy(s->stream);
     delete s;
+}
+
+int32_t tsb_session_set_comm(tsb_session* s, tsb_comm* c) {
+    if (!s) return TSB_ERR_INVALID;
+    DeviceGuard g(s->ctx);
+    TSB_CUDA(s->ctx, cudaStreamSynchronize(s->stream));
+    if (s->graph) cudaGraphExecDestroy(s->graph), s->graph = nullptr;  // captured rounds hold the old exchange steps
+    s->comm = c;
+    return TSB_OK;
 }
 
 tsb_kv* tsb_session_kv(tsb_session* s, int32_t which) { return !s ? nullptr : (which == 0 ? s->target.kv : s->draft.kv); }
@@ -1689,29 +1734,34 @@ int32_t tsb_session_time_matmuls(tsb_session* s, int32_t rows, int32_t iters, fl
     const tsb_model* m = rt.model;
     const tsb_model_config& c = m->cfg;
     const int64_t qkv_dim = (int64_t)(c.n_q_heads + 2 * c.n_kv_heads) * c.head_dim;
-    const ActOperand in_d{rt.act_d.xp, rt.act_d.xs}, in_o{rt.act_o.xp, rt.act_o.xs}, in_f{rt.act_f.xp, rt.act_f.xs};
     cudaStream_t st = s->stream;
     int64_t bytes = 0;
     int launches = 0;
-    // plain epilogues into the logits buffer: the weight streaming and the mma work are those of the forward pass
-    void* sink = s->logits_target;
+    // The launches are the pass's own: the same kernels with the same fused epilogues (1/rms + RoPE + K/V store,
+    // residual + norm operand, SiLU * up), writing the session's real buffers; the rows sit past every stream's cursor
+    // (in-flight slots nobody committed), so the caches' committed contents are untouched.  Attention, embedding and
+    // head are left out.
+    TSB_REQUIRE(ctx, rows % s->n_streams == 0, "rows must be a whole number of rows per stream");
+    const int per = rows / s->n_streams;
+    std::vector<int32_t> streams(s->n_streams);
+    for (int q = 0; q < s->n_streams; q++) streams[q] = q;
+    const tsb_row_desc* rd;
+    int max_len;
+    s->stage_used = 0;
+    int32_t rc = stage_rows(s, rt, streams.data(), s->n_streams, per, nullptr, nullptr, &rd, nullptr, &max_len);
+    if (rc) return rc;
+    TSB_REQUIRE(ctx, !rt.wide_ok, "the matmul timing covers sessions whose target runs the few-row matmul path (largest pass below %d rows)", WIDE_MIN_ROWS);
     for (int it = -1; it < iters; it++) {  // iteration -1 is a warm-up
         if (it == 0) TSB_CUDA(ctx, cudaEventRecord(s->ev[0], st));
-        for (int L = 0; L < c.n_layers; L++) {
-            const LayerW& l = m->layers[L];
-            TSB_CUDA(ctx, launch_gemm_quant(ctx, st, l.wqkv.qtype, l.wqkv.data, l.wqkv.rows, l.wqkv.cols, in_d, sink, qkv_dim, rows, false));
-            if (l.wv.data) TSB_CUDA(ctx, launch_gemm_quant(ctx, st, l.wv.qtype, l.wv.data, l.wv.rows, l.wv.cols, in_d, sink, qkv_dim, rows, false));
-            TSB_CUDA(ctx, launch_gemm_quant(ctx, st, l.wo.qtype, l.wo.data, l.wo.rows, l.wo.cols, in_o, sink, c.d_model, rows, false));
-            TSB_CUDA(ctx, launch_gemm_quant(ctx, st, l.wgu.qtype, l.wgu.data, l.wgu.rows, l.wgu.cols, in_d, sink, 2 * (int64_t)c.ffn, rows, false));
-            TSB_CUDA(ctx, launch_gemm_quant(ctx, st, l.wdown.qtype, l.wdown.data, l.wdown.rows, l.wdown.cols, in_f, sink, c.d_model, rows, false));
-            if (it == 0) {
-                bytes += mat_bytes(l.wqkv) + mat_bytes(l.wv) + mat_bytes(l.wo) + mat_bytes(l.wgu) + mat_bytes(l.wdown);
-                launches += (l.wv.data ? 5 : 4) * ((rows + 63) / 64);
-            }
-        }
+        TSB_CUDA(ctx, forward_device(s, rt, nullptr, 1, rd, rows, per, max_len, nullptr, 0, false, true));
+    }
+    for (const LayerW& l : m->layers) {
+        bytes += mat_bytes(l.wqkv) + mat_bytes(l.wv) + mat_bytes(l.wo) + mat_bytes(l.wgu) + mat_bytes(l.wdown);
+        launches += (l.wv.data ? 5 : 4) * ((rows + 63) / 64);
     }
     TSB_CUDA(ctx, cudaEventRecord(s->ev[1], st));
-    int32_t rc = tsb_stream_sync(ctx, st);
+    rc = tsb_stream_sync(ctx, st);
+    s->stage_used = 0;
     if (rc) return rc;
     TSB_CUDA(ctx, cudaEventElapsedTime(out_ms, s->ev[0], s->ev[1]));
     // activations in and out per launch are part of the algorithmic bytes too

@@ -37,6 +37,7 @@ struct tsb_model {
     uint16_t* out_norm = nullptr;
     bool out_norm_owned = false;
     int n_experts = 0, top_k = 0, moe_ffn = 0;  // n_experts > 0: every layer's feed-forward is routed
+    int expert_lo = 0, n_local_experts = 0;     // the experts this model holds (all of them unless sharded)
 };
 
 // Shape of the trees a session drafts (tsb_session_set_tree, or a run configuration's tree fields).
@@ -72,7 +73,9 @@ struct ModelRt {
     ActBuf act_d, act_o, act_f;  // matmul operands of width d_model, n_q_heads*head_dim, ffn
     void* attn_scratch = nullptr;
     size_t attn_scratch_bytes = 0;
-    // many-row passes (24 rows and more, all matrices Q4_K): natural-layout f16 buffers around the tensor-memory matmul
+    // wide_ok: every pass of this model in this session runs the tensor-memory matmul (all matrices Q4_K and the model's
+    // largest pass has 24 rows or more) with natural-layout f16 buffers around it; otherwise every pass runs the
+    // register path.  Never a mix: the two sum in different orders.
     bool wide_ok = false;
     __half *w_xn = nullptr, *w_qkv = nullptr, *w_ao = nullptr, *w_o = nullptr, *w_gu = nullptr, *w_a = nullptr, *w_logits = nullptr;
     void* w_ws = nullptr;
@@ -83,6 +86,7 @@ struct ModelRt {
     __half *moe_w = nullptr, *moe_zero = nullptr;
     float* moe_unit_ss = nullptr;  // [R] sums of squares that make the q|k|v epilogue's 1/rms exactly one (the operand is already normed)
     void* moe_ws = nullptr;
+    float* tp_partial = nullptr;  // [R, d_model] f32: this rank's share of the o_proj sums, summed over the ranks in place
     std::vector<std::vector<int32_t>> fed;  // per stream: tokens absorbed, by position (target only)
     std::vector<PendingVerify> pending;     // per stream (target only)
 };
@@ -122,7 +126,12 @@ struct tsb_session {
     uint64_t graph_key = 0, graph_launches = 0;
     int rounds_done = 0;
     TreeShape tree;  // what tsb_producer_tree_nodes / tsb_producer_draft_tree use
+    tsb_comm* comm = nullptr;  // exchange steps of a sharded routed model (null: single GPU)
 };
+
+// comm.cu: in-place f32 sum over the ranks on `st` (a no-op for a null or single-rank comm).
+cudaError_t comm_all_reduce_f32(tsb_comm* c, cudaStream_t st, float* buf, size_t count);
+int comm_world(const tsb_comm* c);
 
 // One speculative round for the listed streams with k proposals each (model.cu).
 int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_active, int k, const tsb_run_config* cfg,

@@ -161,7 +161,9 @@ __global__ void moe_combine_kernel(const __half* __restrict__ residual, const fl
 __global__ void __launch_bounds__(1024)
     moe_dispatch_kernel(const int32_t* __restrict__ ids, int P, int k, int n_experts, int32_t* __restrict__ count,
                         int32_t* __restrict__ tile_start, int32_t* __restrict__ src_pad, int32_t* __restrict__ dst_pad, int pad_slots,
-                        uint32_t* __restrict__ err) {
+                        uint32_t* __restrict__ err, int n_total, int expert_lo) {
+    // n_experts experts are held here: [expert_lo, expert_lo + n_experts) of the n_total the router picks from;
+    // pairs routed to the others belong to another rank and are left out
     __shared__ int cnt[MOE_MAX_EXPERTS], fill[MOE_MAX_EXPERTS], tstart[MOE_MAX_EXPERTS];
     pdl_wait();
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) cnt[e] = 0, fill[e] = 0;
@@ -169,10 +171,12 @@ __global__ void __launch_bounds__(1024)
     __syncthreads();
     for (int i = threadIdx.x; i < P; i += blockDim.x) {
         int e = ids[i];
-        if (e < 0 || e >= n_experts) {
+        if (e < 0 || e >= n_total) {
             atomicCAS(err, 0u, (uint32_t)TSB_DEV_BAD_INDEX);
-            e = 0;
+            e = expert_lo;
         }
+        e -= expert_lo;
+        if (e < 0 || e >= n_experts) continue;
         atomicAdd(&cnt[e], 1);
     }
     __syncthreads();
@@ -186,7 +190,9 @@ __global__ void __launch_bounds__(1024)
     __syncthreads();
     for (int i = threadIdx.x; i < P; i += blockDim.x) {
         int e = ids[i];
-        if (e < 0 || e >= n_experts) e = 0;
+        if (e < 0 || e >= n_total) e = expert_lo;
+        e -= expert_lo;
+        if (e < 0 || e >= n_experts) continue;
         const int p = tstart[e] * 8 + atomicAdd(&fill[e], 1);
         src_pad[p] = i / k, dst_pad[p] = i;
     }
@@ -248,8 +254,10 @@ size_t moe_ffn_workspace_bytes(int tokens, int k, int n_experts, int d_model, in
 // phase (per 64 rows of the fullest expert's possible load), the slot-ordered combine.  Graph-capturable.
 cudaError_t launch_moe_ffn(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8_t* gate_up, const uint8_t* down, int n_experts,
                            int d_model, int ffn, const __half* x, int64_t x_stride, const __half* residual, const int32_t* ids,
-                           const __half* weights, int tokens, int k, __half* y, void* workspace) {
+                           const __half* weights, int tokens, int k, __half* y, void* workspace, int expert_lo, int n_local) {
     const MoeLayout L = moe_layout(tokens, k, n_experts, d_model, ffn);
+    const int n_total = n_experts;
+    if (n_local > 0) n_experts = n_local;  // the matrices hold this rank's experts only
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     int32_t* count = reinterpret_cast<int32_t*>(ws + L.off_count);
     int32_t* tstart = reinterpret_cast<int32_t*>(ws + L.off_tstart);
@@ -260,8 +268,11 @@ cudaError_t launch_moe_ffn(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8
     const ActOperand xin{xin_w.xp, xin_w.xs}, act{act_w.xp, act_w.xs};
     float* values = reinterpret_cast<float*>(ws + L.off_values);
     const int P = tokens * k, slots = L.pad_tiles * 8;
-    cudaError_t e = tsb_launch(ctx, moe_dispatch_kernel, dim3(1), dim3(1024), 0, st, true, ids, P, k, n_experts, count, tstart, src_pad,
-                               dst_pad, slots, ctx->dev_error);
+    cudaError_t e = cudaSuccess;
+    // a sharded call writes only its own experts' (row, slot) outputs: the others must read as zero for the exact sum
+    if (n_local > 0 && (e = cudaMemsetAsync(values, 0, (size_t)P * d_model * sizeof(float), st)) != cudaSuccess) return e;
+    e = tsb_launch(ctx, moe_dispatch_kernel, dim3(1), dim3(1024), 0, st, n_local == 0, ids, P, k, n_experts, count, tstart, src_pad,
+                   dst_pad, slots, ctx->dev_error, n_total, n_local > 0 ? expert_lo : 0);
     if (e != cudaSuccess) return e;
     if ((e = launch_act_prepare_gather(ctx, st, x, x_stride, src_pad, slots, d_model, xin_w.xp, xin_w.xs)) != cudaSuccess) return e;
     const int64_t gu_bytes = (int64_t)2 * ffn * tsb_row_bytes(qtype, d_model), down_bytes = (int64_t)d_model * tsb_row_bytes(qtype, ffn);
@@ -282,7 +293,16 @@ cudaError_t launch_moe_ffn(tsb_ctx* ctx, cudaStream_t st, int qtype, const uint8
 }
 
 namespace {
+__global__ void f32_to_f16_kernel(const float* __restrict__ x, __half* __restrict__ y, int64_t n) {
+    pdl_wait();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = __float2half_rn(x[i]);
+}
 }  // namespace
+
+cudaError_t launch_f32_to_f16(tsb_ctx* ctx, cudaStream_t st, const float* x, __half* y, int64_t n) {
+    return tsb_launch(ctx, f32_to_f16_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, false, x, y, n);
+}
 
 extern "C" {
 
