@@ -551,81 +551,62 @@ __device__ __forceinline__ void run_epilogue(const EpiArgs& e, const Group& gr, 
                 reinterpret_cast<__half*>(e.y)[o] = __float2half_rn(v);
         }
     } else if constexpr (EPI == EPI_RESID_NORM) {
-        // thread = (token, eight columns); the two threads of a token are neighbours
-        const int tok = tid >> 1, part = tid & 1;
-        const bool active = tok < tokens;
-        const int col0 = gr.tile0 * TILE_ROWS + part * 8;
-        float ss = 0.f, sx = 0.f;
-        if (active) {
-            __half* hp = e.h + (size_t)(tok0 + tok) * rows + col0;
-            uint4 hv = *reinterpret_cast<const uint4*>(hp);
-            const uint4 gv = *reinterpret_cast<const uint4*>(e.g + col0);
-            __half* hh = reinterpret_cast<__half*>(&hv);
-            const uint16_t* gg = reinterpret_cast<const uint16_t*>(&gv);
-            __half xg[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
+        // thread = one (token, column) of the tile; the sixteen columns of a token sit in one half-warp, which sums
+        // their h^2 and their operand values with a butterfly
+        for (int idx = tid; idx < NTOK * 16; idx += CONSUMER_WARPS * 32) {
+            const int tok = idx >> 4, col = idx & 15;
+            const bool active = tok < tokens;
+            const int gcol = gr.tile0 * TILE_ROWS + col;
+            float hn = 0.f, xv = 0.f;
+            if (active) {
+                __half* hp = e.h + (size_t)(tok0 + tok) * rows + gcol;
                 // the matmul output is rounded to f16, then added to the residual stream in fp32 and rounded again
                 // (crates/gpu/src/shaders/dequant_q4_k.metal:112-130, utility.metal:199-208)
-                const float y = __half2float(__float2half_rn(tile_out[tok * 16 + part * 8 + i]));
-                hh[i] = __float2half_rn(__half2float(hh[i]) + y);
-                const float hn = __half2float(hh[i]);
-                ss = fmaf(hn, hn, ss);
-                xg[i] = __float2half_rn(hn * bf16_bits_to_float(gg[i]));
-                sx += __half2float(xg[i]);
+                const float y = __half2float(__float2half_rn(tile_out[idx]));
+                const __half hnew = __float2half_rn(__half2float(*hp) + y);
+                *hp = hnew;
+                hn = __half2float(hnew);
+                const __half xg = __float2half_rn(hn * bf16_bits_to_float(e.g[gcol]));
+                reinterpret_cast<__half*>(e.out.xp)[act_xp_half_index(tok0 + tok, gcol, (int)(rows >> 8))] = xg;
+                xv = __half2float(xg);
             }
-            *reinterpret_cast<uint4*>(hp) = hv;
-            e.out.xp[act_xp_index(tok0 + tok, col0, (int)(rows >> 8))] = act_pack8(xg);
-        }
-        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-        sx += __shfl_xor_sync(0xffffffffu, sx, 1);
-        if (active && part == 0) {
-            act_store_sum16(e.out.xs, tok0 + tok, gr.tile0 * TILE_ROWS, (int)(rows >> 8), sx);
-            e.ss_out[(size_t)(tok0 + tok) * (rows / 16) + gr.tile0] = ss;
-        }
-    } else if constexpr (EPI == EPI_SILU) {
-        const int tok = tid >> 1, part = tid & 1;
-        const bool active = tok < tokens;
-        const int ffn = (int)(rows / 2);
-        const int col0 = gr.tile0 * TILE_ROWS + part * 8;
-        float sx = 0.f;
-        if (active) {
-            const float inv = inv_rms[tok];
-            __half a[8];
+            float ss = hn * hn, sx = xv;
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const float g = __half2float(__float2half_rn(inv * tile_out[tok * 16 + part * 8 + i]));
-                const float u = __half2float(__float2half_rn(inv * tile_out[NTOK * 16 + tok * 16 + part * 8 + i]));
-                // utility.metal:41-52: (g / (1 + exp(-g))) * u in f32
-                const float ex = (float)exp((double)(-g));
-                a[i] = __float2half_rn(__fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, ex)), u));
-                sx += __half2float(a[i]);
+            for (int o = 8; o > 0; o >>= 1) {
+                ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                sx += __shfl_xor_sync(0xffffffffu, sx, o);
             }
-            e.out.xp[act_xp_index(tok0 + tok, col0, ffn >> 8)] = act_pack8(a);
+            if (active && col == 0) {
+                act_store_sum16(e.out.xs, tok0 + tok, gr.tile0 * TILE_ROWS, (int)(rows >> 8), sx);
+                e.ss_out[(size_t)(tok0 + tok) * (rows / 16) + gr.tile0] = ss;
+            }
         }
-        sx += __shfl_xor_sync(0xffffffffu, sx, 1);
-        if (active && part == 0) act_store_sum16(e.out.xs, tok0 + tok, gr.tile0 * TILE_ROWS, ffn >> 8, sx);
-    } else if constexpr (EPI == EPI_MOE_ACT) {
-        // crates/gpu/src/shaders/moe_gguf.metal:561-606: gate and up stay f32, acts = half(act(gate) * up)
-        const int tok = tid >> 1, part = tid & 1;
-        const bool active = tok < tokens;
+    } else if constexpr (EPI == EPI_SILU || EPI == EPI_MOE_ACT) {
+        // pair (gate tile, up tile): thread = one (token, column).  EPI_SILU: gate and up are the normed operand's
+        // products, scaled by 1/rms and rounded to f16 first (utility.metal:41-52: (g / (1 + exp(-g))) * u in f32).
+        // EPI_MOE_ACT: gate and up stay f32 (crates/gpu/src/shaders/moe_gguf.metal:561-606).
         const int ffn = (int)(rows / 2);
-        const int col0 = gr.tile0 * TILE_ROWS + part * 8;
-        float sx = 0.f;
-        if (active) {
-            __half a[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const float g = tile_out[tok * 16 + part * 8 + i];
-                const float u = tile_out[NTOK * 16 + tok * 16 + part * 8 + i];
+        for (int idx = tid; idx < NTOK * 16; idx += CONSUMER_WARPS * 32) {
+            const int tok = idx >> 4, col = idx & 15;
+            const bool active = tok < tokens;
+            const int gcol = gr.tile0 * TILE_ROWS + col;
+            float sx = 0.f;
+            if (active) {
+                float g = tile_out[idx], u = tile_out[NTOK * 16 + idx];
+                if constexpr (EPI == EPI_SILU) {
+                    const float inv = inv_rms[tok];
+                    g = __half2float(__float2half_rn(inv * g));
+                    u = __half2float(__float2half_rn(inv * u));
+                }
                 const float ex = (float)exp((double)(-g));
-                a[i] = __float2half_rn(__fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, ex)), u));
-                sx += __half2float(a[i]);
+                const __half a = __float2half_rn(__fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, ex)), u));
+                reinterpret_cast<__half*>(e.out.xp)[act_xp_half_index(tok0 + tok, gcol, ffn >> 8)] = a;
+                sx = __half2float(a);
             }
-            e.out.xp[act_xp_index(tok0 + tok, col0, ffn >> 8)] = act_pack8(a);
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) sx += __shfl_xor_sync(0xffffffffu, sx, o);
+            if (active && col == 0) act_store_sum16(e.out.xs, tok0 + tok, gr.tile0 * TILE_ROWS, ffn >> 8, sx);
         }
-        sx += __shfl_xor_sync(0xffffffffu, sx, 1);
-        if (active && part == 0) act_store_sum16(e.out.xs, tok0 + tok, gr.tile0 * TILE_ROWS, ffn >> 8, sx);
     } else if constexpr (EPI == EPI_ROPE_STORE) {
         const int hd = e.head_dim, tph = hd / 16;
         const int head = gr.tile0 / tph, t_in = gr.tile0 % tph;

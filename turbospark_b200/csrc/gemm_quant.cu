@@ -24,6 +24,35 @@
 
 namespace {
 
+// 1/rms of every token from the partial sums of x^2 its producer left (one warp).  Per token the lanes add their
+// partials in index order and meet in a butterfly - the order does not depend on the token count - but the loads of
+// four tokens are issued before the first sum, so the warp pays one memory latency per four tokens, not per token.
+__device__ __forceinline__ void token_inv_rms(const EpiArgs& epi, int tokens, int tok0, int lane, float* inv_rms) {
+    constexpr int TB = 4, PL = 8;  // tokens per batch, partials per lane per token (covers 256 partials)
+    const int parts = epi.ss_parts;
+    for (int t0 = 0; t0 < tokens; t0 += TB) {
+        float v[TB][PL];
+#pragma unroll
+        for (int tt = 0; tt < TB; tt++)
+#pragma unroll
+            for (int j = 0; j < PL; j++) {
+                const int i = lane + 32 * j;
+                v[tt][j] = (t0 + tt < tokens && i < parts) ? epi.ss_in[(size_t)(tok0 + t0 + tt) * parts + i] : 0.f;
+            }
+#pragma unroll
+        for (int tt = 0; tt < TB; tt++) {
+            if (t0 + tt >= tokens) break;
+            float sacc = 0.f;
+#pragma unroll
+            for (int j = 0; j < PL; j++) sacc += v[tt][j];
+            for (int i = lane + 32 * PL; i < parts; i += 32) sacc += epi.ss_in[(size_t)(tok0 + t0 + tt) * parts + i];  // wider models
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sacc += __shfl_xor_sync(0xffffffffu, sacc, o);
+            if (lane == 0) inv_rms[t0 + tt] = 1.0f / sqrtf(sacc / (float)epi.d_in + epi.eps);
+        }
+    }
+}
+
 // GROUPED: one launch over many matrices of one shape (the experts of a routed feed-forward).  Work item =
 // (matrix m, row group g); matrix m sits at W + m * w_stride, multiplies count[m] token rows whose operand tiles
 // start at tile tile_start[m] of `act`, and its outputs are indexed from token tile_start[m] * 8.  A launch covers
@@ -132,13 +161,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, (gemm_ctas_per_sm<QT, NT>()))
                             // the ring is primed: before blocking on it, turn the predecessor's partial sums of
                             // x^2 into 1/rms per token for the epilogue (the consumers pick it up at barrier 2)
                             pdl_wait();
-                            for (int t = 0; t < tokens; t++) {
-                                float sacc = 0.f;
-                                for (int i = lane; i < epi.ss_parts; i += 32) sacc += epi.ss_in[(size_t)(tok0 + t) * epi.ss_parts + i];
-#pragma unroll
-                                for (int o = 16; o > 0; o >>= 1) sacc += __shfl_xor_sync(0xffffffffu, sacc, o);
-                                if (lane == 0) inv_rms[t] = 1.0f / sqrtf(sacc / (float)epi.d_in + epi.eps);
-                            }
+                            token_inv_rms(epi, tokens, tok0, lane, inv_rms);
                             __syncwarp();
                             asm volatile("bar.arrive 2, %0;" ::"n"(GEMM_THREADS) : "memory");
                             inv_done = true;
@@ -165,13 +188,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, (gemm_ctas_per_sm<QT, NT>()))
         }
         if (!inv_done) {
             pdl_wait();
-            for (int t = 0; t < tokens; t++) {
-                float sacc = 0.f;
-                for (int i = lane; i < epi.ss_parts; i += 32) sacc += epi.ss_in[(size_t)(tok0 + t) * epi.ss_parts + i];
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) sacc += __shfl_xor_sync(0xffffffffu, sacc, o);
-                if (lane == 0) inv_rms[t] = 1.0f / sqrtf(sacc / (float)epi.d_in + epi.eps);
-            }
+            token_inv_rms(epi, tokens, tok0, lane, inv_rms);
             __syncwarp();
             asm volatile("bar.arrive 2, %0;" ::"n"(GEMM_THREADS) : "memory");
         }
