@@ -673,17 +673,6 @@ __global__ void __launch_bounds__(ACC_THREADS)
         }
         total = cluster_sum_f64(cluster, &c.xch, 1, block_sum_f64(acc, c.red));
         }
-        if (threadIdx.x == 0) c.best_exp = ~0ull, c.best_idx = 0;
-        __syncthreads();
-        atomicMin(&c.best_exp, best);
-        cluster.sync();
-        unsigned long long gbest = ~0ull;
-        for (int rr = 0; rr < CL; rr++) gbest = min(gbest, cluster.map_shared_rank(&c, rr)->best_exp);
-        if (best == gbest && best != ~0ull) atomicMax(&c.best_idx, best_i);
-        cluster.sync();
-        unsigned int last = 0;
-        for (int rr = 0; rr < CL; rr++) last = max(last, cluster.map_shared_rank(&c, rr)->best_idx);
-        cluster.sync();
         {
             const double scale = FP_ONE / total;
             for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) fp[j] = (unsigned long long)__double2ull_rn(ecache[j] * scale);
@@ -691,7 +680,23 @@ __global__ void __launch_bounds__(ACC_THREADS)
         __syncthreads();
         const unsigned long long tgt = (unsigned long long)(uniforms[(size_t)b * uni_stride] >> 11) << 7;
         token = cluster_radix_draw<LT>(cluster, c, fp, row, sl, tgt, &gap);
-        if (token < 0) token = (int)last, gap = 0;
+        if (token < 0) {
+            // the target lies past the last cumulative sum (rounding of the masses): the reference's walk then returns
+            // the last entry in rank order - the smallest exp, and of those the largest index.  Rare, so the cluster-wide
+            // search runs only here (the same answer in every CTA of the cluster, which all take this branch together).
+            if (threadIdx.x == 0) c.best_exp = ~0ull, c.best_idx = 0;
+            __syncthreads();
+            atomicMin(&c.best_exp, best);
+            cluster.sync();
+            unsigned long long gbest = ~0ull;
+            for (int rr = 0; rr < CL; rr++) gbest = min(gbest, cluster.map_shared_rank(&c, rr)->best_exp);
+            if (best == gbest && best != ~0ull) atomicMax(&c.best_idx, best_i);
+            cluster.sync();
+            unsigned int last = 0;
+            for (int rr = 0; rr < CL; rr++) last = max(last, cluster.map_shared_rank(&c, rr)->best_idx);
+            cluster.sync();
+            token = (int)last, gap = 0;
+        }
     }
     pdl_launch_dependents();
     if (rank == 0 && threadIdx.x == 0) {

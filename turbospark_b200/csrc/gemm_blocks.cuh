@@ -521,6 +521,28 @@ __device__ __forceinline__ Group group_of(int g, int n_tiles, const EpiArgs& e) 
     return r;
 }
 
+// What a group's epilogue will read from global memory, asked for early (an L1 prefetch issued before the
+// reduction barrier, so the loads after it find their lines on chip): the residual-stream element and norm weight
+// of the thread's output element, or its rotation table entries and row descriptor.
+template <int EPI, int NT>
+__device__ __forceinline__ void epilogue_prefetch(const EpiArgs& e, const Group& gr, int64_t rows, int tokens, int tok0) {
+    const int idx = threadIdx.x;
+    if (idx >= NT * 8 * 16) return;
+    const int tok = idx >> 4, col = idx & 15;
+    if (tok >= tokens) return;
+    if constexpr (EPI == EPI_RESID_NORM) {
+        const int gcol = gr.tile0 * TILE_ROWS + col;
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(e.h + (size_t)(tok0 + tok) * rows + gcol));
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(e.g + gcol));
+    } else if constexpr (EPI == EPI_ROPE_STORE) {
+        const int hd = e.head_dim, tph = hd / 16;
+        const int i = (gr.tile0 % tph) * 16 + col;
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(e.cs + (size_t)(tok0 + tok) * hd + i));
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(e.cs + (size_t)(tok0 + tok) * hd + hd / 2 + i));
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(e.row_desc + tok0 + tok));
+    }
+}
+
 // ---- epilogues: 256 consumer threads, results of the group's tiles in tile_out[which][token][row] ---------
 template <int EPI, int NT>
 __device__ __forceinline__ void run_epilogue(const EpiArgs& e, const Group& gr, const float* tile_out, const float* inv_rms,

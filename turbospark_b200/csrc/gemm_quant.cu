@@ -67,6 +67,9 @@ struct GroupedArgs {
     int chunk0 = 0;
     int lo = 0, hi = 0x7fffffff;  // only matrices with lo < count <= hi take part in this launch
     int64_t w_stride = 0;
+#ifdef TSB_GEMM_TRACE
+    unsigned long long* trace = nullptr;  // development builds: eight nanosecond stamps per CTA
+#endif
 };
 
 // Resident CTAs per SM the kernel is compiled for (register cap) and launched with.
@@ -92,13 +95,22 @@ __global__ void __launch_bounds__(GEMM_THREADS, (gemm_ctas_per_sm<QT, NT>()))
     float* inv_rms = reinterpret_cast<float*>(smem + 64);                                  // [NTOK] (<= 64 floats)
     float* red = reinterpret_cast<float*>(smem + 64 + 256);                                // [2][8 warps][NT][4][32]
     float* tile_out0 = red + 2 * CONSUMER_WARPS * NT * 4 * 32;                             // [2 groups in turn][2][NTOK][16]
-    // The plain and the scaling epilogue are elementwise: the thread that sums an output element also stores it, so
-    // those kernels alternate between two reduction buffers and keep one barrier per tile instead of three.
-    constexpr bool ELEMWISE = EPI == EPI_PLAIN || EPI == EPI_SCALE;
+    // Single-tile epilogues work element by element with the thread-to-element mapping of the sum loop (thread idx sums
+    // and finishes element idx), so they alternate between two reduction buffers and keep one barrier per tile; the
+    // paired ones park both tiles' partial sums first and need a second barrier before the buffers are reused.
+    constexpr bool ELEMWISE = EPI == EPI_PLAIN || EPI == EPI_SCALE || EPI == EPI_RESID_NORM;
     uint8_t* stages = reinterpret_cast<uint8_t*>(tile_out0 + 4 * NTOK * 16);
     constexpr bool NEEDS_INV = EPI == EPI_SCALE || EPI == EPI_SILU || EPI == EPI_ROPE_STORE;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef TSB_GEMM_TRACE
+    unsigned long long* trc = grp.trace ? grp.trace + (size_t)blockIdx.x * 8 : nullptr;
+#define GTRC(i) if (trc && threadIdx.x == 0) trc[i] = global_timer_ns()
+    if (trc && threadIdx.x == CONSUMER_WARPS * 32) trc[7] = global_timer_ns();
+#else
+#define GTRC(i)
+#endif
+    GTRC(0);
     const int n_tiles = (int)((rows + TILE_ROWS - 1) / TILE_ROWS);
     const int n_groups = num_groups<EPI>(n_tiles, epi);
     const int iters = (units + STAGE_UNITS - 1) / STAGE_UNITS;  // stages per row tile
@@ -206,6 +218,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, (gemm_ctas_per_sm<QT, NT>()))
         la.xs[nt] = act.xs + (size_t)nt * units * 32 + lane;
     }
     pdl_wait();  // activations come from the previous kernel
+    GTRC(1);
     const ActOperand act0 = act;
 
     bool ok = true, have_inv = !NEEDS_INV;
@@ -248,6 +261,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, (gemm_ctas_per_sm<QT, NT>()))
             for (int it = 0; it < iters; it++, n++) {
                 const uint32_t s = n % NUM_STAGES;
                 if (ok) ok = mbar_wait(&full[s], (n / NUM_STAGES) & 1, err);
+                if (n == 0) { GTRC(2); }
                 const int nun = min(STAGE_UNITS, units - it * STAGE_UNITS);
                 if (ok && warp < nun) {
                     // slack of this stage's source address: the row start's slack plus the stage offset
@@ -267,9 +281,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, (gemm_ctas_per_sm<QT, NT>()))
                 if (lane == 0) mbar_arrive(&empty[s]);
             }
 
-            // ---- fixed-order reduction over the eight consumer warps into tile_out[ti].  Elementwise epilogues take
-            // the two reduction buffers in turn (one barrier per tile); the paired ones park the first tile's partial
-            // sums in buffer 0, the second's in buffer 1, and reduce both behind one pair of barriers.
+            // ---- fixed-order reduction over the eight consumer warps into tile_out[ti].  Single-tile epilogues take the
+            // two reduction buffers in turn (one barrier per tile); the paired ones park the first tile's partial sums
+            // in buffer 0, the second's in buffer 1, and reduce both behind one pair of barriers.
+            if (item == (int)blockIdx.x && ti == 0) { GTRC(3); }
             constexpr int RED_FLOATS = CONSUMER_WARPS * NT * 4 * 32;
             float* redb = red + (ELEMWISE ? (tile_no++ & 1u) : (uint32_t)ti) * RED_FLOATS;
 #pragma unroll
@@ -277,6 +292,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, (gemm_ctas_per_sm<QT, NT>()))
 #pragma unroll
                 for (int i = 0; i < 4; i++) redb[((warp * NT + nt) * 4 + i) * 32 + lane] = acc[nt][i];
             if (!ELEMWISE && ti + 1 < gr.n) continue;  // the pair's second tile first
+            epilogue_prefetch<EPI, NT>(epi, gr, rows, tokens, tok0);
             asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");
             for (int t2 = ELEMWISE ? ti : 0; t2 <= ti; t2++) {
                 const float* rsrc = ELEMWISE ? redb : red + t2 * RED_FLOATS;
@@ -292,17 +308,25 @@ __global__ void __launch_bounds__(GEMM_THREADS, (gemm_ctas_per_sm<QT, NT>()))
                 }
             }
             if constexpr (!ELEMWISE)
-                asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");  // tile_out complete, red reusable
+                asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory");  // red reusable
         }
         if (!have_inv) {
             asm volatile("bar.sync 2, %0;" ::"n"(GEMM_THREADS) : "memory");  // 1/rms per token from the producer warp
             have_inv = true;
         }
-        // (elementwise epilogues: run_epilogue reads tile_out[idx] with the same idx -> thread mapping as the sum loop)
+        // (run_epilogue reads tile_out[idx] with the same idx -> thread mapping as the sum loop: no barrier between)
+        if (item == (int)blockIdx.x) { GTRC(4); }
         if (ok) run_epilogue<EPI, NT>(epi, gr, tile_out, inv_rms, rows, tokens, tok0, err);
+        if (item == (int)blockIdx.x) { GTRC(5); }
     }
+    GTRC(6);
     if (!have_inv) asm volatile("bar.sync 2, %0;" ::"n"(GEMM_THREADS) : "memory");
 }
+
+#ifdef TSB_GEMM_TRACE
+unsigned long long* g_gemm_trace = nullptr;
+size_t g_gemm_trace_cap = 0, g_gemm_trace_used = 0;
+#endif
 
 template <int QT, int NT>
 constexpr size_t gemm_smem_bytes() {
@@ -327,7 +351,13 @@ cudaError_t launch_one(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t 
     const int per_sm = gemm_ctas_per_sm<QT, NT>();
     if (GROUPED) groups *= grp.n_mats;
     dim3 grid((unsigned)min(groups, ctx->sm_count * per_sm));
+#ifdef TSB_GEMM_TRACE
+    GroupedArgs g2 = grp;
+    if (g_gemm_trace && (g_gemm_trace_used + 1) * 2400 <= g_gemm_trace_cap) g2.trace = g_gemm_trace + (g_gemm_trace_used++) * 2400;
+    return tsb_launch(ctx, kern, grid, dim3(GEMM_THREADS), smem, st, true, w, rows, units, act, tokens, tok0, args, ctx->dev_error, g2);
+#else
     return tsb_launch(ctx, kern, grid, dim3(GEMM_THREADS), smem, st, true, w, rows, units, act, tokens, tok0, args, ctx->dev_error, grp);
+#endif
 }
 
 // The matrices are binned by their row count, one launch per bin with the token-tile width that fits it: a matrix
@@ -471,6 +501,11 @@ cudaError_t launch_gemm_quant(tsb_ctx* ctx, cudaStream_t st, int qtype, const ui
 
 // ------------------------------------------------------------------ C ABI
 extern "C" {
+#ifdef TSB_GEMM_TRACE
+__attribute__((visibility("default"))) void tsb_debug_set_gemm_trace(void* p, size_t n_u64) {
+    g_gemm_trace = static_cast<unsigned long long*>(p), g_gemm_trace_cap = n_u64, g_gemm_trace_used = 0;
+}
+#endif
 
 int32_t tsb_gemm_quant(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* region, uint64_t w_off, int64_t rows,
                        int64_t cols, const void* x_f16, void* y, int32_t tokens, int32_t y_f32) {
