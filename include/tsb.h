@@ -113,6 +113,18 @@ TSB_API uint64_t tsb_launch_count(const tsb_ctx* ctx);
 TSB_API int32_t tsb_gemm_quant(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* region, uint64_t w_off,
                                int64_t rows, int64_t cols, const void* x_f16, void* y, int32_t tokens,
                                int32_t y_f32);
+/* tsb_gemm_quant without allocations: the caller owns the operand workspace (tsb_gemm_workspace_bytes, 256-byte
+ * aligned).  tsb_gemm_prepare converts token rows x into the layout the matmul kernel reads (the step
+ * tsb_gemm_quant does on every call); tsb_gemm_quant_prepared is then the matmul alone and may be repeated over many
+ * matrices with the same operand - how the reference reuses one activation buffer across the q, k, v projections
+ * (crates/gpu/src/real_forward_dispatch.rs:900-1054).  With 24 token rows and more of a Q4_K matrix whose rows are a
+ * multiple of 128 the tensor-memory kernel runs instead; it converts inside its own launch sequence, into the same
+ * workspace. */
+TSB_API size_t tsb_gemm_workspace_bytes(int32_t qtype, int64_t rows, int64_t cols, int32_t tokens);
+TSB_API int32_t tsb_gemm_prepare(tsb_ctx* ctx, tsb_stream s, int32_t qtype, int64_t rows, int64_t cols, const void* x_f16, int32_t tokens,
+                                 void* workspace, size_t workspace_bytes);
+TSB_API int32_t tsb_gemm_quant_prepared(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* region, uint64_t w_off, int64_t rows,
+                                        int64_t cols, const void* x_f16, void* workspace, void* y, int32_t tokens, int32_t y_f32);
 /* The reference's per-format names, kept so a binding reads like the original call sites. */
 TSB_API int32_t tsb_gemv_q4k(tsb_ctx* ctx, tsb_stream s, const void* region, uint64_t w_off, int64_t rows,
                              int64_t cols, const void* x_f16, void* y_f16);
@@ -331,8 +343,9 @@ TSB_API int32_t tsb_moe_route(tsb_ctx* ctx, tsb_stream s, const float* router_lo
  * float(weight) * down_e(half(act(gate_e x) * (up_e x)))).  Expert e's gate rows then up rows sit at
  * gate_up_region + gate_up_off + e * (2*ffn rows of d_model columns), its down rows at down_region + down_off +
  * e * (d_model rows of ffn columns), all verbatim blocks of `qtype`.  x, residual and y are [tokens, d_model] f16;
- * ids / weights come from tsb_moe_route.  The call reads the routing result back once (it synchronises the
- * stream) and runs the rows of each active expert through the matmul kernel.  Replaces
+ * ids / weights come from tsb_moe_route.  Nothing comes back to the host: a device kernel sorts the (row, slot) pairs
+ * into per-expert tiles, one grouped launch of the matmul kernel per phase covers every active expert, and an expert
+ * id outside the table sets the context's device error word (reported by tsb_stream_sync).  Replaces
  * moe_phase1_gate_up_act_* and moe_phase2_down_reduce_k8_* (crates/gpu/src/shaders/moe_gguf.metal:561-678). */
 TSB_API int32_t tsb_moe_ffn(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* gate_up_region, uint64_t gate_up_off,
                             const void* down_region, uint64_t down_off, int32_t n_experts, int32_t d_model, int32_t ffn,
@@ -599,6 +612,12 @@ TSB_API int32_t tsb_session_round_times(tsb_session* s, float* out4_ms);
  * them with seeded pseudo-random K/V. */
 TSB_API int32_t tsb_session_fill_context(tsb_session* s, int64_t tokens, uint64_t seed);
 
+/* verify_tree for every stream of the session in ONE target pass: stream b's slots are feed[b * n .. b * n + n), all
+ * streams share the tree shape slot_parent[0..n) (crates/runtime/src/families/qwen/batched_scratch.rs:97-124) and
+ * each starts at its own cursor.  Row b * n + j of the logits belongs to stream b's slot j; logits_out_host may be
+ * NULL to leave them on the device.  Afterwards each stream is in the state tsb_producer_verify_tree leaves it in:
+ * tsb_producer_compact_tree and tsb_producer_rollback_retaining finish the round stream by stream. */
+TSB_API int32_t tsb_session_verify_tree(tsb_session* s, const int32_t* feed, const int32_t* slot_parent, int32_t n, void* logits_out_host);
 /* The CUDA stream (cudaStream_t) the session enqueues on, so a caller can record its own events on it. */
 TSB_API void* tsb_session_stream(tsb_session* s);
 /* Measurement aid: enqueue the target's layer matmuls exactly as a pass of `rows` rows launches them (q|k|v with the

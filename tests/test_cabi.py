@@ -24,7 +24,8 @@ def test_header_declares_the_operator_and_producer_surface():
                    "tsb_producer_tree_nodes", "tsb_producer_draft_block", "tsb_producer_commit_pending",
                    "tsb_producer_discard_pending", "tsb_producer_supports_retaining_rollback",
                    "tsb_producer_supports_headless_prefill", "tsb_best_first_tree", "tsb_tree_accept",
-                   "tsb_tree_slot_parents", "tsb_ctx_set_wait_limit_us"):
+                   "tsb_tree_slot_parents", "tsb_ctx_set_wait_limit_us", "tsb_gemm_workspace_bytes", "tsb_gemm_prepare",
+                   "tsb_gemm_quant_prepared"):
         assert needed in syms, needed
     assert len(syms) >= 60
 

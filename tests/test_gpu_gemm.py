@@ -77,6 +77,30 @@ def test_many_token_rows_take_the_tensor_memory_path_and_match_the_oracle(ctx, o
     assert np.array_equal(y2.download(np.float32, 24 * rows).reshape(24, rows), got[:24])
 
 
+@pytest.mark.parametrize("kind,rows,cols,tokens", [(0, 48, 2048, 6), (2, 100, 1536, 8), (1, 64, 512, 1), (0, 256, 2048, 40), (4, 40, 4096, 17)])
+def test_the_matmul_over_a_caller_workspace_gives_the_one_call_operators_bits(ctx, oracle, kind, rows, cols, tokens):
+    """tsb_gemm_prepare + tsb_gemm_quant_prepared (no allocation, the operand converted once and reused over two
+    matrices) against tsb_gemm_quant; a short workspace and a misaligned one are refused."""
+    import turbospark_b200 as tsb
+    qa, qb = _weights(oracle, kind, rows, cols, 3), _weights(oracle, kind, rows, cols, 4)
+    rng = np.random.default_rng(11)
+    xd = ctx.to_device(oracle.f32_to_f16_bits(rng.standard_normal((tokens, cols)).astype(np.float32)))
+    need = ctx.gemm_workspace_bytes(kind, rows, cols, tokens)
+    assert need > 0 and ctx.gemm_workspace_bytes(kind, rows, cols + 32, tokens) == 0
+    work = ctx.alloc(need)
+    ctx.gemm_prepare(kind, rows, cols, xd, tokens, work)
+    for q in (qa, qb):
+        w = ctx.upload_weights(q)
+        y1, y2 = ctx.alloc(tokens * rows * 4), ctx.alloc(tokens * rows * 4)
+        ctx.gemm_quant(kind, w, rows, cols, xd, y1, tokens, y_f32=True)
+        ctx.gemm_quant_prepared(kind, w, rows, cols, xd, work, y2, tokens, y_f32=True)
+        ctx.sync()
+        assert np.array_equal(y1.download(np.uint32, tokens * rows), y2.download(np.uint32, tokens * rows))
+    short = ctx.alloc(need - 256)
+    with pytest.raises(tsb.TsbError):
+        ctx.gemm_prepare(kind, rows, cols, xd, tokens, short)
+
+
 @pytest.mark.parametrize("kind", [0, 1, 2, 3, 4])
 def test_a_tokens_result_does_not_depend_on_the_batch(ctx, oracle, kind):
     # the verify batch must reproduce the decode step bit for bit, at every width

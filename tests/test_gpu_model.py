@@ -110,6 +110,43 @@ def test_tree_verify_matches_the_oracle_and_compaction_restores_a_chain(rig, ora
     sess.close()
 
 
+@pytest.mark.parametrize("streams", [3, 5])
+def test_a_tree_verify_over_every_stream_in_one_pass_equals_the_per_stream_calls(rig, oracle, streams):
+    """3 streams x 7 slots stay on the few-row matmul path, 5 x 7 = 35 rows take the many-row one; in both the
+    batched pass gives each stream the bits its own verify_tree gives, and the per-stream compaction follows."""
+    tsb = rig["tsb"]
+    parent = [-1, 0, 0, 1, 1, 2, 5]
+    rng = np.random.default_rng(40 + streams)
+    prompts = [rng.integers(0, rig["cfg"].vocab, size=9 + 2 * b).astype(np.int32) for b in range(streams)]  # ragged cursors
+    feed = rng.integers(0, rig["cfg"].vocab, size=(streams, len(parent))).astype(np.int32)
+    sess = tsb.Session(rig["ctx"], rig["target"], None, streams, 8)
+    for b, pr in enumerate(prompts):
+        for i, t in enumerate(pr):
+            sess.produce_prefill(int(t), i, stream=b)
+    single = []
+    for b in range(streams):
+        base = sess.checkpoint(stream=b)
+        single.append(sess.verify_tree(feed[b], parent, base, stream=b).copy())
+        sess.discard_pending(stream=b)
+        assert sess.checkpoint(stream=b) == base
+    batch = sess.verify_tree_streams(feed, parent)
+    for b in range(streams):
+        assert np.array_equal(batch[b], single[b]), b
+    ost = oracle.State(rig["ot"])
+    ost.forward(prompts[1], 0, want_logits=False)
+    _close(oracle, batch[1], ost.forward(feed[1], len(prompts[1]), parent=parent), rel=4e-3, abs_=4e-3)
+    # each stream finishes its round on its own: stream 1 keeps the path 0 -> 2 -> 5 -> 6
+    base = len(prompts[1])
+    sess.compact_tree(base, [0, 2, 5, 6], stream=1)
+    sess.rollback_retaining(base, 4, stream=1)
+    sess.commit_pending(4, stream=1)
+    assert sess.checkpoint(stream=1) == base + 4
+    ost.cursor = base
+    ost.forward([int(feed[1][j]) for j in (0, 2, 5, 6)], base, want_logits=False)
+    _close(oracle, sess.produce(11, base + 4, stream=1), ost.forward([11], base + 4)[0], rel=4e-3, abs_=4e-3)
+    sess.close()
+
+
 def test_rollback_retaining_after_a_tree_verify_needs_the_compaction_first(rig, oracle):
     tsb = rig["tsb"]
     sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 8)

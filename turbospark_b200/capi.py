@@ -70,7 +70,7 @@ def lib():
         L.tsb_launch_count.argtypes = [C.c_void_p]
         L.tsb_uniform_u64.restype = C.c_uint64
         L.tsb_uniform_u64.argtypes = [C.c_int32, C.c_uint64, C.c_uint64]
-        for name in ("tsb_attn_scratch_bytes", "tsb_accept_scratch_bytes", "tsb_accept_history_scratch_bytes"):
+        for name in ("tsb_attn_scratch_bytes", "tsb_accept_scratch_bytes", "tsb_accept_history_scratch_bytes", "tsb_gemm_workspace_bytes"):
             if hasattr(L, name):
                 getattr(L, name).restype = C.c_size_t
         if hasattr(L, "tsb_kv_cursor"):
@@ -175,6 +175,17 @@ class Ctx:
     def gemm_quant(self, qtype, w, rows, cols, x, y, tokens, y_f32=False, w_off=0, stream=None):
         self.check(lib().tsb_gemm_quant(self.h, stream, C.c_int32(qtype), _vp(w), C.c_uint64(w_off), C.c_int64(rows),
                                         C.c_int64(cols), _vp(x), _vp(y), C.c_int32(tokens), C.c_int32(int(y_f32))))
+
+    def gemm_workspace_bytes(self, qtype, rows, cols, tokens):
+        return int(lib().tsb_gemm_workspace_bytes(C.c_int32(qtype), C.c_int64(rows), C.c_int64(cols), C.c_int32(tokens)))
+
+    def gemm_prepare(self, qtype, rows, cols, x, tokens, workspace, stream=None):
+        self.check(lib().tsb_gemm_prepare(self.h, stream, C.c_int32(qtype), C.c_int64(rows), C.c_int64(cols), _vp(x), C.c_int32(tokens),
+                                          _vp(workspace), C.c_size_t(workspace.nbytes)))
+
+    def gemm_quant_prepared(self, qtype, w, rows, cols, x, workspace, y, tokens, y_f32=False, w_off=0, stream=None):
+        self.check(lib().tsb_gemm_quant_prepared(self.h, stream, C.c_int32(qtype), _vp(w), C.c_uint64(w_off), C.c_int64(rows),
+                                                 C.c_int64(cols), _vp(x), _vp(workspace), _vp(y), C.c_int32(tokens), C.c_int32(int(y_f32))))
 
     def dequant_rows(self, qtype, w, cols, row_ids, n_rows, out, w_off=0, stream=None):
         self.check(lib().tsb_dequant_rows(self.h, stream, C.c_int32(qtype), _vp(w), C.c_uint64(w_off), C.c_int64(cols),

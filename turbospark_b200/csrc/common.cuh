@@ -166,6 +166,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// The same with a suspend-time hint (nanoseconds): the thread sleeps in hardware until the phase completes or the
+// hint runs out, instead of coming back after the short default limit and polling again.  A waiting warp then takes
+// no issue slots from the warps it shares a scheduler with.
+__device__ __forceinline__ bool mbar_try_wait_sleep(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ unsigned long long global_timer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -173,12 +189,17 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 }
 // Bounded wait: bounded by time, not by polls.  The limit (microseconds) sits in the word after the error word;
 // when it runs out the wait records why and returns false, so the caller can drain and leave and the context
-// stays usable.  The clock is read only every 64 failed polls, so a wait that succeeds quickly never touches it.
+// stays usable.  A failed poll sleeps up to 20 us in hardware; the clock is read only every 8 failed polls, so a
+// wait that succeeds quickly never touches it.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* err_word) {
+    if (mbar_try_wait(bar, parity)) return true;
     unsigned long long t0 = 0, limit_ns = 0;
     for (uint32_t i = 1;; i++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63u) == 0) {
+#ifndef TSB_WAIT_HINT_NS
+#define TSB_WAIT_HINT_NS 20000
+#endif
+        if (TSB_WAIT_HINT_NS ? mbar_try_wait_sleep(bar, parity, (uint32_t)TSB_WAIT_HINT_NS) : mbar_try_wait(bar, parity)) return true;
+        if ((i & 7u) == 0) {
             const unsigned long long now = global_timer_ns();
             if (t0 == 0) {
                 t0 = now;

@@ -499,6 +499,16 @@ cudaError_t launch_gemm_quant(tsb_ctx* ctx, cudaStream_t st, int qtype, const ui
     return launch_gemm_fused(ctx, st, qtype, w, rows, cols, act, tokens, EPI_PLAIN, a);
 }
 
+// 24 token rows and more of a supported matrix dequantise every weight once per 128-row tile on the tensor-memory path
+static bool gemm_takes_wide(int qtype, int64_t rows, int64_t cols, int tokens) {
+    static int wide_min = -1;
+    if (wide_min < 0) {
+        const char* env = getenv("TSB_WIDE_MIN");
+        wide_min = env ? atoi(env) : 24;
+    }
+    return tokens >= wide_min && gemm_wide_supported(qtype, rows, cols, tokens);
+}
+
 // ------------------------------------------------------------------ C ABI
 extern "C" {
 #ifdef TSB_GEMM_TRACE
@@ -523,18 +533,10 @@ int32_t tsb_gemm_quant(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* re
         TSB_REQUIRE(ctx, ((reinterpret_cast<uintptr_t>(region) + w_off) & 3u) == 0, "MXFP4 rows must start on a 4-byte boundary");
     DeviceGuard g(ctx);
     cudaStream_t st = (cudaStream_t)s;
-    {
-        // many token rows: the tensor-memory path dequantises every weight once per 128-row tile
-        static int wide_min = -1;
-        if (wide_min < 0) {
-            const char* env = getenv("TSB_WIDE_MIN");
-            wide_min = env ? atoi(env) : 24;
-        }
-        if (tokens >= wide_min && gemm_wide_supported(qtype, rows, cols, tokens)) {
-            TSB_CUDA(ctx, launch_gemm_wide_q4k(ctx, st, static_cast<const uint8_t*>(region) + w_off, rows, cols, (const __half*)x_f16, cols,
-                                               tokens, y, rows, y_f32 != 0));
-            return TSB_OK;
-        }
+    if (gemm_takes_wide(qtype, rows, cols, tokens)) {  // many token rows: the tensor-memory path
+        TSB_CUDA(ctx, launch_gemm_wide_q4k(ctx, st, static_cast<const uint8_t*>(region) + w_off, rows, cols, (const __half*)x_f16, cols,
+                                           tokens, y, rows, y_f32 != 0));
+        return TSB_OK;
     }
     const size_t xp_bytes = (act_xp_bytes(tokens, cols) + 255) & ~(size_t)255;
     uint8_t* tmp = nullptr;
@@ -548,6 +550,60 @@ int32_t tsb_gemm_quant(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* re
     cudaError_t e2 = cudaFreeAsync(tmp, st);
     TSB_CUDA(ctx, e);
     TSB_CUDA(ctx, e2);
+    return TSB_OK;
+}
+
+// ---- the same operator with the caller's workspace: no allocation, and the operand conversion on its own
+// the operand copy of the many-row path, 256-byte aligned, then its partial sums (sized for the current device)
+static size_t wide_operand_bytes(int64_t cols) { return (gemm_wide_workspace_bytes(cols) + 255) & ~(size_t)255; }
+
+size_t tsb_gemm_workspace_bytes(int32_t qtype, int64_t rows, int64_t cols, int32_t tokens) {
+    if (tokens <= 0 || cols <= 0 || cols % 256 != 0) return 0;
+    if (gemm_takes_wide(qtype, rows, cols, tokens)) {
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return 0;
+        return wide_operand_bytes(cols) + gemm_wide_partial_bytes_for(sms, rows, cols) + 256;
+    }
+    return ((act_xp_bytes(tokens, cols) + 255) & ~(size_t)255) + act_xs_bytes(tokens, cols) + 256;
+}
+
+int32_t tsb_gemm_prepare(tsb_ctx* ctx, tsb_stream s, int32_t qtype, int64_t rows, int64_t cols, const void* x_f16, int32_t tokens,
+                         void* workspace, size_t workspace_bytes) {
+    if (!ctx) return TSB_ERR_INVALID;
+    TSB_REQUIRE(ctx, x_f16 && workspace, "null buffer");
+    TSB_REQUIRE(ctx, qtype >= TSB_Q4_K && qtype <= TSB_QTYPE_LAST && rows > 0 && cols > 0 && cols % 256 == 0 && tokens > 0, "bad shape or format");
+    TSB_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(x_f16) & 15u) == 0 && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, "x must be 16-byte, the workspace 256-byte aligned");
+    TSB_REQUIRE(ctx, workspace_bytes >= tsb_gemm_workspace_bytes(qtype, rows, cols, tokens), "workspace too small");
+    DeviceGuard g(ctx);
+    if (gemm_takes_wide(qtype, rows, cols, tokens)) return TSB_OK;  // that path converts inside its own launch sequence
+    const size_t xp_bytes = (act_xp_bytes(tokens, cols) + 255) & ~(size_t)255;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    TSB_CUDA(ctx, launch_act_prepare(ctx, (cudaStream_t)s, (const __half*)x_f16, cols, tokens, (int)cols, reinterpret_cast<uint4*>(ws),
+                                     reinterpret_cast<uint4*>(ws + xp_bytes)));
+    return TSB_OK;
+}
+
+int32_t tsb_gemm_quant_prepared(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* region, uint64_t w_off, int64_t rows, int64_t cols,
+                                const void* x_f16, void* workspace, void* y, int32_t tokens, int32_t y_f32) {
+    if (!ctx) return TSB_ERR_INVALID;
+    TSB_REQUIRE(ctx, region && x_f16 && workspace && y, "null buffer");
+    TSB_REQUIRE(ctx, qtype >= TSB_Q4_K && qtype <= TSB_QTYPE_LAST && rows > 0 && cols > 0 && cols % 256 == 0 && tokens > 0, "bad shape or format");
+    if (qtype == TSB_Q4_K || qtype == TSB_Q5_K || qtype == TSB_Q8_0)
+        TSB_REQUIRE(ctx, ((reinterpret_cast<uintptr_t>(region) + w_off) & 15u) == 0, "rows of this format must start on a 16-byte boundary");
+    if (qtype == TSB_MXFP4) TSB_REQUIRE(ctx, ((reinterpret_cast<uintptr_t>(region) + w_off) & 3u) == 0, "MXFP4 rows must start on a 4-byte boundary");
+    DeviceGuard g(ctx);
+    cudaStream_t st = (cudaStream_t)s;
+    const uint8_t* w = static_cast<const uint8_t*>(region) + w_off;
+    if (gemm_takes_wide(qtype, rows, cols, tokens)) {
+        const bool cut = gemm_wide_partial_bytes(ctx, rows, cols) > 0;
+        TSB_CUDA(ctx, launch_gemm_wide_q4k(ctx, st, w, rows, cols, (const __half*)x_f16, cols, tokens, y, rows, y_f32 != 0, workspace,
+                                           cut ? static_cast<uint8_t*>(workspace) + wide_operand_bytes(cols) : nullptr));
+        return TSB_OK;
+    }
+    const size_t xp_bytes = (act_xp_bytes(tokens, cols) + 255) & ~(size_t)255;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    TSB_CUDA(ctx, launch_gemm_quant(ctx, st, qtype, w, rows, cols, ActOperand{reinterpret_cast<uint4*>(ws), reinterpret_cast<uint4*>(ws + xp_bytes)}, y,
+                                    rows, tokens, y_f32 != 0));
     return TSB_OK;
 }
 

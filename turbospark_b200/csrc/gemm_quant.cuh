@@ -124,6 +124,7 @@ bool gemm_wide_supported(int qtype, int64_t rows, int64_t cols, int tokens);
 // workspace: gemm_wide_workspace_bytes(cols) bytes the call may use for its operand copy (null: stream-ordered allocation)
 // partials: gemm_wide_partial_bytes(...) bytes for the split sums of matrices with few row tiles (0: none needed)
 size_t gemm_wide_workspace_bytes(int64_t cols);
+size_t gemm_wide_partial_bytes_for(int sm_count, int64_t rows, int64_t cols);  // the same for a device with that many SMs
 size_t gemm_wide_partial_bytes(const tsb_ctx* ctx, int64_t rows, int64_t cols);
 cudaError_t launch_gemm_wide_q4k(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t rows, int64_t cols, const __half* x,
                                  int64_t x_stride, int tokens, void* y, int64_t y_stride, bool y_f32, void* workspace = nullptr,

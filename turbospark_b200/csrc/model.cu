@@ -1021,6 +1021,34 @@ int32_t tsb_producer_verify_tree(tsb_session* s, int32_t stream, const int32_t* 
     return forward_stream(s, s->target, stream, feed, n, slot_parent, s->logits_target, logits_out_host);
 }
 
+int32_t tsb_session_verify_tree(tsb_session* s, const int32_t* feed, const int32_t* slot_parent, int32_t n, void* logits_out_host) {
+    if (!s) return TSB_ERR_INVALID;
+    tsb_ctx* ctx = s->ctx;
+    TSB_REQUIRE(ctx, feed && slot_parent && n > 0 && n <= s->max_rows, "verify_tree takes 1..%d rows per stream", s->max_rows);
+    DeviceGuard g(ctx);
+    const int S = s->n_streams;
+    std::vector<int32_t> streams(S);
+    for (int b = 0; b < S; b++) streams[b] = b;
+    const tsb_row_desc* rd;
+    const int32_t* td;
+    int max_len;
+    int32_t rc = stage_rows(s, s->target, streams.data(), S, n, slot_parent, feed, &rd, &td, &max_len);
+    if (rc) return rc;
+    const int vocab = s->target.model->cfg.vocab;
+    TSB_CUDA(ctx, forward_device(s, s->target, td, 1, rd, S * n, n, max_len, s->logits_target, vocab));
+    for (int b = 0; b < S; b++) {
+        const int64_t base = tsb_kv_cursor(s->target.kv, b);
+        PendingVerify& pv = s->target.pending[b];
+        pv.active = true, pv.tree = true, pv.base = base, pv.rows = n, pv.feed.assign(feed + (size_t)b * n, feed + (size_t)(b + 1) * n), pv.drafter_rows = 0;
+        tsb_kv_set_cursor(s->target.kv, b, base + n);
+    }
+    if (logits_out_host) {
+        TSB_CUDA(ctx, cudaMemcpyAsync(logits_out_host, s->logits_target, (size_t)S * n * vocab * 2, cudaMemcpyDeviceToHost, s->stream));
+        return tsb_stream_sync(ctx, s->stream);
+    }
+    return TSB_OK;
+}
+
 int32_t tsb_producer_compact_tree(tsb_session* s, int32_t stream, int64_t base, const uint32_t* path, int32_t keep) {
     if (!s) return TSB_ERR_INVALID;
     tsb_ctx* ctx = s->ctx;

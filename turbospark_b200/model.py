@@ -171,6 +171,16 @@ class Session:
                                                       out.ctypes.data_as(C.c_void_p)))
         return out
 
+    def verify_tree_streams(self, feed, slot_parent, want_logits=True):
+        """verify_tree of every stream in one target pass: feed is [n_streams, n] slot tokens over one shared tree."""
+        feed = np.ascontiguousarray(feed, dtype=np.int32)
+        par = np.ascontiguousarray(slot_parent, dtype=np.int32)
+        assert feed.ndim == 2 and feed.shape[1] == par.size
+        out = self._logits(feed.size) if want_logits else None
+        self.ctx.check(lib().tsb_session_verify_tree(self.h, feed.ctypes.data_as(C.c_void_p), par.ctypes.data_as(C.c_void_p),
+                                                     C.c_int32(par.size), out.ctypes.data_as(C.c_void_p) if want_logits else None))
+        return out.reshape(feed.shape[0], par.size, -1) if want_logits else None
+
     def compact_tree(self, base, path, stream=0):
         p = np.ascontiguousarray(path, dtype=np.uint32)
         self.ctx.check(lib().tsb_producer_compact_tree(self.h, C.c_int32(stream), C.c_int64(base),

@@ -8,6 +8,8 @@
 
 Each line reports the launch time (CUDA events around `--iters` back-to-back launches that rotate over weight
 copies larger than the L2 cache, minimum of five repeats after warm-up) and the algorithmic bytes over that time.
+The matmul is timed through tsb_gemm_quant_prepared (operand converted once, as a model pass does once per three or
+four matrices); --whole-call times the one-call operator, which allocates and converts on every call.
 Weights are random valid blocks (finite scales, random quants); values do not matter for timing.
 """
 import argparse
@@ -65,7 +67,7 @@ def time_launches(fn, iters, repeats=5, warm=3):
     return best
 
 
-def bench_gemm(ctx, qtype, rows, cols, tokens, iters, rng, repeats=5, warm=3):
+def bench_gemm(ctx, qtype, rows, cols, tokens, iters, rng, repeats=5, warm=3, whole_call=False):
     kind, blk, nbytes = QTYPES[qtype]
     w_bytes = rows * (cols // blk) * nbytes
     copies = max(2, -(-2 * L2_BYTES // w_bytes))  # rotate over more than an L2's worth of distinct weights
@@ -73,12 +75,19 @@ def bench_gemm(ctx, qtype, rows, cols, tokens, iters, rng, repeats=5, warm=3):
     ws = [ctx.upload_weights(host) for _ in range(copies)]
     x = ctx.to_device(f16_bits(rng.standard_normal((tokens, cols))))
     y = ctx.alloc(tokens * rows * 2)
-    ms = time_launches(lambda i: ctx.gemm_quant(kind, ws[i % copies], rows, cols, x, y, tokens), iters, repeats, warm)
+    if whole_call:  # the one-call operator: stream-ordered allocation + operand conversion + matmul every time
+        ms = time_launches(lambda i: ctx.gemm_quant(kind, ws[i % copies], rows, cols, x, y, tokens), iters, repeats, warm)
+    else:  # the operand converted once into the caller's workspace, the matmul launch alone timed
+        work = ctx.alloc(ctx.gemm_workspace_bytes(kind, rows, cols, tokens))
+        ctx.gemm_prepare(kind, rows, cols, x, tokens, work)
+        ms = time_launches(lambda i: ctx.gemm_quant_prepared(kind, ws[i % copies], rows, cols, x, work, y, tokens), iters, repeats, warm)
+        work.free()
     algo = w_bytes + tokens * cols * 2 + tokens * rows * 2
     for w in ws:
         w.free()
     return {"op": "gemm", "qtype": qtype, "rows": rows, "cols": cols, "tokens": tokens, "us": round(ms * 1e3, 2),
-            "bytes": algo, "gbs": round(algo / ms / 1e6, 1), "weight_copies": copies}
+            "bytes": algo, "gbs": round(algo / ms / 1e6, 1), "weight_copies": copies,
+            "timed": "tsb_gemm_quant" if whole_call else "tsb_gemm_quant_prepared"}
 
 
 def bench_attention(ctx, hd, nq, nkv, context, tokens, streams, iters, repeats=5, warm=3):
@@ -149,6 +158,7 @@ def main():
     ap.add_argument("--repeats", type=int, default=5)
     ap.add_argument("--warm", type=int, default=3)
     ap.add_argument("--sweep", action="store_true")
+    ap.add_argument("--whole-call", action="store_true", help="time tsb_gemm_quant (allocation + conversion + matmul) instead of the prepared matmul")
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--q-heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
@@ -164,7 +174,7 @@ def main():
         cases = [(q, r, c, t) for q in ("q4k", "mxfp4") for (r, c) in SWEEP_SHAPES for t in SWEEP_TOKENS] if a.sweep \
             else [(a.qtype, a.rows, a.cols, a.tokens)]
         for q, r, c, t in cases:
-            print(json.dumps(bench_gemm(ctx, q, r, c, t, a.iters, rng, a.repeats, a.warm)), flush=True)
+            print(json.dumps(bench_gemm(ctx, q, r, c, t, a.iters, rng, a.repeats, a.warm, a.whole_call)), flush=True)
     elif a.op == "attention":
         print(json.dumps(bench_attention(ctx, a.head_dim, a.q_heads, a.kv_heads, a.context, a.tokens, a.streams, a.iters,
                                          a.repeats, a.warm)), flush=True)
