@@ -54,7 +54,7 @@ __device__ __forceinline__ uint32_t tile_off(int r, int c) {
     return (uint32_t)(r * (HD * 2) + ((c ^ (r & 7)) << 4));
 }
 
-// MT = query m-tiles per CTA (1 -> 16 queries, 4 warps; 2 -> 32 queries, 8 warps).  Whatever MT is, a warp owns one
+// MT = query m-tiles per CTA (1 -> 16 queries, 4 warps; 2 -> 32 queries, 8 warps; 4 -> 64 queries, 16 warps).  Whatever MT is, a warp owns one
 // m-tile and one 16-token slice of every 64-token tile, so the arithmetic done for a query - the order of its
 // running maxima, sums and merges - does not depend on how many other rows are in flight: a row verified in a
 // batch of six comes out bit-identical to the same row decoded alone.
@@ -554,6 +554,13 @@ __global__ void __launch_bounds__(MERGE_THREADS)
 
 }  // namespace
 
+// Dynamic shared memory of a CTA: the K/V ring, or - four m-tiles - the larger area the warps' partials are merged in.
+static size_t attn_smem_bytes(int hd, int mt) {
+    const size_t ring = (size_t)NST * 2 * TILE_TOKENS * hd * sizeof(__half);
+    const size_t merge = ((size_t)4 * mt * 16 * (hd + 4) + 2 * 4 * mt * 16 + (size_t)16 * mt * hd + 2 * 16 * mt) * sizeof(float);
+    return ring > merge ? ring : merge;
+}
+
 // How many clusters of `cs` CTAs of the kernel can be resident at once (cached per shape and device).
 template <int HD, int MT>
 static int max_clusters_t(int device, int cs) {
@@ -561,7 +568,7 @@ static int max_clusters_t(int device, int cs) {
     const int slot = cs == 16 ? 4 : cs == 8 ? 3 : cs == 4 ? 2 : cs == 2 ? 1 : 0;
     if (device < 0 || device >= ATTN_MAX_DEVICES) return 0;
     if (cache[device][slot]) return cache[device][slot] > 0 ? cache[device][slot] : 0;
-    const size_t smem = (size_t)NST * 2 * TILE_TOKENS * HD * sizeof(__half);
+    const size_t smem = attn_smem_bytes(HD, MT);
     if (cudaFuncSetAttribute(attn_partial_kernel<HD, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
     // clusters of sixteen are beyond the portable size: allowed on this part, the occupancy query says whether they fit
     if (cudaFuncSetAttribute(attn_partial_kernel<HD, MT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
@@ -591,8 +598,8 @@ static int max_clusters_t(int device, int cs) {
     return cache[device][slot] > 0 ? cache[device][slot] : 0;
 }
 static int max_clusters(int device, int hd, int mt, int cs) {
-    if (hd == 128) return mt == 2 ? max_clusters_t<128, 2>(device, cs) : max_clusters_t<128, 1>(device, cs);
-    return mt == 2 ? max_clusters_t<64, 2>(device, cs) : max_clusters_t<64, 1>(device, cs);
+    if (hd == 128) return mt == 4 ? max_clusters_t<128, 4>(device, cs) : mt == 2 ? max_clusters_t<128, 2>(device, cs) : max_clusters_t<128, 1>(device, cs);
+    return mt == 4 ? max_clusters_t<64, 4>(device, cs) : mt == 2 ? max_clusters_t<64, 2>(device, cs) : max_clusters_t<64, 1>(device, cs);
 }
 
 AttnPlan attn_plan(const tsb_ctx* ctx, const tsb_kv* kv, int rows, int rows_per_seq, int n_q_heads, int max_len) {
@@ -725,7 +732,9 @@ static AttnPlan attn_plan_partials(const tsb_ctx* ctx, const tsb_kv* kv, int row
     AttnPlan p;
     const int G = n_q_heads / kv->view.kv_heads;
     const int n_queries = rows_per_seq * G;
-    p.mt = n_queries <= 16 ? 1 : 2;
+    // every query tile of a (stream, kv head) streams that head's K and V again, so many queries (a tree's rows x the
+    // group's heads) go 64 to a CTA
+    p.mt = n_queries <= 16 ? 1 : n_queries <= 64 ? 2 : 4;
     p.n_qtiles = (n_queries + 16 * p.mt - 1) / (16 * p.mt);
     p.groups = rows / rows_per_seq;
     p.cluster_size = 1;
@@ -736,7 +745,16 @@ static AttnPlan attn_plan_partials(const tsb_ctx* ctx, const tsb_kv* kv, int row
     if (resident > ctx->sm_count * 2) resident = ctx->sm_count * 2;
     if (resident < 1) resident = ctx->sm_count;
     int splits = resident / (base_ctas > 0 ? base_ctas : 1);
-    if (splits < 1) splits = 1;
+    if (splits < 1) {
+        // more CTAs than the device holds: cut the context so that the waves come out even (a CTA costs its tiles
+        // plus about four tiles' time of fixed work)
+        float best = 1e30f;
+        for (int s = 1; s <= 8 && s <= tiles_total; s++) {
+            const int waves = (base_ctas * s + resident - 1) / resident;
+            const float cost = (float)waves * ((float)((tiles_total + s - 1) / s) + 4.f);
+            if (cost < best - 1e-3f) best = cost, splits = s;
+        }
+    }
     if (splits > MAX_SPLITS) splits = MAX_SPLITS;
     if (splits > tiles_total) splits = tiles_total;
     const int tiles_per = (tiles_total + splits - 1) / splits;
@@ -762,15 +780,21 @@ cudaError_t launch_attn_partials(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, int 
     *part_o_out = part_o, *part_ml_out = part_ml, *n_splits_out = p.n_splits;
     const float scale_log2e = scale * 1.4426950408889634f;
     dim3 grid((unsigned)p.n_splits, (unsigned)(kv->view.kv_heads * p.n_qtiles), (unsigned)p.groups);
-    const size_t smem = (size_t)NST * 2 * TILE_TOKENS * hd * sizeof(__half);
+    const size_t smem = attn_smem_bytes(hd, p.mt);
     const ActOut none{nullptr, nullptr};
     if (hd == 128) {
+        if (p.mt == 4)
+            return launch_attn_t<128, 4>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
+                                         scale_log2e, part_o, part_ml, ATTN_TICKETS, nullptr, none, 1);
         if (p.mt == 2)
             return launch_attn_t<128, 2>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
                                          scale_log2e, part_o, part_ml, ATTN_TICKETS, nullptr, none, 1);
         return launch_attn_t<128, 1>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
                                      scale_log2e, part_o, part_ml, ATTN_TICKETS, nullptr, none, 1);
     }
+    if (p.mt == 4)
+        return launch_attn_t<64, 4>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
+                                    scale_log2e, part_o, part_ml, ATTN_TICKETS, nullptr, none, 1);
     if (p.mt == 2)
         return launch_attn_t<64, 2>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
                                     scale_log2e, part_o, part_ml, ATTN_TICKETS, nullptr, none, 1);

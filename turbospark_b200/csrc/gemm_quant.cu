@@ -555,14 +555,14 @@ int32_t tsb_gemm_quant(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const void* re
 
 // ---- the same operator with the caller's workspace: no allocation, and the operand conversion on its own
 // the operand copy of the many-row path, 256-byte aligned, then its partial sums (sized for the current device)
-static size_t wide_operand_bytes(int64_t cols) { return (gemm_wide_workspace_bytes(cols) + 255) & ~(size_t)255; }
+static size_t wide_operand_bytes(int64_t cols, int tokens) { return (gemm_wide_workspace_bytes(cols, tokens) + 255) & ~(size_t)255; }
 
 size_t tsb_gemm_workspace_bytes(int32_t qtype, int64_t rows, int64_t cols, int32_t tokens) {
     if (tokens <= 0 || cols <= 0 || cols % 256 != 0) return 0;
     if (gemm_takes_wide(qtype, rows, cols, tokens)) {
         int dev = 0, sms = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return 0;
-        return wide_operand_bytes(cols) + gemm_wide_partial_bytes_for(sms, rows, cols) + 256;
+        return wide_operand_bytes(cols, tokens) + gemm_wide_partial_bytes_for(sms, rows, cols) + 256;
     }
     return ((act_xp_bytes(tokens, cols) + 255) & ~(size_t)255) + act_xs_bytes(tokens, cols) + 256;
 }
@@ -575,7 +575,12 @@ int32_t tsb_gemm_prepare(tsb_ctx* ctx, tsb_stream s, int32_t qtype, int64_t rows
     TSB_REQUIRE(ctx, (reinterpret_cast<uintptr_t>(x_f16) & 15u) == 0 && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, "x must be 16-byte, the workspace 256-byte aligned");
     TSB_REQUIRE(ctx, workspace_bytes >= tsb_gemm_workspace_bytes(qtype, rows, cols, tokens), "workspace too small");
     DeviceGuard g(ctx);
-    if (gemm_takes_wide(qtype, rows, cols, tokens)) return TSB_OK;  // that path converts inside its own launch sequence
+    if (gemm_takes_wide(qtype, rows, cols, tokens)) {
+        // that path converts inside its own launch sequence; the ticket words of its partial sums start at zero
+        if (gemm_wide_partial_bytes(ctx, rows, cols) > 0)
+            TSB_CUDA(ctx, cudaMemsetAsync(static_cast<uint8_t*>(workspace) + wide_operand_bytes(cols, tokens), 0, 4096, (cudaStream_t)s));
+        return TSB_OK;
+    }
     const size_t xp_bytes = (act_xp_bytes(tokens, cols) + 255) & ~(size_t)255;
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     TSB_CUDA(ctx, launch_act_prepare(ctx, (cudaStream_t)s, (const __half*)x_f16, cols, tokens, (int)cols, reinterpret_cast<uint4*>(ws),
@@ -597,7 +602,7 @@ int32_t tsb_gemm_quant_prepared(tsb_ctx* ctx, tsb_stream s, int32_t qtype, const
     if (gemm_takes_wide(qtype, rows, cols, tokens)) {
         const bool cut = gemm_wide_partial_bytes(ctx, rows, cols) > 0;
         TSB_CUDA(ctx, launch_gemm_wide_q4k(ctx, st, w, rows, cols, (const __half*)x_f16, cols, tokens, y, rows, y_f32 != 0, workspace,
-                                           cut ? static_cast<uint8_t*>(workspace) + wide_operand_bytes(cols) : nullptr));
+                                           cut ? static_cast<uint8_t*>(workspace) + wide_operand_bytes(cols, tokens) : nullptr));
         return TSB_OK;
     }
     const size_t xp_bytes = (act_xp_bytes(tokens, cols) + 255) & ~(size_t)255;

@@ -121,9 +121,10 @@ cudaError_t launch_f32_to_f16(tsb_ctx* ctx, cudaStream_t st, const float* x, __h
 
 // The tensor-memory (tcgen05) path for many token rows: Q4_K, rows a multiple of 128.  x is natural f16.
 bool gemm_wide_supported(int qtype, int64_t rows, int64_t cols, int tokens);
-// workspace: gemm_wide_workspace_bytes(cols) bytes the call may use for its operand copy (null: stream-ordered allocation)
-// partials: gemm_wide_partial_bytes(...) bytes for the split sums of matrices with few row tiles (0: none needed)
-size_t gemm_wide_workspace_bytes(int64_t cols);
+// workspace: gemm_wide_workspace_bytes(cols, tokens) bytes the call may use for its operand copy (null: stream-ordered allocation)
+// partials: gemm_wide_partial_bytes(...) bytes for the sums of tiles cut into runs (0: none needed).  Its first 4096
+// bytes are ticket words: zero before the first call; every call leaves them zero again
+size_t gemm_wide_workspace_bytes(int64_t cols, int tokens);
 size_t gemm_wide_partial_bytes_for(int sm_count, int64_t rows, int64_t cols);  // the same for a device with that many SMs
 size_t gemm_wide_partial_bytes(const tsb_ctx* ctx, int64_t rows, int64_t cols);
 cudaError_t launch_gemm_wide_q4k(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t rows, int64_t cols, const __half* x,

@@ -141,41 +141,50 @@ struct WideBars {
     uint64_t mma_done[2];  // block nb's MMAs have finished: its A slot is free and its accumulators are complete
     uint32_t tmem_base;
     uint32_t failed;
+    uint32_t ticket;
 };
 
-// x natural [tokens, cols] f16 -> per 256-column block, 34 chunks x n_pad tokens x 16 bytes (see the file header)
-__global__ void wide_prepare_kernel(const __half* __restrict__ x, int64_t x_stride, int tokens, int n_pad, int units,
-                                    uint4* __restrict__ xw) {
+// x natural [tokens, cols] f16 -> for every pass of `per_pass` token rows and every 256-column block, 34 chunks x n_pad
+// tokens x 16 bytes (see the file header); pass p starts at p * units * 34 * per_pass chunks and its own n_pad is its
+// token count rounded up to 16.  A CTA takes eight tokens of one block: warp = token, lane = 16-byte chunk; the
+// 32-column sums come from two shuffles over the four lanes of a sub-block; the CTA's 34 x 8 chunks go out through
+// shared memory as 128-byte runs.
+__global__ void __launch_bounds__(256) wide_prepare_kernel(const __half* __restrict__ x, int64_t x_stride, int tokens, int per_pass, int units,
+                                                           uint4* __restrict__ xw) {
+    __shared__ uint4 tile[WIDE_CHUNKS][8];
     pdl_wait();
-    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const int64_t total = (int64_t)units * WIDE_CHUNKS * n_pad;
-    if (idx >= total) return;
-    const int n = (int)(idx % n_pad);
-    const int c = (int)((idx / n_pad) % WIDE_CHUNKS);
-    const int blk = (int)(idx / ((int64_t)n_pad * WIDE_CHUNKS));
+    const int blk = blockIdx.x;
+    const int pass = blockIdx.y / (per_pass >> 3), grp = blockIdx.y % (per_pass >> 3);
+    const int nt = min(per_pass, tokens - pass * per_pass);  // token rows of this pass
+    const int n_pad = (nt + 15) / 16 * 16;
+    if (nt <= 0 || grp * 8 >= n_pad) return;
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = grp * 8 + w;  // token row within the pass
     uint4 o = make_uint4(0, 0, 0, 0);
-    if (n < tokens) {
-        const __half* row = x + (size_t)n * x_stride + (size_t)blk * 256;
-        if (c < 32) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(row + 8 * c);
-            __half h[8];
-            *reinterpret_cast<uint4*>(h) = raw;
-            o = act_pack8(h);
-        } else {
-            __half out[8];
+    float sum = 0.f;
+    if (n < nt) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)(pass * per_pass + n) * x_stride + (size_t)blk * 256 + 8 * lane);
+        __half h[8];
+        *reinterpret_cast<uint4*>(h) = raw;
 #pragma unroll
-            for (int s = 0; s < 4; s++) {
-                const __half* p = row + ((c - 32) * 4 + s) * 32;
-                float sum = 0.f;
-                for (int i = 0; i < 32; i++) sum += __half2float(p[i]);
-                const __half hi = __float2half_rn(sum);
-                out[2 * s] = hi;
-                out[2 * s + 1] = __float2half_rn(sum - __half2float(hi));
-            }
-            o = *reinterpret_cast<uint4*>(out);
-        }
+        for (int i = 0; i < 8; i++) sum += __half2float(h[i]);
+        o = act_pack8(h);
     }
-    xw[idx] = o;
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    tile[lane][w] = o;
+    if ((lane & 3) == 0) {  // sub-block lane / 4: (hi, lo) halves at chunk 32 + sub / 4, pair sub % 4
+        const int sub = lane >> 2;
+        const __half hi = __float2half_rn(sum);
+        const __half2 hl = __halves2half2(hi, __float2half_rn(sum - __half2float(hi)));
+        reinterpret_cast<__half2*>(&tile[32 + (sub >> 2)][w])[sub & 3] = hl;
+    }
+    __syncthreads();
+    uint4* dst = xw + (size_t)pass * units * WIDE_CHUNKS * per_pass + (size_t)blk * WIDE_CHUNKS * n_pad;
+    for (int i = threadIdx.x; i < WIDE_CHUNKS * 8; i += 256) {
+        const int c = i >> 3, t = i & 7;
+        dst[(size_t)c * n_pad + grp * 8 + t] = tile[c][t];
+    }
 }
 
 // One box of the weight matrix (128 rows x one 144-byte block) lands as 128 consecutive 144-byte rows: a lane stride
@@ -208,7 +217,8 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1)
 #endif
     // Work items, dealt round-robin to the CTAs: the first n_whole tiles (a multiple of the grid) go whole; each of the
     // remaining tiles - fewer than CTAs - is cut into `ksplit` runs of its blocks so that the last wave fills the
-    // device too.  The runs' partial sums go to `part` and a small kernel adds them in run order.
+    // device too.  A run leaves its partial sums in `part` (after 1024 ticket words); the CTA that finishes a tile's last
+    // run adds them in run order and writes the tile.
     const int n_tiles = (int)(rows / WM);
     const int n_items = n_whole + (n_tiles - n_whole) * ksplit;
     const int upk = (units + ksplit - 1) / ksplit;  // blocks per run
@@ -449,20 +459,66 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1)
             // the item's last block(s)
             if (lag == 2 && nblk >= 2) drain(nb - 2, d_p2, dmin_p2, acc);
             if (nblk >= 1) drain(nb - 1, d_p1, dmin_p1, acc);
-            if (ok) {
-                const int64_t orow = (int64_t)tile * WM + row;
+            const int64_t orow = (int64_t)tile * WM + row;
+            if (ks < 0) {
+                if (ok) {
+#pragma unroll
+                    for (int i = 0; i < 16 * ROUNDS; i++) {
+                        const int n = g * cpw + i;
+                        if (i < cpw && n < tokens) {
+                            if (y_f32)
+                                reinterpret_cast<float*>(y)[(size_t)n * y_stride + orow] = acc[i];
+                            else
+                                reinterpret_cast<__half*>(y)[(size_t)n * y_stride + orow] = __float2half_rn(acc[i]);
+                        }
+                    }
+                }
+            } else {
+                // a run of a cut tile: leave the partial sums, take a ticket; whoever holds the last one adds the runs in
+                // run order (so the result does not depend on who that is) and puts the counter back to zero
+                uint32_t* tickets = reinterpret_cast<uint32_t*>(part);
+                float* pdata = part + 1024;
+                const int64_t trow = orow - (int64_t)n_whole * WM;
 #pragma unroll
                 for (int i = 0; i < 16 * ROUNDS; i++) {
                     const int n = g * cpw + i;
-                    if (i < cpw && n < tokens) {
-                        if (ks >= 0)
-                            part[((size_t)ks * tokens + n) * tail_rows + (orow - (int64_t)n_whole * WM)] = acc[i];
-                        else if (y_f32)
-                            reinterpret_cast<float*>(y)[(size_t)n * y_stride + orow] = acc[i];
-                        else
-                            reinterpret_cast<__half*>(y)[(size_t)n * y_stride + orow] = __float2half_rn(acc[i]);
+                    if (i < cpw && n < tokens) pdata[((size_t)ks * tokens + n) * tail_rows + trow] = ok ? acc[i] : 0.f;
+                }
+                __threadfence();
+                asm volatile("bar.sync 1, %0;" ::"n"(WIDE_DEQ_WARPS * 32) : "memory");
+                if (threadIdx.x == 0) {
+                    const uint32_t t = atomicAdd(&tickets[tile - n_whole], 1u);
+                    if (t == (uint32_t)ksplit - 1) tickets[tile - n_whole] = 0;
+                    bars->ticket = t;
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(WIDE_DEQ_WARPS * 32) : "memory");
+                if (bars->ticket == (uint32_t)ksplit - 1) {
+                    __threadfence();
+                    // run by run, every column of the run loaded before the adds: the loads of a run are in flight together
+#pragma unroll
+                    for (int i = 0; i < 16 * ROUNDS; i++) acc[i] = 0.f;
+                    for (int k = 0; k < ksplit; k++) {
+                        float v[16 * ROUNDS];
+#pragma unroll
+                        for (int i = 0; i < 16 * ROUNDS; i++) {
+                            const int n = g * cpw + i;
+                            v[i] = (i < cpw && n < tokens) ? __ldcg(&pdata[((size_t)k * tokens + n) * tail_rows + trow]) : 0.f;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 16 * ROUNDS; i++) acc[i] += v[i];
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16 * ROUNDS; i++) {
+                        const int n = g * cpw + i;
+                        if (i < cpw && n < tokens) {
+                            if (y_f32)
+                                reinterpret_cast<float*>(y)[(size_t)n * y_stride + orow] = acc[i];
+                            else
+                                reinterpret_cast<__half*>(y)[(size_t)n * y_stride + orow] = __float2half_rn(acc[i]);
+                        }
                     }
                 }
+                asm volatile("bar.sync 1, %0;" ::"n"(WIDE_DEQ_WARPS * 32) : "memory");  // the ticket word is reused by the next cut tile
             }
         }
         if (!ok && lane == 0) bars->failed = 1;
@@ -476,22 +532,6 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1)
     }
 }
 
-// y[n, row0 + r] = sum over runs, in run order, of part[run][n][r] for the tail_rows rows whose tiles were cut into runs
-__global__ void wide_reduce_kernel(const float* __restrict__ part, int ksplit, int tokens, int64_t tail_rows, int64_t row0, void* __restrict__ y,
-                                   int64_t y_stride, int y_f32) {
-    pdl_wait();
-    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (int64_t)tokens * tail_rows) return;
-    const int n = (int)(idx / tail_rows);
-    const int64_t r = idx % tail_rows;
-    float v = 0.f;
-    for (int k = 0; k < ksplit; k++) v += part[((size_t)k * tokens + n) * tail_rows + r];
-    if (y_f32)
-        reinterpret_cast<float*>(y)[(size_t)n * y_stride + row0 + r] = v;
-    else
-        reinterpret_cast<__half*>(y)[(size_t)n * y_stride + row0 + r] = __float2half_rn(v);
-}
-
 }  // namespace
 
 bool gemm_wide_supported(int qtype, int64_t rows, int64_t cols, int tokens) {
@@ -499,13 +539,17 @@ bool gemm_wide_supported(int qtype, int64_t rows, int64_t cols, int tokens) {
 }
 
 // How a matrix's 128-row tiles are dealt to the CTAs: whole tiles while they fill complete waves, the rest cut into
-// `ksplit` runs of blocks.  ksplit minimises the longest CTA's block count; a quarter block per run stands for the
-// cost of writing and adding the partial sums.
+// `ksplit` runs of blocks.  ksplit minimises the longest CTA's time in units of one block (18 KB of weights): a run
+// of a cut tile also writes its 128 x n_pad partial sums and the tile's last run reads them all back, which at 128
+// token rows costs as much as seven blocks, plus one block's worth of fixed work.  The plan must not depend on the
+// token count - the order in which a row's sums are added, and so its bits, would change with its batch mates - so
+// the cost is taken at 96 token rows whatever the pass carries.
 struct WidePlan {
     int n_whole, ksplit;
     int64_t tail_rows;
 };
 static WidePlan wide_plan(int sm_count, int64_t rows, int units) {
+    constexpr int n_pad = 96;
     const int tiles = (int)(rows / WM), grid = sm_count;
     WidePlan p;
     p.n_whole = tiles / grid * grid;
@@ -513,22 +557,29 @@ static WidePlan wide_plan(int sm_count, int64_t rows, int units) {
     p.ksplit = 1;
     p.tail_rows = (int64_t)tail * WM;
     if (tail == 0) return p;
-    float best = 1e30f;
-    for (int k = 1; k <= units && k <= 16; k++) {
+    const float per_run = 1.f + (float)n_pad / 18.f;
+    float best = (float)((tail + grid - 1) / grid) * (float)units;
+    for (int k = 2; k <= units && k <= 16; k++) {
         const int upk = (units + k - 1) / k;
-        const float load = (float)((tail * k + grid - 1) / grid) * (float)upk + 0.25f * (float)(k - 1);
+        const float load = (float)((tail * k + grid - 1) / grid) * ((float)upk + per_run);
         if (load < best - 1e-3f) best = load, p.ksplit = k;
     }
+    if (const char* env = getenv("TSB_WIDE_KSPLIT")) p.ksplit = std::max(1, std::min(units, atoi(env)));  // experiments
+    const int upk = (units + p.ksplit - 1) / p.ksplit;
+    p.ksplit = (units + upk - 1) / upk;  // no empty runs: every run of a tile takes a ticket
     return p;
 }
-size_t gemm_wide_workspace_bytes(int64_t cols) { return (size_t)(cols / 256) * WIDE_CHUNKS * WIDE_NMAX * 16; }
+// the operand copy of every pass of a call with `tokens` token rows
+size_t gemm_wide_workspace_bytes(int64_t cols, int tokens) {
+    const int passes = (tokens + WIDE_NMAX - 1) / WIDE_NMAX;
+    return (size_t)(passes < 1 ? 1 : passes) * (size_t)(cols / 256) * WIDE_CHUNKS * WIDE_NMAX * 16;
+}
 size_t gemm_wide_partial_bytes_for(int sm_count, int64_t rows, int64_t cols) {
     const WidePlan p = wide_plan(sm_count, rows, (int)(cols / 256));
-    return p.ksplit > 1 ? (size_t)p.ksplit * WIDE_NMAX * p.tail_rows * sizeof(float) : 0;
+    return p.ksplit > 1 ? 4096 + (size_t)p.ksplit * WIDE_NMAX * p.tail_rows * sizeof(float) : 0;
 }
 size_t gemm_wide_partial_bytes(const tsb_ctx* ctx, int64_t rows, int64_t cols) {
-    const WidePlan p = wide_plan(ctx->sm_count, rows, (int)(cols / 256));
-    return p.ksplit > 1 ? (size_t)p.ksplit * WIDE_NMAX * p.tail_rows * sizeof(float) : 0;
+    return gemm_wide_partial_bytes_for(ctx->sm_count, rows, cols);
 }
 
 static size_t wide_smem_bytes(int n_pad) {
@@ -587,28 +638,27 @@ extern "C" __attribute__((visibility("default"))) void tsb_debug_set_wide_trace(
 cudaError_t launch_gemm_wide_q4k(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w, int64_t rows, int64_t cols, const __half* x,
                                  int64_t x_stride, int tokens, void* y, int64_t y_stride, bool y_f32, void* workspace, void* partials) {
     const int units = (int)(cols / 256);
-    const WidePlan plan = wide_plan(ctx->sm_count, rows, units);
-    const int ksplit = plan.ksplit;
     static SmemOptIn configured1, configured2;
     const size_t smem_max = std::max(wide_smem_bytes(WIDE_NDUAL), wide_smem_bytes(WIDE_NMAX));
     if (cudaError_t e = tsb_opt_in_smem(ctx, gemm_wide_q4k_kernel<1>, smem_max, configured1); e != cudaSuccess) return e;
     if (cudaError_t e = tsb_opt_in_smem(ctx, gemm_wide_q4k_kernel<2>, smem_max, configured2); e != cudaSuccess) return e;
     CUtensorMap wmap;
     if (cudaError_t e = wide_weight_map(w, rows, units, &wmap); e != cudaSuccess) return e;
-    // token rows go through in equal passes of at most WIDE_NMAX
+    // token rows go through in equal passes of at most WIDE_NMAX; one launch lays out the operand of every pass
     const int passes = (tokens + WIDE_NMAX - 1) / WIDE_NMAX;
     const int per_pass = ((tokens + passes - 1) / passes + 15) / 16 * 16;
-    for (int t0 = 0; t0 < tokens; t0 += per_pass) {
+    const size_t pass_chunks = (size_t)units * WIDE_CHUNKS * per_pass;
+    uint4* xw_all = static_cast<uint4*>(workspace);
+    if (!workspace)
+        if (cudaError_t e = cudaMallocAsync((void**)&xw_all, pass_chunks * passes * 16, st); e != cudaSuccess) return e;
+    cudaError_t e = tsb_launch(ctx, wide_prepare_kernel, dim3((unsigned)units, (unsigned)(passes * (per_pass >> 3))), dim3(256), 0, st, true, x,
+                               x_stride, tokens, per_pass, units, xw_all);
+    for (int t0 = 0, pass = 0; t0 < tokens && e == cudaSuccess; t0 += per_pass, pass++) {
         const int nt = min(per_pass, tokens - t0);
         const int n_pad = (nt + 15) / 16 * 16;
-        uint4* xw = static_cast<uint4*>(workspace);  // successive passes reuse it in stream order
-        const size_t xw_bytes = (size_t)units * WIDE_CHUNKS * n_pad * 16;
-        cudaError_t e = cudaSuccess;
-        if (!workspace) e = cudaMallocAsync((void**)&xw, xw_bytes, st);
-        if (e != cudaSuccess) return e;
-        const int64_t total = (int64_t)units * WIDE_CHUNKS * n_pad;
-        e = tsb_launch(ctx, wide_prepare_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, true, x + (size_t)t0 * x_stride,
-                       x_stride, nt, n_pad, units, xw);
+        const uint4* xw = xw_all + pass * pass_chunks;
+        const WidePlan plan = wide_plan(ctx->sm_count, rows, units);
+        const int ksplit = plan.ksplit;
         if (e == cudaSuccess) {
             // one CTA per SM: the kernel wants the whole tensor memory and most of the shared memory
             const size_t smem = wide_smem_bytes(n_pad);
@@ -616,7 +666,10 @@ cudaError_t launch_gemm_wide_q4k(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w
             dim3 grid((unsigned)min(n_items, ctx->sm_count));
             uint8_t* yp = static_cast<uint8_t*>(y) + (size_t)t0 * y_stride * (y_f32 ? 4 : 2);
             float* part = static_cast<float*>(partials);
-            if (ksplit > 1 && !part) e = cudaMallocAsync((void**)&part, (size_t)ksplit * nt * plan.tail_rows * sizeof(float), st);
+            if (ksplit > 1 && !part) {
+                e = cudaMallocAsync((void**)&part, 4096 + (size_t)ksplit * nt * plan.tail_rows * sizeof(float), st);
+                if (e == cudaSuccess) e = cudaMemsetAsync(part, 0, 4096, st);  // the ticket words start at zero
+            }
             if (e == cudaSuccess) {
                 if (n_pad <= 64)
                     e = tsb_launch(ctx, gemm_wide_q4k_kernel<1>, grid, dim3(WIDE_THREADS), smem, st, true, wmap, rows, units, (const uint4*)xw,
@@ -625,15 +678,9 @@ cudaError_t launch_gemm_wide_q4k(tsb_ctx* ctx, cudaStream_t st, const uint8_t* w
                     e = tsb_launch(ctx, gemm_wide_q4k_kernel<2>, grid, dim3(WIDE_THREADS), smem, st, true, wmap, rows, units, (const uint4*)xw,
                                    n_pad, nt, (void*)yp, y_stride, (int)(y_f32 ? 1 : 0), plan.n_whole, ksplit, part, ctx->dev_error);
             }
-            if (e == cudaSuccess && ksplit > 1) {
-                const int64_t total = (int64_t)nt * plan.tail_rows;
-                e = tsb_launch(ctx, wide_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, true, (const float*)part,
-                               ksplit, nt, plan.tail_rows, (int64_t)plan.n_whole * WM, (void*)yp, y_stride, (int)(y_f32 ? 1 : 0));
-            }
             if (ksplit > 1 && !partials && part) cudaFreeAsync(part, st);
         }
-        if (!workspace) cudaFreeAsync(xw, st);
-        if (e != cudaSuccess) return e;
     }
-    return cudaSuccess;
+    if (!workspace) cudaFreeAsync(xw_all, st);
+    return e;
 }

@@ -518,12 +518,13 @@ static int32_t runtime_init(tsb_session* s, ModelRt& rt, const tsb_model* model,
         if ((rc = A((size_t)R * c.d_model * 2, (void**)&rt.w_xn)) || (rc = A((size_t)R * qkv_dim * 2, (void**)&rt.w_qkv)) ||
             (rc = A((size_t)R * od * 2, (void**)&rt.w_ao)) || (rc = A((size_t)R * c.d_model * 2, (void**)&rt.w_o)) ||
             (rc = A((size_t)R * 2 * c.ffn * 2, (void**)&rt.w_gu)) || (rc = A((size_t)R * c.ffn * 2, (void**)&rt.w_a)) ||
-            (rc = A((size_t)R * c.vocab * 2, (void**)&rt.w_logits)) || (rc = A(gemm_wide_workspace_bytes(widest), &rt.w_ws)))
+            (rc = A((size_t)R * c.vocab * 2, (void**)&rt.w_logits)) || (rc = A(gemm_wide_workspace_bytes(widest, R), &rt.w_ws)))
             return rc;
         size_t part = gemm_wide_partial_bytes(ctx, model->lm_head.rows, model->lm_head.cols);
         for (const LayerW& l : model->layers)
             for (const Mat* mt : {&l.wqkv, &l.wo, &l.wgu, &l.wdown}) part = std::max(part, gemm_wide_partial_bytes(ctx, mt->rows, mt->cols));
         if (part && (rc = A(part, &rt.w_part))) return rc;
+        if (part) TSB_CUDA(ctx, cudaMemset(rt.w_part, 0, 4096));  // the ticket words of cut tiles
         rt.wide_ok = true;
     }
     return TSB_OK;
