@@ -612,6 +612,14 @@ TSB_API int32_t tsb_session_round_times(tsb_session* s, float* out4_ms);
  * them with seeded pseudo-random K/V. */
 TSB_API int32_t tsb_session_fill_context(tsb_session* s, int64_t tokens, uint64_t seed);
 
+/* The history penalties of a shaping record (repetition over the whole history, presence / frequency over the tokens
+ * generated in this turn; crates/selection/src/penalty.rs:15-39,59-82) are applied inside tsb_session_round,
+ * tsb_spec_run and tsb_sequential_run: a stream's history is the record of tokens fed to its cache plus the confirmed
+ * token entering the round.  `generated` says how many tokens at the end of that history count as generated; the
+ * generation loops keep it themselves, tsb_session_round adds what each round commits, tsb_producer_reset zeroes it
+ * and this call sets it (a serving loop calls it after the prompt: generated = 1 once the first token is chosen).
+ * Penalised rounds stage the history from the host every round and run as plain launches, not as a graph. */
+TSB_API int32_t tsb_session_set_generated(tsb_session* s, int32_t stream, int32_t generated);
 /* verify_tree for every stream of the session in ONE target pass: stream b's slots are feed[b * n .. b * n + n), all
  * streams share the tree shape slot_parent[0..n) (crates/runtime/src/families/qwen/batched_scratch.rs:97-124) and
  * each starts at its own cursor.  Row b * n + j of the logits belongs to stream b's slot j; logits_out_host may be

@@ -353,6 +353,86 @@ def test_sampled_round_decisions_match_the_oracle_given_the_devices_logits(rig, 
     sess.close()
 
 
+def test_penalised_rounds_match_the_oracle_given_the_devices_logits(rig, oracle):
+    """Repetition, presence and frequency penalties inside the round: every proposal is shaped with the history the
+    round started with, target row i with the history grown by the proposals accepted before it
+    (crates/runtime/src/speculative.rs:636-648,701-734); decisions, tokens and draw counts equal the oracle's on the
+    logits the kernels saw, and they differ from the unpenalised ones (the test is not vacuous)."""
+    tsb = rig["tsb"]
+    ctx = rig["ctx"]
+    K = 4
+    sess = tsb.Session(ctx, rig["target"], rig["draft"], 1, K + 1)
+    rng = np.random.default_rng(13)
+    prompt = rng.integers(0, rig["cfg"].vocab, size=24).astype(np.int32)
+    for i, t in enumerate(prompt[:-1]):
+        sess.produce_prefill(int(t), i)
+    sess.produce(int(prompt[-1]), len(prompt) - 1)
+    sess.prime_drafter(int(prompt[-1]), len(prompt) - 2)
+    pen = dict(temperature=1.0, seed=2, repetition_penalty=1.4, presence_penalty=0.6, frequency_penalty=0.3)
+    rc = tsb.run_config(tsb.shaping(**pen), 64, K, uniform_mode=1)
+    ocfg, plain = oracle.shaping(**pen), oracle.shaping(temperature=1.0, seed=2)
+    nxt = np.array([int(prompt[3])], dtype=np.int32)  # a token that is already in the history
+    steps = np.zeros(1, dtype=np.uint64)
+    history, gen = list(map(int, prompt)), 1
+    sess.set_generated(gen)
+    moved = 0
+    for rnd in range(6):
+        base = sess.checkpoint()
+        step0 = int(steps[0])
+        confirmed = int(nxt[0])
+        hist0 = history + [confirmed]
+        accepted = sess.round(rc, nxt, steps)[0]
+        sess.kv(0).set_cursor(0, base)
+        sess.kv(1).set_cursor(0, base)
+        chained, props, dlogits = confirmed, [], []
+        for d in range(K):
+            lg = sess.draft_step(chained, base - 1 + d)
+            tok, _ = oracle.sample(lg, ocfg, oracle.uniform_u64(1, 2, step0 + d), history=hist0, generated=gen)
+            moved += tok != oracle.sample(lg, plain, oracle.uniform_u64(1, 2, step0 + d))[0]
+            dlogits.append(lg), props.append(tok)
+            chained = tok
+        tlogits = sess.verify([confirmed] + props, base)
+        unis = [oracle.uniform_u64(1, 2, step0 + K + 1 + j) for j in range(2 * K + 1)]
+        acc, toks, draws, _ = oracle.accept_round(tlogits, np.stack(dlogits), props, ocfg, unis, history=hist0, generated=gen)
+        assert acc == accepted and toks[-1] == nxt[0], (rnd, acc, accepted, toks, nxt)
+        assert int(steps[0]) == step0 + K + 1 + draws
+        sess.kv(0).set_cursor(0, base + acc + 1)
+        sess.kv(1).set_cursor(0, base + acc + 1)
+        history = hist0 + [int(t) for t in toks[:acc]]
+        gen += acc + 1
+    assert moved > 0
+    sess.close()
+
+
+def test_penalised_generation_loops_run_and_agree_on_the_first_token(rig, oracle):
+    """The loops take a shaping record with penalties (they refused it before): the sequential loop's tokens equal the
+    oracle's select over the device logits with the growing history, and the speculative loop starts from the same token."""
+    tsb = rig["tsb"]
+    sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 8)
+    rng = np.random.default_rng(17)
+    prompt = rng.integers(0, rig["cfg"].vocab, size=12).astype(np.int32)
+    pen = dict(temperature=0.9, seed=5, repetition_penalty=1.3, presence_penalty=0.5, frequency_penalty=0.25, top_k=40)
+    rc = tsb.run_config(tsb.shaping(**pen), 10, 3)
+    hist, emitted, res = sess.sequential_run(prompt, rc)
+    assert res.new_tokens == 10
+    # replay: feed the same tokens and select with the oracle on the device's logits
+    ocfg = oracle.shaping(**pen)
+    sess.reset()
+    for i, t in enumerate(prompt[:-1]):
+        sess.produce_prefill(int(t), i)
+    logits = sess.produce(int(prompt[-1]), len(prompt) - 1)
+    history = list(map(int, prompt))
+    for g in range(10):
+        tok, _ = oracle.sample(logits, ocfg, oracle.uniform_u64(0, 5, g), history=history, generated=g)
+        assert tok == int(emitted[g]), (g, tok, int(emitted[g]))
+        history.append(tok)
+        if g < 9:
+            logits = sess.produce(tok, len(history) - 1)
+    _, spec_emitted, res2 = sess.spec_run(prompt, rc)
+    assert res2.new_tokens == 10 and int(spec_emitted[0]) == int(emitted[0])
+    sess.close()
+
+
 def test_stop_token_budget_and_refusals(rig, oracle):
     tsb = rig["tsb"]
     sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 8)
@@ -367,7 +447,7 @@ def test_stop_token_budget_and_refusals(rig, oracle):
     assert r1.reason == r2.reason == 1 and np.array_equal(e1, e2) and np.array_equal(h1, h2)
     assert e2[-1] == stop_tok and len(h2) == len(prompt) + len(e2) - 1  # the stopping token is counted, not fed
     for bad in (tsb.run_config(tsb.shaping(temperature=0.0), 24, 0), tsb.run_config(tsb.shaping(temperature=0.0), 0, 2),
-                tsb.run_config(tsb.shaping(temperature=0.0), 600, 2), tsb.run_config(tsb.shaping(temperature=0.7, repetition_penalty=1.2), 8, 2)):
+                tsb.run_config(tsb.shaping(temperature=0.0), 600, 2), tsb.run_config(tsb.shaping(temperature=0.7, repetition_penalty=0.0), 8, 2)):
         with pytest.raises(tsb.TsbError):
             sess.spec_run(prompt, bad)
     with pytest.raises(tsb.TsbError):

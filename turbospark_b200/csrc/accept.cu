@@ -918,7 +918,7 @@ static PenaltyArgs penalty_args(const tsb_shaping& sh, const int32_t* history, i
 cudaError_t launch_accept_history(tsb_ctx* ctx, cudaStream_t st, const __half* target, const __half* draft, const int32_t* proposals,
                                   int prop_stride, const uint64_t* uniforms, int batch, int k, int vocab, const tsb_shaping& sh,
                                   const int32_t* history, int hist_stride, const int32_t* hist_len, const int32_t* generated,
-                                  tsb_accept_out* out_dev, void* scratch) {
+                                  tsb_accept_out* out_dev, void* scratch, int32_t* next_tokens, int next_stride) {
     const int rps = 2 * k + 1;
     uint8_t* base = reinterpret_cast<uint8_t*>(scratch) + accept_scratch_bytes(batch, k, vocab);
     float* t32 = reinterpret_cast<float*>(base);
@@ -929,22 +929,24 @@ cudaError_t launch_accept_history(tsb_ctx* ctx, cudaStream_t st, const __half* t
     e = tsb_launch(ctx, penalize_rows_kernel, dim3((unsigned)(batch * rps)), dim3(1024), 0, st, false, target, draft, k, vocab, rps, (int64_t)0,
                    penalty_args(sh, history, hist_stride, hist_len, generated, proposals, prop_stride), t32, d32, marks);
     if (e != cudaSuccess) return e;
-    return launch_accept_t<float>(ctx, st, t32, d32, proposals, prop_stride, uniforms, batch, k, vocab, AcceptShape(sh), out_dev, nullptr, 0,
-                                  scratch);
+    return launch_accept_t<float>(ctx, st, t32, d32, proposals, prop_stride, uniforms, batch, k, vocab, AcceptShape(sh), out_dev, next_tokens,
+                                  next_stride, scratch);
 }
 
 cudaError_t launch_sample_history(tsb_ctx* ctx, cudaStream_t st, const __half* logits, const uint64_t* uniforms, int batch, int vocab,
                                   const tsb_shaping& sh, const int32_t* history, int hist_stride, const int32_t* hist_len,
-                                  const int32_t* generated, int32_t* tokens_dev, double* margins_dev, void* scratch) {
+                                  const int32_t* generated, int32_t* tokens_dev, double* margins_dev, void* scratch, int64_t logits_stride,
+                                  int uni_stride, int token_stride) {
+    if (logits_stride <= 0) logits_stride = vocab;
     uint8_t* base = reinterpret_cast<uint8_t*>(scratch) + accept_scratch_bytes(batch, 0, vocab);
     float* l32 = reinterpret_cast<float*>(base);
     uint32_t* marks = reinterpret_cast<uint32_t*>(base + penalty_rows_bytes(batch, 1, vocab));
     cudaError_t e = cudaMemsetAsync(marks, 0, penalty_rows_bytes(batch, 1, vocab), st);
     if (e != cudaSuccess) return e;
     e = tsb_launch(ctx, penalize_rows_kernel, dim3((unsigned)batch), dim3(1024), 0, st, false, logits, (const __half*)nullptr, 0, vocab, 1,
-                   (int64_t)vocab, penalty_args(sh, history, hist_stride, hist_len, generated, nullptr, 0), l32, (float*)nullptr, marks);
+                   logits_stride, penalty_args(sh, history, hist_stride, hist_len, generated, nullptr, 0), l32, (float*)nullptr, marks);
     if (e != cudaSuccess) return e;
-    return launch_sample_t<float>(ctx, st, l32, vocab, uniforms, 1, batch, vocab, AcceptShape(sh), tokens_dev, 1, margins_dev);
+    return launch_sample_t<float>(ctx, st, l32, vocab, uniforms, uni_stride, batch, vocab, AcceptShape(sh), tokens_dev, token_stride, margins_dev);
 }
 
 cudaError_t launch_topk_rows(tsb_ctx* ctx, cudaStream_t st, const __half* logits, int vocab, const int32_t* rows_dev, int n_rows,
@@ -969,7 +971,10 @@ void accept_row_stats_read(const void* host_stats, int row, int32_t* argmax, int
     *nonfinite = st->nonfinite;
 }
 
-int32_t accept_check_shaping(tsb_ctx* ctx, const tsb_shaping* sh) { return check_shaping(ctx, sh); }
+int32_t accept_check_shaping(tsb_ctx* ctx, const tsb_shaping* sh, bool have_history) { return check_shaping(ctx, sh, have_history); }
+bool accept_has_penalties(const tsb_shaping& sh) {
+    return sh.temperature != 0.0 && (sh.repetition_penalty != 1.0 || sh.presence_penalty != 0.0 || sh.frequency_penalty != 0.0);
+}
 
 extern "C" {
 

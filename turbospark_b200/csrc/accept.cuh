@@ -13,7 +13,9 @@ struct AcceptShape {
 };
 size_t accept_scratch_bytes(int batch, int k, int vocab);
 int accept_max_vocab();  // largest vocabulary the on-chip draw holds
-int32_t accept_check_shaping(tsb_ctx* ctx, const tsb_shaping* sh);
+// have_history: the caller can supply the token history, so the history penalties are accepted
+int32_t accept_check_shaping(tsb_ctx* ctx, const tsb_shaping* sh, bool have_history = false);
+bool accept_has_penalties(const tsb_shaping& sh);  // the record carries a penalty that changes a sampled distribution
 // proposals[b * prop_stride + i]; when next_tokens != null the corrected / bonus token of stream b is also
 // written to next_tokens[b * next_stride].
 cudaError_t launch_accept(tsb_ctx* ctx, cudaStream_t st, const __half* target, const __half* draft, const int32_t* proposals,
@@ -30,10 +32,11 @@ size_t accept_history_scratch_bytes(int batch, int k, int vocab);
 cudaError_t launch_accept_history(tsb_ctx* ctx, cudaStream_t st, const __half* target, const __half* draft, const int32_t* proposals,
                                   int prop_stride, const uint64_t* uniforms, int batch, int k, int vocab, const tsb_shaping& sh,
                                   const int32_t* history, int hist_stride, const int32_t* hist_len, const int32_t* generated,
-                                  tsb_accept_out* out_dev, void* scratch);
+                                  tsb_accept_out* out_dev, void* scratch, int32_t* next_tokens = nullptr, int next_stride = 0);
 cudaError_t launch_sample_history(tsb_ctx* ctx, cudaStream_t st, const __half* logits, const uint64_t* uniforms, int batch, int vocab,
                                   const tsb_shaping& sh, const int32_t* history, int hist_stride, const int32_t* hist_len,
-                                  const int32_t* generated, int32_t* tokens_dev, double* margins_dev, void* scratch);
+                                  const int32_t* generated, int32_t* tokens_dev, double* margins_dev, void* scratch,
+                                  int64_t logits_stride = 0, int uni_stride = 1, int token_stride = 1);
 // The `width` (<= 8) largest logits of rows rows_dev[0..n_rows) of a [*, vocab] matrix, value descending, token id
 // ascending on ties; row r's picks land in out_dev[r * 8 ..].
 cudaError_t launch_topk_rows(tsb_ctx* ctx, cudaStream_t st, const __half* logits, int vocab, const int32_t* rows_dev, int n_rows,

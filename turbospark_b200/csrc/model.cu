@@ -843,6 +843,7 @@ int32_t tsb_session_create(tsb_ctx* ctx, const tsb_model* target, const tsb_mode
     tsb_session* s = new (std::nothrow) tsb_session();
     if (!s) return TSB_ERR_OOM;
     s->ctx = ctx, s->n_streams = n_streams, s->max_rows = max_rows;
+    s->generated.assign(n_streams, 0);
     auto fail = [&](int32_t code) {
         tsb_session_destroy(s);
         return code;
@@ -922,9 +923,17 @@ int32_t tsb_producer_reset(tsb_session* s, int32_t stream) {
     if (rc) return rc;
     s->target.fed[stream].clear();
     s->target.pending[stream] = PendingVerify();
+    s->generated[stream] = 0;
     if (s->has_draft) {
         if ((rc = tsb_kv_reset(s->draft.kv, stream))) return rc;
     }
+    return TSB_OK;
+}
+
+int32_t tsb_session_set_generated(tsb_session* s, int32_t stream, int32_t generated) {
+    if (!s) return TSB_ERR_INVALID;
+    TSB_REQUIRE(s->ctx, stream >= 0 && stream < s->n_streams && generated >= 0, "bad stream or count");
+    s->generated[stream] = generated;
     return TSB_OK;
 }
 
@@ -1297,13 +1306,52 @@ int32_t tsb_session_fill_context(tsb_session* s, int64_t tokens, uint64_t seed) 
 
 }  // extern "C"
 
+int32_t session_stage_history(tsb_session* s, const int32_t* streams, int n_active, const int32_t* next_tokens) {
+    tsb_ctx* ctx = s->ctx;
+    const int max_ctx = s->target.model->cfg.max_context, V = s->target.model->cfg.vocab;
+    if (!s->hist_dev) {
+        TSB_CUDA(ctx, cudaMalloc((void**)&s->hist_dev, (size_t)s->n_streams * max_ctx * sizeof(int32_t)));
+        s->owned.push_back(s->hist_dev);
+        TSB_CUDA(ctx, cudaMalloc((void**)&s->hist_len_dev, (size_t)s->n_streams * 2 * sizeof(int32_t)));
+        s->owned.push_back(s->hist_len_dev);
+        s->gen_dev = s->hist_len_dev + s->n_streams;
+        TSB_CUDA(ctx, cudaMalloc(&s->pen_scratch, accept_history_scratch_bytes(s->n_streams, std::min(15, s->max_rows - 1 > 0 ? s->max_rows - 1 : 1), V)));
+        s->owned.push_back(s->pen_scratch);
+    }
+    s->hist_host.assign((size_t)n_active * max_ctx + 2 * (size_t)n_active, 0);
+    int32_t* lens = s->hist_host.data() + (size_t)n_active * max_ctx;
+    for (int a = 0; a < n_active; a++) {
+        const int q = streams[a];
+        const auto& fed = s->target.fed[q];
+        const int64_t ct = tsb_kv_cursor(s->target.kv, q);
+        if ((int64_t)fed.size() < ct) return tsb_fail(ctx, TSB_ERR_STATE, "stream %d: the record of fed tokens ends before the cursor", q);
+        if (ct + (next_tokens ? 1 : 0) > max_ctx) return tsb_fail(ctx, TSB_ERR_STATE, "stream %d: history beyond the context window", q);
+        int32_t* row = s->hist_host.data() + (size_t)a * max_ctx;
+        std::copy(fed.begin(), fed.begin() + ct, row);
+        int n = (int)ct;
+        if (next_tokens) row[n++] = next_tokens[a];
+        lens[a] = n;
+        lens[n_active + a] = std::min(s->generated[q], n);
+    }
+    // rows are uploaded at their used length; the copies come from pageable memory, so they are complete when the
+    // calls return and hist_host may be reused
+    for (int a = 0; a < n_active; a++)
+        if (lens[a] > 0)
+            TSB_CUDA(ctx, cudaMemcpyAsync(s->hist_dev + (size_t)a * max_ctx, s->hist_host.data() + (size_t)a * max_ctx, (size_t)lens[a] * sizeof(int32_t),
+                                          cudaMemcpyHostToDevice, s->stream));
+    TSB_CUDA(ctx, cudaMemcpyAsync(s->hist_len_dev, lens, (size_t)n_active * sizeof(int32_t), cudaMemcpyHostToDevice, s->stream));
+    TSB_CUDA(ctx, cudaMemcpyAsync(s->gen_dev, lens + n_active, (size_t)n_active * sizeof(int32_t), cudaMemcpyHostToDevice, s->stream));
+    return TSB_OK;
+}
+
 int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_active, int k, const tsb_run_config* cfg,
                               int32_t* next_tokens_host, int32_t* accepted_host, int32_t* tokens_out, int32_t* draws_out,
                               uint64_t* draw_step_inout) {
     tsb_ctx* ctx = s->ctx;
     if (!s->has_draft) return tsb_fail(ctx, TSB_ERR_STATE, "the session has no drafter");
-    int32_t rc = accept_check_shaping(ctx, &cfg->shaping);
+    int32_t rc = accept_check_shaping(ctx, &cfg->shaping, true);
     if (rc) return rc;
+    const bool penalised = accept_has_penalties(cfg->shaping);
     const int K = k, S = n_active;
     TSB_REQUIRE(ctx, K >= 1 && K <= 15 && K + 1 <= s->max_rows, "block must be 1..15 and fit the session's max_rows");
     TSB_REQUIRE(ctx, S >= 1 && S <= s->n_streams, "bad stream count");
@@ -1341,6 +1389,9 @@ int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_acti
         s->pair_host[2 * a] = fed[(size_t)ct - 1];
         s->pair_host[2 * a + 1] = next_tokens_host[a];
     }
+    // a penalised round reads each stream's history - the tokens before the cursor, then the confirmed one - on the device
+    if (penalised && (rc = session_stage_history(s, streams, S, next_tokens_host))) return rc;
+    const int max_ctx = s->target.model->cfg.max_context;
     uint64_t* un_draft = s->uniforms_dev;
     uint64_t* un_acc = s->uniforms_dev + (size_t)S * UD;
     // pages for every row of the round are reserved up front (a reservation copies the page table synchronously,
@@ -1393,9 +1444,15 @@ int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_acti
                 TSB_CUDA(ctx, forward_device(s, s->draft, s->feed_dev + d, K + 1, rd, S, 1, max_len,
                                              s->logits_draft + (size_t)d * V, (int64_t)K * V));
             for (int a = 0; a < S; a++) tsb_kv_set_cursor(s->draft.kv, streams[a], tsb_kv_cursor(s->draft.kv, streams[a]) + nrow);
-            if (!s->replay)
-                TSB_CUDA(ctx, launch_sample(ctx, st, s->logits_draft + (size_t)d * V, (int64_t)K * V, un_draft + d, UD, S, V, AcceptShape(cfg->shaping),
-                                            s->feed_dev + d + 1, K + 1, nullptr, s->accept_scratch));
+            if (!s->replay) {
+                if (penalised)  // every proposal of a round is shaped with the history the round started with (speculative.rs:636-648)
+                    TSB_CUDA(ctx, launch_sample_history(ctx, st, s->logits_draft + (size_t)d * V, un_draft + d, S, V, cfg->shaping, s->hist_dev, max_ctx,
+                                                        s->hist_len_dev, s->gen_dev, s->feed_dev + d + 1, nullptr, s->pen_scratch, (int64_t)K * V, UD,
+                                                        K + 1));
+                else
+                    TSB_CUDA(ctx, launch_sample(ctx, st, s->logits_draft + (size_t)d * V, (int64_t)K * V, un_draft + d, UD, S, V, AcceptShape(cfg->shaping),
+                                                s->feed_dev + d + 1, K + 1, nullptr, s->accept_scratch));
+            }
         }
         if (!s->replay && !s->capturing) TSB_CUDA(ctx, cudaEventRecord(s->ev[1], st));
         // ---- verify: K+1 rows per stream in one pass
@@ -1408,8 +1465,13 @@ int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_acti
         if (!s->replay) {
             if (!s->capturing) TSB_CUDA(ctx, cudaEventRecord(s->ev[2], st));
             // ---- accept on the device; the next confirmed token also lands in feed[.][0]
-            TSB_CUDA(ctx, launch_accept(ctx, st, s->logits_target, s->logits_draft, s->feed_dev + 1, K + 1, un_acc, S, K, V, AcceptShape(cfg->shaping),
-                                        s->accept_out_dev, s->feed_dev, K + 1, s->accept_scratch));
+            if (penalised)
+                TSB_CUDA(ctx, launch_accept_history(ctx, st, s->logits_target, s->logits_draft, s->feed_dev + 1, K + 1, un_acc, S, K, V, cfg->shaping,
+                                                    s->hist_dev, max_ctx, s->hist_len_dev, s->gen_dev, s->accept_out_dev, s->pen_scratch, s->feed_dev,
+                                                    K + 1));
+            else
+                TSB_CUDA(ctx, launch_accept(ctx, st, s->logits_target, s->logits_draft, s->feed_dev + 1, K + 1, un_acc, S, K, V, AcceptShape(cfg->shaping),
+                                            s->accept_out_dev, s->feed_dev, K + 1, s->accept_scratch));
             TSB_CUDA(ctx, cudaMemcpyAsync(s->accept_out_host, s->accept_out_dev, (size_t)S * sizeof(tsb_accept_out),
                                           cudaMemcpyDeviceToHost, st));
             if (!s->capturing) TSB_CUDA(ctx, cudaEventRecord(s->ev[3], st));
@@ -1426,7 +1488,7 @@ int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_acti
         s->stage_used = 0;
         return code;
     };
-    const bool want_graph = s->use_graph && s->rounds_done >= 1;
+    const bool want_graph = s->use_graph && s->rounds_done >= 1 && !penalised;
     if (want_graph && s->graph && s->graph_key == key) {
         s->replay = true;  // host-side staging only: descriptors land in the pinned ring at the captured offsets
         rc = body();
@@ -1490,6 +1552,7 @@ int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_acti
         if (tokens_out) memcpy(tokens_out + (size_t)a * 16, o.tokens, sizeof(o.tokens));
         if (draws_out) draws_out[a] = o.draws;
         next_tokens_host[a] = o.tokens[o.accepted];
+        s->generated[q] += o.accepted + 1;  // the accepted proposals and the token that enters the next round
         draw_step_inout[a] += (sampled ? (uint64_t)(K + 1) : 0) + (uint64_t)o.draws;
     }
     return TSB_OK;
@@ -1707,17 +1770,25 @@ int32_t session_tree_commit(tsb_session* s, int stream, int64_t base, const std:
     return TSB_OK;
 }
 
-int32_t session_select_target(tsb_session* s, const tsb_run_config* cfg, uint64_t uniform, int32_t* token_host) {
+int32_t session_select_target(tsb_session* s, int stream, const tsb_run_config* cfg, uint64_t uniform, int32_t* token_host) {
     tsb_ctx* ctx = s->ctx;
     const int V = s->target.model->cfg.vocab;
+    int32_t rc = accept_check_shaping(ctx, &cfg->shaping, true);
+    if (rc) return rc;
     uint64_t* u = s->uniforms_host;
     u[0] = uniform;
     TSB_CUDA(ctx, cudaMemcpyAsync(s->uniforms_dev, u, sizeof(uint64_t), cudaMemcpyHostToDevice, s->stream));
-    TSB_CUDA(ctx, launch_sample(ctx, s->stream, s->logits_target, V, s->uniforms_dev, 1, 1, V, AcceptShape(cfg->shaping),
-                                s->tok1_dev, 1, nullptr, s->accept_scratch));
+    if (accept_has_penalties(cfg->shaping)) {
+        // select(logits, shaping, history): the history is everything fed so far (crates/selection/src/choose.rs:139-154)
+        if ((rc = session_stage_history(s, &stream, 1, nullptr))) return rc;
+        TSB_CUDA(ctx, launch_sample_history(ctx, s->stream, s->logits_target, s->uniforms_dev, 1, V, cfg->shaping, s->hist_dev,
+                                            s->target.model->cfg.max_context, s->hist_len_dev, s->gen_dev, s->tok1_dev, nullptr, s->pen_scratch));
+    } else {
+        TSB_CUDA(ctx, launch_sample(ctx, s->stream, s->logits_target, V, s->uniforms_dev, 1, 1, V, AcceptShape(cfg->shaping),
+                                    s->tok1_dev, 1, nullptr, s->accept_scratch));
+    }
     TSB_CUDA(ctx, cudaMemcpyAsync(s->feed_host, s->tok1_dev, sizeof(int32_t), cudaMemcpyDeviceToHost, s->stream));
-    int32_t rc = tsb_stream_sync(ctx, s->stream);
-    if (rc) return rc;
+    if ((rc = tsb_stream_sync(ctx, s->stream))) return rc;
     *token_host = s->feed_host[0];
     return TSB_OK;
 }

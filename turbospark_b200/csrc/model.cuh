@@ -125,6 +125,15 @@ struct tsb_session {
     cudaGraphExec_t graph = nullptr;
     uint64_t graph_key = 0, graph_launches = 0;
     int rounds_done = 0;
+    // History penalties (repetition / presence / frequency): the sampler and the acceptance then read every stream's
+    // token history from the device.  The buffers are made on first use; a round that needs them runs as plain
+    // launches (the history is staged from the host record every round).
+    std::vector<int32_t> generated;   // per stream: how many tokens at the end of its history were generated in this turn
+    int32_t* hist_dev = nullptr;      // [n_streams, max_context]
+    int32_t* hist_len_dev = nullptr;  // [n_streams]
+    int32_t* gen_dev = nullptr;       // [n_streams]
+    void* pen_scratch = nullptr;      // f32 rows + mark words of the penalised distributions
+    std::vector<int32_t> hist_host;
     TreeShape tree;  // what tsb_producer_tree_nodes / tsb_producer_draft_tree use
     tsb_comm* comm = nullptr;  // exchange steps of a sharded routed model (null: single GPU)
 };
@@ -141,6 +150,10 @@ int32_t session_round_streams(tsb_session* s, const int32_t* streams, int n_acti
 // anchor + nodes in one target pass and returns, per slot (0 = anchor, node i = slot i + 1), the fed token, the
 // slot's parent and the target's pick at that row.  Both caches' cursors are left at `base`; rows base + slot hold
 // the tree (the drafter's only for the first *drafter_rows slots).
+// Stage the token history of `n_active` streams for the penalised sampler: stream q's history is the record of
+// tokens fed to its target cache up to the cursor, followed by next_tokens[a] when given (the confirmed token that
+// enters a round); its generated count is s->generated[q].  Rows land at hist_dev[a * max_context ..].
+int32_t session_stage_history(tsb_session* s, const int32_t* streams, int n_active, const int32_t* next_tokens);
 int32_t session_tree_round(tsb_session* s, int stream, const tsb_run_config* cfg, int32_t next, int64_t base,
                            std::vector<int32_t>& feed, std::vector<int32_t>& slot_parent, std::vector<int32_t>& picks,
                            int* drafter_rows);
@@ -199,4 +212,4 @@ int32_t session_tree_commit(tsb_session* s, int stream, int64_t base, const std:
 // produce_prefill for tokens[0..n) starting at the stream's cursor, several rows per pass (model.cu).
 int32_t session_prefill_rows(tsb_session* s, int stream, const int32_t* tokens, int n);
 // token = select(logits row of the last single-row target forward) for one stream (model.cu).
-int32_t session_select_target(tsb_session* s, const tsb_run_config* cfg, uint64_t uniform, int32_t* token_host);
+int32_t session_select_target(tsb_session* s, int stream, const tsb_run_config* cfg, uint64_t uniform, int32_t* token_host);

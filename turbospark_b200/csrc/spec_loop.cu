@@ -143,7 +143,8 @@ int32_t tsb_spec_run(tsb_session* s, int32_t stream, const int32_t* prompt, int3
     int64_t position = n_prompt;
 
     int32_t next;
-    if ((rc = session_select_target(s, cfg, first_uniform(cfg), &next))) return rc;
+    s->generated[stream] = 0;
+    if ((rc = session_select_target(s, stream, cfg, first_uniform(cfg), &next))) return rc;
     // the confirmed token's stream seed offset is zero for a single-stream run
     tsb_run_config round_cfg = *cfg;
     round_cfg.shaping.seed = cfg->shaping.seed - (uint64_t)stream;
@@ -220,6 +221,7 @@ int32_t tsb_spec_run(tsb_session* s, int32_t stream, const int32_t* prompt, int3
 
         int32_t accepted = 0, draws = 0, toks[16];
         int32_t confirmed = next;
+        s->generated[stream] = sink.generated;  // the history penalties count the tokens of this turn, the confirmed one included
         if ((rc = session_round_streams(s, &stream, 1, (int)round_block, &round_cfg, &confirmed, &accepted, toks, &draws, &draw_step)))
             return rc;
         rounds++;
@@ -275,7 +277,8 @@ int32_t tsb_sequential_run(tsb_session* s, int32_t stream, const int32_t* prompt
         const uint64_t u = cfg->uniform_mode == 0 ? tsb_uniform_u64(0, cfg->shaping.seed, (uint64_t)sink.generated)
                                                   : tsb_uniform_u64(cfg->uniform_mode, cfg->shaping.seed, (1ull << 63) + (uint64_t)sink.generated);
         int32_t next;
-        if ((rc = session_select_target(s, cfg, u, &next))) return rc;
+        s->generated[stream] = sink.generated;
+        if ((rc = session_select_target(s, stream, cfg, u, &next))) return rc;
         const int stop = sink.commit(next);
         if (stop >= 0) {
             reason = stop;

@@ -285,6 +285,10 @@ class Session:
         """The passes of this session exchange through `comm` (a turbospark_b200.comm.Comm; None: single GPU)."""
         self.ctx.check(lib().tsb_session_set_comm(self.h, comm.h if comm is not None else None))
 
+    def set_generated(self, generated, stream=0):
+        """How many tokens at the end of the stream's history count as generated (the presence / frequency penalties' window)."""
+        self.ctx.check(lib().tsb_session_set_generated(self.h, C.c_int32(stream), C.c_int32(generated)))
+
     def set_graph(self, enabled):
         self.ctx.check(lib().tsb_session_set_graph(self.h, C.c_int32(int(enabled))))
 
