@@ -36,7 +36,8 @@ namespace {
 constexpr int ACC_THREADS = 1024;
 constexpr int CL = 8;               // CTAs per cluster
 constexpr int SLICE_MAX = 20480;    // vocabulary entries one CTA can hold (8 * 20480 = 163840)
-constexpr int NBINS = 2048;
+constexpr int RADIX_BINS = 256;     // the draw resolves a key eight bits at a time
+constexpr int HIST_COPIES = 16;     // histogram copies per CTA: two warps share one
 constexpr double FP_ONE = 1152921504606846976.0;  // 2^60
 
 struct RowStats {
@@ -93,6 +94,13 @@ struct Logit<float> {
     static __device__ __forceinline__ uint32_t key(float x) { return desc_key(x == 0.f ? 0.f : x); }
 };
 
+#ifdef TSB_SAMPLE_TRACE
+__device__ unsigned long long* g_sample_trace = nullptr;  // development builds: phase stamps of cluster 0, rank 0, thread 0
+#define STRC(i) do { if (g_sample_trace && blockIdx.x == 0 && threadIdx.x == 0) g_sample_trace[i] = global_timer_ns(); } while (0)
+#else
+#define STRC(i)
+#endif
+
 // w_i of reweight (choose.rs:296-321): ((e/sum)/top)^(1/T), top = max_i e_i/sum = 1/sum.
 __device__ __forceinline__ double weight_of(double e, double sum, double top, double inv_t, bool unit_t) {
     const double p = e / sum;
@@ -136,7 +144,7 @@ __device__ __forceinline__ Slice my_slice(int vocab, int rank) {
 
 // --------------------------------------------------------------------- draw
 struct DrawShared {
-    unsigned long long hist[NBINS];
+    unsigned long long hist[HIST_COPIES][RADIX_BINS];
     unsigned long long scan[ACC_THREADS / 32];
     double red[ACC_THREADS / 32];
     Xchg xch;
@@ -161,21 +169,36 @@ __device__ int cluster_radix_select(cg::cluster_group& cluster, DrawShared& c, M
     constexpr int PASSES = Logit<LT>::KEY_PASSES;
     for (int pass = 0; pass < PASSES; pass++) {
         const int shift = 8 * (PASSES - 1 - pass);
-        for (int i = threadIdx.x; i < RB; i += ACC_THREADS) c.hist[i] = 0;
+        for (int i = threadIdx.x; i < HIST_COPIES * RB; i += ACC_THREADS) (&c.hist[0][0])[i] = 0;
         __syncthreads();
-        for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
-            const uint32_t kd = Logit<LT>::key(krow[sl.lo + j]);
-            if (pass == 0 || (kd >> (shift + 8)) == (prefix >> (shift + 8))) {
-                const unsigned long long m = fp(j);
-                if (m) atomicAdd(&c.hist[(kd >> shift) & (RB - 1)], m);
+        // Masses go into one of HIST_COPIES histograms (two warps share a copy): the first pass would otherwise
+        // serialise every warp of the CTA on the handful of bins that hold most of a row (sign, exponent and two
+        // mantissa bits of a logit).  Integer sums: the result does not depend on the order.
+        {
+            unsigned long long* hist = c.hist[(threadIdx.x >> 5) & (HIST_COPIES - 1)];
+            for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) {
+                const uint32_t kd = Logit<LT>::key(krow[sl.lo + j]);
+                if (pass == 0 || (kd >> (shift + 8)) == (prefix >> (shift + 8))) {
+                    const unsigned long long m = fp(j);
+                    if (m) atomicAdd(&hist[(kd >> shift) & (RB - 1)], m);
+                }
             }
         }
+        __syncthreads();
+        if (threadIdx.x < RB) {  // the copies fold into the first one, which is what the cluster's first CTA reads
+            unsigned long long t = 0;
+#pragma unroll
+            for (int cp = 0; cp < HIST_COPIES; cp++) t += c.hist[cp][threadIdx.x];
+            c.hist[0][threadIdx.x] = t;
+        }
+        STRC(6 + 2 * (pass & 1));
         cluster.sync();
+        STRC(7 + 2 * (pass & 1));
         if (rank == 0) {
             // sum the members' histograms bin by bin, scan, find the bin the target falls into
             unsigned long long t = 0;
             if (threadIdx.x < RB)
-                for (int rr = 0; rr < CL; rr++) t += cluster.map_shared_rank(c.hist, rr)[threadIdx.x];
+                for (int rr = 0; rr < CL; rr++) t += cluster.map_shared_rank(&c, rr)->hist[0][threadIdx.x];
             unsigned long long v = t;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -581,7 +604,9 @@ __global__ void __launch_bounds__(ACC_THREADS)
     __shared__ int bad_flag;
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
+    STRC(0);
     pdl_wait();
+    STRC(1);
     const int b = blockIdx.x / CL;
     const LT* row = logits + (size_t)b * logits_stride;
     const Slice sl = my_slice(vocab, rank);
@@ -625,6 +650,7 @@ __global__ void __launch_bounds__(ACC_THREADS)
 
     int token;
     unsigned long long gap = ~0ull;
+    STRC(2);
     if (nonfinite) {
         token = -1;
         if (rank == 0 && threadIdx.x == 0) atomicCAS(err, 0u, (uint32_t)TSB_DEV_NONFINITE);
@@ -645,7 +671,9 @@ __global__ void __launch_bounds__(ACC_THREADS)
             const unsigned long long eb = (unsigned long long)__double_as_longlong(e);
             if (eb <= best) best = eb, best_i = (unsigned int)(sl.lo + j);  // indices grow with j
         }
+        STRC(3);
         const double sum = cluster_sum_f64(cluster, &c.xch, 0, block_sum_f64(acc, c.red));
+        STRC(4);
         const double top = 1.0 / sum;
         RowStats st;
         st.has_cut = 0, st.cut_key = Logit<LT>::KEY_MAX, st.cut_idx = 0x7fffffff, st.min_e = 0.0;
@@ -678,8 +706,10 @@ __global__ void __launch_bounds__(ACC_THREADS)
             for (int j = threadIdx.x; j < sl.n; j += ACC_THREADS) fp[j] = (unsigned long long)__double2ull_rn(ecache[j] * scale);
         }
         __syncthreads();
+        STRC(5);
         const unsigned long long tgt = (unsigned long long)(uniforms[(size_t)b * uni_stride] >> 11) << 7;
         token = cluster_radix_draw<LT>(cluster, c, fp, row, sl, tgt, &gap);
+        STRC(10);
         if (token < 0) {
             // the target lies past the last cumulative sum (rounding of the masses): the reference's walk then returns
             // the last entry in rank order - the smallest exp, and of those the largest index.  Rare, so the cluster-wide
@@ -975,6 +1005,13 @@ int32_t accept_check_shaping(tsb_ctx* ctx, const tsb_shaping* sh, bool have_hist
 bool accept_has_penalties(const tsb_shaping& sh) {
     return sh.temperature != 0.0 && (sh.repetition_penalty != 1.0 || sh.presence_penalty != 0.0 || sh.frequency_penalty != 0.0);
 }
+
+#ifdef TSB_SAMPLE_TRACE
+extern "C" __attribute__((visibility("default"))) void tsb_debug_set_sample_trace(void* p) {
+    unsigned long long* q = static_cast<unsigned long long*>(p);
+    cudaMemcpyToSymbol(g_sample_trace, &q, sizeof(q));
+}
+#endif
 
 extern "C" {
 
