@@ -503,10 +503,35 @@ __global__ void __launch_bounds__(MERGE_THREADS)
     float m = -INFINITY, den = 0.f, accv[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) accv[i] = 0.f;
+    // a group has at most MAX_SPLITS / 16 = 4 splits: all their loads are issued together (one round trip to L2
+    // instead of two dependent ones), then folded in split order exactly as a loop over them would
     {
-        for (int c = grp; c < n_splits; c += n_groups) m = fmaxf(m, __ldcg(&part_ml[pi + c]).x);
+        constexpr int PER = 4;
+        float2 ml[PER];
+        float4 va[PER], vb[PER];
+#pragma unroll
+        for (int k = 0; k < PER; k++) {
+            const int c = grp + k * n_groups;
+            ml[k] = make_float2(-INFINITY, 0.f), va[k] = vb[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < n_splits) {
+                ml[k] = __ldcg(&part_ml[pi + c]);
+                const float4* po = reinterpret_cast<const float4*>(part_o + (pi + c) * head_dim + part * 8);
+                va[k] = __ldcg(po), vb[k] = __ldcg(po + 1);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < PER; k++) m = fmaxf(m, ml[k].x);
+        for (int c = grp + PER * n_groups; c < n_splits; c += n_groups) m = fmaxf(m, __ldcg(&part_ml[pi + c]).x);  // never taken at <= 64 splits
         const float mu = (m == -INFINITY) ? 0.f : m;
-        for (int c = grp; c < n_splits; c += n_groups) {
+#pragma unroll
+        for (int k = 0; k < PER; k++)
+            if (grp + k * n_groups < n_splits) {
+                const float wgt = exp2f(ml[k].x - mu);
+                den += ml[k].y * wgt;
+                accv[0] += va[k].x * wgt, accv[1] += va[k].y * wgt, accv[2] += va[k].z * wgt, accv[3] += va[k].w * wgt;
+                accv[4] += vb[k].x * wgt, accv[5] += vb[k].y * wgt, accv[6] += vb[k].z * wgt, accv[7] += vb[k].w * wgt;
+            }
+        for (int c = grp + PER * n_groups; c < n_splits; c += n_groups) {
             const float2 v = __ldcg(&part_ml[pi + c]);
             const float wgt = exp2f(v.x - mu);
             den += v.y * wgt;
