@@ -50,7 +50,8 @@ def test_gemm_matches_oracle(ctx, oracle, kind, rows, cols, tokens):
     assert np.array_equal(got16, oracle.f32_to_f16_bits(got))
 
 
-@pytest.mark.parametrize("rows,cols,tokens", [(128, 256, 24), (256, 2048, 40), (1024, 4096, 64), (384, 1536, 100), (128, 14336, 33)])
+@pytest.mark.parametrize("rows,cols,tokens", [(128, 256, 24), (256, 2048, 40), (1024, 4096, 64), (384, 1536, 100), (128, 14336, 33),
+                                              (19200, 512, 130), (640, 2048, 300)])
 def test_many_token_rows_take_the_tensor_memory_path_and_match_the_oracle(ctx, oracle, rows, cols, tokens):
     """24 token rows and more of a Q4_K matrix whose rows are a multiple of 128 run on tcgen05 with the dequantised
     operand in tensor memory; q*sc is exact in f16 and d, dmin are applied in fp32, so the sums match as closely as

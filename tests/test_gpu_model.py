@@ -579,6 +579,48 @@ def test_lockstep_rounds_over_several_streams_equal_single_stream_runs(rig, orac
     sess.close()
 
 
+def test_penalised_lockstep_rounds_over_streams_equal_each_streams_own_rounds(rig, oracle):
+    """Three streams with different histories in one penalised round sequence: every stream's accepted counts and
+    tokens equal those of the same stream driven alone (its history row on the device is its own, whatever its place
+    in the batch)."""
+    tsb = rig["tsb"]
+    S, K, ROUNDS = 3, 3, 5
+    pen = dict(temperature=1.0, seed=9, repetition_penalty=1.5, presence_penalty=0.7, frequency_penalty=0.2)
+    rc = tsb.run_config(tsb.shaping(**pen), 1 << 20, K, uniform_mode=1)
+    rng = np.random.default_rng(55)
+    prompts = [rng.integers(0, rig["cfg"].vocab, size=n).astype(np.int32) for n in (10, 17, 13)]
+
+    def start(sess, q, p):
+        sess.reset(stream=q)
+        for i, t in enumerate(p[:-1]):
+            sess.produce_prefill(int(t), i, stream=q)
+        sess.produce(int(p[-1]), len(p) - 1, stream=q, want_logits=False)
+        sess.prime_drafter(int(p[-1]), len(p) - 2, stream=q)
+        sess.set_generated(1, stream=q)
+
+    sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], S, K + 1)
+    for q, p in enumerate(prompts):
+        start(sess, q, p)
+    nxt = np.array([int(p[2]) for p in prompts], dtype=np.int32)
+    steps = np.zeros(S, dtype=np.uint64)
+    together = []
+    for _ in range(ROUNDS):
+        acc, toks = sess.round_tokens(rc, nxt, steps)
+        together.append((acc.copy(), toks.copy(), nxt.copy()))
+    sess.close()
+    # a stream's seed is the record's seed plus its index: alone in a one-stream session it sits at index 0
+    for q, p in enumerate(prompts):
+        solo = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, K + 1)
+        start(solo, 0, p)
+        rcq = tsb.run_config(tsb.shaping(**dict(pen, seed=pen["seed"] + q)), 1 << 20, K, uniform_mode=1)
+        n1 = np.array([int(p[2])], dtype=np.int32)
+        s1 = np.zeros(1, dtype=np.uint64)
+        for r in range(ROUNDS):
+            acc, toks = solo.round_tokens(rcq, n1, s1)
+            assert acc[0] == together[r][0][q] and np.array_equal(toks[0], together[r][1][q]) and n1[0] == together[r][2][q], (q, r)
+        solo.close()
+
+
 def test_prefix_reuse_with_a_long_prompt_equals_a_cold_run_on_the_many_row_path(rig, oracle):
     """A session whose largest pass has 24 rows or more prefills in chunks of that size; a later turn that reuses a
     prefix prefills in other chunk sizes.  One matmul path per (session, model) keeps the cache rows - and the
