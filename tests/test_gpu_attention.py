@@ -82,6 +82,38 @@ def test_chain_rows_match_the_oracle(ctx, oracle, hd, nq, nkv, base, rows):
     kv.close()
 
 
+@pytest.mark.parametrize("hd,nq,nkv,rows", [(128, 32, 8, 3), (64, 32, 8, 1)])
+def test_many_streams_take_the_single_split_launch_and_match_the_oracle(ctx, oracle, hd, nq, nkv, rows):
+    """48 streams x 8 kv heads are more CTAs than the device holds, so the context is not cut: the one launch finishes
+    the queries itself (no merge launch).  Streams of different lengths; a sample of them against the oracle."""
+    seqs = 48
+    lens = [150 + 37 * (s % 5) for s in range(seqs)]
+    import turbospark_b200 as tsb
+    page = 64
+    pages_per = (max(lens) + rows) // page + 2
+    kv = tsb.KvCache(ctx, 1, nkv, hd, page, pages_per * seqs + 2, seqs, pages_per)
+    rng = np.random.default_rng(hd + rows)
+    keep = {}
+    for s in range(seqs):
+        n = lens[s] + rows
+        kv.reserve(s, n)
+        k = oracle.f32_to_f16_bits(rng.standard_normal((n, nkv * hd)).astype(np.float32))
+        v = oracle.f32_to_f16_bits(rng.standard_normal((n, nkv * hd)).astype(np.float32))
+        kv.write_rows(s, 0, 0, k, v)
+        if s % 11 == 0 or s == seqs - 1:
+            keep[s] = (k, v)
+    q16 = oracle.f32_to_f16_bits(rng.standard_normal((seqs * rows, nq * hd)).astype(np.float32))
+    entries = [(s, lens[s], m, lens[s] + m, (1 << (m + 1)) - 1) for s in range(seqs) for m in range(rows)]
+    got = _attend(ctx, kv, 0, q16, entries, rows, nq, hd, max(lens) + rows)
+    for s, (k, v) in keep.items():
+        kf, vf = oracle.f16_bits_to_f32(k), oracle.f16_bits_to_f32(v)
+        for m in range(rows):
+            n = lens[s] + m + 1
+            want = oracle.causal_attention(oracle.f16_bits_to_f32(q16[s * rows + m]), kf[:n], vf[:n], hd, nq, nkv, n, 1.0 / np.sqrt(hd))
+            _close(oracle, got[s * rows + m], want)
+    kv.close()
+
+
 def test_tree_rows_match_indexed_attention_and_identity_equals_chain(ctx, oracle):
     # crates/gpu/tests/attention_tree_parity.rs:136-206
     parent = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "tree_parent.json")))["parent"]

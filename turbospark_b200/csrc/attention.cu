@@ -718,8 +718,8 @@ cudaError_t launch_attn_decode_rows(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, i
         const float2* part_ml;
         int n_splits;
         cudaError_t e = launch_attn_partials(ctx, st, kv, layer, q, q_stride, rows_dev, rows, rows_per_seq, n_q_heads, scale, max_len, scratch,
-                                             &part_o, &part_ml, &n_splits);
-        if (e != cudaSuccess) return e;
+                                             &part_o, &part_ml, &n_splits, out, act);
+        if (e != cudaSuccess || n_splits == 1) return e;  // a single split wrote the output itself
         return tsb_launch(ctx, attn_merge_kernel, dim3((unsigned)(rows * n_q_heads)), dim3(MERGE_THREADS), 0, st, true, part_o, part_ml, n_splits,
                           n_q_heads, kv->view.head_dim, out, act);
     }
@@ -797,7 +797,8 @@ extern "C" __attribute__((visibility("default"))) void tsb_debug_set_attn_trace(
 #endif
 cudaError_t launch_attn_partials(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, int layer, const __half* q, int64_t q_stride,
                                  const tsb_row_desc* rows_dev, int rows, int rows_per_seq, int n_q_heads, float scale, int max_len,
-                                 void* scratch, const float** part_o_out, const float2** part_ml_out, int* n_splits_out) {
+                                 void* scratch, const float** part_o_out, const float2** part_ml_out, int* n_splits_out, __half* out_single,
+                                 ActOut act_single) {
     const AttnPlan p = attn_plan_partials(ctx, kv, rows, rows_per_seq, n_q_heads, max_len);
     const int hd = kv->view.head_dim;
     float* part_o = reinterpret_cast<float*>(scratch);
@@ -806,25 +807,25 @@ cudaError_t launch_attn_partials(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, int 
     const float scale_log2e = scale * 1.4426950408889634f;
     dim3 grid((unsigned)p.n_splits, (unsigned)(kv->view.kv_heads * p.n_qtiles), (unsigned)p.groups);
     const size_t smem = attn_smem_bytes(hd, p.mt);
+    // one split: nothing to merge - the CTAs finish their queries themselves and write the output (the same arithmetic
+    // as a merge of one share: weight 2^0, one division)
+    const bool single = p.n_splits == 1;
     const ActOut none{nullptr, nullptr};
+    __half* out = single ? out_single : nullptr;
+    const ActOut act = single ? act_single : none;
+    const int defer = single ? 0 : 1;
+#define TSB_ATTN_LAUNCH(HDV, MTV)                                                                                                          \
+    return launch_attn_t<HDV, MTV>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads, scale_log2e, part_o, \
+                                   part_ml, ATTN_TICKETS, out, act, defer)
     if (hd == 128) {
-        if (p.mt == 4)
-            return launch_attn_t<128, 4>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
-                                         scale_log2e, part_o, part_ml, ATTN_TICKETS, nullptr, none, 1);
-        if (p.mt == 2)
-            return launch_attn_t<128, 2>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
-                                         scale_log2e, part_o, part_ml, ATTN_TICKETS, nullptr, none, 1);
-        return launch_attn_t<128, 1>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
-                                     scale_log2e, part_o, part_ml, ATTN_TICKETS, nullptr, none, 1);
+        if (p.mt == 4) TSB_ATTN_LAUNCH(128, 4);
+        if (p.mt == 2) TSB_ATTN_LAUNCH(128, 2);
+        TSB_ATTN_LAUNCH(128, 1);
     }
-    if (p.mt == 4)
-        return launch_attn_t<64, 4>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
-                                    scale_log2e, part_o, part_ml, ATTN_TICKETS, nullptr, none, 1);
-    if (p.mt == 2)
-        return launch_attn_t<64, 2>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
-                                    scale_log2e, part_o, part_ml, ATTN_TICKETS, nullptr, none, 1);
-    return launch_attn_t<64, 1>(ctx, st, p, grid, smem, kv->view, layer, q, q_stride, rows_dev, rows_per_seq, n_q_heads,
-                                scale_log2e, part_o, part_ml, ATTN_TICKETS, nullptr, none, 1);
+    if (p.mt == 4) TSB_ATTN_LAUNCH(64, 4);
+    if (p.mt == 2) TSB_ATTN_LAUNCH(64, 2);
+    TSB_ATTN_LAUNCH(64, 1);
+#undef TSB_ATTN_LAUNCH
 }
 
 extern "C" {

@@ -20,9 +20,11 @@ cudaError_t launch_attn_decode_rows(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, i
                                     int n_q_heads, float scale, int max_len, void* scratch, int rows_cap);
 // Partials only: every (stream, kv head, query tile, KV chunk) CTA leaves its share (O, and (m, l)) in `scratch`,
 // laid out [rows * n_q_heads][n_splits]; nobody merges (attn_merge_kernel, launched next, does).  Returns where
-// the shares sit and how many splits were cut.
+// the shares sit and how many splits were cut.  When the plan cuts the context into ONE split there is nothing to
+// merge: the launch then writes out_single / act_single itself and the caller skips the merge.
 cudaError_t launch_attn_partials(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, int layer, const __half* q, int64_t q_stride,
                                  const tsb_row_desc* rows_dev, int rows, int rows_per_seq, int n_q_heads, float scale, int max_len,
-                                 void* scratch, const float** part_o_out, const float2** part_ml_out, int* n_splits_out);
+                                 void* scratch, const float** part_o_out, const float2** part_ml_out, int* n_splits_out,
+                                 __half* out_single = nullptr, ActOut act_single = ActOut{nullptr, nullptr});
 cudaError_t launch_rope_store_kv(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, int layer, __half* qkv,
                                  const tsb_row_desc* rows_dev, int rows, int n_q_heads, float theta);
