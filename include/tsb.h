@@ -634,6 +634,10 @@ TSB_API void* tsb_session_stream(tsb_session* s);
  * past the streams' cursors, and return the elapsed device time and the bytes one sequence streams. */
 TSB_API int32_t tsb_session_time_matmuls(tsb_session* s, int32_t rows, int32_t iters, float* out_ms, int64_t* out_bytes_per_iter,
                                          int32_t* out_launches_per_iter);
+/* Measurement aid, the complement of tsb_session_time_matmuls: enqueue every launch of a `rows`-row pass EXCEPT the
+ * layer matmuls (embedding + norm, attention partials and merge of every layer, the head matmul) `iters` times and
+ * return the elapsed device time.  A pass's time minus this is what the layer matmuls take inside the pass. */
+TSB_API int32_t tsb_session_time_pass_rest(tsb_session* s, int32_t rows, int32_t iters, float* out_ms);
 
 #ifdef __cplusplus
 }

@@ -13,10 +13,14 @@ constexpr int GEMM_THREADS = (CONSUMER_WARPS + 1) * 32;
 constexpr int NUM_STAGES = 3;
 // Row stride inside a stage: the payload (<= 8*210 + 30 slack) rounded so that
 // stride = 64 (mod 128) bytes, which makes the 16-byte fragment loads of the
-// eight row groups hit distinct banks.
+// eight row groups hit distinct banks (Q4_K).  The other formats' routines read
+// 4-byte words, the four lanes of a row group side by side: there stride = 16
+// (mod 128) puts the eight row groups of a warp on eight different 16-byte bank
+// groups (with stride = 64 every second row group met the same banks: a
+// four-way conflict on every load).
 __host__ __device__ constexpr int row_stride_for(int unit_bytes) {
     int span = STAGE_UNITS * unit_bytes + 32;
-    int s = (span + 127) / 128 * 128 + 64;
+    int s = (span + 127) / 128 * 128 + (unit_bytes == 144 ? 64 : 16);
     return s;
 }
 
@@ -227,22 +231,33 @@ __device__ __forceinline__ float mxfp4_scale_dev(uint32_t e) {
     return __uint_as_float(e < 2 ? (0x00200000u << e) : ((e - 1u) << 23));
 }
 
-// e2m1 code n = s e1 e0 m  ->  f16 bits (n & 7) << 9 | (n & 8) << 12: exponent field e1e0, top mantissa bit m.  That
-// f16 is the e2m1 value times 2^-14 exactly (a subnormal for the codes below 1.0); the fp32 partial sum is scaled by
-// 2^15 before the block scale (crates/compute/src/quant_gguf_mxfp4.rs:76-78: the table holds 2 * e2m1).
-// v carries four codes in the low nibbles of its bytes (the high nibbles are ignored): elements (0,2) and (1,3).
-__device__ __forceinline__ void e2m1_pairs(uint32_t v, uint32_t& p02, uint32_t& p13) {
-    constexpr uint32_t M = 0x0E000E00u, S = 0x80008000u;
-    p02 = lop3_and_or(v << 9, M, (v << 12) & S);
-    p13 = lop3_and_or(v << 1, M, (v << 4) & S);
+// Four code bytes -> four f16 pairs with the hardware conversion (cvt.rn.f16x2.e2m1x2: the byte's low nibble becomes the
+// low half, its high nibble the high half; the eight magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6 are exact in f16).  Byte i
+// of a block holds elements i (low) and i + 16 (high), so pair i is (element i, element i + 16).
+__device__ __forceinline__ void e2m1_bytes_to_f16x2(uint32_t v, uint32_t& p0, uint32_t& p1, uint32_t& p2, uint32_t& p3) {
+    asm("{\n"
+        ".reg .b8 b0, b1, b2, b3;\n"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n"
+        "}"
+        : "=r"(p0), "=r"(p1), "=r"(p2), "=r"(p3)
+        : "r"(v));
 }
 
 // One 256-column unit = eight 17-byte blocks.  One mma must stay inside one block, because the block scale
-// multiplies its fp32 sum: lane tig takes code bytes 4tig..4tig+3 of every block (elements 4tig..4tig+3 from the low
-// nibbles, 16+4tig.. from the high ones), whose activations are the halves (tig & 1) of two adjacent uint4 slots of
-// the operand; with b unrolled every offset is an immediate: uint4 index ((b/4)*4 + (b&1))*32 + ((b/2)&1)*2 past
-// the lane's base.  Rows start on a 4-byte boundary (checked where the weights come in) and a unit is 136 bytes, so
-// the lane's code word of block b, bytes 17b + 1 + 4tig .. +3, is a funnel shift by an immediate over two aligned words.
+// multiplies its fp32 sum.  Lane tig takes code bytes 4tig..4tig+3 of every block: byte 4tig+i converts to the pair
+// (element 4tig+i, element 16+4tig+i), which is one A register, so the contraction slots of an mma are numbered
+// (2tig, 2tig+1) = the two elements of byte 4tig+2m and (2tig+8, 2tig+9) = those of byte 4tig+2m+1 for mma m = 0, 1
+// of the block.  The B registers follow the same numbering: the operand keeps a token's columns as (x0,x2),(x1,x3)
+// words, elements 4tig.. in one 8-byte slot and 16+4tig.. in the next 16-byte slot, so a byte permute of the two
+// words (low halves for mma 0, high halves for mma 1) pairs column e with column e + 16.  With b unrolled every
+// offset is an immediate: uint4 index ((b/4)*4 + (b&1))*32 + ((b/2)&1)*2 past the lane's base.  Rows start on a
+// 4-byte boundary (checked where the weights come in) and a unit is 136 bytes, so the lane's code word of block b,
+// bytes 17b + 1 + 4tig .. +3, is a funnel shift by an immediate over two aligned words.  The reference's table holds
+// 2 * e2m1 (crates/compute/src/quant_gguf_mxfp4.rs:76-78): the factor 2 goes into the block scale.
 template <int NT>
 __device__ __forceinline__ void mxfp4_unit(const uint8_t* rA, const uint8_t* rB, const ActOperand& act, int nblk,
                                            int unit, int gid, int tig, float (&acc)[NT][4]) {
@@ -261,23 +276,24 @@ __device__ __forceinline__ void mxfp4_unit(const uint8_t* rA, const uint8_t* rB,
             cwA = __funnelshift_r(cwA, wA[(o >> 2) + 1], (o & 3) * 8);
             cwB = __funnelshift_r(cwB, wB[(o >> 2) + 1], (o & 3) * 8);
         }
-        uint32_t alo[4], ahi[4];
-        e2m1_pairs(cwA, alo[0], alo[2]);
-        e2m1_pairs(cwB, alo[1], alo[3]);
-        e2m1_pairs(cwA >> 4, ahi[0], ahi[2]);
-        e2m1_pairs(cwB >> 4, ahi[1], ahi[3]);
+        uint32_t pa[4], pb[4];
+        e2m1_bytes_to_f16x2(cwA, pa[0], pa[1], pa[2], pa[3]);
+        e2m1_bytes_to_f16x2(cwB, pb[0], pb[1], pb[2], pb[3]);
+        const uint32_t a0[4] = {pa[0], pb[0], pa[1], pb[1]}, a1[4] = {pa[2], pb[2], pa[3], pb[3]};
+        const float sA2 = scA + scA, sB2 = scB + scB;
         const int u4 = (((b >> 2) * 4 + (b & 1)) * 32 + ((b >> 1) & 1) * 2) * 2;  // in uint2 units
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
             const uint2 l = __ldg(xb[nt] + u4), hh = __ldg(xb[nt] + u4 + 2);
-            const uint32_t bl[2] = {l.x, l.y}, bh[2] = {hh.x, hh.y};
+            const uint32_t b0[2] = {__byte_perm(l.x, hh.x, 0x5410), __byte_perm(l.y, hh.y, 0x5410)};
+            const uint32_t b1[2] = {__byte_perm(l.x, hh.x, 0x7632), __byte_perm(l.y, hh.y, 0x7632)};
             float c[4];
-            mma_16816_first(c, alo, bl);
-            mma_16816(c, ahi, bh);
-            acc[nt][0] += scA * (c[0] * 32768.f);
-            acc[nt][1] += scA * (c[1] * 32768.f);
-            acc[nt][2] += scB * (c[2] * 32768.f);
-            acc[nt][3] += scB * (c[3] * 32768.f);
+            mma_16816_first(c, a0, b0);
+            mma_16816(c, a1, b1);
+            acc[nt][0] += sA2 * c[0];
+            acc[nt][1] += sA2 * c[1];
+            acc[nt][2] += sB2 * c[2];
+            acc[nt][3] += sB2 * c[3];
         }
     }
 }

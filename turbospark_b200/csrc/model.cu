@@ -657,16 +657,21 @@ static cudaError_t forward_device_moe(tsb_session* s, ModelRt& rt, const int32_t
     return cudaSuccess;
 }
 
+// Which launches of a pass forward_device enqueues: all of them, or - for the two timing entry points - only the
+// layer matmuls / everything but the layer matmuls.
+enum { PASS_ALL = 0, PASS_MATMULS = 1, PASS_REST = 2 };
+
 // One forward pass over `rows` rows (rows_per_seq per stream).  Row descriptors and token ids are
 // already on the device.  Cursors are not touched here.
 static cudaError_t forward_device(tsb_session* s, ModelRt& rt, const int32_t* tokens_dev, int token_stride,
                                   const tsb_row_desc* rows_dev, int rows, int rows_per_seq, int max_len, __half* logits,
-                                  int64_t logits_stride, bool last_rows_only = false, bool matmuls_only = false) {
+                                  int64_t logits_stride, bool last_rows_only = false, int only = PASS_ALL) {
     if (s->replay) return cudaSuccess;  // the captured graph already holds this work
+    const bool matmuls_only = only == PASS_MATMULS, skip_matmuls = only == PASS_REST;
     if (rt.model->n_experts > 0)
         return forward_device_moe(s, rt, tokens_dev, token_stride, rows_dev, rows, rows_per_seq, (max_len + 511) / 512 * 512, logits,
                                   logits_stride, last_rows_only);
-    if (rt.wide_ok && !matmuls_only)
+    if (rt.wide_ok && only == PASS_ALL)
         return forward_device_wide(s, rt, tokens_dev, token_stride, rows_dev, rows, rows_per_seq, (max_len + 511) / 512 * 512, logits,
                                    logits_stride, last_rows_only);
     tsb_ctx* ctx = s->ctx;
@@ -686,13 +691,14 @@ static cudaError_t forward_device(tsb_session* s, ModelRt& rt, const int32_t* to
     const int R = s->n_streams * s->max_rows;
     const int parts = c.d_model / 16;
     auto ss_slot = [&](int i) { return rt.ss + (size_t)i * R * parts; };
-    // (matmuls_only: the measurement aid - the layer matmuls with their real epilogues over whatever the buffers hold)
+    // (PASS_MATMULS / PASS_REST: the measurement aids - only the layer matmuls with their real epilogues, or only the
+    // other launches of the pass (embedding, attention, head), over whatever the buffers hold)
     // embedding: residual stream, layer 0's operand f16(h * g), sum of h^2 (one partial per row), RoPE table
     if (!matmuls_only) FW(launch_embed_norm(ctx, st, m->embed.qtype, m->embed.data, c.vocab, c.d_model, tokens_dev, token_stride, rows, rt.h,
                          m->layers[0].attn_norm, out_d, ss_slot(0), rt.cs, rows_dev, c.head_dim, c.rope_theta));
     for (int L = 0; L < c.n_layers; L++) {
         const LayerW& l = m->layers[L];
-        {   // q|k|v matmul; epilogue: 1/rms, RoPE, q -> buffer, k and v -> cache slots
+        if (!skip_matmuls) {   // q|k|v matmul; epilogue: 1/rms, RoPE, q -> buffer, k and v -> cache slots
             EpiArgs a;
             a.ss_in = ss_slot(2 * L), a.ss_parts = L == 0 ? 1 : parts, a.d_in = c.d_model, a.eps = c.rms_eps;
             a.kv = rt.kv->view, a.layer = L, a.row_desc = rows_dev, a.cs = rt.cs, a.q_out = rt.q;
@@ -707,6 +713,7 @@ static cudaError_t forward_device(tsb_session* s, ModelRt& rt, const int32_t* to
         if (!matmuls_only)
             FW(launch_attn_decode_rows(ctx, st, rt.kv, L, rt.q, (int64_t)c.n_q_heads * c.head_dim, nullptr, out_o, rows_dev, rows,
                                        rows_per_seq, c.n_q_heads, scale, max_len, rt.attn_scratch, s->n_streams * s->max_rows));
+        if (skip_matmuls) continue;
         {   // o_proj; epilogue: residual add, next operand f16(h * g_ffn), partial sums of h^2
             EpiArgs a;
             a.h = rt.h, a.g = l.ffn_norm, a.out = out_d, a.ss_out = ss_slot(2 * L + 1);
@@ -1853,7 +1860,7 @@ int32_t tsb_session_time_matmuls(tsb_session* s, int32_t rows, int32_t iters, fl
     TSB_REQUIRE(ctx, !rt.wide_ok, "the matmul timing covers sessions whose target runs the few-row matmul path (largest pass below %d rows)", WIDE_MIN_ROWS);
     for (int it = -1; it < iters; it++) {  // iteration -1 is a warm-up
         if (it == 0) TSB_CUDA(ctx, cudaEventRecord(s->ev[0], st));
-        TSB_CUDA(ctx, forward_device(s, rt, nullptr, 1, rd, rows, per, max_len, nullptr, 0, false, true));
+        TSB_CUDA(ctx, forward_device(s, rt, nullptr, 1, rd, rows, per, max_len, nullptr, 0, false, PASS_MATMULS));
     }
     for (const LayerW& l : m->layers) {
         bytes += mat_bytes(l.wqkv) + mat_bytes(l.wv) + mat_bytes(l.wo) + mat_bytes(l.wgu) + mat_bytes(l.wdown);
@@ -1869,6 +1876,37 @@ int32_t tsb_session_time_matmuls(tsb_session* s, int32_t rows, int32_t iters, fl
                                               2 * (int64_t)c.ffn + c.ffn + c.d_model) * c.n_layers;
     if (out_bytes_per_iter) *out_bytes_per_iter = bytes + act;
     if (out_launches_per_iter) *out_launches_per_iter = launches;
+    return TSB_OK;
+}
+
+int32_t tsb_session_time_pass_rest(tsb_session* s, int32_t rows, int32_t iters, float* out_ms) {
+    if (!s || !out_ms) return TSB_ERR_INVALID;
+    tsb_ctx* ctx = s->ctx;
+    TSB_REQUIRE(ctx, rows > 0 && rows <= s->n_streams * s->max_rows && iters > 0, "bad rows / iters");
+    if (s->target.model->n_experts > 0) return tsb_fail(ctx, TSB_ERR_UNSUPPORTED, "the pass timing covers dense layers only");
+    DeviceGuard g(ctx);
+    ModelRt& rt = s->target;
+    TSB_REQUIRE(ctx, rows % s->n_streams == 0, "rows must be a whole number of rows per stream");
+    TSB_REQUIRE(ctx, !rt.wide_ok, "the pass timing covers sessions whose target runs the few-row matmul path (largest pass below %d rows)", WIDE_MIN_ROWS);
+    const int per = rows / s->n_streams;
+    std::vector<int32_t> streams(s->n_streams), toks(rows, 0);
+    for (int q = 0; q < s->n_streams; q++) streams[q] = q;
+    const tsb_row_desc* rd;
+    const int32_t* td;
+    int max_len;
+    s->stage_used = 0;
+    int32_t rc = stage_rows(s, rt, streams.data(), s->n_streams, per, nullptr, toks.data(), &rd, &td, &max_len);
+    if (rc) return rc;
+    cudaStream_t st = s->stream;
+    for (int it = -1; it < iters; it++) {  // iteration -1 is a warm-up
+        if (it == 0) TSB_CUDA(ctx, cudaEventRecord(s->ev[0], st));
+        TSB_CUDA(ctx, forward_device(s, rt, td, 1, rd, rows, per, max_len, s->logits_target, rt.model->cfg.vocab, false, PASS_REST));
+    }
+    TSB_CUDA(ctx, cudaEventRecord(s->ev[1], st));
+    rc = tsb_stream_sync(ctx, st);
+    s->stage_used = 0;
+    if (rc) return rc;
+    TSB_CUDA(ctx, cudaEventElapsedTime(out_ms, s->ev[0], s->ev[1]));
     return TSB_OK;
 }
 

@@ -309,6 +309,12 @@ class Session:
                                                       C.byref(ln)))
         return ms.value / iters, by.value, ln.value
 
+    def time_pass_rest(self, rows, iters):
+        """-> ms per sequence of a pass's launches other than the layer matmuls (embedding, attention, head)"""
+        ms = C.c_float()
+        self.ctx.check(lib().tsb_session_time_pass_rest(self.h, C.c_int32(rows), C.c_int32(iters), C.byref(ms)))
+        return ms.value / iters
+
     def kv(self, which=0):
         lib().tsb_session_kv.restype = C.c_void_p
         k = capi.KvCache.__new__(capi.KvCache)
