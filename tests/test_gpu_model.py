@@ -314,6 +314,31 @@ def test_greedy_speculative_equals_greedy_sequential_token_for_token(rig, oracle
     sess.close()
 
 
+def test_the_timing_aids_leave_the_committed_state_alone(rig, oracle):
+    """tsb_session_time_matmuls and tsb_session_time_pass_rest enqueue a pass's launches over rows past the cursor:
+    afterwards the next logits are the bits they would have been without the calls."""
+    tsb = rig["tsb"]
+    rng = np.random.default_rng(5)
+    prompt = rng.integers(0, rig["cfg"].vocab, size=20).astype(np.int32)
+    sess = tsb.Session(rig["ctx"], rig["target"], rig["draft"], 1, 8)
+    for i, t in enumerate(prompt[:-1]):
+        sess.produce(int(t), i)
+    want = None
+    for timed in (False, True):
+        if timed:
+            ms, nbytes, launches = sess.time_matmuls(6, 2)
+            rest = sess.time_pass_rest(6, 2)
+            assert ms > 0 and rest > 0 and nbytes > 0 and launches >= 4 * rig["cfg"].n_layers
+        point = sess.checkpoint()
+        got = sess.produce(int(prompt[-1]), point)
+        sess.rollback_retaining(point, 0)
+        if want is None:
+            want = got
+        else:
+            assert np.array_equal(got, want)
+    sess.close()
+
+
 def test_sampled_round_decisions_match_the_oracle_given_the_devices_logits(rig, oracle):
     tsb = rig["tsb"]
     ctx = rig["ctx"]

@@ -223,6 +223,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, (gemm_ctas_per_sm<QT, NT>()))
 
     bool ok = true, have_inv = !NEEDS_INV;
     uint32_t n = 0, tile_no = 0, group_no = 0;
+    uint32_t stage = 0, phase = 0;  // ring position of block n: n % NUM_STAGES and the parity of n / NUM_STAGES
     for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
         if (item + (int)gridDim.x >= n_items) pdl_launch_dependents();  // last item of this CTA
         int g = item;
@@ -259,8 +260,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, (gemm_ctas_per_sm<QT, NT>()))
             const uint32_t slackB = ALIGNED_ROWS ? 0u : (uint32_t)(reinterpret_cast<uintptr_t>(W + (row0 + gid + 8) * row_bytes) & 15u);
 
             for (int it = 0; it < iters; it++, n++) {
-                const uint32_t s = n % NUM_STAGES;
-                if (ok) ok = mbar_wait(&full[s], (n / NUM_STAGES) & 1, err);
+                const uint32_t s = stage;
+                if (ok) ok = mbar_wait(&full[s], phase, err);
+                if (++stage == NUM_STAGES) stage = 0, phase ^= 1u;
                 if (n == 0) { GTRC(2); }
                 const int nun = min(STAGE_UNITS, units - it * STAGE_UNITS);
                 if (ok && warp < nun) {
