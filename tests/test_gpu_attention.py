@@ -179,6 +179,34 @@ def test_many_streams_with_different_lengths(ctx, oracle):
     kv.close()
 
 
+@pytest.mark.parametrize("rows", [17, 40, 128])
+def test_many_rows_per_stream_take_the_tensor_memory_kernel_and_match_the_oracle(ctx, oracle, rows):
+    """More than 64 queries per (stream, kv head) at head_dim 128 (17 rows x 4 heads and up): chain rows of streams of
+    different lengths, one of them starting at position 0, pages of 32 tokens."""
+    import turbospark_b200 as tsb
+    hd, nq, nkv = 128, 32, 8
+    bases = [0, 70, 513]
+    kv = tsb.KvCache(ctx, 1, nkv, hd, 32, 80, len(bases), 24)
+    rng = np.random.default_rng(rows)
+    ks, vs = [], []
+    for s, b in enumerate(bases):
+        kv.reserve(s, b + rows)
+        k = oracle.f32_to_f16_bits(rng.standard_normal((b + rows, nkv * hd)).astype(np.float32))
+        v = oracle.f32_to_f16_bits(rng.standard_normal((b + rows, nkv * hd)).astype(np.float32))
+        kv.write_rows(s, 0, 0, k, v)
+        ks.append(k), vs.append(v)
+    q16 = oracle.f32_to_f16_bits(rng.standard_normal((len(bases) * rows, nq * hd)).astype(np.float32))
+    entries = [(s, b, m, b + m, (1 << (m + 1)) - 1) for s, b in enumerate(bases) for m in range(rows)]
+    got = _attend(ctx, kv, 0, q16, entries, rows, nq, hd, max(bases) + rows)
+    for s, b in enumerate(bases):
+        kf, vf = oracle.f16_bits_to_f32(ks[s]), oracle.f16_bits_to_f32(vs[s])
+        for m in sorted(set([0, 1, rows // 2, 63 % rows, 64 % rows, rows - 2, rows - 1])):
+            want = oracle.causal_attention(oracle.f16_bits_to_f32(q16[s * rows + m]), kf[:b + m + 1], vf[:b + m + 1], hd, nq,
+                                           nkv, b + m + 1, 1.0 / np.sqrt(hd))
+            _close(oracle, got[s * rows + m], want)
+    kv.close()
+
+
 def test_rope_store_kv_writes_rotated_k_and_plain_v(ctx, oracle):
     import turbospark_b200 as tsb
     hd, nq, nkv = 128, 8, 2

@@ -717,6 +717,14 @@ cudaError_t launch_attn_decode_rows(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, i
         const float* part_o;
         const float2* part_ml;
         int n_splits;
+        if (attn_tc_applicable(kv, rows_per_seq, n_q_heads)) {
+            // many queries per (stream, kv head): the tensor-memory kernel; its shares always go through the merge
+            cudaError_t e = launch_attn_tc_partials(ctx, st, kv, layer, q, q_stride, rows_dev, rows, rows_per_seq, n_q_heads, scale, max_len,
+                                                    scratch, &part_o, &part_ml, &n_splits);
+            if (e != cudaSuccess) return e;
+            return tsb_launch(ctx, attn_merge_kernel, dim3((unsigned)(rows * n_q_heads)), dim3(MERGE_THREADS), 0, st, true, part_o, part_ml,
+                              n_splits, n_q_heads, kv->view.head_dim, out, act);
+        }
         cudaError_t e = launch_attn_partials(ctx, st, kv, layer, q, q_stride, rows_dev, rows, rows_per_seq, n_q_heads, scale, max_len, scratch,
                                              &part_o, &part_ml, &n_splits, out, act);
         if (e != cudaSuccess || n_splits == 1) return e;  // a single split wrote the output itself

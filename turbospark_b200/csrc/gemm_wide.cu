@@ -33,6 +33,7 @@
 #include <mutex>
 
 #include "gemm_quant.cuh"
+#include "tc05.cuh"
 
 namespace {
 
@@ -59,73 +60,6 @@ __device__ __forceinline__ uint32_t hsub2_bits(uint32_t a, uint32_t b) {
     asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
     return r;
 }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// D[tmem_d] (+)= A[tmem_a] * B[smem descriptor]; M = 128, K = 16, f16 inputs, f32 accumulate.  ACC = false overwrites D.
-// The whole MMA warp runs the issue loop in step and only the instruction itself is predicated on `leader`: addresses
-// and descriptors are then warp-uniform values, and the issuing warp - which shares its scheduler with dequantising
-// warps - spends as few instructions per MMA as possible.
-template <bool ACC>
-__device__ __forceinline__ void tc_mma_ts(uint32_t leader, uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc) {
-    asm volatile(
-        "{\n"
-        ".reg .pred p, e;\n"
-        "setp.ne.b32 e, %5, 0;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
-        "}\n" ::"r"(tmem_d),
-        "r"(tmem_a), "l"(desc_b), "r"(idesc), "n"(ACC ? 1 : 0), "r"(leader)
-        : "memory");
-}
-// the same with A from shared memory (a matrix descriptor like B's)
-template <bool ACC>
-__device__ __forceinline__ void tc_mma_ss(uint32_t leader, uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
-    asm volatile(
-        "{\n"
-        ".reg .pred p, e;\n"
-        "setp.ne.b32 e, %5, 0;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-        "}\n" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "n"(ACC ? 1 : 0), "r"(leader)
-        : "memory");
-}
-__device__ __forceinline__ void tc_commit_if(uint32_t leader, uint64_t* bar) {
-    asm volatile(
-        "{\n"
-        ".reg .pred e;\n"
-        "setp.ne.b32 e, %1, 0;\n"
-        "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
-        "}\n" ::"r"(smem_u32(bar)),
-        "r"(leader)
-        : "memory");
-}
-// generic-proxy writes to shared memory become visible to the tensor core's (async-proxy) reads
-__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
-        "%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
-        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
-        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
-        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
-        "r"(r[31])
-        : "memory");
-}
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
-
 #ifdef TSB_WIDE_TRACE
 // development builds: nanosecond stamps of CTA 0 - [blk][0..7] from dequantising warp 0, [blk][8..11] from the MMA thread
 __device__ unsigned long long* g_wide_trace = nullptr;

@@ -155,6 +155,13 @@ int32_t tsb_kv_create(tsb_ctx* ctx, int32_t layers, int32_t kv_heads, int32_t he
         delete kv;
         return tsb_fail(ctx, TSB_ERR_OOM, "K/V pool of %zu bytes: %s", pool_bytes, cudaGetErrorString(e));
     }
+    // rows nobody has written yet are read by kernels that fetch whole pages (and mask them): they must hold finite values
+    e = cudaMemset(v.pool, 0, pool_bytes);
+    if (e != cudaSuccess) {
+        cudaFree(v.pool);
+        delete kv;
+        return tsb_fail(ctx, TSB_ERR_CUDA, "clearing the K/V pool: %s", cudaGetErrorString(e));
+    }
     const size_t pt = (size_t)max_seqs * max_pages_per_seq;
     kv->page_table_host.assign(pt, -1);
     e = cudaMalloc((void**)&kv->page_table_dev, pt * sizeof(int32_t));
