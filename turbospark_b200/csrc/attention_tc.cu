@@ -4,13 +4,14 @@
 // A CTA owns one (stream, kv head, 128-query tile, KV chunk) and walks the chunk in 128-token tiles (one
 // tcgen05.mma costs about a hundred cycles however narrow it is: 94 with both operands in shared memory and N <= 128,
 // 111 with A in tensor memory, 128 = the full rate only at N = 256 - so the tiles are as wide as tensor memory allows):
-//   warps 0-7  two softmax warpgroups; group w takes tiles w, w + 2, ... and keeps its own running (m, l, O), so a CTA
-//              leaves two shares per query.  Thread t of a group is query t of the tile and owns lane t of tensor
-//              memory.  It reads its row of S = Q K^T (tcgen05.ld), applies the tree mask, and writes
-//              P = 2^(S * scale - m) as f16 back to tensor memory over the scores, the A operand of the second product.  O stays in
-//              tensor memory and the tensor core accumulates into it; m is a reference, not the exact maximum: it
-//              moves only when a tile's maximum exceeds it by more than 8 (P then stays below 2^8, far inside f16),
-//              and only then the group rescales its O in place (tcgen05.ld, multiply, tcgen05.st)
+//   warps 0-7  two softmax warpgroups.  Thread t of group w is query t of the tile - it owns lane t of tensor memory -
+//              and takes tokens 64 w .. 64 w + 63 of every tile: it reads its half row of S = Q K^T (tcgen05.ld),
+//              applies the tree mask, meets the other group's half-row maximum through shared memory, and writes
+//              P = 2^(S * scale - m) as f16 back to tensor memory over the tile's scores, the A operand of the second
+//              product.  O stays in tensor memory and the tensor core accumulates into it; m is a reference, not the
+//              exact maximum: it moves only when a tile's maximum exceeds it by more than 8 (P then stays below 2^8,
+//              far inside f16), and only then the groups rescale O in place, 64 columns each (tcgen05.ld, multiply,
+//              tcgen05.st)
 //   warp 8     loader: one thread issues tensor copies (cp.async.bulk.tensor, a 2-D map over the whole K/V pool) of the
 //              tile's K and V rows, page by page, into the 128-byte-swizzled operand layout (rows of 128 bytes = 64
 //              columns, two column blocks per tile), which serves K as a K-major B operand (N = tokens, K = head_dim)
@@ -18,11 +19,11 @@
 //              1.4 us per tile to issue and were the bottleneck; without the swizzle the tensor core fetched its
 //              operands at about a third of the rate.)
 //   warp 9     one thread issues tcgen05.mma: S(i) = Q K_i^T (both operands in shared memory, 8 steps of K = 16) into
-//              group (i & 1)'s 128-column score accumulator, and O += P V_i (A from tensor memory, 8 steps) into that
-//              group's 128-column output accumulator; S(i+2) is issued right behind (P V)(i), so the tensor pipe works
-//              on a group's next scores while the group is busy with the current ones, and the two groups alternate
-// Every group leaves one partial (m, l, O[128]) per query in memory, in the layout of the few-query kernel (a CTA's
-// two groups are two splits), and the same merge launch finishes the rows.  All waits are bounded; a wait that runs
+//              score accumulator i & 1 (128 columns), and O += P V_i (A from tensor memory, 8 steps) into the 128-column
+//              output accumulator; S(i+2) is issued right behind (P V)(i), so the tensor pipe works on the next
+//              tile's scores while the softmax warps are busy with this one's
+// Every CTA leaves one partial (m, l, O[128]) per query in memory, in the layout of the few-query kernel, and the same
+// merge launch finishes the rows.  All waits are bounded; a wait that runs
 // out marks the launch failed, the roles leave their loops, tensor memory is freed and the kernel returns.
 //
 // Masking as in the few-query kernel: positions below the row's `base` are the committed prefix; position base + j is
@@ -46,10 +47,11 @@ constexpr int TC_THREADS = (TC_SOFTMAX_WARPS + TC_LOAD_WARPS + 1) * 32;
 constexpr int TC_Q_BYTES = TC_QM * TC_HD * 2;
 constexpr int TC_TILE_BYTES = TC_TN * TC_HD * 2;  // K or V of one tile
 constexpr int TC_STAGE_BYTES = 2 * TC_TILE_BYTES;
-constexpr int TC_SMEM_BYTES = 1024 + TC_Q_BYTES + TC_STAGES * TC_STAGE_BYTES;
-constexpr int TC_MAX_SPLITS = 32;  // KV chunks; every chunk leaves two shares (one per softmax warpgroup)
-// tensor-memory columns, one set per softmax warpgroup: score accumulator (128 columns; P, 128 f16 = 64 columns, is
-// written over its first half once the scores are in registers), output accumulator (128 columns)
+constexpr int TC_HEADER_BYTES = 3072;  // barriers, then (at 1024) the row maxima the two softmax warpgroups exchange
+constexpr int TC_SMEM_BYTES = TC_HEADER_BYTES + TC_Q_BYTES + TC_STAGES * TC_STAGE_BYTES;  // 227 KB: all there is
+constexpr int TC_MAX_SPLITS = 64;  // KV chunks = shares per query
+// tensor-memory columns: two score accumulators of 128 columns (P, 128 f16 = 64 columns, is written over the first half
+// of a tile's scores once they are in registers) and the output accumulator (128 columns)
 constexpr uint32_t TC_COL_S = 0, TC_COL_PV = 256, TC_TMEM_COLS = 512;
 
 #ifdef TSB_ATTN_TC_TRACE
@@ -62,7 +64,8 @@ __device__ unsigned long long g_tc_trace[64 * 8];
 
 struct TcBars {
     uint64_t kv_full[TC_STAGES], kv_empty[TC_STAGES];
-    uint64_t s_full[2], p_full[2], pv_full[2];
+    uint64_t s_full[2], p_full[2], mx_full[2];
+    uint64_t pv_full, fin_full;
     uint32_t tmem_base, failed;
 };
 
@@ -96,7 +99,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                            float2* __restrict__ part_ml, uint32_t* __restrict__ err) {
     extern __shared__ __align__(1024) uint8_t smem[];
     TcBars* bars = reinterpret_cast<TcBars*>(smem);
-    uint8_t* q_tile = smem + 1024;
+    float* xbuf = reinterpret_cast<float*>(smem + 1024);  // [2 tiles in turn][2 warpgroups][128 queries]
+    uint8_t* q_tile = smem + TC_HEADER_BYTES;
     uint8_t* ring = q_tile + TC_Q_BYTES;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = n_q_heads / kv.kv_heads;
@@ -111,7 +115,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < TC_STAGES; i++) mbar_init(&bars->kv_full[i], 1), mbar_init(&bars->kv_empty[i], 1);
-        for (int i = 0; i < 2; i++) mbar_init(&bars->s_full[i], 1), mbar_init(&bars->p_full[i], 4), mbar_init(&bars->pv_full[i], 1);
+        for (int i = 0; i < 2; i++) mbar_init(&bars->s_full[i], 1), mbar_init(&bars->p_full[i], TC_SOFTMAX_WARPS), mbar_init(&bars->mx_full[i], TC_SOFTMAX_WARPS);
+        mbar_init(&bars->pv_full, 1), mbar_init(&bars->fin_full, TC_SOFTMAX_WARPS);
         bars->failed = 0;
         mbar_fence_init();
     }
@@ -227,14 +232,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             TTRC(t, 1);
             tc_fence_after();
             const uint64_t desc_v = desc_mnmaj | (uint64_t)((smem_u32(ring + st * TC_STAGE_BYTES + TC_TILE_BYTES) >> 4) & 0x3FFFu);
-            const uint32_t d = tmem + TC_COL_PV + (uint32_t)(t & 1) * TC_HD;
-            const uint32_t a = tmem + TC_COL_S + (uint32_t)(t & 1) * TC_TN;  // P sits where the group's scores were
-            if (t < 2) tc_mma_ts<false>(leader, d, a, desc_v, idesc_pv);  // a group's first tile starts its output
+            const uint32_t d = tmem + TC_COL_PV;
+            const uint32_t a = tmem + TC_COL_S + (uint32_t)(t & 1) * TC_TN;  // P sits where the tile's scores were
+            if (t == 0) tc_mma_ts<false>(leader, d, a, desc_v, idesc_pv);  // the first tile starts the output
             else tc_mma_ts<true>(leader, d, a, desc_v, idesc_pv);
 #pragma unroll
             for (int kt = 1; kt < TC_TN / 16; kt++)  // sixteen tokens per step: two 1024-byte token groups = 128 address units
                 tc_mma_ts<true>(leader, d, a + 8 * kt, desc_v + (uint64_t)(128 * kt), idesc_pv);
-            tc_commit_if(leader, &bars->pv_full[t & 1]);
+            tc_commit_if(leader, &bars->pv_full);
             tc_commit_if(leader, &bars->kv_empty[st]);
             TTRC(t, 0);
             if (t + 2 < n_tiles) scores(t + 2);
@@ -242,7 +247,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         }
         if (!ok && lane == 0) bars->failed = 1;
     } else {
-        // ---- softmax warpgroups: thread = query `ql` of the tile = tensor-memory lane ql; group wg takes tiles wg, wg + 2, ...
+        // ---- softmax warpgroups: thread = (query ql of the tile = tensor-memory lane ql, half wg of every tile's 128 tokens).
+        // A failed wait does not leave the loop: the other group's barriers still get their arrivals, nobody is left waiting.
         const int wg = warp >> 2;
         const int ql = threadIdx.x & (TC_QM - 1);
         const int qi = qtile * TC_QM + ql;
@@ -251,78 +257,71 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         uint64_t mask[2] = {0, 0};
         if (valid) mask[0] = rows[row_first + row].mask[0], mask[1] = rows[row_first + row].mask[1];
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-        const uint32_t col_s = tmem + lane_base + TC_COL_S + (uint32_t)wg * TC_TN;
-        const uint32_t col_o = tmem + lane_base + TC_COL_PV + (uint32_t)wg * TC_HD;
-        float m_ref = -INFINITY, l_run = 0.f;
+        const uint32_t col_o = tmem + lane_base + TC_COL_PV + (uint32_t)wg * (TC_HD / 2);  // this group's half of the output columns
+        float m_ref = -INFINITY, l_run = 0.f;  // l_run: over this group's tokens only
         bool ok = true;
-        int done = 0;  // tiles this group has handed to the tensor core
-        for (int t = wg; t < n_tiles; t += 2, done++) {
-            const uint32_t c = (uint32_t)(t >> 1);  // this group's c-th tile
-            if ((warp & 3) == 0) TTRC(t, 3);
-            if (ok) ok = mbar_wait(&bars->s_full[wg], c & 1u, err);
-            if (!ok) break;
-            if ((warp & 3) == 0) TTRC(t, 4);
+        for (int t = 0; t < n_tiles; t++) {
+            const int buf = t & 1;
+            const uint32_t c = (uint32_t)(t >> 1);  // completion index on the barriers of buffer `buf`
+            const uint32_t col_s = tmem + lane_base + TC_COL_S + (uint32_t)buf * TC_TN;
+            if ((warp & 3) == 0) TTRC(t, 3 + wg);
+            if (ok) ok = mbar_wait(&bars->s_full[buf], c & 1u, err);
             tc_fence_after();
-            // pass 1: the row's maximum over the tile's 128 scores; the first 64 stay in registers
-            const int pos0 = t_begin + t * TC_TN;
-            const bool masked = pos0 + TC_TN > base;  // the tile reaches in-flight slots (or the end of the stream)
-            auto load64 = [&](int half, float (&v)[64]) {
+            // this group's 64 scores of the row
+            float s[64];
+            {
                 uint32_t r0[16], r1[16], r2[16], r3[16];
-                tc_ld16(col_s + 64 * half, r0);
-                tc_ld16(col_s + 64 * half + 16, r1);
-                tc_ld16(col_s + 64 * half + 32, r2);
-                tc_ld16(col_s + 64 * half + 48, r3);
+                tc_ld16(col_s + 64 * wg, r0);
+                tc_ld16(col_s + 64 * wg + 16, r1);
+                tc_ld16(col_s + 64 * wg + 32, r2);
+                tc_ld16(col_s + 64 * wg + 48, r3);
                 tc_wait_ld();
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
-                    v[i] = __uint_as_float(r0[i]);
-                    v[16 + i] = __uint_as_float(r1[i]);
-                    v[32 + i] = __uint_as_float(r2[i]);
-                    v[48 + i] = __uint_as_float(r3[i]);
+                    s[i] = __uint_as_float(r0[i]);
+                    s[16 + i] = __uint_as_float(r1[i]);
+                    s[32 + i] = __uint_as_float(r2[i]);
+                    s[48 + i] = __uint_as_float(r3[i]);
                 }
-                if (masked) {
-#pragma unroll
-                    for (int j2 = 0; j2 < 64; j2++) {
-                        const int j = pos0 + 64 * half + j2 - base;
-                        bool vis = j < 0;
-                        if (j >= 0 && j < 128) vis = (mask[j >> 6] >> (j & 63)) & 1ull;
-                        if (!vis) v[j2] = -INFINITY;
-                    }
-                }
-            };
-            auto max64 = [&](const float (&v)[64]) {
-                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-                for (int j2 = 0; j2 < 64; j2 += 4) {
-                    mx4[0] = fmaxf(mx4[0], v[j2]), mx4[1] = fmaxf(mx4[1], v[j2 + 1]);
-                    mx4[2] = fmaxf(mx4[2], v[j2 + 2]), mx4[3] = fmaxf(mx4[3], v[j2 + 3]);
-                }
-                return fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            };
-            float s0[64];
-            load64(0, s0);
-            float mx = max64(s0);
-            {
-                float s1[64];
-                load64(1, s1);
-                mx = fmaxf(mx, max64(s1));
             }
-            if ((warp & 3) == 0) TTRC(t, 5);
-            mx *= scale_log2e;  // the scale is positive
-            // the reference moves only when the tile's maximum is more than 8 above it (or it was -inf)
+            const int pos0 = t_begin + t * TC_TN + 64 * wg;
+            if (pos0 + 64 > base) {  // the half tile reaches in-flight slots (or the end of the stream): mask
+#pragma unroll
+                for (int j2 = 0; j2 < 64; j2++) {
+                    const int j = pos0 + j2 - base;
+                    bool vis = j < 0;
+                    if (j >= 0 && j < 128) vis = (mask[j >> 6] >> (j & 63)) & 1ull;
+                    if (!vis) s[j2] = -INFINITY;
+                }
+            }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int j2 = 0; j2 < 64; j2 += 4) {
+                mx4[0] = fmaxf(mx4[0], s[j2]), mx4[1] = fmaxf(mx4[1], s[j2 + 1]);
+                mx4[2] = fmaxf(mx4[2], s[j2 + 2]), mx4[3] = fmaxf(mx4[3], s[j2 + 3]);
+            }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // the row's maximum over the whole tile: the two groups exchange their halves' maxima.  Arriving also says
+            // that this warp has its scores in registers, so the other group may write P over them.
+            xbuf[(buf * 2 + wg) * TC_QM + ql] = mx;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->mx_full[buf]);
+            if (ok) ok = mbar_wait(&bars->mx_full[buf], c & 1u, err);
+            mx = fmaxf(mx, xbuf[(buf * 2 + (wg ^ 1)) * TC_QM + ql]) * scale_log2e;  // the scale is positive
+            if ((warp & 3) == 0 && wg == 0) TTRC(t, 5);
+            // the reference moves only when the tile's maximum is more than 8 above it (or it was -inf); both groups
+            // take the same decision from the same numbers
             const bool grow = mx > m_ref + 8.f;
             const float m_new = grow ? mx : m_ref;
             const float alpha = grow ? exp2f(m_ref - m_new) : 1.f;  // 0 when nothing was visible before
             const bool rescale = grow && m_ref != -INFINITY;
-            // this group's previous product has to be complete before its P is overwritten or its O touched
-            if (c > 0) {
-                ok = mbar_wait(&bars->pv_full[wg], (c - 1u) & 1u, err);
-                if (!ok) break;
-                tc_fence_after();
-            }
             if (__any_sync(0xffffffffu, rescale)) {
+                // the output so far is rescaled in place, this group's 64 columns of it: the previous tile's product
+                // has to be complete first (completion t - 1 of the barrier; nothing newer can have completed yet)
+                if (ok && t > 0) ok = mbar_wait(&bars->pv_full, (uint32_t)(t - 1) & 1u, err);
+                tc_fence_after();
 #pragma unroll
-                for (int c0 = 0; c0 < TC_HD; c0 += 32) {
+                for (int c0 = 0; c0 < TC_HD / 2; c0 += 32) {
                     uint32_t a16[16], b16[16], w32[32];
                     tc_ld16(col_o + c0, a16);
                     tc_ld16(col_o + c0 + 16, b16);
@@ -335,48 +334,42 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     tc_st32(col_o + c0, w32);
                 }
             }
-            // pass 2: P = 2^(S * scale - m) as f16 pairs over the first half of the score columns (all of which this
-            // thread has read by now: the second half is read again below, after the first half's P is written)
+            // P = 2^(S * scale - m) as f16 pairs: this group's 64 tokens are columns 32 wg .. 32 wg + 31 of the buffer
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
             float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-            auto exp_pack_store = [&](const float (&v)[64], int half) {
-                uint32_t pk[32];
+            uint32_t pk[32];
 #pragma unroll
-                for (int j2 = 0; j2 < 64; j2 += 4) {
-                    const float p0 = ex2_approx(fmaf(v[j2], scale_log2e, -m_use)), p1 = ex2_approx(fmaf(v[j2 + 1], scale_log2e, -m_use));
-                    const float p2 = ex2_approx(fmaf(v[j2 + 2], scale_log2e, -m_use)), p3 = ex2_approx(fmaf(v[j2 + 3], scale_log2e, -m_use));
-                    rs4[0] += p0, rs4[1] += p1, rs4[2] += p2, rs4[3] += p3;
-                    pk[j2 >> 1] = pack_half2_tc(p0, p1);
-                    pk[(j2 >> 1) + 1] = pack_half2_tc(p2, p3);
-                }
-                tc_st32(col_s + 32 * half, pk);
-            };
-            exp_pack_store(s0, 0);
-            {
-                float s1[64];
-                load64(1, s1);
-                exp_pack_store(s1, 1);
+            for (int j2 = 0; j2 < 64; j2 += 4) {
+                const float p0 = ex2_approx(fmaf(s[j2], scale_log2e, -m_use)), p1 = ex2_approx(fmaf(s[j2 + 1], scale_log2e, -m_use));
+                const float p2 = ex2_approx(fmaf(s[j2 + 2], scale_log2e, -m_use)), p3 = ex2_approx(fmaf(s[j2 + 3], scale_log2e, -m_use));
+                rs4[0] += p0, rs4[1] += p1, rs4[2] += p2, rs4[3] += p3;
+                pk[j2 >> 1] = pack_half2_tc(p0, p1);
+                pk[(j2 >> 1) + 1] = pack_half2_tc(p2, p3);
             }
             l_run = l_run * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
             m_ref = m_new;
+            tc_st32(col_s + 32 * wg, pk);
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
-            if ((warp & 3) == 0) TTRC(t, 6);
-            if (lane == 0) mbar_arrive(&bars->p_full[wg]);
+            if ((warp & 3) == 0 && wg == 0) TTRC(t, 6);
+            if (lane == 0) mbar_arrive(&bars->p_full[buf]);
         }
-        // the group's last product, then its share: (m, l, O) of every query
-        if (ok && done > 0) {
-            ok = mbar_wait(&bars->pv_full[wg], (uint32_t)(done - 1) & 1u, err);
-            if (ok) tc_fence_after();
-        }
+        // the last product, the other group's share of the row sum, then the query's share: (m, l, O)
+        if (ok && n_tiles > 0) ok = mbar_wait(&bars->pv_full, (uint32_t)(n_tiles - 1) & 1u, err);
+        tc_fence_after();
+        xbuf[wg * TC_QM + ql] = l_run;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->fin_full);
+        if (ok) ok = mbar_wait(&bars->fin_full, 0u, err);
+        const float l_all = l_run + xbuf[(wg ^ 1) * TC_QM + ql];
         if (!ok) bars->failed = 1;
         pdl_launch_dependents();
-        const size_t pi = ((size_t)(row_first + row) * n_q_heads + head) * (gridDim.x * 2) + blockIdx.x * 2 + wg;
-        float4* po = reinterpret_cast<float4*>(part_o + pi * TC_HD);
-        if (ok && done > 0) {
+        const size_t pi = ((size_t)(row_first + row) * n_q_heads + head) * gridDim.x + blockIdx.x;
+        float4* po = reinterpret_cast<float4*>(part_o + pi * TC_HD + wg * (TC_HD / 2));
+        if (ok && n_tiles > 0) {
 #pragma unroll
-            for (int c0 = 0; c0 < TC_HD; c0 += 32) {
+            for (int c0 = 0; c0 < TC_HD / 2; c0 += 32) {
                 uint32_t a16[16], b16[16];
                 tc_ld16(col_o + c0, a16);
                 tc_ld16(col_o + c0 + 16, b16);
@@ -391,11 +384,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     }
                 }
             }
-            if (valid) part_ml[pi] = make_float2(m_ref, l_run);
-        } else if (ok && valid) {  // the group had no tile: an empty share
+            if (valid && wg == 0) part_ml[pi] = make_float2(m_ref, l_all);
+        } else if (ok && valid) {  // no tile in this chunk: an empty share
 #pragma unroll
-            for (int i = 0; i < TC_HD / 4; i++) po[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            part_ml[pi] = make_float2(-INFINITY, 0.f);
+            for (int i = 0; i < TC_HD / 8; i++) po[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (wg == 0) part_ml[pi] = make_float2(-INFINITY, 0.f);
         }
     }
     tc_fence_before();
@@ -508,9 +501,8 @@ cudaError_t launch_attn_tc_partials(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, i
                                     void* scratch, const float** part_o_out, const float2** part_ml_out, int* n_splits_out) {
     const TcPlan p = attn_tc_plan(ctx, kv, rows, rows_per_seq, n_q_heads, max_len);
     float* part_o = reinterpret_cast<float*>(scratch);
-    const int shares = 2 * p.n_splits;  // one per softmax warpgroup of every chunk CTA
-    float2* part_ml = reinterpret_cast<float2*>(part_o + (size_t)rows * n_q_heads * shares * TC_HD);
-    *part_o_out = part_o, *part_ml_out = part_ml, *n_splits_out = shares;
+    float2* part_ml = reinterpret_cast<float2*>(part_o + (size_t)rows * n_q_heads * p.n_splits * TC_HD);
+    *part_o_out = part_o, *part_ml_out = part_ml, *n_splits_out = p.n_splits;
     const int box_rows = kv->view.page_tokens < TC_TN ? kv->view.page_tokens : TC_TN;
     CUtensorMap kvmap;
     if (cudaError_t e = tc_kv_map(kv->view, box_rows, &kvmap); e != cudaSuccess) return e;

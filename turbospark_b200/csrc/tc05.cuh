@@ -13,8 +13,8 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
 }
 // D[tmem_d] (+)= A[tmem_a] * B[smem descriptor]; M = 128, K = 16, f16 inputs, f32 accumulate.  ACC = false overwrites D.
 // The whole MMA warp runs the issue loop in step and only the instruction itself is predicated on `leader`: addresses
-// and descriptors are then warp-uniform values, and the issuing warp - which shares its scheduler with dequantising
-// warps - spends as few instructions per MMA as possible.
+// and descriptors are then warp-uniform values, and the issuing warp - which shares its scheduler with other warps of
+// the CTA - spends as few instructions per MMA as possible.
 template <bool ACC>
 __device__ __forceinline__ void tc_mma_ts(uint32_t leader, uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc) {
     asm volatile(
