@@ -717,8 +717,9 @@ cudaError_t launch_attn_decode_rows(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, i
         const float* part_o;
         const float2* part_ml;
         int n_splits;
-        if (attn_tc_applicable(kv, rows_per_seq, n_q_heads)) {
-            // many queries per (stream, kv head): the tensor-memory kernel; its shares always go through the merge
+        if (attn_tc_applicable(ctx, kv, rows, rows_per_seq, n_q_heads)) {
+            // many queries per (stream, kv head), or streams enough to fill the device: the tensor-memory kernel; its shares
+            // always go through the merge
             cudaError_t e = launch_attn_tc_partials(ctx, st, kv, layer, q, q_stride, rows_dev, rows, rows_per_seq, n_q_heads, scale, max_len,
                                                     scratch, &part_o, &part_ml, &n_splits);
             if (e != cudaSuccess) return e;

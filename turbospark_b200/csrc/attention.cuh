@@ -26,9 +26,10 @@ cudaError_t launch_attn_partials(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, int 
                                  const tsb_row_desc* rows_dev, int rows, int rows_per_seq, int n_q_heads, float scale, int max_len,
                                  void* scratch, const float** part_o_out, const float2** part_ml_out, int* n_splits_out,
                                  __half* out_single = nullptr, ActOut act_single = ActOut{nullptr, nullptr});
-// The tensor-memory (tcgen05) kernel for passes with more than 64 queries per (stream, kv head) at head_dim 128: the same
-// partials in the same layout; the merge launch always follows (also after a single split).
-bool attn_tc_applicable(const tsb_kv* kv, int rows_per_seq, int n_q_heads);
+// The tensor-memory (tcgen05) kernel at head_dim 128: for passes with more than 64 queries per (stream, kv head), and for
+// passes whose streams x kv heads alone give every SM a CTA.  The same partials in the same layout; the merge launch always
+// follows (also after a single split).
+bool attn_tc_applicable(const tsb_ctx* ctx, const tsb_kv* kv, int rows, int rows_per_seq, int n_q_heads);
 cudaError_t launch_attn_tc_partials(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, int layer, const __half* q, int64_t q_stride,
                                     const tsb_row_desc* rows_dev, int rows, int rows_per_seq, int n_q_heads, float scale, int max_len,
                                     void* scratch, const float** part_o_out, const float2** part_ml_out, int* n_splits_out);

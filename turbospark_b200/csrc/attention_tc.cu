@@ -481,7 +481,7 @@ cudaError_t tc_kv_map(const KvView& v, int box_rows, CUtensorMap* out) {
 
 }  // namespace
 
-bool attn_tc_applicable(const tsb_kv* kv, int rows_per_seq, int n_q_heads) {
+bool attn_tc_applicable(const tsb_ctx* ctx, const tsb_kv* kv, int rows, int rows_per_seq, int n_q_heads) {
     static int enabled = -1, min_queries = 65;  // TSB_ATTN_TC=0 keeps every pass on the mma.sync kernel (experiments)
     if (enabled < 0) {
         const char* env = getenv("TSB_ATTN_TC");
@@ -493,7 +493,11 @@ bool attn_tc_applicable(const tsb_kv* kv, int rows_per_seq, int n_q_heads) {
     // the tensor copies take whole boxes of a page: pages of 8, 16, ... token rows, all rows of the pool within 32-bit coordinates
     const int pt = kv->view.page_tokens;
     if (pt < 8 || (pt & (pt - 1)) != 0 || (int64_t)kv->view.layers * 2 * kv->view.num_pages * pt >= (int64_t)1 << 31) return false;
-    return rows_per_seq * (n_q_heads / kv->view.kv_heads) >= min_queries;
+    if (rows_per_seq * (n_q_heads / kv->view.kv_heads) >= min_queries) return true;
+    // few queries per stream but many streams: when streams x kv heads fill the device, a CTA per SM that streams its K/V
+    // through tensor copies is the faster one (64 streams x 6 rows at context 4096: 262 vs 316 us per layer); below
+    // that the few-query kernel wins, whose smaller CTAs overlap the neighbouring matmuls' prologues
+    return rows_per_seq > 0 && (rows / rows_per_seq) * kv->view.kv_heads >= ctx->sm_count;
 }
 
 cudaError_t launch_attn_tc_partials(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, int layer, const __half* q, int64_t q_stride,
