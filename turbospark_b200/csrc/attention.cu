@@ -577,6 +577,61 @@ __global__ void __launch_bounds__(MERGE_THREADS)
     if (act.xp) act_store8(o, act.xp, act.xs, row, active ? e0 : 0, (n_q_heads * head_dim) >> 8, active);
 }
 
+// The same merge for at most four splits: a thread is (query row x head, eight-column part) and folds the query's
+// shares itself, in split order, all loads in one round trip - no shared memory, no barrier, sixteen (head_dim 128) or
+// thirty-two (64) queries per CTA.  Passes over many rows cut the context into few chunks and have tens of thousands of
+// queries to finish; one CTA per query, most of whose threads have no split to fold, took 40 us there.
+template <int HD>
+__global__ void __launch_bounds__(MERGE_THREADS)
+    attn_merge_few_kernel(const float* __restrict__ part_o, const float2* __restrict__ part_ml, int n_splits, int n_items, int n_q_heads,
+                          __half* __restrict__ out, ActOut act) {
+    constexpr int LPI = HD / 8;
+    const int item = blockIdx.x * (MERGE_THREADS / LPI) + threadIdx.x / LPI, part = threadIdx.x % LPI;
+    const bool active = item < n_items;
+    pdl_wait();
+    float2 ml[4];
+    float4 va[4], vb[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        ml[k] = make_float2(-INFINITY, 0.f), va[k] = vb[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (active && k < n_splits) {
+            const size_t pi = (size_t)item * n_splits + k;
+            ml[k] = __ldcg(&part_ml[pi]);
+            const float4* po = reinterpret_cast<const float4*>(part_o + pi * HD + part * 8);
+            va[k] = __ldcg(po), vb[k] = __ldcg(po + 1);
+        }
+    }
+    pdl_launch_dependents();
+    float m = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < 4; k++) m = fmaxf(m, ml[k].x);
+    const float mu = (m == -INFINITY) ? 0.f : m;
+    float den = 0.f, o[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) o[i] = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; k++)
+        if (k < n_splits) {
+            const float wgt = exp2f(ml[k].x - mu);
+            den += ml[k].y * wgt;
+            o[0] += va[k].x * wgt, o[1] += va[k].y * wgt, o[2] += va[k].z * wgt, o[3] += va[k].w * wgt;
+            o[4] += vb[k].x * wgt, o[5] += vb[k].y * wgt, o[6] += vb[k].z * wgt, o[7] += vb[k].w * wgt;
+        }
+    const float inv = den > 0.f ? 1.0f / den : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) o[i] *= inv;
+    const int row = active ? item / n_q_heads : 0, head = active ? item % n_q_heads : 0;
+    const int e0 = head * HD + part * 8;
+    if (out && active) {
+        uint4 pk;
+        __half* pp = reinterpret_cast<__half*>(&pk);
+#pragma unroll
+        for (int i = 0; i < 8; i++) pp[i] = __float2half_rn(o[i]);
+        *reinterpret_cast<uint4*>(out + (size_t)row * n_q_heads * HD + e0) = pk;
+    }
+    if (act.xp) act_store8(o, act.xp, act.xs, row, e0, (n_q_heads * HD) >> 8, active);
+}
+
 }  // namespace
 
 // Dynamic shared memory of a CTA: the K/V ring, or - four m-tiles - the larger area the warps' partials are merged in.
@@ -709,6 +764,21 @@ static bool attn_split_merge_mode() {
     return mode == 1;
 }
 
+// The merge launch that follows a partials launch: the per-query kernel, or - few splits - the many-queries-per-CTA one.
+static cudaError_t launch_attn_merge(tsb_ctx* ctx, cudaStream_t st, const float* part_o, const float2* part_ml, int n_splits, int rows,
+                                     int n_q_heads, int head_dim, __half* out, ActOut act) {
+    const int items = rows * n_q_heads;
+    if (n_splits <= 4 && (head_dim == 128 || head_dim == 64)) {
+        const int per_cta = MERGE_THREADS / (head_dim / 8);
+        const dim3 grid((unsigned)((items + per_cta - 1) / per_cta));
+        if (head_dim == 128)
+            return tsb_launch(ctx, attn_merge_few_kernel<128>, grid, dim3(MERGE_THREADS), 0, st, true, part_o, part_ml, n_splits, items, n_q_heads, out, act);
+        return tsb_launch(ctx, attn_merge_few_kernel<64>, grid, dim3(MERGE_THREADS), 0, st, true, part_o, part_ml, n_splits, items, n_q_heads, out, act);
+    }
+    return tsb_launch(ctx, attn_merge_kernel, dim3((unsigned)items), dim3(MERGE_THREADS), 0, st, true, part_o, part_ml, n_splits, n_q_heads,
+                      head_dim, out, act);
+}
+
 cudaError_t launch_attn_decode_rows(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, int layer, const __half* q, int64_t q_stride,
                                     __half* out, ActOut act, const tsb_row_desc* rows_dev, int rows, int rows_per_seq,
                                     int n_q_heads, float scale, int max_len, void* scratch, int rows_cap) {
@@ -723,14 +793,12 @@ cudaError_t launch_attn_decode_rows(tsb_ctx* ctx, cudaStream_t st, tsb_kv* kv, i
             cudaError_t e = launch_attn_tc_partials(ctx, st, kv, layer, q, q_stride, rows_dev, rows, rows_per_seq, n_q_heads, scale, max_len,
                                                     scratch, &part_o, &part_ml, &n_splits);
             if (e != cudaSuccess) return e;
-            return tsb_launch(ctx, attn_merge_kernel, dim3((unsigned)(rows * n_q_heads)), dim3(MERGE_THREADS), 0, st, true, part_o, part_ml,
-                              n_splits, n_q_heads, kv->view.head_dim, out, act);
+            return launch_attn_merge(ctx, st, part_o, part_ml, n_splits, rows, n_q_heads, kv->view.head_dim, out, act);
         }
         cudaError_t e = launch_attn_partials(ctx, st, kv, layer, q, q_stride, rows_dev, rows, rows_per_seq, n_q_heads, scale, max_len, scratch,
                                              &part_o, &part_ml, &n_splits, out, act);
         if (e != cudaSuccess || n_splits == 1) return e;  // a single split wrote the output itself
-        return tsb_launch(ctx, attn_merge_kernel, dim3((unsigned)(rows * n_q_heads)), dim3(MERGE_THREADS), 0, st, true, part_o, part_ml, n_splits,
-                          n_q_heads, kv->view.head_dim, out, act);
+        return launch_attn_merge(ctx, st, part_o, part_ml, n_splits, rows, n_q_heads, kv->view.head_dim, out, act);
     }
     const AttnPlan p = attn_plan(ctx, kv, rows, rows_per_seq, n_q_heads, max_len);
     const int hd = kv->view.head_dim;
