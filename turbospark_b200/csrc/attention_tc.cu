@@ -94,8 +94,8 @@ __device__ __forceinline__ uint32_t sw128_off(int r, int c, int rows) {
 }
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
-    attn_tc_partial_kernel(const __grid_constant__ CUtensorMap kvmap, int box_rows, KvView kv, int layer, const __half* __restrict__ q, int64_t q_stride, const tsb_row_desc* __restrict__ rows,
-                           int rows_per_seq, int n_q_heads, float scale_log2e, int chunk, float* __restrict__ part_o,
+    attn_tc_partial_kernel(const __grid_constant__ CUtensorMap kvmap, int box_rows, KvView kv, int layer, const __half* __restrict__ q,
+                           int64_t q_stride, const tsb_row_desc* __restrict__ rows, int rows_per_seq, int n_q_heads, float scale_log2e, int chunk, float* __restrict__ part_o,
                            float2* __restrict__ part_ml, uint32_t* __restrict__ err) {
     extern __shared__ __align__(1024) uint8_t smem[];
     TcBars* bars = reinterpret_cast<TcBars*>(smem);
@@ -192,14 +192,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     } else if (warp == TC_SOFTMAX_WARPS + TC_LOAD_WARPS) {
         // ---- MMA issue: the warp walks the tiles together, lane 0 issues
         const uint32_t leader = lane == 0 ? 1u : 0u;
-        // instruction descriptors: f32 accumulate, f16 A and B, M = 128; scores N = 64, both operands K-major;
-        // P V N = 128 with B (V) MN-major
+        // instruction descriptors: f32 accumulate, f16 A and B, M = 128; scores N = 128 tokens, both operands K-major;
+        // P V N = 128 columns with B (V) MN-major
         const uint32_t idesc_s = (1u << 4) | ((uint32_t)(TC_TN >> 3) << 17) | ((uint32_t)(TC_QM >> 4) << 24);
         const uint32_t idesc_pv = (1u << 4) | (1u << 16) | ((uint32_t)(TC_HD >> 3) << 17) | ((uint32_t)(TC_QM >> 4) << 24);
         // shared-memory matrix descriptors without the start address (version 1, 128-byte swizzle).  K-major (Q, K):
         // eight-row groups 1024 bytes apart (stride byte offset), the leading offset is not used; a K = 16 step moves
         // the start address by 32 bytes inside the 64-element block, the second block starts rows * 128 bytes later.
-        // MN-major (V): eight-token groups 1024 bytes apart (stride), the two 64-column blocks 8192 bytes apart (leading)
+        // MN-major (V): eight-token groups 1024 bytes apart (stride), the two 64-column blocks a block's size apart (leading)
         constexpr uint64_t SW128 = 2ull << 61;
         const uint64_t desc_kmaj = ((uint64_t)1u << 16) | ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | SW128;
         const uint64_t desc_mnmaj = ((uint64_t)((uint32_t)(TC_TN * 128) >> 4) << 16) | ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | SW128;
