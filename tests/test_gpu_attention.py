@@ -83,9 +83,10 @@ def test_chain_rows_match_the_oracle(ctx, oracle, hd, nq, nkv, base, rows):
 
 
 @pytest.mark.parametrize("hd,nq,nkv,rows", [(128, 32, 8, 3), (64, 32, 8, 1)])
-def test_many_streams_take_the_single_split_launch_and_match_the_oracle(ctx, oracle, hd, nq, nkv, rows):
-    """48 streams x 8 kv heads are more CTAs than the device holds, so the context is not cut: the one launch finishes
-    the queries itself (no merge launch).  Streams of different lengths; a sample of them against the oracle."""
+def test_many_streams_fill_the_device_and_match_the_oracle(ctx, oracle, hd, nq, nkv, rows):
+    """48 streams x 8 kv heads are more CTAs than the device holds.  At head_dim 64 the context is then not cut and the
+    one launch finishes the queries itself (no merge launch); at head_dim 128 such a pass takes the tensor-memory kernel.
+    Streams of different lengths; a sample of them against the oracle."""
     seqs = 48
     lens = [150 + 37 * (s % 5) for s in range(seqs)]
     import turbospark_b200 as tsb
