@@ -696,7 +696,7 @@ AttnPlan attn_plan(const tsb_ctx* ctx, const tsb_kv* kv, int rows, int rows_per_
     const int base_ctas = p.groups * kv->view.kv_heads * p.n_qtiles;
     // one wave: as many chunks per (stream, kv head, query tile) as the device can hold at once, in clusters of
     // up to four CTAs (larger clusters leave SMs of a GPC unused)
-    int cand_splits[5] = {1, 0, 0, 0, 0}, cand_clusters[5] = {1, 0, 0, 0, 0}, most = 1;  // for cluster sizes 1, 2, 4, 8, 16
+    int cand_splits[5] = {1, 0, 0, 0, 0}, most = 1;  // for cluster sizes 1, 2, 4, 8, 16
     static int per_sm = 0, max_cs_log2 = -1;  // TSB_ATTN_CTAS_PER_SM, TSB_ATTN_MAX_CLUSTER override (experiments)
     if (!per_sm) {
         const char* env = getenv("TSB_ATTN_CTAS_PER_SM");
@@ -719,7 +719,6 @@ AttnPlan attn_plan(const tsb_ctx* ctx, const tsb_kv* kv, int rows, int rows_per_
         int splits = clusters_per * cs;
         if (splits > tiles_total) splits = (tiles_total / cs) * cs;
         cand_splits[i] = splits;  // 0 when a cluster would be longer than the context
-        cand_clusters[i] = splits / cs;
         if (splits > most) most = splits;
     }
     // the largest cluster that keeps at least 4/5 of the parallelism: fewer shares travel through memory
